@@ -1,0 +1,67 @@
+// Shared helpers of the sm_100a kernels: status codes, typed loads and stores,
+// warp and block reductions.  Every entry point is extern "C", takes raw device
+// pointers plus sizes and a stream, checks its arguments on the host and returns
+// a status the Python side turns into an exception; it never allocates.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include <math.h>
+
+#define AIRUN_OK 0
+#define AIRUN_ERR_ARG 1000        // a size or pointer the kernel refuses
+#define AIRUN_ERR_UNSUPPORTED 1001
+
+// Bits of the device-side error word kernels set instead of trapping.
+#define AIRUN_DEV_BAD_PAGE 1      // a block-table entry outside [0, num_pages)
+#define AIRUN_DEV_BAD_REQ 2       // a token naming a request outside the batch
+#define AIRUN_DEV_BAD_TOKEN 4     // a token id outside the vocabulary
+#define AIRUN_DEV_TIMEOUT 8       // a bounded wait ran out
+
+#define AIRUN_DT_F32 0
+#define AIRUN_DT_BF16 1
+
+#define AIRUN_EXPORT extern "C" __attribute__((visibility("default")))
+
+static inline int airun_launch_status() {
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? AIRUN_OK : (int)e;
+}
+
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over the block; every thread gets the result.  `red` holds 33 floats.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarp = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();               // `red` may still be read from an earlier call
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < nwarp ? red[lane] : 0.0f;
+        t = warp_sum(t);
+        if (lane == 0) red[32] = t;
+    }
+    __syncthreads();
+    return red[32];
+}
+
+static inline int ceil_div_i(long long a, long long b) { return (int)((a + b - 1) / b); }

@@ -1,0 +1,150 @@
+// Everything between the q/k/v projection and attention, in one launch:
+// per-head RMSNorm of q and k, rotary position encoding of both, q out in the
+// attention kernel's input type, and k and v into their cache pages.
+//
+// Formulas as the reference computes them
+// (crates/airun-cuda/kernels/ops.cu:422-501, crates/airun-cuda/kernels/airun.cuh:147-163):
+//   per head row h of head_dim values: h = h * rsqrt(sum(h^2)/head_dim + eps) * w
+//   (one weight vector shared by all heads, same eps as the layer norms, before
+//   the rotation; v is not normed);
+//   rotation (NeoX pairing): pair i couples dims i and i + r/2,
+//   theta = pos * inv_freq[i],  x'_i = x_i cos - x_{i+r/2} sin,
+//   x'_{i+r/2} = x_i sin + x_{i+r/2} cos; dims >= r are left alone; the accurate
+//   sincosf is used on purpose (angles reach thousands of radians).
+// inv_freq[i] = theta_base^(-2i/r) is computed on the host in double precision
+// and rounded once to float32, so the device and a plain implementation multiply
+// the position by the very same constant.
+//
+// Cache layout of one layer: [num_pages][2 (K,V)][n_kv_heads][page_size][head_dim];
+// the token at position p of request r lives in page block_table[r][p / page_size],
+// row p % page_size.  A block-table entry outside [0, num_pages) sets an error
+// bit and the store is skipped; nothing traps.
+#include "common.cuh"
+
+#define ROPE_NONE 0
+#define ROPE_NEOX 1
+#define MAX_PER_LANE 8   // head_dim <= 256
+
+template <typename TQ, typename TKV>
+__global__ __launch_bounds__(256) void qkv_post_kernel(
+    const float* __restrict__ qkv, long long ld_qkv,
+    TQ* __restrict__ q_out,
+    const float* __restrict__ q_norm_w, const float* __restrict__ k_norm_w, float eps,
+    const int32_t* __restrict__ positions, const int32_t* __restrict__ req_of_token,
+    int rope_kind, int rotary_dim, const float* __restrict__ inv_freq,
+    TKV* __restrict__ pool, const int32_t* __restrict__ block_table, int max_blocks,
+    int num_reqs, int num_pages, int page_size, int do_store, int kv_from_qkv,
+    int nh, int nkv, int hd, int* __restrict__ err) {
+    extern __shared__ float smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nwarp = blockDim.x >> 5;
+    float* row = smem + (size_t)warp * hd;
+    const int t = blockIdx.x;
+    const int pos = positions[t];
+    const int req = req_of_token[t];
+    const int total_heads = kv_from_qkv ? nh + 2 * nkv : nh;
+    const int half = rotary_dim / 2;
+
+    for (int h = warp; h < total_heads; h += nwarp) {
+        const bool is_q = h < nh;
+        const bool is_k = !is_q && h < nh + nkv;
+        const float* src = qkv + (size_t)t * ld_qkv + (size_t)h * hd;
+        float x[MAX_PER_LANE];
+        float ss = 0.0f;
+#pragma unroll
+        for (int i = 0; i < MAX_PER_LANE; ++i) {
+            const int d = lane + i * 32;
+            x[i] = d < hd ? src[d] : 0.0f;
+            ss = fmaf(x[i], x[i], ss);
+        }
+        const float* w = is_q ? q_norm_w : (is_k ? k_norm_w : nullptr);
+        if (w) {
+            ss = warp_sum(ss);
+            const float inv = rsqrtf(ss / (float)hd + eps);
+#pragma unroll
+            for (int i = 0; i < MAX_PER_LANE; ++i) {
+                const int d = lane + i * 32;
+                if (d < hd) x[i] = x[i] * inv * w[d];
+            }
+        }
+        if (rope_kind == ROPE_NEOX && (is_q || is_k)) {
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < MAX_PER_LANE; ++i) {
+                const int d = lane + i * 32;
+                if (d < hd) row[d] = x[i];
+            }
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < MAX_PER_LANE; ++i) {
+                const int d = lane + i * 32;
+                if (d < rotary_dim && d < hd) {
+                    const bool first = d < half;
+                    const int pair = first ? d : d - half;
+                    const int other = first ? d + half : d - half;
+                    float s, c;
+                    sincosf((float)pos * inv_freq[pair], &s, &c);
+                    const float x0 = first ? row[d] : row[other];
+                    const float x1 = first ? row[other] : row[d];
+                    x[i] = first ? x0 * c - x1 * s : x0 * s + x1 * c;
+                }
+            }
+        }
+        if (is_q) {
+            TQ* dst = q_out + ((size_t)t * nh + h) * hd;
+#pragma unroll
+            for (int i = 0; i < MAX_PER_LANE; ++i) {
+                const int d = lane + i * 32;
+                if (d < hd) dst[d] = from_f32<TQ>(x[i]);
+            }
+        } else if (do_store && req >= 0 && pos >= 0) {
+            if (req >= num_reqs) {
+                if (lane == 0) atomicOr(err, AIRUN_DEV_BAD_REQ);
+                continue;
+            }
+            const int blk = pos / page_size;
+            const int page = blk < max_blocks ? block_table[(size_t)req * max_blocks + blk] : -1;
+            if (page < 0 || page >= num_pages) {
+                if (lane == 0) atomicOr(err, AIRUN_DEV_BAD_PAGE);
+                continue;
+            }
+            const int kvh = is_k ? h - nh : h - nh - nkv;
+            TKV* dst = pool + ((((size_t)page * 2 + (is_k ? 0 : 1)) * nkv + kvh) * page_size
+                               + (pos % page_size)) * hd;
+#pragma unroll
+            for (int i = 0; i < MAX_PER_LANE; ++i) {
+                const int d = lane + i * 32;
+                if (d < hd) dst[d] = from_f32<TKV>(x[i]);
+            }
+        }
+    }
+}
+
+// kv_from_qkv = 0: the row holds q only (the layer reads another layer's cache).
+AIRUN_EXPORT int airun_qkv_post(
+    const float* qkv, long long ld_qkv, void* q_out, int q_dtype,
+    const float* q_norm_w, const float* k_norm_w, float eps,
+    const int32_t* positions, const int32_t* req_of_token, int T,
+    int rope_kind, int rotary_dim, const float* inv_freq,
+    void* pool, int kv_dtype, const int32_t* block_table, int max_blocks, int num_reqs,
+    int num_pages, int page_size, int do_store, int kv_from_qkv,
+    int nh, int nkv, int hd, int* err, cudaStream_t stream) {
+    if (T < 0 || nh <= 0 || nkv <= 0 || hd <= 0 || hd > 32 * MAX_PER_LANE) return AIRUN_ERR_ARG;
+    if (rope_kind != ROPE_NONE && (rotary_dim <= 0 || rotary_dim > hd || rotary_dim % 2 != 0 || !inv_freq))
+        return AIRUN_ERR_ARG;
+    if (do_store && (page_size <= 0 || num_pages <= 0 || !pool || !block_table || !err)) return AIRUN_ERR_ARG;
+    if (q_dtype != kv_dtype) return AIRUN_ERR_UNSUPPORTED;
+    if (T == 0) return AIRUN_OK;
+    const int heads = kv_from_qkv ? nh + 2 * nkv : nh;
+    int warps = heads < 8 ? heads : 8;
+    const size_t smem = (size_t)warps * hd * sizeof(float);
+#define LAUNCH(TQ, TKV) \
+    qkv_post_kernel<TQ, TKV><<<T, warps * 32, smem, stream>>>(qkv, ld_qkv, (TQ*)q_out, q_norm_w, k_norm_w, eps, \
+        positions, req_of_token, rope_kind, rotary_dim, inv_freq, (TKV*)pool, block_table, max_blocks, num_reqs, \
+        num_pages, page_size, do_store, kv_from_qkv, nh, nkv, hd, err)
+    if (q_dtype == AIRUN_DT_F32) LAUNCH(float, float);
+    else if (q_dtype == AIRUN_DT_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
+    else return AIRUN_ERR_UNSUPPORTED;
+#undef LAUNCH
+    return airun_launch_status();
+}

@@ -1,0 +1,251 @@
+"""The engine: a model folder (or a configuration and a seed) in, tokens out.
+
+``Engine`` owns the model, the cache manager with its device storage, the step
+function and a scheduler, and offers ``generate`` (token ids in, token ids
+out), ``add_request`` / ``run_step`` for callers that drive the loop
+themselves, and ``runner.step`` for raw logits.  The reference's Rust API is
+``loader::load`` followed by ``Runtime::generate``
+(crates/airun-core/src/loader.rs:216, crates/airun-core/src/runtime.rs:4903-5089);
+its per-run statistics (prompt / generated counts, prefill and decode
+milliseconds, stop reason) are ``GenerationStats`` (runtime.rs:5130-5165).
+"""
+from __future__ import annotations
+
+import itertools
+import time
+from dataclasses import dataclass, field
+from typing import Dict, Hashable, List, Optional, Sequence, Union
+
+import numpy as np
+import torch
+
+from ..cache.manager import CacheManager, CacheStorage
+from ..config.base import ModelConfig, architecture_name, lookup_architecture, read_config_json
+from ..kernels import ops
+from ..sampling.sampler import SamplingParams
+from ..weights.loader import open_model_folder
+from .scheduler import FinishReason, Plan, Request, Scheduler
+from .step import StepEntry, StepRunner
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
+           torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
+
+
+@dataclass
+class EngineOptions:
+    dtype: Union[str, torch.dtype] = "bfloat16"
+    device: str = "cuda:0"
+    page_size: int = 16
+    num_pages: Optional[int] = None          # pages per cache group; None: from cache_tokens
+    cache_tokens: Optional[int] = None       # tokens the cache holds; None: from memory_fraction
+    memory_fraction: float = 0.85            # of the memory free after loading the weights
+    max_batch_tokens: int = 2048             # token budget of one step (the reference's -b/--batch-size)
+    max_requests: int = 64                   # requests live at a time (the reference's --parallel slots)
+    max_context: Optional[int] = None        # longest request (the reference's -c/--ctx-size)
+
+
+@dataclass
+class GenerationStats:
+    prompt_tokens: int = 0
+    generated_tokens: int = 0
+    prefill_ms: float = 0.0
+    decode_ms: float = 0.0
+    steps: int = 0
+    preemptions: int = 0
+
+    @property
+    def prefill_tps(self) -> float:
+        return self.prompt_tokens / (self.prefill_ms / 1e3) if self.prefill_ms > 0 else 0.0
+
+    @property
+    def decode_tps(self) -> float:
+        return self.generated_tokens / (self.decode_ms / 1e3) if self.decode_ms > 0 else 0.0
+
+
+@dataclass
+class GenerationResult:
+    token_ids: List[int]
+    finish_reason: str
+    prompt_tokens: int
+
+
+class Engine:
+    def __init__(self, config: ModelConfig, model, options: EngineOptions):
+        self.config, self.model, self.options = config, model, options
+        self.device = model.device
+        self.dtype = model.dtype
+        o = options
+        specs, cache_from = model.cache_specs()
+        ps = o.page_size
+        if o.num_pages is not None:
+            num_pages = int(o.num_pages)
+        else:
+            tokens = o.cache_tokens if o.cache_tokens is not None else self._tokens_that_fit(specs, cache_from, o)
+            num_pages = max(1, (int(tokens) + ps - 1) // ps)
+        self.max_context = int(o.max_context or min(num_pages * ps,
+                                                    max(getattr(config, "max_position_embeddings", 4096), 1)))
+        self.max_context = min(self.max_context, num_pages * ps)
+        self.manager = CacheManager(specs, cache_from, ps, num_pages, o.max_requests)
+        self.storage = CacheStorage(self.manager, self.dtype, self.device)
+        self.runner = StepRunner(model, self.manager, self.storage, o.max_batch_tokens,
+                                 min(o.max_requests, o.max_batch_tokens), self.max_context)
+        self.scheduler = Scheduler(self.manager, o.max_batch_tokens, self.runner.R_max, self.max_context)
+        self._ids = itertools.count()
+        R = self.runner.R_max
+        self._small_host = torch.zeros(2 * R, dtype=torch.float32, pin_memory=self.device.type == "cuda")
+        self._small_dev = torch.zeros(2 * R, dtype=torch.float32, device=self.device)
+        self._picked_dev = torch.zeros(R + 1, dtype=torch.int32, device=self.device)
+        self._picked_host = torch.zeros(R + 1, dtype=torch.int32, pin_memory=self.device.type == "cuda")
+        self.stats = GenerationStats()
+
+    # ------------------------------------------------------------ construction
+    @staticmethod
+    def _tokens_that_fit(specs, cache_from, o: EngineOptions) -> int:
+        from ..parts.base import PagedKVSpec
+        dt = _DTYPES[o.dtype]
+        esz = 2 if dt == torch.bfloat16 else 4
+        per_token = sum(2 * s.num_kv_heads * s.head_dim * esz
+                        for s, src in zip(specs, cache_from) if isinstance(s, PagedKVSpec) and src is None)
+        if per_token == 0:
+            return o.page_size
+        free, _ = torch.cuda.mem_get_info(torch.device(o.device))
+        return max(o.page_size, int(free * o.memory_fraction) // per_token)
+
+    @classmethod
+    def from_folder(cls, model_dir: str, options: Optional[EngineOptions] = None, **kw) -> "Engine":
+        """Loads config.json and model.safetensors of ``model_dir``."""
+        options = options or EngineOptions(**kw)
+        cls._require_gpu(options)
+        d = read_config_json(model_dir)
+        config_cls, builder = lookup_architecture(architecture_name(d))
+        config = config_cls.from_dict(d)
+        model = builder(config, _DTYPES[options.dtype], options.device)
+        src = open_model_folder(model_dir)
+        try:
+            model.load(src)
+        finally:
+            src.close()
+        return cls(config, model, options)
+
+    @classmethod
+    def from_config(cls, config: ModelConfig, seed: int, options: Optional[EngineOptions] = None, **kw) -> "Engine":
+        """Random-weights mode: seeded weights made on the device, no files."""
+        options = options or EngineOptions(**kw)
+        cls._require_gpu(options)
+        _, builder = lookup_architecture(config.architecture)
+        model = builder(config, _DTYPES[options.dtype], options.device)
+        model.load_random(seed)
+        return cls(config, model, options)
+
+    @staticmethod
+    def _require_gpu(options: EngineOptions) -> None:
+        if options.dtype not in _DTYPES:
+            raise ValueError(f"dtype {options.dtype!r}: the engine computes in bfloat16 or float32")
+        if not torch.cuda.is_available():
+            raise RuntimeError("airun_b200 runs on a CUDA GPU (sm_100a); none is visible and there is no CPU path")
+
+    # ------------------------------------------------------------ requests
+    def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None,
+                    max_new_tokens: int = 256, eog_tokens: Sequence[int] = (), rid: Hashable = None) -> Request:
+        rid = next(self._ids) if rid is None else rid
+        V = self.config.vocab_size
+        bad = [t for t in prompt if not (0 <= int(t) < V)]
+        if bad:
+            raise ValueError(f"prompt holds token ids outside [0, {V}): {bad[:5]}")
+        req = Request(rid, [int(t) for t in prompt], params or SamplingParams(), int(max_new_tokens),
+                      tuple(int(t) for t in eog_tokens))
+        self.scheduler.add(req)
+        return req
+
+    def has_work(self) -> bool:
+        return self.scheduler.has_work()
+
+    def run_step(self) -> List[Request]:
+        """One scheduler step: plan, run, sample.  Returns the requests that finished."""
+        plan = self.scheduler.plan()
+        finished = list(plan.finished)
+        if not plan.entries:
+            return finished
+        entries = []
+        wanting: List[Request] = []
+        for e in plan.entries:
+            toks = e.request.tokens[e.start:e.start + e.count]
+            entries.append(StepEntry(e.request.rid, toks, (e.count - 1,) if e.wants_logits else ()))
+            if e.wants_logits:
+                wanting.append(e.request)
+        logits = self.runner.step(entries)
+        self.scheduler.advance(plan)
+        if wanting:
+            tokens = self._sample(logits, wanting)
+            for req, tok in zip(wanting, tokens):
+                if self.scheduler.accept(req, tok) is not None:
+                    finished.append(req)
+        self.stats.steps += 1
+        self.stats.preemptions += len(plan.preempted)
+        return finished
+
+    def _sample(self, logits: torch.Tensor, reqs: List[Request]) -> List[int]:
+        n = len(reqs)
+        R = self.runner.R_max
+        host = self._small_host.numpy()
+        for i, r in enumerate(reqs):
+            p = r.params
+            dev = p.device_ok
+            host[i] = p.temperature if (dev and p.temperature > 0.0) else 0.0
+            host[R + i] = r.sampler.next_uniform() if (dev and p.temperature > 0.0) else 0.0
+        self._small_dev.copy_(self._small_host, non_blocking=True)
+        ops.sample(logits, self._picked_dev, self._small_dev[:R], self._small_dev[R:])
+        self._picked_dev[R:R + 1].copy_(self.runner.err)
+        self._picked_host.copy_(self._picked_dev, non_blocking=True)
+        host_rows = [i for i, r in enumerate(reqs) if not r.params.device_ok]
+        rows_host = logits[host_rows].cpu().numpy() if host_rows else None
+        torch.cuda.current_stream().synchronize()
+        picked = self._picked_host.numpy()
+        if picked[R]:
+            self.runner.err.zero_()
+            raise RuntimeError("a kernel reported: " + ops.describe_device_error(int(picked[R])))
+        out = [int(picked[i]) for i in range(n)]
+        for j, i in enumerate(host_rows):
+            out[i] = reqs[i].sampler.sample(rows_host[j], reqs[i].tokens)
+        return out
+
+    # ------------------------------------------------------------ generation
+    def generate(self, prompts: Union[Sequence[int], Sequence[Sequence[int]]],
+                 params: Union[None, SamplingParams, Sequence[SamplingParams]] = None,
+                 max_new_tokens: int = 256, eog_tokens: Sequence[int] = (),
+                 on_token=None) -> Union[GenerationResult, List[GenerationResult]]:
+        """Generates for one prompt (a list of ids) or several (a list of lists)."""
+        single = len(prompts) > 0 and not isinstance(prompts[0], (list, tuple, np.ndarray))
+        plist = [prompts] if single else list(prompts)
+        if isinstance(params, SamplingParams) or params is None:
+            params_list = [params] * len(plist)
+        else:
+            params_list = list(params)
+        reqs = []
+        for p, sp in zip(plist, params_list):
+            if sp is not None and len(plist) > 1:
+                sp = SamplingParams(**{**sp.__dict__})          # one generator per request
+            reqs.append(self.add_request(p, sp, max_new_tokens, eog_tokens))
+        self.stats = GenerationStats(prompt_tokens=sum(len(p) for p in plist))
+        emitted = {id(r): 0 for r in reqs}
+        t0 = time.perf_counter()
+        t_first = None
+        while any(r.finished is None for r in reqs):
+            if not self.has_work():
+                break
+            self.run_step()
+            if t_first is None and all(r.output or r.finished for r in reqs):
+                t_first = time.perf_counter()
+            if on_token is not None:
+                for r in reqs:
+                    while emitted[id(r)] < len(r.output):
+                        on_token(r, r.output[emitted[id(r)]])
+                        emitted[id(r)] += 1
+        t1 = time.perf_counter()
+        t_first = t_first or t1
+        self.stats.prefill_ms = (t_first - t0) * 1e3
+        self.stats.decode_ms = (t1 - t_first) * 1e3
+        self.stats.generated_tokens = sum(len(r.output) for r in reqs)
+        res = [GenerationResult(list(r.output), (r.finished or FinishReason.CANCELLED).value, len(r.prompt))
+               for r in reqs]
+        return res[0] if single else res

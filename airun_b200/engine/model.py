@@ -1,0 +1,111 @@
+"""A decoder put together from parts, layer by layer, from a configuration.
+
+The model is: token embedding, a list of layers (each an arrangement of norm,
+mixer, feed-forward chosen by the configuration's ``layer_specs()``), an
+execution order (a list of :class:`LayerCall`, which may name a layer twice or
+let an entry read an earlier entry's cache), a final norm and an output head.
+Tensor names come from the configuration's ``tensor_names()``.  The reference
+assembles the same pieces per layer (crates/airun-core/src/model.rs:612-628,
+crates/airun-core/src/runtime.rs:3482-3602) and keeps the output norm fused with
+the last residual add (runtime.rs:3745-3746).
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..config.base import LayerCall, ModelConfig
+from ..parts.base import make_part
+from ..parts.embedding import LMHead, TokenEmbedding
+from ..weights.loader import (DictSource, TensorSource, WeightSpec, load_tensors, random_tensors)
+
+DEFAULT_NAMES = dict(embed="model.embed_tokens.weight", layer="model.layers.{i}", mixer="self_attn",
+                     ffn="mlp", norm1="input_layernorm", norm2="post_attention_layernorm",
+                     final_norm="model.norm", head="lm_head.weight")
+
+
+class DecoderModel:
+    def __init__(self, config: ModelConfig, dtype: torch.dtype, device):
+        if dtype not in (torch.float32, torch.bfloat16):
+            raise ValueError(f"the engine computes in float32 or bfloat16, not {dtype}")
+        self.config, self.dtype, self.device = config, dtype, torch.device(device)
+        names = dict(DEFAULT_NAMES)
+        names.update(getattr(config, "tensor_names", lambda: {})())
+        self.names = names
+        V, H = config.vocab_size, config.hidden_size
+        self.V, self.H = V, H
+        self.embedding = TokenEmbedding(names["embed"], V, H)
+        self.layers = []
+        for i, spec in enumerate(config.layer_specs()):
+            p = names["layer"].format(i=i)
+            common = dict(dtype=dtype, device=self.device)
+            norm1 = make_part("norm", spec.norm, prefix=f"{p}.{names['norm1']}", **spec.norm_args, **common)
+            norm2 = make_part("norm", spec.norm, prefix=f"{p}.{names['norm2']}", **spec.norm_args, **common)
+            mixer = make_part("mixer", spec.mixer, prefix=f"{p}.{names['mixer']}", **spec.mixer_args, **common)
+            ffn = make_part("feed_forward", spec.feed_forward, prefix=f"{p}.{names['ffn']}", **spec.ffn_args, **common)
+            self.layers.append(make_part("arrangement", spec.arrangement, norm1=norm1, mixer=mixer,
+                                         norm2=norm2, ffn=ffn, dtype=dtype))
+        self.order: List[LayerCall] = list(config.execution_order())
+        for c in self.order:
+            if not (0 <= c.layer < len(self.layers)):
+                raise ValueError(f"the execution order names layer {c.layer}, the model has {len(self.layers)}")
+        fn_name, fn_args = config.final_norm() if hasattr(config, "final_norm") else \
+            ("rmsnorm", dict(size=H, eps=config.rms_norm_eps))
+        self.final_norm = make_part("norm", fn_name, prefix=names["final_norm"], dtype=dtype,
+                                    device=self.device, **fn_args)
+        tied = bool(getattr(config, "tie_word_embeddings", False))
+        self.head = LMHead(names["head"], V, H, self.embedding if tied else None)
+        self.tied = tied
+
+    # ---- weights ----
+    def parts(self):
+        return [self.embedding] + self.layers + [self.final_norm, self.head]
+
+    def weight_specs(self) -> List[WeightSpec]:
+        return [s for p in self.parts() for s in p.weight_specs()]
+
+    def ignorable_tensors(self) -> List[str]:
+        # a tied model's file may still carry the head; it is the same matrix
+        return [self.names["head"]] if self.tied else []
+
+    def load(self, source: TensorSource) -> None:
+        tensors = load_tensors(self.weight_specs(), source, self.dtype, self.device, self.ignorable_tensors())
+        for p in self.parts():
+            p.load_weights(tensors)
+
+    def load_random(self, seed: int) -> None:
+        """Seeded random weights made on the model's device, through the same loading path."""
+        tensors = random_tensors(self.weight_specs(), seed, self.device,
+                                 torch.bfloat16)
+        self.load(DictSource(tensors))
+
+    # ---- cache needs ----
+    def cache_specs(self) -> Tuple[List[object], List[Optional[int]]]:
+        return ([self.layers[c.layer].cache_spec() for c in self.order],
+                [c.cache_from for c in self.order])
+
+    # ---- one pass over the given tokens ----
+    def forward(self, ctx, want_rows: Optional[torch.Tensor], n_want: int) -> Optional[torch.Tensor]:
+        T = ctx.num_tokens
+        ctx.ws_main.reset()
+        x = ctx.ws_main.alloc((T, self.H), torch.float32)
+        self.embedding.forward(ctx, ctx.token_ids[:T], x)
+        delta = None
+        for ci, call in enumerate(self.order):
+            ctx.ws = ctx.ws_pair[ci % 2]
+            ctx.ws.reset()
+            delta = self.layers[call.layer].forward(ctx, x, delta, ctx.caches[ci])
+        if n_want == 0:
+            return None
+        ctx.ws = ctx.ws_pair[len(self.order) % 2]
+        ctx.ws.reset()
+        hsel = ctx.ws.alloc((n_want, self.H), self.dtype)
+        self.final_norm.forward(ctx, x, hsel, delta=delta, rows=want_rows[:n_want])
+        logits = ctx.ws_main.alloc((n_want, self.V), torch.float32)
+        self.head.forward(ctx, hsel, logits)
+        return logits
+
+
+def build_decoder(config: ModelConfig, dtype: torch.dtype, device) -> DecoderModel:
+    return DecoderModel(config, dtype, device)

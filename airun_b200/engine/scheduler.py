@@ -1,0 +1,251 @@
+"""The scheduler: admits requests, cuts prompts into portions under a token
+budget, decodes, finishes and frees.
+
+The reference's scheduler keeps a FIFO of jobs, admits one waiting job per loop
+iteration when a slot is free, prefills it alone and whole, and otherwise
+decodes one token for every active request (crates/airun-cli/src/sched.rs:82-213,
+:485-508); its finish reasons are MaxTokens, EndOfGeneration (the end token is
+not emitted), Cancelled and ContextFull (sched.rs:511-539,
+crates/airun-core/src/runtime.rs:5099-5108, :5020-5023).  It can never run out
+of cache at run time because every slot owns a full context.  Here the cache is
+paged, so each step is planned under two limits, a token budget and the free
+pages:
+
+1. Every running request comes first, in admission order: one token if it is
+   decoding, else the next portion of its prompt, as large as budget and free
+   pages allow (a portion may be as small as one token).
+2. If a decoding request cannot get the page it needs, the most recently
+   admitted running request is preempted: its pages are given back and it
+   returns to the FRONT of the waiting queue, to be recomputed later from its
+   prompt plus the tokens it has produced.  A request that is alone and still
+   cannot get a page ends with ContextFull.
+3. Then waiting requests are admitted first-in first-out while budget, request
+   slots and pages for at least part of the prompt remain.
+A prompt longer than the whole pool or the context limit is refused at submission.
+
+The scheduler is host-side only; it decides, the step function runs.
+"""
+from __future__ import annotations
+
+import itertools
+from collections import deque
+from dataclasses import dataclass, field
+from enum import Enum
+from typing import Deque, Dict, Hashable, List, Optional, Sequence, Tuple
+
+from ..cache.manager import CacheManager
+from ..sampling.sampler import Sampler, SamplingParams
+
+
+class FinishReason(str, Enum):
+    MAX_TOKENS = "MaxTokens"
+    END_OF_GENERATION = "EndOfGeneration"
+    CANCELLED = "Cancelled"
+    CONTEXT_FULL = "ContextFull"
+    REFUSED = "Refused"
+
+
+@dataclass
+class Request:
+    rid: Hashable
+    prompt: List[int]
+    params: SamplingParams
+    max_new_tokens: int
+    eog_tokens: Tuple[int, ...] = ()
+    output: List[int] = field(default_factory=list)
+    num_computed: int = 0            # tokens whose keys and values are in the cache
+    finished: Optional[FinishReason] = None
+    cancelled: bool = False
+    preemptions: int = 0
+    sampler: Optional[Sampler] = None
+
+    def __post_init__(self):
+        if self.sampler is None:
+            self.sampler = Sampler(self.params)
+
+    @property
+    def tokens(self) -> List[int]:
+        return self.prompt + self.output
+
+    @property
+    def num_tokens(self) -> int:
+        return len(self.prompt) + len(self.output)
+
+    @property
+    def decoding(self) -> bool:
+        return self.num_computed >= len(self.prompt) and self.num_tokens - self.num_computed == 1
+
+
+@dataclass
+class PlannedEntry:
+    request: Request
+    start: int                       # first token (index into request.tokens) run this step
+    count: int
+    wants_logits: bool               # the portion ends at the newest token: sample after it
+
+
+@dataclass
+class Plan:
+    entries: List[PlannedEntry]
+    preempted: List[Request]
+    finished: List[Request]          # requests ended while planning (ContextFull)
+
+
+class Scheduler:
+    def __init__(self, manager: CacheManager, max_batch_tokens: int, max_batch_reqs: int, max_context: int):
+        self.manager = manager
+        self.max_batch_tokens, self.max_batch_reqs, self.max_context = max_batch_tokens, max_batch_reqs, max_context
+        self.waiting: Deque[Request] = deque()
+        self.running: List[Request] = []        # in admission order
+        self.stats = dict(steps=0, preemptions=0, admitted=0, refused=0)
+
+    # ------------------------------------------------------------ submission
+    def add(self, req: Request) -> None:
+        capacity = self.manager.max_tokens_possible()
+        if len(req.prompt) == 0:
+            req.finished = FinishReason.REFUSED
+        elif len(req.prompt) + 1 > min(capacity, self.max_context):
+            req.finished = FinishReason.REFUSED
+        if req.finished is not None:
+            self.stats["refused"] += 1
+            return
+        self.waiting.append(req)
+
+    def has_work(self) -> bool:
+        return bool(self.waiting or self.running)
+
+    # ------------------------------------------------------------ planning
+    def _pages_fit(self, req: Request, n: int, planned: Dict[int, int]) -> bool:
+        return self.manager.can_reserve(req.rid, n, planned)
+
+    def _note(self, req: Request, n: int, planned: Dict[int, int]) -> None:
+        for gid, k in self.manager.pages_needed(req.rid, n).items():
+            planned[gid] = planned.get(gid, 0) + k
+
+    def _largest_portion(self, req: Request, want: int, planned: Dict[int, int]) -> int:
+        """Largest n <= want whose pages are free now (0 if not even one token fits)."""
+        if self._pages_fit(req, want, planned):
+            return want
+        lo, hi = 0, want                         # fits(lo) holds, fits(hi) fails
+        while hi - lo > 1:
+            mid = (lo + hi) // 2
+            if self._pages_fit(req, mid, planned):
+                lo = mid
+            else:
+                hi = mid
+        return lo
+
+    def _preempt(self, victim: Request) -> None:
+        self.manager.free_request(victim.rid)
+        victim.num_computed = 0
+        victim.preemptions += 1
+        self.running.remove(victim)
+        self.waiting.appendleft(victim)
+        self.stats["preemptions"] += 1
+
+    def _finish(self, req: Request, reason: FinishReason) -> None:
+        req.finished = reason
+        if req in self.running:
+            self.running.remove(req)
+            self.manager.free_request(req.rid)
+
+    def plan(self) -> Plan:
+        preempted: List[Request] = []
+        finished: List[Request] = []
+        for req in [r for r in self.running if r.cancelled]:
+            self._finish(req, FinishReason.CANCELLED)
+            finished.append(req)
+
+        while True:
+            entries, stuck = self._plan_running()
+            if stuck is None:
+                break
+            # ``stuck`` cannot get a page.  Give back the newest running request's pages.
+            victim = self.running[-1]
+            if len(self.running) == 1:
+                self._finish(victim, FinishReason.CONTEXT_FULL)
+                finished.append(victim)
+            else:
+                self._preempt(victim)
+                preempted.append(victim)
+
+        budget = self.max_batch_tokens - sum(e.count for e in entries)
+        planned: Dict[int, int] = {}
+        for e in entries:
+            self._note(e.request, e.count, planned)
+        while (self.waiting and budget > 0 and len(entries) < self.max_batch_reqs
+               and self.manager.has_free_slot() and not preempted):
+            req = self.waiting[0]
+            if req.cancelled:
+                self.waiting.popleft()
+                req.finished = FinishReason.CANCELLED
+                finished.append(req)
+                continue
+            self.manager.add_request(req.rid)
+            want = min(req.num_tokens - req.num_computed, budget)
+            if not self._pages_fit(req, want, planned):
+                self.manager.free_request(req.rid)
+                if not self.running:
+                    # nothing else holds pages, so this request can never start
+                    self.waiting.popleft()
+                    req.finished = FinishReason.CONTEXT_FULL
+                    finished.append(req)
+                    continue
+                break
+            self.waiting.popleft()
+            self.running.append(req)
+            self.stats["admitted"] += 1
+            entries.append(PlannedEntry(req, 0, want, want == req.num_tokens))
+            self._note(req, want, planned)
+            budget -= want
+        self.stats["steps"] += 1
+        return Plan(entries, preempted, finished)
+
+    def _plan_running(self) -> Tuple[List[PlannedEntry], Optional[Request]]:
+        """Portions for the running requests, in admission order.  Returns the
+        entries and, if the step cannot go on as it is, the request that is stuck:
+        a decoding request without a page, or, when nothing at all could be planned,
+        the first request that is waiting for pages."""
+        budget = self.max_batch_tokens
+        entries: List[PlannedEntry] = []
+        planned: Dict[int, int] = {}
+        starved: Optional[Request] = None
+        for req in self.running:
+            if budget <= 0 or len(entries) >= self.max_batch_reqs:
+                break
+            want = min(req.num_tokens - req.num_computed, budget)
+            n = self._largest_portion(req, want, planned)
+            if n == 0:
+                if req.decoding:
+                    return entries, req
+                starved = starved or req
+                continue
+            entries.append(PlannedEntry(req, req.num_computed, n, req.num_computed + n == req.num_tokens))
+            self._note(req, n, planned)
+            budget -= n
+        if not entries and starved is not None:
+            return entries, starved
+        return entries, None
+
+    # ------------------------------------------------------------ after the step
+    def advance(self, plan: Plan) -> None:
+        """The step ran: the planned tokens are in the cache."""
+        for e in plan.entries:
+            e.request.num_computed += e.count
+
+    def accept(self, req: Request, token: int) -> Optional[FinishReason]:
+        """Takes the token sampled for ``req``; returns the finish reason if it ends."""
+        if req.cancelled:
+            reason = FinishReason.CANCELLED
+        elif token in req.eog_tokens:
+            reason = FinishReason.END_OF_GENERATION     # the end token is not emitted
+        else:
+            req.output.append(int(token))
+            if len(req.output) >= req.max_new_tokens:
+                reason = FinishReason.MAX_TOKENS
+            elif req.num_tokens >= self.max_context:
+                reason = FinishReason.CONTEXT_FULL
+            else:
+                return None
+        self._finish(req, reason)
+        return reason

@@ -1,0 +1,197 @@
+"""The step function: one batch of (request, its next tokens) through the model.
+
+``StepRunner.step(entries)`` takes a list of ``StepEntry(rid, tokens, want)``:
+portions of prompts beside single decoded tokens, cut anywhere.  It takes the
+pages the new tokens need, runs only the tokens it is given, as one batch, from
+the cache that earlier steps left, writes their keys and values, and returns the
+float32 logits at the wanted places, in the order of the entries and of
+``want``.  It is policy-free: the scheduler and the trace replay both drive it.
+
+The reference's equivalents are ``Runtime::step`` for n tokens of one sequence
+and ``decode_rows`` for one token of each of n slots
+(crates/airun-core/src/runtime.rs:2046-2100, :3050-3147); a non-final prompt
+chunk returns nothing and does not synchronise (runtime.rs:2032-2037).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, Hashable, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache.manager import CacheManager, CacheStorage, OutOfPages
+from ..kernels import ops
+from .batch import CacheView, StepContext, Workspace
+from .model import DecoderModel
+
+
+@dataclass
+class StepEntry:
+    rid: Hashable
+    tokens: Sequence[int]
+    want: Sequence[int] = ()          # places among ``tokens`` whose logits are wanted
+
+
+class StepError(RuntimeError):
+    pass
+
+
+class StepRunner:
+    def __init__(self, model: DecoderModel, manager: CacheManager, storage: CacheStorage,
+                 max_batch_tokens: int, max_batch_reqs: int, max_context: int):
+        self.model, self.manager, self.storage = model, manager, storage
+        self.device = model.device
+        self.T_max, self.R_max = int(max_batch_tokens), int(max_batch_reqs)
+        self.max_context = int(max_context)
+        self.max_blocks = (self.max_context + manager.page_size - 1) // manager.page_size
+        n_groups = len(manager.paged)
+        # one pinned staging buffer, one device mirror, fixed offsets
+        sizes = [("token_ids", self.T_max), ("positions", self.T_max), ("req_of_token", self.T_max),
+                 ("want_rows", self.T_max), ("cu_tokens", self.R_max + 1), ("context_lens", self.R_max),
+                 ("state_slots", self.R_max)]
+        sizes += [(f"bt{g}", self.R_max * self.max_blocks) for g in range(n_groups)]
+        self.offsets: Dict[str, tuple] = {}
+        off = 0
+        for name, n in sizes:
+            self.offsets[name] = (off, n)
+            off += (n + 63) // 64 * 64
+        # a ring of pinned staging buffers: the host may run ahead of the copies of earlier steps
+        self._ring = []
+        for _ in range(4):
+            h = torch.zeros(off, dtype=torch.int32, pin_memory=self.device.type == "cuda")
+            self._ring.append((h, h.numpy(), torch.cuda.Event() if self.device.type == "cuda" else None))
+        self._ring_i = 0
+        self.meta_host, self.meta_np, self._meta_event = self._ring[0]
+        self._ring_used = [False] * 4
+        self.meta_dev = torch.zeros(off, dtype=torch.int32, device=self.device)
+        self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.ws_main = Workspace(self.device)
+        self.ws_pair = (Workspace(self.device), Workspace(self.device))
+        self.steps_run = 0
+
+    def _view(self, name: str, dev: bool = True):
+        off, n = self.offsets[name]
+        return (self.meta_dev if dev else self.meta_np)[off:off + n]
+
+    def _cache_views(self) -> List[CacheView]:
+        views = []
+        for b in self.manager.bindings:
+            if b.kind == "paged":
+                bt = self._view(f"bt{b.gid}").view(self.R_max, self.max_blocks)
+                views.append(CacheView("paged", b.shared, self.storage.paged[b.gid][b.index], bt,
+                                       self.manager.page_size, gid=b.gid))
+            elif b.kind == "state":
+                views.append(CacheView("state", b.shared, state=self.storage.state[b.gid][b.index], gid=b.gid))
+            else:
+                views.append(CacheView("none"))
+        return views
+
+    def check_entries(self, entries: Sequence[StepEntry]) -> None:
+        if not entries:
+            raise StepError("a step needs at least one entry")
+        if len(entries) > self.R_max:
+            raise StepError(f"{len(entries)} requests in one step, the runner was made for {self.R_max}")
+        total = sum(len(e.tokens) for e in entries)
+        if total > self.T_max:
+            raise StepError(f"{total} tokens in one step, the runner was made for {self.T_max}")
+        seen = set()
+        for e in entries:
+            if e.rid in seen:
+                raise StepError(f"request {e.rid!r} appears twice in one step")
+            seen.add(e.rid)
+            if len(e.tokens) == 0:
+                raise StepError(f"request {e.rid!r} brings no tokens")
+            rc = self.manager.get(e.rid)
+            if rc.num_tokens + len(e.tokens) > self.max_context:
+                raise StepError(f"request {e.rid!r} would reach {rc.num_tokens + len(e.tokens)} tokens, "
+                                f"the context limit is {self.max_context}")
+            for w in e.want:
+                if not (0 <= w < len(e.tokens)):
+                    raise StepError(f"request {e.rid!r} wants place {w} of {len(e.tokens)} tokens")
+
+    def reserve(self, entries: Sequence[StepEntry]) -> None:
+        """Takes the pages of all entries, or of none."""
+        need: Dict[int, int] = {}
+        for e in entries:
+            for gid, n in self.manager.pages_needed(e.rid, len(e.tokens)).items():
+                need[gid] = need.get(gid, 0) + n
+        free = self.manager.free_pages()
+        for gid, n in need.items():
+            if n > free[gid]:
+                raise OutOfPages(f"the step needs {n} pages in group {gid}, {free[gid]} are free")
+        for e in entries:
+            self.manager.reserve(e.rid, len(e.tokens))
+
+    def build_context(self, entries: Sequence[StepEntry]) -> tuple:
+        """Fills the staging buffer and returns (StepContext, n_want)."""
+        m = self.manager
+        self._ring_i = (self._ring_i + 1) % len(self._ring)
+        self.meta_host, self.meta_np, self._meta_event = self._ring[self._ring_i]
+        if self._ring_used[self._ring_i] and self._meta_event is not None:
+            self._meta_event.synchronize()      # the copy that last read this buffer is done
+        tok, pos, rot, want = (self._view(n, dev=False) for n in ("token_ids", "positions", "req_of_token", "want_rows"))
+        cu, cl, sl = (self._view(n, dev=False) for n in ("cu_tokens", "context_lens", "state_slots"))
+        t = 0
+        n_want = 0
+        qlens, clens, slots = [], [], []
+        for r, e in enumerate(entries):
+            rc = m.get(e.rid)
+            n = len(e.tokens)
+            tok[t:t + n] = np.asarray(e.tokens, dtype=np.int32)
+            pos[t:t + n] = np.arange(rc.num_tokens, rc.num_tokens + n, dtype=np.int32)
+            rot[t:t + n] = r
+            for w in e.want:
+                want[n_want] = t + w
+                n_want += 1
+            cu[r] = t
+            cl[r] = rc.num_tokens + n
+            sl[r] = rc.slot
+            qlens.append(n)
+            clens.append(rc.num_tokens + n)
+            slots.append(rc.slot)
+            for g in m.paged:
+                bt = self._view(f"bt{g.gid}", dev=False)
+                blocks = rc.blocks[g.gid]
+                base = r * self.max_blocks
+                bt[base:base + len(blocks)] = blocks
+            t += n
+        cu[len(entries)] = t
+        self.meta_dev.copy_(self.meta_host, non_blocking=True)
+        if self._meta_event is not None:
+            self._meta_event.record()
+            self._ring_used[self._ring_i] = True
+        ctx = StepContext(
+            num_tokens=t, num_reqs=len(entries),
+            token_ids=self._view("token_ids"), positions=self._view("positions"),
+            req_of_token=self._view("req_of_token"), cu_tokens=self._view("cu_tokens"),
+            context_lens=self._view("context_lens"), state_slots=self._view("state_slots"),
+            err=self.err, ws_pair=self.ws_pair, ws_main=self.ws_main, caches=self._cache_views(),
+            query_lens=qlens, context_lens_host=clens, state_slots_host=slots,
+            max_query_len=max(qlens), max_context_len=max(clens),
+            decode_only=all(q == 1 for q in qlens))
+        return ctx, n_want
+
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Runs the entries as one batch; returns float32 logits [wanted, vocab] on
+        the device (valid until the next step) or None when nothing is wanted."""
+        self.check_entries(entries)
+        self.reserve(entries)
+        ctx, n_want = self.build_context(entries)
+        logits = self.model.forward(ctx, self._view("want_rows"), n_want)
+        for e in entries:
+            self.manager.commit(e.rid, len(e.tokens))
+        self.steps_run += 1
+        return logits
+
+    def device_error(self) -> int:
+        """Error bits the kernels have set since the last call (synchronises)."""
+        bits = int(self.err.item())
+        if bits:
+            self.err.zero_()
+        return bits
+
+    def raise_on_device_error(self) -> None:
+        bits = self.device_error()
+        if bits:
+            raise StepError("a kernel reported: " + ops.describe_device_error(bits))

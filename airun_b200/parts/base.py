@@ -1,0 +1,106 @@
+"""Interfaces of the parts a model is put together from, and their registries.
+
+A layer is an arrangement (``Block``) of a mixer, a feed-forward and norms; the
+mixer may use a position encoding.  Each part takes its sizes and constants as
+constructor parameters, declares the weight tensors it needs by name, and, if it
+keeps something between tokens, declares that as a cache spec.  No part knows
+which model it belongs to.  The reference switches mixer and feed-forward per
+layer through two enums around shared norm/residual code
+(crates/airun-core/src/model.rs:446-464, crates/airun-core/src/runtime.rs:3537-3589);
+here the choice is a name looked up in a registry, so that a new part needs no
+change to existing files.
+
+Interfaces
+----------
+Part            weight_specs() -> [WeightSpec];  load_weights(tensors: dict) -> None
+Norm            forward(ctx, x, out, delta=None, rows=None)
+                  out = norm(x [+ delta]); with delta and no rows, x += delta in place
+PositionEncoding fused() -> (kind, rotary_dim, inv_freq) the attention prologue
+                  kernel understands
+Mixer           cache_spec() -> PagedKVSpec | StateSpec | None
+                forward(ctx, h, cache) -> float32 [T, hidden] (the residual delta)
+FeedForward     forward(ctx, h) -> float32 [T, hidden]
+Block           forward(ctx, x, delta, cache) -> delta of the block's last sub-layer,
+                  still to be added to x by whoever norms x next
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Any, Callable, Dict, List, Optional, Tuple
+
+import torch
+
+from ..weights.loader import WeightSpec
+
+
+@dataclass(frozen=True)
+class PagedKVSpec:
+    """Keys and values of every (or the last ``window``) token(s), in pages."""
+    num_kv_heads: int
+    head_dim: int
+    window: int = 0          # 0: all tokens are kept
+
+
+@dataclass(frozen=True)
+class StateSpec:
+    """Per-request state of fixed size, zero when a request starts."""
+    shape: Tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+class Part:
+    """Something with weights.  ``prefix`` is its tensor-name prefix in the model file."""
+
+    prefix: str = ""
+
+    def weight_specs(self) -> List[WeightSpec]:
+        return []
+
+    def load_weights(self, tensors: Dict[str, torch.Tensor]) -> None:
+        pass
+
+
+class Norm(Part):
+    def forward(self, ctx, x: torch.Tensor, out: torch.Tensor,
+                delta: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None) -> None:
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    def fused(self) -> Optional[Tuple[int, int, Optional[torch.Tensor]]]:
+        return None
+
+
+class Mixer(Part):
+    def cache_spec(self):
+        return None
+
+    def forward(self, ctx, h: torch.Tensor, cache) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, ctx, h: torch.Tensor) -> torch.Tensor:
+        raise NotImplementedError
+
+
+_REGISTRIES: Dict[str, Dict[str, Callable]] = {
+    "mixer": {}, "feed_forward": {}, "norm": {}, "position": {}, "arrangement": {}}
+
+
+def register_part(kind: str, name: str, factory: Callable) -> None:
+    """Registers ``factory(prefix=..., dtype=..., device=..., **args)`` under ``name``."""
+    if kind not in _REGISTRIES:
+        raise KeyError(f"unknown kind of part {kind!r}; kinds: {sorted(_REGISTRIES)}")
+    _REGISTRIES[kind][name] = factory
+
+
+def make_part(kind: str, name: str, **kwargs):
+    reg = _REGISTRIES[kind]
+    if name not in reg:
+        raise KeyError(f"no {kind} named {name!r} is registered; registered: {sorted(reg)}")
+    return reg[name](**kwargs)
+
+
+def registered_parts(kind: str) -> List[str]:
+    return sorted(_REGISTRIES[kind])
