@@ -1,0 +1,139 @@
+"""Command line in the manner of the reference's ``airun run``.
+
+Option names, meanings and defaults follow crates/airun-cli/src/run.rs:50-220:
+``-n/--predict`` 256, ``-c/--ctx-size``, ``-b/--batch-size``, ``--temp`` 0.8,
+``--top-k`` 40, ``--top-p`` 0.95, ``--min-p`` 0.05, ``--typical-p`` 1.0,
+``--top-n-sigma`` 0, ``--repeat-penalty`` 1.1, ``--presence-penalty`` 0,
+``--frequency-penalty`` 0, ``--repeat-last-n`` 64, ``--seed`` 0 (0 = from the
+clock), ``--stats``, ``-q/--quiet``.  The model is a folder with config.json
+and model.safetensors; the prompt is a list of token ids (``-p 1,2,3``, a file,
+or standard input), since the engine works on token ids.  ``--dtype`` takes the
+place of ``--kv-type``: the cache is kept in the compute type.
+
+Subcommands: ``run`` (generate), ``init`` (random-weights mode: write a model
+folder from a config.json and a seed), ``inspect`` (print the configuration).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import re
+import sys
+import time
+from typing import List, Optional
+
+
+def parse_ids(text: str) -> List[int]:
+    ids = [int(t) for t in re.split(r"[\s,]+", text.strip()) if t]
+    if not ids:
+        raise SystemExit("the prompt holds no token ids")
+    return ids
+
+
+def build_parser() -> argparse.ArgumentParser:
+    ap = argparse.ArgumentParser(prog="airun", description="airun_b200: Qwen3 inference on one B200")
+    sub = ap.add_subparsers(dest="cmd", required=True)
+
+    run = sub.add_parser("run", help="generate from a prompt of token ids")
+    run.add_argument("model", help="folder with config.json and model.safetensors")
+    run.add_argument("-p", "--prompt", help="token ids separated by commas or spaces; standard input when omitted")
+    run.add_argument("--prompt-file", help="file holding the token ids")
+    run.add_argument("-n", "--predict", type=int, default=256, help="tokens to generate")
+    run.add_argument("-c", "--ctx-size", type=int, default=None, help="longest context of a request")
+    run.add_argument("-b", "--batch-size", type=int, default=512, help="token budget of one step")
+    run.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
+    run.add_argument("--page-size", type=int, default=16)
+    run.add_argument("--cache-tokens", type=int, default=None, help="tokens the cache holds (default: what fits)")
+    run.add_argument("--parallel", type=int, default=8, help="requests live at a time")
+    run.add_argument("--temp", type=float, default=0.8)
+    run.add_argument("--top-k", type=int, default=40)
+    run.add_argument("--top-p", type=float, default=0.95)
+    run.add_argument("--min-p", type=float, default=0.05)
+    run.add_argument("--typical-p", type=float, default=1.0)
+    run.add_argument("--top-n-sigma", type=float, default=0.0)
+    run.add_argument("--repeat-penalty", type=float, default=1.1)
+    run.add_argument("--presence-penalty", type=float, default=0.0)
+    run.add_argument("--frequency-penalty", type=float, default=0.0)
+    run.add_argument("--repeat-last-n", type=int, default=64)
+    run.add_argument("--seed", type=int, default=0)
+    run.add_argument("--eog", default="", help="token ids that end generation")
+    run.add_argument("--stats", action="store_true", help="print timing to stderr")
+    run.add_argument("-q", "--quiet", action="store_true", help="print only the generated ids")
+
+    init = sub.add_parser("init", help="write a model folder with seeded random weights")
+    init.add_argument("config", help="a config.json of the architecture")
+    init.add_argument("out", help="folder to write")
+    init.add_argument("--seed", type=int, default=1)
+
+    ins = sub.add_parser("inspect", help="print the configuration of a model folder")
+    ins.add_argument("model")
+    return ap
+
+
+def cmd_run(a) -> int:
+    from . import Engine, EngineOptions, SamplingParams
+    if a.prompt is not None:
+        prompt = parse_ids(a.prompt)
+    elif a.prompt_file:
+        with open(a.prompt_file) as f:
+            prompt = parse_ids(f.read())
+    else:
+        prompt = parse_ids(sys.stdin.read())
+    t0 = time.perf_counter()
+    eng = Engine.from_folder(a.model, EngineOptions(
+        dtype=a.dtype, page_size=a.page_size, cache_tokens=a.cache_tokens, max_batch_tokens=a.batch_size,
+        max_requests=a.parallel, max_context=a.ctx_size))
+    load_s = time.perf_counter() - t0
+    if not a.quiet:
+        print(f"[airun] {eng.config.summary()}; context {eng.max_context}, "
+              f"{eng.manager.num_pages} pages of {eng.manager.page_size}", file=sys.stderr)
+    params = SamplingParams(temperature=a.temp, top_k=a.top_k, top_p=a.top_p, min_p=a.min_p,
+                            typical_p=a.typical_p, top_n_sigma=a.top_n_sigma, repeat_penalty=a.repeat_penalty,
+                            presence_penalty=a.presence_penalty, frequency_penalty=a.frequency_penalty,
+                            repeat_last_n=a.repeat_last_n, seed=a.seed)
+    eog = parse_ids(a.eog) if a.eog.strip() else []
+
+    def on_token(req, tok):
+        if not a.quiet:
+            print(tok, end=" ", flush=True)
+
+    res = eng.generate(prompt, params, max_new_tokens=a.predict, eog_tokens=eog, on_token=on_token)
+    if a.quiet:
+        print(",".join(str(t) for t in res.token_ids))
+    else:
+        print()
+    if a.stats or not a.quiet:
+        s = eng.stats
+        print(f"[airun] prompt {s.prompt_tokens} tokens in {s.prefill_ms:.1f} ms ({s.prefill_tps:.1f} tok/s), "
+              f"generated {s.generated_tokens} in {s.decode_ms:.1f} ms ({s.decode_tps:.1f} tok/s), "
+              f"stop: {res.finish_reason}, load {load_s:.1f} s", file=sys.stderr)
+    return 0
+
+
+def cmd_init(a) -> int:
+    import torch
+    from .config import architecture_name, lookup_architecture
+    from .weights import write_model_folder
+    with open(a.config) as f:
+        d = json.load(f)
+    config_cls, builder = lookup_architecture(architecture_name(d))
+    config = config_cls.from_dict(d)
+    model = builder(config, torch.float32, "cpu")
+    write_model_folder(a.out, config, model.weight_specs(), a.seed)
+    print(f"wrote {a.out}: {config.summary()}")
+    return 0
+
+
+def cmd_inspect(a) -> int:
+    from .config import load_config
+    print(load_config(a.model).summary())
+    return 0
+
+
+def main(argv: Optional[List[str]] = None) -> int:
+    a = build_parser().parse_args(argv)
+    return {"run": cmd_run, "init": cmd_init, "inspect": cmd_inspect}[a.cmd](a)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -171,6 +171,8 @@ class Engine:
         for e in plan.entries:
             toks = e.request.tokens[e.start:e.start + e.count]
             entries.append(StepEntry(e.request.rid, toks, (e.count - 1,) if e.wants_logits else ()))
+            if e.start == 0 and self.storage.state:
+                self.storage.zero_state_slot(self.manager.get(e.request.rid).slot)   # a request starts from zero state
             if e.wants_logits:
                 wanting.append(e.request)
         logits = self.runner.step(entries)

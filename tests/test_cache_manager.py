@@ -1,0 +1,165 @@
+"""The cache manager without a GPU: no page lost, held twice or freed twice, under
+random orders of requests; groups with a window give pages back; state slots."""
+import random
+
+import pytest
+import torch
+
+from airun_b200.cache import CacheError, CacheManager, CacheStorage, OutOfPages, PageAllocator
+from airun_b200.parts.base import PagedKVSpec, StateSpec
+
+FULL = PagedKVSpec(2, 16, 0)
+WIN = PagedKVSpec(2, 16, 24)
+
+
+def manager(specs=(FULL, FULL), cache_from=None, page=8, pages=12, reqs=4):
+    return CacheManager(list(specs), list(cache_from or [None] * len(specs)), page, pages, reqs)
+
+
+def test_allocator_hands_out_a_freed_page_next():
+    a = PageAllocator(4)
+    p = a.take(3)
+    assert p == [0, 1, 2] and a.num_free == 1
+    a.give_back(1)
+    assert a.take(1) == [1]
+    with pytest.raises(OutOfPages):
+        a.take(2)
+    a.give_back(0)
+    with pytest.raises(CacheError):
+        a.give_back(0)                       # freed twice
+    with pytest.raises(CacheError):
+        a.give_back(9)
+
+
+def test_groups_by_equal_spec_and_sharing_entries():
+    m = manager([FULL, WIN, FULL, WIN, None, StateSpec((3, 5))], [None] * 6)
+    assert [g.spec for g in m.paged] == [FULL, WIN]
+    assert m.paged[0].owners == [0, 2] and m.paged[1].owners == [1, 3]
+    assert m.bindings[2].gid == 0 and m.bindings[2].index == 1
+    assert m.bindings[4].kind == "none" and m.bindings[5].kind == "state"
+    m2 = manager([FULL, FULL, FULL], [None, None, 0])
+    assert m2.bindings[2].shared and m2.bindings[2].index == 0 and m2.paged[0].owners == [0, 1]
+    with pytest.raises(ValueError):
+        manager([FULL, WIN], [None, 0])      # cannot read a cache of another shape
+    with pytest.raises(ValueError):
+        manager([FULL, FULL, FULL], [None, 0, 1])   # must read an owner
+
+
+def test_pages_follow_the_tokens():
+    m = manager(page=8, pages=6)
+    m.add_request("a")
+    assert m.pages_needed("a", 9) == {0: 2}
+    m.reserve("a", 9)
+    m.commit("a", 9)
+    assert m.block_table("a", 0) == [0, 1]
+    m.reserve("a", 7)                        # tokens 9..15 fit the second page
+    assert m.block_table("a", 0) == [0, 1]
+    m.commit("a", 7)
+    m.reserve("a", 1)
+    assert m.block_table("a", 0) == [0, 1, 2]
+    with pytest.raises(CacheError):
+        m.commit("a", 9)                     # beyond what was reserved
+    m.commit("a", 1)
+    m.add_request("b")
+    with pytest.raises(OutOfPages):
+        m.reserve("b", 8 * 4)                # only 3 pages are free; nothing is taken
+    assert m.free_pages() == {0: 3} and m.block_table("b", 0) == []
+    m.free_request("a")
+    assert m.free_pages() == {0: 6}
+    with pytest.raises(CacheError):
+        m.free_request("a")
+    m.check_invariants()
+
+
+def test_window_group_gives_pages_back_as_the_window_passes():
+    m = manager([FULL, WIN], page=8, pages=16)
+    m.add_request("a")
+    m.reserve("a", 40)
+    assert m.free_pages() == {0: 11, 1: 11}
+    m.commit("a", 40)
+    # the next query sits at 40 and sees keys 17..40: blocks 0 and 1 (keys 0..15) are behind the window
+    assert m.block_table("a", 1)[:2] == [-1, -1] and m.block_table("a", 1)[2] >= 0
+    assert m.free_pages() == {0: 11, 1: 13}
+    for _ in range(30):
+        m.reserve("a", 1)
+        m.commit("a", 1)
+    live = [p for p in m.block_table("a", 1) if p >= 0]
+    assert len(live) <= 24 // 8 + 2           # never more than the window needs
+    assert all(p >= 0 for p in m.block_table("a", 0))
+    m.check_invariants()
+    m.free_request("a")
+    assert m.free_pages() == {0: 16, 1: 16}
+
+
+def test_window_edge_is_exact():
+    """A page is given back only when its LAST key is behind the window of the next query."""
+    m = manager([WIN], page=8, pages=8)
+    m.add_request("a")
+    m.reserve("a", 31)
+    m.commit("a", 31)                         # next query at 31 sees keys 8..31: key 7 is dead, block 0 goes
+    assert m.block_table("a", 0)[0] == -1
+    m2 = manager([WIN], page=8, pages=8)
+    m2.add_request("a")
+    m2.reserve("a", 30)
+    m2.commit("a", 30)                        # next query at 30 sees keys 7..30: block 0 still holds key 7
+    assert m2.block_table("a", 0)[0] >= 0
+
+
+def test_state_slots():
+    m = manager([StateSpec((4,)), FULL], page=8, pages=4, reqs=2)
+    a = m.add_request("a")
+    b = m.add_request("b")
+    assert {a.slot, b.slot} == {0, 1}
+    assert not m.has_free_slot()
+    with pytest.raises(CacheError):
+        m.add_request("c")
+    with pytest.raises(CacheError):
+        m.add_request("a")
+    m.free_request("a")
+    assert m.add_request("c").slot == a.slot
+    st = CacheStorage(m, torch.float32, "cpu")
+    assert st.state[0].shape == (1, 2, 4) and st.paged[0].shape == (1, 4, 2, 2, 8, 16)
+    st.state[0].fill_(3.0)
+    st.zero_state_slot(1)
+    assert float(st.state[0][0, 1].abs().sum()) == 0 and float(st.state[0][0, 0].sum()) == 12
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_orders_keep_every_page_accounted_for(seed):
+    rng = random.Random(seed)
+    m = manager([FULL, WIN, FULL], page=4, pages=40, reqs=6)
+    live = {}
+    next_id = 0
+    for step in range(600):
+        r = rng.random()
+        if r < 0.25 and m.has_free_slot():
+            m.add_request(next_id)
+            live[next_id] = 0
+            next_id += 1
+        elif r < 0.85 and live:
+            rid = rng.choice(list(live))
+            n = rng.choice([1, 1, 1, 2, 5, 13])
+            if m.can_reserve(rid, n):
+                m.reserve(rid, n)
+                m.commit(rid, n)
+                live[rid] += n
+            else:
+                with pytest.raises(OutOfPages):
+                    m.reserve(rid, n)
+        elif live:
+            rid = rng.choice(list(live))
+            m.free_request(rid)
+            del live[rid]
+        m.check_invariants()
+        for rid, n in live.items():
+            assert m.get(rid).num_tokens == n
+            full = m.block_table(rid, 0)
+            assert len(full) == (n + 3) // 4 and all(p >= 0 for p in full)
+            # every key the next query can see in the window group still has its page
+            win = m.block_table(rid, 1)
+            for j in range(max(0, n - 24 + 1), n):
+                assert win[j // 4] >= 0
+    for rid in list(live):
+        m.free_request(rid)
+    assert m.free_pages() == {0: 40, 1: 40}
+    m.check_invariants()

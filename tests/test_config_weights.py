@@ -1,0 +1,230 @@
+"""Configuration, registry, safetensors files and weight errors (no GPU)."""
+import json
+import os
+import struct
+
+import pytest
+import torch
+
+from airun_b200.config import (ConfigError, Qwen3Config, load_config, lookup_architecture,
+                               registered_architectures)
+from airun_b200.engine.model import DecoderModel
+from airun_b200.weights import (DictSource, SafetensorsError, SafetensorsFolder, WeightError, check_source,
+                                load_tensors, random_tensors, write_model_folder, write_safetensors)
+from helpers import TINY
+
+
+def test_defaults_and_derived_sizes():
+    c = Qwen3Config.from_dict(dict(architectures=["Qwen3ForCausalLM"], vocab_size=1000, hidden_size=128,
+                                   num_hidden_layers=2, num_attention_heads=8, intermediate_size=256))
+    assert c.num_key_value_heads == 8 and c.head_dim == 16
+    assert c.rms_norm_eps == 1e-6 and c.rope_theta == 10000.0 and c.max_position_embeddings == 4096
+    assert not c.tie_word_embeddings and c.layer_windows == ()
+    assert c.q_dim == 128 and c.kv_dim == 128 and c.gqa_ratio == 1
+    assert c.kv_bytes_per_token(2) == 2 * 128 * 2 * 2
+
+
+def test_8b_shape_cache_bytes():
+    c = Qwen3Config.from_dict(dict(architectures=["Qwen3ForCausalLM"], vocab_size=151936, hidden_size=4096,
+                                   num_hidden_layers=36, num_attention_heads=32, num_key_value_heads=8,
+                                   head_dim=128, intermediate_size=12288))
+    assert c.kv_bytes_per_token(2) == 147456          # 144 KiB per token in bfloat16
+    assert c.attn_scale == 128 ** -0.5
+
+
+def test_missing_keys_are_all_named():
+    with pytest.raises(ConfigError) as e:
+        Qwen3Config.from_dict(dict(architectures=["Qwen3ForCausalLM"], hidden_size=64))
+    msg = str(e.value)
+    for k in ("vocab_size", "num_hidden_layers", "num_attention_heads", "intermediate_size"):
+        assert k in msg
+
+
+def test_every_problem_is_listed():
+    bad = dict(TINY["A"]["cfg"], num_key_value_heads=3, head_dim=15, rope_scaling={"type": "yarn"},
+               attention_bias=True, hidden_act="gelu")
+    with pytest.raises(ConfigError) as e:
+        Qwen3Config.from_dict(bad)
+    msg = str(e.value)
+    for frag in ("multiple of num_key_value_heads", "head_dim", "rope_scaling", "attention_bias", "hidden_act"):
+        assert frag in msg
+
+
+def test_windows_from_layer_types_and_max_window_layers():
+    c = Qwen3Config.from_dict(TINY["C"]["cfg"])
+    assert c.layer_windows == (0, 24, 0, 24)
+    d = dict(TINY["C"]["cfg"])
+    del d["layer_types"]
+    d["max_window_layers"] = 3
+    assert Qwen3Config.from_dict(d).layer_windows == (0, 0, 0, 24)
+    d["use_sliding_window"] = False
+    assert Qwen3Config.from_dict(d).layer_windows == ()
+
+
+def test_round_trip_and_registry(tmp_path):
+    for name, spec in TINY.items():
+        c = Qwen3Config.from_dict(spec["cfg"])
+        assert Qwen3Config.from_dict(c.to_dict()) == c
+    assert "Qwen3ForCausalLM" in registered_architectures()
+    with pytest.raises(ConfigError) as e:
+        lookup_architecture("NoSuchModel")
+    assert "Qwen3ForCausalLM" in str(e.value)
+    with pytest.raises(ConfigError):
+        load_config(str(tmp_path))
+    (tmp_path / "config.json").write_text("{not json")
+    with pytest.raises(ConfigError):
+        load_config(str(tmp_path))
+
+
+def test_layer_specs_carry_every_constant():
+    c = Qwen3Config.from_dict(TINY["C"]["cfg"])
+    specs = c.layer_specs()
+    assert len(specs) == 4
+    assert specs[1].mixer_args["window"] == 24 and specs[0].mixer_args["window"] == 0
+    assert specs[0].mixer_args["position_args"] == dict(rotary_dim=48, theta=500000.0)
+    assert specs[0].norm_args == dict(size=80, eps=3e-6)
+    assert specs[0].ffn_args == dict(hidden_size=80, intermediate_size=176)
+
+
+def _model(name="A"):
+    cfg = Qwen3Config.from_dict(TINY[name]["cfg"])
+    return cfg, DecoderModel(cfg, torch.float32, "cpu")
+
+
+def test_weight_names_of_the_architecture():
+    cfg, m = _model("B")
+    names = {s.name for s in m.weight_specs()}
+    assert "model.embed_tokens.weight" in names and "lm_head.weight" in names and "model.norm.weight" in names
+    for l in range(3):
+        for suffix in ("input_layernorm.weight", "post_attention_layernorm.weight", "self_attn.q_proj.weight",
+                       "self_attn.k_proj.weight", "self_attn.v_proj.weight", "self_attn.o_proj.weight",
+                       "self_attn.q_norm.weight", "self_attn.k_norm.weight", "mlp.gate_proj.weight",
+                       "mlp.up_proj.weight", "mlp.down_proj.weight"):
+            assert f"model.layers.{l}.{suffix}" in names
+    shapes = {s.name: s.shape for s in m.weight_specs()}
+    assert shapes["model.layers.0.self_attn.q_proj.weight"] == (256, 96)       # heads*head_dim != hidden
+    assert shapes["model.layers.0.self_attn.k_proj.weight"] == (32, 96)
+    assert shapes["model.layers.0.self_attn.o_proj.weight"] == (96, 256)
+    _, tied = _model("A")
+    assert "lm_head.weight" not in {s.name for s in tied.weight_specs()}
+
+
+def test_one_error_lists_missing_unexpected_and_wrong_shapes():
+    cfg, m = _model("A")
+    t = random_tensors(m.weight_specs(), 1)
+    del t["model.layers.1.mlp.up_proj.weight"]
+    del t["model.norm.weight"]
+    t["model.layers.0.self_attn.q_proj.weight"] = torch.zeros(10, 10, dtype=torch.bfloat16)
+    t["model.layers.7.extra.weight"] = torch.zeros(3)
+    with pytest.raises(WeightError) as e:
+        m.load(DictSource(t))
+    err = e.value
+    assert set(err.missing) == {"model.layers.1.mlp.up_proj.weight", "model.norm.weight"}
+    assert err.unexpected == ["model.layers.7.extra.weight"]
+    assert err.wrong_shape == [("model.layers.0.self_attn.q_proj.weight", (10, 10), (64, 64))]
+    msg = str(err)
+    for frag in ("missing tensors (2)", "unexpected tensors (1)", "wrong shapes (1)", "[10, 10]", "[64, 64]"):
+        assert frag in msg
+
+
+def test_tied_model_ignores_a_stored_head_and_untied_needs_it():
+    cfg, m = _model("A")
+    t = random_tensors(m.weight_specs(), 1)
+    t["lm_head.weight"] = t["model.embed_tokens.weight"].clone()
+    m.load(DictSource(t))
+    assert m.head.weight is m.embedding.table          # the table itself, not a copy
+    cfgb, mb = _model("B")
+    tb = random_tensors(mb.weight_specs(), 1)
+    del tb["lm_head.weight"]
+    with pytest.raises(WeightError) as e:
+        mb.load(DictSource(tb))
+    assert e.value.missing == ["lm_head.weight"]
+
+
+def test_storage_types():
+    cfg, m = _model("A")
+    specs = m.weight_specs()
+    t = random_tensors(specs, 1)
+    assert t["model.embed_tokens.weight"].dtype == torch.bfloat16
+    assert t["model.norm.weight"].dtype == torch.float32
+    bf = load_tensors(specs, DictSource(t), torch.bfloat16, "cpu")
+    assert bf["model.layers.0.mlp.down_proj.weight"].dtype == torch.bfloat16
+    assert bf["model.layers.0.input_layernorm.weight"].dtype == torch.float32     # stored in 32-bit, stays so
+    f32 = load_tensors(specs, DictSource(t), torch.float32, "cpu")
+    assert f32["model.layers.0.mlp.down_proj.weight"].dtype == torch.float32
+    assert torch.equal(f32["model.layers.0.mlp.down_proj.weight"],
+                       t["model.layers.0.mlp.down_proj.weight"].float())
+    from airun_b200.weights.loader import WeightSpec, stored_dtype
+    assert stored_dtype(WeightSpec("t", (4,), storage="as_stored"), torch.int64, torch.bfloat16) == torch.int32
+    assert stored_dtype(WeightSpec("t", (4,), storage="as_stored"), torch.float32, torch.bfloat16) == torch.float32
+    assert stored_dtype(WeightSpec("t", (4,), storage="as_stored"), torch.bfloat16, torch.bfloat16) == torch.bfloat16
+
+
+def test_random_weights_are_seeded_and_independent_of_order():
+    cfg, m = _model("A")
+    specs = m.weight_specs()
+    a = random_tensors(specs, 5)
+    b = random_tensors(list(reversed(specs)), 5)
+    c = random_tensors(specs, 6)
+    for n in a:
+        assert torch.equal(a[n], b[n])
+    assert not torch.equal(a["model.embed_tokens.weight"], c["model.embed_tokens.weight"])
+    w = a["model.layers.0.mlp.gate_proj.weight"].float()
+    assert abs(float(w.std()) - 0.02) < 0.002
+    nw = a["model.layers.0.input_layernorm.weight"]
+    assert abs(float(nw.mean()) - 1.0) < 0.05 and 0.05 < float(nw.std()) < 0.15
+
+
+def test_model_folder_round_trip(tmp_path):
+    cfg, m = _model("B")
+    d = str(tmp_path / "m")
+    write_model_folder(d, cfg, m.weight_specs(), seed=9)
+    assert load_config(d) == cfg
+    folder = SafetensorsFolder(d)
+    want = random_tensors(m.weight_specs(), 9)
+    assert set(folder.names()) == set(want)
+    for n in want:
+        assert torch.equal(folder.read(n), want[n])
+    from safetensors.torch import load_file          # an independent reader agrees
+    other = load_file(os.path.join(d, "model.safetensors"))
+    for n in want:
+        assert torch.equal(other[n], want[n])
+    m.load(folder)
+    folder.close()
+
+
+def test_broken_safetensors_files(tmp_path):
+    p = tmp_path / "model.safetensors"
+    p.write_bytes(b"\x01\x02")
+    with pytest.raises(SafetensorsError):
+        SafetensorsFolder(str(tmp_path))
+    p.write_bytes(struct.pack("<Q", 1 << 40) + b"{}")
+    with pytest.raises(SafetensorsError):
+        SafetensorsFolder(str(tmp_path))
+    hdr = json.dumps({"a": {"dtype": "F32", "shape": [4], "data_offsets": [0, 16]}}).encode()
+    p.write_bytes(struct.pack("<Q", len(hdr)) + hdr + b"\0" * 8)          # payload truncated
+    with pytest.raises(SafetensorsError) as e:
+        SafetensorsFolder(str(tmp_path))
+    assert "truncated" in str(e.value)
+    hdr = json.dumps({"a": {"dtype": "F32", "shape": [5], "data_offsets": [0, 16]}}).encode()
+    p.write_bytes(struct.pack("<Q", len(hdr)) + hdr + b"\0" * 16)         # count does not match the span
+    with pytest.raises(SafetensorsError):
+        SafetensorsFolder(str(tmp_path))
+    hdr = json.dumps({"a": {"dtype": "Q4", "shape": [4], "data_offsets": [0, 16]}}).encode()
+    p.write_bytes(struct.pack("<Q", len(hdr)) + hdr + b"\0" * 16)
+    with pytest.raises(SafetensorsError):
+        SafetensorsFolder(str(tmp_path))
+    os.unlink(p)
+    with pytest.raises(SafetensorsError):
+        SafetensorsFolder(str(tmp_path))
+
+
+def test_sharded_folder(tmp_path):
+    write_safetensors(str(tmp_path / "s1.safetensors"), {"a": torch.arange(4.0)})
+    write_safetensors(str(tmp_path / "s2.safetensors"), {"b": torch.arange(3, dtype=torch.int64)})
+    (tmp_path / "model.safetensors.index.json").write_text(json.dumps(
+        {"weight_map": {"a": "s1.safetensors", "b": "s2.safetensors"}}))
+    f = SafetensorsFolder(str(tmp_path))
+    assert sorted(f.names()) == ["a", "b"]
+    assert torch.equal(f.read("b"), torch.arange(3, dtype=torch.int64))
+    f.close()
