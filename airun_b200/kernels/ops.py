@@ -52,8 +52,12 @@ def _cuda(*ts: Optional[torch.Tensor]) -> None:
             _need(t.is_cuda, "kernel arguments must live on the GPU (there is no CPU path)")
 
 
+LAUNCHES = [0]          # kernels launched through this module (CUDA-graph replays are counted by their owner)
+
+
 def _check(status: int, what: str) -> None:
     if status == 0:
+        LAUNCHES[0] += 1
         return
     if status == 1000:
         raise KernelError(f"{what}: the kernel refuses these sizes or pointers")

@@ -1,0 +1,299 @@
+#!/usr/bin/env python3
+"""Benchmark: decode tokens a second of the Qwen3-8B shape on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--batch B] [--context C]
+
+A step is one decode step of a batch of requests whose contexts stand at
+``context`` tokens.  Weights are random N(0, 0.02); the caches are filled with
+random keys and values (synthetic data) so that no time goes to prefilling them.
+Prints ONE JSON line: ``value`` is the device-timed decode rate of the step
+function, ``e2e`` the rate through the Python entry point (scheduler, sampling,
+host tokens in and out), ``prefill`` a 2,048-token prompt in one step,
+``roofline`` the bytes a decode step must read over its time, ``points`` the
+decode rate at batch 1 and 64.  ``--impl reference`` reports that the reference
+cannot be installed here.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+QWEN3_8B = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=151936, hidden_size=4096,
+                num_hidden_layers=36, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+                intermediate_size=12288, max_position_embeddings=40960, rms_norm_eps=1e-6,
+                rope_theta=1000000.0, tie_word_embeddings=False)
+FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0)
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(p):
+        try:
+            with open(p) as f:
+                d = json.load(f)
+            return dict(hbm_gbs=float(d["hbm_gbs"]), bf16_tflops=float(d["bf16_tflops"]),
+                        bf16_tflops_sustained=float(d.get("bf16_tflops_sustained", d["bf16_tflops"])),
+                        source="measured")
+        except (KeyError, ValueError, TypeError):
+            pass
+    return dict(FALLBACK_PEAKS, bf16_tflops_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region is timed."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.lines, self.proc = [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        sm, mx, reasons = [], 0, set()
+        for l in self.lines:
+            parts = [x.strip() for x in l.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(int(parts[0]))
+                mx = max(mx, int(parts[1]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return dict(sm_mhz=int(statistics.median(sm)) if sm else None, sm_max_mhz=mx or None,
+                    reasons=sorted(reasons), samples=len(sm))
+
+
+def decode_bytes(cfg, n_layers, batch, context, esz=2):
+    """Bytes one decode step has to read: every weight it uses once (the embedding rows
+    of the batch, not the table) and the cache of the live requests."""
+    H, I, V = cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size
+    per_layer = (cfg.q_dim + 2 * cfg.kv_dim) * H + H * cfg.q_dim + 3 * H * I
+    weights = (n_layers * per_layer + V * H) * esz + batch * H * esz
+    norms = (n_layers * (2 * H + 2 * cfg.head_dim) + H) * 4
+    kv = batch * context * 2 * cfg.kv_dim * esz * n_layers
+    return weights + norms + kv
+
+
+def prefill_flops(cfg, n_layers, T):
+    H, I, V = cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size
+    per_layer = (cfg.q_dim + 2 * cfg.kv_dim) * H + H * cfg.q_dim + 3 * H * I
+    gemm = 2.0 * T * n_layers * per_layer + 2.0 * V * H
+    attn = n_layers * cfg.num_attention_heads * 4.0 * cfg.head_dim * T * (T + 1) / 2
+    return gemm + attn
+
+
+def fill_contexts(eng, rids, context, seed=0):
+    """Gives every request ``context`` tokens of random keys and values without running the model."""
+    import torch
+    g = torch.Generator(device=eng.device)
+    g.manual_seed(seed)
+    for rid in rids:
+        if rid not in eng.manager.requests:
+            eng.manager.add_request(rid)
+        eng.manager.reserve(rid, context)
+        eng.manager.commit(rid, context)
+    for pool in eng.storage.paged:
+        for layer in range(pool.shape[0]):
+            pool[layer].copy_(torch.randn(pool[layer].shape, generator=g, device=eng.device, dtype=torch.float32)
+                              .mul_(0.5).to(pool.dtype))
+
+
+def time_decode(eng, batch, context, steps, warmup, tag):
+    """Device time of ``steps`` decode steps of ``batch`` requests standing at ``context``."""
+    import torch
+    from airun_b200 import StepEntry
+    from airun_b200.kernels import ops
+    rids = [f"{tag}{i}" for i in range(batch)]
+    fill_contexts(eng, rids, context - steps - warmup - 1)
+    V = eng.config.vocab_size
+    toks = torch.randint(0, V, (steps + warmup + 1, batch), generator=torch.Generator().manual_seed(1)).tolist()
+    picked = torch.zeros(batch, dtype=torch.int32, device=eng.device)
+
+    def one(i):
+        logits = eng.runner.step([StepEntry(r, [toks[i][j]], (0,)) for j, r in enumerate(rids)])
+        ops.sample(logits, picked)
+
+    for i in range(warmup):
+        one(i)
+    torch.cuda.synchronize()
+    l0 = ops.LAUNCHES[0] + getattr(eng.runner, "graph_launches", 0)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for i in range(warmup, warmup + steps):
+        one(i)
+    ev1.record()
+    torch.cuda.synchronize()
+    launches = ops.LAUNCHES[0] + getattr(eng.runner, "graph_launches", 0) - l0
+    ms = ev0.elapsed_time(ev1) / steps
+    eng.runner.raise_on_device_error()
+    for r in rids:
+        eng.manager.free_request(r)
+    return ms, launches
+
+
+def time_e2e(eng, batch, context, steps, warmup):
+    """The same decode through the Python entry point: requests live in the scheduler, every step
+    copies the step's inputs from pinned host memory and reads the sampled tokens back."""
+    import torch
+    from airun_b200 import SamplingParams
+    from airun_b200.engine.scheduler import Request
+    rids = [f"e{i}" for i in range(batch)]
+    start = context - steps - warmup - 1
+    fill_contexts(eng, rids, start - 1)
+    g = torch.Generator().manual_seed(2)
+    reqs = []
+    for rid in rids:
+        prompt = torch.randint(0, eng.config.vocab_size, (start,), generator=g).tolist()
+        r = Request(rid, prompt, SamplingParams.greedy(), steps + warmup + 8)
+        r.num_computed = start - 1                # its cache stands one token short of the prompt
+        eng.scheduler.running.append(r)
+        reqs.append(r)
+    for _ in range(warmup):
+        eng.run_step()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        eng.run_step()
+    torch.cuda.synchronize()
+    ms = (time.perf_counter() - t0) * 1e3 / steps
+    assert all(len(r.output) == steps + warmup for r in reqs), "the entry point did not decode every step"
+    for r in reqs:
+        eng.scheduler._finish(r, "bench")
+    h2d = eng.runner.meta_host.numel() * 4 + eng._small_host.numel() * 4
+    d2h = eng._picked_host.numel() * 4
+    return ms, h2d, d2h
+
+
+def time_prefill(eng, T, runs=3):
+    import torch
+    from airun_b200 import StepEntry
+    toks = torch.randint(0, eng.config.vocab_size, (T,), generator=torch.Generator().manual_seed(3)).tolist()
+    times = []
+    for i in range(runs + 1):
+        rid = f"p{i}"
+        eng.manager.add_request(rid)
+        torch.cuda.synchronize()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        eng.runner.step([StepEntry(rid, toks, (T - 1,))])
+        ev1.record()
+        torch.cuda.synchronize()
+        times.append(ev0.elapsed_time(ev1))
+        eng.manager.free_request(rid)
+    eng.runner.raise_on_device_error()
+    return statistics.median(times[1:])
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=16)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--layers", type=int, default=None, help="layers to build (default: all 36)")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=4096)
+    ap.add_argument("--dtype", default="bfloat16")
+    ap.add_argument("--skip-points", action="store_true")
+    a = ap.parse_args()
+    if a.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference is a Rust workspace (no setup.py or pyproject.toml: pip reports "
+                          "'not installable') and neither cargo nor rustc is in this image"}))
+        return 0
+    if a.gpus != 1:
+        print(f"bench.py measures one GPU; --gpus {a.gpus} is not supported (the engine is single-GPU)")
+        return 2
+    a.warmup = max(a.warmup, 3)
+
+    import torch
+    from airun_b200 import Engine, EngineOptions, Qwen3Config
+    d = dict(QWEN3_8B)
+    full_layers = d["num_hidden_layers"]
+    if a.layers:
+        d["num_hidden_layers"] = a.layers
+    cfg = Qwen3Config.from_dict(d)
+    L = cfg.num_hidden_layers
+    pk = peaks()
+    max_batch = max(64, a.batch)
+    cache_tokens = max_batch * a.context + 4096
+    eng = Engine.from_config(cfg, seed=0, options=EngineOptions(
+        dtype=a.dtype, page_size=16, cache_tokens=cache_tokens, max_batch_tokens=2048,
+        max_requests=max_batch, max_context=a.context))
+    esz = 2 if a.dtype == "bfloat16" else 4
+
+    sampler = ClockSampler()
+    sampler.start()
+    ms, launches = time_decode(eng, a.batch, a.context, a.steps, a.warmup, "d")
+    clocks = sampler.stop()
+    value = a.batch / (ms / 1e3)
+
+    e2e_ms, h2d, d2h = time_e2e(eng, a.batch, a.context, a.steps, a.warmup)
+    points = {}
+    if not a.skip_points:
+        for b in (1, 64):
+            pms, _ = time_decode(eng, b, a.context, max(4, a.steps // 2), a.warmup, f"b{b}_")
+            points[f"decode_b{b}"] = round(b / (pms / 1e3), 2)
+    T = 2048
+    pre_ms = time_prefill(eng, T)
+    peak_flops = pk["bf16_tflops"] * 1e12 if a.dtype == "bfloat16" else None
+    pre = {"value": round(T / (pre_ms / 1e3), 1), "tokens": T, "ms": round(pre_ms, 3),
+           "frac": round(prefill_flops(cfg, L, T) / (pre_ms / 1e3) / peak_flops, 4) if peak_flops else None}
+    gbs = decode_bytes(cfg, L, a.batch, a.context, esz) / (ms / 1e3) / 1e9
+    out = {
+        "metric": "Qwen3-8B decode tok/s @ batch 8, context 4096", "value": round(value, 2), "unit": "tokens/s",
+        "n_gpus": 1, "steps": a.steps, "warmup": a.warmup, "ms_per_step": round(ms, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16" if a.dtype == "bfloat16" else "fp32", "data": "synthetic", "impl": "ours",
+        "config": {"model": "Qwen3-8B shape, random weights", "layers": L, "layers_full": full_layers,
+                   "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads,
+                   "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
+                   "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
+                   "global_batch": a.batch, "seq_len": a.context, "page_size": 16, "parallelism": "single GPU",
+                   "l2": "inputs larger than L2 (weights and cache are read once per step)",
+                   "peaks": pk["source"]},
+        "e2e": {"value": round(a.batch / (e2e_ms / 1e3), 2), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": launches,
+        "prefill": pre,
+        "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(gbs / pk["hbm_gbs"], 4)},
+        "points": points,
+        "clocks": clocks,
+    }
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,103 @@
+"""Generation through the Python entry point and the command line, on the GPU."""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as P
+from helpers import ROOT, TINY, make_model_folder, random_tokens
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    root = tmp_path_factory.mktemp("gen_models")
+    return {n: make_model_folder(n, str(root)) for n in TINY}
+
+
+@pytest.mark.parametrize("name", list(TINY))
+def test_greedy_generation_matches_the_plain_implementation(name, folders):
+    import airun_b200
+    cfg, W = P.read_model_folder(folders[name])
+    prompts = [random_tokens(n, cfg["vocab_size"], 50 + i) for i, n in enumerate((5, 17, 33))]
+    want = [P.plain_greedy_generate(cfg, W, p, 16) for p in prompts]
+    eng = airun_b200.Engine.from_folder(folders[name], dtype="float32", page_size=TINY[name]["page_size"],
+                                        cache_tokens=512, max_batch_tokens=24, max_requests=4)
+    got = eng.generate(prompts, airun_b200.SamplingParams.greedy(), max_new_tokens=16)
+    assert [g.token_ids for g in got] == want
+    assert all(g.finish_reason == "MaxTokens" for g in got)
+    one = eng.generate(prompts[1], airun_b200.SamplingParams.greedy(), max_new_tokens=16)
+    assert one.token_ids == want[1]                      # alone or in a batch: the same tokens
+    assert eng.manager.free_pages() == {g.gid: eng.manager.num_pages for g in eng.manager.paged}
+
+
+def test_generation_survives_preemption(folders):
+    """A pool too small for all requests at once: some are preempted and recomputed, and
+    every request still gets the tokens it gets when it runs alone."""
+    import airun_b200
+    name = "B"
+    cfg, W = P.read_model_folder(folders[name])
+    prompts = [random_tokens(n, cfg["vocab_size"], 80 + i) for i, n in enumerate((30, 26, 22, 18))]
+    want = [P.plain_greedy_generate(cfg, W, p, 12) for p in prompts]
+    eng = airun_b200.Engine.from_folder(folders[name], dtype="float32", page_size=8, num_pages=14,
+                                        max_batch_tokens=32, max_requests=4, max_context=112)
+    got = eng.generate(prompts, airun_b200.SamplingParams.greedy(), max_new_tokens=12)
+    assert [g.token_ids for g in got] == want
+    assert eng.scheduler.stats["preemptions"] >= 1
+    eng.manager.check_invariants()
+
+
+def test_temperature_sampling_is_seeded_and_independent_of_the_batch(folders):
+    import airun_b200
+    name = "B"
+    cfg, _ = P.read_model_folder(folders[name])
+    prompts = [random_tokens(n, cfg["vocab_size"], 90 + i) for i, n in enumerate((70, 12, 9))]
+    eng = airun_b200.Engine.from_folder(folders[name], dtype="float32", page_size=8, cache_tokens=1024,
+                                        max_batch_tokens=24, max_requests=4)
+    params = [airun_b200.SamplingParams.temperature_only(0.8, seed=100 + i) for i in range(3)]
+    a = eng.generate(prompts, params, max_new_tokens=10)
+    b = eng.generate(prompts, params, max_new_tokens=10)
+    assert [x.token_ids for x in a] == [x.token_ids for x in b]
+    alone = eng.generate(prompts[0], params[0], max_new_tokens=10)
+    assert alone.token_ids == a[0].token_ids
+    other = eng.generate(prompts[0], airun_b200.SamplingParams.temperature_only(0.8, seed=999), max_new_tokens=10)
+    assert len(other.token_ids) == 10
+    full = airun_b200.SamplingParams(seed=5)              # the whole chain runs on the host
+    c = eng.generate(prompts[1], full, max_new_tokens=8)
+    d = eng.generate(prompts[1], airun_b200.SamplingParams(seed=5), max_new_tokens=8)
+    assert c.token_ids == d.token_ids and len(c.token_ids) == 8
+
+
+def test_end_token_stops_and_is_not_emitted(folders):
+    import airun_b200
+    cfg, W = P.read_model_folder(folders["B"])
+    prompt = random_tokens(15, cfg["vocab_size"], 7)
+    want = P.plain_greedy_generate(cfg, W, prompt, 8)
+    eng = airun_b200.Engine.from_folder(folders["B"], dtype="float32", page_size=8, cache_tokens=256,
+                                        max_batch_tokens=64, max_requests=2)
+    stop = want[3]
+    first = want.index(stop)
+    got = eng.generate(prompt, airun_b200.SamplingParams.greedy(), max_new_tokens=8, eog_tokens=[stop])
+    assert got.token_ids == want[:first] and got.finish_reason == "EndOfGeneration"
+
+
+def test_command_line(folders, tmp_path):
+    cfg, W = P.read_model_folder(folders["A"])
+    prompt = random_tokens(9, cfg["vocab_size"], 3)
+    want = P.plain_greedy_generate(cfg, W, prompt, 6)
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "airun"), "run", folders["A"],
+                          "-p", ",".join(map(str, prompt)), "-n", "6", "--temp", "0", "--repeat-penalty", "1.0",
+                          "--dtype", "float32", "--cache-tokens", "256", "-q"],
+                         capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr
+    assert [int(t) for t in out.stdout.strip().split(",")] == want
+
+
+def test_smoke_entry():
+    sys.path.insert(0, ROOT)
+    import __graft_entry__ as g
+    g.smoke()
