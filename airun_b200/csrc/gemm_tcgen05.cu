@@ -1,0 +1,488 @@
+// bfloat16 matrix product on the 5th-generation tensor cores:
+//   out[M][N] = x[M][K] * W[N][K]^T, float32 accumulation in tensor memory.
+//
+// One CTA computes one 128 x BN tile D = A * B^T of two K-major operands
+// ("rows of K contiguous values"), over one slice of K:
+//   warp 0   : one thread issues TMA loads (cp.async.bulk.tensor, 128-byte
+//              swizzle) of A and B blocks of 64 k-values into a ring of stages;
+//   warp 1   : allocates tensor memory; one thread issues tcgen05.mma
+//              (M=128, N=BN, K=16, four per block) and commits to mbarriers;
+//   warps 2-5: read the accumulator with tcgen05.ld, apply the epilogue, store.
+// Which operand is A decides the mode:
+//   normal (prompt portions): A = activations (128 tokens), B = weights (BN rows);
+//   swapped (few tokens)    : A = weights (128 rows), B = activations (BN >= tokens),
+//                             so a decode step streams each weight once and wastes
+//                             no tensor-core rows on padding.
+// With ksplit > 1 the CTAs of one tile each write a float32 partial tile to a
+// scratch buffer; the last one to finish (a counter per tile) adds the partials
+// in slice order and runs the epilogue, so the result does not depend on timing.
+// Epilogues: float32 store, bfloat16 store, SwiGLU (columns alternate between
+// blocks of 16 gate and 16 up values; out = silu(g) * u as bfloat16).
+//
+// Every wait on an mbarrier is bounded: when it runs out the kernel sets an
+// error bit, skips the rest of its work, frees its tensor memory and returns.
+// No cluster launch and no multicast are used.
+//
+// The reference's counterparts are its wmma prefill GEMM and its half-precision
+// matvec kernels (crates/airun-cuda/kernels/matmul.cu:518-636, :1498-1563); its
+// fused gate/up/SwiGLU decode kernel is matmul.cu:150-214.
+#include "common.cuh"
+#include <cuda.h>
+#include <mutex>
+#include <unordered_map>
+#include <string>
+#include <cstring>
+
+#define BM 128
+#define BK 64
+#define EPI_F32 0
+#define EPI_BF16 1
+#define EPI_SWIGLU 2
+#define GEMM_THREADS 192
+#define WAIT_LIMIT_NS 2000000000ull
+
+namespace {
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait; false when about two seconds have passed without the phase completing.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (int i = 0; i < 64; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_ns();
+    for (;;) {
+        for (int i = 0; i < 256; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (global_ns() - t0 > WAIT_LIMIT_NS) return false;
+    }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 bf16) with the
+// 128-byte swizzle: 8-row groups 1024 bytes apart, version 1, layout type SWIZZLE_128B.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr >> 4) & 0x3FFF);
+    d |= (uint64_t)1 << 16;                 // leading byte offset (unused with swizzle)
+    d |= (uint64_t)(1024 >> 4) << 32;       // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;                 // descriptor version
+    d |= (uint64_t)2 << 61;                 // SWIZZLE_128B
+    return d;
+}
+
+__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + __expf(-g)) * u; }
+
+struct GemmParams {
+    int a_rows, b_rows, K;        // extents of the A and B operands
+    int k_blocks_per_split;       // blocks of 64 k-values per slice
+    int ksplit;
+    void* out;
+    long long ldc;                // output row stride in elements
+    float* scratch;               // [tiles][ksplit][BN][128] partial tiles
+    int* counters;                // [tiles], zero between launches
+    int* err;
+};
+
+template <int BN, int STAGES>
+struct SmemLayout {
+    static constexpr int A_BYTES = BM * BK * 2;
+    static constexpr int B_BYTES = BN * BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+    static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 1) * 8 + 16 + 1024;   // + alignment slack
+};
+
+// Epilogue for 16 consecutive accumulator columns [c0, c0+16) of this thread's row.
+template <int EPI, bool SWAP>
+__device__ __forceinline__ void store_chunk(const GemmParams& p, const float* v, int a_row, int b0, int c0) {
+    // normal: out[a_row][b0 + c0 + i];  swapped: out[b0 + c0 + i][a_row]
+    if (!SWAP) {
+        if (a_row >= p.a_rows) return;
+        const int n0 = b0 + c0;
+        if (EPI == EPI_F32) {
+            float* o = (float*)p.out + (size_t)a_row * p.ldc + n0;
+            if (n0 + 16 <= p.b_rows && (((size_t)o) & 15) == 0) {
+#pragma unroll
+                for (int i = 0; i < 16; i += 4) *reinterpret_cast<float4*>(o + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) if (n0 + i < p.b_rows) o[i] = v[i];
+            }
+        } else {
+            __nv_bfloat16* o = (__nv_bfloat16*)p.out + (size_t)a_row * p.ldc + n0;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) if (n0 + i < p.b_rows) o[i] = __float2bfloat16_rn(v[i]);
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const int tok = b0 + c0 + i;
+            if (tok < p.b_rows && a_row < p.a_rows) {
+                if (EPI == EPI_F32) ((float*)p.out)[(size_t)tok * p.ldc + a_row] = v[i];
+                else ((__nv_bfloat16*)p.out)[(size_t)tok * p.ldc + a_row] = __float2bfloat16_rn(v[i]);
+            }
+        }
+    }
+}
+
+// SwiGLU, normal mode: g = columns [c0, c0+16), u = columns [c0+16, c0+32) of this row.
+__device__ __forceinline__ void store_swiglu_normal(const GemmParams& p, const float* g, const float* u,
+                                                    int a_row, int b0, int c0) {
+    if (a_row >= p.a_rows) return;
+    const int n_out = (b0 + c0) / 2;
+    __nv_bfloat16* o = (__nv_bfloat16*)p.out + (size_t)a_row * p.ldc + n_out;
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+        if (b0 + c0 + 16 + i < p.b_rows) o[i] = __float2bfloat16_rn(silu_mul(g[i], u[i]));
+}
+
+// SwiGLU, swapped mode: this lane's row is a gate row when (a_row / 16) is even, and lane + 16
+// holds the matching up row.  v: 16 columns (tokens).
+__device__ __forceinline__ void store_swiglu_swapped(const GemmParams& p, const float* v, int a_row, int b0, int c0) {
+    const int lane = threadIdx.x & 31;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const float up = __shfl_down_sync(0xffffffffu, v[i], 16);
+        const int tok = b0 + c0 + i;
+        if (lane < 16 && tok < p.b_rows && a_row < p.a_rows) {
+            const int n_out = (a_row / 32) * 16 + (a_row % 32);
+            ((__nv_bfloat16*)p.out)[(size_t)tok * p.ldc + n_out] = __float2bfloat16_rn(silu_mul(v[i], up));
+        }
+    }
+}
+
+template <int BN, int STAGES, int EPI, bool SWAP>
+__global__ __launch_bounds__(GEMM_THREADS, 1) void gemm_tcgen05_kernel(
+    const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
+    using L = SmemLayout<BN, STAGES>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = (uint64_t*)(smem + L::BAR_OFFSET);
+    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 1);
+    __shared__ int s_ticket;
+    __shared__ int s_abort;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int a0 = blockIdx.x * BM;            // first A row of the tile
+    const int b0 = blockIdx.y * BN;            // first B row of the tile
+    const int split = blockIdx.z;
+    const int kb_total = (p.K + BK - 1) / BK;
+    const int kb_begin = split * p.k_blocks_per_split;
+    int kb_end = kb_begin + p.k_blocks_per_split;
+    if (kb_end > kb_total) kb_end = kb_total;
+    const int n_kb = kb_end > kb_begin ? kb_end - kb_begin : 0;
+    constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+
+    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES), accum = smem_u32(bars + 2 * STAGES);
+    if (threadIdx.x == 0) {
+        s_abort = 0;
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        mbar_init(accum, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int i = 0; i < n_kb; ++i) {
+                const int s = i % STAGES;
+                const uint32_t phase = (i / STAGES) & 1;
+                if (!mbar_wait(empty0 + 8 * s, phase ^ 1)) { atomicOr(p.err, AIRUN_DEV_TIMEOUT); s_abort = 1; break; }
+                mbar_expect_tx(full0 + 8 * s, L::STAGE_BYTES);
+                const uint32_t sa = smem_u32(smem + s * L::STAGE_BYTES);
+                const int k = (kb_begin + i) * BK;
+                tma_load_2d(sa, &map_a, full0 + 8 * s, k, a0);
+                tma_load_2d(sa + L::A_BYTES, &map_b, full0 + 8 * s, k, b0);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            bool ok = true;
+            for (int i = 0; i < n_kb && ok; ++i) {
+                const int s = i % STAGES;
+                const uint32_t phase = (i / STAGES) & 1;
+                if (!mbar_wait(full0 + 8 * s, phase)) { atomicOr(p.err, AIRUN_DEV_TIMEOUT); s_abort = 1; ok = false; break; }
+                tc_fence_after();
+                const uint32_t sa = smem_u32(smem + s * L::STAGE_BYTES);
+                const uint64_t da = smem_desc_sw128(sa), db = smem_desc_sw128(sa + L::A_BYTES);
+#pragma unroll
+                for (int k = 0; k < BK / 16; ++k)
+                    umma_bf16(tmem_base, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (i > 0 || k > 0) ? 1u : 0u);
+                umma_commit(empty0 + 8 * s);      // the stage is free once these MMAs have read it
+            }
+            umma_commit(accum);                   // arrives when every MMA issued so far is complete
+        }
+    } else {
+        // epilogue warps 2..5: warp w may touch the 32 TMEM lanes of quadrant w % 4
+        const int quad = warp & 3;
+        const int a_row = a0 + quad * 32 + lane;
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
+        bool ok = n_kb == 0 ? true : mbar_wait(accum, 0);
+        if (!ok) { atomicOr(p.err, AIRUN_DEV_TIMEOUT); }
+        tc_fence_after();
+        const bool direct = p.ksplit == 1;
+        bool last = true;
+        float* part = nullptr;
+        const int tile = blockIdx.y * gridDim.x + blockIdx.x;
+        if (!direct) {
+            part = p.scratch + ((size_t)tile * p.ksplit + split) * (BN * BM);
+            if (ok) {
+                for (int c = 0; c < BN; c += 16) {
+                    float v[16];
+                    if (n_kb > 0) tmem_ld16(lane_addr + c, v);
+                    else {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) v[i] = 0.0f;
+                    }
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) part[(size_t)(c + i) * BM + quad * 32 + lane] = v[i];
+                }
+            }
+            __threadfence();
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (threadIdx.x == 64) s_ticket = atomicAdd(p.counters + tile, 1);
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            last = s_ticket == p.ksplit - 1;
+            if (last) {
+                __threadfence();
+                if (threadIdx.x == 64) p.counters[tile] = 0;       // ready for the next launch
+            }
+        }
+        if (ok && last) {
+            const float* all = direct ? nullptr : p.scratch + (size_t)tile * p.ksplit * (BN * BM);
+            constexpr int STEP = (EPI == EPI_SWIGLU && !SWAP) ? 32 : 16;
+            for (int c = 0; c < BN; c += STEP) {
+                float v[16], u[16];
+                if (direct) {
+                    if (n_kb > 0) {
+                        tmem_ld16(lane_addr + c, v);
+                        if (STEP == 32) tmem_ld16(lane_addr + c + 16, u);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) { v[i] = 0.0f; u[i] = 0.0f; }
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) { v[i] = 0.0f; u[i] = 0.0f; }
+                    for (int s = 0; s < p.ksplit; ++s) {
+                        const float* ps = all + (size_t)s * (BN * BM) + quad * 32 + lane;
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            v[i] += __ldcg(ps + (size_t)(c + i) * BM);
+                            if (STEP == 32) u[i] += __ldcg(ps + (size_t)(c + 16 + i) * BM);
+                        }
+                    }
+                }
+                if (EPI == EPI_SWIGLU) {
+                    if (SWAP) store_swiglu_swapped(p, v, a_row, b0, c);
+                    else store_swiglu_normal(p, v, u, a_row, b0, c);
+                } else {
+                    store_chunk<EPI, SWAP>(p, v, a_row, b0, c);
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* f = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)f;
+    });
+    return fn;
+}
+
+struct MapKey {
+    const void* ptr; long long rows, K, ld; int box_rows;
+    bool operator==(const MapKey& o) const {
+        return ptr == o.ptr && rows == o.rows && K == o.K && ld == o.ld && box_rows == o.box_rows;
+    }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        size_t h = (size_t)k.ptr;
+        h = h * 1000003u ^ (size_t)k.rows;
+        h = h * 1000003u ^ (size_t)k.K;
+        h = h * 1000003u ^ (size_t)k.ld;
+        h = h * 1000003u ^ (size_t)k.box_rows;
+        return h;
+    }
+};
+
+// A tensor map of a row-major [rows][K] bfloat16 matrix with boxes of box_rows x 64.
+int make_map(CUtensorMap* out, const void* ptr, long long rows, long long K, long long ld, int box_rows) {
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    static std::mutex mu;
+    MapKey key{ptr, rows, K, ld, box_rows};
+    std::lock_guard<std::mutex> g(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) { *out = it->second; return AIRUN_OK; }
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return AIRUN_ERR_UNSUPPORTED;
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return AIRUN_ERR_ARG;
+    if (cache.size() > 8192) cache.clear();
+    cache.emplace(key, *out);
+    return AIRUN_OK;
+}
+
+template <int BN, int STAGES, int EPI, bool SWAP>
+int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, dim3 grid, cudaStream_t stream) {
+    using L = SmemLayout<BN, STAGES>;
+    static bool configured = false;
+    auto kern = gemm_tcgen05_kernel<BN, STAGES, EPI, SWAP>;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    kern<<<grid, GEMM_THREADS, L::TOTAL, stream>>>(ma, mb, p);
+    return airun_launch_status();
+}
+
+template <int EPI>
+int dispatch(bool swap, int bn, const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, dim3 grid,
+             cudaStream_t stream) {
+    if (!swap) {
+        if (bn == 128) return launch<128, 6, EPI, false>(ma, mb, p, grid, stream);
+        if (bn == 256) return launch<256, 4, EPI, false>(ma, mb, p, grid, stream);
+        return AIRUN_ERR_UNSUPPORTED;
+    }
+    if (bn == 16) return launch<16, 6, EPI, true>(ma, mb, p, grid, stream);
+    if (bn == 32) return launch<32, 6, EPI, true>(ma, mb, p, grid, stream);
+    if (bn == 64) return launch<64, 6, EPI, true>(ma, mb, p, grid, stream);
+    if (bn == 128) return launch<128, 6, EPI, true>(ma, mb, p, grid, stream);
+    return AIRUN_ERR_UNSUPPORTED;
+}
+
+}  // namespace
+
+// Scratch the caller must provide for ksplit > 1: floats and tile counters.
+AIRUN_EXPORT long long airun_gemm_tcgen05_scratch_floats(int M, int N, int swap, int bn, int ksplit) {
+    const long long a_rows = swap ? N : M, b_rows = swap ? M : N;
+    const long long tiles = ((a_rows + BM - 1) / BM) * ((b_rows + bn - 1) / bn);
+    return ksplit > 1 ? tiles * ksplit * bn * BM : 0;
+}
+
+// out[M][N] = x[M][K] * W[N][K]^T.  x, W bfloat16 row-major (K % 8 == 0, 16-byte aligned rows).
+// epi: 0 float32 out [M][N]; 1 bfloat16 out [M][N]; 2 SwiGLU, bfloat16 out [M][N/2].
+// swap: weights as the 128-row operand (bn >= M, one B tile per 'bn' tokens).
+// counters: one int per tile, zero on entry when ksplit > 1 (the kernel leaves them zero).
+AIRUN_EXPORT int airun_gemm_tcgen05(const void* x, const void* W, void* out, int M, int N, int K,
+                                    long long ldx, long long ldw, long long ldc, int epi, int swap, int bn,
+                                    int ksplit, float* scratch, int* counters, int* err, cudaStream_t stream) {
+    if (M <= 0 || N <= 0 || K <= 0 || !err) return M == 0 ? AIRUN_OK : AIRUN_ERR_ARG;
+    if (K % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0 || ((uintptr_t)x & 15) || ((uintptr_t)W & 15)) return AIRUN_ERR_ARG;
+    if (epi == EPI_SWIGLU && (N % 32 != 0)) return AIRUN_ERR_ARG;
+    if (ksplit < 1 || (ksplit > 1 && (!scratch || !counters))) return AIRUN_ERR_ARG;
+    const int kb_total = (K + BK - 1) / BK;
+    if (ksplit > kb_total) ksplit = kb_total;
+    GemmParams p;
+    p.a_rows = swap ? N : M;
+    p.b_rows = swap ? M : N;
+    p.K = K;
+    p.k_blocks_per_split = (kb_total + ksplit - 1) / ksplit;
+    p.ksplit = (kb_total + p.k_blocks_per_split - 1) / p.k_blocks_per_split;
+    p.out = out;
+    p.ldc = ldc;
+    p.scratch = scratch;
+    p.counters = counters;
+    p.err = err;
+    CUtensorMap ma, mb;
+    int r;
+    if (swap) {
+        if ((r = make_map(&ma, W, N, K, ldw, BM)) != AIRUN_OK) return r;
+        if ((r = make_map(&mb, x, M, K, ldx, bn)) != AIRUN_OK) return r;
+    } else {
+        if ((r = make_map(&ma, x, M, K, ldx, BM)) != AIRUN_OK) return r;
+        if ((r = make_map(&mb, W, N, K, ldw, bn)) != AIRUN_OK) return r;
+    }
+    dim3 grid((p.a_rows + BM - 1) / BM, (p.b_rows + bn - 1) / bn, p.ksplit);
+    if (grid.y > 65535 || grid.z > 65535) return AIRUN_ERR_ARG;
+    if (epi == EPI_F32) return dispatch<EPI_F32>(swap != 0, bn, ma, mb, p, grid, stream);
+    if (epi == EPI_BF16) return dispatch<EPI_BF16>(swap != 0, bn, ma, mb, p, grid, stream);
+    if (epi == EPI_SWIGLU) return dispatch<EPI_SWIGLU>(swap != 0, bn, ma, mb, p, grid, stream);
+    return AIRUN_ERR_UNSUPPORTED;
+}
