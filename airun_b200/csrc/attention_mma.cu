@@ -1,0 +1,518 @@
+// Tensor-core attention over cache pages for bfloat16 q and pages, one head size per
+// build (-DHD=<head_dim>, a multiple of 16 up to 256).
+//
+// Both kernels pack the query heads that share a KV head into the rows of one
+// matrix product, so every key and value row is read once for the whole group
+// (the reference's decode kernel makes "the G query heads rows of the MMA",
+// crates/airun-cuda/kernels/ops.cu:1167-1364; its prefill kernel is the FA-2 style
+// crates/airun-cuda/kernels/ops.cu:1796-2078).  Scores are s = scale * q.K in float32
+// from bfloat16 operands; the running maximum, the sum and the output accumulate
+// in float32; probabilities are rounded to bfloat16 for the P.V product.  Key j is
+// visible to a query at position p iff j <= p and (window == 0 or p - j < window).
+//
+//  attn_prefill: one CTA = 64 packed rows (64/G tokens x G heads) of one request and
+//    KV head; 4 warps x 16 rows; K/V tiles of 64 keys gathered page by page with
+//    cp.async into double-buffered, swizzled shared memory; tiles wholly hidden by
+//    the causal rule or the window are skipped.
+//  attn_decode: one CTA = one token, one KV head (16 heads of its group at most),
+//    one slice of the keys; its 4 warps take 16-key tiles in turn with private
+//    cp.async stages and merge in shared memory.  With more than one slice each CTA
+//    writes (max, sum, acc) to scratch and the last CTA of the token and head (a
+//    counter, no spinning) merges the slices in order.
+#include "common.cuh"
+
+#ifndef HD
+#error "compile with -DHD=<head_dim>"
+#endif
+static_assert(HD % 16 == 0 && HD >= 16 && HD <= 256, "head_dim must be a multiple of 16 up to 256");
+
+#define CHUNKS (HD / 8)                 // 16-byte chunks per row
+#define SWZ (HD % 64 == 0)
+#define NEG_BIG (-1.0e30f)
+#define LOG2E 1.4426950408889634f
+
+namespace {
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ int swz(int row, int chunk) { return SWZ ? (chunk ^ (row & 7)) : chunk; }
+// byte offset of (row, chunk) inside a [rows][HD] bf16 tile
+__device__ __forceinline__ uint32_t tile_off(int row, int chunk) { return (uint32_t)(row * CHUNKS + swz(row, chunk)) * 16u; }
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+    const int n = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void ldsm4(uint32_t* r, uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm4t(uint32_t* r, uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+struct AttnParams {
+    const __nv_bfloat16* q;        // [T][nh][HD]
+    __nv_bfloat16* out;            // [T][nh][HD]
+    const __nv_bfloat16* pool;     // [pages][2][nkv][page_size][HD]
+    const int32_t* block_table;    // [R][max_blocks]
+    const int32_t* positions;      // [T]
+    const int32_t* req_of_token;   // [T]
+    int max_blocks, num_reqs, num_pages, page_size, nh, nkv, G;
+    float scale_log2;              // scale * log2(e)
+    int window;
+    int* err;
+};
+
+// Address of key j's row (K) of KV head kvh; V is v_off elements further.  Returns nullptr for a
+// bad page (and records it).
+__device__ __forceinline__ const __nv_bfloat16* key_row(const AttnParams& p, const int32_t* bt, int kvh, int j) {
+    const int blk = j / p.page_size;
+    const int page = blk < p.max_blocks ? bt[blk] : -1;
+    if (page < 0 || page >= p.num_pages) { atomicOr(p.err, AIRUN_DEV_BAD_PAGE); return nullptr; }
+    return p.pool + (((size_t)page * 2 * p.nkv + kvh) * p.page_size + (j - blk * p.page_size)) * HD;
+}
+
+// ------------------------------------------------------------------ prefill
+#define PM 64          // packed rows per CTA
+#define PN 64          // keys per tile
+
+struct PrefillTile { int req, tok0, n_tok, first_row; };   // tokens [tok0, tok0+n_tok) of the batch, all of request req
+
+__global__ __launch_bounds__(128) void attn_prefill_kernel(const AttnParams p, const int4* __restrict__ tiles) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint8_t* sQ = smem;                               // [PM][HD]
+    uint8_t* sK = sQ + PM * HD * 2;                   // [2][PN][HD]
+    uint8_t* sV = sK + 2 * PN * HD * 2;               // [2][PN][HD]
+    const int4 t4 = tiles[blockIdx.x];
+    const int req = t4.x, tok0 = t4.y, n_tok = t4.z;
+    const int kvh = blockIdx.y;
+    const int G = p.G;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int n_rows = n_tok * G;                     // valid packed rows (<= PM)
+    const int32_t* bt = p.block_table + (size_t)req * p.max_blocks;
+    const size_t v_off = (size_t)p.nkv * p.page_size * HD;
+
+    // positions of the first and last token of the tile (tokens of a request are in position order)
+    const int pos_lo = p.positions[tok0], pos_hi = p.positions[tok0 + n_tok - 1];
+
+    // ---- Q tile -> shared memory
+    for (int i = threadIdx.x; i < PM * CHUNKS; i += 128) {
+        const int r = i / CHUNKS, c = i - r * CHUNKS;
+        const bool valid = r < n_rows;
+        const int tok = tok0 + (valid ? r / G : 0), head = kvh * G + (valid ? r % G : 0);
+        cp_async16(smem_u32(sQ) + tile_off(r, c), p.q + ((size_t)tok * p.nh + head) * HD + c * 8, valid);
+    }
+    cp_commit();
+
+    const int k_first = p.window > 0 ? max(0, pos_lo - p.window + 1) : 0;
+    const int tile_first = k_first / PN;
+    const int tile_last = pos_hi / PN;
+    const int n_tiles = tile_last - tile_first + 1;
+
+    auto load_kv = [&](int tile, int stage) {
+        const int j0 = tile * PN;
+        uint32_t kb = smem_u32(sK + stage * PN * HD * 2), vb = smem_u32(sV + stage * PN * HD * 2);
+        for (int i = threadIdx.x; i < PN * CHUNKS; i += 128) {
+            const int r = i / CHUNKS, c = i - r * CHUNKS;
+            const int j = j0 + r;
+            const __nv_bfloat16* src = (j <= pos_hi && j >= k_first) ? key_row(p, bt, kvh, j) : nullptr;
+            const bool valid = src != nullptr;
+            const __nv_bfloat16* s = valid ? src + c * 8 : p.pool;
+            cp_async16(kb + tile_off(r, c), s, valid);
+            cp_async16(vb + tile_off(r, c), valid ? s + v_off : s, valid);
+        }
+        cp_commit();
+    };
+
+    load_kv(tile_first, 0);
+
+    // this thread's two rows: warp*16 + g and + 8
+    const int r0 = warp * 16 + g, r1 = r0 + 8;
+    const int pos0 = r0 < n_rows ? p.positions[tok0 + r0 / G] : -1;
+    const int pos1 = r1 < n_rows ? p.positions[tok0 + r1 / G] : -1;
+
+    float m0 = NEG_BIG, m1 = NEG_BIG, l0 = 0.0f, l1 = 0.0f;
+    float o[HD / 8][4];
+#pragma unroll
+    for (int n = 0; n < HD / 8; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f; }
+
+    uint32_t qf[HD / 16][4];
+    for (int it = 0; it < n_tiles; ++it) {
+        const int stage = it & 1;
+        if (it + 1 < n_tiles) { load_kv(tile_first + it + 1, stage ^ 1); cp_wait<1>(); } else { cp_wait<0>(); }
+        __syncthreads();
+        if (it == 0) {
+#pragma unroll
+            for (int k = 0; k < HD / 16; ++k)
+                ldsm4(qf[k], smem_u32(sQ) + tile_off(warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, 2 * k + (lane >> 4)));
+        }
+        const uint32_t kb = smem_u32(sK + stage * PN * HD * 2), vb = smem_u32(sV + stage * PN * HD * 2);
+        const int j0 = (tile_first + it) * PN;
+
+        float s[PN / 8][4];
+#pragma unroll
+        for (int n = 0; n < PN / 8; ++n) { s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.0f; }
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k) {
+#pragma unroll
+            for (int n2 = 0; n2 < PN / 16; ++n2) {
+                uint32_t b[4];
+                ldsm4(b, kb + tile_off(n2 * 16 + ((lane >> 4) << 3) + (lane & 7), 2 * k + ((lane >> 3) & 1)));
+                mma16816(s[2 * n2], qf[k], b[0], b[1]);
+                mma16816(s[2 * n2 + 1], qf[k], b[2], b[3]);
+            }
+        }
+        // mask, scale, running maximum
+        float mx0 = m0, mx1 = m1;
+#pragma unroll
+        for (int n = 0; n < PN / 8; ++n) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int j = j0 + n * 8 + 2 * t + (e & 1);
+                const int pos = (e < 2) ? pos0 : pos1;
+                const bool vis = j <= pos && (p.window == 0 || pos - j < p.window);
+                const float v = vis ? s[n][e] * p.scale_log2 : NEG_BIG;
+                s[n][e] = v;
+                if (e < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
+            }
+        }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        const float c0 = exp2f(m0 - mx0), c1 = exp2f(m1 - mx1);
+        m0 = mx0; m1 = mx1;
+        float rs0 = 0.0f, rs1 = 0.0f;
+        uint32_t pf[PN / 16][4];
+#pragma unroll
+        for (int n = 0; n < PN / 8; ++n) {
+            // a fully hidden row keeps m = NEG_BIG: exp2(NEG_BIG - NEG_BIG) would be 1, so test visibility by value
+            const float p00 = s[n][0] > 0.5f * NEG_BIG ? exp2f(s[n][0] - mx0) : 0.0f;
+            const float p01 = s[n][1] > 0.5f * NEG_BIG ? exp2f(s[n][1] - mx0) : 0.0f;
+            const float p10 = s[n][2] > 0.5f * NEG_BIG ? exp2f(s[n][2] - mx1) : 0.0f;
+            const float p11 = s[n][3] > 0.5f * NEG_BIG ? exp2f(s[n][3] - mx1) : 0.0f;
+            rs0 += p00 + p01;
+            rs1 += p10 + p11;
+            pf[n >> 1][(n & 1) * 2 + 0] = pack_bf16(p00, p01);
+            pf[n >> 1][(n & 1) * 2 + 1] = pack_bf16(p10, p11);
+        }
+        l0 = l0 * c0 + rs0;
+        l1 = l1 * c1 + rs1;
+#pragma unroll
+        for (int n = 0; n < HD / 8; ++n) { o[n][0] *= c0; o[n][1] *= c0; o[n][2] *= c1; o[n][3] *= c1; }
+#pragma unroll
+        for (int kk = 0; kk < PN / 16; ++kk) {
+#pragma unroll
+            for (int n2 = 0; n2 < HD / 16; ++n2) {
+                uint32_t b[4];
+                ldsm4t(b, vb + tile_off(kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, 2 * n2 + (lane >> 4)));
+                mma16816(o[2 * n2], pf[kk], b[0], b[1]);
+                mma16816(o[2 * n2 + 1], pf[kk], b[2], b[3]);
+            }
+        }
+        __syncthreads();       // everyone is done with this stage before it is refilled
+    }
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    const float i0 = l0 > 0.0f ? 1.0f / l0 : 0.0f, i1 = l1 > 0.0f ? 1.0f / l1 : 0.0f;
+    if (r0 < n_rows) {
+        __nv_bfloat16* dst = p.out + ((size_t)(tok0 + r0 / G) * p.nh + kvh * G + r0 % G) * HD;
+#pragma unroll
+        for (int n = 0; n < HD / 8; ++n)
+            *reinterpret_cast<uint32_t*>(dst + n * 8 + 2 * t) = pack_bf16(o[n][0] * i0, o[n][1] * i0);
+    }
+    if (r1 < n_rows) {
+        __nv_bfloat16* dst = p.out + ((size_t)(tok0 + r1 / G) * p.nh + kvh * G + r1 % G) * HD;
+#pragma unroll
+        for (int n = 0; n < HD / 8; ++n)
+            *reinterpret_cast<uint32_t*>(dst + n * 8 + 2 * t) = pack_bf16(o[n][2] * i1, o[n][3] * i1);
+    }
+}
+
+// ------------------------------------------------------------------ decode
+#define DW 4                    // warps per CTA
+#define DSTAGES 2
+#define DN 16                   // keys per tile
+
+struct DecodeExtra {
+    const int32_t* rows;        // [n] batch rows (tokens) this launch handles
+    int n_splits;
+    float* scratch;             // [n][nkv*hgroups][n_splits][16][HD + 2]
+    int* counters;              // [n][nkv*hgroups], zero between launches
+};
+
+__global__ __launch_bounds__(32 * DW) void attn_decode_kernel(const AttnParams p, const DecodeExtra x) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    // per warp: DSTAGES x (K tile + V tile); the Q tile [16][HD] sits after them
+    constexpr int TILE_BYTES = DN * HD * 2;
+    constexpr int WARP_BYTES = DSTAGES * 2 * TILE_BYTES;
+    uint8_t* sQ = smem + DW * WARP_BYTES;
+    __shared__ float s_m[DW][16], s_l[DW][16];
+    __shared__ int s_ticket;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int split = blockIdx.x;
+    const int hgroups = (p.G + 15) / 16;
+    const int kvh = blockIdx.y / hgroups, hg = blockIdx.y - kvh * hgroups;
+    const int tok = x.rows[blockIdx.z];
+    const int pos = p.positions[tok];
+    const int req = p.req_of_token[tok];
+    const int heads = min(16, p.G - hg * 16);          // valid rows
+    const int head0 = kvh * p.G + hg * 16;
+    const bool live = req >= 0 && req < p.num_reqs && pos >= 0;
+    const int32_t* bt = p.block_table + (size_t)(live ? req : 0) * p.max_blocks;
+    const size_t v_off = (size_t)p.nkv * p.page_size * HD;
+
+    // Q rows -> shared memory (rows >= heads are zero)
+    for (int i = threadIdx.x; i < 16 * CHUNKS; i += 32 * DW) {
+        const int r = i / CHUNKS, c = i - r * CHUNKS;
+        const bool valid = r < heads;
+        cp_async16(smem_u32(sQ) + tile_off(r, c), p.q + ((size_t)tok * p.nh + head0 + (valid ? r : 0)) * HD + c * 8, valid);
+    }
+    cp_commit();
+
+    // key tiles of this token, this slice, this warp
+    const int k_first = live ? (p.window > 0 ? max(0, pos - p.window + 1) : 0) : 0;
+    const int tile_first = k_first / DN;
+    const int n_tiles_all = live ? pos / DN - tile_first + 1 : 0;
+    const int per_split = (n_tiles_all + x.n_splits - 1) / x.n_splits;
+    const int tb = tile_first + split * per_split;
+    const int te = min(tile_first + n_tiles_all, tb + per_split);
+    const int my_n = te > tb + warp ? (te - tb - warp + DW - 1) / DW : 0;      // tiles tb+warp, tb+warp+DW, ...
+
+    uint8_t* wbase = smem + warp * WARP_BYTES;
+    auto load_tile = [&](int tile, int stage) {
+        const int j0 = tile * DN;
+        const uint32_t kb = smem_u32(wbase + stage * 2 * TILE_BYTES), vb = kb + TILE_BYTES;
+        for (int i = lane; i < DN * CHUNKS; i += 32) {
+            const int r = i / CHUNKS, c = i - r * CHUNKS;
+            const int j = j0 + r;
+            const __nv_bfloat16* src = (j <= pos && j >= k_first) ? key_row(p, bt, kvh, j) : nullptr;
+            const bool valid = src != nullptr;
+            const __nv_bfloat16* s = valid ? src + c * 8 : p.pool;
+            cp_async16(kb + tile_off(r, c), s, valid);
+            cp_async16(vb + tile_off(r, c), valid ? s + v_off : s, valid);
+        }
+        cp_commit();
+    };
+    if (my_n > 0) load_tile(tb + warp, 0);
+
+    float m0 = NEG_BIG, m1 = NEG_BIG, l0 = 0.0f, l1 = 0.0f;
+    float o[HD / 8][4];
+#pragma unroll
+    for (int n = 0; n < HD / 8; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f; }
+
+    cp_wait<0>();
+    __syncthreads();                       // Q (and each warp's first tile) has landed
+    uint32_t qf[HD / 16][4];
+#pragma unroll
+    for (int k = 0; k < HD / 16; ++k)
+        ldsm4(qf[k], smem_u32(sQ) + tile_off((lane & 7) + ((lane >> 3) & 1) * 8, 2 * k + (lane >> 4)));
+
+    for (int it = 0; it < my_n; ++it) {
+        const int stage = it & 1;
+        if (it + 1 < my_n) { load_tile(tb + warp + (it + 1) * DW, stage ^ 1); cp_wait<1>(); } else { cp_wait<0>(); }
+        __syncwarp();
+        const uint32_t kb = smem_u32(wbase + stage * 2 * TILE_BYTES), vb = kb + TILE_BYTES;
+        const int j0 = (tb + warp + it * DW) * DN;
+        float s[2][4] = {{0.0f, 0.0f, 0.0f, 0.0f}, {0.0f, 0.0f, 0.0f, 0.0f}};
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k) {
+            uint32_t b[4];
+            ldsm4(b, kb + tile_off(((lane >> 4) << 3) + (lane & 7), 2 * k + ((lane >> 3) & 1)));
+            mma16816(s[0], qf[k], b[0], b[1]);
+            mma16816(s[1], qf[k], b[2], b[3]);
+        }
+        float mx0 = m0, mx1 = m1;
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int j = j0 + n * 8 + 2 * t + (e & 1);
+                const bool vis = j <= pos && j >= k_first;
+                const float v = vis ? s[n][e] * p.scale_log2 : NEG_BIG;
+                s[n][e] = v;
+                if (e < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
+            }
+        }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        const float c0 = exp2f(m0 - mx0), c1 = exp2f(m1 - mx1);
+        m0 = mx0; m1 = mx1;
+        uint32_t pf[4];
+        float rs0 = 0.0f, rs1 = 0.0f;
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+            const float p00 = s[n][0] > 0.5f * NEG_BIG ? exp2f(s[n][0] - mx0) : 0.0f;
+            const float p01 = s[n][1] > 0.5f * NEG_BIG ? exp2f(s[n][1] - mx0) : 0.0f;
+            const float p10 = s[n][2] > 0.5f * NEG_BIG ? exp2f(s[n][2] - mx1) : 0.0f;
+            const float p11 = s[n][3] > 0.5f * NEG_BIG ? exp2f(s[n][3] - mx1) : 0.0f;
+            rs0 += p00 + p01;
+            rs1 += p10 + p11;
+            pf[n * 2 + 0] = pack_bf16(p00, p01);
+            pf[n * 2 + 1] = pack_bf16(p10, p11);
+        }
+        l0 = l0 * c0 + rs0;
+        l1 = l1 * c1 + rs1;
+#pragma unroll
+        for (int n = 0; n < HD / 8; ++n) { o[n][0] *= c0; o[n][1] *= c0; o[n][2] *= c1; o[n][3] *= c1; }
+#pragma unroll
+        for (int n2 = 0; n2 < HD / 16; ++n2) {
+            uint32_t b[4];
+            ldsm4t(b, vb + tile_off((lane & 7) + ((lane >> 3) & 1) * 8, 2 * n2 + (lane >> 4)));
+            mma16816(o[2 * n2], pf, b[0], b[1]);
+            mma16816(o[2 * n2 + 1], pf, b[2], b[3]);
+        }
+        __syncwarp();
+    }
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+
+    // ---- merge the warps: each warp's (m, l, o) -> shared memory (its own K/V stages are free now)
+    __syncthreads();
+    float* wo = reinterpret_cast<float*>(wbase);         // [16][HD] floats = 64*HD bytes <= WARP_BYTES
+    if (t == 0) { s_m[warp][g] = m0; s_m[warp][g + 8] = m1; s_l[warp][g] = l0; s_l[warp][g + 8] = l1; }
+#pragma unroll
+    for (int n = 0; n < HD / 8; ++n) {
+        wo[g * HD + n * 8 + 2 * t] = o[n][0];
+        wo[g * HD + n * 8 + 2 * t + 1] = o[n][1];
+        wo[(g + 8) * HD + n * 8 + 2 * t] = o[n][2];
+        wo[(g + 8) * HD + n * 8 + 2 * t + 1] = o[n][3];
+    }
+    __syncthreads();
+    // thread i handles element(s) (row, d): row = e / HD
+    const int unit = blockIdx.z * gridDim.y + blockIdx.y;
+    float* part = x.n_splits > 1 ? x.scratch + ((size_t)unit * x.n_splits + split) * (16 * (HD + 2)) : nullptr;
+    for (int e = threadIdx.x; e < heads * HD; e += 32 * DW) {
+        const int r = e / HD, d = e - r * HD;
+        float gm = NEG_BIG;
+#pragma unroll
+        for (int w = 0; w < DW; ++w) gm = fmaxf(gm, s_m[w][r]);
+        float acc = 0.0f, sum = 0.0f;
+#pragma unroll
+        for (int w = 0; w < DW; ++w) {
+            const float f = s_l[w][r] > 0.0f ? exp2f(s_m[w][r] - gm) : 0.0f;
+            acc = fmaf(reinterpret_cast<float*>(smem + w * WARP_BYTES)[r * HD + d], f, acc);
+            sum = fmaf(s_l[w][r], f, sum);
+        }
+        if (part) {
+            part[r * (HD + 2) + 2 + d] = acc;
+            if (d == 0) { part[r * (HD + 2)] = gm; part[r * (HD + 2) + 1] = sum; }
+        } else {
+            p.out[((size_t)tok * p.nh + head0 + r) * HD + d] = __float2bfloat16_rn(sum > 0.0f ? acc / sum : 0.0f);
+        }
+    }
+    if (!part) return;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) s_ticket = atomicAdd(x.counters + unit, 1);
+    __syncthreads();
+    if (s_ticket != x.n_splits - 1) return;
+    __threadfence();
+    if (threadIdx.x == 0) x.counters[unit] = 0;
+    const float* all = x.scratch + (size_t)unit * x.n_splits * (16 * (HD + 2));
+    for (int e = threadIdx.x; e < heads * HD; e += 32 * DW) {
+        const int r = e / HD, d = e - r * HD;
+        float gm = NEG_BIG;
+        for (int sp = 0; sp < x.n_splits; ++sp) gm = fmaxf(gm, __ldcg(all + (size_t)sp * 16 * (HD + 2) + r * (HD + 2)));
+        float acc = 0.0f, sum = 0.0f;
+        for (int sp = 0; sp < x.n_splits; ++sp) {
+            const float* ps = all + (size_t)sp * 16 * (HD + 2) + r * (HD + 2);
+            const float l = __ldcg(ps + 1);
+            const float f = l > 0.0f ? exp2f(__ldcg(ps) - gm) : 0.0f;
+            acc = fmaf(__ldcg(ps + 2 + d), f, acc);
+            sum = fmaf(l, f, sum);
+        }
+        p.out[((size_t)tok * p.nh + head0 + r) * HD + d] = __float2bfloat16_rn(sum > 0.0f ? acc / sum : 0.0f);
+    }
+}
+
+AttnParams make_params(const void* q, void* out, const void* pool, const int32_t* block_table, int max_blocks,
+                       const int32_t* positions, const int32_t* req_of_token, int num_reqs, int num_pages,
+                       int page_size, int nh, int nkv, float scale, int window, int* err) {
+    AttnParams p;
+    p.q = (const __nv_bfloat16*)q; p.out = (__nv_bfloat16*)out; p.pool = (const __nv_bfloat16*)pool;
+    p.block_table = block_table; p.positions = positions; p.req_of_token = req_of_token;
+    p.max_blocks = max_blocks; p.num_reqs = num_reqs; p.num_pages = num_pages; p.page_size = page_size;
+    p.nh = nh; p.nkv = nkv; p.G = nh / nkv; p.scale_log2 = scale * LOG2E; p.window = window; p.err = err;
+    return p;
+}
+
+}  // namespace
+
+AIRUN_EXPORT int airun_attn_head_dim() { return HD; }
+
+// Tokens per prefill tile for a group of G heads.
+AIRUN_EXPORT int airun_attn_prefill_tokens_per_tile(int G) { return G > 0 && G <= PM ? PM / G : 0; }
+
+// tiles: [n_tiles] int4 {request, first token row, token count (<= PM / G), 0}
+AIRUN_EXPORT int airun_attn_prefill(const void* q, void* out, const void* pool, const int32_t* block_table,
+                                    int max_blocks, const int32_t* positions, const int32_t* req_of_token,
+                                    int num_reqs, int num_pages, int page_size, int nh, int nkv, float scale,
+                                    int window, const void* tiles, int n_tiles, int* err, cudaStream_t stream) {
+    if (n_tiles < 0 || nh <= 0 || nkv <= 0 || nh % nkv != 0 || nh / nkv > PM || page_size <= 0 || !err) return AIRUN_ERR_ARG;
+    if (n_tiles == 0) return AIRUN_OK;
+    if (nkv > 65535) return AIRUN_ERR_ARG;
+    const AttnParams p = make_params(q, out, pool, block_table, max_blocks, positions, req_of_token, num_reqs,
+                                     num_pages, page_size, nh, nkv, scale, window, err);
+    const int smem = (PM + 4 * PN) * HD * 2;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    attn_prefill_kernel<<<dim3(n_tiles, nkv), 128, smem, stream>>>(p, (const int4*)tiles);
+    return airun_launch_status();
+}
+
+AIRUN_EXPORT long long airun_attn_decode_scratch_floats(int n_rows, int nh, int nkv, int n_splits) {
+    const int hgroups = (nh / nkv + 15) / 16;
+    return n_splits > 1 ? (long long)n_rows * nkv * hgroups * n_splits * 16 * (HD + 2) : 0;
+}
+
+// rows: [n_rows] batch rows (one decoded token each).  counters: [n_rows * nkv * hgroups] ints, zero on entry.
+AIRUN_EXPORT int airun_attn_decode(const void* q, void* out, const void* pool, const int32_t* block_table,
+                                   int max_blocks, const int32_t* positions, const int32_t* req_of_token,
+                                   int num_reqs, int num_pages, int page_size, int nh, int nkv, float scale,
+                                   int window, const int32_t* rows, int n_rows, int n_splits, float* scratch,
+                                   int* counters, int* err, cudaStream_t stream) {
+    if (n_rows < 0 || nh <= 0 || nkv <= 0 || nh % nkv != 0 || page_size <= 0 || n_splits < 1 || !err) return AIRUN_ERR_ARG;
+    if (n_splits > 1 && (!scratch || !counters)) return AIRUN_ERR_ARG;
+    if (n_rows == 0) return AIRUN_OK;
+    const int hgroups = (nh / nkv + 15) / 16;
+    if (nkv * hgroups > 65535 || n_rows > 65535) return AIRUN_ERR_ARG;
+    const AttnParams p = make_params(q, out, pool, block_table, max_blocks, positions, req_of_token, num_reqs,
+                                     num_pages, page_size, nh, nkv, scale, window, err);
+    DecodeExtra x{rows, n_splits, scratch, counters};
+    const int smem = DW * DSTAGES * 2 * DN * HD * 2 + 16 * HD * 2;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    attn_decode_kernel<<<dim3(n_splits, nkv * hgroups, n_rows), 32 * DW, smem, stream>>>(p, x);
+    return airun_launch_status();
+}

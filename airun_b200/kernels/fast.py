@@ -7,7 +7,7 @@ caller runs the plain kernel.  ``gemm_tcgen05`` is the raw entry.
 from __future__ import annotations
 
 import os
-from ctypes import c_int, c_longlong, c_void_p
+from ctypes import c_float, c_int, c_longlong, c_void_p
 from typing import Dict, Optional, Tuple
 
 import torch
@@ -26,7 +26,7 @@ DISABLED = set(filter(None, os.environ.get("AIRUN_DISABLE_FAST", "").split(","))
 
 
 def all_libraries():
-    return [("gemm_tcgen05", None)]
+    return [("gemm_tcgen05", None), ("attention_mma", {"HD": 128}), ("attention_mma", {"HD": 64})]
 
 
 def scratch_for(device: torch.device) -> Tuple[torch.Tensor, torch.Tensor]:
@@ -117,5 +117,109 @@ def linear_swiglu_bf16(ctx, x: torch.Tensor, w_gu: torch.Tensor, out: torch.Tens
     return True
 
 
+# ---------------------------------------------------------------- attention
+_ARANGE: Dict[torch.device, torch.Tensor] = {}
+DECODE_TARGET_CTAS = 592               # four CTAs for each of 148 SMs
+DECODE_MIN_KEYS_PER_SPLIT = 128
+
+
+def _arange(device: torch.device, n: int) -> torch.Tensor:
+    a = _ARANGE.get(device)
+    if a is None or a.numel() < n:
+        a = torch.arange(max(n, 4096), dtype=torch.int32, device=device)
+        _ARANGE[device] = a
+    return a
+
+
+def attention_supported(hd: int, nh: int, nkv: int) -> bool:
+    return "attention" not in DISABLED and hd % 16 == 0 and 16 <= hd <= 256 and nh % nkv == 0 and nh // nkv <= 64
+
+
+def _attn_common_args(q, out, cache, ctx, nh, nkv, scale, window):
+    pool, bt = cache.pool, cache.block_table
+    return [_p(q), _p(out), _p(pool), _p(bt), bt.stride(0), _p(ctx.positions), _p(ctx.req_of_token),
+            int(ctx.num_reqs), pool.shape[0], pool.shape[3], nh, nkv, float(scale), int(window)]
+
+
+_COMMON_SIG = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+               c_float, c_int]
+
+
+def attn_prefill(ctx, q, out, cache, nh, nkv, hd, scale, window, tiles: torch.Tensor, n_tiles: int) -> None:
+    """Flash attention of prompt portions; ``tiles`` is int32 [n, 4] = (request, first row, tokens, 0)."""
+    _cuda(q, out, cache.pool, cache.block_table, tiles)
+    _need(q.dtype == torch.bfloat16 and cache.pool.dtype == torch.bfloat16 and q.is_contiguous() and out.is_contiguous(),
+          "tensor-core attention takes contiguous bfloat16 q, out and pages")
+    _need(tiles.dtype == torch.int32 and tiles.is_contiguous() and tiles.numel() >= 4 * n_tiles, "tiles must be int32 [n, 4]")
+    f = _fn("attention_mma", "airun_attn_prefill", _COMMON_SIG + [c_void_p, c_int, c_void_p, c_void_p], {"HD": hd})
+    _check(f(*_attn_common_args(q, out, cache, ctx, nh, nkv, scale, window), _p(tiles), n_tiles, _p(ctx.err), _stream()),
+           "attn_prefill")
+
+
+def attn_decode(ctx, q, out, cache, nh, nkv, hd, scale, window, rows: torch.Tensor, n_rows: int, n_splits: int) -> None:
+    """Attention of single decoded tokens (batch rows ``rows``), the keys cut into ``n_splits`` slices."""
+    _cuda(q, out, cache.pool, cache.block_table, rows)
+    _need(q.dtype == torch.bfloat16 and cache.pool.dtype == torch.bfloat16 and q.is_contiguous() and out.is_contiguous(),
+          "tensor-core attention takes contiguous bfloat16 q, out and pages")
+    _need(rows.dtype == torch.int32 and rows.is_contiguous() and rows.numel() >= n_rows, "rows must be int32 [n]")
+    scratch, counters = scratch_for(q.device)
+    hgroups = (nh // nkv + 15) // 16
+    if n_splits > 1:
+        need = n_rows * nkv * hgroups * n_splits * 16 * (hd + 2)
+        _need(need <= scratch.numel() and n_rows * nkv * hgroups <= counters.numel(),
+              "split-K scratch is too small for this decode launch")
+    f = _fn("attention_mma", "airun_attn_decode",
+            _COMMON_SIG + [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p], {"HD": hd})
+    _check(f(*_attn_common_args(q, out, cache, ctx, nh, nkv, scale, window), _p(rows), n_rows, n_splits,
+             _p(scratch), _p(counters), _p(ctx.err), _stream()), "attn_decode")
+
+
+def plan_decode_splits(n_rows: int, nkv: int, hgroups: int, context_len: int, hd: int) -> int:
+    units = max(1, n_rows * nkv * hgroups)
+    splits = max(1, min(DECODE_TARGET_CTAS // units, (context_len + DECODE_MIN_KEYS_PER_SPLIT - 1) // DECODE_MIN_KEYS_PER_SPLIT))
+    while splits > 1 and units * splits * 16 * (hd + 2) > SCRATCH_FLOATS:
+        splits -= 1
+    return splits
+
+
+def _attention_plan(ctx, G: int):
+    """Which rows are single decoded tokens and how the prompt portions are cut into tiles
+    of 64 // G tokens; made once per step and group size."""
+    key = ("attn_plan", G)
+    plan = ctx.extras.get(key)
+    if plan is not None:
+        return plan
+    dev = ctx.token_ids.device
+    if ctx.decode_only:
+        plan = dict(rows=_arange(dev, ctx.num_tokens), n_rows=ctx.num_tokens, tiles=None, n_tiles=0)
+    else:
+        per = max(1, 64 // G)
+        rows, tiles, t = [], [], 0
+        for r, n in enumerate(ctx.query_lens):
+            if n == 1:
+                rows.append(t)
+            else:
+                for s in range(0, n, per):
+                    tiles.append((r, t + s, min(per, n - s), 0))
+            t += n
+        plan = dict(
+            rows=torch.tensor(rows, dtype=torch.int32).to(dev, non_blocking=True) if rows else None, n_rows=len(rows),
+            tiles=torch.tensor(tiles, dtype=torch.int32).to(dev, non_blocking=True) if tiles else None, n_tiles=len(tiles))
+    ctx.extras[key] = plan
+    return plan
+
+
 def attention_bf16(ctx, q, out, cache, nh: int, nkv: int, hd: int, scale: float, window: int) -> bool:
-    return False
+    if not attention_supported(hd, nh, nkv) or q.dtype != torch.bfloat16:
+        return False
+    G = nh // nkv
+    plan = _attention_plan(ctx, G)
+    if plan["n_tiles"]:
+        attn_prefill(ctx, q, out, cache, nh, nkv, hd, scale, window, plan["tiles"], plan["n_tiles"])
+    if plan["n_rows"]:
+        context = ctx.extras.get("planning_context_len", ctx.max_context_len)
+        if window > 0:
+            context = min(context, window)
+        splits = plan_decode_splits(plan["n_rows"], nkv, (G + 15) // 16, context, hd)
+        attn_decode(ctx, q, out, cache, nh, nkv, hd, scale, window, plan["rows"], plan["n_rows"], splits)
+    return True

@@ -1,0 +1,414 @@
+"""Each kernel alone against its plain reference, at sizes other than the engine's."""
+from __future__ import annotations
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as P
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _err():
+    return torch.zeros(1, dtype=torch.int32, device=DEV)
+
+
+class Ctx:
+    """The few fields of a step context the attention wrappers read."""
+
+    def __init__(self, positions, req_of_token, num_reqs, query_lens, context_lens):
+        self.positions = torch.tensor(positions, dtype=torch.int32, device=DEV)
+        self.req_of_token = torch.tensor(req_of_token, dtype=torch.int32, device=DEV)
+        self.token_ids = self.positions
+        self.num_reqs, self.num_tokens = num_reqs, len(positions)
+        self.query_lens, self.context_lens_host = query_lens, context_lens
+        self.max_context_len = max(context_lens)
+        self.decode_only = all(q == 1 for q in query_lens)
+        self.err = _err()
+        self.extras = {}
+
+
+class Cache:
+    def __init__(self, pool, block_table, page_size):
+        self.pool, self.block_table, self.page_size, self.shared = pool, block_table, page_size, False
+
+
+def paged_from_dense(ks, vs, page_size, dtype, extra_pages=5, seed=0):
+    """ks, vs: per request [n_i, nkv, hd] float tensors.  Scatters them into a pool through a
+    shuffled block table, and fills unused pages with large values that must never be read."""
+    nkv, hd = ks[0].shape[1:]
+    blocks = [(k.shape[0] + page_size - 1) // page_size for k in ks]
+    n_pages = sum(blocks) + extra_pages
+    g = np.random.default_rng(seed)
+    perm = g.permutation(n_pages)
+    pool = torch.full((n_pages, 2, nkv, page_size, hd), 1e4, dtype=torch.float32)
+    bt = torch.full((len(ks), max(blocks) + 2), -1, dtype=torch.int32)
+    p = 0
+    for r, (k, v) in enumerate(zip(ks, vs)):
+        for b in range(blocks[r]):
+            page = int(perm[p]); p += 1
+            bt[r, b] = page
+            n = min(page_size, k.shape[0] - b * page_size)
+            pool[page, 0, :, :n] = k[b * page_size:b * page_size + n].transpose(0, 1)
+            pool[page, 1, :, :n] = v[b * page_size:b * page_size + n].transpose(0, 1)
+    return pool.to(dtype).to(DEV), bt.to(DEV)
+
+
+# ----------------------------------------------------------------------------- elementwise
+@pytest.mark.parametrize("T,H,out_dtype", [(5, 100, torch.float32), (3, 4096, torch.bfloat16), (1, 36, torch.float32),
+                                          (7, 1500, torch.bfloat16)])
+def test_rmsnorm_and_fused_add(T, H, out_dtype):
+    from airun_b200.kernels import ops
+    torch.manual_seed(1)
+    x = torch.randn(T, H) * 3
+    d = torch.randn(T, H)
+    w = 1 + 0.5 * torch.rand(H)
+    eps = 3e-5
+    tol = 1e-4 if out_dtype == torch.float32 else 1e-2
+    xd, out = x.to(DEV), torch.empty(T, H, dtype=out_dtype, device=DEV)
+    ops.rmsnorm(xd, w.to(DEV), eps, out)
+    want = P.plain_rmsnorm(x.double(), w.double(), eps)
+    assert torch.allclose(out.cpu().double(), want, rtol=tol, atol=tol * 1e-1)
+    ops.rmsnorm(xd, w.to(DEV), eps, out, delta=d.to(DEV))              # x += d, then the norm
+    assert torch.allclose(xd.cpu(), x + d, rtol=0, atol=1e-6)
+    want = P.plain_rmsnorm((x + d).double(), w.double(), eps)
+    assert torch.allclose(out.cpu().double(), want, rtol=tol, atol=tol * 1e-1)
+    rows = torch.tensor([T - 1, 0], dtype=torch.int32, device=DEV)     # gathered rows leave x alone
+    x2 = x.to(DEV)
+    out2 = torch.empty(2, H, dtype=out_dtype, device=DEV)
+    ops.rmsnorm(x2, w.to(DEV), eps, out2, delta=d.to(DEV), rows=rows)
+    assert torch.equal(x2.cpu(), x)
+    assert torch.allclose(out2.cpu().double(), want[[T - 1, 0]], rtol=tol, atol=tol * 1e-1)
+
+
+def test_embedding_and_bad_token_flag():
+    from airun_b200.kernels import ops
+    torch.manual_seed(2)
+    for dt in (torch.float32, torch.bfloat16):
+        table = torch.randn(37, 52).to(dt)
+        ids = [3, 36, 0, 36, 17]
+        out = torch.empty(5, 52, device=DEV)
+        err = _err()
+        ops.embed(table.to(DEV), torch.tensor(ids, dtype=torch.int32, device=DEV), out, err)
+        assert torch.equal(out.cpu(), P.plain_embedding(table, ids, torch.float32))
+        assert err.item() == 0
+        ops.embed(table.to(DEV), torch.tensor([1, 99], dtype=torch.int32, device=DEV), out[:2], err)
+        assert err.item() == 4 and torch.equal(out[1].cpu(), table[0].float())    # out of range reads row 0
+
+
+@pytest.mark.parametrize("group", [16, 8, 48])
+def test_swiglu_interleaved(group):
+    from airun_b200.kernels import ops
+    torch.manual_seed(3)
+    T, I = 6, 96
+    g, u = torch.randn(T, I) * 4, torch.randn(T, I)
+    gu = torch.stack([g.view(T, I // group, group), u.view(T, I // group, group)], dim=2).reshape(T, 2 * I)
+    want = g.double() / (1 + torch.exp(-g.double())) * u.double()
+    out = torch.empty(T, I, device=DEV)
+    ops.swiglu(gu.to(DEV), out, group)
+    assert torch.allclose(out.cpu().double(), want, rtol=1e-5, atol=1e-6)
+    outb = torch.empty(T, I, dtype=torch.bfloat16, device=DEV)
+    ops.swiglu(gu.to(DEV), outb, group)
+    assert torch.allclose(outb.cpu().double(), want, rtol=1e-2, atol=1e-2)
+
+
+# ----------------------------------------------------------------------------- matrix products
+@pytest.mark.parametrize("M,N,K", [(1, 70, 33), (65, 129, 100), (130, 64, 257), (7, 1000, 64)])
+def test_gemm_simt_float32_is_true_32_bit(M, N, K):
+    """Backward-error bound of a float32 dot product: |err| <= eps * sqrt(K) * 4 * sum|a*w|
+    (the reference's matvec test uses this bound, crates/airun-cli/src/selftest.rs:382-409)."""
+    from airun_b200.kernels import ops
+    torch.manual_seed(4)
+    a, w = torch.randn(M, K), torch.randn(N, K)
+    out = torch.empty(M, N, device=DEV)
+    ops.gemm_simt(a.to(DEV), w.to(DEV), out)
+    want = a.double() @ w.double().T
+    bound = np.finfo(np.float32).eps * math.sqrt(K) * 4 * (a.abs().double() @ w.abs().double().T)
+    assert bool(((out.cpu().double() - want).abs() <= bound).all())
+    # tf32 would miss this: float32 keeps 2^-20 next to 1
+    a2 = torch.zeros(1, 8); a2[0, 0] = 1.0; a2[0, 1] = 1.0
+    w2 = torch.zeros(1, 8); w2[0, 0] = 1.0; w2[0, 1] = 2.0 ** -20
+    o2 = torch.empty(1, 1, device=DEV)
+    ops.gemm_simt(a2.to(DEV), w2.to(DEV), o2)
+    assert o2.item() == 1.0 + 2.0 ** -20
+
+
+CASES_TC = [  # M, N, K, epi, swap, bn, ksplit
+    (128, 128, 64, 0, False, 128, 1), (200, 384, 520, 0, False, 128, 1), (130, 300, 72, 0, False, 128, 1),
+    (300, 520, 1000, 0, False, 256, 1), (257, 256, 2048, 0, False, 256, 3), (8, 256, 512, 0, True, 16, 1),
+    (5, 300, 72, 0, True, 16, 1), (33, 392, 1024, 0, True, 64, 4), (64, 520, 4096, 0, True, 64, 8),
+    (100, 264, 2048, 1, True, 128, 3), (256, 448, 512, 2, False, 128, 1), (7, 448, 512, 2, True, 16, 1),
+    (20, 4128, 1024, 2, True, 32, 2), (1, 96, 8, 0, True, 16, 1)]
+
+
+@pytest.mark.parametrize("M,N,K,epi,swap,bn,ksplit", CASES_TC)
+def test_gemm_tcgen05_against_the_plain_kernel(M, N, K, epi, swap, bn, ksplit):
+    from airun_b200.kernels import fast, ops
+    torch.manual_seed(5)
+    x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(N, K, device=DEV) * 0.1).to(torch.bfloat16)
+    ref = torch.empty(M, N, device=DEV)
+    ops.gemm_simt(x, w, ref)                                   # float32 accumulation of the same operands
+    err = _err()
+    if epi == 2:
+        g = ref.view(M, N // 32, 2, 16)
+        want = (g[:, :, 0] / (1 + torch.exp(-g[:, :, 0])) * g[:, :, 1]).reshape(M, N // 2)
+        out = torch.full((M, N // 2), 7.0, dtype=torch.bfloat16, device=DEV)
+    else:
+        want = ref
+        out = torch.full((M, N), 7.0, dtype=torch.float32 if epi == 0 else torch.bfloat16, device=DEV)
+    for _ in range(2):                                         # twice: the tile counters must come back to zero
+        fast.gemm_tcgen05(x, w, out, epi, swap, bn, ksplit, err)
+        torch.cuda.synchronize()
+        assert err.item() == 0
+        if epi == 0:
+            # same operands, float32 sums in another order
+            bound = 1e-5 * math.sqrt(K) * (x.float().abs() @ w.float().abs().T) + 1e-6
+            assert bool(((out - want).abs() <= bound).all())
+        else:
+            assert torch.allclose(out.float(), want, rtol=1e-2, atol=1e-2)
+        out.fill_(7.0)
+    want64 = x.cpu().double() @ w.cpu().double().T              # and the plain kernel itself is right
+    assert torch.allclose(ref.cpu().double(), want64, rtol=1e-4, atol=1e-4)
+
+
+def test_gemm_tcgen05_refuses_what_it_cannot_take():
+    from airun_b200.kernels import fast
+    from airun_b200.kernels.ops import KernelError
+    x = torch.zeros(4, 12, device=DEV, dtype=torch.bfloat16)          # K not a multiple of 8
+    w = torch.zeros(16, 12, device=DEV, dtype=torch.bfloat16)
+    with pytest.raises(KernelError):
+        fast.gemm_tcgen05(x, w, torch.zeros(4, 16, device=DEV), 0, True, 16, 1, _err())
+    x = torch.zeros(4, 16, device=DEV, dtype=torch.bfloat16)
+    w = torch.zeros(24, 16, device=DEV, dtype=torch.bfloat16)          # SwiGLU needs N % 32 == 0
+    with pytest.raises(KernelError):
+        fast.gemm_tcgen05(x, w, torch.zeros(4, 12, device=DEV, dtype=torch.bfloat16), 2, True, 16, 1, _err())
+
+
+# ----------------------------------------------------------------------------- q/k norm + rope + cache write
+@pytest.mark.parametrize("nh,nkv,hd,page,dtype", [(4, 2, 16, 4, torch.float32), (6, 3, 48, 16, torch.bfloat16),
+                                                  (8, 1, 128, 8, torch.float32), (3, 3, 80, 32, torch.float32)])
+def test_qkv_post_against_the_plain_parts(nh, nkv, hd, page, dtype):
+    from airun_b200.kernels import ops
+    from airun_b200.parts.rope import RotaryNeox
+    torch.manual_seed(6)
+    positions = [3, 17, 40, 41, 63, 0, 1, 2]                     # two requests; the first at scattered places
+    req = [0, 0, 0, 0, 0, 1, 1, 1]
+    T = len(positions)
+    qkv = torch.randn(T, (nh + 2 * nkv) * hd) * 2
+    qw, kw = 1 + 0.5 * torch.rand(hd), 1 + 0.5 * torch.rand(hd)
+    eps, theta = 1e-5, 1e6
+    rope = RotaryNeox(rotary_dim=hd, theta=theta, device=DEV)
+    n_pages = 40
+    pool = torch.zeros(n_pages, 2, nkv, page, hd, dtype=dtype, device=DEV)
+    bt = torch.full((2, 20), -1, dtype=torch.int32)
+    perm = np.random.default_rng(0).permutation(n_pages)
+    bt[0, :17] = torch.tensor(perm[:17].astype(np.int32))
+    bt[1, :3] = torch.tensor(perm[17:20].astype(np.int32))
+    q_out = torch.empty(T, nh * hd, dtype=dtype, device=DEV)
+    err = _err()
+    kind, rdim, inv = rope.fused()
+    ops.qkv_post(qkv.to(DEV), q_out, qw.to(DEV), kw.to(DEV), eps, torch.tensor(positions, dtype=torch.int32, device=DEV),
+                 torch.tensor(req, dtype=torch.int32, device=DEV), kind, rdim, inv, pool, bt.to(DEV), 2, page,
+                 nh, nkv, hd, err)
+    assert err.item() == 0
+    q = qkv[:, :nh * hd].view(T, nh, hd)
+    k = qkv[:, nh * hd:(nh + nkv) * hd].view(T, nkv, hd)
+    v = qkv[:, (nh + nkv) * hd:].view(T, nkv, hd)
+    want_q = P.plain_rope_neox(P.plain_rmsnorm(q, qw, eps), positions, theta, hd)
+    want_k = P.plain_rope_neox(P.plain_rmsnorm(k, kw, eps), positions, theta, hd)
+    tol = 2e-5 if dtype == torch.float32 else 2e-2
+    assert torch.allclose(q_out.cpu().float().view(T, nh, hd), want_q, rtol=tol, atol=tol)
+    poolc = pool.cpu().float()
+    for t in range(T):
+        pg, row = int(bt[req[t], positions[t] // page]), positions[t] % page
+        assert torch.allclose(poolc[pg, 0, :, row], want_k[t], rtol=tol, atol=tol)
+        assert torch.allclose(poolc[pg, 1, :, row], v[t].to(dtype).float(), rtol=0, atol=0)
+    written = sum(1 for _ in range(T)) * 2 * nkv * hd
+    assert int((poolc != 0).sum()) <= written                     # nothing else was touched
+    # a block-table entry outside the pool sets the flag and writes nothing
+    bad = bt.clone(); bad[1, 0] = n_pages + 3
+    pool2 = torch.zeros_like(pool)
+    ops.qkv_post(qkv.to(DEV), q_out, qw.to(DEV), kw.to(DEV), eps, torch.tensor(positions, dtype=torch.int32, device=DEV),
+                 torch.tensor(req, dtype=torch.int32, device=DEV), kind, rdim, inv, pool2, bad.to(DEV), 2, page,
+                 nh, nkv, hd, err)
+    assert err.item() == 1
+
+
+# ----------------------------------------------------------------------------- attention
+def attention_case(nh, nkv, hd, page, window, lens, qlens, dtype, seed, peaked=True):
+    """Requests with contexts ``lens``; the last ``qlens[i]`` tokens of each are this step's queries.
+    With ``peaked`` one far key per (request, head) is made to dominate, so a kernel that loses
+    it (a page's edge, a slice's edge, the window's edge) gives a visibly different row."""
+    torch.manual_seed(seed)
+    g = nh // nkv
+    ks = [torch.randn(n, nkv, hd) for n in lens]
+    vs = [torch.randn(n, nkv, hd) for n in lens]
+    qs, positions, req = [], [], []
+    for r, (n, ql) in enumerate(zip(lens, qlens)):
+        q = torch.randn(ql, nh, hd)
+        if peaked:
+            for i in range(ql):
+                pos = n - ql + i
+                lo = max(0, pos - window + 1) if window else 0
+                for h in range(nh):
+                    far = lo if (h + i) % 2 == 0 else (lo + pos) // 2     # the window's first key, or a middle one
+                    q[i, h] = q[i, h] * 0.3 + ks[r][far, h // g] * (6.0 / math.sqrt(hd))
+        qs.append(q)
+        positions += list(range(n - ql, n))
+        req += [r] * ql
+    scale = hd ** -0.5
+    ks = [k.to(dtype).float() for k in ks]
+    vs = [v.to(dtype).float() for v in vs]
+    qs = [q.to(dtype).float() for q in qs]
+    want = []
+    for r, (n, ql) in enumerate(zip(lens, qlens)):
+        # plain attention of the whole request, then the rows of this step's queries
+        full_q = torch.zeros(n, nh, hd)
+        full_q[n - ql:] = qs[r]
+        want.append(P.plain_attention(full_q, ks[r], vs[r], list(range(n)), scale, window)[n - ql:])
+    want = torch.cat(want).reshape(len(positions), nh * hd)
+    pool, bt = paged_from_dense(ks, vs, page, dtype, seed=seed)
+    q = torch.cat(qs).reshape(len(positions), nh * hd).to(dtype).to(DEV)
+    ctx = Ctx(positions, req, len(lens), list(qlens), list(lens))
+    return ctx, Cache(pool, bt, page), q, want, scale
+
+
+ATT = [  # nh, nkv, hd, page, window, context lengths, query lengths
+    (4, 2, 16, 4, 0, [5, 33, 70], [5, 1, 50]),            # a whole short prompt, one decoded token, a portion at 20..69
+    (8, 1, 32, 8, 0, [130, 17], [2, 17]),                 # MQA, a two-token portion
+    (6, 3, 48, 16, 24, [90, 25, 64], [1, 25, 40]),        # window 24, head size 48
+    (4, 4, 64, 32, 0, [300], [1]),                        # a far key among hundreds
+    (16, 2, 128, 16, 0, [257, 129], [1, 129]),            # page edge + 1
+    (2, 1, 128, 16, 100, [1000], [1]),                    # window in a long context
+    (20, 1, 16, 8, 0, [40, 9], [1, 9]),                   # more than 16 heads in a group
+]
+
+
+@pytest.mark.parametrize("case", ATT)
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_generic(case, dtype):
+    from airun_b200.kernels import ops
+    nh, nkv, hd, page, window, lens, qlens = case
+    ctx, cache, q, want, scale = attention_case(nh, nkv, hd, page, window, lens, qlens, dtype, seed=11)
+    out = torch.empty_like(q)
+    ops.attention_generic(q, out, cache.pool, cache.block_table, ctx.positions, ctx.req_of_token, ctx.num_reqs,
+                          nh, nkv, hd, scale, window, ctx.err)
+    assert ctx.err.item() == 0
+    tol = 1e-3 if dtype == torch.float32 else 2e-2           # 1e-3: the reference's float32 attention bound
+    assert torch.allclose(out.cpu().float(), want, rtol=tol, atol=tol)
+
+
+@pytest.mark.parametrize("case", ATT)
+def test_attention_tensor_core(case):
+    from airun_b200.kernels import fast
+    nh, nkv, hd, page, window, lens, qlens = case
+    ctx, cache, q, want, scale = attention_case(nh, nkv, hd, page, window, lens, qlens, torch.bfloat16, seed=12)
+    out = torch.full_like(q, 9.0)
+    assert fast.attention_bf16(ctx, q, out, cache, nh, nkv, hd, scale, window)
+    torch.cuda.synchronize()
+    assert ctx.err.item() == 0
+    assert torch.allclose(out.cpu().float(), want, rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("splits", [1, 2, 5, 16])
+def test_decode_attention_slices_agree(splits):
+    """Cutting the keys into slices changes nothing beyond rounding; empty slices are harmless."""
+    from airun_b200.kernels import fast
+    nh, nkv, hd, page, window = 8, 2, 64, 16, 0
+    lens = [1, 15, 16, 17, 100, 1000]
+    ctx, cache, q, want, scale = attention_case(nh, nkv, hd, page, window, lens, [1] * len(lens), torch.bfloat16, seed=13)
+    out = torch.full_like(q, 9.0)
+    rows = torch.arange(len(lens), dtype=torch.int32, device=DEV)
+    for _ in range(2):                                        # counters return to zero
+        fast.attn_decode(ctx, q, out, cache, nh, nkv, hd, scale, window, rows, len(lens), splits)
+        torch.cuda.synchronize()
+        assert ctx.err.item() == 0
+        assert torch.allclose(out.cpu().float(), want, rtol=2e-2, atol=2e-2)
+        out.fill_(9.0)
+
+
+def test_window_of_one_returns_the_value_at_its_own_place():
+    from airun_b200.kernels import fast, ops
+    nh, nkv, hd, page = 4, 2, 32, 8
+    for dtype in (torch.float32, torch.bfloat16):
+        ctx, cache, q, want, scale = attention_case(nh, nkv, hd, page, 1, [37, 50], [1, 20], dtype, seed=14, peaked=False)
+        out = torch.empty_like(q)
+        ops.attention_generic(q, out, cache.pool, cache.block_table, ctx.positions, ctx.req_of_token, 2,
+                              nh, nkv, hd, scale, 1, ctx.err)
+        assert torch.allclose(out.cpu().float(), want, rtol=1e-6, atol=1e-6)
+        if dtype == torch.bfloat16:
+            out2 = torch.empty_like(q)
+            assert fast.attention_bf16(ctx, q, out2, cache, nh, nkv, hd, scale, 1)
+            assert torch.allclose(out2.cpu().float(), want, rtol=1e-2, atol=1e-2)
+
+
+def test_attention_flags_a_bad_page():
+    from airun_b200.kernels import fast, ops
+    nh, nkv, hd, page = 4, 2, 64, 16
+    ctx, cache, q, want, scale = attention_case(nh, nkv, hd, page, 0, [40, 40], [1, 40], torch.bfloat16, seed=15)
+    cache.block_table[0, 1] = cache.pool.shape[0] + 7
+    out = torch.empty_like(q)
+    ops.attention_generic(q, out, cache.pool, cache.block_table, ctx.positions, ctx.req_of_token, 2,
+                          nh, nkv, hd, scale, 0, ctx.err)
+    assert ctx.err.item() == 1
+    ctx.err.zero_()
+    fast.attention_bf16(ctx, q, out, cache, nh, nkv, hd, scale, 0)
+    torch.cuda.synchronize()
+    assert ctx.err.item() == 1
+
+
+# ----------------------------------------------------------------------------- sampling
+def test_sample_kernel_first_maximum_and_temperature():
+    from airun_b200.kernels import ops
+    torch.manual_seed(7)
+    V = 151936
+    logits = torch.randn(6, V)
+    logits[0, 777] = logits[0, 90000] = 50.0                  # a tie: the first wins
+    logits[1] = float("-inf")                                 # all -inf gives 0
+    logits[2, :5] = float("nan"); logits[2, 9] = 40.0         # NaN never wins
+    logits[3, V - 1] = 60.0
+    picked = torch.zeros(6, dtype=torch.int32, device=DEV)
+    ops.sample(logits.to(DEV), picked)
+    got = picked.cpu().tolist()
+    assert got[:4] == [777, 0, 9, V - 1]
+    assert got[4] == P.plain_argmax(logits[4].tolist()) and got[5] == int(torch.argmax(logits[5]))
+    # temperature: the draw inverts the cumulative sum in vocabulary order at u * total
+    small = torch.log(torch.tensor([[0.5, 0.25, 0.125, 0.125]] * 4))
+    temp = torch.tensor([1.0, 1.0, 1.0, 0.0], device=DEV)
+    u = torch.tensor([0.1, 0.6, 0.99, 0.99], device=DEV)
+    out = torch.zeros(4, dtype=torch.int32, device=DEV)
+    ops.sample(small.to(DEV), out, temp, u)
+    assert out.cpu().tolist() == [0, 1, 3, 0]
+    # a large vocabulary: the picked index brackets the target in the host's cumulative sum
+    big = (torch.randn(3, 50000) * 2).to(DEV)
+    temp = torch.tensor([0.8, 1.3, 0.2], device=DEV)
+    u = torch.tensor([0.3, 0.77, 0.5], device=DEV)
+    out = torch.zeros(3, dtype=torch.int32, device=DEV)
+    ops.sample(big, out, temp, u)
+    for r in range(3):
+        l = big[r].cpu().double()
+        p = torch.exp((l - l.max()) / float(temp[r]))
+        cdf = torch.cumsum(p, 0) / p.sum()
+        i = int(out[r])
+        lo = float(cdf[i - 1]) if i > 0 else 0.0
+        assert lo - 1e-4 <= float(u[r]) <= float(cdf[i]) + 1e-4
+
+
+def test_sample_kernel_distribution():
+    from airun_b200.kernels import ops
+    probs = torch.tensor([0.4, 0.3, 0.2, 0.1])
+    n = 4000
+    logits = torch.log(probs).repeat(n, 1).to(DEV)
+    from airun_b200.sampling.sampler import XorShift64
+    rng = XorShift64(123)
+    u = torch.tensor([rng.next_f32() for _ in range(n)], device=DEV)
+    out = torch.zeros(n, dtype=torch.int32, device=DEV)
+    ops.sample(logits, out, torch.ones(n, device=DEV), u)
+    counts = np.bincount(out.cpu().numpy(), minlength=4)
+    chi2 = float(((counts - n * probs.numpy()) ** 2 / (n * probs.numpy())).sum())
+    assert chi2 < 16.3
