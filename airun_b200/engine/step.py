@@ -69,6 +69,14 @@ class StepRunner:
         self.ws_main = Workspace(self.device)
         self.ws_pair = (Workspace(self.device), Workspace(self.device))
         self.steps_run = 0
+        # CUDA graphs of decode-only steps, one per batch-size bucket
+        self.use_graphs = True
+        self.graph_buckets = [b for b in (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256) if b <= self.R_max]
+        if self.graph_buckets and self.graph_buckets[-1] < self.R_max and self.R_max <= 512:
+            self.graph_buckets.append(self.R_max)
+        self.graphs: Dict[int, tuple] = {}
+        self.graph_launches = 0
+        self.want_arange = torch.arange(max(self.R_max, 1), dtype=torch.int32, device=self.device)
 
     def _view(self, name: str, dev: bool = True):
         off, n = self.offsets[name]
@@ -123,8 +131,10 @@ class StepRunner:
         for e in entries:
             self.manager.reserve(e.rid, len(e.tokens))
 
-    def build_context(self, entries: Sequence[StepEntry]) -> tuple:
-        """Fills the staging buffer and returns (StepContext, n_want)."""
+    def build_context(self, entries: Sequence[StepEntry], pad_to: int = 0) -> tuple:
+        """Fills the staging buffer and returns (StepContext, n_want).  With ``pad_to`` the
+        batch is padded with rows that belong to no request (request -1, position -1), which
+        every kernel skips; that is how a captured graph of a fixed size runs a smaller batch."""
         m = self.manager
         self._ring_i = (self._ring_i + 1) % len(self._ring)
         self.meta_host, self.meta_np, self._meta_event = self._ring[self._ring_i]
@@ -157,12 +167,18 @@ class StepRunner:
                 bt[base:base + len(blocks)] = blocks
             t += n
         cu[len(entries)] = t
+        n_real = t
+        if pad_to > t:
+            tok[t:pad_to] = 0
+            pos[t:pad_to] = -1
+            rot[t:pad_to] = -1
+            t = pad_to
         self.meta_dev.copy_(self.meta_host, non_blocking=True)
         if self._meta_event is not None:
             self._meta_event.record()
             self._ring_used[self._ring_i] = True
         ctx = StepContext(
-            num_tokens=t, num_reqs=len(entries),
+            num_tokens=t, num_reqs=self.R_max if pad_to else len(entries),
             token_ids=self._view("token_ids"), positions=self._view("positions"),
             req_of_token=self._view("req_of_token"), cu_tokens=self._view("cu_tokens"),
             context_lens=self._view("context_lens"), state_slots=self._view("state_slots"),
@@ -177,12 +193,48 @@ class StepRunner:
         the device (valid until the next step) or None when nothing is wanted."""
         self.check_entries(entries)
         self.reserve(entries)
-        ctx, n_want = self.build_context(entries)
-        logits = self.model.forward(ctx, self._view("want_rows"), n_want)
+        if self.use_graphs and self.device.type == "cuda" and all(
+                len(e.tokens) == 1 and tuple(e.want) == (0,) for e in entries):
+            logits = self._decode_step_graphed(entries)
+        else:
+            ctx, n_want = self.build_context(entries)
+            logits = self.model.forward(ctx, self._view("want_rows"), n_want)
         for e in entries:
             self.manager.commit(e.rid, len(e.tokens))
         self.steps_run += 1
         return logits
+
+    def _decode_step_graphed(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """A step of single decoded tokens, all of whose logits are wanted, replayed from a
+        CUDA graph of the next larger captured batch size.  The reference captures its decode
+        step the same way, with token, position and cache addresses read from device buffers
+        that outlive the replays (crates/airun-core/src/runtime.rs:2285-2359).  Here the graph
+        reads the step's metadata from the runner's fixed device buffer; the number of key
+        slices of the attention kernel is fixed at capture for the longest allowed context."""
+        n = len(entries)
+        bucket = next((b for b in self.graph_buckets if b >= n), None)
+        if bucket is None:
+            ctx, n_want = self.build_context(entries)
+            return self.model.forward(ctx, self._view("want_rows"), n_want)
+        ctx, n_want = self.build_context(entries, pad_to=bucket)
+        entry = self.graphs.get(bucket)
+        if entry is None:
+            # the first step of this size runs eagerly (it loads and configures every kernel), then
+            # the same step is captured; replaying it writes the same keys and values again
+            ctx.extras["planning_context_len"] = self.max_context
+            self.model.forward(ctx, self.want_arange, bucket)
+            torch.cuda.current_stream().synchronize()
+            before = ops.LAUNCHES[0]
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                out = self.model.forward(ctx, self.want_arange, bucket)
+            entry = (graph, out, ops.LAUNCHES[0] - before)
+            ops.LAUNCHES[0] = before
+            self.graphs[bucket] = entry
+        graph, out, kernels = entry
+        graph.replay()
+        self.graph_launches += kernels
+        return out[:n]
 
     def device_error(self) -> int:
         """Error bits the kernels have set since the last call (synchronises)."""
