@@ -70,7 +70,7 @@ struct AttnParams {
     const int32_t* block_table;    // [R][max_blocks]
     const int32_t* positions;      // [T]
     const int32_t* req_of_token;   // [T]
-    int max_blocks, num_reqs, num_pages, page_size, nh, nkv, G;
+    int max_blocks, num_reqs, num_pages, page_size, page_shift, nh, nkv, G;   // page_shift: log2(page_size) or -1
     float scale_log2;              // scale * log2(e)
     int window;
     int* err;
@@ -79,8 +79,8 @@ struct AttnParams {
 // Address of key j's row (K) of KV head kvh; V is v_off elements further.  Returns nullptr for a
 // bad page (and records it).
 __device__ __forceinline__ const __nv_bfloat16* key_row(const AttnParams& p, const int32_t* bt, int kvh, int j) {
-    const int blk = j / p.page_size;
-    const int page = blk < p.max_blocks ? bt[blk] : -1;
+    const int blk = p.page_shift >= 0 ? (j >> p.page_shift) : j / p.page_size;
+    const int page = blk < p.max_blocks ? __ldg(bt + blk) : -1;
     if (page < 0 || page >= p.num_pages) { atomicOr(p.err, AIRUN_DEV_BAD_PAGE); return nullptr; }
     return p.pool + (((size_t)page * 2 * p.nkv + kvh) * p.page_size + (j - blk * p.page_size)) * HD;
 }
@@ -126,6 +126,7 @@ __global__ __launch_bounds__(128) void attn_prefill_kernel(const AttnParams p, c
     auto load_kv = [&](int tile, int stage) {
         const int j0 = tile * PN;
         uint32_t kb = smem_u32(sK + stage * PN * HD * 2), vb = smem_u32(sV + stage * PN * HD * 2);
+#pragma unroll 4
         for (int i = threadIdx.x; i < PN * CHUNKS; i += 128) {
             const int r = i / CHUNKS, c = i - r * CHUNKS;
             const int j = j0 + r;
@@ -212,8 +213,10 @@ __global__ __launch_bounds__(128) void attn_prefill_kernel(const AttnParams p, c
         }
         l0 = l0 * c0 + rs0;
         l1 = l1 * c1 + rs1;
+        if (__any_sync(0xffffffffu, c0 != 1.0f || c1 != 1.0f)) {      // the maximum moved somewhere in the warp
 #pragma unroll
-        for (int n = 0; n < HD / 8; ++n) { o[n][0] *= c0; o[n][1] *= c0; o[n][2] *= c1; o[n][3] *= c1; }
+            for (int n = 0; n < HD / 8; ++n) { o[n][0] *= c0; o[n][1] *= c0; o[n][2] *= c1; o[n][3] *= c1; }
+        }
 #pragma unroll
         for (int kk = 0; kk < PN / 16; ++kk) {
 #pragma unroll
@@ -249,6 +252,7 @@ __global__ __launch_bounds__(128) void attn_prefill_kernel(const AttnParams p, c
 #define DW 4                    // warps per CTA
 #define DSTAGES 2
 #define DN 16                   // keys per tile
+#define MAX_SPLITS 64
 
 struct DecodeExtra {
     const int32_t* rows;        // [n] batch rows (tokens) this launch handles
@@ -298,17 +302,35 @@ __global__ __launch_bounds__(32 * DW) void attn_decode_kernel(const AttnParams p
     const int my_n = te > tb + warp ? (te - tb - warp + DW - 1) / DW : 0;      // tiles tb+warp, tb+warp+DW, ...
 
     uint8_t* wbase = smem + warp * WARP_BYTES;
+    // A 16-key tile lies inside one page when the page size is a multiple of 16: one block-table
+    // lookup per tile, and the tile's K rows (and V rows) are one contiguous run of 16 * HD values.
+    const bool one_page = p.page_shift >= 4;
     auto load_tile = [&](int tile, int stage) {
         const int j0 = tile * DN;
         const uint32_t kb = smem_u32(wbase + stage * 2 * TILE_BYTES), vb = kb + TILE_BYTES;
-        for (int i = lane; i < DN * CHUNKS; i += 32) {
-            const int r = i / CHUNKS, c = i - r * CHUNKS;
-            const int j = j0 + r;
-            const __nv_bfloat16* src = (j <= pos && j >= k_first) ? key_row(p, bt, kvh, j) : nullptr;
-            const bool valid = src != nullptr;
-            const __nv_bfloat16* s = valid ? src + c * 8 : p.pool;
-            cp_async16(kb + tile_off(r, c), s, valid);
-            cp_async16(vb + tile_off(r, c), valid ? s + v_off : s, valid);
+        if (one_page) {
+            const __nv_bfloat16* base = key_row(p, bt, kvh, j0);
+            const bool inside = j0 >= k_first && j0 + DN - 1 <= pos;
+#pragma unroll
+            for (int k = 0; k < DN * CHUNKS / 32; ++k) {
+                const int i = lane + 32 * k;
+                const int r = i / CHUNKS, c = i - r * CHUNKS;
+                const bool valid = base != nullptr && (inside || (j0 + r <= pos && j0 + r >= k_first));
+                const __nv_bfloat16* s = valid ? base + i * 8 : p.pool;
+                cp_async16(kb + tile_off(r, c), s, valid);
+                cp_async16(vb + tile_off(r, c), valid ? s + v_off : s, valid);
+            }
+        } else {
+#pragma unroll 4
+            for (int i = lane; i < DN * CHUNKS; i += 32) {
+                const int r = i / CHUNKS, c = i - r * CHUNKS;
+                const int j = j0 + r;
+                const __nv_bfloat16* src = (j <= pos && j >= k_first) ? key_row(p, bt, kvh, j) : nullptr;
+                const bool valid = src != nullptr;
+                const __nv_bfloat16* s = valid ? src + c * 8 : p.pool;
+                cp_async16(kb + tile_off(r, c), s, valid);
+                cp_async16(vb + tile_off(r, c), valid ? s + v_off : s, valid);
+            }
         }
         cp_commit();
     };
@@ -373,8 +395,10 @@ __global__ __launch_bounds__(32 * DW) void attn_decode_kernel(const AttnParams p
         }
         l0 = l0 * c0 + rs0;
         l1 = l1 * c1 + rs1;
+        if (__any_sync(0xffffffffu, c0 != 1.0f || c1 != 1.0f)) {      // the maximum moved somewhere in the warp
 #pragma unroll
-        for (int n = 0; n < HD / 8; ++n) { o[n][0] *= c0; o[n][1] *= c0; o[n][2] *= c1; o[n][3] *= c1; }
+            for (int n = 0; n < HD / 8; ++n) { o[n][0] *= c0; o[n][1] *= c0; o[n][2] *= c1; o[n][3] *= c1; }
+        }
 #pragma unroll
         for (int n2 = 0; n2 < HD / 16; ++n2) {
             uint32_t b[4];
@@ -431,20 +455,44 @@ __global__ __launch_bounds__(32 * DW) void attn_decode_kernel(const AttnParams p
     if (s_ticket != x.n_splits - 1) return;
     __threadfence();
     if (threadIdx.x == 0) x.counters[unit] = 0;
+    // The last CTA of this token and head group merges the slices, in slice order.
     const float* all = x.scratch + (size_t)unit * x.n_splits * (16 * (HD + 2));
-    for (int e = threadIdx.x; e < heads * HD; e += 32 * DW) {
-        const int r = e / HD, d = e - r * HD;
+    __shared__ float s_f[MAX_SPLITS][16];
+    __shared__ float s_inv[16];
+    for (int i = threadIdx.x; i < x.n_splits * 16; i += 32 * DW) {
+        const int sp = i >> 4, r = i & 15;
+        s_f[sp][r] = r < heads ? __ldcg(all + (size_t)sp * 16 * (HD + 2) + r * (HD + 2)) : NEG_BIG;      // the slice's maximum
+    }
+    __syncthreads();
+    if (threadIdx.x < heads) {
+        const int r = threadIdx.x;
         float gm = NEG_BIG;
-        for (int sp = 0; sp < x.n_splits; ++sp) gm = fmaxf(gm, __ldcg(all + (size_t)sp * 16 * (HD + 2) + r * (HD + 2)));
-        float acc = 0.0f, sum = 0.0f;
+        for (int sp = 0; sp < x.n_splits; ++sp) gm = fmaxf(gm, s_f[sp][r]);
+        float sum = 0.0f;
         for (int sp = 0; sp < x.n_splits; ++sp) {
-            const float* ps = all + (size_t)sp * 16 * (HD + 2) + r * (HD + 2);
-            const float l = __ldcg(ps + 1);
-            const float f = l > 0.0f ? exp2f(__ldcg(ps) - gm) : 0.0f;
-            acc = fmaf(__ldcg(ps + 2 + d), f, acc);
+            const float l = __ldcg(all + (size_t)sp * 16 * (HD + 2) + r * (HD + 2) + 1);
+            const float f = l > 0.0f ? exp2f(s_f[sp][r] - gm) : 0.0f;
+            s_f[sp][r] = f;
             sum = fmaf(l, f, sum);
         }
-        p.out[((size_t)tok * p.nh + head0 + r) * HD + d] = __float2bfloat16_rn(sum > 0.0f ? acc / sum : 0.0f);
+        s_inv[r] = sum > 0.0f ? 1.0f / sum : 0.0f;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < heads * HD; e += 32 * DW) {
+        const int r = e / HD, d = e - r * HD;
+        const float* ps = all + r * (HD + 2) + 2 + d;
+        float acc = 0.0f;
+        int sp = 0;
+        for (; sp + 4 <= x.n_splits; sp += 4) {
+            const float v0 = __ldcg(ps + (size_t)(sp + 0) * 16 * (HD + 2)), v1 = __ldcg(ps + (size_t)(sp + 1) * 16 * (HD + 2));
+            const float v2 = __ldcg(ps + (size_t)(sp + 2) * 16 * (HD + 2)), v3 = __ldcg(ps + (size_t)(sp + 3) * 16 * (HD + 2));
+            acc = fmaf(v0, s_f[sp][r], acc);
+            acc = fmaf(v1, s_f[sp + 1][r], acc);
+            acc = fmaf(v2, s_f[sp + 2][r], acc);
+            acc = fmaf(v3, s_f[sp + 3][r], acc);
+        }
+        for (; sp < x.n_splits; ++sp) acc = fmaf(__ldcg(ps + (size_t)sp * 16 * (HD + 2)), s_f[sp][r], acc);
+        p.out[((size_t)tok * p.nh + head0 + r) * HD + d] = __float2bfloat16_rn(acc * s_inv[r]);
     }
 }
 
@@ -455,6 +503,8 @@ AttnParams make_params(const void* q, void* out, const void* pool, const int32_t
     p.q = (const __nv_bfloat16*)q; p.out = (__nv_bfloat16*)out; p.pool = (const __nv_bfloat16*)pool;
     p.block_table = block_table; p.positions = positions; p.req_of_token = req_of_token;
     p.max_blocks = max_blocks; p.num_reqs = num_reqs; p.num_pages = num_pages; p.page_size = page_size;
+    p.page_shift = -1;
+    for (int sft = 0; sft < 20; ++sft) if ((1 << sft) == page_size) p.page_shift = sft;
     p.nh = nh; p.nkv = nkv; p.G = nh / nkv; p.scale_log2 = scale * LOG2E; p.window = window; p.err = err;
     return p;
 }
@@ -498,7 +548,7 @@ AIRUN_EXPORT int airun_attn_decode(const void* q, void* out, const void* pool, c
                                    int num_reqs, int num_pages, int page_size, int nh, int nkv, float scale,
                                    int window, const int32_t* rows, int n_rows, int n_splits, float* scratch,
                                    int* counters, int* err, cudaStream_t stream) {
-    if (n_rows < 0 || nh <= 0 || nkv <= 0 || nh % nkv != 0 || page_size <= 0 || n_splits < 1 || !err) return AIRUN_ERR_ARG;
+    if (n_rows < 0 || nh <= 0 || nkv <= 0 || nh % nkv != 0 || page_size <= 0 || n_splits < 1 || n_splits > MAX_SPLITS || !err) return AIRUN_ERR_ARG;
     if (n_splits > 1 && (!scratch || !counters)) return AIRUN_ERR_ARG;
     if (n_rows == 0) return AIRUN_OK;
     const int hgroups = (nh / nkv + 15) / 16;

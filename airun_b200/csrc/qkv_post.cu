@@ -45,7 +45,7 @@ __global__ __launch_bounds__(256) void qkv_post_kernel(
     const int total_heads = kv_from_qkv ? nh + 2 * nkv : nh;
     const int half = rotary_dim / 2;
 
-    for (int h = warp; h < total_heads; h += nwarp) {
+    for (int h = blockIdx.y * nwarp + warp; h < total_heads; h += gridDim.y * nwarp) {
         const bool is_q = h < nh;
         const bool is_k = !is_q && h < nh + nkv;
         const float* src = qkv + (size_t)t * ld_qkv + (size_t)h * hd;
@@ -136,10 +136,13 @@ AIRUN_EXPORT int airun_qkv_post(
     if (q_dtype != kv_dtype) return AIRUN_ERR_UNSUPPORTED;
     if (T == 0) return AIRUN_OK;
     const int heads = kv_from_qkv ? nh + 2 * nkv : nh;
-    int warps = heads < 8 ? heads : 8;
+    // few tokens: one head per warp and many small blocks, so a decode step is not a handful of
+    // blocks each walking all heads; many tokens: eight heads per block
+    int warps = T <= 64 ? (heads < 2 ? heads : 2) : (heads < 8 ? heads : 8);
+    const int blocks_y = T <= 64 ? (heads + warps - 1) / warps : 1;
     const size_t smem = (size_t)warps * hd * sizeof(float);
 #define LAUNCH(TQ, TKV) \
-    qkv_post_kernel<TQ, TKV><<<T, warps * 32, smem, stream>>>(qkv, ld_qkv, (TQ*)q_out, q_norm_w, k_norm_w, eps, \
+    qkv_post_kernel<TQ, TKV><<<dim3(T, blocks_y), warps * 32, smem, stream>>>(qkv, ld_qkv, (TQ*)q_out, q_norm_w, k_norm_w, eps, \
         positions, req_of_token, rope_kind, rotary_dim, inv_freq, (TKV*)pool, block_table, max_blocks, num_reqs, \
         num_pages, page_size, do_store, kv_from_qkv, nh, nkv, hd, err)
     if (q_dtype == AIRUN_DT_F32) LAUNCH(float, float);

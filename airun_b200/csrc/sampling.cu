@@ -51,10 +51,30 @@ __device__ BestPair block_best(BestPair p, BestPair* sh) {
 // One block per row.  Each thread owns one contiguous slice of the vocabulary so
 // that the per-thread sums, scanned in thread order, form the cumulative sum in
 // vocabulary order.
+// First stage of the argmax over a large vocabulary: block (c, r) finds the first maximum of its
+// slice of row r.  The reference splits its device argmax the same way
+// (crates/airun-cuda/kernels/ops.cu:118-149: 128 partial blocks, then one final block).
+#define ARGMAX_CHUNKS 64
+__global__ __launch_bounds__(256) void argmax_partial_kernel(
+    const float* __restrict__ logits, long long ld, int V, BestPair* __restrict__ partial) {
+    __shared__ BestPair sh_best[33];
+    const int r = blockIdx.y, c = blockIdx.x;
+    const float* row = logits + (size_t)r * ld;
+    const int per = (V + ARGMAX_CHUNKS - 1) / ARGMAX_CHUNKS;
+    const int lo = min(V, c * per), hi = min(V, lo + per);
+    BestPair best{-INFINITY, 0x7fffffff};
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+        const float v = row[i];
+        if (v > best.v) { best.v = v; best.i = i; }
+    }
+    best = block_best(best, sh_best);
+    if (threadIdx.x == 0) partial[(size_t)r * ARGMAX_CHUNKS + c] = best;
+}
+
 __global__ __launch_bounds__(SAMPLE_THREADS) void sample_kernel(
     const float* __restrict__ logits, long long ld, int V,
     const float* __restrict__ temperature, const float* __restrict__ uniform,
-    int32_t* __restrict__ out) {
+    int32_t* __restrict__ out, const BestPair* __restrict__ partial) {
     __shared__ BestPair sh_best[33];
     __shared__ float sh_sum[SAMPLE_THREADS];
     __shared__ float red[33];
@@ -63,9 +83,13 @@ __global__ __launch_bounds__(SAMPLE_THREADS) void sample_kernel(
     const float* row = logits + (size_t)r * ld;
 
     BestPair best{-INFINITY, 0x7fffffff};
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
-        const float v = row[i];
-        if (v > best.v) { best.v = v; best.i = i; }     // NaN compares false: never wins
+    if (partial) {
+        if (threadIdx.x < ARGMAX_CHUNKS) best = partial[(size_t)r * ARGMAX_CHUNKS + threadIdx.x];
+    } else {
+        for (int i = threadIdx.x; i < V; i += blockDim.x) {
+            const float v = row[i];
+            if (v > best.v) { best.v = v; best.i = i; }     // NaN compares false: never wins
+        }
     }
     best = block_best(best, sh_best);
     if (best.i == 0x7fffffff) best.i = 0;               // all -inf or NaN
@@ -109,12 +133,20 @@ __global__ __launch_bounds__(SAMPLE_THREADS) void sample_kernel(
     }
 }
 
+// scratch: rows * 64 * 8 bytes for the first stage of the argmax, or null (one block per row then
+// walks the whole row, which is fine for small vocabularies).
 AIRUN_EXPORT int airun_sample(const float* logits, long long ld, int rows, int V,
                               const float* temperature, const float* uniform,
-                              int32_t* out, cudaStream_t stream) {
+                              int32_t* out, void* scratch, cudaStream_t stream) {
     if (rows < 0 || V <= 0 || ld < V) return AIRUN_ERR_ARG;
     if (temperature && !uniform) return AIRUN_ERR_ARG;
     if (rows == 0) return AIRUN_OK;
-    sample_kernel<<<rows, SAMPLE_THREADS, 0, stream>>>(logits, ld, V, temperature, uniform, out);
+    if (rows > 65535) return AIRUN_ERR_ARG;
+    BestPair* partial = nullptr;
+    if (scratch && V >= 8192) {
+        partial = (BestPair*)scratch;
+        argmax_partial_kernel<<<dim3(ARGMAX_CHUNKS, rows), 256, 0, stream>>>(logits, ld, V, partial);
+    }
+    sample_kernel<<<rows, SAMPLE_THREADS, 0, stream>>>(logits, ld, V, temperature, uniform, out, partial);
     return airun_launch_status();
 }

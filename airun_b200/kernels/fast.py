@@ -119,7 +119,7 @@ def linear_swiglu_bf16(ctx, x: torch.Tensor, w_gu: torch.Tensor, out: torch.Tens
 
 # ---------------------------------------------------------------- attention
 _ARANGE: Dict[torch.device, torch.Tensor] = {}
-DECODE_TARGET_CTAS = 592               # four CTAs for each of 148 SMs
+DECODE_SLOTS = 444                     # CTAs of the decode kernel resident at once: three on each of 148 SMs
 DECODE_MIN_KEYS_PER_SPLIT = 128
 
 
@@ -175,11 +175,19 @@ def attn_decode(ctx, q, out, cache, nh, nkv, hd, scale, window, rows: torch.Tens
 
 
 def plan_decode_splits(n_rows: int, nkv: int, hgroups: int, context_len: int, hd: int) -> int:
+    """Slices of the keys per (token, KV head): the count that needs the least time when CTAs run
+    in waves of DECODE_SLOTS, i.e. minimises ceil(units * s / slots) / s."""
     units = max(1, n_rows * nkv * hgroups)
-    splits = max(1, min(DECODE_TARGET_CTAS // units, (context_len + DECODE_MIN_KEYS_PER_SPLIT - 1) // DECODE_MIN_KEYS_PER_SPLIT))
-    while splits > 1 and units * splits * 16 * (hd + 2) > SCRATCH_FLOATS:
-        splits -= 1
-    return splits
+    most = max(1, min(64, (context_len + DECODE_MIN_KEYS_PER_SPLIT - 1) // DECODE_MIN_KEYS_PER_SPLIT))
+    best, best_cost = 1, None
+    for s in range(1, most + 1):
+        if s > 1 and units * s * 16 * (hd + 2) > SCRATCH_FLOATS:
+            break
+        waves = -(-units * s // DECODE_SLOTS)
+        cost = waves / s + s * 16.0 / max(context_len, 16)     # plus about one tile of work for every slice's merge
+        if best_cost is None or cost < best_cost - 1e-9:
+            best, best_cost = s, cost
+    return best
 
 
 def _attention_plan(ctx, G: int):

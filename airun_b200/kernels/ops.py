@@ -250,10 +250,19 @@ def sample(logits: torch.Tensor, out: torch.Tensor, temperature: Optional[torch.
     for t in (temperature, uniform):
         if t is not None:
             _need(t.dtype == torch.float32 and t.shape[0] >= R and t.is_contiguous(), "temperature / uniform must be float32 [R]")
+    scratch = None
+    if V >= 8192:
+        scratch = _SAMPLE_SCRATCH.get(logits.device)
+        if scratch is None or scratch.numel() < R * 128:
+            scratch = torch.empty(max(R, 256) * 128, dtype=torch.int32, device=logits.device)
+            _SAMPLE_SCRATCH[logits.device] = scratch
     f = _fn("sampling", "airun_sample",
-            [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
+            [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
     _check(f(_p(logits), logits.stride(0) if R > 1 else max(V, logits.stride(0)), R, V,
-             _p(temperature), _p(uniform), _p(out), _stream()), "sample")
+             _p(temperature), _p(uniform), _p(out), _p(scratch), _stream()), "sample")
+
+
+_SAMPLE_SCRATCH = {}
 
 
 def describe_device_error(bits: int) -> str:

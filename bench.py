@@ -225,6 +225,7 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--dtype", default="bfloat16")
     ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--decode-only", action="store_true", help="time the decode step only (for profiling runs)")
     a = ap.parse_args()
     if a.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -258,6 +259,10 @@ def main() -> int:
     clocks = sampler.stop()
     value = a.batch / (ms / 1e3)
 
+    if a.decode_only:
+        print(json.dumps({"decode_only": True, "ms_per_step": round(ms, 4), "value": round(value, 2),
+                          "layers": L, "batch": a.batch, "context": a.context}))
+        return 0
     e2e_ms, h2d, d2h = time_e2e(eng, a.batch, a.context, a.steps, a.warmup)
     points = {}
     if not a.skip_points:
