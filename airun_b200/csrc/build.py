@@ -125,6 +125,14 @@ def build(name: str, defines: Optional[Dict[str, object]] = None,
             os.unlink(tmp)
         raise BuildError(f"nvcc failed on {source} (exit {proc.returncode}):\n{' '.join(cmd)}\n{out}")
     os.replace(tmp, path)
+    # libraries of older versions of this source (another hash) are of no use any more
+    prefix = os.path.basename(path).rsplit("_", 1)[0] + "_"
+    for f in os.listdir(os.path.dirname(path)):
+        if f.startswith(prefix) and f.endswith(".so") and f != os.path.basename(path):
+            try:
+                os.unlink(os.path.join(os.path.dirname(path), f))
+            except OSError:
+                pass
     if not quiet:
         print(f"[airun_b200] compiled {label} in {time.time() - t0:.1f} s", file=sys.stderr, flush=True)
     return path
