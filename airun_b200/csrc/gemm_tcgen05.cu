@@ -486,3 +486,99 @@ AIRUN_EXPORT int airun_gemm_tcgen05(const void* x, const void* W, void* out, int
     if (epi == EPI_SWIGLU) return dispatch<EPI_SWIGLU>(swap != 0, bn, ma, mb, p, grid, stream);
     return AIRUN_ERR_UNSUPPORTED;
 }
+
+// ------------------------------------------------------------------ no-allocation variant
+// See gemm_tcgen05_static.h: the same kernel, with its split-K scratch in arrays that belong
+// to this library instead of buffers the caller allocates.
+#include "gemm_tcgen05_static.h"
+
+static __device__ __align__(256) float g_static_scratch[AIRUN_STATIC_SCRATCH_FLOATS];
+static __device__ __align__(256) int g_static_counters[AIRUN_STATIC_COUNTERS];
+
+namespace {
+constexpr int STATIC_MAX_DEVICES = 64;
+float* g_static_scratch_addr[STATIC_MAX_DEVICES];
+int* g_static_counters_addr[STATIC_MAX_DEVICES];
+std::mutex g_static_mu;
+
+// In host code the array names above are only stand-ins; the device addresses come from
+// cudaGetSymbolAddress, once per device, with that device current.
+int static_addresses(float** scratch, int** counters) {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= STATIC_MAX_DEVICES) return AIRUN_ERR_STATIC_SETUP;
+    std::lock_guard<std::mutex> g(g_static_mu);
+    if (!g_static_scratch_addr[dev]) {
+        float* s = nullptr;
+        int* c = nullptr;
+        if (cudaGetSymbolAddress((void**)&s, g_static_scratch) != cudaSuccess || !s) return AIRUN_ERR_STATIC_SETUP;
+        if (cudaGetSymbolAddress((void**)&c, g_static_counters) != cudaSuccess || !c) return AIRUN_ERR_STATIC_SETUP;
+        g_static_scratch_addr[dev] = s;
+        g_static_counters_addr[dev] = c;
+    }
+    *scratch = g_static_scratch_addr[dev];
+    *counters = g_static_counters_addr[dev];
+    return AIRUN_OK;
+}
+
+// A tensor map made on the spot, without the cache (which lives on the host heap).
+int make_map_uncached(CUtensorMap* out, const void* ptr, long long rows, long long K, long long ld, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return AIRUN_ERR_UNSUPPORTED;
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? AIRUN_OK : AIRUN_ERR_ARG;
+}
+}  // namespace
+
+AIRUN_EXPORT int airun_gemm_tcgen05_static(const void* x, const void* W, void* out, int M, int N, int K,
+                                           long long ldx, long long ldw, long long ldc, int epi, int swap, int bn,
+                                           int ksplit, int* err, cudaStream_t stream) {
+    if (M <= 0 || N <= 0 || K <= 0 || !err) return M == 0 ? AIRUN_OK : AIRUN_ERR_ARG;
+    if (K % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0 || ((uintptr_t)x & 15) || ((uintptr_t)W & 15)) return AIRUN_ERR_ARG;
+    if (epi == EPI_SWIGLU && (N % 32 != 0)) return AIRUN_ERR_ARG;
+    if (ksplit < 1) return AIRUN_ERR_ARG;
+    if (swap ? !(bn == 16 || bn == 32 || bn == 64 || bn == 128) : !(bn == 128 || bn == 256)) return AIRUN_ERR_UNSUPPORTED;
+    const int kb_total = (K + BK - 1) / BK;
+    if (ksplit > kb_total) ksplit = kb_total;
+    GemmParams p;
+    p.a_rows = swap ? N : M;
+    p.b_rows = swap ? M : N;
+    p.K = K;
+    p.k_blocks_per_split = (kb_total + ksplit - 1) / ksplit;
+    p.ksplit = (kb_total + p.k_blocks_per_split - 1) / p.k_blocks_per_split;
+    p.out = out;
+    p.ldc = ldc;
+    p.err = err;
+    p.scratch = nullptr;
+    p.counters = nullptr;
+    const long long tiles = (long long)((p.a_rows + BM - 1) / BM) * ((p.b_rows + bn - 1) / bn);
+    if (p.ksplit > 1) {
+        if (tiles * p.ksplit * bn * BM > (long long)AIRUN_STATIC_SCRATCH_FLOATS || tiles > AIRUN_STATIC_COUNTERS)
+            return AIRUN_ERR_STATIC_TOO_LARGE;
+        const int r = static_addresses(&p.scratch, &p.counters);
+        if (r != AIRUN_OK) return r;
+        // the counters must start at zero whatever an earlier call left behind
+        cudaError_t e = cudaMemsetAsync(p.counters, 0, (size_t)tiles * sizeof(int), stream);
+        if (e != cudaSuccess) return (int)e;
+    }
+    CUtensorMap ma, mb;
+    int r;
+    if (swap) {
+        if ((r = make_map_uncached(&ma, W, N, K, ldw, BM)) != AIRUN_OK) return r;
+        if ((r = make_map_uncached(&mb, x, M, K, ldx, bn)) != AIRUN_OK) return r;
+    } else {
+        if ((r = make_map_uncached(&ma, x, M, K, ldx, BM)) != AIRUN_OK) return r;
+        if ((r = make_map_uncached(&mb, W, N, K, ldw, bn)) != AIRUN_OK) return r;
+    }
+    dim3 grid((p.a_rows + BM - 1) / BM, (p.b_rows + bn - 1) / bn, p.ksplit);
+    if (grid.y > 65535 || grid.z > 65535) return AIRUN_ERR_ARG;
+    if (epi == EPI_F32) return dispatch<EPI_F32>(swap != 0, bn, ma, mb, p, grid, stream);
+    if (epi == EPI_BF16) return dispatch<EPI_BF16>(swap != 0, bn, ma, mb, p, grid, stream);
+    if (epi == EPI_SWIGLU) return dispatch<EPI_SWIGLU>(swap != 0, bn, ma, mb, p, grid, stream);
+    return AIRUN_ERR_UNSUPPORTED;
+}
