@@ -75,6 +75,7 @@ class StepRunner:
         if self.graph_buckets and self.graph_buckets[-1] < self.R_max and self.R_max <= 512:
             self.graph_buckets.append(self.R_max)
         self.graphs: Dict[int, tuple] = {}
+        self._warm_buckets = set()
         self.graph_launches = 0
         self.want_arange = torch.arange(max(self.R_max, 1), dtype=torch.int32, device=self.device)
 
@@ -218,11 +219,14 @@ class StepRunner:
             return self.model.forward(ctx, self._view("want_rows"), n_want)
         ctx, n_want = self.build_context(entries, pad_to=bucket)
         entry = self.graphs.get(bucket)
+        ctx.extras["planning_context_len"] = self.max_context
         if entry is None:
-            # the first step of this size runs eagerly (it loads and configures every kernel), then
-            # the same step is captured; replaying it writes the same keys and values again
-            ctx.extras["planning_context_len"] = self.max_context
-            self.model.forward(ctx, self.want_arange, bucket)
+            if bucket not in self._warm_buckets:
+                # the first step of this size runs eagerly, on the padded batch: it loads and
+                # configures every kernel the graph will hold
+                self._warm_buckets.add(bucket)
+                return self.model.forward(ctx, self.want_arange, bucket)[:n]
+            # the second one is captured (capturing runs nothing) and then replayed below
             torch.cuda.current_stream().synchronize()
             before = ops.LAUNCHES[0]
             graph = torch.cuda.CUDAGraph()
