@@ -25,6 +25,8 @@ __global__ __launch_bounds__(32 * ATTN_WARPS) void attention_generic_kernel(
     const int32_t* __restrict__ positions, const int32_t* __restrict__ req_of_token,
     int num_reqs, int num_pages, int page_size, int nh, int nkv, int hd,
     float scale, int window, int* __restrict__ err) {
+    pdl_trigger();
+    pdl_wait();
     extern __shared__ float smem[];
     float* s_max = smem;
     float* s_sum = smem + ATTN_WARPS;
@@ -122,7 +124,7 @@ AIRUN_EXPORT int airun_attention_generic(
     dim3 grid(T, nh);
     const size_t smem = (size_t)ATTN_WARPS * (2 + hd) * sizeof(float);
 #define LAUNCH(TQ, TKV) \
-    attention_generic_kernel<TQ, TKV><<<grid, 32 * ATTN_WARPS, smem, stream>>>((const TQ*)q, (TQ*)out, (const TKV*)pool, \
+    airun_launch(attention_generic_kernel<TQ, TKV>, dim3(grid), dim3(32 * ATTN_WARPS), smem, stream, (const TQ*)q, (TQ*)out, (const TKV*)pool, \
         block_table, max_blocks, positions, req_of_token, num_reqs, num_pages, page_size, nh, nkv, hd, scale, window, err)
     if (q_dtype == AIRUN_DT_F32) LAUNCH(float, float);
     else if (q_dtype == AIRUN_DT_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);

@@ -92,6 +92,8 @@ __device__ __forceinline__ const __nv_bfloat16* key_row(const AttnParams& p, con
 struct PrefillTile { int req, tok0, n_tok, first_row; };   // tokens [tok0, tok0+n_tok) of the batch, all of request req
 
 __global__ __launch_bounds__(128) void attn_prefill_kernel(const AttnParams p, const int4* __restrict__ tiles) {
+    pdl_trigger();
+    pdl_wait();
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t* sQ = smem;                               // [PM][HD]
     uint8_t* sK = sQ + PM * HD * 2;                   // [2][PN][HD]
@@ -262,6 +264,8 @@ struct DecodeExtra {
 };
 
 __global__ __launch_bounds__(32 * DW) void attn_decode_kernel(const AttnParams p, const DecodeExtra x) {
+    pdl_trigger();
+    pdl_wait();
     extern __shared__ __align__(128) uint8_t smem[];
     // per warp: DSTAGES x (K tile + V tile); the Q tile [16][HD] sits after them
     constexpr int TILE_BYTES = DN * HD * 2;
@@ -533,7 +537,7 @@ AIRUN_EXPORT int airun_attn_prefill(const void* q, void* out, const void* pool, 
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    attn_prefill_kernel<<<dim3(n_tiles, nkv), 128, smem, stream>>>(p, (const int4*)tiles);
+    airun_launch(attn_prefill_kernel, dim3(dim3(n_tiles, nkv)), dim3(128), smem, stream, p, (const int4*)tiles);
     return airun_launch_status();
 }
 
@@ -563,6 +567,6 @@ AIRUN_EXPORT int airun_attn_decode(const void* q, void* out, const void* pool, c
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    attn_decode_kernel<<<dim3(n_splits, nkv * hgroups, n_rows), 32 * DW, smem, stream>>>(p, x);
+    airun_launch(attn_decode_kernel, dim3(dim3(n_splits, nkv * hgroups, n_rows)), dim3(32 * DW), smem, stream, p, x);
     return airun_launch_status();
 }

@@ -7,6 +7,7 @@
 #include <cuda_bf16.h>
 #include <stdint.h>
 #include <math.h>
+#include <stdlib.h>
 
 #define AIRUN_OK 0
 #define AIRUN_ERR_ARG 1000        // a size or pointer the kernel refuses
@@ -23,8 +24,51 @@
 
 #define AIRUN_EXPORT extern "C" __attribute__((visibility("default")))
 
+// Programmatic dependent launch: a kernel launched with the attribute may become resident while
+// the kernel before it in the stream is still running; it must call pdl_wait() before it touches
+// global memory that an earlier kernel writes or reads (the wait returns when the earlier kernels
+// have finished and their writes are visible).  Every kernel calls pdl_trigger() first, which lets
+// the kernel after it become resident as soon as room is free.  What a kernel does before
+// pdl_wait() (shared-memory barriers, tensor-memory allocation, loads of WEIGHTS, which no kernel
+// writes) overlaps the tail of the kernel before it.  AIRUN_PDL=0 in the environment turns it off.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+static thread_local int airun_launch_rc = 0;
+
+static inline bool airun_pdl_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char* e = getenv("AIRUN_PDL");
+        on = (e && e[0] == '0') ? 0 : 1;
+    }
+    return on == 1;
+}
+
+template <typename... KArgs, typename... Args>
+static inline void airun_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    if (airun_pdl_enabled()) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+    }
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+    if (e != cudaSuccess && airun_launch_rc == 0) airun_launch_rc = (int)e;
+}
+
 static inline int airun_launch_status() {
     cudaError_t e = cudaGetLastError();
+    int rc = airun_launch_rc;
+    airun_launch_rc = 0;
+    if (rc) return rc;
     return e == cudaSuccess ? AIRUN_OK : (int)e;
 }
 

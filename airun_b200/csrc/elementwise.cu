@@ -12,6 +12,8 @@
 template <typename TTab>
 __global__ void embed_kernel(const TTab* __restrict__ table, const int32_t* __restrict__ ids,
                              float* __restrict__ out, int H, int V, int* __restrict__ err) {
+    pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.x;
     int id = ids[t];
     if (id < 0 || id >= V) {
@@ -29,9 +31,9 @@ AIRUN_EXPORT int airun_embed(const void* table, int table_dtype, const int32_t* 
     if (T == 0) return AIRUN_OK;
     const int threads = H >= 1024 ? 256 : 128;
     if (table_dtype == AIRUN_DT_F32)
-        embed_kernel<float><<<T, threads, 0, stream>>>((const float*)table, ids, out, H, V, err);
+        airun_launch(embed_kernel<float>, dim3(T), dim3(threads), 0, stream, (const float*)table, ids, out, H, V, err);
     else if (table_dtype == AIRUN_DT_BF16)
-        embed_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>((const __nv_bfloat16*)table, ids, out, H, V, err);
+        airun_launch(embed_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, (const __nv_bfloat16*)table, ids, out, H, V, err);
     else
         return AIRUN_ERR_UNSUPPORTED;
     return airun_launch_status();
@@ -39,33 +41,71 @@ AIRUN_EXPORT int airun_embed(const void* table, int table_dtype, const int32_t* 
 
 // One block per output row.  Source row = rows ? rows[r] : r.  With `delta` the
 // sum x + delta is normed; it is written back to x only when write_back is set
-// (a gathered final norm leaves x alone).
-template <typename TOut>
+// (a gathered final norm leaves x alone).  VEC = 4 reads float4 (n % 4 == 0) and keeps up to
+// KEEP vectors per thread in registers between the two passes; longer rows are read again.
+#define KEEP 4
+template <typename TOut, int VEC>
 __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta,
                                const float* __restrict__ w, TOut* __restrict__ out,
                                const int32_t* __restrict__ rows, int n, float eps, int write_back) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float red[33];
     const int r = blockIdx.x;
     const int src = rows ? rows[r] : r;
     float* xr = x + (size_t)src * n;
     const float* dr = delta ? delta + (size_t)src * n : nullptr;
     TOut* outr = out + (size_t)r * n;
-
+    const int nv = n / VEC;                       // vectors in the row
+    float keep[KEEP][VEC];
     float ss = 0.0f;
-    for (int i = threadIdx.x; i < n; i += blockDim.x) {
-        float v = xr[i];
-        if (dr) {
-            v += dr[i];
-            if (write_back) xr[i] = v;
+#pragma unroll
+    for (int k = 0; k < KEEP; ++k) {
+        const int i = threadIdx.x + k * blockDim.x;
+        if (i < nv) {
+            if (VEC == 4) {
+                float4 v = reinterpret_cast<const float4*>(xr)[i];
+                if (dr) {
+                    const float4 d = reinterpret_cast<const float4*>(dr)[i];
+                    v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+                    if (write_back) reinterpret_cast<float4*>(xr)[i] = v;
+                }
+                keep[k][0] = v.x; keep[k][1 % VEC] = v.y; keep[k][2 % VEC] = v.z; keep[k][3 % VEC] = v.w;
+            } else {
+                float v = xr[i];
+                if (dr) { v += dr[i]; if (write_back) xr[i] = v; }
+                keep[k][0] = v;
+            }
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) ss = fmaf(keep[k][e], keep[k][e], ss);
         }
-        ss = fmaf(v, v, ss);
+    }
+    for (int i = threadIdx.x + KEEP * blockDim.x; i < nv; i += blockDim.x) {       // the rest of a long row
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+            float v = xr[i * VEC + e];
+            if (dr) { v += dr[i * VEC + e]; if (write_back) xr[i * VEC + e] = v; }
+            ss = fmaf(v, v, ss);
+        }
     }
     ss = block_sum(ss, red);
     const float inv = rsqrtf(ss / (float)n + eps);
-    for (int i = threadIdx.x; i < n; i += blockDim.x) {
-        float v = xr[i];
-        if (dr && !write_back) v += dr[i];
-        outr[i] = from_f32<TOut>(v * inv * (w ? w[i] : 1.0f));
+#pragma unroll
+    for (int k = 0; k < KEEP; ++k) {
+        const int i = threadIdx.x + k * blockDim.x;
+        if (i < nv) {
+#pragma unroll
+            for (int e = 0; e < VEC; ++e)
+                outr[i * VEC + e] = from_f32<TOut>(keep[k][e] * inv * (w ? w[i * VEC + e] : 1.0f));
+        }
+    }
+    for (int i = threadIdx.x + KEEP * blockDim.x; i < nv; i += blockDim.x) {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+            float v = xr[i * VEC + e];
+            if (dr && !write_back) v += dr[i * VEC + e];
+            outr[i * VEC + e] = from_f32<TOut>(v * inv * (w ? w[i * VEC + e] : 1.0f));
+        }
     }
 }
 
@@ -75,15 +115,18 @@ AIRUN_EXPORT int airun_rmsnorm(float* x, const float* delta, const float* w, voi
     if (n_rows < 0 || n <= 0) return AIRUN_ERR_ARG;
     if (rows && write_back) return AIRUN_ERR_ARG;
     if (n_rows == 0) return AIRUN_OK;
-    int threads = ((n + 3) / 4 + 31) / 32 * 32;
+    const bool vec = n % 4 == 0 && (((uintptr_t)x | (uintptr_t)delta) & 15) == 0;
+    const int nv = vec ? n / 4 : n;
+    int threads = (nv + 31) / 32 * 32;
     if (threads > 1024) threads = 1024;
     if (threads < 32) threads = 32;
-    if (out_dtype == AIRUN_DT_F32)
-        rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>(x, delta, w, (float*)out, rows, n, eps, write_back);
-    else if (out_dtype == AIRUN_DT_BF16)
-        rmsnorm_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>(x, delta, w, (__nv_bfloat16*)out, rows, n, eps, write_back);
-    else
-        return AIRUN_ERR_UNSUPPORTED;
+    if (n_rows <= 64 && threads > 256 && vec) threads = 256;      // few rows: more loads in flight per thread
+#define LAUNCH(TOut, VEC) \
+    airun_launch(rmsnorm_kernel<TOut, VEC>, dim3(n_rows), dim3(threads), 0, stream, x, delta, w, (TOut*)out, rows, n, eps, write_back)
+    if (out_dtype == AIRUN_DT_F32) { if (vec) LAUNCH(float, 4); else LAUNCH(float, 1); }
+    else if (out_dtype == AIRUN_DT_BF16) { if (vec) LAUNCH(__nv_bfloat16, 4); else LAUNCH(__nv_bfloat16, 1); }
+    else return AIRUN_ERR_UNSUPPORTED;
+#undef LAUNCH
     return airun_launch_status();
 }
 
@@ -92,6 +135,8 @@ AIRUN_EXPORT int airun_rmsnorm(float* x, const float* delta, const float* w, voi
 template <typename TIn, typename TOut>
 __global__ void swiglu_kernel(const TIn* __restrict__ in, TOut* __restrict__ out,
                               long long total, int I, int group) {
+    pdl_trigger();
+    pdl_wait();
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total) return;
     const long long t = idx / I;
@@ -111,11 +156,11 @@ AIRUN_EXPORT int airun_swiglu(const void* in, int in_dtype, void* out, int out_d
     const int threads = 256;
     const int blocks = ceil_div_i(total, threads);
     if (in_dtype == AIRUN_DT_F32 && out_dtype == AIRUN_DT_F32)
-        swiglu_kernel<float, float><<<blocks, threads, 0, stream>>>((const float*)in, (float*)out, total, I, group);
+        airun_launch(swiglu_kernel<float, float>, dim3(blocks), dim3(threads), 0, stream, (const float*)in, (float*)out, total, I, group);
     else if (in_dtype == AIRUN_DT_F32 && out_dtype == AIRUN_DT_BF16)
-        swiglu_kernel<float, __nv_bfloat16><<<blocks, threads, 0, stream>>>((const float*)in, (__nv_bfloat16*)out, total, I, group);
+        airun_launch(swiglu_kernel<float, __nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, (const float*)in, (__nv_bfloat16*)out, total, I, group);
     else if (in_dtype == AIRUN_DT_BF16 && out_dtype == AIRUN_DT_BF16)
-        swiglu_kernel<__nv_bfloat16, __nv_bfloat16><<<blocks, threads, 0, stream>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, total, I, group);
+        airun_launch(swiglu_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, (const __nv_bfloat16*)in, (__nv_bfloat16*)out, total, I, group);
     else
         return AIRUN_ERR_UNSUPPORTED;
     return airun_launch_status();
@@ -124,6 +169,8 @@ AIRUN_EXPORT int airun_swiglu(const void* in, int in_dtype, void* out, int out_d
 // out[r] = in[rows[r]] for rows of n elements of `elt` bytes (n*elt a multiple of 4).
 __global__ void gather_rows_kernel(const uint32_t* __restrict__ in, uint32_t* __restrict__ out,
                                    const int32_t* __restrict__ rows, int words) {
+    pdl_trigger();
+    pdl_wait();
     const uint32_t* s = in + (size_t)rows[blockIdx.x] * words;
     uint32_t* d = out + (size_t)blockIdx.x * words;
     for (int i = threadIdx.x; i < words; i += blockDim.x) d[i] = s[i];
@@ -133,6 +180,6 @@ AIRUN_EXPORT int airun_gather_rows(const void* in, void* out, const int32_t* row
                                    int row_bytes, cudaStream_t stream) {
     if (n_rows < 0 || row_bytes <= 0 || row_bytes % 4 != 0) return AIRUN_ERR_ARG;
     if (n_rows == 0) return AIRUN_OK;
-    gather_rows_kernel<<<n_rows, 256, 0, stream>>>((const uint32_t*)in, (uint32_t*)out, rows, row_bytes / 4);
+    airun_launch(gather_rows_kernel, dim3(n_rows), dim3(256), 0, stream, (const uint32_t*)in, (uint32_t*)out, rows, row_bytes / 4);
     return airun_launch_status();
 }

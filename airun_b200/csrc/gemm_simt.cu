@@ -18,6 +18,8 @@ template <typename TA, typename TW, typename TC>
 __global__ __launch_bounds__(256) void gemm_simt_kernel(
     const TA* __restrict__ A, const TW* __restrict__ W, TC* __restrict__ C,
     int M, int N, int K, long long lda, long long ldw, long long ldc) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ __align__(16) float As[TK][TM + PAD];
     __shared__ __align__(16) float Ws[TK][TN + PAD];
     const int tid = threadIdx.x;
@@ -78,7 +80,7 @@ AIRUN_EXPORT int airun_gemm_simt(const void* A, int a_dtype, const void* W, int 
     dim3 grid(ceil_div_i(N, TN), ceil_div_i(M, TM));
     if (grid.y > 65535) return AIRUN_ERR_ARG;
 #define LAUNCH(TA, TW, TC) \
-    gemm_simt_kernel<TA, TW, TC><<<grid, 256, 0, stream>>>((const TA*)A, (const TW*)W, (TC*)C, M, N, K, lda, ldw, ldc)
+    airun_launch(gemm_simt_kernel<TA, TW, TC>, dim3(grid), dim3(256), 0, stream, (const TA*)A, (const TW*)W, (TC*)C, M, N, K, lda, ldw, ldc)
     if (a_dtype == AIRUN_DT_F32 && w_dtype == AIRUN_DT_F32 && c_dtype == AIRUN_DT_F32) LAUNCH(float, float, float);
     else if (a_dtype == AIRUN_DT_BF16 && w_dtype == AIRUN_DT_BF16 && c_dtype == AIRUN_DT_F32) LAUNCH(__nv_bfloat16, __nv_bfloat16, float);
     else if (a_dtype == AIRUN_DT_BF16 && w_dtype == AIRUN_DT_BF16 && c_dtype == AIRUN_DT_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16, __nv_bfloat16);

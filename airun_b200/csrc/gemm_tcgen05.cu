@@ -216,6 +216,7 @@ __global__ __launch_bounds__(GEMM_THREADS, 1) void gemm_tcgen05_kernel(
     __shared__ int s_ticket;
     __shared__ int s_abort;
 
+    pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int a0 = blockIdx.x * BM;            // first A row of the tile
     const int b0 = blockIdx.y * BN;            // first B row of the tile
@@ -240,16 +241,36 @@ __global__ __launch_bounds__(GEMM_THREADS, 1) void gemm_tcgen05_kernel(
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // The weight operand (A when swapped, B otherwise) is written by no kernel, so the first stages'
+    // weight blocks are requested before waiting for the kernel before this one: the weights keep
+    // streaming across the boundary between two kernels.
+    const int n_pre = n_kb < STAGES ? n_kb : STAGES;
+    if (warp == 0 && lane == 0) {
+        for (int i = 0; i < n_pre; ++i) {
+            mbar_expect_tx(full0 + 8 * i, L::STAGE_BYTES);
+            const uint32_t sa = smem_u32(smem + i * L::STAGE_BYTES);
+            const int k = (kb_begin + i) * BK;
+            if (SWAP) tma_load_2d(sa, &map_a, full0 + 8 * i, k, a0);
+            else tma_load_2d(sa + L::A_BYTES, &map_b, full0 + 8 * i, k, b0);
+        }
+    }
+    // from here on the results of earlier kernels are read and their buffers written
+    pdl_wait();
 
     if (warp == 0) {
         if (lane == 0) {
             for (int i = 0; i < n_kb; ++i) {
                 const int s = i % STAGES;
+                const uint32_t sa = smem_u32(smem + s * L::STAGE_BYTES);
+                const int k = (kb_begin + i) * BK;
+                if (i < n_pre) {                 // the weight half of this stage is already on its way
+                    if (SWAP) tma_load_2d(sa + L::A_BYTES, &map_b, full0 + 8 * s, k, b0);
+                    else tma_load_2d(sa, &map_a, full0 + 8 * s, k, a0);
+                    continue;
+                }
                 const uint32_t phase = (i / STAGES) & 1;
                 if (!mbar_wait(empty0 + 8 * s, phase ^ 1)) { atomicOr(p.err, AIRUN_DEV_TIMEOUT); s_abort = 1; break; }
                 mbar_expect_tx(full0 + 8 * s, L::STAGE_BYTES);
-                const uint32_t sa = smem_u32(smem + s * L::STAGE_BYTES);
-                const int k = (kb_begin + i) * BK;
                 tma_load_2d(sa, &map_a, full0 + 8 * s, k, a0);
                 tma_load_2d(sa + L::A_BYTES, &map_b, full0 + 8 * s, k, b0);
             }
@@ -324,12 +345,23 @@ __global__ __launch_bounds__(GEMM_THREADS, 1) void gemm_tcgen05_kernel(
                 } else {
 #pragma unroll
                     for (int i = 0; i < 16; ++i) { v[i] = 0.0f; u[i] = 0.0f; }
-                    for (int s = 0; s < p.ksplit; ++s) {
-                        const float* ps = all + (size_t)s * (BN * BM) + quad * 32 + lane;
+                    // slices are added in order; loads of four slices are in flight at a time
+                    for (int s0 = 0; s0 < p.ksplit; s0 += 4) {
+                        float t[4][STEP];
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) {
-                            v[i] += __ldcg(ps + (size_t)(c + i) * BM);
-                            if (STEP == 32) u[i] += __ldcg(ps + (size_t)(c + 16 + i) * BM);
+                        for (int d = 0; d < 4; ++d) {
+                            const float* ps = all + (size_t)(s0 + d) * (BN * BM) + quad * 32 + lane;
+#pragma unroll
+                            for (int i = 0; i < STEP; ++i)
+                                t[d][i] = (s0 + d < p.ksplit) ? __ldcg(ps + (size_t)(c + i) * BM) : 0.0f;
+                        }
+#pragma unroll
+                        for (int d = 0; d < 4; ++d) {
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) {
+                                v[i] += t[d][i];
+                                if (STEP == 32) u[i] += t[d][(STEP == 32 ? 16 : 0) + i];
+                            }
                         }
                     }
                 }
@@ -418,7 +450,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, di
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    kern<<<grid, GEMM_THREADS, L::TOTAL, stream>>>(ma, mb, p);
+    airun_launch(kern, dim3(grid), dim3(GEMM_THREADS), L::TOTAL, stream, ma, mb, p);
     return airun_launch_status();
 }
 

@@ -35,15 +35,27 @@ __global__ __launch_bounds__(256) void qkv_post_kernel(
     TKV* __restrict__ pool, const int32_t* __restrict__ block_table, int max_blocks,
     int num_reqs, int num_pages, int page_size, int do_store, int kv_from_qkv,
     int nh, int nkv, int hd, int* __restrict__ err) {
+    pdl_trigger();
+    pdl_wait();
     extern __shared__ float smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nwarp = blockDim.x >> 5;
     float* row = smem + (size_t)warp * hd;
+    float* cs = smem + (size_t)nwarp * hd;          // cos[half], sin[half] of this token, shared by its heads
     const int t = blockIdx.x;
     const int pos = positions[t];
     const int req = req_of_token[t];
     const int total_heads = kv_from_qkv ? nh + 2 * nkv : nh;
     const int half = rotary_dim / 2;
+    if (rope_kind == ROPE_NEOX) {
+        for (int i = threadIdx.x; i < half; i += blockDim.x) {
+            float s, c;
+            sincosf((float)pos * inv_freq[i], &s, &c);
+            cs[i] = c;
+            cs[half + i] = s;
+        }
+        __syncthreads();
+    }
 
     for (int h = blockIdx.y * nwarp + warp; h < total_heads; h += gridDim.y * nwarp) {
         const bool is_q = h < nh;
@@ -82,8 +94,7 @@ __global__ __launch_bounds__(256) void qkv_post_kernel(
                     const bool first = d < half;
                     const int pair = first ? d : d - half;
                     const int other = first ? d + half : d - half;
-                    float s, c;
-                    sincosf((float)pos * inv_freq[pair], &s, &c);
+                    const float c = cs[pair], s = cs[half + pair];
                     const float x0 = first ? row[d] : row[other];
                     const float x1 = first ? row[other] : row[d];
                     x[i] = first ? x0 * c - x1 * s : x0 * s + x1 * c;
@@ -140,9 +151,9 @@ AIRUN_EXPORT int airun_qkv_post(
     // blocks each walking all heads; many tokens: eight heads per block
     int warps = T <= 64 ? (heads < 2 ? heads : 2) : (heads < 8 ? heads : 8);
     const int blocks_y = T <= 64 ? (heads + warps - 1) / warps : 1;
-    const size_t smem = (size_t)warps * hd * sizeof(float);
+    const size_t smem = ((size_t)warps * hd + (rope_kind != ROPE_NONE ? rotary_dim : 0)) * sizeof(float);
 #define LAUNCH(TQ, TKV) \
-    qkv_post_kernel<TQ, TKV><<<dim3(T, blocks_y), warps * 32, smem, stream>>>(qkv, ld_qkv, (TQ*)q_out, q_norm_w, k_norm_w, eps, \
+    airun_launch(qkv_post_kernel<TQ, TKV>, dim3(dim3(T, blocks_y)), dim3(warps * 32), smem, stream, qkv, ld_qkv, (TQ*)q_out, q_norm_w, k_norm_w, eps, \
         positions, req_of_token, rope_kind, rotary_dim, inv_freq, (TKV*)pool, block_table, max_blocks, num_reqs, \
         num_pages, page_size, do_store, kv_from_qkv, nh, nkv, hd, err)
     if (q_dtype == AIRUN_DT_F32) LAUNCH(float, float);

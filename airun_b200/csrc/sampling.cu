@@ -57,6 +57,8 @@ __device__ BestPair block_best(BestPair p, BestPair* sh) {
 #define ARGMAX_CHUNKS 64
 __global__ __launch_bounds__(256) void argmax_partial_kernel(
     const float* __restrict__ logits, long long ld, int V, BestPair* __restrict__ partial) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ BestPair sh_best[33];
     const int r = blockIdx.y, c = blockIdx.x;
     const float* row = logits + (size_t)r * ld;
@@ -75,6 +77,8 @@ __global__ __launch_bounds__(SAMPLE_THREADS) void sample_kernel(
     const float* __restrict__ logits, long long ld, int V,
     const float* __restrict__ temperature, const float* __restrict__ uniform,
     int32_t* __restrict__ out, const BestPair* __restrict__ partial) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ BestPair sh_best[33];
     __shared__ float sh_sum[SAMPLE_THREADS];
     __shared__ float red[33];
@@ -145,8 +149,8 @@ AIRUN_EXPORT int airun_sample(const float* logits, long long ld, int rows, int V
     BestPair* partial = nullptr;
     if (scratch && V >= 8192) {
         partial = (BestPair*)scratch;
-        argmax_partial_kernel<<<dim3(ARGMAX_CHUNKS, rows), 256, 0, stream>>>(logits, ld, V, partial);
+        airun_launch(argmax_partial_kernel, dim3(dim3(ARGMAX_CHUNKS, rows)), dim3(256), 0, stream, logits, ld, V, partial);
     }
-    sample_kernel<<<rows, SAMPLE_THREADS, 0, stream>>>(logits, ld, V, temperature, uniform, out, partial);
+    airun_launch(sample_kernel, dim3(rows), dim3(SAMPLE_THREADS), 0, stream, logits, ld, V, temperature, uniform, out, partial);
     return airun_launch_status();
 }
