@@ -20,6 +20,11 @@
 //    writes (max, sum, acc) to scratch and the last CTA of the token and head (a
 //    counter, no spinning) merges the slices in order.
 #include "common.cuh"
+#include <cuda.h>
+#include <mutex>
+#include <unordered_map>
+#include <cstring>
+#include <utility>
 
 #ifndef HD
 #error "compile with -DHD=<head_dim>"
@@ -58,6 +63,44 @@ __device__ __forceinline__ void mma16816(float* c, const uint32_t* a, uint32_t b
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// ---- TMA pieces of the decode kernel (pages whose size is a multiple of 16, head_dim a multiple of 64)
+// A 16-key K (or V) tile is HD/64 boxes of 16 rows x 128 bytes, landed with the 128-byte swizzle.
+__device__ __forceinline__ uint32_t tile_off_tma(int row, int chunk) {
+    return (uint32_t)((chunk >> 3) * 2048 + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {     // bounded: about two seconds
+    for (int i = 0; i < 64; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    unsigned long long t0, t1;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
+    for (;;) {
+        for (int i = 0; i < 256; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t1));
+        if (t1 - t0 > 2000000000ull) return false;
+    }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
@@ -252,7 +295,6 @@ __global__ __launch_bounds__(128) void attn_prefill_kernel(const AttnParams p, c
 
 // ------------------------------------------------------------------ decode
 #define DW 4                    // warps per CTA
-#define DSTAGES 2
 #define DN 16                   // keys per tile
 #define MAX_SPLITS 64
 
@@ -263,14 +305,26 @@ struct DecodeExtra {
     int* counters;              // [n][nkv*hgroups], zero between launches
 };
 
-__global__ __launch_bounds__(32 * DW) void attn_decode_kernel(const AttnParams p, const DecodeExtra x) {
+// TMA = true: K/V tiles arrive by cp.async.bulk.tensor (one lane of each warp issues HD/64 boxes per
+// tile, three stages per warp, an mbarrier per stage); TMA = false: cp.async, two stages, any page size.
+template <bool TMA>
+__global__ __launch_bounds__(32 * DW) void attn_decode_kernel(const AttnParams p, const DecodeExtra x,
+                                                              const __grid_constant__ CUtensorMap kv_map) {
     pdl_trigger();
-    pdl_wait();
-    extern __shared__ __align__(128) uint8_t smem[];
-    // per warp: DSTAGES x (K tile + V tile); the Q tile [16][HD] sits after them
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    // per warp: DSTAGES x (K tile + V tile); the Q tile [16][HD] and the mbarriers sit after them
+    constexpr int DSTAGES = TMA ? 3 : 2;
     constexpr int TILE_BYTES = DN * HD * 2;
     constexpr int WARP_BYTES = DSTAGES * 2 * TILE_BYTES;
     uint8_t* sQ = smem + DW * WARP_BYTES;
+    uint64_t* bars = (uint64_t*)(sQ + 16 * HD * 2) + (threadIdx.x >> 5) * DSTAGES;
+    if (TMA && (threadIdx.x & 31) == 0) {
+        for (int s = 0; s < DSTAGES; ++s) mbar_init(smem_u32(bars + s), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    pdl_wait();
     __shared__ float s_m[DW][16], s_l[DW][16];
     __shared__ int s_ticket;
 
@@ -279,7 +333,7 @@ __global__ __launch_bounds__(32 * DW) void attn_decode_kernel(const AttnParams p
     const int split = blockIdx.x;
     const int hgroups = (p.G + 15) / 16;
     const int kvh = blockIdx.y / hgroups, hg = blockIdx.y - kvh * hgroups;
-    const int tok = x.rows[blockIdx.z];
+    const int tok = x.rows ? x.rows[blockIdx.z] : (int)blockIdx.z;     // no list: row i is token i
     const int pos = p.positions[tok];
     const int req = p.req_of_token[tok];
     const int heads = min(16, p.G - hg * 16);          // valid rows
@@ -338,7 +392,30 @@ __global__ __launch_bounds__(32 * DW) void attn_decode_kernel(const AttnParams p
         }
         cp_commit();
     };
-    if (my_n > 0) load_tile(tb + warp, 0);
+    // TMA: lane 0 arms the stage's barrier with the tile's bytes and issues its boxes.  Rows of the
+    // page beyond the context hold older or zero data; those keys are masked below.
+    auto issue_tile = [&](int tile, int stage) {
+        const int j0 = tile * DN;
+        const int blk = j0 >> p.page_shift;
+        int page = blk < p.max_blocks ? __ldg(bt + blk) : -1;
+        if (page < 0 || page >= p.num_pages) { atomicOr(p.err, AIRUN_DEV_BAD_PAGE); page = 0; }
+        const int krow = (((page * 2) * p.nkv + kvh) << p.page_shift) + (j0 & (p.page_size - 1));
+        const int vrow = krow + (p.nkv << p.page_shift);
+        const uint32_t bar = smem_u32(bars + stage);
+        const uint32_t kb = smem_u32(wbase + stage * 2 * TILE_BYTES), vb = kb + TILE_BYTES;
+        mbar_expect_tx(bar, 2 * TILE_BYTES);
+#pragma unroll
+        for (int h = 0; h < HD / 64; ++h) {
+            tma_load_2d(kb + h * 2048, &kv_map, bar, h * 64, krow);
+            tma_load_2d(vb + h * 2048, &kv_map, bar, h * 64, vrow);
+        }
+    };
+    if (TMA) {
+        if (lane == 0)
+            for (int i = 0; i < DSTAGES - 1 && i < my_n; ++i) issue_tile(tb + warp + i * DW, i);
+    } else if (my_n > 0) {
+        load_tile(tb + warp, 0);
+    }
 
     float m0 = NEG_BIG, m1 = NEG_BIG, l0 = 0.0f, l1 = 0.0f;
     float o[HD / 8][4];
@@ -352,17 +429,28 @@ __global__ __launch_bounds__(32 * DW) void attn_decode_kernel(const AttnParams p
     for (int k = 0; k < HD / 16; ++k)
         ldsm4(qf[k], smem_u32(sQ) + tile_off((lane & 7) + ((lane >> 3) & 1) * 8, 2 * k + (lane >> 4)));
 
+    bool timed_out = false;
     for (int it = 0; it < my_n; ++it) {
-        const int stage = it & 1;
-        if (it + 1 < my_n) { load_tile(tb + warp + (it + 1) * DW, stage ^ 1); cp_wait<1>(); } else { cp_wait<0>(); }
-        __syncwarp();
+        const int stage = TMA ? it % DSTAGES : (it & 1);
+        if (TMA) {
+            if (lane == 0 && it + DSTAGES - 1 < my_n) {
+                // the stage being refilled was read (by ldmatrix) in the iteration before this one
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                issue_tile(tb + warp + (it + DSTAGES - 1) * DW, (it + DSTAGES - 1) % DSTAGES);
+            }
+            if (!mbar_wait(smem_u32(bars + stage), (it / DSTAGES) & 1)) { timed_out = true; break; }
+        } else {
+            if (it + 1 < my_n) { load_tile(tb + warp + (it + 1) * DW, stage ^ 1); cp_wait<1>(); } else { cp_wait<0>(); }
+            __syncwarp();
+        }
         const uint32_t kb = smem_u32(wbase + stage * 2 * TILE_BYTES), vb = kb + TILE_BYTES;
         const int j0 = (tb + warp + it * DW) * DN;
         float s[2][4] = {{0.0f, 0.0f, 0.0f, 0.0f}, {0.0f, 0.0f, 0.0f, 0.0f}};
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k) {
             uint32_t b[4];
-            ldsm4(b, kb + tile_off(((lane >> 4) << 3) + (lane & 7), 2 * k + ((lane >> 3) & 1)));
+            ldsm4(b, kb + (TMA ? tile_off_tma(((lane >> 4) << 3) + (lane & 7), 2 * k + ((lane >> 3) & 1))
+                               : tile_off(((lane >> 4) << 3) + (lane & 7), 2 * k + ((lane >> 3) & 1))));
             mma16816(s[0], qf[k], b[0], b[1]);
             mma16816(s[1], qf[k], b[2], b[3]);
         }
@@ -406,12 +494,14 @@ __global__ __launch_bounds__(32 * DW) void attn_decode_kernel(const AttnParams p
 #pragma unroll
         for (int n2 = 0; n2 < HD / 16; ++n2) {
             uint32_t b[4];
-            ldsm4t(b, vb + tile_off((lane & 7) + ((lane >> 3) & 1) * 8, 2 * n2 + (lane >> 4)));
+            ldsm4t(b, vb + (TMA ? tile_off_tma((lane & 7) + ((lane >> 3) & 1) * 8, 2 * n2 + (lane >> 4))
+                                : tile_off((lane & 7) + ((lane >> 3) & 1) * 8, 2 * n2 + (lane >> 4))));
             mma16816(o[2 * n2], pf, b[0], b[1]);
             mma16816(o[2 * n2 + 1], pf, b[2], b[3]);
         }
         __syncwarp();
     }
+    if (timed_out && lane == 0) atomicOr(p.err, AIRUN_DEV_TIMEOUT);
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
     l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
@@ -459,13 +549,18 @@ __global__ __launch_bounds__(32 * DW) void attn_decode_kernel(const AttnParams p
     if (s_ticket != x.n_splits - 1) return;
     __threadfence();
     if (threadIdx.x == 0) x.counters[unit] = 0;
-    // The last CTA of this token and head group merges the slices, in slice order.
+    // The last CTA of this token and head group merges the slices, in slice order.  The loads of
+    // several slices and elements are issued together: this part runs alone, so what it costs is
+    // the number of dependent round trips to the L2 cache.
     const float* all = x.scratch + (size_t)unit * x.n_splits * (16 * (HD + 2));
     __shared__ float s_f[MAX_SPLITS][16];
+    __shared__ float s_l2[MAX_SPLITS][16];
     __shared__ float s_inv[16];
     for (int i = threadIdx.x; i < x.n_splits * 16; i += 32 * DW) {
         const int sp = i >> 4, r = i & 15;
-        s_f[sp][r] = r < heads ? __ldcg(all + (size_t)sp * 16 * (HD + 2) + r * (HD + 2)) : NEG_BIG;      // the slice's maximum
+        const float* ps = all + (size_t)sp * 16 * (HD + 2) + r * (HD + 2);
+        s_f[sp][r] = r < heads ? __ldcg(ps) : NEG_BIG;          // the slice's maximum
+        s_l2[sp][r] = r < heads ? __ldcg(ps + 1) : 0.0f;        // and its sum
     }
     __syncthreads();
     if (threadIdx.x < heads) {
@@ -474,7 +569,7 @@ __global__ __launch_bounds__(32 * DW) void attn_decode_kernel(const AttnParams p
         for (int sp = 0; sp < x.n_splits; ++sp) gm = fmaxf(gm, s_f[sp][r]);
         float sum = 0.0f;
         for (int sp = 0; sp < x.n_splits; ++sp) {
-            const float l = __ldcg(all + (size_t)sp * 16 * (HD + 2) + r * (HD + 2) + 1);
+            const float l = s_l2[sp][r];
             const float f = l > 0.0f ? exp2f(s_f[sp][r] - gm) : 0.0f;
             s_f[sp][r] = f;
             sum = fmaf(l, f, sum);
@@ -482,22 +577,78 @@ __global__ __launch_bounds__(32 * DW) void attn_decode_kernel(const AttnParams p
         s_inv[r] = sum > 0.0f ? 1.0f / sum : 0.0f;
     }
     __syncthreads();
-    for (int e = threadIdx.x; e < heads * HD; e += 32 * DW) {
-        const int r = e / HD, d = e - r * HD;
-        const float* ps = all + r * (HD + 2) + 2 + d;
-        float acc = 0.0f;
-        int sp = 0;
-        for (; sp + 4 <= x.n_splits; sp += 4) {
-            const float v0 = __ldcg(ps + (size_t)(sp + 0) * 16 * (HD + 2)), v1 = __ldcg(ps + (size_t)(sp + 1) * 16 * (HD + 2));
-            const float v2 = __ldcg(ps + (size_t)(sp + 2) * 16 * (HD + 2)), v3 = __ldcg(ps + (size_t)(sp + 3) * 16 * (HD + 2));
-            acc = fmaf(v0, s_f[sp][r], acc);
-            acc = fmaf(v1, s_f[sp + 1][r], acc);
-            acc = fmaf(v2, s_f[sp + 2][r], acc);
-            acc = fmaf(v3, s_f[sp + 3][r], acc);
+    constexpr int EG = 4, SG = 8;                                // elements and slices per round of loads
+    const int total = heads * HD;
+    for (int e0 = threadIdx.x; e0 < total; e0 += 32 * DW * EG) {
+        float acc[EG];
+#pragma unroll
+        for (int k = 0; k < EG; ++k) acc[k] = 0.0f;
+        for (int s0 = 0; s0 < x.n_splits; s0 += SG) {
+            float v[EG][SG];
+#pragma unroll
+            for (int k = 0; k < EG; ++k) {
+                const int e = e0 + k * 32 * DW;
+                const int r = e / HD, d = e - r * HD;
+#pragma unroll
+                for (int j = 0; j < SG; ++j)
+                    v[k][j] = (e < total && s0 + j < x.n_splits)
+                                  ? __ldcg(all + (size_t)(s0 + j) * 16 * (HD + 2) + r * (HD + 2) + 2 + d) : 0.0f;
+            }
+#pragma unroll
+            for (int k = 0; k < EG; ++k) {
+                const int e = e0 + k * 32 * DW;
+                const int r = e < total ? e / HD : 0;
+#pragma unroll
+                for (int j = 0; j < SG; ++j)
+                    if (s0 + j < x.n_splits) acc[k] = fmaf(v[k][j], s_f[s0 + j][r], acc[k]);
+            }
         }
-        for (; sp < x.n_splits; ++sp) acc = fmaf(__ldcg(ps + (size_t)sp * 16 * (HD + 2)), s_f[sp][r], acc);
-        p.out[((size_t)tok * p.nh + head0 + r) * HD + d] = __float2bfloat16_rn(acc * s_inv[r]);
+#pragma unroll
+        for (int k = 0; k < EG; ++k) {
+            const int e = e0 + k * 32 * DW;
+            if (e < total) {
+                const int r = e / HD, d = e - r * HD;
+                p.out[((size_t)tok * p.nh + head0 + r) * HD + d] = __float2bfloat16_rn(acc[k] * s_inv[r]);
+            }
+        }
     }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* f = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)f;
+    });
+    return fn;
+}
+
+// Tensor map of one layer's pages seen as [rows][HD] bfloat16, boxes of 16 rows x 64 values.
+int kv_map_for(CUtensorMap* out, const void* pool, long long rows) {
+    static std::unordered_map<const void*, std::pair<long long, CUtensorMap>> cache;
+    static std::mutex mu;
+    std::lock_guard<std::mutex> g(mu);
+    auto it = cache.find(pool);
+    if (it != cache.end() && it->second.first == rows) { *out = it->second.second; return AIRUN_OK; }
+    cuuint64_t dims[2] = {(cuuint64_t)HD, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)HD * 2};
+    cuuint32_t box[2] = {64, DN};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = encode_fn()(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pool), dims, strides, box, estr,
+                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return AIRUN_ERR_ARG;
+    if (cache.size() > 4096) cache.clear();
+    cache[pool] = std::make_pair(rows, *out);
+    return AIRUN_OK;
 }
 
 AttnParams make_params(const void* q, void* out, const void* pool, const int32_t* block_table, int max_blocks,
@@ -560,13 +711,25 @@ AIRUN_EXPORT int airun_attn_decode(const void* q, void* out, const void* pool, c
     const AttnParams p = make_params(q, out, pool, block_table, max_blocks, positions, req_of_token, num_reqs,
                                      num_pages, page_size, nh, nkv, scale, window, err);
     DecodeExtra x{rows, n_splits, scratch, counters};
-    const int smem = DW * DSTAGES * 2 * DN * HD * 2 + 16 * HD * 2;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
+    // TMA needs whole 16-key tiles inside one page and 128-byte boxes
+    static const bool tma_allowed = !(getenv("AIRUN_ATTN_TMA") && getenv("AIRUN_ATTN_TMA")[0] == '0');
+    const bool tma = tma_allowed && (HD % 64 == 0) && p.page_shift >= 4 && encode_fn() != nullptr;
+    CUtensorMap map;
+    memset(&map, 0, sizeof(map));
+    if (tma) {
+        const int r = kv_map_for(&map, pool, (long long)num_pages * 2 * nkv * page_size);
+        if (r != AIRUN_OK) return r;
     }
-    airun_launch(attn_decode_kernel, dim3(dim3(n_splits, nkv * hgroups, n_rows)), dim3(32 * DW), smem, stream, p, x);
+    const int stages = tma ? 3 : 2;
+    const int smem = DW * stages * 2 * DN * HD * 2 + 16 * HD * 2 + DW * 3 * 8 + 1024;
+    static bool configured[2] = {false, false};
+    if (!configured[tma ? 1 : 0]) {
+        cudaError_t e = tma ? cudaFuncSetAttribute(attn_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)
+                            : cudaFuncSetAttribute(attn_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        configured[tma ? 1 : 0] = true;
+    }
+    if (tma) airun_launch(attn_decode_kernel<true>, dim3(n_splits, nkv * hgroups, n_rows), dim3(32 * DW), smem, stream, p, x, map);
+    else airun_launch(attn_decode_kernel<false>, dim3(n_splits, nkv * hgroups, n_rows), dim3(32 * DW), smem, stream, p, x, map);
     return airun_launch_status();
 }

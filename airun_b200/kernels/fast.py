@@ -119,7 +119,8 @@ def linear_swiglu_bf16(ctx, x: torch.Tensor, w_gu: torch.Tensor, out: torch.Tens
 
 # ---------------------------------------------------------------- attention
 _ARANGE: Dict[torch.device, torch.Tensor] = {}
-DECODE_SLOTS = 444                     # CTAs of the decode kernel resident at once: three on each of 148 SMs
+DECODE_SLOTS = 444                     # CTAs of the cp.async decode kernel resident at once: three on each of 148 SMs
+DECODE_SLOTS_TMA = 296                 # the TMA variant keeps three stages per warp: two CTAs per SM
 DECODE_MIN_KEYS_PER_SPLIT = 128
 
 
@@ -157,11 +158,13 @@ def attn_prefill(ctx, q, out, cache, nh, nkv, hd, scale, window, tiles: torch.Te
 
 
 def attn_decode(ctx, q, out, cache, nh, nkv, hd, scale, window, rows: torch.Tensor, n_rows: int, n_splits: int) -> None:
-    """Attention of single decoded tokens (batch rows ``rows``), the keys cut into ``n_splits`` slices."""
+    """Attention of single decoded tokens (batch rows ``rows``; None: rows 0..n_rows-1), the keys cut
+    into ``n_splits`` slices."""
     _cuda(q, out, cache.pool, cache.block_table, rows)
     _need(q.dtype == torch.bfloat16 and cache.pool.dtype == torch.bfloat16 and q.is_contiguous() and out.is_contiguous(),
           "tensor-core attention takes contiguous bfloat16 q, out and pages")
-    _need(rows.dtype == torch.int32 and rows.is_contiguous() and rows.numel() >= n_rows, "rows must be int32 [n]")
+    if rows is not None:
+        _need(rows.dtype == torch.int32 and rows.is_contiguous() and rows.numel() >= n_rows, "rows must be int32 [n]")
     scratch, counters = scratch_for(q.device)
     hgroups = (nh // nkv + 15) // 16
     if n_splits > 1:
@@ -174,17 +177,18 @@ def attn_decode(ctx, q, out, cache, nh, nkv, hd, scale, window, rows: torch.Tens
              _p(scratch), _p(counters), _p(ctx.err), _stream()), "attn_decode")
 
 
-def plan_decode_splits(n_rows: int, nkv: int, hgroups: int, context_len: int, hd: int) -> int:
-    """Slices of the keys per (token, KV head): the count that needs the least time when CTAs run
-    in waves of DECODE_SLOTS, i.e. minimises ceil(units * s / slots) / s."""
+def plan_decode_splits(n_rows: int, nkv: int, hgroups: int, context_len: int, hd: int, slots: int = DECODE_SLOTS) -> int:
+    """Slices of the keys per (token, KV head).  A CTA costs a fixed part (set-up, merge of its warps,
+    its share of the merge of the slices) plus a part per key; CTAs run in waves of ``slots``.  The
+    constants come from timing the kernel at batch 1, 8 and 64 with 4096 keys."""
     units = max(1, n_rows * nkv * hgroups)
     most = max(1, min(64, (context_len + DECODE_MIN_KEYS_PER_SPLIT - 1) // DECODE_MIN_KEYS_PER_SPLIT))
     best, best_cost = 1, None
     for s in range(1, most + 1):
         if s > 1 and units * s * 16 * (hd + 2) > SCRATCH_FLOATS:
             break
-        waves = -(-units * s // DECODE_SLOTS)
-        cost = waves / s + s * 16.0 / max(context_len, 16)     # plus about one tile of work for every slice's merge
+        waves = -(-units * s // slots)
+        cost = waves * (context_len / s * 0.02 + 9.0) + (1.0 if s > 1 else 0.0) + 0.15 * s
         if best_cost is None or cost < best_cost - 1e-9:
             best, best_cost = s, cost
     return best
@@ -199,7 +203,7 @@ def _attention_plan(ctx, G: int):
         return plan
     dev = ctx.token_ids.device
     if ctx.decode_only:
-        plan = dict(rows=_arange(dev, ctx.num_tokens), n_rows=ctx.num_tokens, tiles=None, n_tiles=0)
+        plan = dict(rows=None, n_rows=ctx.num_tokens, tiles=None, n_tiles=0)
     else:
         per = max(1, 64 // G)
         rows, tiles, t = [], [], 0
@@ -228,6 +232,8 @@ def attention_bf16(ctx, q, out, cache, nh: int, nkv: int, hd: int, scale: float,
         context = ctx.extras.get("planning_context_len", ctx.max_context_len)
         if window > 0:
             context = min(context, window)
-        splits = plan_decode_splits(plan["n_rows"], nkv, (G + 15) // 16, context, hd)
+        tma = hd % 64 == 0 and cache.page_size % 16 == 0 and (cache.page_size & (cache.page_size - 1)) == 0
+        splits = plan_decode_splits(plan["n_rows"], nkv, (G + 15) // 16, context, hd,
+                                    DECODE_SLOTS_TMA if tma else DECODE_SLOTS)
         attn_decode(ctx, q, out, cache, nh, nkv, hd, scale, window, plan["rows"], plan["n_rows"], splits)
     return True
