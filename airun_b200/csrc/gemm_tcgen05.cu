@@ -164,8 +164,19 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, const float* v,
             }
         } else {
             __nv_bfloat16* o = (__nv_bfloat16*)p.out + (size_t)a_row * p.ldc + n0;
+            if (n0 + 16 <= p.b_rows && (((size_t)o) & 15) == 0) {
+                uint32_t w[8];
 #pragma unroll
-            for (int i = 0; i < 16; ++i) if (n0 + i < p.b_rows) o[i] = __float2bfloat16_rn(v[i]);
+                for (int i = 0; i < 8; ++i) {
+                    __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+                    w[i] = *reinterpret_cast<uint32_t*>(&h);
+                }
+                *reinterpret_cast<uint4*>(o) = make_uint4(w[0], w[1], w[2], w[3]);
+                *reinterpret_cast<uint4*>(o + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) if (n0 + i < p.b_rows) o[i] = __float2bfloat16_rn(v[i]);
+            }
         }
     } else {
 #pragma unroll
@@ -185,6 +196,17 @@ __device__ __forceinline__ void store_swiglu_normal(const GemmParams& p, const f
     if (a_row >= p.a_rows) return;
     const int n_out = (b0 + c0) / 2;
     __nv_bfloat16* o = (__nv_bfloat16*)p.out + (size_t)a_row * p.ldc + n_out;
+    if (b0 + c0 + 32 <= p.b_rows && (((size_t)o) & 15) == 0) {
+        uint32_t w[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(silu_mul(g[2 * i], u[2 * i]), silu_mul(g[2 * i + 1], u[2 * i + 1]));
+            w[i] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        *reinterpret_cast<uint4*>(o) = make_uint4(w[0], w[1], w[2], w[3]);
+        *reinterpret_cast<uint4*>(o + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+        return;
+    }
 #pragma unroll
     for (int i = 0; i < 16; ++i)
         if (b0 + c0 + 16 + i < p.b_rows) o[i] = __float2bfloat16_rn(silu_mul(g[i], u[i]));
@@ -382,6 +404,115 @@ __global__ __launch_bounds__(GEMM_THREADS, 1) void gemm_tcgen05_kernel(
     }
 }
 
+// ------------------------------------------------------------------ persistent variant (prompt portions)
+// One CTA per SM walks the tiles of the product (m fastest, so CTAs running side by side share a
+// weight tile).  The stage ring runs on across tiles, and the accumulator is double-buffered in
+// tensor memory (2 x 256 columns): while the epilogue warps drain tile i, the MMA thread is already
+// filling tile i + 1.  Normal mode, BN = 256, no K slices.
+#define PBN 256
+#define PSTAGES 4
+template <int EPI>
+__global__ __launch_bounds__(GEMM_THREADS, 1) void gemm_tcgen05_persistent_kernel(
+    const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmParams p,
+    int m_tiles, int n_tiles) {
+    pdl_trigger();
+    using L = SmemLayout<PBN, PSTAGES>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = (uint64_t*)(smem + L::BAR_OFFSET);          // full[S], empty[S], acc_full[2], acc_empty[2]
+    __shared__ uint32_t tmem_slot_p;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int kb_total = (p.K + BK - 1) / BK;
+    const int total_tiles = m_tiles * n_tiles;
+    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + PSTAGES);
+    const uint32_t accf0 = smem_u32(bars + 2 * PSTAGES), acce0 = smem_u32(bars + 2 * PSTAGES + 2);
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < PSTAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(accf0 + 8 * b, 1); mbar_init(acce0 + 8 * b, 4); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(smem_u32(&tmem_slot_p), 2 * PBN);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_slot_p;
+    pdl_wait();
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const int a0 = (tile % m_tiles) * BM, b0 = (tile / m_tiles) * PBN;
+                for (int kb = 0; kb < kb_total; ++kb, ++it) {
+                    const int s = it % PSTAGES;
+                    if (!mbar_wait(empty0 + 8 * s, ((it / PSTAGES) & 1) ^ 1)) { atomicOr(p.err, AIRUN_DEV_TIMEOUT); ok = false; break; }
+                    mbar_expect_tx(full0 + 8 * s, L::STAGE_BYTES);
+                    const uint32_t sa = smem_u32(smem + s * L::STAGE_BYTES);
+                    tma_load_2d(sa, &map_a, full0 + 8 * s, kb * BK, a0);
+                    tma_load_2d(sa + L::A_BYTES, &map_b, full0 + 8 * s, kb * BK, b0);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(PBN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            int it = 0, n = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++n) {
+                const int buf = n & 1;
+                if (!mbar_wait(acce0 + 8 * buf, ((n >> 1) & 1) ^ 1)) { atomicOr(p.err, AIRUN_DEV_TIMEOUT); break; }
+                tc_fence_after();
+                const uint32_t tmem_d = tmem_base + buf * PBN;
+                for (int kb = 0; kb < kb_total; ++kb, ++it) {
+                    const int s = it % PSTAGES;
+                    if (!mbar_wait(full0 + 8 * s, (it / PSTAGES) & 1)) { atomicOr(p.err, AIRUN_DEV_TIMEOUT); ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(smem + s * L::STAGE_BYTES);
+                    const uint64_t da = smem_desc_sw128(sa), db = smem_desc_sw128(sa + L::A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k)
+                        umma_bf16(tmem_d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    umma_commit(empty0 + 8 * s);
+                }
+                umma_commit(accf0 + 8 * buf);
+            }
+        }
+    } else {
+        const int quad = warp & 3;
+        int n = 0;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++n) {
+            const int buf = n & 1;
+            const int a0 = (tile % m_tiles) * BM, b0 = (tile / m_tiles) * PBN;
+            const int a_row = a0 + quad * 32 + lane;
+            if (!mbar_wait(accf0 + 8 * buf, (n >> 1) & 1)) { atomicOr(p.err, AIRUN_DEV_TIMEOUT); break; }
+            tc_fence_after();
+            const uint32_t lane_addr = tmem_base + buf * PBN + ((uint32_t)(quad * 32) << 16);
+            constexpr int STEP = EPI == EPI_SWIGLU ? 32 : 16;
+#pragma unroll 2
+            for (int c = 0; c < PBN; c += STEP) {
+                float v[16], u[16];
+                tmem_ld16(lane_addr + c, v);
+                if (STEP == 32) tmem_ld16(lane_addr + c + 16, u);
+                if (c + STEP >= PBN) {                      // the last columns are in registers: hand the buffer back
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acce0 + 8 * buf) : "memory");
+                }
+                if (EPI == EPI_SWIGLU) store_swiglu_normal(p, v, u, a_row, b0, c);
+                else store_chunk<EPI, false>(p, v, a_row, b0, c);
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 2 * PBN);
+    }
+}
+
 // ------------------------------------------------------------------ host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -455,17 +586,42 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, di
 }
 
 template <int EPI>
+int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, cudaStream_t stream) {
+    using L = SmemLayout<PBN, PSTAGES>;
+    constexpr int SMEM = L::TOTAL + 64;
+    static bool configured = false;
+    static int n_sm = 0;
+    auto kern = gemm_tcgen05_persistent_kernel<EPI>;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        if (e != cudaSuccess) return (int)e;
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
+        configured = true;
+    }
+    const int m_tiles = (p.a_rows + BM - 1) / BM, n_tiles = (p.b_rows + PBN - 1) / PBN;
+    const int total = m_tiles * n_tiles;
+    const int grid = total < n_sm ? total : n_sm;
+    airun_launch(kern, dim3(grid), dim3(GEMM_THREADS), SMEM, stream, ma, mb, p, m_tiles, n_tiles);
+    return airun_launch_status();
+}
+
+template <int EPI>
 int dispatch(bool swap, int bn, const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, dim3 grid,
              cudaStream_t stream) {
     if (!swap) {
+        static const bool persistent_allowed = !(getenv("AIRUN_GEMM_PERSISTENT") && getenv("AIRUN_GEMM_PERSISTENT")[0] == '0');
+        if (bn == 256 && p.ksplit == 1 && persistent_allowed) return launch_persistent<EPI>(ma, mb, p, stream);
         if (bn == 128) return launch<128, 6, EPI, false>(ma, mb, p, grid, stream);
         if (bn == 256) return launch<256, 4, EPI, false>(ma, mb, p, grid, stream);
         return AIRUN_ERR_UNSUPPORTED;
     }
+    // stage counts that leave room for two CTAs on an SM (about 110 KB each)
     if (bn == 16) return launch<16, 6, EPI, true>(ma, mb, p, grid, stream);
-    if (bn == 32) return launch<32, 6, EPI, true>(ma, mb, p, grid, stream);
-    if (bn == 64) return launch<64, 6, EPI, true>(ma, mb, p, grid, stream);
-    if (bn == 128) return launch<128, 6, EPI, true>(ma, mb, p, grid, stream);
+    if (bn == 32) return launch<32, 5, EPI, true>(ma, mb, p, grid, stream);
+    if (bn == 64) return launch<64, 4, EPI, true>(ma, mb, p, grid, stream);
+    if (bn == 128) return launch<128, 3, EPI, true>(ma, mb, p, grid, stream);
     return AIRUN_ERR_UNSUPPORTED;
 }
 

@@ -142,7 +142,10 @@ CASES_TC = [  # M, N, K, epi, swap, bn, ksplit
     (300, 520, 1000, 0, False, 256, 1), (257, 256, 2048, 0, False, 256, 3), (8, 256, 512, 0, True, 16, 1),
     (5, 300, 72, 0, True, 16, 1), (33, 392, 1024, 0, True, 64, 4), (64, 520, 4096, 0, True, 64, 8),
     (100, 264, 2048, 1, True, 128, 3), (256, 448, 512, 2, False, 128, 1), (7, 448, 512, 2, True, 16, 1),
-    (20, 4128, 1024, 2, True, 32, 2), (1, 96, 8, 0, True, 16, 1)]
+    (20, 4128, 1024, 2, True, 32, 2), (1, 96, 8, 0, True, 16, 1),
+    # the persistent kernel: more tiles than SMs (each CTA walks several), ragged edges, every epilogue
+    (2048, 4096, 256, 0, False, 256, 1), (1100, 2336, 200, 2, False, 256, 1), (513, 1000, 320, 1, False, 256, 1),
+    (300, 576, 512, 2, False, 256, 1)]
 
 
 @pytest.mark.parametrize("M,N,K,epi,swap,bn,ksplit", CASES_TC)
