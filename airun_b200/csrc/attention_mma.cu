@@ -129,12 +129,13 @@ __device__ __forceinline__ const __nv_bfloat16* key_row(const AttnParams& p, con
 }
 
 // ------------------------------------------------------------------ prefill
-#define PM 64          // packed rows per CTA
+#define PM 128         // packed rows per CTA (8 warps x 16 rows)
+#define PTHREADS 256
 #define PN 64          // keys per tile
 
 struct PrefillTile { int req, tok0, n_tok, first_row; };   // tokens [tok0, tok0+n_tok) of the batch, all of request req
 
-__global__ __launch_bounds__(128) void attn_prefill_kernel(const AttnParams p, const int4* __restrict__ tiles) {
+__global__ __launch_bounds__(PTHREADS, 2) void attn_prefill_kernel(const AttnParams p, const int4* __restrict__ tiles) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ __align__(128) uint8_t smem[];
@@ -155,7 +156,7 @@ __global__ __launch_bounds__(128) void attn_prefill_kernel(const AttnParams p, c
     const int pos_lo = p.positions[tok0], pos_hi = p.positions[tok0 + n_tok - 1];
 
     // ---- Q tile -> shared memory
-    for (int i = threadIdx.x; i < PM * CHUNKS; i += 128) {
+    for (int i = threadIdx.x; i < PM * CHUNKS; i += PTHREADS) {
         const int r = i / CHUNKS, c = i - r * CHUNKS;
         const bool valid = r < n_rows;
         const int tok = tok0 + (valid ? r / G : 0), head = kvh * G + (valid ? r % G : 0);
@@ -172,7 +173,7 @@ __global__ __launch_bounds__(128) void attn_prefill_kernel(const AttnParams p, c
         const int j0 = tile * PN;
         uint32_t kb = smem_u32(sK + stage * PN * HD * 2), vb = smem_u32(sV + stage * PN * HD * 2);
 #pragma unroll 4
-        for (int i = threadIdx.x; i < PN * CHUNKS; i += 128) {
+        for (int i = threadIdx.x; i < PN * CHUNKS; i += PTHREADS) {
             const int r = i / CHUNKS, c = i - r * CHUNKS;
             const int j = j0 + r;
             const __nv_bfloat16* src = (j <= pos_hi && j >= k_first) ? key_row(p, bt, kvh, j) : nullptr;
@@ -196,16 +197,10 @@ __global__ __launch_bounds__(128) void attn_prefill_kernel(const AttnParams p, c
 #pragma unroll
     for (int n = 0; n < HD / 8; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f; }
 
-    uint32_t qf[HD / 16][4];
     for (int it = 0; it < n_tiles; ++it) {
         const int stage = it & 1;
         if (it + 1 < n_tiles) { load_kv(tile_first + it + 1, stage ^ 1); cp_wait<1>(); } else { cp_wait<0>(); }
         __syncthreads();
-        if (it == 0) {
-#pragma unroll
-            for (int k = 0; k < HD / 16; ++k)
-                ldsm4(qf[k], smem_u32(sQ) + tile_off(warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, 2 * k + (lane >> 4)));
-        }
         const uint32_t kb = smem_u32(sK + stage * PN * HD * 2), vb = smem_u32(sV + stage * PN * HD * 2);
         const int j0 = (tile_first + it) * PN;
 
@@ -214,12 +209,14 @@ __global__ __launch_bounds__(128) void attn_prefill_kernel(const AttnParams p, c
         for (int n = 0; n < PN / 8; ++n) { s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.0f; }
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k) {
+            uint32_t qf[4];                   // the Q fragment is read again for every tile: registers are scarcer than shared-memory reads
+            ldsm4(qf, smem_u32(sQ) + tile_off(warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, 2 * k + (lane >> 4)));
 #pragma unroll
             for (int n2 = 0; n2 < PN / 16; ++n2) {
                 uint32_t b[4];
                 ldsm4(b, kb + tile_off(n2 * 16 + ((lane >> 4) << 3) + (lane & 7), 2 * k + ((lane >> 3) & 1)));
-                mma16816(s[2 * n2], qf[k], b[0], b[1]);
-                mma16816(s[2 * n2 + 1], qf[k], b[2], b[3]);
+                mma16816(s[2 * n2], qf, b[0], b[1]);
+                mma16816(s[2 * n2 + 1], qf, b[2], b[3]);
             }
         }
         // mask, scale, running maximum
@@ -688,7 +685,7 @@ AIRUN_EXPORT int airun_attn_prefill(const void* q, void* out, const void* pool, 
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    airun_launch(attn_prefill_kernel, dim3(dim3(n_tiles, nkv)), dim3(128), smem, stream, p, (const int4*)tiles);
+    airun_launch(attn_prefill_kernel, dim3(n_tiles, nkv), dim3(PTHREADS), smem, stream, p, (const int4*)tiles);
     return airun_launch_status();
 }
 

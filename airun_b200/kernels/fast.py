@@ -122,6 +122,7 @@ _ARANGE: Dict[torch.device, torch.Tensor] = {}
 DECODE_SLOTS = 444                     # CTAs of the cp.async decode kernel resident at once: three on each of 148 SMs
 DECODE_SLOTS_TMA = 296                 # the TMA variant keeps three stages per warp: two CTAs per SM
 DECODE_MIN_KEYS_PER_SPLIT = 128
+PREFILL_ROWS = 128                     # packed rows (tokens x heads of a KV group) of one prefill CTA
 
 
 def _arange(device: torch.device, n: int) -> torch.Tensor:
@@ -133,7 +134,7 @@ def _arange(device: torch.device, n: int) -> torch.Tensor:
 
 
 def attention_supported(hd: int, nh: int, nkv: int) -> bool:
-    return "attention" not in DISABLED and hd % 16 == 0 and 16 <= hd <= 256 and nh % nkv == 0 and nh // nkv <= 64
+    return "attention" not in DISABLED and hd % 16 == 0 and 16 <= hd <= 256 and nh % nkv == 0 and nh // nkv <= PREFILL_ROWS
 
 
 def _attn_common_args(q, out, cache, ctx, nh, nkv, scale, window):
@@ -196,7 +197,7 @@ def plan_decode_splits(n_rows: int, nkv: int, hgroups: int, context_len: int, hd
 
 def _attention_plan(ctx, G: int):
     """Which rows are single decoded tokens and how the prompt portions are cut into tiles
-    of 64 // G tokens; made once per step and group size."""
+    of PREFILL_ROWS // G tokens; made once per step and group size."""
     key = ("attn_plan", G)
     plan = ctx.extras.get(key)
     if plan is not None:
@@ -205,15 +206,19 @@ def _attention_plan(ctx, G: int):
     if ctx.decode_only:
         plan = dict(rows=None, n_rows=ctx.num_tokens, tiles=None, n_tiles=0)
     else:
-        per = max(1, 64 // G)
+        per = max(1, PREFILL_ROWS // G)
         rows, tiles, t = [], [], 0
-        for r, n in enumerate(ctx.query_lens):
+        for r, (n, c) in enumerate(zip(ctx.query_lens, ctx.context_lens_host)):
             if n == 1:
                 rows.append(t)
             else:
                 for s in range(0, n, per):
-                    tiles.append((r, t + s, min(per, n - s), 0))
+                    k = min(per, n - s)
+                    tiles.append((r, t + s, k, c - n + s + k))     # last field: keys its last token sees
             t += n
+        # the tiles with the most keys first: CTAs are handed out in order, and the longest
+        # ones must not be the last to start
+        tiles.sort(key=lambda x: -x[3])
         plan = dict(
             rows=torch.tensor(rows, dtype=torch.int32).to(dev, non_blocking=True) if rows else None, n_rows=len(rows),
             tiles=torch.tensor(tiles, dtype=torch.int32).to(dev, non_blocking=True) if tiles else None, n_tiles=len(tiles))
