@@ -29,6 +29,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
+import numpy as np
 import torch
 
 from ..parts.base import PagedKVSpec, StateSpec
@@ -124,7 +125,7 @@ class CacheBinding:
 
 class CacheManager:
     def __init__(self, specs: Sequence[object], cache_from: Sequence[Optional[int]],
-                 page_size: int, num_pages: int, max_requests: int):
+                 page_size: int, num_pages: int, max_requests: int, max_blocks: Optional[int] = None):
         """``specs[i]`` is the cache spec of entry i of the execution order (or None),
         ``cache_from[i]`` the entry whose cache entry i reads instead of its own."""
         if page_size <= 0:
@@ -161,6 +162,10 @@ class CacheManager:
                 raise TypeError(f"entry {i} has an unknown cache spec {spec!r}")
         self.requests: Dict[Hashable, RequestCache] = {}
         self._free_slots: List[int] = list(range(max_requests - 1, -1, -1))
+        # Host mirror of every request's block table, one row per request slot, so that a step
+        # gathers the rows of its batch with one array operation instead of a loop over requests.
+        self.max_blocks = int(max_blocks) if max_blocks else num_pages
+        self.tables = [np.full((max_requests, self.max_blocks), -1, dtype=np.int32) for _ in self.paged]
 
     # ------------------------------------------------------------ requests
     def add_request(self, rid: Hashable) -> RequestCache:
@@ -194,16 +199,23 @@ class CacheManager:
         need = self.pages_needed(rid, n_new)
         return all(need[g.gid] + (already or {}).get(g.gid, 0) <= g.allocator.num_free for g in self.paged)
 
-    def reserve(self, rid: Hashable, n_new: int) -> None:
-        """Takes the pages for the next ``n_new`` tokens in every group, or none at all."""
+    def reserve(self, rid: Hashable, n_new: int, need: Optional[Dict[int, int]] = None) -> None:
+        """Takes the pages for the next ``n_new`` tokens in every group, or none at all.
+        ``need`` may carry the result of ``pages_needed(rid, n_new)`` if the caller has it."""
         rc = self.get(rid)
-        need = self.pages_needed(rid, n_new)
+        if need is None:
+            need = self.pages_needed(rid, n_new)
         for g in self.paged:
             if need[g.gid] > g.allocator.num_free:
                 raise OutOfPages(f"request {rid!r} needs {need[g.gid]} pages in group {g.gid}, "
                                  f"{g.allocator.num_free} free")
         for g in self.paged:
-            rc.blocks[g.gid].extend(g.allocator.take(need[g.gid]))
+            if need[g.gid]:
+                blocks = rc.blocks[g.gid]
+                first = len(blocks)
+                blocks.extend(g.allocator.take(need[g.gid]))
+                if len(blocks) <= self.max_blocks:
+                    self.tables[g.gid][rc.slot, first:len(blocks)] = blocks[first:]
         rc.reserved = max(rc.reserved, rc.num_tokens + n_new)
 
     def commit(self, rid: Hashable, n_new: int) -> None:
@@ -222,6 +234,8 @@ class CacheManager:
                     if blocks[b] >= 0:
                         g.allocator.give_back(blocks[b])
                         blocks[b] = -1
+                        if b < self.max_blocks:
+                            self.tables[g.gid][rc.slot, b] = -1
                     b += 1
 
     def free_request(self, rid: Hashable) -> None:
@@ -232,6 +246,7 @@ class CacheManager:
             for p in rc.blocks[g.gid]:
                 if p >= 0:
                     g.allocator.give_back(p)
+            self.tables[g.gid][rc.slot, :min(len(rc.blocks[g.gid]), self.max_blocks)] = -1
         self._free_slots.append(rc.slot)
 
     # ------------------------------------------------------------ views

@@ -85,7 +85,8 @@ class Engine:
         self.max_context = int(o.max_context or min(num_pages * ps,
                                                     max(getattr(config, "max_position_embeddings", 4096), 1)))
         self.max_context = min(self.max_context, num_pages * ps)
-        self.manager = CacheManager(specs, cache_from, ps, num_pages, o.max_requests)
+        self.manager = CacheManager(specs, cache_from, ps, num_pages, o.max_requests,
+                                    max_blocks=(self.max_context + ps - 1) // ps)
         self.storage = CacheStorage(self.manager, self.dtype, self.device)
         self.runner = StepRunner(model, self.manager, self.storage, o.max_batch_tokens,
                                  min(o.max_requests, o.max_batch_tokens), self.max_context)
@@ -169,7 +170,7 @@ class Engine:
         entries = []
         wanting: List[Request] = []
         for e in plan.entries:
-            toks = e.request.tokens[e.start:e.start + e.count]
+            toks = e.request.token_slice(e.start, e.count)
             entries.append(StepEntry(e.request.rid, toks, (e.count - 1,) if e.wants_logits else ()))
             if e.start == 0 and self.storage.state:
                 self.storage.zero_state_slot(self.manager.get(e.request.rid).slot)   # a request starts from zero state

@@ -71,6 +71,16 @@ class Request:
     def num_tokens(self) -> int:
         return len(self.prompt) + len(self.output)
 
+    def token_slice(self, start: int, count: int) -> List[int]:
+        """tokens[start:start+count] without building the whole list."""
+        np_ = len(self.prompt)
+        end = start + count
+        if end <= np_:
+            return self.prompt[start:end]
+        if start >= np_:
+            return self.output[start - np_:end - np_]
+        return self.prompt[start:] + self.output[:end - np_]
+
     @property
     def decoding(self) -> bool:
         return self.num_computed >= len(self.prompt) and self.num_tokens - self.num_computed == 1
@@ -115,25 +125,41 @@ class Scheduler:
         return bool(self.waiting or self.running)
 
     # ------------------------------------------------------------ planning
+    def _need_if_fits(self, req: Request, n: int, planned: Dict[int, int]) -> Optional[Dict[int, int]]:
+        """Pages ``n`` more tokens of ``req`` would take, or None if they are not free."""
+        need = self.manager.pages_needed(req.rid, n)
+        free = self.manager.free_pages()
+        for gid, k in need.items():
+            if k + planned.get(gid, 0) > free[gid]:
+                return None
+        return need
+
     def _pages_fit(self, req: Request, n: int, planned: Dict[int, int]) -> bool:
-        return self.manager.can_reserve(req.rid, n, planned)
+        return self._need_if_fits(req, n, planned) is not None
+
+    @staticmethod
+    def _note_need(need: Dict[int, int], planned: Dict[int, int]) -> None:
+        for gid, k in need.items():
+            if k:
+                planned[gid] = planned.get(gid, 0) + k
 
     def _note(self, req: Request, n: int, planned: Dict[int, int]) -> None:
-        for gid, k in self.manager.pages_needed(req.rid, n).items():
-            planned[gid] = planned.get(gid, 0) + k
+        self._note_need(self.manager.pages_needed(req.rid, n), planned)
 
-    def _largest_portion(self, req: Request, want: int, planned: Dict[int, int]) -> int:
-        """Largest n <= want whose pages are free now (0 if not even one token fits)."""
-        if self._pages_fit(req, want, planned):
-            return want
-        lo, hi = 0, want                         # fits(lo) holds, fits(hi) fails
+    def _largest_portion(self, req: Request, want: int, planned: Dict[int, int]) -> Tuple[int, Dict[int, int]]:
+        """Largest n <= want whose pages are free now (0 if not even one token fits), and its pages."""
+        need = self._need_if_fits(req, want, planned)
+        if need is not None:
+            return want, need
+        lo, hi, lo_need = 0, want, {}            # fits(lo) holds, fits(hi) fails
         while hi - lo > 1:
             mid = (lo + hi) // 2
-            if self._pages_fit(req, mid, planned):
-                lo = mid
+            need = self._need_if_fits(req, mid, planned)
+            if need is not None:
+                lo, lo_need = mid, need
             else:
                 hi = mid
-        return lo
+        return lo, lo_need
 
     def _preempt(self, victim: Request) -> None:
         self.manager.free_request(victim.rid)
@@ -214,14 +240,14 @@ class Scheduler:
             if budget <= 0 or len(entries) >= self.max_batch_reqs:
                 break
             want = min(req.num_tokens - req.num_computed, budget)
-            n = self._largest_portion(req, want, planned)
+            n, need = self._largest_portion(req, want, planned)
             if n == 0:
                 if req.decoding:
                     return entries, req
                 starved = starved or req
                 continue
             entries.append(PlannedEntry(req, req.num_computed, n, req.num_computed + n == req.num_tokens))
-            self._note(req, n, planned)
+            self._note_need(need, planned)
             budget -= n
         if not entries and starved is not None:
             return entries, starved

@@ -121,16 +121,20 @@ class StepRunner:
 
     def reserve(self, entries: Sequence[StepEntry]) -> None:
         """Takes the pages of all entries, or of none."""
-        need: Dict[int, int] = {}
-        for e in entries:
-            for gid, n in self.manager.pages_needed(e.rid, len(e.tokens)).items():
-                need[gid] = need.get(gid, 0) + n
-        free = self.manager.free_pages()
-        for gid, n in need.items():
-            if n > free[gid]:
-                raise OutOfPages(f"the step needs {n} pages in group {gid}, {free[gid]} are free")
-        for e in entries:
-            self.manager.reserve(e.rid, len(e.tokens))
+        m = self.manager
+        needs = [m.pages_needed(e.rid, len(e.tokens)) for e in entries]
+        total: Dict[int, int] = {}
+        for need in needs:
+            for gid, n in need.items():
+                if n:
+                    total[gid] = total.get(gid, 0) + n
+        if total:
+            free = m.free_pages()
+            for gid, n in total.items():
+                if n > free[gid]:
+                    raise OutOfPages(f"the step needs {n} pages in group {gid}, {free[gid]} are free")
+        for e, need in zip(entries, needs):
+            m.reserve(e.rid, len(e.tokens), need)
 
     def build_context(self, entries: Sequence[StepEntry], pad_to: int = 0) -> tuple:
         """Fills the staging buffer and returns (StepContext, n_want).  With ``pad_to`` the
@@ -143,30 +147,41 @@ class StepRunner:
             self._meta_event.synchronize()      # the copy that last read this buffer is done
         tok, pos, rot, want = (self._view(n, dev=False) for n in ("token_ids", "positions", "req_of_token", "want_rows"))
         cu, cl, sl = (self._view(n, dev=False) for n in ("cu_tokens", "context_lens", "state_slots"))
-        t = 0
+        R = len(entries)
+        rcs = [m.requests[e.rid] for e in entries]
+        qlens = [len(e.tokens) for e in entries]
+        starts = [rc.num_tokens for rc in rcs]
+        clens = [s0 + q for s0, q in zip(starts, qlens)]
+        slots = [rc.slot for rc in rcs]
         n_want = 0
-        qlens, clens, slots = [], [], []
-        for r, e in enumerate(entries):
-            rc = m.get(e.rid)
-            n = len(e.tokens)
-            tok[t:t + n] = np.asarray(e.tokens, dtype=np.int32)
-            pos[t:t + n] = np.arange(rc.num_tokens, rc.num_tokens + n, dtype=np.int32)
-            rot[t:t + n] = r
-            for w in e.want:
-                want[n_want] = t + w
-                n_want += 1
-            cu[r] = t
-            cl[r] = rc.num_tokens + n
-            sl[r] = rc.slot
-            qlens.append(n)
-            clens.append(rc.num_tokens + n)
-            slots.append(rc.slot)
-            for g in m.paged:
-                bt = self._view(f"bt{g.gid}", dev=False)
-                blocks = rc.blocks[g.gid]
-                base = r * self.max_blocks
-                bt[base:base + len(blocks)] = blocks
-            t += n
+        if all(q == 1 for q in qlens):                     # single tokens: everything is one array operation
+            t = R
+            tok[:R] = [e.tokens[0] for e in entries]
+            pos[:R] = starts
+            rot[:R] = np.arange(R, dtype=np.int32)
+            cu[:R] = rot[:R]
+            for r, e in enumerate(entries):
+                for w in e.want:
+                    want[n_want] = r + w
+                    n_want += 1
+        else:
+            t = 0
+            for r, e in enumerate(entries):
+                n = qlens[r]
+                tok[t:t + n] = e.tokens
+                pos[t:t + n] = np.arange(starts[r], starts[r] + n, dtype=np.int32)
+                rot[t:t + n] = r
+                for w in e.want:
+                    want[n_want] = t + w
+                    n_want += 1
+                cu[r] = t
+                t += n
+        cl[:R] = clens
+        sl[:R] = slots
+        need_blocks = min((max(clens) + m.page_size - 1) // m.page_size, m.max_blocks, self.max_blocks)
+        for g in m.paged:                                   # the block-table rows of the batch, gathered by slot
+            bt = self._view(f"bt{g.gid}", dev=False).reshape(self.R_max, self.max_blocks)
+            bt[:R, :need_blocks] = m.tables[g.gid][slots, :need_blocks]
         cu[len(entries)] = t
         n_real = t
         if pad_to > t:
