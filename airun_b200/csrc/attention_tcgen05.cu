@@ -1,0 +1,522 @@
+// Flash attention of prompt portions on the 5th-generation tensor cores, for bfloat16 q and
+// pages, one head size per build (-DHD=64 or 128), page sizes that are a power of two >= 16.
+//
+// One CTA = 128 packed query rows (128/G tokens x the G heads of one KV head) of one request.
+// Keys and values come in tiles of 128 keys:
+//   warp 0   : one thread issues TMA loads (cp.async.bulk.tensor, 128-byte swizzle) of the K and V
+//              tiles, 16 keys (one page or a part of one) per box, into two stages each;
+//   warp 1   : allocates tensor memory; one thread issues tcgen05.mma:
+//                S_j = Q K_j^T   (M=128, N=128, K=HD)   into one of two S buffers in tensor memory,
+//                O_j = P_j V_j   (M=128, N=HD,  K=128)  into the O buffer, P_j read from shared memory,
+//                                                        V_j as an MN-major operand straight from its tile;
+//              S_{j+1} is issued before O_j so the tensor cores work while the softmax of tile j runs;
+//   warps 2-9: two threads per query row (its lane of tensor memory), one for each half of the
+//              keys of a tile and of the head dimensions: read S_j with tcgen05.ld, mask, running
+//              maximum (agreed between the two through shared memory) and sum in float32 (exp2),
+//              write P_j as bfloat16 into shared memory in the operand layout, and keep the output
+//              row in registers: o = o * 2^(m_{j-2} - m_{j-1}) + O_{j-1}.
+// Key j is visible to a query at position p iff j <= p and (window == 0 or p - j < window); tiles
+// wholly hidden are skipped.  Formulas as the reference's prefill kernel computes them
+// (crates/airun-cuda/kernels/ops.cu:1796-2078: scale * log2(e) folded, exp2, float32 statistics,
+// probabilities rounded to 16 bits for the second product).
+//
+// Every mbarrier wait is bounded (about two seconds); on a time-out the kernel sets an error
+// bit, stops working, frees its tensor memory and returns.  No cluster, no multicast.
+#include "common.cuh"
+#include <cuda.h>
+#include <mutex>
+#include <unordered_map>
+#include <utility>
+#include <cstring>
+
+#ifndef HD
+#error "compile with -DHD=64 or -DHD=128"
+#endif
+static_assert(HD == 64 || HD == 128, "this kernel is built for head_dim 64 or 128");
+
+#define QM 128                    // packed query rows per CTA
+#define KN 128                    // keys per tile
+#define HALVES (HD / 64)          // 64-value (128-byte) column blocks of a head
+#define ROWBLK (128 * 128)        // bytes of one 128-row x 128-byte block
+#define TC_THREADS 320
+#define NEG_BIG (-1.0e30f)
+#define LOG2E 1.4426950408889634f
+#define WAIT_NS 2000000000ull
+
+namespace {
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (int i = 0; i < 64; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    unsigned long long t0, t1;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
+    for (;;) {
+        for (int i = 0; i < 256; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t1));
+        if (t1 - t0 > WAIT_NS) return false;
+    }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// K-major operand (rows of 128 bytes, 128-byte swizzle): 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr >> 4) & 0x3FFF);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// MN-major operand: 64 values of the N dimension are contiguous (128 bytes), the next 64 are a whole
+// 128-row block further (leading byte offset); along K, rows are 128 bytes apart and 8-row groups 1024
+// bytes apart (stride byte offset).
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr >> 4) & 0x3FFF);
+    d |= (uint64_t)(ROWBLK >> 4) << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+struct TcParams {
+    const __nv_bfloat16* q;        // [T][nh][HD]
+    __nv_bfloat16* out;            // [T][nh][HD]
+    const int32_t* block_table;    // [R][max_blocks]
+    const int32_t* positions;      // [T]
+    int max_blocks, num_pages, page_size, page_shift, nh, nkv, G;
+    float scale_log2;
+    int window;
+    int* err;
+};
+
+// shared memory map (after 1024-byte alignment)
+constexpr int Q_BYTES = HALVES * ROWBLK;           // Q tile, K-major
+constexpr int KV_BYTES = HALVES * ROWBLK;          // one K or V tile
+constexpr int P_BYTES = 2 * ROWBLK;                // P tile: 128 rows x 128 keys
+constexpr int OFF_Q = 0;
+constexpr int OFF_K = OFF_Q + Q_BYTES;             // 2 stages
+constexpr int OFF_V = OFF_K + 2 * KV_BYTES;        // 2 stages
+constexpr int OFF_P = OFF_V + 2 * KV_BYTES;
+constexpr int OFF_XM = OFF_P + P_BYTES;             // row maxima exchanged between the two warpgroups
+constexpr int OFF_BAR = OFF_XM + 2 * 2 * 128 * 4;
+constexpr int N_BARS = 16;
+constexpr int SMEM_TOTAL = OFF_BAR + N_BARS * 8 + 64 + 1024;
+enum { B_KFULL = 0, B_KEMPTY = 2, B_VFULL = 4, B_VEMPTY = 6, B_SFULL = 8, B_SFREE = 10, B_PFULL = 12, B_OFULL = 13, B_OFREE = 14, B_XM = 15 };
+
+__global__ __launch_bounds__(TC_THREADS, 1) void attn_prefill_tc_kernel(
+    const TcParams p, const int4* __restrict__ tiles, const __grid_constant__ CUtensorMap kv_map) {
+    pdl_trigger();
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = (uint64_t*)(smem + OFF_BAR);
+    uint32_t* tmem_slot = (uint32_t*)(bars + N_BARS);
+    const uint32_t bar0 = smem_u32(bars);
+    auto BAR = [&](int i) { return bar0 + 8u * (uint32_t)i; };
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < 8; ++i) mbar_init(BAR(i), 1);                 // K/V full and empty
+        mbar_init(BAR(B_SFULL), 1); mbar_init(BAR(B_SFULL + 1), 1);
+        mbar_init(BAR(B_SFREE), 8); mbar_init(BAR(B_SFREE + 1), 8);      // one arrival per softmax warp
+        mbar_init(BAR(B_PFULL), 8);
+        mbar_init(BAR(B_OFULL), 1);
+        mbar_init(BAR(B_OFREE), 8);
+        mbar_init(BAR(B_XM), 8);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(smem_u32(tmem_slot), 512);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    pdl_wait();
+
+    const int4 t4 = tiles[blockIdx.x];
+    const int req = t4.x, tok0 = t4.y, n_tok = t4.z;
+    const int kvh = blockIdx.y;
+    const int G = p.G;
+    const int n_rows = n_tok * G;
+    const int32_t* bt = p.block_table + (size_t)req * p.max_blocks;
+    const int pos_lo = p.positions[tok0], pos_hi = p.positions[tok0 + n_tok - 1];
+    const int k_first = p.window > 0 ? max(0, pos_lo - p.window + 1) : 0;
+    const int tile_first = k_first / KN, tile_last = pos_hi / KN;
+    const int n_tiles = tile_last - tile_first + 1;
+
+    if (warp == 0) {
+        // ------------------------------------------------ TMA producer
+        if (lane == 0) {
+            for (int it = 0; it < n_tiles; ++it) {
+                const int s = it & 1;
+                const uint32_t ph = (it >> 1) & 1;
+                const int j0 = (tile_first + it) * KN;
+                // K tile
+                if (!mbar_wait(BAR(B_KEMPTY + s), ph ^ 1)) { atomicOr(p.err, AIRUN_DEV_TIMEOUT); break; }
+                mbar_expect_tx(BAR(B_KFULL + s), KV_BYTES);
+                const uint32_t kdst = smem_u32(smem + OFF_K + s * KV_BYTES);
+                int rows[KN / 16];
+#pragma unroll
+                for (int gkey = 0; gkey < KN / 16; ++gkey) {
+                    const int j = j0 + gkey * 16;
+                    const int blk = j >> p.page_shift;
+                    int page = (j <= pos_hi && blk < p.max_blocks) ? __ldg(bt + blk) : 0;
+                    if (page < 0 || page >= p.num_pages) {
+                        if (j >= k_first) atomicOr(p.err, AIRUN_DEV_BAD_PAGE);      // a page the window has passed may be gone
+                        page = 0;
+                    }
+                    rows[gkey] = (((page * 2) * p.nkv + kvh) << p.page_shift) + (j & (p.page_size - 1));
+                }
+#pragma unroll
+                for (int gkey = 0; gkey < KN / 16; ++gkey)
+#pragma unroll
+                    for (int h = 0; h < HALVES; ++h)
+                        tma_load_2d(kdst + h * ROWBLK + gkey * 2048, &kv_map, BAR(B_KFULL + s), h * 64, rows[gkey]);
+                // V tile
+                if (!mbar_wait(BAR(B_VEMPTY + s), ph ^ 1)) { atomicOr(p.err, AIRUN_DEV_TIMEOUT); break; }
+                mbar_expect_tx(BAR(B_VFULL + s), KV_BYTES);
+                const uint32_t vdst = smem_u32(smem + OFF_V + s * KV_BYTES);
+                const int vskip = p.nkv << p.page_shift;
+#pragma unroll
+                for (int gkey = 0; gkey < KN / 16; ++gkey)
+#pragma unroll
+                    for (int h = 0; h < HALVES; ++h)
+                        tma_load_2d(vdst + h * ROWBLK + gkey * 2048, &kv_map, BAR(B_VFULL + s), h * 64, rows[gkey] + vskip);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(KN >> 3) << 17) | ((uint32_t)(QM >> 4) << 24);
+            constexpr uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(QM >> 4) << 24);
+            const uint32_t q_addr = smem_u32(smem + OFF_Q), p_addr = smem_u32(smem + OFF_P);
+            bool ok = mbar_wait(BAR(B_PFULL), 0);          // first phase of P_full: the Q tile is in shared memory
+            auto issue_s = [&](int it) -> bool {
+                const int s = it & 1;
+                if (!mbar_wait(BAR(B_KFULL + s), (it >> 1) & 1)) return false;
+                if (!mbar_wait(BAR(B_SFREE + s), ((it >> 1) & 1) ^ 1)) return false;
+                tc_fence_after();
+                const uint32_t k_addr = smem_u32(smem + OFF_K + s * KV_BYTES);
+#pragma unroll
+                for (int k = 0; k < HD / 16; ++k) {
+                    const uint32_t off = (k >> 2) * ROWBLK + (k & 3) * 32;
+                    umma_bf16(tmem_base + s * KN, desc_kmajor(q_addr + off), desc_kmajor(k_addr + off), idesc_s, k > 0 ? 1u : 0u);
+                }
+                umma_commit(BAR(B_KEMPTY + s));
+                umma_commit(BAR(B_SFULL + s));
+                return true;
+            };
+            if (ok) ok = issue_s(0);
+            for (int it = 0; it < n_tiles && ok; ++it) {
+                if (it + 1 < n_tiles) { ok = issue_s(it + 1); if (!ok) break; }
+                const int s = it & 1;
+                // P_it is in shared memory (phase it + 1 of P_full) and the O buffer has been read
+                if (!mbar_wait(BAR(B_PFULL), (it + 1) & 1)) { ok = false; break; }
+                if (!mbar_wait(BAR(B_VFULL + s), (it >> 1) & 1)) { ok = false; break; }
+                if (!mbar_wait(BAR(B_OFREE), (it & 1) ^ 1)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t v_addr = smem_u32(smem + OFF_V + s * KV_BYTES);
+#pragma unroll
+                for (int k = 0; k < KN / 16; ++k) {
+                    const uint32_t poff = (k >> 2) * ROWBLK + (k & 3) * 32;
+                    umma_bf16(tmem_base + 2 * KN, desc_kmajor(p_addr + poff), desc_mnmajor(v_addr + k * 2048), idesc_o, k > 0 ? 1u : 0u);
+                }
+                umma_commit(BAR(B_VEMPTY + s));
+                umma_commit(BAR(B_OFULL));
+            }
+            if (!ok) atomicOr(p.err, AIRUN_DEV_TIMEOUT);
+        }
+    } else {
+        // ------------------------------------------------ softmax, correction, epilogue
+        // Two warpgroups share the 128 rows: thread (half, r) owns row r (its lane of tensor memory), the
+        // keys [64*half, 64*half+64) of every S tile and the head dimensions [DPT*half, DPT*half+DPT) of
+        // the output.  The two threads of a row agree on the row's maximum through shared memory.
+        const int half = (warp - 2) >> 2;
+        const int quad = warp & 3;
+        const int r = quad * 32 + lane;
+        const bool row_ok = r < n_rows;
+        const int tok = tok0 + (row_ok ? r / G : 0);
+        const int head = kvh * G + (row_ok ? r % G : 0);
+        const int pos = row_ok ? p.positions[tok] : -1;
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
+        constexpr int DPT = HD / 2;                               // head dimensions per thread
+        float* xm = reinterpret_cast<float*>(smem + OFF_XM);      // [2 tiles][2 halves][128 rows]
+
+        // this thread's part of the Q row -> shared memory in the K-major swizzled layout
+        {
+            const uint4* src = reinterpret_cast<const uint4*>(p.q + ((size_t)tok * p.nh + head) * HD);
+#pragma unroll
+            for (int i = 0; i < DPT / 8; ++i) {
+                const int c = half * (DPT / 8) + i;
+                const uint4 v = row_ok ? src[c] : make_uint4(0, 0, 0, 0);
+                *reinterpret_cast<uint4*>(smem + OFF_Q + (c >> 3) * ROWBLK + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = v;
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(BAR(B_PFULL));          // phase 0: Q is ready
+        }
+
+        float o[DPT];
+#pragma unroll
+        for (int d = 0; d < DPT; ++d) o[d] = 0.0f;
+        float m = NEG_BIG, l = 0.0f, corr_prev = 1.0f;
+        bool ok = true;
+        const float sc = p.scale_log2;
+        for (int it = 0; it < n_tiles && ok; ++it) {
+            const int s = it & 1;
+            const int j0 = (tile_first + it) * KN + half * 64;           // first key of this thread's columns
+            if (!mbar_wait(BAR(B_SFULL + s), (it >> 1) & 1)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t s_addr = lane_addr + s * KN + half * 64;
+            // every key of the tile is visible to every row: no masks
+            const bool full = p.window == 0 && (tile_first + it) * KN + KN - 1 <= pos_lo;
+            float v[64];
+            tmem_ld32(s_addr, v);
+            tmem_ld32(s_addr + 32, v + 32);
+            // the S buffer is in registers: hand it back
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(BAR(B_SFREE + s));
+            float raw = NEG_BIG;
+            if (full) {
+#pragma unroll
+                for (int i = 0; i < 64; ++i) raw = fmaxf(raw, v[i]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 64; ++i) {
+                    const int j = j0 + i;
+                    const bool vis = j <= pos && (p.window == 0 || pos - j < p.window);
+                    v[i] = vis ? v[i] : NEG_BIG;
+                    raw = fmaxf(raw, v[i]);
+                }
+            }
+            // the row's maximum over both halves
+            float* xmt = xm + (it & 1) * 256;
+            xmt[half * 128 + r] = raw;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(BAR(B_XM));                   // a bounded wait, unlike bar.sync
+            if (!mbar_wait(BAR(B_XM), it & 1)) { ok = false; break; }
+            raw = fmaxf(raw, xmt[(half ^ 1) * 128 + r]);
+            const float mx = fmaxf(m, raw > 0.5f * NEG_BIG ? raw * sc : NEG_BIG);
+            const float corr = ex2(m - mx);
+            m = mx;
+            // the product of the tile before this one, in the scale of its own maximum: o = o * corr_prev + O.
+            // Its arrival also means that the P buffer has been read.
+            if (it > 0) {
+                if (!mbar_wait(BAR(B_OFULL), (it - 1) & 1)) { ok = false; break; }
+                tc_fence_after();
+#pragma unroll
+                for (int c = 0; c < DPT; c += 32) {
+                    float t[32];
+                    tmem_ld32(lane_addr + 2 * KN + half * DPT + c, t);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[c + i] = fmaf(o[c + i], corr_prev, t[i]);
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(BAR(B_OFREE));
+            }
+            corr_prev = corr;
+            // probabilities -> shared memory (operand layout), row sum
+            float rs = 0.0f;
+#pragma unroll
+            for (int q8 = 0; q8 < 8; ++q8) {
+                uint32_t w[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float a = v[q8 * 8 + 2 * i], b = v[q8 * 8 + 2 * i + 1];
+                    const float p0 = a > 0.5f * NEG_BIG ? ex2(fmaf(a, sc, -mx)) : 0.0f;
+                    const float p1 = b > 0.5f * NEG_BIG ? ex2(fmaf(b, sc, -mx)) : 0.0f;
+                    rs += p0 + p1;
+                    __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
+                    w[i] = *reinterpret_cast<uint32_t*>(&h2);
+                }
+                *reinterpret_cast<uint4*>(smem + OFF_P + half * ROWBLK + r * 128 + ((q8 ^ (r & 7)) << 4)) =
+                    make_uint4(w[0], w[1], w[2], w[3]);
+            }
+            l = l * corr + rs;
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(BAR(B_PFULL));
+        }
+        // the last tile's product
+        if (ok && n_tiles > 0) {
+            if (mbar_wait(BAR(B_OFULL), (n_tiles - 1) & 1)) {
+                tc_fence_after();
+#pragma unroll
+                for (int c = 0; c < DPT; c += 32) {
+                    float t[32];
+                    tmem_ld32(lane_addr + 2 * KN + half * DPT + c, t);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[c + i] = fmaf(o[c + i], corr_prev, t[i]);
+                }
+            } else {
+                ok = false;
+            }
+        }
+        // the row's sum is the sum of its two halves
+        float* xl = xm + (n_tiles & 1) * 256;
+        xl[half * 128 + r] = l;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(BAR(B_XM));
+        if (ok && mbar_wait(BAR(B_XM), n_tiles & 1)) l += xl[(half ^ 1) * 128 + r];
+        else ok = false;
+        if (!ok) atomicOr(p.err, AIRUN_DEV_TIMEOUT);
+        if (row_ok && ok) {
+            const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+            uint4* dst = reinterpret_cast<uint4*>(p.out + ((size_t)tok * p.nh + head) * HD + half * DPT);
+#pragma unroll
+            for (int c = 0; c < DPT / 8; ++c) {
+                uint32_t w[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    __nv_bfloat162 h2 = __floats2bfloat162_rn(o[c * 8 + 2 * i] * inv, o[c * 8 + 2 * i + 1] * inv);
+                    w[i] = *reinterpret_cast<uint32_t*>(&h2);
+                }
+                dst[c] = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* f = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)f;
+    });
+    return fn;
+}
+// One layer's pages seen as [rows][HD] bfloat16, boxes of 16 rows x 64 values.
+int kv_map_for(CUtensorMap* out, const void* pool, long long rows) {
+    static std::unordered_map<const void*, std::pair<long long, CUtensorMap>> cache;
+    static std::mutex mu;
+    std::lock_guard<std::mutex> g(mu);
+    auto it = cache.find(pool);
+    if (it != cache.end() && it->second.first == rows) { *out = it->second.second; return AIRUN_OK; }
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return AIRUN_ERR_UNSUPPORTED;
+    cuuint64_t dims[2] = {(cuuint64_t)HD, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)HD * 2};
+    cuuint32_t box[2] = {64, 16};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pool), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return AIRUN_ERR_ARG;
+    if (cache.size() > 4096) cache.clear();
+    cache[pool] = std::make_pair(rows, *out);
+    return AIRUN_OK;
+}
+
+}  // namespace
+
+AIRUN_EXPORT int airun_attn_tc_head_dim() { return HD; }
+
+// tiles: [n_tiles] int4 {request, first token row, token count (<= 128 / G), -}.  Pages must be a
+// power of two >= 16 tokens; G = nh / nkv <= 128.
+AIRUN_EXPORT int airun_attn_prefill_tc(const void* q, void* out, const void* pool, const int32_t* block_table,
+                                       int max_blocks, const int32_t* positions, int num_pages, int page_size,
+                                       int nh, int nkv, float scale, int window, const void* tiles, int n_tiles,
+                                       int* err, cudaStream_t stream) {
+    if (n_tiles < 0 || nh <= 0 || nkv <= 0 || nh % nkv != 0 || nh / nkv > QM || !err) return AIRUN_ERR_ARG;
+    int shift = -1;
+    for (int s = 4; s < 20; ++s) if ((1 << s) == page_size) shift = s;
+    if (shift < 0) return AIRUN_ERR_UNSUPPORTED;
+    if (n_tiles == 0) return AIRUN_OK;
+    if (nkv > 65535) return AIRUN_ERR_ARG;
+    TcParams p;
+    p.q = (const __nv_bfloat16*)q; p.out = (__nv_bfloat16*)out; p.block_table = block_table; p.positions = positions;
+    p.max_blocks = max_blocks; p.num_pages = num_pages; p.page_size = page_size; p.page_shift = shift;
+    p.nh = nh; p.nkv = nkv; p.G = nh / nkv; p.scale_log2 = scale * LOG2E; p.window = window; p.err = err;
+    CUtensorMap map;
+    const int r = kv_map_for(&map, pool, (long long)num_pages * 2 * nkv * page_size);
+    if (r != AIRUN_OK) return r;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    airun_launch(attn_prefill_tc_kernel, dim3(n_tiles, nkv), dim3(TC_THREADS), SMEM_TOTAL, stream, p, (const int4*)tiles, map);
+    return airun_launch_status();
+}

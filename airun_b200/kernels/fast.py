@@ -26,7 +26,8 @@ DISABLED = set(filter(None, os.environ.get("AIRUN_DISABLE_FAST", "").split(","))
 
 
 def all_libraries():
-    return [("gemm_tcgen05", None), ("attention_mma", {"HD": 128}), ("attention_mma", {"HD": 64})]
+    return [("gemm_tcgen05", None), ("attention_mma", {"HD": 128}), ("attention_mma", {"HD": 64}),
+            ("attention_tcgen05", {"HD": 128}), ("attention_tcgen05", {"HD": 64})]
 
 
 def scratch_for(device: torch.device) -> Tuple[torch.Tensor, torch.Tensor]:
@@ -158,6 +159,27 @@ def attn_prefill(ctx, q, out, cache, nh, nkv, hd, scale, window, tiles: torch.Te
            "attn_prefill")
 
 
+def prefill_tc_supported(hd: int, page_size: int) -> bool:
+    """The tcgen05 prefill kernel takes head sizes 64 and 128 and pages of 16, 32, 64, ... tokens."""
+    return ("attention_tc" not in DISABLED and hd in (64, 128) and page_size >= 16
+            and (page_size & (page_size - 1)) == 0)
+
+
+def attn_prefill_tc(ctx, q, out, cache, nh, nkv, hd, scale, window, tiles: torch.Tensor, n_tiles: int) -> None:
+    """Flash attention of prompt portions on tcgen05 (csrc/attention_tcgen05.cu); same tiles as attn_prefill."""
+    _cuda(q, out, cache.pool, cache.block_table, tiles)
+    _need(q.dtype == torch.bfloat16 and cache.pool.dtype == torch.bfloat16 and q.is_contiguous() and out.is_contiguous(),
+          "tensor-core attention takes contiguous bfloat16 q, out and pages")
+    _need(prefill_tc_supported(hd, cache.pool.shape[3]), "head size or page size not taken by the tcgen05 attention")
+    _need(tiles.dtype == torch.int32 and tiles.is_contiguous() and tiles.numel() >= 4 * n_tiles, "tiles must be int32 [n, 4]")
+    pool, bt = cache.pool, cache.block_table
+    f = _fn("attention_tcgen05", "airun_attn_prefill_tc",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int,
+             c_void_p, c_int, c_void_p, c_void_p], {"HD": hd})
+    _check(f(_p(q), _p(out), _p(pool), _p(bt), bt.stride(0), _p(ctx.positions), pool.shape[0], pool.shape[3],
+             nh, nkv, float(scale), int(window), _p(tiles), n_tiles, _p(ctx.err), _stream()), "attn_prefill_tc")
+
+
 def attn_decode(ctx, q, out, cache, nh, nkv, hd, scale, window, rows: torch.Tensor, n_rows: int, n_splits: int) -> None:
     """Attention of single decoded tokens (batch rows ``rows``; None: rows 0..n_rows-1), the keys cut
     into ``n_splits`` slices."""
@@ -232,7 +254,10 @@ def attention_bf16(ctx, q, out, cache, nh: int, nkv: int, hd: int, scale: float,
     G = nh // nkv
     plan = _attention_plan(ctx, G)
     if plan["n_tiles"]:
-        attn_prefill(ctx, q, out, cache, nh, nkv, hd, scale, window, plan["tiles"], plan["n_tiles"])
+        if prefill_tc_supported(hd, cache.page_size):
+            attn_prefill_tc(ctx, q, out, cache, nh, nkv, hd, scale, window, plan["tiles"], plan["n_tiles"])
+        else:
+            attn_prefill(ctx, q, out, cache, nh, nkv, hd, scale, window, plan["tiles"], plan["n_tiles"])
     if plan["n_rows"]:
         context = ctx.extras.get("planning_context_len", ctx.max_context_len)
         if window > 0:

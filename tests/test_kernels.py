@@ -289,6 +289,10 @@ ATT = [  # nh, nkv, hd, page, window, context lengths, query lengths
     (16, 2, 128, 16, 0, [257, 129], [1, 129]),            # page edge + 1
     (2, 1, 128, 16, 100, [1000], [1]),                    # window in a long context
     (20, 1, 16, 8, 0, [40, 9], [1, 9]),                   # more than 16 heads in a group
+    (8, 2, 128, 16, 0, [700, 300, 131], [700, 45, 3]),    # long prompts: several 128-key tiles, ragged ends
+    (8, 2, 128, 32, 200, [900, 260], [400, 260]),         # window across tiles, pages of 32
+    (12, 4, 64, 16, 0, [513, 64], [513, 2]),              # head size 64, three heads in a group
+    (5, 1, 128, 64, 0, [260], [260]),                     # a group of 5: 25 tokens per tile, rows left over
 ]
 
 
