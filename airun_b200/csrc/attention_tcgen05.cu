@@ -7,14 +7,15 @@
 //              tiles, 16 keys (one page or a part of one) per box, into two stages each;
 //   warp 1   : allocates tensor memory; one thread issues tcgen05.mma:
 //                S_j = Q K_j^T   (M=128, N=128, K=HD)   into one of two S buffers in tensor memory,
-//                O_j = P_j V_j   (M=128, N=HD,  K=128)  into the O buffer, P_j read from shared memory,
+//                O  += P_j V_j   (M=128, N=HD,  K=128)  into the O buffer, P_j read from shared memory,
 //                                                        V_j as an MN-major operand straight from its tile;
 //              S_{j+1} is issued before O_j so the tensor cores work while the softmax of tile j runs;
 //   warps 2-9: two threads per query row (its lane of tensor memory), one for each half of the
 //              keys of a tile and of the head dimensions: read S_j with tcgen05.ld, mask, running
 //              maximum (agreed between the two through shared memory) and sum in float32 (exp2),
-//              write P_j as bfloat16 into shared memory in the operand layout, and keep the output
-//              row in registers: o = o * 2^(m_{j-2} - m_{j-1}) + O_{j-1}.
+//              write P_j as bfloat16 into shared memory in the operand layout.  O accumulates in
+//              tensor memory over the tiles; a row of it is rescaled only when the row's maximum
+//              has to be raised (by more than 2^8), which is rare after the first tiles.
 // Key j is visible to a query at position p iff j <= p and (window == 0 or p - j < window); tiles
 // wholly hidden are skipped.  Formulas as the reference's prefill kernel computes them
 // (crates/airun-cuda/kernels/ops.cu:1796-2078: scale * log2(e) folded, exp2, float32 statistics,
@@ -114,6 +115,47 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// 32 columns of this thread's lane -> tensor memory
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* v) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr),
+          "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+          "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+          "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+          "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])),
+          "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+          "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
+          "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
+          "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// two loads in flight, one wait
+__device__ __forceinline__ void tmem_ld64(uint32_t taddr, float* v) {
+    uint32_t r[64];
+#define LD32(base, off) \
+    asm volatile( \
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 " \
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15," \
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];" \
+        : "=r"(r[off + 0]), "=r"(r[off + 1]), "=r"(r[off + 2]), "=r"(r[off + 3]), "=r"(r[off + 4]), "=r"(r[off + 5]), \
+          "=r"(r[off + 6]), "=r"(r[off + 7]), "=r"(r[off + 8]), "=r"(r[off + 9]), "=r"(r[off + 10]), "=r"(r[off + 11]), \
+          "=r"(r[off + 12]), "=r"(r[off + 13]), "=r"(r[off + 14]), "=r"(r[off + 15]), "=r"(r[off + 16]), "=r"(r[off + 17]), \
+          "=r"(r[off + 18]), "=r"(r[off + 19]), "=r"(r[off + 20]), "=r"(r[off + 21]), "=r"(r[off + 22]), "=r"(r[off + 23]), \
+          "=r"(r[off + 24]), "=r"(r[off + 25]), "=r"(r[off + 26]), "=r"(r[off + 27]), "=r"(r[off + 28]), "=r"(r[off + 29]), \
+          "=r"(r[off + 30]), "=r"(r[off + 31]) \
+        : "r"(base))
+    LD32(taddr, 0);
+    LD32(taddr + 32, 32);
+#undef LD32
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 64; ++i) v[i] = __uint_as_float(r[i]);
 }
 
 __device__ __forceinline__ float ex2(float x) {
@@ -279,13 +321,13 @@ __global__ __launch_bounds__(TC_THREADS, 1) void attn_prefill_tc_kernel(
                 // P_it is in shared memory (phase it + 1 of P_full) and the O buffer has been read
                 if (!mbar_wait(BAR(B_PFULL), (it + 1) & 1)) { ok = false; break; }
                 if (!mbar_wait(BAR(B_VFULL + s), (it >> 1) & 1)) { ok = false; break; }
-                if (!mbar_wait(BAR(B_OFREE), (it & 1) ^ 1)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t v_addr = smem_u32(smem + OFF_V + s * KV_BYTES);
 #pragma unroll
-                for (int k = 0; k < KN / 16; ++k) {
+                for (int k = 0; k < KN / 16; ++k) {              // O accumulates over the tiles in tensor memory
                     const uint32_t poff = (k >> 2) * ROWBLK + (k & 3) * 32;
-                    umma_bf16(tmem_base + 2 * KN, desc_kmajor(p_addr + poff), desc_mnmajor(v_addr + k * 2048), idesc_o, k > 0 ? 1u : 0u);
+                    umma_bf16(tmem_base + 2 * KN, desc_kmajor(p_addr + poff), desc_mnmajor(v_addr + k * 2048), idesc_o,
+                              (it > 0 || k > 0) ? 1u : 0u);
                 }
                 umma_commit(BAR(B_VEMPTY + s));
                 umma_commit(BAR(B_OFULL));
@@ -322,10 +364,11 @@ __global__ __launch_bounds__(TC_THREADS, 1) void attn_prefill_tc_kernel(
             if (lane == 0) mbar_arrive(BAR(B_PFULL));          // phase 0: Q is ready
         }
 
-        float o[DPT];
-#pragma unroll
-        for (int d = 0; d < DPT; ++d) o[d] = 0.0f;
-        float m = NEG_BIG, l = 0.0f, corr_prev = 1.0f;
+        // The output accumulates in tensor memory.  A row's running maximum is only raised when the
+        // new maximum exceeds it by more than 2^8 (probabilities then stay below 256, harmless in
+        // float32 and bfloat16); raising it means rescaling the row of O, which is rare after the
+        // first tiles, so the product of one tile overlaps the softmax of the next.
+        float m = NEG_BIG, l = 0.0f;
         bool ok = true;
         const float sc = p.scale_log2;
         for (int it = 0; it < n_tiles && ok; ++it) {
@@ -333,12 +376,10 @@ __global__ __launch_bounds__(TC_THREADS, 1) void attn_prefill_tc_kernel(
             const int j0 = (tile_first + it) * KN + half * 64;           // first key of this thread's columns
             if (!mbar_wait(BAR(B_SFULL + s), (it >> 1) & 1)) { ok = false; break; }
             tc_fence_after();
-            const uint32_t s_addr = lane_addr + s * KN + half * 64;
             // every key of the tile is visible to every row: no masks
             const bool full = p.window == 0 && (tile_first + it) * KN + KN - 1 <= pos_lo;
             float v[64];
-            tmem_ld32(s_addr, v);
-            tmem_ld32(s_addr + 32, v + 32);
+            tmem_ld64(lane_addr + s * KN + half * 64, v);
             // the S buffer is in registers: hand it back
             tc_fence_before();
             __syncwarp();
@@ -363,27 +404,32 @@ __global__ __launch_bounds__(TC_THREADS, 1) void attn_prefill_tc_kernel(
             if (lane == 0) mbar_arrive(BAR(B_XM));                   // a bounded wait, unlike bar.sync
             if (!mbar_wait(BAR(B_XM), it & 1)) { ok = false; break; }
             raw = fmaxf(raw, xmt[(half ^ 1) * 128 + r]);
-            const float mx = fmaxf(m, raw > 0.5f * NEG_BIG ? raw * sc : NEG_BIG);
-            const float corr = ex2(m - mx);
-            m = mx;
-            // the product of the tile before this one, in the scale of its own maximum: o = o * corr_prev + O.
-            // Its arrival also means that the P buffer has been read.
-            if (it > 0) {
+            const float mx = raw > 0.5f * NEG_BIG ? raw * sc : NEG_BIG;
+            const bool raise = mx > m + 8.0f;
+            bool landed = it == 0;                                   // has the product of the tile before landed?
+            if (it == 0) {
+                m = mx;                                              // nothing accumulated yet
+            } else if (__any_sync(0xffffffffu, raise)) {
+                // rescale this warp's rows of O: the product of the tile before must have landed
                 if (!mbar_wait(BAR(B_OFULL), (it - 1) & 1)) { ok = false; break; }
+                landed = true;
                 tc_fence_after();
+                const float f = raise ? ex2(m - mx) : 1.0f;
 #pragma unroll
                 for (int c = 0; c < DPT; c += 32) {
                     float t[32];
                     tmem_ld32(lane_addr + 2 * KN + half * DPT + c, t);
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) o[c + i] = fmaf(o[c + i], corr_prev, t[i]);
+                    for (int i = 0; i < 32; ++i) t[i] *= f;
+                    tmem_st32(lane_addr + 2 * KN + half * DPT + c, t);
                 }
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(BAR(B_OFREE));
+                tmem_st_wait();
+                l *= f;
+                if (raise) m = mx;
             }
-            corr_prev = corr;
-            // probabilities -> shared memory (operand layout), row sum
+            // probabilities -> shared memory (operand layout), row sum.  The P buffer is free once the
+            // product of the tile before, which reads it, has landed.
+            if (!landed && !mbar_wait(BAR(B_OFULL), (it - 1) & 1)) { ok = false; break; }
             float rs = 0.0f;
 #pragma unroll
             for (int q8 = 0; q8 < 8; ++q8) {
@@ -391,8 +437,8 @@ __global__ __launch_bounds__(TC_THREADS, 1) void attn_prefill_tc_kernel(
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     const float a = v[q8 * 8 + 2 * i], b = v[q8 * 8 + 2 * i + 1];
-                    const float p0 = a > 0.5f * NEG_BIG ? ex2(fmaf(a, sc, -mx)) : 0.0f;
-                    const float p1 = b > 0.5f * NEG_BIG ? ex2(fmaf(b, sc, -mx)) : 0.0f;
+                    const float p0 = a > 0.5f * NEG_BIG ? ex2(fmaf(a, sc, -m)) : 0.0f;
+                    const float p1 = b > 0.5f * NEG_BIG ? ex2(fmaf(b, sc, -m)) : 0.0f;
                     rs += p0 + p1;
                     __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
                     w[i] = *reinterpret_cast<uint32_t*>(&h2);
@@ -400,22 +446,22 @@ __global__ __launch_bounds__(TC_THREADS, 1) void attn_prefill_tc_kernel(
                 *reinterpret_cast<uint4*>(smem + OFF_P + half * ROWBLK + r * 128 + ((q8 ^ (r & 7)) << 4)) =
                     make_uint4(w[0], w[1], w[2], w[3]);
             }
-            l = l * corr + rs;
+            l += rs;
+            // P written (and O rescaled if need be): hand over to the MMA thread
+            tc_fence_before();
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(BAR(B_PFULL));
         }
-        // the last tile's product
+        // the output row
+        float o[DPT];
+#pragma unroll
+        for (int d = 0; d < DPT; ++d) o[d] = 0.0f;
         if (ok && n_tiles > 0) {
             if (mbar_wait(BAR(B_OFULL), (n_tiles - 1) & 1)) {
                 tc_fence_after();
 #pragma unroll
-                for (int c = 0; c < DPT; c += 32) {
-                    float t[32];
-                    tmem_ld32(lane_addr + 2 * KN + half * DPT + c, t);
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) o[c + i] = fmaf(o[c + i], corr_prev, t[i]);
-                }
+                for (int c = 0; c < DPT; c += 32) tmem_ld32(lane_addr + 2 * KN + half * DPT + c, o + c);
             } else {
                 ok = false;
             }
