@@ -109,6 +109,52 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ 
     }
 }
 
+// Many rows: one warp per row, no block-wide synchronisation, 32 float4 loads in flight per lane
+// group.  The sum x + delta is written first and read back (from cache) for the second pass.
+template <typename TOut>
+__global__ __launch_bounds__(256) void rmsnorm_rows_kernel(float* __restrict__ x, const float* __restrict__ delta,
+                                                           const float* __restrict__ w, TOut* __restrict__ out,
+                                                           int n_rows, int n, float eps, int write_back) {
+    pdl_trigger();
+    pdl_wait();
+    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (row >= n_rows) return;
+    float4* xr = reinterpret_cast<float4*>(x + (size_t)row * n);
+    const float4* dr = delta ? reinterpret_cast<const float4*>(delta + (size_t)row * n) : nullptr;
+    const float4* w4 = reinterpret_cast<const float4*>(w);
+    TOut* outr = out + (size_t)row * n;
+    const int nv = n >> 2;
+    float ss = 0.0f;
+    const bool rewrite = dr && write_back;
+    for (int i = lane; i < nv; i += 32) {
+        float4 v = xr[i];
+        if (dr) {
+            const float4 d = dr[i];
+            v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+            if (rewrite) xr[i] = v;
+        }
+        ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
+    }
+    ss = warp_sum(ss);
+    const float inv = rsqrtf(ss / (float)n + eps);
+    for (int i = lane; i < nv; i += 32) {
+        float4 v = xr[i];
+        if (dr && !rewrite) { const float4 d = dr[i]; v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w; }
+        const float4 g = w ? w4[i] : make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+        const float a = v.x * inv * g.x, b = v.y * inv * g.y, c = v.z * inv * g.z, d2 = v.w * inv * g.w;
+        if (sizeof(TOut) == 4) {
+            reinterpret_cast<float4*>(outr)[i] = make_float4(a, b, c, d2);
+        } else {
+            __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d2);
+            uint2 pk;
+            pk.x = *reinterpret_cast<uint32_t*>(&lo);
+            pk.y = *reinterpret_cast<uint32_t*>(&hi);
+            reinterpret_cast<uint2*>(outr)[i] = pk;
+        }
+    }
+}
+
 AIRUN_EXPORT int airun_rmsnorm(float* x, const float* delta, const float* w, void* out, int out_dtype,
                                const int32_t* rows, int n_rows, int n, float eps, int write_back,
                                cudaStream_t stream) {
@@ -116,6 +162,16 @@ AIRUN_EXPORT int airun_rmsnorm(float* x, const float* delta, const float* w, voi
     if (rows && write_back) return AIRUN_ERR_ARG;
     if (n_rows == 0) return AIRUN_OK;
     const bool vec = n % 4 == 0 && (((uintptr_t)x | (uintptr_t)delta) & 15) == 0;
+    if (vec && !rows && n_rows >= 512 && n >= 512 && (((uintptr_t)out | (uintptr_t)w) & 15) == 0) {
+        const int blocks = (n_rows + 7) / 8;
+        if (out_dtype == AIRUN_DT_F32)
+            airun_launch(rmsnorm_rows_kernel<float>, dim3(blocks), dim3(256), 0, stream, x, delta, w, (float*)out, n_rows, n, eps, write_back);
+        else if (out_dtype == AIRUN_DT_BF16)
+            airun_launch(rmsnorm_rows_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, x, delta, w, (__nv_bfloat16*)out, n_rows, n, eps, write_back);
+        else
+            return AIRUN_ERR_UNSUPPORTED;
+        return airun_launch_status();
+    }
     const int nv = vec ? n / 4 : n;
     int threads = (nv + 31) / 32 * 32;
     if (threads > 1024) threads = 1024;

@@ -25,7 +25,8 @@
 #define ROPE_NEOX 1
 #define MAX_PER_LANE 8   // head_dim <= 256
 
-template <typename TQ, typename TKV>
+// DPL: values of a head per lane, ceil(head_dim / 32) rounded up to 1, 2, 4 or 8.
+template <typename TQ, typename TKV, int DPL>
 __global__ __launch_bounds__(256) void qkv_post_kernel(
     const float* __restrict__ qkv, long long ld_qkv,
     TQ* __restrict__ q_out,
@@ -61,10 +62,10 @@ __global__ __launch_bounds__(256) void qkv_post_kernel(
         const bool is_q = h < nh;
         const bool is_k = !is_q && h < nh + nkv;
         const float* src = qkv + (size_t)t * ld_qkv + (size_t)h * hd;
-        float x[MAX_PER_LANE];
+        float x[DPL];
         float ss = 0.0f;
 #pragma unroll
-        for (int i = 0; i < MAX_PER_LANE; ++i) {
+        for (int i = 0; i < DPL; ++i) {
             const int d = lane + i * 32;
             x[i] = d < hd ? src[d] : 0.0f;
             ss = fmaf(x[i], x[i], ss);
@@ -74,7 +75,7 @@ __global__ __launch_bounds__(256) void qkv_post_kernel(
             ss = warp_sum(ss);
             const float inv = rsqrtf(ss / (float)hd + eps);
 #pragma unroll
-            for (int i = 0; i < MAX_PER_LANE; ++i) {
+            for (int i = 0; i < DPL; ++i) {
                 const int d = lane + i * 32;
                 if (d < hd) x[i] = x[i] * inv * w[d];
             }
@@ -82,13 +83,13 @@ __global__ __launch_bounds__(256) void qkv_post_kernel(
         if (rope_kind == ROPE_NEOX && (is_q || is_k)) {
             __syncwarp();
 #pragma unroll
-            for (int i = 0; i < MAX_PER_LANE; ++i) {
+            for (int i = 0; i < DPL; ++i) {
                 const int d = lane + i * 32;
                 if (d < hd) row[d] = x[i];
             }
             __syncwarp();
 #pragma unroll
-            for (int i = 0; i < MAX_PER_LANE; ++i) {
+            for (int i = 0; i < DPL; ++i) {
                 const int d = lane + i * 32;
                 if (d < rotary_dim && d < hd) {
                     const bool first = d < half;
@@ -104,7 +105,7 @@ __global__ __launch_bounds__(256) void qkv_post_kernel(
         if (is_q) {
             TQ* dst = q_out + ((size_t)t * nh + h) * hd;
 #pragma unroll
-            for (int i = 0; i < MAX_PER_LANE; ++i) {
+            for (int i = 0; i < DPL; ++i) {
                 const int d = lane + i * 32;
                 if (d < hd) dst[d] = from_f32<TQ>(x[i]);
             }
@@ -123,7 +124,7 @@ __global__ __launch_bounds__(256) void qkv_post_kernel(
             TKV* dst = pool + ((((size_t)page * 2 + (is_k ? 0 : 1)) * nkv + kvh) * page_size
                                + (pos % page_size)) * hd;
 #pragma unroll
-            for (int i = 0; i < MAX_PER_LANE; ++i) {
+            for (int i = 0; i < DPL; ++i) {
                 const int d = lane + i * 32;
                 if (d < hd) dst[d] = from_f32<TKV>(x[i]);
             }
@@ -152,13 +153,17 @@ AIRUN_EXPORT int airun_qkv_post(
     int warps = T <= 64 ? (heads < 2 ? heads : 2) : (heads < 8 ? heads : 8);
     const int blocks_y = T <= 64 ? (heads + warps - 1) / warps : 1;
     const size_t smem = ((size_t)warps * hd + (rope_kind != ROPE_NONE ? rotary_dim : 0)) * sizeof(float);
-#define LAUNCH(TQ, TKV) \
-    airun_launch(qkv_post_kernel<TQ, TKV>, dim3(dim3(T, blocks_y)), dim3(warps * 32), smem, stream, qkv, ld_qkv, (TQ*)q_out, q_norm_w, k_norm_w, eps, \
+#define LAUNCH(TQ, TKV, DPL) \
+    airun_launch(qkv_post_kernel<TQ, TKV, DPL>, dim3(T, blocks_y), dim3(warps * 32), smem, stream, qkv, ld_qkv, (TQ*)q_out, q_norm_w, k_norm_w, eps, \
         positions, req_of_token, rope_kind, rotary_dim, inv_freq, (TKV*)pool, block_table, max_blocks, num_reqs, \
         num_pages, page_size, do_store, kv_from_qkv, nh, nkv, hd, err)
-    if (q_dtype == AIRUN_DT_F32) LAUNCH(float, float);
-    else if (q_dtype == AIRUN_DT_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
+#define LAUNCH_DPL(TQ, TKV) \
+    do { if (hd <= 32) LAUNCH(TQ, TKV, 1); else if (hd <= 64) LAUNCH(TQ, TKV, 2); \
+         else if (hd <= 128) LAUNCH(TQ, TKV, 4); else LAUNCH(TQ, TKV, 8); } while (0)
+    if (q_dtype == AIRUN_DT_F32) LAUNCH_DPL(float, float);
+    else if (q_dtype == AIRUN_DT_BF16) LAUNCH_DPL(__nv_bfloat16, __nv_bfloat16);
     else return AIRUN_ERR_UNSUPPORTED;
+#undef LAUNCH_DPL
 #undef LAUNCH
     return airun_launch_status();
 }
