@@ -176,7 +176,7 @@ class Engine:
                 self.storage.zero_state_slot(self.manager.get(e.request.rid).slot)   # a request starts from zero state
             if e.wants_logits:
                 wanting.append(e.request)
-        logits = self.runner.step(entries)
+        logits = self.runner.step(entries, checked=True)
         self.scheduler.advance(plan)
         if wanting:
             tokens = self._sample(logits, wanting)

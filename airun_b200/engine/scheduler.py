@@ -176,6 +176,10 @@ class Scheduler:
             self.manager.free_request(req.rid)
 
     def plan(self) -> Plan:
+        fast = self._plan_steady_decode()
+        if fast is not None:
+            self.stats["steps"] += 1
+            return fast
         preempted: List[Request] = []
         finished: List[Request] = []
         for req in [r for r in self.running if r.cancelled]:
@@ -226,6 +230,24 @@ class Scheduler:
             budget -= want
         self.stats["steps"] += 1
         return Plan(entries, preempted, finished)
+
+    def _plan_steady_decode(self) -> Optional[Plan]:
+        """The common step while generating: nobody waits, nobody is cancelled, every running request
+        brings one token, and even if each needed a new page in every group the pages are there.
+        The general planner would decide the same; this only skips its bookkeeping."""
+        running = self.running
+        n = len(running)
+        if self.waiting or n == 0 or n > self.max_batch_reqs or n > self.max_batch_tokens:
+            return None
+        for g in self.manager.paged:
+            if g.allocator.num_free < n:
+                return None
+        entries = []
+        for req in running:
+            if req.cancelled or req.num_computed < len(req.prompt) or req.num_tokens - req.num_computed != 1:
+                return None
+            entries.append(PlannedEntry(req, req.num_computed, 1, True))
+        return Plan(entries, [], [])
 
     def _plan_running(self) -> Tuple[List[PlannedEntry], Optional[Request]]:
         """Portions for the running requests, in admission order.  Returns the

@@ -122,6 +122,23 @@ class StepRunner:
     def reserve(self, entries: Sequence[StepEntry]) -> None:
         """Takes the pages of all entries, or of none."""
         m = self.manager
+        ps = m.page_size
+        if all(len(e.tokens) == 1 for e in entries):
+            # single tokens: a page is needed only by the requests whose next token opens a block
+            # (every paged group holds the same number of blocks for a request)
+            reqs = m.requests
+            if m.paged:
+                g0 = m.paged[0].gid
+                opening = [e for e in entries if len(reqs[e.rid].blocks[g0]) * ps <= reqs[e.rid].num_tokens]
+            else:
+                opening = []
+            for e in entries:
+                rc = reqs[e.rid]
+                if rc.reserved <= rc.num_tokens:
+                    rc.reserved = rc.num_tokens + 1
+            if not opening:
+                return
+            entries = opening
         needs = [m.pages_needed(e.rid, len(e.tokens)) for e in entries]
         total: Dict[int, int] = {}
         for need in needs:
@@ -204,10 +221,12 @@ class StepRunner:
             decode_only=all(q == 1 for q in qlens))
         return ctx, n_want
 
-    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], checked: bool = False) -> Optional[torch.Tensor]:
         """Runs the entries as one batch; returns float32 logits [wanted, vocab] on
-        the device (valid until the next step) or None when nothing is wanted."""
-        self.check_entries(entries)
+        the device (valid until the next step) or None when nothing is wanted.
+        ``checked``: the caller (the scheduler) has made the entries itself and vouches for them."""
+        if not checked:
+            self.check_entries(entries)
         self.reserve(entries)
         if self.use_graphs and self.device.type == "cuda" and all(
                 len(e.tokens) == 1 and tuple(e.want) == (0,) for e in entries):
