@@ -10,8 +10,12 @@ and model.safetensors; the prompt is a list of token ids (``-p 1,2,3``, a file,
 or standard input), since the engine works on token ids.  ``--dtype`` takes the
 place of ``--kv-type``: the cache is kept in the compute type.
 
-Subcommands: ``run`` (generate), ``init`` (random-weights mode: write a model
-folder from a config.json and a seed), ``inspect`` (print the configuration).
+Subcommands: ``run`` (generate), ``bench`` (prefill and decode rates of a model
+folder, median of runs, in the manner of crates/airun-cli/src/bench.rs:11-92),
+``perplexity`` (loss and top-1 of a token file, token by token or in chunks,
+crates/airun-cli/src/perplexity.rs:97-222), ``init`` (random-weights mode: write
+a model folder from a config.json and a seed), ``inspect`` (print the
+configuration).
 """
 from __future__ import annotations
 
@@ -59,6 +63,24 @@ def build_parser() -> argparse.ArgumentParser:
     run.add_argument("--eog", default="", help="token ids that end generation")
     run.add_argument("--stats", action="store_true", help="print timing to stderr")
     run.add_argument("-q", "--quiet", action="store_true", help="print only the generated ids")
+
+    be = sub.add_parser("bench", help="prefill and decode tokens a second of a model folder")
+    be.add_argument("model")
+    be.add_argument("--prefill", default="128,512", help="prompt lengths to time, comma separated")
+    be.add_argument("--decode", type=int, default=128, help="tokens to decode per run")
+    be.add_argument("--decode-at", type=int, default=16, help="context depth at which decoding starts")
+    be.add_argument("--parallel", type=int, default=1, help="requests decoding side by side")
+    be.add_argument("--runs", type=int, default=3)
+    be.add_argument("--warmup", type=int, default=1)
+    be.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
+    be.add_argument("-b", "--batch-size", type=int, default=2048)
+    be.add_argument("--json", action="store_true")
+
+    pp = sub.add_parser("perplexity", help="loss and top-1 accuracy over a file of token ids")
+    pp.add_argument("model")
+    pp.add_argument("--tokens-file", required=True)
+    pp.add_argument("--chunk", type=int, default=1, help="tokens per step (1: the decode kernels; more: the prefill kernels)")
+    pp.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
 
     init = sub.add_parser("init", help="write a model folder with seeded random weights")
     init.add_argument("config", help="a config.json of the architecture")
@@ -110,6 +132,113 @@ def cmd_run(a) -> int:
     return 0
 
 
+def _random_ids(n: int, vocab: int, seed: int = 0x2545F4914F6CDD1D) -> List[int]:
+    """A fixed-seed xorshift id stream, as the reference's bench --random-tokens
+    (crates/airun-cli/src/bench.rs:177-187)."""
+    x, out = seed, []
+    for _ in range(n):
+        x ^= (x << 13) & 0xFFFFFFFFFFFFFFFF
+        x ^= x >> 7
+        x ^= (x << 17) & 0xFFFFFFFFFFFFFFFF
+        out.append(x % vocab)
+    return out
+
+
+def cmd_bench(a) -> int:
+    import statistics
+    import torch
+    from . import Engine, EngineOptions, StepEntry
+    from .kernels import ops
+    lengths = [int(x) for x in a.prefill.split(",") if x]
+    need = max(lengths + [a.decode_at + a.decode + 1]) + 64
+    eng = Engine.from_folder(a.model, EngineOptions(dtype=a.dtype, cache_tokens=need * max(a.parallel, 1) + 64,
+                                                     max_batch_tokens=max(a.batch_size, 16), max_requests=max(a.parallel, 1),
+                                                     max_context=need))
+    V = eng.config.vocab_size
+    picked = torch.zeros(max(a.parallel, 1), dtype=torch.int32, device=eng.device)
+
+    def timed(fn):
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1)
+
+    def prefill(rid, toks):
+        eng.manager.add_request(rid)
+        for p0 in range(0, len(toks), a.batch_size):
+            part = toks[p0:p0 + a.batch_size]
+            last = p0 + len(part) == len(toks)
+            eng.runner.step([StepEntry(rid, part, (len(part) - 1,) if last else ())])
+
+    report = {"prefill": {}, "decode": {}}
+    for n in lengths:
+        toks = _random_ids(n, V)
+        ms = []
+        for r in range(a.warmup + a.runs):
+            t = timed(lambda: prefill("p", toks))
+            eng.manager.free_request("p")
+            if r >= a.warmup:
+                ms.append(t)
+        report["prefill"][n] = dict(tokens_per_s=n / (statistics.median(ms) / 1e3), ms=ms)
+    rids = [f"d{i}" for i in range(max(a.parallel, 1))]
+    ms = []
+    for r in range(a.warmup + a.runs):
+        for i, rid in enumerate(rids):
+            prefill(rid, _random_ids(a.decode_at, V, seed=1234 + i))
+        toks = _random_ids(a.decode * len(rids), V, seed=99)
+
+        def decode():
+            for s in range(a.decode):
+                logits = eng.runner.step([StepEntry(rid, [toks[s * len(rids) + i]], (0,)) for i, rid in enumerate(rids)])
+                ops.sample(logits, picked)
+
+        t = timed(decode)
+        for rid in rids:
+            eng.manager.free_request(rid)
+        if r >= a.warmup:
+            ms.append(t)
+    report["decode"] = dict(tokens_per_s=a.decode * len(rids) / (statistics.median(ms) / 1e3), depth=a.decode_at,
+                            parallel=len(rids), ms=ms)
+    eng.runner.raise_on_device_error()
+    if a.json:
+        print(json.dumps(report))
+    else:
+        for n, v in report["prefill"].items():
+            print(f"prefill {n:6d} tokens: {v['tokens_per_s']:10.1f} tok/s (median of {len(v['ms'])})")
+        d = report["decode"]
+        print(f"decode {a.decode} tokens at depth {d['depth']} x {d['parallel']}: {d['tokens_per_s']:10.1f} tok/s")
+    return 0
+
+
+def cmd_perplexity(a) -> int:
+    import math
+    import torch
+    from . import Engine, EngineOptions, StepEntry
+    with open(a.tokens_file) as f:
+        ids = parse_ids(f.read())
+    if len(ids) < 2:
+        raise SystemExit("perplexity needs at least two tokens")
+    eng = Engine.from_folder(a.model, EngineOptions(dtype=a.dtype, cache_tokens=len(ids) + 64, max_requests=1,
+                                                     max_batch_tokens=max(a.chunk, 16), max_context=len(ids) + 64))
+    eng.manager.add_request("t")
+    nll, hits, n = 0.0, 0, 0
+    for p0 in range(0, len(ids) - 1, a.chunk):
+        part = ids[p0:min(p0 + a.chunk, len(ids) - 1)]
+        logits = eng.runner.step([StepEntry("t", part, tuple(range(len(part))))]).float()
+        logp = torch.log_softmax(logits, dim=-1).cpu()
+        for i in range(len(part)):
+            target = ids[p0 + i + 1]
+            nll -= float(logp[i, target])
+            hits += int(int(torch.argmax(logp[i])) == target)
+            n += 1
+    eng.runner.raise_on_device_error()
+    print(f"tokens {n}  loss {nll / n:.4f} nats/token  perplexity {math.exp(nll / n):.3f}  top-1 {100.0 * hits / n:.1f} %")
+    return 0
+
+
 def cmd_init(a) -> int:
     import torch
     from .config import architecture_name, lookup_architecture
@@ -132,7 +261,8 @@ def cmd_inspect(a) -> int:
 
 def main(argv: Optional[List[str]] = None) -> int:
     a = build_parser().parse_args(argv)
-    return {"run": cmd_run, "init": cmd_init, "inspect": cmd_inspect}[a.cmd](a)
+    return {"run": cmd_run, "bench": cmd_bench, "perplexity": cmd_perplexity, "init": cmd_init,
+            "inspect": cmd_inspect}[a.cmd](a)
 
 
 if __name__ == "__main__":

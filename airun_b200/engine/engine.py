@@ -27,6 +27,10 @@ from ..weights.loader import open_model_folder
 from .scheduler import FinishReason, Plan, Request, Scheduler
 from .step import StepEntry, StepRunner
 
+# AIRUN_SCHED_TIMING=1 prints the host time of every scheduler step (the reference's switch of the
+# same name, crates/airun-cli/src/sched.rs:345-348).
+SCHED_TIMING = __import__("os").environ.get("AIRUN_SCHED_TIMING", "") not in ("", "0")
+
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
            torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
 
@@ -163,6 +167,7 @@ class Engine:
 
     def run_step(self) -> List[Request]:
         """One scheduler step: plan, run, sample.  Returns the requests that finished."""
+        t_start = time.perf_counter() if SCHED_TIMING else 0.0
         plan = self.scheduler.plan()
         finished = list(plan.finished)
         if not plan.entries:
@@ -185,6 +190,11 @@ class Engine:
                     finished.append(req)
         self.stats.steps += 1
         self.stats.preemptions += len(plan.preempted)
+        if SCHED_TIMING:
+            import sys
+            print(f"[airun_b200] step {self.stats.steps}: {len(plan.entries)} requests, "
+                  f"{sum(e.count for e in plan.entries)} tokens, {(time.perf_counter() - t_start) * 1e3:.3f} ms",
+                  file=sys.stderr)
         return finished
 
     def _sample(self, logits: torch.Tensor, reqs: List[Request]) -> List[int]:

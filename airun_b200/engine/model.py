@@ -11,6 +11,8 @@ the last residual add (runtime.rs:3745-3746).
 """
 from __future__ import annotations
 
+import os
+import sys
 from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
@@ -19,6 +21,10 @@ from ..config.base import LayerCall, ModelConfig
 from ..parts.base import make_part
 from ..parts.embedding import LMHead, TokenEmbedding
 from ..weights.loader import (DictSource, TensorSource, WeightSpec, load_tensors, random_tensors)
+
+# AIRUN_TRACE_LAYERS=1 prints the residual stream's rms and mean after every block (the reference's
+# switch of the same name, crates/airun-core/src/runtime.rs:5265-5302).  Off by default.
+TRACE_LAYERS = os.environ.get("AIRUN_TRACE_LAYERS", "") not in ("", "0")
 
 DEFAULT_NAMES = dict(embed="model.embed_tokens.weight", layer="model.layers.{i}", mixer="self_attn",
                      ffn="mlp", norm1="input_layernorm", norm2="post_attention_layernorm",
@@ -92,10 +98,15 @@ class DecoderModel:
         x = ctx.ws_main.alloc((T, self.H), torch.float32)
         self.embedding.forward(ctx, ctx.token_ids[:T], x)
         delta = None
+        trace = TRACE_LAYERS and not torch.cuda.is_current_stream_capturing()
         for ci, call in enumerate(self.order):
             ctx.ws = ctx.ws_pair[ci % 2]
             ctx.ws.reset()
             delta = self.layers[call.layer].forward(ctx, x, delta, ctx.caches[ci])
+            if trace:           # synchronises after every block: a debugging aid, as the reference's AIRUN_TRACE_LAYERS
+                r = (x[:ctx.num_tokens] + delta[:ctx.num_tokens]).float()
+                print(f"[airun_b200] entry {ci} layer {call.layer}: rms {float(r.pow(2).mean().sqrt()):.6f} "
+                      f"mean {float(r.mean()):+.6f}", file=sys.stderr)
         if n_want == 0:
             return None
         ctx.ws = ctx.ws_pair[len(self.order) % 2]

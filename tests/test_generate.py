@@ -101,3 +101,31 @@ def test_smoke_entry():
     sys.path.insert(0, ROOT)
     import __graft_entry__ as g
     g.smoke()
+
+
+def test_perplexity_and_bench_subcommands(folders, tmp_path):
+    """Token by token (the decode kernels) and in chunks (the prefill kernels) the loss agrees, and it
+    is the plain implementation's (the reference's check: crates/airun-cli/src/perplexity.rs:9-11)."""
+    import math
+    import re
+    cfg, W = P.read_model_folder(folders["C"])
+    ids = random_tokens(90, cfg["vocab_size"], 21)
+    logp = torch.log_softmax(P.plain_forward(cfg, W, ids, torch.float32), dim=-1)
+    want = -sum(float(logp[i, ids[i + 1]]) for i in range(len(ids) - 1)) / (len(ids) - 1)
+    f = tmp_path / "ids.txt"
+    f.write_text(" ".join(map(str, ids)))
+    losses = []
+    for chunk in ("1", "24"):
+        out = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "airun"), "perplexity", folders["C"],
+                              "--tokens-file", str(f), "--chunk", chunk, "--dtype", "float32"],
+                             capture_output=True, text=True, timeout=300)
+        assert out.returncode == 0, out.stderr
+        losses.append(float(re.search(r"loss ([0-9.]+)", out.stdout).group(1)))
+    assert abs(losses[0] - want) < 2e-4 and abs(losses[1] - want) < 2e-4
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "airun"), "bench", folders["C"], "--prefill", "33,64",
+                          "--decode", "8", "--decode-at", "20", "--parallel", "2", "--runs", "2", "--json"],
+                         capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr
+    import json
+    rep = json.loads(out.stdout.strip().splitlines()[-1])
+    assert set(rep["prefill"]) == {"33", "64"} and rep["decode"]["tokens_per_s"] > 0 and rep["decode"]["parallel"] == 2
