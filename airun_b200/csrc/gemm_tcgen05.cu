@@ -38,6 +38,7 @@
 #define EPI_F32 0
 #define EPI_BF16 1
 #define EPI_SWIGLU 2
+#define EPI_RESID 3
 #define GEMM_THREADS 192
 #define WAIT_LIMIT_NS 2000000000ull
 
@@ -135,6 +136,18 @@ struct GemmParams {
     float* scratch;               // [tiles][ksplit][BN][128] partial tiles
     int* counters;                // [tiles], zero between launches
     int* err;
+    // RMSNorm folded into two products.  The product that ENDS a sub-layer (EPI_RESID) adds its result to
+    // the residual stream x, writes h' = bfloat16(x * w_norm) for the next product and the sums of x^2
+    // per token in parts; the product that STARTS the next sub-layer reads h' and multiplies each
+    // token's results by rsqrt(sum of the parts / n + eps): (s * h') W^T = s * (h' W^T).
+    const float* ssq_in;          // [ssq_parts][ssq_ld] or null: token scales of the input
+    int ssq_parts, ssq_ld;
+    float eps_in, inv_n_in;       // 1 / (size of the normed row)
+    float* resid;                 // [tokens][ld_resid] float32 residual stream (EPI_RESID)
+    long long ld_resid;
+    const float* norm_w;          // [weight rows] weight of the norm that follows (EPI_RESID)
+    float* ssq_out;               // [parts][ssq_out_ld] (EPI_RESID)
+    int ssq_out_ld;
 };
 
 template <int BN, int STAGES>
@@ -224,6 +237,71 @@ __device__ __forceinline__ void store_swiglu_swapped(const GemmParams& p, const 
             const int n_out = (a_row / 32) * 16 + (a_row % 32);
             ((__nv_bfloat16*)p.out)[(size_t)tok * p.ldc + n_out] = __float2bfloat16_rn(silu_mul(v[i], up));
         }
+    }
+}
+
+// rsqrt(sum of the parts / n + eps) of one token
+__device__ __forceinline__ float token_scale(const GemmParams& p, int tok) {
+    float s = 0.0f;
+    for (int i = 0; i < p.ssq_parts; ++i) s += __ldcg(p.ssq_in + (size_t)i * p.ssq_ld + tok);
+    return rsqrtf(s * p.inv_n_in + p.eps_in);
+}
+
+// EPI_RESID, normal mode: this thread's token row, 16 weight rows from n0.  Returns the sum of squares.
+__device__ __forceinline__ float store_resid_normal(const GemmParams& p, const float* v, int a_row, int n0) {
+    if (a_row >= p.a_rows) return 0.0f;
+    float* xr = p.resid + (size_t)a_row * p.ld_resid + n0;
+    __nv_bfloat16* o = (__nv_bfloat16*)p.out + (size_t)a_row * p.ldc + n0;
+    float sq = 0.0f;
+    if (n0 + 16 <= p.b_rows && ((((size_t)xr) | ((size_t)(p.norm_w + n0))) & 15) == 0 && (((size_t)o) & 15) == 0) {
+        uint32_t w[8];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            float4 x4 = *reinterpret_cast<float4*>(xr + 4 * q);
+            const float4 g = *reinterpret_cast<const float4*>(p.norm_w + n0 + 4 * q);
+            x4.x += v[4 * q]; x4.y += v[4 * q + 1]; x4.z += v[4 * q + 2]; x4.w += v[4 * q + 3];
+            *reinterpret_cast<float4*>(xr + 4 * q) = x4;
+            sq = fmaf(x4.x, x4.x, fmaf(x4.y, x4.y, fmaf(x4.z, x4.z, fmaf(x4.w, x4.w, sq))));
+            __nv_bfloat162 lo = __floats2bfloat162_rn(x4.x * g.x, x4.y * g.y), hi = __floats2bfloat162_rn(x4.z * g.z, x4.w * g.w);
+            w[2 * q] = *reinterpret_cast<uint32_t*>(&lo);
+            w[2 * q + 1] = *reinterpret_cast<uint32_t*>(&hi);
+        }
+        *reinterpret_cast<uint4*>(o) = make_uint4(w[0], w[1], w[2], w[3]);
+        *reinterpret_cast<uint4*>(o + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            if (n0 + i < p.b_rows) {
+                const float xn = xr[i] + v[i];
+                xr[i] = xn;
+                sq = fmaf(xn, xn, sq);
+                o[i] = __float2bfloat16_rn(xn * p.norm_w[n0 + i]);
+            }
+        }
+    }
+    return sq;
+}
+
+// EPI_RESID, swapped mode: this lane's weight row a_row, 16 tokens from b0 + c0.  The sums of squares
+// over the warp's 32 weight rows go to part (a_row / 32) of each token.
+__device__ __forceinline__ void store_resid_swapped(const GemmParams& p, const float* v, int a_row, int b0, int c0) {
+    const int lane = threadIdx.x & 31;
+    const bool row_ok = a_row < p.a_rows;
+    const float g = row_ok ? p.norm_w[a_row] : 0.0f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const int tok = b0 + c0 + i;
+        float sq = 0.0f;
+        if (row_ok && tok < p.b_rows) {
+            float* xr = p.resid + (size_t)tok * p.ld_resid + a_row;
+            const float xn = *xr + v[i];
+            *xr = xn;
+            sq = xn * xn;
+            ((__nv_bfloat16*)p.out)[(size_t)tok * p.ldc + a_row] = __float2bfloat16_rn(xn * g);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+        if (lane == 0 && tok < p.b_rows) p.ssq_out[(size_t)(a_row >> 5) * p.ssq_out_ld + tok] = sq;
     }
 }
 
@@ -320,6 +398,18 @@ __global__ __launch_bounds__(GEMM_THREADS, 1) void gemm_tcgen05_kernel(
         const int quad = warp & 3;
         const int a_row = a0 + quad * 32 + lane;
         const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
+        // token scales of a normed input, while the MMAs run
+        __shared__ float s_scale[SWAP ? BN : 1];
+        float row_scale = 1.0f;
+        if (p.ssq_in) {
+            if (SWAP) {
+                for (int j = threadIdx.x - 64; j < BN; j += 128) s_scale[j] = b0 + j < p.b_rows ? token_scale(p, b0 + j) : 0.0f;
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+            } else if (a_row < p.a_rows) {
+                row_scale = token_scale(p, a_row);
+            }
+        }
+        float ssq_acc = 0.0f;
         bool ok = n_kb == 0 ? true : mbar_wait(accum, 0);
         if (!ok) { atomicOr(p.err, AIRUN_DEV_TIMEOUT); }
         tc_fence_after();
@@ -387,13 +477,25 @@ __global__ __launch_bounds__(GEMM_THREADS, 1) void gemm_tcgen05_kernel(
                         }
                     }
                 }
+                if (p.ssq_in) {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const float f = SWAP ? s_scale[c + i] : row_scale;
+                        v[i] *= f;
+                        if (STEP == 32) u[i] *= f;
+                    }
+                }
                 if (EPI == EPI_SWIGLU) {
                     if (SWAP) store_swiglu_swapped(p, v, a_row, b0, c);
                     else store_swiglu_normal(p, v, u, a_row, b0, c);
+                } else if (EPI == EPI_RESID) {
+                    if (SWAP) store_resid_swapped(p, v, a_row, b0, c);
+                    else ssq_acc += store_resid_normal(p, v, a_row, b0 + c);
                 } else {
                     store_chunk<EPI, SWAP>(p, v, a_row, b0, c);
                 }
             }
+            if (EPI == EPI_RESID && !SWAP && a_row < p.a_rows) p.ssq_out[(size_t)blockIdx.y * p.ssq_out_ld + a_row] = ssq_acc;
         }
     }
     tc_fence_before();
@@ -486,6 +588,8 @@ __global__ __launch_bounds__(GEMM_THREADS, 1) void gemm_tcgen05_persistent_kerne
             const int buf = n & 1;
             const int a0 = (tile % m_tiles) * BM, b0 = (tile / m_tiles) * PBN;
             const int a_row = a0 + quad * 32 + lane;
+            const float row_scale = (p.ssq_in && a_row < p.a_rows) ? token_scale(p, a_row) : 1.0f;   // while the MMAs run
+            float ssq_acc = 0.0f;
             if (!mbar_wait(accf0 + 8 * buf, (n >> 1) & 1)) { atomicOr(p.err, AIRUN_DEV_TIMEOUT); break; }
             tc_fence_after();
             const uint32_t lane_addr = tmem_base + buf * PBN + ((uint32_t)(quad * 32) << 16);
@@ -500,9 +604,15 @@ __global__ __launch_bounds__(GEMM_THREADS, 1) void gemm_tcgen05_persistent_kerne
                     __syncwarp();
                     if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acce0 + 8 * buf) : "memory");
                 }
+                if (p.ssq_in) {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) { v[i] *= row_scale; if (STEP == 32) u[i] *= row_scale; }
+                }
                 if (EPI == EPI_SWIGLU) store_swiglu_normal(p, v, u, a_row, b0, c);
+                else if (EPI == EPI_RESID) ssq_acc += store_resid_normal(p, v, a_row, b0 + c);
                 else store_chunk<EPI, false>(p, v, a_row, b0, c);
             }
+            if (EPI == EPI_RESID && a_row < p.a_rows) p.ssq_out[(size_t)(tile / m_tiles) * p.ssq_out_ld + a_row] = ssq_acc;
         }
     }
     tc_fence_before();
@@ -635,19 +745,28 @@ AIRUN_EXPORT long long airun_gemm_tcgen05_scratch_floats(int M, int N, int swap,
 }
 
 // out[M][N] = x[M][K] * W[N][K]^T.  x, W bfloat16 row-major (K % 8 == 0, 16-byte aligned rows).
-// epi: 0 float32 out [M][N]; 1 bfloat16 out [M][N]; 2 SwiGLU, bfloat16 out [M][N/2].
+// epi: 0 float32 out [M][N]; 1 bfloat16 out [M][N]; 2 SwiGLU, bfloat16 out [M][N/2];
+//      3 residual + norm: resid[M][N] += result, out[M][N] = bfloat16(resid * norm_w), ssq_out[parts][ssq_out_ld]
+//        = sums of resid^2 per token; parts = 4 * ceil(N / 128) when swapped, ceil(N / bn) otherwise.
 // swap: weights as the 128-row operand (bn >= M, one B tile per 'bn' tokens).
 // counters: one int per tile, zero on entry when ksplit > 1 (the kernel leaves them zero).
-AIRUN_EXPORT int airun_gemm_tcgen05(const void* x, const void* W, void* out, int M, int N, int K,
-                                    long long ldx, long long ldw, long long ldc, int epi, int swap, int bn,
-                                    int ksplit, float* scratch, int* counters, int* err, cudaStream_t stream) {
+// ssq_in: when not null, x is an un-normalised bfloat16(resid * norm_w) and every token's results are
+//   multiplied by rsqrt(sum over ssq_parts of ssq_in[part][token] / norm_size + eps).
+AIRUN_EXPORT int airun_gemm_tcgen05_ex(const void* x, const void* W, void* out, int M, int N, int K,
+                                       long long ldx, long long ldw, long long ldc, int epi, int swap, int bn,
+                                       int ksplit, float* scratch, int* counters, int* err, cudaStream_t stream,
+                                       const float* ssq_in, int ssq_parts, int ssq_ld, float eps_in, int norm_size,
+                                       float* resid, long long ld_resid, const float* norm_w, float* ssq_out,
+                                       int ssq_out_ld) {
     if (M <= 0 || N <= 0 || K <= 0 || !err) return M == 0 ? AIRUN_OK : AIRUN_ERR_ARG;
     if (K % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0 || ((uintptr_t)x & 15) || ((uintptr_t)W & 15)) return AIRUN_ERR_ARG;
     if (epi == EPI_SWIGLU && (N % 32 != 0)) return AIRUN_ERR_ARG;
     if (ksplit < 1 || (ksplit > 1 && (!scratch || !counters))) return AIRUN_ERR_ARG;
+    if (ssq_in && (ssq_parts <= 0 || ssq_ld < M || norm_size <= 0)) return AIRUN_ERR_ARG;
+    if (epi == EPI_RESID && (!resid || !norm_w || !ssq_out || ssq_out_ld < M || ld_resid < N)) return AIRUN_ERR_ARG;
     const int kb_total = (K + BK - 1) / BK;
     if (ksplit > kb_total) ksplit = kb_total;
-    GemmParams p;
+    GemmParams p = {};
     p.a_rows = swap ? N : M;
     p.b_rows = swap ? M : N;
     p.K = K;
@@ -658,6 +777,9 @@ AIRUN_EXPORT int airun_gemm_tcgen05(const void* x, const void* W, void* out, int
     p.scratch = scratch;
     p.counters = counters;
     p.err = err;
+    p.ssq_in = ssq_in; p.ssq_parts = ssq_parts; p.ssq_ld = ssq_ld; p.eps_in = eps_in;
+    p.inv_n_in = norm_size > 0 ? 1.0f / (float)norm_size : 0.0f;
+    p.resid = resid; p.ld_resid = ld_resid; p.norm_w = norm_w; p.ssq_out = ssq_out; p.ssq_out_ld = ssq_out_ld;
     CUtensorMap ma, mb;
     int r;
     if (swap) {
@@ -672,7 +794,16 @@ AIRUN_EXPORT int airun_gemm_tcgen05(const void* x, const void* W, void* out, int
     if (epi == EPI_F32) return dispatch<EPI_F32>(swap != 0, bn, ma, mb, p, grid, stream);
     if (epi == EPI_BF16) return dispatch<EPI_BF16>(swap != 0, bn, ma, mb, p, grid, stream);
     if (epi == EPI_SWIGLU) return dispatch<EPI_SWIGLU>(swap != 0, bn, ma, mb, p, grid, stream);
+    if (epi == EPI_RESID) return dispatch<EPI_RESID>(swap != 0, bn, ma, mb, p, grid, stream);
     return AIRUN_ERR_UNSUPPORTED;
+}
+
+AIRUN_EXPORT int airun_gemm_tcgen05(const void* x, const void* W, void* out, int M, int N, int K,
+                                    long long ldx, long long ldw, long long ldc, int epi, int swap, int bn,
+                                    int ksplit, float* scratch, int* counters, int* err, cudaStream_t stream) {
+    if (epi == EPI_RESID) return AIRUN_ERR_ARG;
+    return airun_gemm_tcgen05_ex(x, W, out, M, N, K, ldx, ldw, ldc, epi, swap, bn, ksplit, scratch, counters, err, stream,
+                                 nullptr, 0, 0, 0.0f, 0, nullptr, 0, nullptr, nullptr, 0);
 }
 
 // ------------------------------------------------------------------ no-allocation variant
@@ -733,7 +864,7 @@ AIRUN_EXPORT int airun_gemm_tcgen05_static(const void* x, const void* W, void* o
     if (swap ? !(bn == 16 || bn == 32 || bn == 64 || bn == 128) : !(bn == 128 || bn == 256)) return AIRUN_ERR_UNSUPPORTED;
     const int kb_total = (K + BK - 1) / BK;
     if (ksplit > kb_total) ksplit = kb_total;
-    GemmParams p;
+    GemmParams p = {};
     p.a_rows = swap ? N : M;
     p.b_rows = swap ? M : N;
     p.K = K;

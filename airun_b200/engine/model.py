@@ -102,9 +102,14 @@ class DecoderModel:
         for ci, call in enumerate(self.order):
             ctx.ws = ctx.ws_pair[ci % 2]
             ctx.ws.reset()
-            delta = self.layers[call.layer].forward(ctx, x, delta, ctx.caches[ci])
+            nxt = self.layers[self.order[ci + 1].layer] if ci + 1 < len(self.order) else None
+            next_norm = nxt.norm1 if (nxt is not None and getattr(nxt, "accepts_normed", lambda: False)()) else None
+            if next_norm is not None:
+                delta = self.layers[call.layer].forward(ctx, x, delta, ctx.caches[ci], next_norm=next_norm)
+            else:
+                delta = self.layers[call.layer].forward(ctx, x, delta, ctx.caches[ci])
             if trace:           # synchronises after every block: a debugging aid, as the reference's AIRUN_TRACE_LAYERS
-                r = (x[:ctx.num_tokens] + delta[:ctx.num_tokens]).float()
+                r = x[:ctx.num_tokens] if not isinstance(delta, torch.Tensor) else (x[:ctx.num_tokens] + delta[:ctx.num_tokens])
                 print(f"[airun_b200] entry {ci} layer {call.layer}: rms {float(r.pow(2).mean().sqrt()):.6f} "
                       f"mean {float(r.mean()):+.6f}", file=sys.stderr)
         if n_want == 0:

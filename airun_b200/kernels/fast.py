@@ -15,7 +15,7 @@ import torch
 from . import ops
 from .ops import _check, _cuda, _fn, _need, _p, _stream
 
-EPI_F32, EPI_BF16, EPI_SWIGLU = 0, 1, 2
+EPI_F32, EPI_BF16, EPI_SWIGLU, EPI_RESID = 0, 1, 2, 3
 TARGET_CTAS = 296                      # two waves of 148 SMs
 
 _SCRATCH: Dict[torch.device, Tuple[torch.Tensor, torch.Tensor]] = {}
@@ -41,11 +41,22 @@ def scratch_for(device: torch.device) -> Tuple[torch.Tensor, torch.Tensor]:
     return s
 
 
+def resid_parts(N: int, swap: bool, bn: int) -> int:
+    """Parts the residual + norm epilogue writes the sums of squares in."""
+    return 4 * ((N + 127) // 128) if swap else (N + bn - 1) // bn
+
+
 def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: int, swap: bool, bn: int,
                  ksplit: int, err: torch.Tensor, scratch: Optional[torch.Tensor] = None,
-                 counters: Optional[torch.Tensor] = None) -> None:
-    """out = x @ w^T on tcgen05 (see csrc/gemm_tcgen05.cu for the modes)."""
-    _cuda(x, w, out, err, scratch, counters)
+                 counters: Optional[torch.Tensor] = None, ssq_in: Optional[torch.Tensor] = None,
+                 eps_in: float = 0.0, norm_size: int = 0, resid: Optional[torch.Tensor] = None,
+                 norm_w: Optional[torch.Tensor] = None, ssq_out: Optional[torch.Tensor] = None) -> None:
+    """out = x @ w^T on tcgen05 (see csrc/gemm_tcgen05.cu for the modes).
+
+    ``ssq_in`` [parts, M] float32: x is bfloat16(residual * norm weight) and each token's results are
+    scaled by rsqrt(sum of its parts / norm_size + eps_in).  ``epi == EPI_RESID``: ``resid`` [M, N]
+    float32 += result, out = bfloat16(resid * norm_w), ssq_out [resid_parts, M] = sums of resid^2."""
+    _cuda(x, w, out, err, scratch, counters, ssq_in, resid, norm_w, ssq_out)
     _need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16, "tcgen05 gemm takes bfloat16 operands")
     M, K = x.shape
     N = w.shape[0]
@@ -55,6 +66,13 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: int, 
     if epi == EPI_SWIGLU:
         _need(N % 32 == 0 and tuple(out.shape) == (M, N // 2) and out.dtype == torch.bfloat16,
               "SwiGLU epilogue writes bfloat16 [M, N/2]")
+    elif epi == EPI_RESID:
+        _need(tuple(out.shape) == (M, N) and out.dtype == torch.bfloat16, "residual epilogue writes bfloat16 [M, N]")
+        _need(resid is not None and resid.dtype == torch.float32 and tuple(resid.shape) == (M, N) and resid.stride(1) == 1,
+              "resid must be float32 [M, N]")
+        _need(norm_w is not None and norm_w.dtype == torch.float32 and tuple(norm_w.shape) == (N,), "norm_w must be float32 [N]")
+        _need(ssq_out is not None and ssq_out.dtype == torch.float32 and ssq_out.dim() == 2 and ssq_out.is_contiguous()
+              and ssq_out.shape[0] >= resid_parts(N, swap, bn) and ssq_out.shape[1] >= M, "ssq_out must be float32 [parts, M]")
     else:
         _need(tuple(out.shape) == (M, N), "output must be [M, N]")
         _need(out.dtype == (torch.float32 if epi == EPI_F32 else torch.bfloat16), "output type does not match the epilogue")
@@ -71,12 +89,19 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: int, 
         a_rows, b_rows = (N, M) if swap else (M, N)
         tiles = ((a_rows + 127) // 128) * ((b_rows + bn - 1) // bn)
         _need(need <= scratch.numel() and tiles <= counters.numel(), "split-K scratch is too small for this launch")
-    f = _fn("gemm_tcgen05", "airun_gemm_tcgen05",
+    if ssq_in is not None:
+        _need(ssq_in.dtype == torch.float32 and ssq_in.dim() == 2 and ssq_in.is_contiguous() and ssq_in.shape[1] >= M
+              and norm_size > 0, "ssq_in must be float32 [parts, M]")
+    f = _fn("gemm_tcgen05", "airun_gemm_tcgen05_ex",
             [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong,
-             c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
+             c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+             c_void_p, c_int, c_int, c_float, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_int])
     _check(f(_p(x), _p(w), _p(out), M, N, K, x.stride(0) if M > 1 else max(K, x.stride(0)),
              w.stride(0), out.stride(0) if M > 1 else max(out.shape[1], out.stride(0)),
-             epi, 1 if swap else 0, bn, ksplit, _p(scratch), _p(counters), _p(err), _stream()), "gemm_tcgen05")
+             epi, 1 if swap else 0, bn, ksplit, _p(scratch), _p(counters), _p(err), _stream(),
+             _p(ssq_in), ssq_in.shape[0] if ssq_in is not None else 0, ssq_in.shape[1] if ssq_in is not None else 0,
+             float(eps_in), int(norm_size), _p(resid), resid.stride(0) if resid is not None and M > 1 else N,
+             _p(norm_w), _p(ssq_out), ssq_out.shape[1] if ssq_out is not None else 0), "gemm_tcgen05")
 
 
 def plan_gemm(M: int, N: int, K: int) -> Tuple[bool, int, int]:
@@ -102,20 +127,54 @@ def _usable(x: torch.Tensor, w: torch.Tensor) -> bool:
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and x.shape[0] > 0)
 
 
-def linear_bf16(ctx, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
+def _normed_args(normed) -> dict:
+    return {} if normed is None else dict(ssq_in=normed.ssq, eps_in=normed.eps, norm_size=normed.size)
+
+
+def linear_bf16(ctx, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, normed=None) -> bool:
+    """``normed``: x is the un-normalised activation of a NormedActivations; its token scales are
+    applied in the epilogue."""
     if not _usable(x, w) or out.dtype not in (torch.float32, torch.bfloat16):
         return False
     swap, bn, ksplit = plan_gemm(x.shape[0], w.shape[0], x.shape[1])
-    gemm_tcgen05(x, w, out, EPI_F32 if out.dtype == torch.float32 else EPI_BF16, swap, bn, ksplit, ctx.err)
+    gemm_tcgen05(x, w, out, EPI_F32 if out.dtype == torch.float32 else EPI_BF16, swap, bn, ksplit, ctx.err,
+                 **_normed_args(normed))
     return True
 
 
-def linear_swiglu_bf16(ctx, x: torch.Tensor, w_gu: torch.Tensor, out: torch.Tensor, group: int) -> bool:
+def linear_swiglu_bf16(ctx, x: torch.Tensor, w_gu: torch.Tensor, out: torch.Tensor, group: int, normed=None) -> bool:
     if group != 16 or not _usable(x, w_gu) or w_gu.shape[0] % 32 != 0:
         return False
     swap, bn, ksplit = plan_gemm(x.shape[0], w_gu.shape[0], x.shape[1])
-    gemm_tcgen05(x, w_gu, out, EPI_SWIGLU, swap, bn, ksplit, ctx.err)
+    gemm_tcgen05(x, w_gu, out, EPI_SWIGLU, swap, bn, ksplit, ctx.err, **_normed_args(normed))
     return True
+
+
+# Folding the residual add and the RMSNorm into the products around them (EPI_RESID + token scales)
+# removes two launches per layer, but as measured on the Qwen3-8B shape the heavier epilogues cost
+# what the launches saved (decode) or more (prompt portions, whose epilogue accesses are strided),
+# so it is off unless AIRUN_NORM_FUSION=1; tests exercise it either way.
+NORM_FUSION = os.environ.get("AIRUN_NORM_FUSION", "") not in ("", "0")
+
+
+def fusion_usable(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Can the product x @ w^T end a sub-layer with the residual add and the next norm folded in?"""
+    return NORM_FUSION and _usable(x, w) and w.shape[0] % 8 == 0
+
+
+def linear_resid_norm_bf16(ctx, x: torch.Tensor, w: torch.Tensor, resid: torch.Tensor, norm_w: torch.Tensor,
+                           h_out: torch.Tensor, ssq_out: torch.Tensor) -> int:
+    """resid += x @ w^T; h_out = bfloat16(resid * norm_w); ssq_out[:parts] = sums of resid^2 per token.
+    Returns the number of parts written."""
+    M, K = x.shape
+    N = w.shape[0]
+    swap, bn, ksplit = plan_gemm(M, N, K)
+    gemm_tcgen05(x, w, h_out, EPI_RESID, swap, bn, ksplit, ctx.err, resid=resid, norm_w=norm_w, ssq_out=ssq_out)
+    return resid_parts(N, swap, bn)
+
+
+def max_resid_parts(N: int) -> int:
+    return 4 * ((N + 127) // 128)
 
 
 # ---------------------------------------------------------------- attention

@@ -20,11 +20,13 @@ import torch
 
 from ..kernels import ops
 from ..weights.loader import WeightSpec
-from .base import Mixer, PagedKVSpec, make_part, register_part
-from .linear import linear
+from .base import Mixer, NormedActivations, PagedKVSpec, make_part, register_part
+from .linear import linear, linear_into_residual
 
 
 class GQAAttention(Mixer):
+    fuses_norms = True        # takes NormedActivations as input and a ResidualSink for its output
+
     def __init__(self, prefix: str, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  scale: float, window: int = 0, qk_norm: bool = True, qk_norm_eps: float = 1e-6,
                  position: str = "rotary_neox", position_args: Optional[dict] = None,
@@ -71,8 +73,8 @@ class GQAAttention(Mixer):
         return PagedKVSpec(self.nkv, self.hd, self.window)
 
     # ---- compute ----
-    def forward(self, ctx, h: torch.Tensor, cache) -> torch.Tensor:
-        T = h.shape[0]
+    def forward(self, ctx, h, cache, sink=None):
+        T = h.h.shape[0] if isinstance(h, NormedActivations) else h.shape[0]
         ws = ctx.ws
         owns = not cache.shared
         width = (self.nh + 2 * self.nkv) * self.hd if owns else self.nh * self.hd
@@ -85,6 +87,9 @@ class GQAAttention(Mixer):
                      self.nh, self.nkv, self.hd, ctx.err, store=owns, kv_in_row=owns)
         attn = ws.alloc((T, self.nh * self.hd), self.dtype)
         self.attend(ctx, q, attn, cache)
+        fused = linear_into_residual(ctx, attn, self.w_o, sink)
+        if fused is not None:
+            return fused
         delta = ws.alloc((T, self.H), torch.float32)
         linear(ctx, attn, self.w_o, delta)
         return delta

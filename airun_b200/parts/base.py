@@ -20,6 +20,10 @@ PositionEncoding fused() -> (kind, rotary_dim, inv_freq) the attention prologue
 Mixer           cache_spec() -> PagedKVSpec | StateSpec | None
                 forward(ctx, h, cache) -> float32 [T, hidden] (the residual delta)
 FeedForward     forward(ctx, h) -> float32 [T, hidden]
+                Optional, for both: ``fuses_norms = True`` says that forward also takes
+                ``sink=ResidualSink`` (then it adds its result to the residual itself and returns
+                NormedActivations for the next sub-layer, or ignores the sink and returns a delta)
+                and accepts NormedActivations as ``h``.
 Block           forward(ctx, x, delta, cache) -> delta of the block's last sub-layer,
                   still to be added to x by whoever norms x next
 """
@@ -46,6 +50,27 @@ class StateSpec:
     """Per-request state of fixed size, zero when a request starts."""
     shape: Tuple[int, ...]
     dtype: torch.dtype = torch.float32
+
+
+@dataclass
+class NormedActivations:
+    """The input of a sub-layer whose RMSNorm has been folded into the products around it:
+    ``h`` = bfloat16(x * norm weight) without the 1/rms factor, and the sums of x^2 per token in
+    ``ssq`` [parts, T]; the product that reads ``h`` multiplies each token's results by
+    rsqrt(sum of parts / size + eps), which is the same as norming first."""
+    h: torch.Tensor
+    ssq: torch.Tensor
+    eps: float
+    size: int
+
+
+@dataclass
+class ResidualSink:
+    """Handed to the last product of a sub-layer that may fold the residual add and the norm that
+    follows: the residual stream ``x`` and that norm's weight and eps."""
+    x: torch.Tensor
+    norm_weight: torch.Tensor
+    eps: float
 
 
 class Part:

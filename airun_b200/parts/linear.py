@@ -12,11 +12,33 @@ import torch
 from ..kernels import ops
 
 
-def linear(ctx, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """out[T, N] = x[T, K] @ w[N, K]^T."""
+def linear(ctx, x, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[T, N] = x[T, K] @ w[N, K]^T.  ``x`` may be NormedActivations (see parts/base.py)."""
+    from .base import NormedActivations
+    if isinstance(x, NormedActivations):
+        from ..kernels import fast
+        if not fast.linear_bf16(ctx, x.h, w, out, normed=x):
+            raise RuntimeError("a folded norm reached a product the tensor-core kernel does not take")
+        return out
     if x.dtype == torch.bfloat16:
         from ..kernels import fast
         if fast.linear_bf16(ctx, x, w, out):
             return out
     ops.gemm_simt(x, w, out)
     return out
+
+
+def linear_into_residual(ctx, x: torch.Tensor, w: torch.Tensor, sink):
+    """The last product of a sub-layer with the residual add and the next norm folded in:
+    sink.x += x @ w^T, and the un-normalised input of the next sub-layer is returned as
+    NormedActivations.  Returns None when the tensor-core kernel does not take the sizes (the
+    caller then returns a plain delta)."""
+    from .base import NormedActivations
+    from ..kernels import fast
+    if sink is None or x.dtype != torch.bfloat16 or not fast.fusion_usable(x, w):
+        return None
+    T, N = x.shape[0], w.shape[0]
+    h = ctx.ws.alloc((T, N), torch.bfloat16)
+    ssq = ctx.ws.alloc((fast.max_resid_parts(N), T), torch.float32)
+    parts = fast.linear_resid_norm_bf16(ctx, x, w, sink.x[:T], sink.norm_weight, h, ssq)
+    return NormedActivations(h, ssq[:parts], sink.eps, N)

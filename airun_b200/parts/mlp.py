@@ -14,13 +14,15 @@ import torch
 
 from ..kernels import ops
 from ..weights.loader import WeightSpec
-from .base import FeedForward, register_part
-from .linear import linear
+from .base import FeedForward, NormedActivations, register_part
+from .linear import linear, linear_into_residual
 
 INTERLEAVE = 16
 
 
 class SwiGLU(FeedForward):
+    fuses_norms = True        # takes NormedActivations as input and a ResidualSink for its output
+
     def __init__(self, prefix: str, hidden_size: int, intermediate_size: int,
                  dtype: torch.dtype = torch.bfloat16, device=None, names: Optional[Dict[str, str]] = None):
         self.prefix, self.H, self.I = prefix, int(hidden_size), int(intermediate_size)
@@ -44,17 +46,22 @@ class SwiGLU(FeedForward):
             .reshape(2 * self.I, self.H).contiguous()
         self.w_down = tensors.pop(nm["down"])
 
-    def forward(self, ctx, h: torch.Tensor) -> torch.Tensor:
-        T, ws = h.shape[0], ctx.ws
+    def forward(self, ctx, h, sink=None):
+        normed = h if isinstance(h, NormedActivations) else None
+        hx = normed.h if normed is not None else h
+        T, ws = hx.shape[0], ctx.ws
         act = ws.alloc((T, self.I), self.dtype)
         done = False
-        if h.dtype == torch.bfloat16:
+        if hx.dtype == torch.bfloat16:
             from ..kernels import fast
-            done = fast.linear_swiglu_bf16(ctx, h, self.w_gu, act, self.group)
+            done = fast.linear_swiglu_bf16(ctx, hx, self.w_gu, act, self.group, normed=normed)
         if not done:
             gu = ws.alloc((T, 2 * self.I), torch.float32)
             linear(ctx, h, self.w_gu, gu)
             ops.swiglu(gu, act, self.group)
+        fused = linear_into_residual(ctx, act, self.w_down, sink)
+        if fused is not None:
+            return fused
         delta = ws.alloc((T, self.H), torch.float32)
         linear(ctx, act, self.w_down, delta)
         return delta

@@ -32,5 +32,9 @@ class RMSNorm(Norm):
     def forward(self, ctx, x, out, delta=None, rows=None) -> None:
         ops.rmsnorm(x, self.weight, self.eps, out, delta=delta, rows=rows)
 
+    def fusable(self):
+        """(weight, eps) for products that fold this norm in (out = x * rsqrt(mean x^2 + eps) * weight)."""
+        return self.weight, self.eps
+
 
 register_part("norm", "rmsnorm", RMSNorm)

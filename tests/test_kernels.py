@@ -179,6 +179,56 @@ def test_gemm_tcgen05_against_the_plain_kernel(M, N, K, epi, swap, bn, ksplit):
     assert torch.allclose(ref.cpu().double(), want64, rtol=1e-4, atol=1e-4)
 
 
+@pytest.mark.parametrize("M,N,K,swap,bn,ksplit", [(8, 256, 512, True, 16, 1), (5, 328, 1024, True, 16, 4),
+                                                   (40, 1024, 2048, True, 64, 3), (100, 264, 512, True, 128, 2),
+                                                   (300, 520, 256, False, 256, 1), (1000, 2304, 320, False, 256, 1),
+                                                   (200, 392, 512, False, 128, 2)])
+def test_gemm_tcgen05_folded_norm(M, N, K, swap, bn, ksplit):
+    """The product that ends a sub-layer adds into the residual and prepares the next norm; the
+    product that starts the next sub-layer applies the token scales: together they equal
+    add -> RMSNorm -> product."""
+    from airun_b200.kernels import fast
+    torch.manual_seed(8)
+    eps = 1e-5
+    act = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    w1 = (torch.randn(N, K, device=DEV) * 0.05).to(torch.bfloat16)
+    resid0 = torch.randn(M, N, device=DEV)
+    norm_w = (1 + 0.3 * torch.randn(N, device=DEV)).contiguous()
+    err = _err()
+    resid = resid0.clone()
+    h = torch.full((M, N), 3.0, dtype=torch.bfloat16, device=DEV)
+    ssq = torch.zeros(fast.max_resid_parts(N), M, device=DEV)
+    parts = fast.resid_parts(N, swap, bn)
+    for _ in range(2):                                           # counters come back to zero
+        resid.copy_(resid0)
+        fast.gemm_tcgen05(act, w1, h, fast.EPI_RESID, swap, bn, ksplit, err, resid=resid, norm_w=norm_w, ssq_out=ssq)
+        torch.cuda.synchronize()
+        assert err.item() == 0
+    want_resid = resid0.double() + act.double() @ w1.double().T
+    assert torch.allclose(resid.double(), want_resid, rtol=1e-4, atol=1e-4)
+    assert torch.allclose(h.double(), (resid.double() * norm_w.double()), rtol=1e-2, atol=1e-2)
+    assert torch.allclose(ssq[:parts].sum(0).double(), (want_resid ** 2).sum(1), rtol=1e-4)
+    # the consumer: scales from the parts, float32 and SwiGLU epilogues, both modes
+    N2 = 320
+    w2 = (torch.randn(N2, N, device=DEV) * 0.05).to(torch.bfloat16)
+    normed = want_resid * torch.rsqrt((want_resid ** 2).mean(1, keepdim=True) + eps) * norm_w.double()
+    want = normed @ w2.double().T
+    for (swap2, bn2, ks2) in ((True, 128 if M > 64 else 64 if M > 16 else 16, 2), (False, 256, 1), (False, 128, 1)):
+        if swap2 and M > 128:
+            continue
+        out = torch.zeros(M, N2, device=DEV)
+        fast.gemm_tcgen05(h, w2, out, fast.EPI_F32, swap2, bn2, ks2, err, ssq_in=ssq[:parts], eps_in=eps, norm_size=N)
+        torch.cuda.synchronize()
+        assert err.item() == 0
+        assert torch.allclose(out.double(), want, rtol=2e-2, atol=2e-2 * float(want.abs().max())), (swap2, bn2)
+        g = want.view(M, N2 // 32, 2, 16)
+        want_act = (g[:, :, 0] / (1 + torch.exp(-g[:, :, 0])) * g[:, :, 1]).reshape(M, N2 // 2)
+        out2 = torch.zeros(M, N2 // 2, dtype=torch.bfloat16, device=DEV)
+        fast.gemm_tcgen05(h, w2, out2, fast.EPI_SWIGLU, swap2, bn2, ks2, err, ssq_in=ssq[:parts], eps_in=eps, norm_size=N)
+        torch.cuda.synchronize()
+        assert torch.allclose(out2.double(), want_act, rtol=3e-2, atol=3e-2 * float(want_act.abs().max())), (swap2, bn2)
+
+
 def test_gemm_tcgen05_refuses_what_it_cannot_take():
     from airun_b200.kernels import fast
     from airun_b200.kernels.ops import KernelError

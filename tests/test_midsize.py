@@ -110,3 +110,32 @@ def test_greedy_generation_in_a_batch_picks_defensible_tokens(engines):
             gap = float(outs["b"][t].max() - outs["b"][t][tok])
             assert gap <= 2 * noise + 1e-3, (i, t, gap, noise)
     assert e16.manager.free_pages() == {gr.gid: e16.manager.num_pages for gr in e16.manager.paged}
+
+
+def test_folded_norms_give_the_same_logits(engines):
+    """RMSNorm folded into the products around it (off by default) against the separate kernels."""
+    from airun_b200.kernels import fast
+    eng = engines["bfloat16"]
+    g = np.random.default_rng(9)
+    a = [int(t) for t in g.integers(0, MID["vocab_size"], size=400)]
+    b = [int(t) for t in g.integers(0, MID["vocab_size"], size=37)]
+    plan = [[("a", a[:390]), ("b", b[:30])]] + [[("a", [a[390 + i]]), ("b", [b[30 + i]])] for i in range(7)]
+    plain = logits_of(eng, plan)
+    ref = logits_of(engines["float32"], plan)
+    old = fast.NORM_FUSION
+    fast.NORM_FUSION = True
+    saved = (dict(eng.runner.graphs), set(eng.runner._warm_buckets))
+    eng.runner.graphs.clear()
+    eng.runner._warm_buckets.clear()                 # graphs captured without the fusion must not be replayed
+    try:
+        fused = logits_of(eng, plan)
+    finally:
+        fast.NORM_FUSION = old
+        eng.runner.graphs.clear()
+        eng.runner._warm_buckets.clear()
+        eng.runner.graphs.update(saved[0])
+        eng.runner._warm_buckets.update(saved[1])
+    for rid in ("a", "b"):
+        noise = float(np.abs(plain[rid] - ref[rid]).max())
+        assert float(np.abs(fused[rid] - plain[rid]).max()) <= noise + 1e-3, rid
+        assert float(np.abs(fused[rid] - plain[rid]).max()) > 0.0      # it really took the other path
