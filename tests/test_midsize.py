@@ -139,3 +139,36 @@ def test_folded_norms_give_the_same_logits(engines):
         noise = float(np.abs(plain[rid] - ref[rid]).max())
         assert float(np.abs(fused[rid] - plain[rid]).max()) <= noise + 1e-3, rid
         assert float(np.abs(fused[rid] - plain[rid]).max()) > 0.0      # it really took the other path
+
+
+def test_long_context_in_portions_then_decoding():
+    """Five thousand tokens in portions of 1024, then single tokens: block tables of hundreds of
+    pages, positions in the thousands, many key tiles and several key slices per token."""
+    import airun_b200
+    cfg = airun_b200.Qwen3Config.from_dict(dict(MID, num_hidden_layers=2, vocab_size=5000))
+    g = np.random.default_rng(11)
+    seq = [int(t) for t in g.integers(0, 5000, size=5030)]
+    want_at = [1023, 2047, 4095, 4999]                        # ends of portions, the page edge at 4096
+    outs = {}
+    for dt in ("float32", "bfloat16"):
+        eng = airun_b200.Engine.from_config(cfg, seed=4, dtype=dt, page_size=16, cache_tokens=5120,
+                                            max_batch_tokens=1024, max_requests=2, max_context=5120)
+        from airun_b200 import StepEntry
+        eng.manager.add_request("r")
+        rows = []
+        for p0 in range(0, 5000, 1024):
+            part = seq[p0:min(p0 + 1024, 5000)]
+            want = tuple(w - p0 for w in want_at if p0 <= w < p0 + len(part))
+            out = eng.runner.step([StepEntry("r", part, want)])
+            if want:
+                rows.append(out.float().cpu().numpy())
+        for t in seq[5000:]:
+            rows.append(eng.runner.step([StepEntry("r", [t], (0,))]).float().cpu().numpy())
+        eng.runner.raise_on_device_error()
+        outs[dt] = np.concatenate(rows)
+        del eng
+        torch.cuda.empty_cache()
+    assert outs["float32"].shape == (len(want_at) + 30, 5000)
+    for i in range(outs["float32"].shape[0]):
+        assert cosine(outs["float32"][i], outs["bfloat16"][i]) > 0.999, i
+    assert np.mean(outs["float32"].argmax(-1) == outs["bfloat16"].argmax(-1)) > 0.9
