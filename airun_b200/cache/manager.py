@@ -18,6 +18,13 @@ with pages:
   runs the tokens that need them, and given back when the request ends or, in a
   group with a window, when every key of the page lies behind the window of all
   tokens still to come; a freed page is the next one handed out.
+* Pages may be shared: ``fork`` gives a child request the parent's pages with one more holder
+  each, and ``truncate`` moves a request's end back.  A page that more than one table holds is
+  never written: the page a request writes next is its own, which ``fork`` and ``truncate`` see
+  to by handing out a fresh page and telling the caller which page to copy into it.  (The
+  reference rewinds a slot by moving its cursor, crates/airun-core/src/runtime.rs:3280-3308, and
+  reuses the common prefix of a slot's history, runtime.rs:3256-3273; with pages the same prefix
+  can serve several live requests at once.)
 * State groups hold ``[max_requests, *shape]`` per owner; a request gets a slot
   at admission (the caller zero-fills it) and returns it at the end.
 
@@ -112,6 +119,14 @@ class RequestCache:
     num_tokens: int = 0                                  # tokens whose cache content is final
     reserved: int = 0                                    # tokens pages are held for (>= num_tokens)
     blocks: Dict[int, List[int]] = field(default_factory=dict)   # gid -> page id per block, -1 = given back
+
+
+@dataclass
+class CopyPlan:
+    """Device copies that make a fork or a cut-back true: whole pages ``(gid, src, dst)`` in every
+    layer of their group, and the state of request slot ``state[0]`` into slot ``state[1]``."""
+    pages: List[Tuple[int, int, int]] = field(default_factory=list)
+    state: Optional[Tuple[int, int]] = None
 
 
 @dataclass(frozen=True)
@@ -249,6 +264,84 @@ class CacheManager:
             self.tables[g.gid][rc.slot, :min(len(rc.blocks[g.gid]), self.max_blocks)] = -1
         self._free_slots.append(rc.slot)
 
+    # ------------------------------------------------------------ sharing and rewinding
+    def fork(self, parent: Hashable, child: Hashable) -> "CopyPlan":
+        """Makes ``child`` a live request holding the same ``num_tokens`` tokens as ``parent``.
+        Whole pages are shared (one more holder); a last page that is only partly filled is the
+        place both would write next, so the child gets a fresh one.  Returns the copies the caller
+        has to run on the device before the child's first step: pages ``(gid, src, dst)`` and the
+        state slot.  Takes everything or, if pages or slots are short, nothing."""
+        prc = self.get(parent)
+        if child in self.requests:
+            raise CacheError(f"request {child!r} is already live")
+        if not self._free_slots:
+            raise CacheError(f"all {self.max_requests} request slots are in use")
+        n = prc.num_tokens
+        full, part = divmod(n, self.page_size)
+        for g in self.paged:
+            if part and prc.blocks[g.gid][full] >= 0 and g.allocator.num_free < 1:
+                raise OutOfPages(f"forking {parent!r} needs a page in group {g.gid}, none is free")
+        crc = RequestCache(child, self._free_slots.pop(), num_tokens=n, reserved=n,
+                           blocks={g.gid: [] for g in self.paged})
+        plan = CopyPlan(state=(prc.slot, crc.slot) if self.state else None)
+        for g in self.paged:
+            src = prc.blocks[g.gid]
+            blocks = list(src[:full])
+            for p in blocks:
+                if p >= 0:
+                    g.allocator.share(p)
+            if part:
+                if src[full] >= 0:
+                    new = g.allocator.take(1)[0]
+                    plan.pages.append((g.gid, src[full], new))
+                    blocks.append(new)
+                else:
+                    blocks.append(-1)
+            crc.blocks[g.gid] = blocks
+            self.tables[g.gid][crc.slot, :min(len(blocks), self.max_blocks)] = blocks[:self.max_blocks]
+        self.requests[child] = crc
+        return plan
+
+    def truncate(self, rid: Hashable, n_tokens: int) -> "CopyPlan":
+        """Moves the end of ``rid`` back to ``n_tokens``: pages wholly past it are given back, and
+        if the page that is written next has other holders the request gets a copy of its own
+        (returned for the caller to run on the device).  Fixed-size state cannot be moved back, and
+        neither can a window whose pages are gone."""
+        rc = self.get(rid)
+        if not (0 <= n_tokens <= rc.num_tokens):
+            raise CacheError(f"request {rid!r} holds {rc.num_tokens} tokens and cannot be cut to {n_tokens}")
+        if n_tokens == rc.num_tokens and rc.reserved == rc.num_tokens:
+            return CopyPlan()
+        if self.state and n_tokens < rc.num_tokens:
+            raise CacheError("a request with fixed-size state cannot be moved back, only restarted")
+        full, part = divmod(n_tokens, self.page_size)
+        for g in self.paged:
+            blocks = rc.blocks[g.gid]
+            if g.window > 0 and n_tokens > 0:
+                first_needed = max(0, n_tokens - g.window + 1) // self.page_size
+                if first_needed < len(blocks) and blocks[first_needed] < 0:
+                    raise CacheError(f"request {rid!r}: the window's pages before token {n_tokens} were given back")
+            if part and blocks[full] >= 0 and g.allocator.holders(blocks[full]) > 1 and g.allocator.num_free < 1:
+                raise OutOfPages(f"cutting {rid!r} inside a shared page needs a page in group {g.gid}")
+        plan = CopyPlan()
+        keep = full + (1 if part else 0)
+        for g in self.paged:
+            blocks = rc.blocks[g.gid]
+            for p in blocks[keep:]:
+                if p >= 0:
+                    g.allocator.give_back(p)
+            self.tables[g.gid][rc.slot, keep:min(len(blocks), self.max_blocks)] = -1
+            del blocks[keep:]
+            if part and blocks[full] >= 0 and g.allocator.holders(blocks[full]) > 1:
+                new = g.allocator.take(1)[0]
+                plan.pages.append((g.gid, blocks[full], new))
+                g.allocator.give_back(blocks[full])
+                blocks[full] = new
+                if full < self.max_blocks:
+                    self.tables[g.gid][rc.slot, full] = new
+        rc.num_tokens = rc.reserved = n_tokens
+        return plan
+
     # ------------------------------------------------------------ views
     def block_table(self, rid: Hashable, gid: int) -> List[int]:
         return self.get(rid).blocks[gid]
@@ -281,6 +374,13 @@ class CacheManager:
                                      f"{g.allocator.holders(p)} holders")
             if len(free) + len(seen) != g.allocator.num_pages:
                 raise CacheError(f"group {g.gid}: {g.allocator.num_pages - len(free) - len(seen)} pages are lost")
+            for rc in self.requests.values():
+                b = rc.num_tokens // self.page_size
+                blocks = rc.blocks[g.gid]
+                for p in blocks[b:]:
+                    if p >= 0 and g.allocator.holders(p) != 1:
+                        raise CacheError(f"group {g.gid}: request {rc.rid!r} would write page {p}, which "
+                                         f"{g.allocator.holders(p)} tables hold")
         slots = [rc.slot for rc in self.requests.values()]
         if len(set(slots)) != len(slots) or set(slots) & set(self._free_slots):
             raise CacheError("a request slot is held twice")
@@ -302,6 +402,14 @@ class CacheStorage:
     def zero_state_slot(self, slot: int) -> None:
         for t in self.state:
             t[:, slot].zero_()
+
+    def run_copies(self, plan: CopyPlan) -> None:
+        """Runs the copies of a fork or cut-back on the current stream."""
+        for gid, src, dst in plan.pages:
+            self.paged[gid][:, dst].copy_(self.paged[gid][:, src])
+        if plan.state is not None:
+            for t in self.state:
+                t[:, plan.state[1]].copy_(t[:, plan.state[0]])
 
     def bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in self.paged + self.state)

@@ -135,9 +135,12 @@ __device__ __forceinline__ const __nv_bfloat16* key_row(const AttnParams& p, con
 
 struct PrefillTile { int req, tok0, n_tok, first_row; };   // tokens [tok0, tok0+n_tok) of the batch, all of request req
 
-__global__ __launch_bounds__(PTHREADS, 2) void attn_prefill_kernel(const AttnParams p, const int4* __restrict__ tiles) {
+// n_tiles_dev: null, or the number of tiles another kernel has written (the grid may be larger)
+__global__ __launch_bounds__(PTHREADS, 2) void attn_prefill_kernel(const AttnParams p, const int4* __restrict__ tiles,
+                                                                   const int* __restrict__ n_tiles_dev) {
     pdl_trigger();
     pdl_wait();
+    if (n_tiles_dev && (int)blockIdx.x >= *n_tiles_dev) return;
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t* sQ = smem;                               // [PM][HD]
     uint8_t* sK = sQ + PM * HD * 2;                   // [2][PN][HD]
@@ -300,6 +303,9 @@ struct DecodeExtra {
     int n_splits;
     float* scratch;             // [n][nkv*hgroups][n_splits][16][HD + 2]
     int* counters;              // [n][nkv*hgroups], zero between launches
+    const int32_t* n_rows_dev;  // null, or: the rows in use are read on the device (the grid may be larger) and
+    int dyn_slots;              //   every row picks its own number of slices, at most n_splits, so that about
+                                //   dyn_slots CTAs run and a slice has 128 keys or more
 };
 
 // TMA = true: K/V tiles arrive by cp.async.bulk.tensor (one lane of each warp issues HD/64 boxes per
@@ -330,6 +336,8 @@ __global__ __launch_bounds__(32 * DW) void attn_decode_kernel(const AttnParams p
     const int split = blockIdx.x;
     const int hgroups = (p.G + 15) / 16;
     const int kvh = blockIdx.y / hgroups, hg = blockIdx.y - kvh * hgroups;
+    const int n_rows_used = x.n_rows_dev ? *x.n_rows_dev : (int)gridDim.z;
+    if ((int)blockIdx.z >= n_rows_used) return;
     const int tok = x.rows ? x.rows[blockIdx.z] : (int)blockIdx.z;     // no list: row i is token i
     const int pos = p.positions[tok];
     const int req = p.req_of_token[tok];
@@ -338,6 +346,16 @@ __global__ __launch_bounds__(32 * DW) void attn_decode_kernel(const AttnParams p
     const bool live = req >= 0 && req < p.num_reqs && pos >= 0;
     const int32_t* bt = p.block_table + (size_t)(live ? req : 0) * p.max_blocks;
     const size_t v_off = (size_t)p.nkv * p.page_size * HD;
+    const int k_first = live ? (p.window > 0 ? max(0, pos - p.window + 1) : 0) : 0;
+    const int tile_first = k_first / DN;
+    const int n_tiles_all = live ? pos / DN - tile_first + 1 : 0;
+    int ns = x.n_splits, ns_stride = x.n_splits;       // slices of this row; slices the scratch has room for
+    if (x.n_rows_dev) {
+        const int fit = max(1, x.dyn_slots / max(1, n_rows_used * (int)gridDim.y));
+        ns_stride = min(x.n_splits, fit);
+        ns = max(1, min(ns_stride, (n_tiles_all + 7) / 8));
+        if (split >= ns) return;
+    }
 
     // Q rows -> shared memory (rows >= heads are zero)
     for (int i = threadIdx.x; i < 16 * CHUNKS; i += 32 * DW) {
@@ -348,10 +366,7 @@ __global__ __launch_bounds__(32 * DW) void attn_decode_kernel(const AttnParams p
     cp_commit();
 
     // key tiles of this token, this slice, this warp
-    const int k_first = live ? (p.window > 0 ? max(0, pos - p.window + 1) : 0) : 0;
-    const int tile_first = k_first / DN;
-    const int n_tiles_all = live ? pos / DN - tile_first + 1 : 0;
-    const int per_split = (n_tiles_all + x.n_splits - 1) / x.n_splits;
+    const int per_split = (n_tiles_all + ns - 1) / ns;
     const int tb = tile_first + split * per_split;
     const int te = min(tile_first + n_tiles_all, tb + per_split);
     const int my_n = te > tb + warp ? (te - tb - warp + DW - 1) / DW : 0;      // tiles tb+warp, tb+warp+DW, ...
@@ -518,7 +533,7 @@ __global__ __launch_bounds__(32 * DW) void attn_decode_kernel(const AttnParams p
     __syncthreads();
     // thread i handles element(s) (row, d): row = e / HD
     const int unit = blockIdx.z * gridDim.y + blockIdx.y;
-    float* part = x.n_splits > 1 ? x.scratch + ((size_t)unit * x.n_splits + split) * (16 * (HD + 2)) : nullptr;
+    float* part = ns > 1 ? x.scratch + ((size_t)unit * ns_stride + split) * (16 * (HD + 2)) : nullptr;
     for (int e = threadIdx.x; e < heads * HD; e += 32 * DW) {
         const int r = e / HD, d = e - r * HD;
         float gm = NEG_BIG;
@@ -543,17 +558,17 @@ __global__ __launch_bounds__(32 * DW) void attn_decode_kernel(const AttnParams p
     __syncthreads();
     if (threadIdx.x == 0) s_ticket = atomicAdd(x.counters + unit, 1);
     __syncthreads();
-    if (s_ticket != x.n_splits - 1) return;
+    if (s_ticket != ns - 1) return;
     __threadfence();
     if (threadIdx.x == 0) x.counters[unit] = 0;
     // The last CTA of this token and head group merges the slices, in slice order.  The loads of
     // several slices and elements are issued together: this part runs alone, so what it costs is
     // the number of dependent round trips to the L2 cache.
-    const float* all = x.scratch + (size_t)unit * x.n_splits * (16 * (HD + 2));
+    const float* all = x.scratch + (size_t)unit * ns_stride * (16 * (HD + 2));
     __shared__ float s_f[MAX_SPLITS][16];
     __shared__ float s_l2[MAX_SPLITS][16];
     __shared__ float s_inv[16];
-    for (int i = threadIdx.x; i < x.n_splits * 16; i += 32 * DW) {
+    for (int i = threadIdx.x; i < ns * 16; i += 32 * DW) {
         const int sp = i >> 4, r = i & 15;
         const float* ps = all + (size_t)sp * 16 * (HD + 2) + r * (HD + 2);
         s_f[sp][r] = r < heads ? __ldcg(ps) : NEG_BIG;          // the slice's maximum
@@ -563,9 +578,9 @@ __global__ __launch_bounds__(32 * DW) void attn_decode_kernel(const AttnParams p
     if (threadIdx.x < heads) {
         const int r = threadIdx.x;
         float gm = NEG_BIG;
-        for (int sp = 0; sp < x.n_splits; ++sp) gm = fmaxf(gm, s_f[sp][r]);
+        for (int sp = 0; sp < ns; ++sp) gm = fmaxf(gm, s_f[sp][r]);
         float sum = 0.0f;
-        for (int sp = 0; sp < x.n_splits; ++sp) {
+        for (int sp = 0; sp < ns; ++sp) {
             const float l = s_l2[sp][r];
             const float f = l > 0.0f ? exp2f(s_f[sp][r] - gm) : 0.0f;
             s_f[sp][r] = f;
@@ -580,7 +595,7 @@ __global__ __launch_bounds__(32 * DW) void attn_decode_kernel(const AttnParams p
         float acc[EG];
 #pragma unroll
         for (int k = 0; k < EG; ++k) acc[k] = 0.0f;
-        for (int s0 = 0; s0 < x.n_splits; s0 += SG) {
+        for (int s0 = 0; s0 < ns; s0 += SG) {
             float v[EG][SG];
 #pragma unroll
             for (int k = 0; k < EG; ++k) {
@@ -588,7 +603,7 @@ __global__ __launch_bounds__(32 * DW) void attn_decode_kernel(const AttnParams p
                 const int r = e / HD, d = e - r * HD;
 #pragma unroll
                 for (int j = 0; j < SG; ++j)
-                    v[k][j] = (e < total && s0 + j < x.n_splits)
+                    v[k][j] = (e < total && s0 + j < ns)
                                   ? __ldcg(all + (size_t)(s0 + j) * 16 * (HD + 2) + r * (HD + 2) + 2 + d) : 0.0f;
             }
 #pragma unroll
@@ -597,7 +612,7 @@ __global__ __launch_bounds__(32 * DW) void attn_decode_kernel(const AttnParams p
                 const int r = e < total ? e / HD : 0;
 #pragma unroll
                 for (int j = 0; j < SG; ++j)
-                    if (s0 + j < x.n_splits) acc[k] = fmaf(v[k][j], s_f[s0 + j][r], acc[k]);
+                    if (s0 + j < ns) acc[k] = fmaf(v[k][j], s_f[s0 + j][r], acc[k]);
             }
         }
 #pragma unroll
@@ -668,11 +683,13 @@ AIRUN_EXPORT int airun_attn_head_dim() { return HD; }
 // Tokens per prefill tile for a group of G heads.
 AIRUN_EXPORT int airun_attn_prefill_tokens_per_tile(int G) { return G > 0 && G <= PM ? PM / G : 0; }
 
-// tiles: [n_tiles] int4 {request, first token row, token count (<= PM / G), 0}
+// tiles: [n_tiles] int4 {request, first token row, token count (<= PM / G), 0}.  With n_tiles_dev the
+// grid has n_tiles CTAs and those from *n_tiles_dev on (read on the device) leave at once.
 AIRUN_EXPORT int airun_attn_prefill(const void* q, void* out, const void* pool, const int32_t* block_table,
                                     int max_blocks, const int32_t* positions, const int32_t* req_of_token,
                                     int num_reqs, int num_pages, int page_size, int nh, int nkv, float scale,
-                                    int window, const void* tiles, int n_tiles, int* err, cudaStream_t stream) {
+                                    int window, const void* tiles, int n_tiles, const int32_t* n_tiles_dev,
+                                    int* err, cudaStream_t stream) {
     if (n_tiles < 0 || nh <= 0 || nkv <= 0 || nh % nkv != 0 || nh / nkv > PM || page_size <= 0 || !err) return AIRUN_ERR_ARG;
     if (n_tiles == 0) return AIRUN_OK;
     if (nkv > 65535) return AIRUN_ERR_ARG;
@@ -685,7 +702,7 @@ AIRUN_EXPORT int airun_attn_prefill(const void* q, void* out, const void* pool, 
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    airun_launch(attn_prefill_kernel, dim3(n_tiles, nkv), dim3(PTHREADS), smem, stream, p, (const int4*)tiles);
+    airun_launch(attn_prefill_kernel, dim3(n_tiles, nkv), dim3(PTHREADS), smem, stream, p, (const int4*)tiles, n_tiles_dev);
     return airun_launch_status();
 }
 
@@ -695,11 +712,16 @@ AIRUN_EXPORT long long airun_attn_decode_scratch_floats(int n_rows, int nh, int 
 }
 
 // rows: [n_rows] batch rows (one decoded token each).  counters: [n_rows * nkv * hgroups] ints, zero on entry.
+// With n_rows_dev the grid is made for n_rows rows and n_splits slices, but only the first *n_rows_dev rows
+// (read on the device) are run, each with its own number of slices (see DecodeExtra); the scratch then needs
+// min(n_splits, dyn_slots / (rows x head groups), at least 1) slices per row and head group.
 AIRUN_EXPORT int airun_attn_decode(const void* q, void* out, const void* pool, const int32_t* block_table,
                                    int max_blocks, const int32_t* positions, const int32_t* req_of_token,
                                    int num_reqs, int num_pages, int page_size, int nh, int nkv, float scale,
                                    int window, const int32_t* rows, int n_rows, int n_splits, float* scratch,
-                                   int* counters, int* err, cudaStream_t stream) {
+                                   int* counters, const int32_t* n_rows_dev, int dyn_slots, int* err,
+                                   cudaStream_t stream) {
+    if (n_rows_dev && (dyn_slots <= 0 || !rows)) return AIRUN_ERR_ARG;
     if (n_rows < 0 || nh <= 0 || nkv <= 0 || nh % nkv != 0 || page_size <= 0 || n_splits < 1 || n_splits > MAX_SPLITS || !err) return AIRUN_ERR_ARG;
     if (n_splits > 1 && (!scratch || !counters)) return AIRUN_ERR_ARG;
     if (n_rows == 0) return AIRUN_OK;
@@ -707,7 +729,7 @@ AIRUN_EXPORT int airun_attn_decode(const void* q, void* out, const void* pool, c
     if (nkv * hgroups > 65535 || n_rows > 65535) return AIRUN_ERR_ARG;
     const AttnParams p = make_params(q, out, pool, block_table, max_blocks, positions, req_of_token, num_reqs,
                                      num_pages, page_size, nh, nkv, scale, window, err);
-    DecodeExtra x{rows, n_splits, scratch, counters};
+    DecodeExtra x{rows, n_splits, scratch, counters, n_rows_dev, dyn_slots};
     // TMA needs whole 16-key tiles inside one page and 128-byte boxes
     static const bool tma_allowed = !(getenv("AIRUN_ATTN_TMA") && getenv("AIRUN_ATTN_TMA")[0] == '0');
     const bool tma = tma_allowed && (HD % 64 == 0) && p.page_shift >= 4 && encode_fn() != nullptr;

@@ -213,7 +213,8 @@ constexpr int SMEM_TOTAL = OFF_BAR + N_BARS * 8 + 64 + 1024;
 enum { B_KFULL = 0, B_KEMPTY = 2, B_VFULL = 4, B_VEMPTY = 6, B_SFULL = 8, B_SFREE = 10, B_PFULL = 12, B_OFULL = 13, B_OFREE = 14, B_XM = 15 };
 
 __global__ __launch_bounds__(TC_THREADS, 1) void attn_prefill_tc_kernel(
-    const TcParams p, const int4* __restrict__ tiles, const __grid_constant__ CUtensorMap kv_map) {
+    const TcParams p, const int4* __restrict__ tiles, const __grid_constant__ CUtensorMap kv_map,
+    const int* __restrict__ n_tiles_dev) {
     pdl_trigger();
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -240,6 +241,15 @@ __global__ __launch_bounds__(TC_THREADS, 1) void attn_prefill_tc_kernel(
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     pdl_wait();
+    if (n_tiles_dev && (int)blockIdx.x >= *n_tiles_dev) {       // a CTA beyond the tiles in use: nothing to do
+        tc_fence_before();
+        __syncthreads();
+        if (warp == 1) {
+            tc_fence_after();
+            tmem_dealloc(tmem_base, 512);
+        }
+        return;
+    }
 
     const int4 t4 = tiles[blockIdx.x];
     const int req = t4.x, tok0 = t4.y, n_tok = t4.z;
@@ -539,11 +549,12 @@ int kv_map_for(CUtensorMap* out, const void* pool, long long rows) {
 AIRUN_EXPORT int airun_attn_tc_head_dim() { return HD; }
 
 // tiles: [n_tiles] int4 {request, first token row, token count (<= 128 / G), -}.  Pages must be a
-// power of two >= 16 tokens; G = nh / nkv <= 128.
+// power of two >= 16 tokens; G = nh / nkv <= 128.  With n_tiles_dev the grid has n_tiles CTAs and
+// those from *n_tiles_dev on (read on the device) leave at once.
 AIRUN_EXPORT int airun_attn_prefill_tc(const void* q, void* out, const void* pool, const int32_t* block_table,
                                        int max_blocks, const int32_t* positions, int num_pages, int page_size,
                                        int nh, int nkv, float scale, int window, const void* tiles, int n_tiles,
-                                       int* err, cudaStream_t stream) {
+                                       const int32_t* n_tiles_dev, int* err, cudaStream_t stream) {
     if (n_tiles < 0 || nh <= 0 || nkv <= 0 || nh % nkv != 0 || nh / nkv > QM || !err) return AIRUN_ERR_ARG;
     int shift = -1;
     for (int s = 4; s < 20; ++s) if ((1 << s) == page_size) shift = s;
@@ -563,6 +574,6 @@ AIRUN_EXPORT int airun_attn_prefill_tc(const void* q, void* out, const void* poo
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    airun_launch(attn_prefill_tc_kernel, dim3(n_tiles, nkv), dim3(TC_THREADS), SMEM_TOTAL, stream, p, (const int4*)tiles, map);
+    airun_launch(attn_prefill_tc_kernel, dim3(n_tiles, nkv), dim3(TC_THREADS), SMEM_TOTAL, stream, p, (const int4*)tiles, map, n_tiles_dev);
     return airun_launch_status();
 }

@@ -109,8 +109,11 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ 
     }
 }
 
-// Many rows: one warp per row, no block-wide synchronisation, 32 float4 loads in flight per lane
-// group.  The sum x + delta is written first and read back (from cache) for the second pass.
+// Many rows: one warp per row, no block-wide synchronisation.  The loads of a batch of RB float4 per
+// lane (and as many of delta) are all issued before the first of them is used or anything is stored:
+// a load after a store through the same pointer would otherwise wait for it.  The sum x + delta is
+// written back and read again (from cache) for the second pass.
+#define RB 8
 template <typename TOut>
 __global__ __launch_bounds__(256) void rmsnorm_rows_kernel(float* __restrict__ x, const float* __restrict__ delta,
                                                            const float* __restrict__ w, TOut* __restrict__ out,
@@ -127,30 +130,60 @@ __global__ __launch_bounds__(256) void rmsnorm_rows_kernel(float* __restrict__ x
     const int nv = n >> 2;
     float ss = 0.0f;
     const bool rewrite = dr && write_back;
-    for (int i = lane; i < nv; i += 32) {
-        float4 v = xr[i];
-        if (dr) {
-            const float4 d = dr[i];
-            v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
-            if (rewrite) xr[i] = v;
+    for (int i0 = lane; i0 < nv; i0 += 32 * RB) {
+        float4 v[RB], d[RB];
+#pragma unroll
+        for (int u = 0; u < RB; ++u) {
+            const int i = i0 + 32 * u;
+            v[u] = i < nv ? xr[i] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
         }
-        ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
+        if (dr) {
+#pragma unroll
+            for (int u = 0; u < RB; ++u) {
+                const int i = i0 + 32 * u;
+                d[u] = i < nv ? dr[i] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            }
+#pragma unroll
+            for (int u = 0; u < RB; ++u) { v[u].x += d[u].x; v[u].y += d[u].y; v[u].z += d[u].z; v[u].w += d[u].w; }
+        }
+#pragma unroll
+        for (int u = 0; u < RB; ++u) {
+            const int i = i0 + 32 * u;
+            if (rewrite && i < nv) xr[i] = v[u];
+            ss = fmaf(v[u].x, v[u].x, fmaf(v[u].y, v[u].y, fmaf(v[u].z, v[u].z, fmaf(v[u].w, v[u].w, ss))));
+        }
     }
     ss = warp_sum(ss);
     const float inv = rsqrtf(ss / (float)n + eps);
-    for (int i = lane; i < nv; i += 32) {
-        float4 v = xr[i];
-        if (dr && !rewrite) { const float4 d = dr[i]; v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w; }
-        const float4 g = w ? w4[i] : make_float4(1.0f, 1.0f, 1.0f, 1.0f);
-        const float a = v.x * inv * g.x, b = v.y * inv * g.y, c = v.z * inv * g.z, d2 = v.w * inv * g.w;
-        if (sizeof(TOut) == 4) {
-            reinterpret_cast<float4*>(outr)[i] = make_float4(a, b, c, d2);
-        } else {
-            __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d2);
-            uint2 pk;
-            pk.x = *reinterpret_cast<uint32_t*>(&lo);
-            pk.y = *reinterpret_cast<uint32_t*>(&hi);
-            reinterpret_cast<uint2*>(outr)[i] = pk;
+    for (int i0 = lane; i0 < nv; i0 += 32 * RB) {
+        float4 v[RB], g[RB];
+#pragma unroll
+        for (int u = 0; u < RB; ++u) {
+            const int i = i0 + 32 * u;
+            v[u] = i < nv ? xr[i] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            g[u] = (w && i < nv) ? w4[i] : make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+        }
+        if (dr && !rewrite) {
+#pragma unroll
+            for (int u = 0; u < RB; ++u) {
+                const int i = i0 + 32 * u;
+                if (i < nv) { const float4 d = dr[i]; v[u].x += d.x; v[u].y += d.y; v[u].z += d.z; v[u].w += d.w; }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < RB; ++u) {
+            const int i = i0 + 32 * u;
+            if (i >= nv) continue;
+            const float a = v[u].x * inv * g[u].x, b = v[u].y * inv * g[u].y, c = v[u].z * inv * g[u].z, d2 = v[u].w * inv * g[u].w;
+            if (sizeof(TOut) == 4) {
+                reinterpret_cast<float4*>(outr)[i] = make_float4(a, b, c, d2);
+            } else {
+                __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d2);
+                uint2 pk;
+                pk.x = *reinterpret_cast<uint32_t*>(&lo);
+                pk.y = *reinterpret_cast<uint32_t*>(&hi);
+                reinterpret_cast<uint2*>(outr)[i] = pk;
+            }
         }
     }
 }
@@ -162,12 +195,14 @@ AIRUN_EXPORT int airun_rmsnorm(float* x, const float* delta, const float* w, voi
     if (rows && write_back) return AIRUN_ERR_ARG;
     if (n_rows == 0) return AIRUN_OK;
     const bool vec = n % 4 == 0 && (((uintptr_t)x | (uintptr_t)delta) & 15) == 0;
-    if (vec && !rows && n_rows >= 512 && n >= 512 && (((uintptr_t)out | (uintptr_t)w) & 15) == 0) {
-        const int blocks = (n_rows + 7) / 8;
+    if (vec && !rows && n_rows >= 256 && n >= 512 && (((uintptr_t)out | (uintptr_t)w) & 15) == 0) {
+        // enough warps per block that the blocks still cover the SMs twice
+        const int wpb = n_rows >= 2368 ? 8 : n_rows >= 1184 ? 4 : 2;
+        const int blocks = (n_rows + wpb - 1) / wpb;
         if (out_dtype == AIRUN_DT_F32)
-            airun_launch(rmsnorm_rows_kernel<float>, dim3(blocks), dim3(256), 0, stream, x, delta, w, (float*)out, n_rows, n, eps, write_back);
+            airun_launch(rmsnorm_rows_kernel<float>, dim3(blocks), dim3(32 * wpb), 0, stream, x, delta, w, (float*)out, n_rows, n, eps, write_back);
         else if (out_dtype == AIRUN_DT_BF16)
-            airun_launch(rmsnorm_rows_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, x, delta, w, (__nv_bfloat16*)out, n_rows, n, eps, write_back);
+            airun_launch(rmsnorm_rows_kernel<__nv_bfloat16>, dim3(blocks), dim3(32 * wpb), 0, stream, x, delta, w, (__nv_bfloat16*)out, n_rows, n, eps, write_back);
         else
             return AIRUN_ERR_UNSUPPORTED;
         return airun_launch_status();

@@ -162,6 +162,18 @@ class Engine:
         self.scheduler.add(req)
         return req
 
+    def fork_request(self, parent: Request, params: Optional[SamplingParams] = None,
+                     max_new_tokens: Optional[int] = None, rid: Hashable = None) -> Request:
+        """A new request that continues ``parent``'s tokens so far with its own sampling, reading
+        the parent's cache pages instead of computing them again (only a partly filled last page
+        is copied).  Raises ``OutOfPages`` / ``CacheError`` if a page or a request slot is short."""
+        rid = next(self._ids) if rid is None else rid
+        child = Request(rid, list(parent.tokens), params or SamplingParams(**{**parent.params.__dict__}),
+                        int(max_new_tokens if max_new_tokens is not None else parent.max_new_tokens),
+                        parent.eog_tokens)
+        self.storage.run_copies(self.scheduler.fork(parent, child))
+        return child
+
     def has_work(self) -> bool:
         return self.scheduler.has_work()
 

@@ -86,6 +86,12 @@ class DecoderModel:
                                  torch.bfloat16)
         self.load(DictSource(tensors))
 
+    def device_driven(self) -> bool:
+        """True if every layer reads the batch's layout from the device arrays only, so that a step
+        of a given padded size always launches the same kernels (and can be replayed from a graph)."""
+        return all(getattr(l, "device_driven", lambda: False)() for l in self.layers) \
+            and getattr(self.final_norm, "device_driven", False)
+
     # ---- cache needs ----
     def cache_specs(self) -> Tuple[List[object], List[Optional[int]]]:
         return ([self.layers[c.layer].cache_spec() for c in self.order],

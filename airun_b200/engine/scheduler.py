@@ -124,6 +124,20 @@ class Scheduler:
     def has_work(self) -> bool:
         return bool(self.waiting or self.running)
 
+    def fork(self, parent: Request, child: Request):
+        """``child`` (whose prompt must be the parent's tokens so far) starts from the parent's
+        cache instead of computing it again: whole pages are shared.  Returns the device copies
+        the caller has to run before the next step."""
+        if parent not in self.running or parent.finished is not None:
+            raise ValueError("only a running request can be forked")
+        if child.prompt != parent.tokens:
+            raise ValueError("a fork continues the parent's tokens; its prompt must equal them")
+        copies = self.manager.fork(parent.rid, child.rid)
+        child.num_computed = parent.num_computed
+        self.running.append(child)
+        self.stats["admitted"] += 1
+        return copies
+
     # ------------------------------------------------------------ planning
     def _need_if_fits(self, req: Request, n: int, planned: Dict[int, int]) -> Optional[Dict[int, int]]:
         """Pages ``n`` more tokens of ``req`` would take, or None if they are not free."""

@@ -74,9 +74,18 @@ class StepRunner:
         self.graph_buckets = [b for b in (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256) if b <= self.R_max]
         if self.graph_buckets and self.graph_buckets[-1] < self.R_max and self.R_max <= 512:
             self.graph_buckets.append(self.R_max)
-        self.graphs: Dict[int, tuple] = {}
+        self.graphs: Dict[object, tuple] = {}
         self._warm_buckets = set()
         self.graph_launches = 0
+        # ... and of any other step (prompt portions, several wanted places) of a model whose parts
+        # read the batch's layout on the device: one graph per (padded tokens, padded wanted rows)
+        self.mixed_graphs = bool(getattr(model, "device_driven", lambda: False)())
+        self.max_mixed_graphs = 96
+        self.token_buckets = sorted({b for k in range(3, 24) for b in (1 << k, 3 << (k - 1)) if b <= self.T_max}
+                                    | {self.T_max})
+        self.want_buckets = sorted({4 ** k for k in range(12) if 4 ** k < self.T_max} | {self.T_max})
+        self.row_buckets = sorted({8 * 4 ** k for k in range(8) if 8 * 4 ** k < self.R_max} | {self.R_max})
+        self.portion_buckets = sorted({4 ** k for k in range(8) if 4 ** k < self.R_max} | {self.R_max})
         self.want_arange = torch.arange(max(self.R_max, 1), dtype=torch.int32, device=self.device)
 
     def _view(self, name: str, dev: bool = True):
@@ -153,10 +162,11 @@ class StepRunner:
         for e, need in zip(entries, needs):
             m.reserve(e.rid, len(e.tokens), need)
 
-    def build_context(self, entries: Sequence[StepEntry], pad_to: int = 0) -> tuple:
+    def build_context(self, entries: Sequence[StepEntry], pad_to: int = 0, pad_want: int = 0) -> tuple:
         """Fills the staging buffer and returns (StepContext, n_want).  With ``pad_to`` the
         batch is padded with rows that belong to no request (request -1, position -1), which
-        every kernel skips; that is how a captured graph of a fixed size runs a smaller batch."""
+        every kernel skips, and with requests that bring no tokens; that is how a captured graph
+        of a fixed size runs a smaller batch.  ``pad_want`` pads the wanted rows with row 0."""
         m = self.manager
         self._ring_i = (self._ring_i + 1) % len(self._ring)
         self.meta_host, self.meta_np, self._meta_event = self._ring[self._ring_i]
@@ -200,7 +210,10 @@ class StepRunner:
             bt = self._view(f"bt{g.gid}", dev=False).reshape(self.R_max, self.max_blocks)
             bt[:R, :need_blocks] = m.tables[g.gid][slots, :need_blocks]
         cu[len(entries)] = t
-        n_real = t
+        if pad_to:
+            cu[R:self.R_max + 1] = t
+        if pad_want > n_want:
+            want[n_want:pad_want] = 0
         if pad_to > t:
             tok[t:pad_to] = 0
             pos[t:pad_to] = -1
@@ -231,6 +244,8 @@ class StepRunner:
         if self.use_graphs and self.device.type == "cuda" and all(
                 len(e.tokens) == 1 and tuple(e.want) == (0,) for e in entries):
             logits = self._decode_step_graphed(entries)
+        elif self.use_graphs and self.mixed_graphs and self.device.type == "cuda":
+            logits = self._mixed_step_graphed(entries)
         else:
             ctx, n_want = self.build_context(entries)
             logits = self.model.forward(ctx, self._view("want_rows"), n_want)
@@ -252,27 +267,67 @@ class StepRunner:
             ctx, n_want = self.build_context(entries)
             return self.model.forward(ctx, self._view("want_rows"), n_want)
         ctx, n_want = self.build_context(entries, pad_to=bucket)
-        entry = self.graphs.get(bucket)
         ctx.extras["planning_context_len"] = self.max_context
+        return self._run_graphed(bucket, ctx, self.want_arange, bucket)[:n]
+
+    def _run_graphed(self, key, ctx, want_rows: torch.Tensor, n_want: int) -> Optional[torch.Tensor]:
+        """Runs the padded batch of ``ctx``: kernel by kernel the first time a step of this shape comes
+        (that loads and configures every kernel the graph will hold), captured the second time
+        (capturing runs nothing) and replayed from then on."""
+        entry = self.graphs.get(key)
         if entry is None:
-            if bucket not in self._warm_buckets:
-                # the first step of this size runs eagerly, on the padded batch: it loads and
-                # configures every kernel the graph will hold
-                self._warm_buckets.add(bucket)
-                return self.model.forward(ctx, self.want_arange, bucket)[:n]
-            # the second one is captured (capturing runs nothing) and then replayed below
+            if key not in self._warm_buckets:
+                self._warm_buckets.add(key)
+                return self.model.forward(ctx, want_rows, n_want)
             torch.cuda.current_stream().synchronize()
             before = ops.LAUNCHES[0]
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
-                out = self.model.forward(ctx, self.want_arange, bucket)
+                out = self.model.forward(ctx, want_rows, n_want)
             entry = (graph, out, ops.LAUNCHES[0] - before)
             ops.LAUNCHES[0] = before
-            self.graphs[bucket] = entry
+            self.graphs[key] = entry
         graph, out, kernels = entry
         graph.replay()
         self.graph_launches += kernels
-        return out[:n]
+        return out
+
+    def _mixed_step_graphed(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Any other step, replayed from a CUDA graph of the next larger captured shape: tokens,
+        wanted rows, single-token requests and requests with a portion, each rounded up to a bucket.
+        The batch is padded; which rows are portions and which single tokens, how the portions are
+        cut into tiles and how many slices a decoded token's keys get is worked out on the device
+        (kernels/fast.py, ``device_plan``), so one graph serves every batch of its shape.  Shapes
+        beyond the buckets, or more shapes than ``max_mixed_graphs``, run kernel by kernel."""
+        T = W = singles = portions = 0
+        for e in entries:
+            n = len(e.tokens)
+            T += n
+            W += len(e.want)
+            if n == 1:
+                singles += 1
+            else:
+                portions += 1
+        tb = next((b for b in self.token_buckets if b >= T), None)
+        wb = next((b for b in self.want_buckets if b >= W), None) if W else 0
+        ri = next((i for i, b in enumerate(self.row_buckets) if b >= singles), None) if singles else -1
+        pb = next((b for b in self.portion_buckets if b >= portions), None) if portions else 0
+        key = ("mixed", tb, wb, ri, pb)
+        if None in key or (key not in self.graphs and key not in self._warm_buckets
+                           and len(self._warm_buckets) >= self.max_mixed_graphs + len(self.graph_buckets)):
+            ctx, n_want = self.build_context(entries)
+            return self.model.forward(ctx, self._view("want_rows"), n_want)
+        ctx, n_want = self.build_context(entries, pad_to=tb, pad_want=wb)
+        ctx.decode_only = False
+        # what the graph is made for: at most this many single tokens (and more than the bucket
+        # below holds) and at most this many portions
+        ctx.extras["device_plan"] = dict(
+            max_rows=self.row_buckets[ri] if ri >= 0 else 0,
+            min_rows=(self.row_buckets[ri - 1] + 1 if ri > 0 else 1) if ri >= 0 else 0,
+            max_portions=pb)
+        ctx.extras["planning_context_len"] = self.max_context
+        out = self._run_graphed(key, ctx, self._view("want_rows"), wb)
+        return out[:W] if W else None
 
     def device_error(self) -> int:
         """Error bits the kernels have set since the last call (synchronises)."""

@@ -26,7 +26,7 @@ DISABLED = set(filter(None, os.environ.get("AIRUN_DISABLE_FAST", "").split(","))
 
 
 def all_libraries():
-    return [("gemm_tcgen05", None), ("attention_mma", {"HD": 128}), ("attention_mma", {"HD": 64}),
+    return [("gemm_tcgen05", None), ("attention_plan", None), ("attention_mma", {"HD": 128}), ("attention_mma", {"HD": 64}),
             ("attention_tcgen05", {"HD": 128}), ("attention_tcgen05", {"HD": 64})]
 
 
@@ -105,19 +105,25 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: int, 
 
 
 def plan_gemm(M: int, N: int, K: int) -> Tuple[bool, int, int]:
-    """(swap, bn, ksplit) for a product of M tokens with an [N, K] weight."""
+    """(swap, bn, ksplit) for a product of M tokens with an [N, K] weight.
+
+    Up to 128 tokens the weights are the 128-row operand (swap) and the K range is cut until about
+    TARGET_CTAS CTAs stream them.  Above that, tiles of 128 x 256 on the persistent kernel once
+    there are 96 of them; fewer tiles leave SMs idle, so the tile narrows to 128 x 128, and only
+    if that still fills less than one wave and a slice keeps 32 K-steps is K cut as well (cutting K
+    costs a round trip of partial tiles through memory: timed on the Qwen3-1.7B and -8B shapes at 192
+    to 2048 tokens, it loses everywhere else)."""
+    kb = (K + 63) // 64
     if M <= 128:
-        swap = True
         bn = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128
         tiles = (N + 127) // 128
-    else:
-        swap, bn = False, (256 if N >= 256 else 128)
-        tiles = ((M + 127) // 128) * ((N + bn - 1) // bn)
-    kb = (K + 63) // 64
-    ksplit = 1
-    if tiles < TARGET_CTAS:
-        ksplit = max(1, min(TARGET_CTAS // tiles, kb // 4))
-    return swap, bn, ksplit
+        ksplit = max(1, min(TARGET_CTAS // tiles, kb // 4)) if tiles < TARGET_CTAS else 1
+        return True, bn, ksplit
+    mt = (M + 127) // 128
+    if N >= 256 and mt * ((N + 255) // 256) >= 96:
+        return False, 256, 1
+    tiles = mt * ((N + 127) // 128)
+    return False, 128, max(1, min(148 // tiles, kb // 32))
 
 
 def _usable(x: torch.Tensor, w: torch.Tensor) -> bool:
@@ -207,15 +213,17 @@ _COMMON_SIG = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p
                c_float, c_int]
 
 
-def attn_prefill(ctx, q, out, cache, nh, nkv, hd, scale, window, tiles: torch.Tensor, n_tiles: int) -> None:
-    """Flash attention of prompt portions; ``tiles`` is int32 [n, 4] = (request, first row, tokens, 0)."""
+def attn_prefill(ctx, q, out, cache, nh, nkv, hd, scale, window, tiles: torch.Tensor, n_tiles: int,
+                 n_tiles_dev: Optional[torch.Tensor] = None) -> None:
+    """Flash attention of prompt portions; ``tiles`` is int32 [n, 4] = (request, first row, tokens, 0).
+    With ``n_tiles_dev`` (int32 on the device) the launch is made for ``n_tiles`` and runs that many."""
     _cuda(q, out, cache.pool, cache.block_table, tiles)
     _need(q.dtype == torch.bfloat16 and cache.pool.dtype == torch.bfloat16 and q.is_contiguous() and out.is_contiguous(),
           "tensor-core attention takes contiguous bfloat16 q, out and pages")
     _need(tiles.dtype == torch.int32 and tiles.is_contiguous() and tiles.numel() >= 4 * n_tiles, "tiles must be int32 [n, 4]")
-    f = _fn("attention_mma", "airun_attn_prefill", _COMMON_SIG + [c_void_p, c_int, c_void_p, c_void_p], {"HD": hd})
-    _check(f(*_attn_common_args(q, out, cache, ctx, nh, nkv, scale, window), _p(tiles), n_tiles, _p(ctx.err), _stream()),
-           "attn_prefill")
+    f = _fn("attention_mma", "airun_attn_prefill", _COMMON_SIG + [c_void_p, c_int, c_void_p, c_void_p, c_void_p], {"HD": hd})
+    _check(f(*_attn_common_args(q, out, cache, ctx, nh, nkv, scale, window), _p(tiles), n_tiles, _p(n_tiles_dev),
+             _p(ctx.err), _stream()), "attn_prefill")
 
 
 def prefill_tc_supported(hd: int, page_size: int) -> bool:
@@ -224,7 +232,8 @@ def prefill_tc_supported(hd: int, page_size: int) -> bool:
             and (page_size & (page_size - 1)) == 0)
 
 
-def attn_prefill_tc(ctx, q, out, cache, nh, nkv, hd, scale, window, tiles: torch.Tensor, n_tiles: int) -> None:
+def attn_prefill_tc(ctx, q, out, cache, nh, nkv, hd, scale, window, tiles: torch.Tensor, n_tiles: int,
+                    n_tiles_dev: Optional[torch.Tensor] = None) -> None:
     """Flash attention of prompt portions on tcgen05 (csrc/attention_tcgen05.cu); same tiles as attn_prefill."""
     _cuda(q, out, cache.pool, cache.block_table, tiles)
     _need(q.dtype == torch.bfloat16 and cache.pool.dtype == torch.bfloat16 and q.is_contiguous() and out.is_contiguous(),
@@ -234,14 +243,18 @@ def attn_prefill_tc(ctx, q, out, cache, nh, nkv, hd, scale, window, tiles: torch
     pool, bt = cache.pool, cache.block_table
     f = _fn("attention_tcgen05", "airun_attn_prefill_tc",
             [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int,
-             c_void_p, c_int, c_void_p, c_void_p], {"HD": hd})
+             c_void_p, c_int, c_void_p, c_void_p, c_void_p], {"HD": hd})
     _check(f(_p(q), _p(out), _p(pool), _p(bt), bt.stride(0), _p(ctx.positions), pool.shape[0], pool.shape[3],
-             nh, nkv, float(scale), int(window), _p(tiles), n_tiles, _p(ctx.err), _stream()), "attn_prefill_tc")
+             nh, nkv, float(scale), int(window), _p(tiles), n_tiles, _p(n_tiles_dev), _p(ctx.err), _stream()),
+           "attn_prefill_tc")
 
 
-def attn_decode(ctx, q, out, cache, nh, nkv, hd, scale, window, rows: torch.Tensor, n_rows: int, n_splits: int) -> None:
+def attn_decode(ctx, q, out, cache, nh, nkv, hd, scale, window, rows: torch.Tensor, n_rows: int, n_splits: int,
+                n_rows_dev: Optional[torch.Tensor] = None, dyn_slots: int = 0) -> None:
     """Attention of single decoded tokens (batch rows ``rows``; None: rows 0..n_rows-1), the keys cut
-    into ``n_splits`` slices."""
+    into ``n_splits`` slices.  With ``n_rows_dev`` (int32 on the device) the launch is made for ``n_rows``
+    rows and ``n_splits`` slices, runs the rows counted there, and every row picks its slices itself so
+    that about ``dyn_slots`` CTAs run."""
     _cuda(q, out, cache.pool, cache.block_table, rows)
     _need(q.dtype == torch.bfloat16 and cache.pool.dtype == torch.bfloat16 and q.is_contiguous() and out.is_contiguous(),
           "tensor-core attention takes contiguous bfloat16 q, out and pages")
@@ -250,13 +263,29 @@ def attn_decode(ctx, q, out, cache, nh, nkv, hd, scale, window, rows: torch.Tens
     scratch, counters = scratch_for(q.device)
     hgroups = (nh // nkv + 15) // 16
     if n_splits > 1:
-        need = n_rows * nkv * hgroups * n_splits * 16 * (hd + 2)
+        # rows picking their own slices use at most max(dyn_slots, rows x head groups) slices together
+        units = n_rows * nkv * hgroups
+        need = (units * n_splits if n_rows_dev is None else max(dyn_slots, units)) * 16 * (hd + 2)
         _need(need <= scratch.numel() and n_rows * nkv * hgroups <= counters.numel(),
               "split-K scratch is too small for this decode launch")
     f = _fn("attention_mma", "airun_attn_decode",
-            _COMMON_SIG + [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p], {"HD": hd})
+            _COMMON_SIG + [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p], {"HD": hd})
     _check(f(*_attn_common_args(q, out, cache, ctx, nh, nkv, scale, window), _p(rows), n_rows, n_splits,
-             _p(scratch), _p(counters), _p(ctx.err), _stream()), "attn_decode")
+             _p(scratch), _p(counters), _p(n_rows_dev), int(dyn_slots), _p(ctx.err), _stream()), "attn_decode")
+
+
+def attn_plan(ctx, per_tile: int, tiles: torch.Tensor, rows: torch.Tensor, counts: torch.Tensor) -> None:
+    """The attention work lists of the batch, made on the device (csrc/attention_plan.cu): tiles of
+    ``per_tile`` tokens of every portion, the rows of single tokens, and how many of each."""
+    _cuda(ctx.cu_tokens, ctx.context_lens, tiles, rows, counts)
+    for t in (tiles, rows, counts):
+        _need(t.dtype == torch.int32 and t.is_contiguous(), "the plan's lists are contiguous int32")
+    _need(ctx.cu_tokens.numel() >= ctx.num_reqs + 1 and ctx.context_lens.numel() >= ctx.num_reqs and counts.numel() >= 2,
+          "the batch's layout arrays are shorter than its number of requests")
+    f = _fn("attention_plan", "airun_attn_plan",
+            [c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p])
+    _check(f(_p(ctx.cu_tokens), _p(ctx.context_lens), int(ctx.num_reqs), int(per_tile), _p(tiles), tiles.shape[0],
+             _p(rows), rows.numel(), _p(counts), _p(ctx.err), _stream()), "attn_plan")
 
 
 def plan_decode_splits(n_rows: int, nkv: int, hgroups: int, context_len: int, hd: int, slots: int = DECODE_SLOTS) -> int:
@@ -284,7 +313,22 @@ def _attention_plan(ctx, G: int):
     if plan is not None:
         return plan
     dev = ctx.token_ids.device
-    if ctx.decode_only:
+    shape = ctx.extras.get("device_plan")
+    if shape:
+        # the batch is padded and its layout is only on the device: lists long enough for any batch
+        # of this shape (``shape`` bounds its single tokens and portions), filled by a kernel, the
+        # counts read by the attention kernels themselves
+        per = max(1, PREFILL_ROWS // G)
+        T = ctx.num_tokens
+        max_rows, max_portions = min(shape["max_rows"], T), min(shape["max_portions"], T // 2)
+        max_tiles = (T // per + max_portions + 1) if max_portions else 0
+        buf = ctx.ws_main.alloc((4 + 4 * max(max_tiles, 1) + max(max_rows, 1),), torch.int32)
+        counts, tiles = buf[:4], buf[4:4 + 4 * max(max_tiles, 1)].view(max(max_tiles, 1), 4)
+        rows = buf[4 + 4 * max(max_tiles, 1):]
+        attn_plan(ctx, per, tiles, rows, counts)
+        plan = dict(rows=rows, n_rows=max_rows, tiles=tiles, n_tiles=max_tiles,
+                    n_tiles_dev=counts[0:1], n_rows_dev=counts[1:2], min_rows=max(1, shape["min_rows"]))
+    elif ctx.decode_only:
         plan = dict(rows=None, n_rows=ctx.num_tokens, tiles=None, n_tiles=0)
     else:
         per = max(1, PREFILL_ROWS // G)
@@ -312,17 +356,25 @@ def attention_bf16(ctx, q, out, cache, nh: int, nkv: int, hd: int, scale: float,
         return False
     G = nh // nkv
     plan = _attention_plan(ctx, G)
+    n_tiles_dev, n_rows_dev = plan.get("n_tiles_dev"), plan.get("n_rows_dev")
     if plan["n_tiles"]:
         if prefill_tc_supported(hd, cache.page_size):
-            attn_prefill_tc(ctx, q, out, cache, nh, nkv, hd, scale, window, plan["tiles"], plan["n_tiles"])
+            attn_prefill_tc(ctx, q, out, cache, nh, nkv, hd, scale, window, plan["tiles"], plan["n_tiles"], n_tiles_dev)
         else:
-            attn_prefill(ctx, q, out, cache, nh, nkv, hd, scale, window, plan["tiles"], plan["n_tiles"])
+            attn_prefill(ctx, q, out, cache, nh, nkv, hd, scale, window, plan["tiles"], plan["n_tiles"], n_tiles_dev)
     if plan["n_rows"]:
         context = ctx.extras.get("planning_context_len", ctx.max_context_len)
         if window > 0:
             context = min(context, window)
         tma = hd % 64 == 0 and cache.page_size % 16 == 0 and (cache.page_size & (cache.page_size - 1)) == 0
-        splits = plan_decode_splits(plan["n_rows"], nkv, (G + 15) // 16, context, hd,
-                                    DECODE_SLOTS_TMA if tma else DECODE_SLOTS)
-        attn_decode(ctx, q, out, cache, nh, nkv, hd, scale, window, plan["rows"], plan["n_rows"], splits)
+        slots = DECODE_SLOTS_TMA if tma else DECODE_SLOTS
+        if n_rows_dev is not None:
+            # no row takes more slices than fit when the fewest rows of this shape are there
+            fit = max(1, slots // (plan["min_rows"] * nkv * ((G + 15) // 16)))
+            most = max(1, min(64, (context + DECODE_MIN_KEYS_PER_SPLIT - 1) // DECODE_MIN_KEYS_PER_SPLIT, fit))
+            attn_decode(ctx, q, out, cache, nh, nkv, hd, scale, window, plan["rows"], plan["n_rows"], most,
+                        n_rows_dev, slots)
+        else:
+            splits = plan_decode_splits(plan["n_rows"], nkv, (G + 15) // 16, context, hd, slots)
+            attn_decode(ctx, q, out, cache, nh, nkv, hd, scale, window, plan["rows"], plan["n_rows"], splits)
     return True

@@ -25,6 +25,8 @@ from .linear import linear, linear_into_residual
 
 
 class GQAAttention(Mixer):
+    device_driven = True
+
     fuses_norms = True        # takes NormedActivations as input and a ResidualSink for its output
 
     def __init__(self, prefix: str, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,

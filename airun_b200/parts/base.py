@@ -24,6 +24,12 @@ FeedForward     forward(ctx, h) -> float32 [T, hidden]
                 ``sink=ResidualSink`` (then it adds its result to the residual itself and returns
                 NormedActivations for the next sub-layer, or ignores the sink and returns a delta)
                 and accepts NormedActivations as ``h``.
+                Optional, for every part: ``device_driven = True`` promises that forward launches the
+                same kernels with the same arguments for every batch of ctx.num_tokens rows, i.e. that
+                it reads which rows belong to which request, their positions and lengths from the
+                device arrays of ctx only (never from ctx.query_lens and the other host lists), and
+                that rows of request -1 are padding it skips.  Steps of a model whose parts all promise
+                this are replayed from CUDA graphs, prompt portions included.
 Block           forward(ctx, x, delta, cache) -> delta of the block's last sub-layer,
                   still to be added to x by whoever norms x next
 """

@@ -38,6 +38,10 @@ class PreNormBlock(Part):
     def cache_spec(self):
         return self.mixer.cache_spec()
 
+    def device_driven(self) -> bool:
+        """Do all parts of this block read the batch's layout from the device arrays only?"""
+        return all(getattr(p, "device_driven", False) for p in self.parts())
+
     def accepts_normed(self) -> bool:
         """Can this block start from NormedActivations (its first norm folded into the products)?"""
         return self.dtype == torch.bfloat16 and getattr(self.mixer, "fuses_norms", False) \

@@ -21,6 +21,8 @@ INTERLEAVE = 16
 
 
 class SwiGLU(FeedForward):
+    device_driven = True
+
     fuses_norms = True        # takes NormedActivations as input and a ResidualSink for its output
 
     def __init__(self, prefix: str, hidden_size: int, intermediate_size: int,

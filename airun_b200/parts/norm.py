@@ -17,6 +17,8 @@ from .base import Norm, register_part
 
 
 class RMSNorm(Norm):
+    device_driven = True
+
     def __init__(self, prefix: str, size: int, eps: float, dtype=None, device=None,
                  weight_name: str = "weight"):
         self.prefix, self.size, self.eps = prefix, int(size), float(eps)

@@ -10,7 +10,10 @@ Prints ONE JSON line: ``value`` is the device-timed decode rate of the step
 function, ``e2e`` the rate through the Python entry point (scheduler, sampling,
 host tokens in and out), ``prefill`` a 2,048-token prompt in one step,
 ``roofline`` the bytes a decode step must read over its time, ``points`` the
-decode rate at batch 1 and 64.  ``--impl reference`` reports that the reference
+decode rate at batch 1 and 64.  ``--workload serve`` and ``--workload long`` run
+two further workloads end to end (continuous batching of 128 requests on the
+Qwen3-1.7B shape; a 32,768-token prompt on the Qwen3-32B shape) and print a line
+of their own.  ``--impl reference`` reports that the reference
 cannot be installed here.
 """
 from __future__ import annotations
@@ -31,6 +34,10 @@ QWEN3_8B = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_si
                 num_hidden_layers=36, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
                 intermediate_size=12288, max_position_embeddings=40960, rms_norm_eps=1e-6,
                 rope_theta=1000000.0, tie_word_embeddings=False)
+QWEN3_1_7B = dict(QWEN3_8B, hidden_size=2048, num_hidden_layers=28, num_attention_heads=16, num_key_value_heads=8,
+                  intermediate_size=6144, tie_word_embeddings=True)
+QWEN3_32B = dict(QWEN3_8B, hidden_size=5120, num_hidden_layers=64, num_attention_heads=64, num_key_value_heads=8,
+                 intermediate_size=25600, tie_word_embeddings=False)
 FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0)
 
 
@@ -214,6 +221,115 @@ def time_prefill(eng, T, runs=3):
     return statistics.median(times[1:])
 
 
+def workload_serve(a) -> int:
+    """Continuous batching: 128 requests at once, prompt lengths uniform in [64, 2048], 256 new
+    tokens each, a step budget of 512 tokens (Qwen3-1.7B shape).  Runs the whole workload twice
+    through the Python entry point and times the second run (the first warms the CUDA graphs)."""
+    import torch
+    from airun_b200 import Engine, EngineOptions, Qwen3Config, SamplingParams
+    d = dict(QWEN3_1_7B)
+    if a.layers:
+        d["num_hidden_layers"] = a.layers
+    cfg = Qwen3Config.from_dict(d)
+    n_req, new = a.requests, a.new_tokens
+    eng = Engine.from_config(cfg, seed=0, options=EngineOptions(
+        dtype=a.dtype, page_size=16, cache_tokens=n_req * (2048 + new + 16) + 4096, max_batch_tokens=a.budget,
+        max_requests=n_req, max_context=2048 + new + 16))
+    g = torch.Generator().manual_seed(4)
+    lens = torch.randint(64, 2049, (n_req,), generator=g).tolist()
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in lens]
+    res = {}
+    for run in range(2):
+        sampler = ClockSampler()
+        sampler.start()
+        steps0 = eng.stats.steps
+        reqs = [eng.add_request(p, SamplingParams.greedy(), max_new_tokens=new) for p in prompts]
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        steps = 0
+        while eng.has_work():
+            eng.run_step()
+            steps += 1
+        torch.cuda.synchronize()
+        sec = time.perf_counter() - t0
+        clocks = sampler.stop()
+        gen = sum(len(r.output) for r in reqs)
+        assert gen == n_req * new, "a request ended early"
+        res = {"workload": "serve", "model": "Qwen3-1.7B shape, random weights", "layers": cfg.num_hidden_layers,
+               "layers_full": 28, "requests": n_req, "prompt_tokens": sum(lens), "generated_tokens": gen,
+               "step_budget": a.budget, "seconds": round(sec, 3), "steps": steps,
+               "ms_per_step": round(sec * 1e3 / steps, 3),
+               "total_tokens_per_s": round((sum(lens) + gen) / sec, 1), "decode_tokens_per_s": round(gen / sec, 1),
+               "preemptions": eng.scheduler.stats["preemptions"], "dtype": a.dtype, "clocks": clocks}
+    print(json.dumps(res))
+    return 0
+
+
+def workload_long(a) -> int:
+    """Long context: one 32,768-token prompt in portions of 2,048, then 512 tokens decoded alone, then
+    15 forks of the request (reading the same prompt pages: 16 private caches would not fit beside
+    the weights) and 512 tokens decoded by all 16 (Qwen3-32B shape)."""
+    import torch
+    from airun_b200 import Engine, EngineOptions, Qwen3Config, SamplingParams
+    d = dict(QWEN3_32B)
+    if a.layers:
+        d["num_hidden_layers"] = a.layers
+    cfg = Qwen3Config.from_dict(d)
+    T, new, forks = a.prompt, a.new_tokens, a.forks
+    eng = Engine.from_config(cfg, seed=0, options=EngineOptions(
+        dtype=a.dtype, page_size=16, cache_tokens=T + (forks + 2) * (2 * new + 32) + 4096,
+        max_batch_tokens=2048, max_requests=forks + 1, max_context=T + 2 * new + 32))
+    L = cfg.num_hidden_layers
+    pk = peaks()
+    esz = 2 if a.dtype == "bfloat16" else 4
+    prompt = torch.randint(0, cfg.vocab_size, (T,), generator=torch.Generator().manual_seed(5)).tolist()
+    # warm-up: a short request through the same kernels (prefill portion, decode graph)
+    eng.generate(prompt[:4096], SamplingParams.greedy(), max_new_tokens=8)
+    sampler = ClockSampler()
+    sampler.start()
+    parent = eng.add_request(prompt, SamplingParams.greedy(), max_new_tokens=2 * new + 1)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    while not parent.output:
+        eng.run_step()
+    torch.cuda.synchronize()
+    t_pre = time.perf_counter() - t0
+    t0 = time.perf_counter()
+    while len(parent.output) < 1 + new:
+        eng.run_step()
+    torch.cuda.synchronize()
+    t_b1 = time.perf_counter() - t0
+    kids = [eng.fork_request(parent, max_new_tokens=new) for _ in range(forks)]
+    eng.run_step()                                   # the forks' first step is not a pure decode step
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    n_steps = 0
+    while len(kids[0].output) < new:
+        eng.run_step()
+        n_steps += 1
+    torch.cuda.synchronize()
+    t_bn = time.perf_counter() - t0
+    clocks = sampler.stop()
+    H, I, V = cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size
+    per_layer = (cfg.q_dim + 2 * cfg.kv_dim) * H + H * cfg.q_dim + 3 * H * I
+    flops = 2.0 * T * L * per_layer + L * cfg.num_attention_heads * 4.0 * cfg.head_dim * T * (T + 1) / 2
+    b1_bytes = decode_bytes(cfg, L, 1, T + new // 2, esz)
+    bn_bytes = decode_bytes(cfg, L, forks + 1, T + new + new // 2, esz)
+    print(json.dumps({
+        "workload": "long", "model": "Qwen3-32B shape, random weights", "layers": L, "layers_full": 64,
+        "prompt_tokens": T, "portion": 2048, "dtype": a.dtype, "peaks": pk["source"],
+        "prefill": {"seconds": round(t_pre, 3), "tokens_per_s": round(T / t_pre, 1),
+                    "frac_of_bf16_peak": round(flops / t_pre / (pk["bf16_tflops"] * 1e12), 4)},
+        "decode_b1": {"tokens": new, "tokens_per_s": round(new / t_b1, 2), "ms_per_step": round(t_b1 * 1e3 / new, 3),
+                      "hbm_frac": round(b1_bytes / (t_b1 / new) / 1e9 / pk["hbm_gbs"], 4)},
+        f"decode_b{forks + 1}": {"tokens": n_steps * (forks + 1), "tokens_per_s": round(n_steps * (forks + 1) / t_bn, 2),
+                                 "ms_per_step": round(t_bn * 1e3 / n_steps, 3), "shared_prompt_pages": True,
+                                 "hbm_frac_if_every_request_reads_the_prompt":
+                                     round(bn_bytes / (t_bn / n_steps) / 1e9 / pk["hbm_gbs"], 4)},
+        "clocks": clocks}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -226,6 +342,14 @@ def main() -> int:
     ap.add_argument("--dtype", default="bfloat16")
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--decode-only", action="store_true", help="time the decode step only (for profiling runs)")
+    ap.add_argument("--workload", default="decode", choices=("decode", "serve", "long"),
+                    help="decode: the headline line; serve: 128 requests continuously batched (Qwen3-1.7B shape); "
+                         "long: a 32,768-token prompt, then decoding alone and as 16 forks (Qwen3-32B shape)")
+    ap.add_argument("--requests", type=int, default=128, help="serve: requests")
+    ap.add_argument("--new-tokens", type=int, default=None, help="serve / long: tokens decoded per request")
+    ap.add_argument("--budget", type=int, default=512, help="serve: tokens per step")
+    ap.add_argument("--prompt", type=int, default=32768, help="long: prompt length")
+    ap.add_argument("--forks", type=int, default=15, help="long: forks of the request for the batched decode")
     a = ap.parse_args()
     if a.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -236,6 +360,12 @@ def main() -> int:
         print(f"bench.py measures one GPU; --gpus {a.gpus} is not supported (the engine is single-GPU)")
         return 2
     a.warmup = max(a.warmup, 3)
+    if a.workload == "serve":
+        a.new_tokens = a.new_tokens or 256
+        return workload_serve(a)
+    if a.workload == "long":
+        a.new_tokens = a.new_tokens or 512
+        return workload_long(a)
 
     import torch
     from airun_b200 import Engine, EngineOptions, Qwen3Config

@@ -163,3 +163,142 @@ def test_random_orders_keep_every_page_accounted_for(seed):
         m.free_request(rid)
     assert m.free_pages() == {0: 40, 1: 40}
     m.check_invariants()
+
+
+def test_fork_shares_whole_pages_and_copies_the_partial_one():
+    m = manager([FULL], page=8, pages=6)
+    m.add_request("a")
+    m.reserve("a", 19)
+    m.commit("a", 19)                         # pages 0, 1 whole, page 2 holds 3 tokens
+    plan = m.fork("a", "b")
+    assert m.block_table("b", 0)[:2] == [0, 1] and m.block_table("b", 0)[2] == 3
+    assert plan.pages == [(0, 2, 3)] and plan.state is None
+    assert m.paged[0].allocator.holders(0) == 2 and m.paged[0].allocator.holders(2) == 1
+    assert m.get("b").num_tokens == 19
+    m.check_invariants()
+    m.free_request("a")                       # the shared pages stay with b
+    assert m.free_pages() == {0: 3}
+    m.reserve("b", 6)
+    m.commit("b", 6)
+    m.check_invariants()
+    m.free_request("b")
+    assert m.free_pages() == {0: 6}
+    # at a page's edge nothing is copied
+    m.add_request("c")
+    m.reserve("c", 16)
+    m.commit("c", 16)
+    assert m.fork("c", "d").pages == []
+    # short of pages or slots: nothing is taken
+    m2 = manager([FULL], page=8, pages=1, reqs=2)
+    m2.add_request("a")
+    m2.reserve("a", 3)
+    m2.commit("a", 3)
+    with pytest.raises(OutOfPages):
+        m2.fork("a", "b")
+    assert "b" not in m2.requests and m2.has_free_slot()
+    m2.check_invariants()
+
+
+def test_truncate_gives_pages_back_and_never_writes_a_shared_page():
+    m = manager([FULL], page=8, pages=8)
+    m.add_request("a")
+    m.reserve("a", 30)
+    m.commit("a", 30)
+    assert m.truncate("a", 30).pages == []
+    m.fork("a", "b")                          # pages 0..2 shared, page 3 copied
+    plan = m.truncate("b", 12)                # the end falls inside shared page 1
+    assert len(m.block_table("b", 0)) == 2 and m.block_table("b", 0)[0] == 0
+    assert plan.pages and plan.pages[0][1] == 1 and plan.pages[0][2] == m.block_table("b", 0)[1] != 1
+    assert m.paged[0].allocator.holders(1) == 1 and m.paged[0].allocator.holders(2) == 1
+    m.check_invariants()
+    assert m.truncate("a", 16).pages == []    # at a page's edge: pages 2 and 3 go back
+    assert len(m.block_table("a", 0)) == 2
+    with pytest.raises(CacheError):
+        m.truncate("a", 17)
+    m.check_invariants()
+    ms = manager([StateSpec((4,)), FULL], page=8, pages=4)
+    ms.add_request("a")
+    ms.reserve("a", 5)
+    ms.commit("a", 5)
+    assert ms.fork("a", "b").state == (ms.get("a").slot, ms.get("b").slot)
+    with pytest.raises(CacheError):
+        ms.truncate("a", 2)                   # fixed-size state cannot be moved back
+    mw = manager([WIN], page=8, pages=8)
+    mw.add_request("a")
+    mw.reserve("a", 60)
+    mw.commit("a", 60)
+    with pytest.raises(CacheError):
+        mw.truncate("a", 20)                  # the window's pages before 20 are gone
+    assert mw.truncate("a", 58).pages == []
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_forks_and_cuts_every_request_reads_its_own_history(seed):
+    """Pages carry what was written to them (a shadow of the device); through its block table
+    every request must find its own tokens, whatever was shared, copied, cut or freed."""
+    rng = random.Random(100 + seed)
+    P = 4
+    m = manager([FULL, WIN], page=P, pages=48, reqs=6)
+    content = [[[None] * P for _ in range(48)] for _ in m.paged]
+    history = {}
+    next_id, stamp = 0, 0
+
+    def write(rid, start, values):
+        for g in m.paged:
+            bt = m.block_table(rid, g.gid)
+            for i, v in enumerate(values):
+                pos = start + i
+                assert m.paged[g.gid].allocator.holders(bt[pos // P]) == 1, "a shared page is written"
+                content[g.gid][bt[pos // P]][pos % P] = v
+
+    def run(plan):
+        for gid, src, dst in plan.pages:
+            content[gid][dst] = list(content[gid][src])
+
+    for step in range(500):
+        r = rng.random()
+        if r < 0.15 and m.has_free_slot():
+            m.add_request(next_id)
+            history[next_id] = []
+            next_id += 1
+        elif r < 0.65 and history:
+            rid = rng.choice(list(history))
+            n = rng.choice([1, 1, 2, 3, 7])
+            if m.can_reserve(rid, n):
+                m.reserve(rid, n)
+                vals = list(range(stamp, stamp + n))
+                stamp += n
+                write(rid, len(history[rid]), vals)
+                m.commit(rid, n)
+                history[rid] += vals
+        elif r < 0.78 and history and m.has_free_slot():
+            rid = rng.choice(list(history))
+            try:
+                run(m.fork(rid, next_id))
+                history[next_id] = list(history[rid])
+                next_id += 1
+            except OutOfPages:
+                pass
+        elif r < 0.88 and history:
+            rid = rng.choice(list(history))
+            n = rng.randint(max(0, len(history[rid]) - 6), len(history[rid]))
+            try:
+                run(m.truncate(rid, n))
+                del history[rid][n:]
+            except (OutOfPages, CacheError):
+                pass
+        elif history:
+            rid = rng.choice(list(history))
+            m.free_request(rid)
+            del history[rid]
+        m.check_invariants()
+        for rid, h in history.items():
+            assert m.get(rid).num_tokens == len(h)
+            for g in m.paged:
+                bt = m.block_table(rid, g.gid)
+                lo = 0 if g.window == 0 else max(0, len(h) - g.window + 1)
+                for pos in range(lo, len(h)):
+                    assert content[g.gid][bt[pos // P]][pos % P] == h[pos], (rid, g.gid, pos)
+    for rid in list(history):
+        m.free_request(rid)
+    assert m.free_pages() == {0: 48, 1: 48}

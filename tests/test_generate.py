@@ -129,3 +129,64 @@ def test_perplexity_and_bench_subcommands(folders, tmp_path):
     import json
     rep = json.loads(out.stdout.strip().splitlines()[-1])
     assert set(rep["prefill"]) == {"33", "64"} and rep["decode"]["tokens_per_s"] > 0 and rep["decode"]["parallel"] == 2
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_forked_requests_read_the_parents_pages_and_decode_on_their_own(name, folders):
+    """A request is forked while it decodes (its last page partly filled): parent and children go on
+    side by side and each gets the tokens the plain implementation gets for the same sequence."""
+    import airun_b200
+    cfg, W = P.read_model_folder(folders[name])
+    ps = TINY[name]["page_size"]
+    prompt = random_tokens(2 * ps + 3, cfg["vocab_size"], 130)
+    want = P.plain_greedy_generate(cfg, W, prompt, 14)
+    eng = airun_b200.Engine.from_folder(folders[name], dtype="float32", page_size=ps, cache_tokens=40 * ps,
+                                        max_batch_tokens=24, max_requests=4)
+    parent = eng.add_request(prompt, airun_b200.SamplingParams.greedy(), max_new_tokens=14)
+    while len(parent.output) < 4:
+        eng.run_step()
+    free_before = eng.manager.free_pages()[0]
+    kids = [eng.fork_request(parent, max_new_tokens=10) for _ in range(2)]
+    # two whole pages are shared, each child took one page for the partly filled one
+    assert eng.manager.free_pages()[0] == free_before - 2
+    eng.manager.check_invariants()
+    # a third child continues with another token than the parent sampled
+    other = (parent.output[-1] + 1) % cfg["vocab_size"]
+    odd = eng.fork_request(parent, max_new_tokens=6)
+    odd.prompt[-1] = other
+    want_odd = P.plain_greedy_generate(cfg, W, prompt + parent.output[:3] + [other], 6)
+    while eng.has_work():
+        eng.run_step()
+        eng.manager.check_invariants()
+    assert parent.output == want
+    for k in kids:
+        assert k.output == want[4:14]
+    assert odd.output == want_odd
+    assert eng.manager.free_pages() == {g.gid: eng.manager.num_pages for g in eng.manager.paged}
+
+
+def test_cutting_a_request_back_and_going_on(folders):
+    """The step function after ``truncate``: tokens past the cut are gone, the rest is still there,
+    also when the cut falls inside a page that a fork shares."""
+    from airun_b200.engine.step import StepEntry
+    import airun_b200
+    name = "B"
+    cfg, W = P.read_model_folder(folders[name])
+    V = cfg["vocab_size"]
+    eng = airun_b200.Engine.from_folder(folders[name], dtype="float32", page_size=8, cache_tokens=256,
+                                        max_batch_tokens=64, max_requests=4)
+    first = random_tokens(29, V, 140)
+    tail_a, tail_b = random_tokens(9, V, 141), random_tokens(7, V, 142)
+    run, mgr = eng.runner, eng.manager
+    mgr.add_request("a")
+    run.step([StepEntry("a", first, ())])
+    eng.storage.run_copies(mgr.fork("a", "b"))
+    eng.storage.run_copies(mgr.truncate("b", 13))          # inside shared page 1
+    eng.storage.run_copies(mgr.truncate("a", 24))          # at a page's edge
+    mgr.check_invariants()
+    got = run.step([StepEntry("a", tail_a, tuple(range(9))), StepEntry("b", tail_b, tuple(range(7)))]).cpu().numpy()
+    want_a = P.plain_forward(cfg, W, first[:24] + tail_a).numpy()[24:]
+    want_b = P.plain_forward(cfg, W, first[:13] + tail_b).numpy()[13:]
+    from helpers import assert_close
+    assert_close(got[:9], want_a, "float32", "request cut at a page's edge")
+    assert_close(got[9:], want_b, "float32", "fork cut inside a shared page")

@@ -60,7 +60,8 @@ def paged_from_dense(ks, vs, page_size, dtype, extra_pages=5, seed=0):
 
 # ----------------------------------------------------------------------------- elementwise
 @pytest.mark.parametrize("T,H,out_dtype", [(5, 100, torch.float32), (3, 4096, torch.bfloat16), (1, 36, torch.float32),
-                                          (7, 1500, torch.bfloat16), (600, 1024, torch.bfloat16), (515, 2560, torch.float32)])
+                                          (7, 1500, torch.bfloat16), (600, 1024, torch.bfloat16), (515, 2560, torch.float32),
+                                          (1300, 516, torch.float32), (2400, 2048, torch.bfloat16)])
 def test_rmsnorm_and_fused_add(T, H, out_dtype):
     from airun_b200.kernels import ops
     torch.manual_seed(1)
