@@ -28,16 +28,23 @@ with pages:
 * State groups hold ``[max_requests, *shape]`` per owner; a request gets a slot
   at admission (the caller zero-fills it) and returns it at the end.
 
-All bookkeeping is host-side and needs no GPU; ``CacheStorage`` owns the
-device tensors.
+All bookkeeping is host-side and needs no GPU; it is done by the native core
+(``csrc/host_core.cpp``, compiled with the C++ compiler at first use), of which the
+classes here are thin views that map request ids to slots and status codes to
+exceptions.  ``CacheStorage`` owns the device tensors.
 """
 from __future__ import annotations
 
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
+import ctypes
+from ctypes import POINTER, c_char_p, c_int, c_int32, c_longlong, c_void_p
+
 import numpy as np
 import torch
+
+from ..csrc import build
 
 from ..parts.base import PagedKVSpec, StateSpec
 
@@ -50,46 +57,100 @@ class CacheError(RuntimeError):
     """Misuse of the manager (unknown request, double free, ...)."""
 
 
-class PageAllocator:
-    """Free list of page ids with a holder count per page."""
+_LIB = None
 
-    def __init__(self, num_pages: int):
-        if num_pages <= 0:
-            raise ValueError("a page pool needs at least one page")
-        self.num_pages = num_pages
-        self._free: List[int] = list(range(num_pages - 1, -1, -1))   # pop() hands out page 0 first
-        self._holders = [0] * num_pages
+
+def _lib():
+    """The native host core, loaded (and compiled) once."""
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    lib = build.load("host_core")
+    P, I, L = c_void_p, c_int, c_longlong
+    IP, LP = POINTER(c_int), POINTER(c_longlong)
+    sigs = {
+        "airun_pool_create": (P, [I]), "airun_pool_destroy": (None, [P]), "airun_pool_error": (c_char_p, [P]),
+        "airun_pool_num_pages": (I, [P]), "airun_pool_num_free": (I, [P]), "airun_pool_take": (I, [P, I, IP]),
+        "airun_pool_share": (I, [P, I]), "airun_pool_give_back": (I, [P, I]), "airun_pool_holders": (I, [P, I]),
+        "airun_pool_free_list": (I, [P, IP, I]),
+        "airun_cache_create": (P, [I, IP, I, I, I, I, I]), "airun_cache_destroy": (None, [P]),
+        "airun_cache_error": (c_char_p, [P]), "airun_cache_pool": (P, [P, I]),
+        "airun_cache_table": (POINTER(c_int32), [P, I]), "airun_cache_has_free_slot": (I, [P]),
+        "airun_cache_num_live": (I, [P]), "airun_cache_add": (I, [P]), "airun_cache_free": (I, [P, I]),
+        "airun_cache_num_tokens": (L, [P, I]), "airun_cache_reserved": (L, [P, I]),
+        "airun_cache_num_blocks": (I, [P, I, I]), "airun_cache_blocks": (I, [P, I, I, IP, I]),
+        "airun_cache_pages_needed": (I, [P, I, L, IP]), "airun_cache_reserve_many": (I, [P, I, IP, LP]),
+        "airun_cache_commit_many": (I, [P, I, IP, LP]), "airun_cache_fork": (I, [P, I, IP, IP, IP]),
+        "airun_cache_truncate": (I, [P, I, L, IP, IP]), "airun_cache_check": (I, [P]),
+        "airun_cache_build_batch": (I, [P, I, IP, IP, c_void_p, IP, IP, c_void_p, LP, I, I, I, I, LP]),
+    }
+    for name, (res, args) in sigs.items():
+        f = getattr(lib, name)
+        f.restype, f.argtypes = res, args
+    _LIB = lib
+    return lib
+
+
+def _raise(status: int, text: bytes, who: str = "") -> None:
+    msg = (who + ": " if who else "") + text.decode()
+    raise (OutOfPages if status == 1 else CacheError)(msg)
+
+
+def _ints(values) -> ctypes.Array:
+    return (c_int * len(values))(*values)
+
+
+def _longs(values) -> ctypes.Array:
+    return (c_longlong * len(values))(*values)
+
+
+class PageAllocator:
+    """Free list of page ids with a holder count per page (a view of the native pool: its own,
+    or the pool of a cache group)."""
+
+    def __init__(self, num_pages: int, _borrowed: Optional[int] = None):
+        self._lib = _lib()
+        self._own = _borrowed is None
+        if self._own:
+            if num_pages <= 0:
+                raise ValueError("a page pool needs at least one page")
+            self._h = self._lib.airun_pool_create(int(num_pages))
+        else:
+            self._h = _borrowed
+        self.num_pages = int(num_pages)
+
+    def __del__(self):
+        if getattr(self, "_own", False) and self._h:
+            self._lib.airun_pool_destroy(self._h)
+            self._h = None
+
+    def _check(self, status: int) -> None:
+        if status:
+            _raise(status, self._lib.airun_pool_error(self._h))
 
     @property
     def num_free(self) -> int:
-        return len(self._free)
+        return self._lib.airun_pool_num_free(self._h)
 
     def take(self, n: int) -> List[int]:
-        if n > len(self._free):
-            raise OutOfPages(f"{n} pages wanted, {len(self._free)} free of {self.num_pages}")
-        out = [self._free.pop() for _ in range(n)]
-        for p in out:
-            if self._holders[p] != 0:
-                raise CacheError(f"page {p} was on the free list while held")
-            self._holders[p] = 1
-        return out
+        out = (c_int * max(n, 1))()
+        self._check(self._lib.airun_pool_take(self._h, int(n), out))
+        return list(out[:n])
 
     def share(self, page: int) -> None:
-        if self._holders[page] <= 0:
-            raise CacheError(f"page {page} is not held and cannot be shared")
-        self._holders[page] += 1
+        self._check(self._lib.airun_pool_share(self._h, int(page)))
 
     def give_back(self, page: int) -> None:
-        if not (0 <= page < self.num_pages):
-            raise CacheError(f"page {page} is outside the pool")
-        if self._holders[page] <= 0:
-            raise CacheError(f"page {page} is freed twice")
-        self._holders[page] -= 1
-        if self._holders[page] == 0:
-            self._free.append(page)
+        self._check(self._lib.airun_pool_give_back(self._h, int(page)))
 
     def holders(self, page: int) -> int:
-        return self._holders[page]
+        return self._lib.airun_pool_holders(self._h, int(page))
+
+    def free_list(self) -> List[int]:
+        """The free pages, the next one to be handed out last."""
+        out = (c_int * self.num_pages)()
+        n = self._lib.airun_pool_free_list(self._h, out, self.num_pages)
+        return list(out[:n])
 
 
 @dataclass
@@ -98,7 +159,7 @@ class PagedGroup:
     spec: PagedKVSpec
     owners: List[int]                 # entries of the execution order that own a cache in this group
     page_size: int
-    allocator: PageAllocator
+    allocator: Optional[PageAllocator] = None
 
     @property
     def window(self) -> int:
@@ -112,13 +173,25 @@ class StateGroup:
     owners: List[int]
 
 
-@dataclass
 class RequestCache:
-    rid: Hashable
-    slot: int
-    num_tokens: int = 0                                  # tokens whose cache content is final
-    reserved: int = 0                                    # tokens pages are held for (>= num_tokens)
-    blocks: Dict[int, List[int]] = field(default_factory=dict)   # gid -> page id per block, -1 = given back
+    """A live request as the manager sees it: its slot, and views of its counters and pages."""
+
+    __slots__ = ("rid", "slot", "_m")
+
+    def __init__(self, rid: Hashable, slot: int, manager: "CacheManager"):
+        self.rid, self.slot, self._m = rid, slot, manager
+
+    @property
+    def num_tokens(self) -> int:                   # tokens whose cache content is final
+        return self._m._lib.airun_cache_num_tokens(self._m._h, self.slot)
+
+    @property
+    def reserved(self) -> int:                     # tokens pages are held for (>= num_tokens)
+        return self._m._lib.airun_cache_reserved(self._m._h, self.slot)
+
+    @property
+    def blocks(self) -> Dict[int, List[int]]:      # gid -> page id per block, -1 = given back
+        return {g.gid: self._m._blocks(self.slot, g.gid) for g in self._m.paged}
 
 
 @dataclass
@@ -145,6 +218,8 @@ class CacheManager:
         ``cache_from[i]`` the entry whose cache entry i reads instead of its own."""
         if page_size <= 0:
             raise ValueError("page_size must be positive")
+        if num_pages <= 0:
+            raise ValueError("a page pool needs at least one page")
         self.page_size, self.num_pages, self.max_requests = page_size, num_pages, max_requests
         self.paged: List[PagedGroup] = []
         self.state: List[StateGroup] = []
@@ -162,7 +237,7 @@ class CacheManager:
             elif isinstance(spec, PagedKVSpec):
                 g = next((g for g in self.paged if g.spec == spec), None)
                 if g is None:
-                    g = PagedGroup(len(self.paged), spec, [], page_size, PageAllocator(num_pages))
+                    g = PagedGroup(len(self.paged), spec, [], page_size)
                     self.paged.append(g)
                 g.owners.append(i)
                 self.bindings.append(CacheBinding("paged", g.gid, len(g.owners) - 1, False))
@@ -175,25 +250,46 @@ class CacheManager:
                 self.bindings.append(CacheBinding("state", g.gid, len(g.owners) - 1, False))
             else:
                 raise TypeError(f"entry {i} has an unknown cache spec {spec!r}")
-        self.requests: Dict[Hashable, RequestCache] = {}
-        self._free_slots: List[int] = list(range(max_requests - 1, -1, -1))
-        # Host mirror of every request's block table, one row per request slot, so that a step
-        # gathers the rows of its batch with one array operation instead of a loop over requests.
         self.max_blocks = int(max_blocks) if max_blocks else num_pages
-        self.tables = [np.full((max_requests, self.max_blocks), -1, dtype=np.int32) for _ in self.paged]
+        self._lib = _lib()
+        n = len(self.paged)
+        self._h = self._lib.airun_cache_create(n, _ints([g.window for g in self.paged] or [0]), page_size, num_pages,
+                                               max_requests, self.max_blocks, 1 if self.state else 0)
+        if not self._h:
+            raise ValueError("the cache core refuses these sizes")
+        for g in self.paged:
+            g.allocator = PageAllocator(num_pages, _borrowed=self._lib.airun_cache_pool(self._h, g.gid))
+        # The core's mirror of every request's block table, one row per request slot: a step
+        # copies the rows of its batch from here.
+        self.tables = [np.ctypeslib.as_array(self._lib.airun_cache_table(self._h, g.gid),
+                                             shape=(max_requests, self.max_blocks)) for g in self.paged]
+        self.requests: Dict[Hashable, RequestCache] = {}
+        self._need = (c_int * max(n, 1))()
+        self._copies = (c_int * (3 * max(n, 1)))()
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            self.tables = []
+            self._lib.airun_cache_destroy(self._h)
+            self._h = None
+
+    def _check(self, status: int, rid: Hashable = None) -> None:
+        if status:
+            _raise(status, self._lib.airun_cache_error(self._h), f"request {rid!r}" if rid is not None else "")
 
     # ------------------------------------------------------------ requests
     def add_request(self, rid: Hashable) -> RequestCache:
         if rid in self.requests:
             raise CacheError(f"request {rid!r} is already live")
-        if not self._free_slots:
+        slot = self._lib.airun_cache_add(self._h)
+        if slot < 0:
             raise CacheError(f"all {self.max_requests} request slots are in use")
-        rc = RequestCache(rid, self._free_slots.pop(), blocks={g.gid: [] for g in self.paged})
+        rc = RequestCache(rid, slot, self)
         self.requests[rid] = rc
         return rc
 
     def has_free_slot(self) -> bool:
-        return bool(self._free_slots)
+        return bool(self._lib.airun_cache_has_free_slot(self._h))
 
     def get(self, rid: Hashable) -> RequestCache:
         try:
@@ -201,71 +297,46 @@ class CacheManager:
         except KeyError:
             raise CacheError(f"request {rid!r} is not live") from None
 
-    def _blocks_for(self, n_tokens: int) -> int:
-        return (n_tokens + self.page_size - 1) // self.page_size
-
     def pages_needed(self, rid: Hashable, n_new: int) -> Dict[int, int]:
         """Pages each paged group would have to hand out to hold ``n_new`` more tokens."""
-        rc = self.get(rid)
-        want = self._blocks_for(rc.num_tokens + n_new)
-        return {g.gid: max(0, want - len(rc.blocks[g.gid])) for g in self.paged}
+        self._check(self._lib.airun_cache_pages_needed(self._h, self.get(rid).slot, int(n_new), self._need), rid)
+        return {g.gid: self._need[g.gid] for g in self.paged}
 
     def can_reserve(self, rid: Hashable, n_new: int, already: Optional[Dict[int, int]] = None) -> bool:
         need = self.pages_needed(rid, n_new)
         return all(need[g.gid] + (already or {}).get(g.gid, 0) <= g.allocator.num_free for g in self.paged)
 
     def reserve(self, rid: Hashable, n_new: int, need: Optional[Dict[int, int]] = None) -> None:
-        """Takes the pages for the next ``n_new`` tokens in every group, or none at all.
-        ``need`` may carry the result of ``pages_needed(rid, n_new)`` if the caller has it."""
-        rc = self.get(rid)
-        if need is None:
-            need = self.pages_needed(rid, n_new)
-        for g in self.paged:
-            if need[g.gid] > g.allocator.num_free:
-                raise OutOfPages(f"request {rid!r} needs {need[g.gid]} pages in group {g.gid}, "
-                                 f"{g.allocator.num_free} free")
-        for g in self.paged:
-            if need[g.gid]:
-                blocks = rc.blocks[g.gid]
-                first = len(blocks)
-                blocks.extend(g.allocator.take(need[g.gid]))
-                if len(blocks) <= self.max_blocks:
-                    self.tables[g.gid][rc.slot, first:len(blocks)] = blocks[first:]
-        rc.reserved = max(rc.reserved, rc.num_tokens + n_new)
+        """Takes the pages for the next ``n_new`` tokens in every group, or none at all."""
+        self.reserve_many([rid], [n_new])
+
+    def reserve_many(self, rids: Sequence[Hashable], n_new: Sequence[int]) -> None:
+        """Takes the pages for the next tokens of all listed requests, or of none."""
+        slots = [self.get(r).slot for r in rids]
+        self._check(self._lib.airun_cache_reserve_many(self._h, len(slots), _ints(slots), _longs(list(n_new))),
+                    rids[0] if len(rids) == 1 else None)
 
     def commit(self, rid: Hashable, n_new: int) -> None:
         """The step wrote ``n_new`` tokens; pages a window has passed are given back."""
-        rc = self.get(rid)
-        if rc.num_tokens + n_new > rc.reserved:
-            raise CacheError(f"request {rid!r}: {n_new} tokens committed beyond the reserved pages")
-        rc.num_tokens += n_new
-        for g in self.paged:
-            if g.window > 0:
-                # the next query sits at position num_tokens and sees keys j > num_tokens - window
-                last_dead = rc.num_tokens - g.window
-                blocks = rc.blocks[g.gid]
-                b = 0
-                while b < len(blocks) and (b + 1) * self.page_size - 1 <= last_dead:
-                    if blocks[b] >= 0:
-                        g.allocator.give_back(blocks[b])
-                        blocks[b] = -1
-                        if b < self.max_blocks:
-                            self.tables[g.gid][rc.slot, b] = -1
-                    b += 1
+        self.commit_many([rid], [n_new])
+
+    def commit_many(self, rids: Sequence[Hashable], n_new: Sequence[int]) -> None:
+        slots = [self.get(r).slot for r in rids]
+        self._check(self._lib.airun_cache_commit_many(self._h, len(slots), _ints(slots), _longs(list(n_new))),
+                    rids[0] if len(rids) == 1 else None)
 
     def free_request(self, rid: Hashable) -> None:
         rc = self.requests.pop(rid, None)
         if rc is None:
             raise CacheError(f"request {rid!r} is freed twice or was never added")
-        for g in self.paged:
-            for p in rc.blocks[g.gid]:
-                if p >= 0:
-                    g.allocator.give_back(p)
-            self.tables[g.gid][rc.slot, :min(len(rc.blocks[g.gid]), self.max_blocks)] = -1
-        self._free_slots.append(rc.slot)
+        self._check(self._lib.airun_cache_free(self._h, rc.slot), rid)
 
     # ------------------------------------------------------------ sharing and rewinding
-    def fork(self, parent: Hashable, child: Hashable) -> "CopyPlan":
+    def _plan(self, n: int, state: Optional[Tuple[int, int]] = None) -> CopyPlan:
+        c = self._copies
+        return CopyPlan([(c[3 * i], c[3 * i + 1], c[3 * i + 2]) for i in range(n)], state)
+
+    def fork(self, parent: Hashable, child: Hashable) -> CopyPlan:
         """Makes ``child`` a live request holding the same ``num_tokens`` tokens as ``parent``.
         Whole pages are shared (one more holder); a last page that is only partly filled is the
         place both would write next, so the child gets a fresh one.  Returns the copies the caller
@@ -274,77 +345,44 @@ class CacheManager:
         prc = self.get(parent)
         if child in self.requests:
             raise CacheError(f"request {child!r} is already live")
-        if not self._free_slots:
-            raise CacheError(f"all {self.max_requests} request slots are in use")
-        n = prc.num_tokens
-        full, part = divmod(n, self.page_size)
-        for g in self.paged:
-            if part and prc.blocks[g.gid][full] >= 0 and g.allocator.num_free < 1:
-                raise OutOfPages(f"forking {parent!r} needs a page in group {g.gid}, none is free")
-        crc = RequestCache(child, self._free_slots.pop(), num_tokens=n, reserved=n,
-                           blocks={g.gid: [] for g in self.paged})
-        plan = CopyPlan(state=(prc.slot, crc.slot) if self.state else None)
-        for g in self.paged:
-            src = prc.blocks[g.gid]
-            blocks = list(src[:full])
-            for p in blocks:
-                if p >= 0:
-                    g.allocator.share(p)
-            if part:
-                if src[full] >= 0:
-                    new = g.allocator.take(1)[0]
-                    plan.pages.append((g.gid, src[full], new))
-                    blocks.append(new)
-                else:
-                    blocks.append(-1)
-            crc.blocks[g.gid] = blocks
-            self.tables[g.gid][crc.slot, :min(len(blocks), self.max_blocks)] = blocks[:self.max_blocks]
-        self.requests[child] = crc
-        return plan
+        slot, n = c_int(-1), c_int(0)
+        self._check(self._lib.airun_cache_fork(self._h, prc.slot, ctypes.byref(slot), self._copies, ctypes.byref(n)),
+                    parent)
+        self.requests[child] = RequestCache(child, slot.value, self)
+        return self._plan(n.value, (prc.slot, slot.value) if self.state else None)
 
-    def truncate(self, rid: Hashable, n_tokens: int) -> "CopyPlan":
+    def truncate(self, rid: Hashable, n_tokens: int) -> CopyPlan:
         """Moves the end of ``rid`` back to ``n_tokens``: pages wholly past it are given back, and
         if the page that is written next has other holders the request gets a copy of its own
         (returned for the caller to run on the device).  Fixed-size state cannot be moved back, and
         neither can a window whose pages are gone."""
-        rc = self.get(rid)
-        if not (0 <= n_tokens <= rc.num_tokens):
-            raise CacheError(f"request {rid!r} holds {rc.num_tokens} tokens and cannot be cut to {n_tokens}")
-        if n_tokens == rc.num_tokens and rc.reserved == rc.num_tokens:
-            return CopyPlan()
-        if self.state and n_tokens < rc.num_tokens:
-            raise CacheError("a request with fixed-size state cannot be moved back, only restarted")
-        full, part = divmod(n_tokens, self.page_size)
-        for g in self.paged:
-            blocks = rc.blocks[g.gid]
-            if g.window > 0 and n_tokens > 0:
-                first_needed = max(0, n_tokens - g.window + 1) // self.page_size
-                if first_needed < len(blocks) and blocks[first_needed] < 0:
-                    raise CacheError(f"request {rid!r}: the window's pages before token {n_tokens} were given back")
-            if part and blocks[full] >= 0 and g.allocator.holders(blocks[full]) > 1 and g.allocator.num_free < 1:
-                raise OutOfPages(f"cutting {rid!r} inside a shared page needs a page in group {g.gid}")
-        plan = CopyPlan()
-        keep = full + (1 if part else 0)
-        for g in self.paged:
-            blocks = rc.blocks[g.gid]
-            for p in blocks[keep:]:
-                if p >= 0:
-                    g.allocator.give_back(p)
-            self.tables[g.gid][rc.slot, keep:min(len(blocks), self.max_blocks)] = -1
-            del blocks[keep:]
-            if part and blocks[full] >= 0 and g.allocator.holders(blocks[full]) > 1:
-                new = g.allocator.take(1)[0]
-                plan.pages.append((g.gid, blocks[full], new))
-                g.allocator.give_back(blocks[full])
-                blocks[full] = new
-                if full < self.max_blocks:
-                    self.tables[g.gid][rc.slot, full] = new
-        rc.num_tokens = rc.reserved = n_tokens
-        return plan
+        n = c_int(0)
+        self._check(self._lib.airun_cache_truncate(self._h, self.get(rid).slot, int(n_tokens), self._copies,
+                                                   ctypes.byref(n)), rid)
+        return self._plan(n.value)
+
+    # ------------------------------------------------------------ the batch of a step
+    def build_batch(self, rids: Sequence[Hashable], qlens: Sequence[int], tokens: np.ndarray,
+                    want_counts: Sequence[int], want: Sequence[int], base_ptr: int, offsets: ctypes.Array,
+                    max_reqs: int, bt_cols: int, pad_to: int, pad_want: int) -> Tuple[int, int, int, int, List[int]]:
+        """Lays the batch of a step into the staging buffer at ``base_ptr`` (see csrc/host_core.cpp).
+        Returns (tokens, wanted rows, longest context, longest portion, slots)."""
+        slots = [self.requests[r].slot for r in rids]
+        out = (c_longlong * 4)()
+        self._check(self._lib.airun_cache_build_batch(
+            self._h, len(slots), _ints(slots), _ints(list(qlens)), tokens.ctypes.data, _ints(list(want_counts) or [0]),
+            _ints(list(want) or [0]), base_ptr, offsets, max_reqs, bt_cols, pad_to, pad_want, out))
+        return out[0], out[1], out[2], out[3], slots
 
     # ------------------------------------------------------------ views
+    def _blocks(self, slot: int, gid: int) -> List[int]:
+        n = self._lib.airun_cache_num_blocks(self._h, slot, gid)
+        out = (c_int * max(n, 1))()
+        self._lib.airun_cache_blocks(self._h, slot, gid, out, n)
+        return list(out[:n])
+
     def block_table(self, rid: Hashable, gid: int) -> List[int]:
-        return self.get(rid).blocks[gid]
+        return self._blocks(self.get(rid).slot, gid)
 
     def free_pages(self) -> Dict[int, int]:
         return {g.gid: g.allocator.num_free for g in self.paged}
@@ -354,38 +392,13 @@ class CacheManager:
         return self.num_pages * self.page_size
 
     def check_invariants(self) -> None:
-        """No page lost, none held twice: every page is either free or in exactly
-        ``holders`` block tables."""
-        for g in self.paged:
-            seen: Dict[int, int] = {}
-            for rc in self.requests.values():
-                for p in rc.blocks[g.gid]:
-                    if p >= 0:
-                        seen[p] = seen.get(p, 0) + 1
-            free = g.allocator._free
-            if len(set(free)) != len(free):
-                raise CacheError(f"group {g.gid}: a page is on the free list twice")
-            for p in free:
-                if p in seen:
-                    raise CacheError(f"group {g.gid}: page {p} is both free and held")
-            for p, n in seen.items():
-                if g.allocator.holders(p) != n:
-                    raise CacheError(f"group {g.gid}: page {p} is in {n} tables but has "
-                                     f"{g.allocator.holders(p)} holders")
-            if len(free) + len(seen) != g.allocator.num_pages:
-                raise CacheError(f"group {g.gid}: {g.allocator.num_pages - len(free) - len(seen)} pages are lost")
-            for rc in self.requests.values():
-                b = rc.num_tokens // self.page_size
-                blocks = rc.blocks[g.gid]
-                for p in blocks[b:]:
-                    if p >= 0 and g.allocator.holders(p) != 1:
-                        raise CacheError(f"group {g.gid}: request {rc.rid!r} would write page {p}, which "
-                                         f"{g.allocator.holders(p)} tables hold")
-        slots = [rc.slot for rc in self.requests.values()]
-        if len(set(slots)) != len(slots) or set(slots) & set(self._free_slots):
-            raise CacheError("a request slot is held twice")
-        if len(slots) + len(self._free_slots) != self.max_requests:
-            raise CacheError("a request slot is lost")
+        """No page lost, none held twice, none both free and held; every page is in exactly
+        ``holders`` block tables; the page a request writes next has no other holder; no request
+        slot lost or held twice."""
+        self._check(self._lib.airun_cache_check(self._h))
+        if len(self.requests) != self._lib.airun_cache_num_live(self._h) or \
+                len({rc.slot for rc in self.requests.values()}) != len(self.requests):
+            raise CacheError("the request ids and the core's slots do not match")
 
 
 class CacheStorage:

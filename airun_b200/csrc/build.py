@@ -1,6 +1,7 @@
-"""Compiles the CUDA sources for sm_100a with nvcc and loads them with ctypes.
+"""Compiles the CUDA sources for sm_100a with nvcc (and the host-only ``.cpp`` sources with the
+C++ compiler) and loads them with ctypes.
 
-Each ``.cu`` file becomes one shared library, built the first time something
+Each ``.cu`` or ``.cpp`` file becomes one shared library, built the first time something
 needs it and kept next to the sources (``csrc/_build/``; a temporary folder when
 the package folder is read-only).  The library name carries a hash of the
 source, the shared headers, the flags and the ``-D`` defines, so an edited file
@@ -44,6 +45,16 @@ def find_nvcc() -> str:
                      "(set CUDA_HOME or AIRUN_NVCC)")
 
 
+HOST_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden", "-Wall"]
+
+
+def find_cxx() -> str:
+    for cand in (os.environ.get("CXX"), shutil.which("g++"), shutil.which("c++"), shutil.which("clang++")):
+        if cand and (os.path.isfile(cand) or shutil.which(cand)):
+            return shutil.which(cand) or cand
+    raise BuildError("no C++ compiler found (g++, c++ or $CXX): the host core of airun_b200 is compiled at first use")
+
+
 _BUILD_DIR: Optional[str] = None
 
 
@@ -75,7 +86,8 @@ def _key(source: str, defines: Sequence[Tuple[str, object]], extra: Sequence[str
         with open(p, "rb") as f:
             h.update(os.path.basename(p).encode())
             h.update(f.read())
-    h.update(repr((ARCH_FLAGS, BASE_FLAGS, sorted(defines), list(extra))).encode())
+    flags = HOST_FLAGS if source.endswith(".cpp") else (ARCH_FLAGS, BASE_FLAGS)
+    h.update(repr((flags, sorted(defines), list(extra))).encode())
     return h.hexdigest()[:16]
 
 
@@ -83,7 +95,9 @@ def library_path(name: str, defines: Optional[Dict[str, object]] = None,
                  extra_flags: Sequence[str] = ()) -> Tuple[str, str, List[Tuple[str, object]]]:
     source = os.path.join(CSRC_DIR, name + ".cu")
     if not os.path.isfile(source):
-        raise BuildError(f"kernel source {source} is missing")
+        source = os.path.join(CSRC_DIR, name + ".cpp")
+    if not os.path.isfile(source):
+        raise BuildError(f"source {os.path.join(CSRC_DIR, name)}.cu / .cpp is missing")
     defs = sorted((defines or {}).items())
     tag = "".join(f"_{k}{v}" for k, v in defs)
     return (os.path.join(_build_dir(), f"lib{name}{tag}_{_key(source, defs, extra_flags)}.so"), source, defs)
@@ -92,6 +106,9 @@ def library_path(name: str, defines: Optional[Dict[str, object]] = None,
 def compile_command(name: str, defines: Optional[Dict[str, object]] = None,
                     extra_flags: Sequence[str] = (), out: Optional[str] = None) -> List[str]:
     path, source, defs = library_path(name, defines, extra_flags)
+    if source.endswith(".cpp"):
+        return ([find_cxx()] + HOST_FLAGS + list(extra_flags) + [f"-D{k}={v}" for k, v in defs]
+                + ["-I", CSRC_DIR, "-o", out or path, source])
     return ([find_nvcc()] + ARCH_FLAGS + BASE_FLAGS + list(extra_flags)
             + [f"-D{k}={v}" for k, v in defs] + ["-I", CSRC_DIR, "-o", out or path, source])
 
@@ -106,7 +123,8 @@ def build(name: str, defines: Optional[Dict[str, object]] = None,
     cmd = compile_command(name, defines, extra_flags, out=tmp)
     label = os.path.basename(source) + ("" if not defs else " " + " ".join(f"{k}={v}" for k, v in defs))
     if not quiet:
-        print(f"[airun_b200] compiling {label} for sm_100a ...", file=sys.stderr, flush=True)
+        print(f"[airun_b200] compiling {label}" + ("" if source.endswith(".cpp") else " for sm_100a") + " ...",
+              file=sys.stderr, flush=True)
     t0 = time.time()
     proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     done = threading.Event()
@@ -123,7 +141,7 @@ def build(name: str, defines: Optional[Dict[str, object]] = None,
     if proc.returncode != 0:
         if os.path.exists(tmp):
             os.unlink(tmp)
-        raise BuildError(f"nvcc failed on {source} (exit {proc.returncode}):\n{' '.join(cmd)}\n{out}")
+        raise BuildError(f"{os.path.basename(cmd[0])} failed on {source} (exit {proc.returncode}):\n{' '.join(cmd)}\n{out}")
     os.replace(tmp, path)
     # libraries of older versions of this source (another hash) are of no use any more
     prefix = os.path.basename(path).rsplit("_", 1)[0] + "_"

@@ -14,6 +14,7 @@ chunk returns nothing and does not synchronise (runtime.rs:2032-2037).
 """
 from __future__ import annotations
 
+import ctypes
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence
 
@@ -65,6 +66,9 @@ class StepRunner:
         self.meta_host, self.meta_np, self._meta_event = self._ring[0]
         self._ring_used = [False] * 4
         self.meta_dev = torch.zeros(off, dtype=torch.int32, device=self.device)
+        names = ["token_ids", "positions", "req_of_token", "want_rows", "cu_tokens", "context_lens", "state_slots"]
+        names += [f"bt{g}" for g in range(n_groups)]
+        self._offs = (ctypes.c_longlong * len(names))(*[self.offsets[n][0] for n in names])
         self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.ws_main = Workspace(self.device)
         self.ws_pair = (Workspace(self.device), Workspace(self.device))
@@ -130,95 +134,31 @@ class StepRunner:
 
     def reserve(self, entries: Sequence[StepEntry]) -> None:
         """Takes the pages of all entries, or of none."""
-        m = self.manager
-        ps = m.page_size
-        if all(len(e.tokens) == 1 for e in entries):
-            # single tokens: a page is needed only by the requests whose next token opens a block
-            # (every paged group holds the same number of blocks for a request)
-            reqs = m.requests
-            if m.paged:
-                g0 = m.paged[0].gid
-                opening = [e for e in entries if len(reqs[e.rid].blocks[g0]) * ps <= reqs[e.rid].num_tokens]
-            else:
-                opening = []
-            for e in entries:
-                rc = reqs[e.rid]
-                if rc.reserved <= rc.num_tokens:
-                    rc.reserved = rc.num_tokens + 1
-            if not opening:
-                return
-            entries = opening
-        needs = [m.pages_needed(e.rid, len(e.tokens)) for e in entries]
-        total: Dict[int, int] = {}
-        for need in needs:
-            for gid, n in need.items():
-                if n:
-                    total[gid] = total.get(gid, 0) + n
-        if total:
-            free = m.free_pages()
-            for gid, n in total.items():
-                if n > free[gid]:
-                    raise OutOfPages(f"the step needs {n} pages in group {gid}, {free[gid]} are free")
-        for e, need in zip(entries, needs):
-            m.reserve(e.rid, len(e.tokens), need)
+        self.manager.reserve_many([e.rid for e in entries], [len(e.tokens) for e in entries])
 
     def build_context(self, entries: Sequence[StepEntry], pad_to: int = 0, pad_want: int = 0) -> tuple:
         """Fills the staging buffer and returns (StepContext, n_want).  With ``pad_to`` the
         batch is padded with rows that belong to no request (request -1, position -1), which
         every kernel skips, and with requests that bring no tokens; that is how a captured graph
-        of a fixed size runs a smaller batch.  ``pad_want`` pads the wanted rows with row 0."""
+        of a fixed size runs a smaller batch.  ``pad_want`` pads the wanted rows with row 0.
+        The arrays are laid out by the native core (csrc/host_core.cpp: build_batch)."""
         m = self.manager
         self._ring_i = (self._ring_i + 1) % len(self._ring)
         self.meta_host, self.meta_np, self._meta_event = self._ring[self._ring_i]
         if self._ring_used[self._ring_i] and self._meta_event is not None:
             self._meta_event.synchronize()      # the copy that last read this buffer is done
-        tok, pos, rot, want = (self._view(n, dev=False) for n in ("token_ids", "positions", "req_of_token", "want_rows"))
-        cu, cl, sl = (self._view(n, dev=False) for n in ("cu_tokens", "context_lens", "state_slots"))
         R = len(entries)
-        rcs = [m.requests[e.rid] for e in entries]
         qlens = [len(e.tokens) for e in entries]
-        starts = [rc.num_tokens for rc in rcs]
-        clens = [s0 + q for s0, q in zip(starts, qlens)]
-        slots = [rc.slot for rc in rcs]
-        n_want = 0
-        if all(q == 1 for q in qlens):                     # single tokens: everything is one array operation
-            t = R
-            tok[:R] = [e.tokens[0] for e in entries]
-            pos[:R] = starts
-            rot[:R] = np.arange(R, dtype=np.int32)
-            cu[:R] = rot[:R]
-            for r, e in enumerate(entries):
-                for w in e.want:
-                    want[n_want] = r + w
-                    n_want += 1
+        if max(qlens) == 1:
+            toks = np.fromiter((e.tokens[0] for e in entries), dtype=np.int32, count=R)
         else:
-            t = 0
-            for r, e in enumerate(entries):
-                n = qlens[r]
-                tok[t:t + n] = e.tokens
-                pos[t:t + n] = np.arange(starts[r], starts[r] + n, dtype=np.int32)
-                rot[t:t + n] = r
-                for w in e.want:
-                    want[n_want] = t + w
-                    n_want += 1
-                cu[r] = t
-                t += n
-        cl[:R] = clens
-        sl[:R] = slots
-        need_blocks = min((max(clens) + m.page_size - 1) // m.page_size, m.max_blocks, self.max_blocks)
-        for g in m.paged:                                   # the block-table rows of the batch, gathered by slot
-            bt = self._view(f"bt{g.gid}", dev=False).reshape(self.R_max, self.max_blocks)
-            bt[:R, :need_blocks] = m.tables[g.gid][slots, :need_blocks]
-        cu[len(entries)] = t
-        if pad_to:
-            cu[R:self.R_max + 1] = t
-        if pad_want > n_want:
-            want[n_want:pad_want] = 0
-        if pad_to > t:
-            tok[t:pad_to] = 0
-            pos[t:pad_to] = -1
-            rot[t:pad_to] = -1
-            t = pad_to
+            toks = np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries])
+        want = [w for e in entries for w in e.want]
+        t, n_want, max_ctx, max_q, slots = m.build_batch(
+            [e.rid for e in entries], qlens, toks, [len(e.want) for e in entries], want,
+            self.meta_host.data_ptr(), self._offs, self.R_max, self.max_blocks, pad_to, pad_want)
+        clens = self._view("context_lens", dev=False)[:R].tolist()
+        t = max(t, pad_to)
         self.meta_dev.copy_(self.meta_host, non_blocking=True)
         if self._meta_event is not None:
             self._meta_event.record()
@@ -230,8 +170,8 @@ class StepRunner:
             context_lens=self._view("context_lens"), state_slots=self._view("state_slots"),
             err=self.err, ws_pair=self.ws_pair, ws_main=self.ws_main, caches=self._cache_views(),
             query_lens=qlens, context_lens_host=clens, state_slots_host=slots,
-            max_query_len=max(qlens), max_context_len=max(clens),
-            decode_only=all(q == 1 for q in qlens))
+            max_query_len=max_q, max_context_len=max_ctx,
+            decode_only=max_q == 1)
         return ctx, n_want
 
     def step(self, entries: Sequence[StepEntry], checked: bool = False) -> Optional[torch.Tensor]:
@@ -249,8 +189,7 @@ class StepRunner:
         else:
             ctx, n_want = self.build_context(entries)
             logits = self.model.forward(ctx, self._view("want_rows"), n_want)
-        for e in entries:
-            self.manager.commit(e.rid, len(e.tokens))
+        self.manager.commit_many([e.rid for e in entries], [len(e.tokens) for e in entries])
         self.steps_run += 1
         return logits
 

@@ -172,3 +172,37 @@ def test_long_context_in_portions_then_decoding():
     for i in range(outs["float32"].shape[0]):
         assert cosine(outs["float32"][i], outs["bfloat16"][i]) > 0.999, i
     assert np.mean(outs["float32"].argmax(-1) == outs["bfloat16"].argmax(-1)) > 0.9
+
+
+def test_layers_of_the_8b_size_bfloat16_agrees_with_float32():
+    """Two layers with the sizes of the benchmark's model (hidden 4096, 32/8 heads of 128,
+    intermediate 12288, vocabulary 151936): a 200-token prompt in two portions, then eight single
+    tokens, the bfloat16 path against the float32 path on the same weights."""
+    import airun_b200
+    from airun_b200 import StepEntry
+    cfg = airun_b200.Qwen3Config.from_dict(dict(
+        architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=151936, hidden_size=4096,
+        num_hidden_layers=2, num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=12288,
+        max_position_embeddings=40960, rms_norm_eps=1e-6, rope_theta=1000000.0, tie_word_embeddings=False))
+    g = np.random.default_rng(12)
+    seq = [int(t) for t in g.integers(0, 151936, size=208)]
+    outs = {}
+    for dt in ("float32", "bfloat16"):
+        eng = airun_b200.Engine.from_config(cfg, seed=6, dtype=dt, page_size=16, cache_tokens=512,
+                                            max_batch_tokens=256, max_requests=2, max_context=512)
+        eng.manager.add_request("r")
+        rows = [eng.runner.step([StepEntry("r", seq[:130], (0, 64, 129))]).float().cpu().numpy(),
+                eng.runner.step([StepEntry("r", seq[130:200], (69,))]).float().cpu().numpy()]
+        for t in seq[200:]:
+            rows.append(eng.runner.step([StepEntry("r", [t], (0,))]).float().cpu().numpy())
+        eng.runner.raise_on_device_error()
+        outs[dt] = np.concatenate(rows)
+        del eng
+        torch.cuda.empty_cache()
+    assert outs["float32"].shape == (12, 151936)
+    for i in range(12):
+        assert cosine(outs["float32"][i], outs["bfloat16"][i]) > 0.999, i
+        # the token the bfloat16 path picks is, on the float32 path, within bfloat16's own noise of the best
+        pick = int(outs["bfloat16"][i].argmax())
+        noise = float(np.abs(outs["float32"][i] - outs["bfloat16"][i]).max())
+        assert outs["float32"][i].max() - outs["float32"][i][pick] <= 2 * noise, i
