@@ -89,6 +89,10 @@ def build_parser() -> argparse.ArgumentParser:
 
     ins = sub.add_parser("inspect", help="print the configuration of a model folder")
     ins.add_argument("model")
+
+    st = sub.add_parser("selftest", help="every kernel against a plain reference of the same operation")
+    st.add_argument("--device", type=int, default=0)
+    st.add_argument("--verbose", action="store_true")
     return ap
 
 
@@ -259,10 +263,16 @@ def cmd_inspect(a) -> int:
     return 0
 
 
+def cmd_selftest(a) -> int:
+    """The reference's ``airun selftest --device N --verbose`` (crates/airun-cli/src/selftest.rs:13-22)."""
+    from . import selftest
+    return selftest.run(a.device, a.verbose)
+
+
 def main(argv: Optional[List[str]] = None) -> int:
     a = build_parser().parse_args(argv)
     return {"run": cmd_run, "bench": cmd_bench, "perplexity": cmd_perplexity, "init": cmd_init,
-            "inspect": cmd_inspect}[a.cmd](a)
+            "inspect": cmd_inspect, "selftest": cmd_selftest}[a.cmd](a)
 
 
 if __name__ == "__main__":

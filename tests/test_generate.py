@@ -190,3 +190,10 @@ def test_cutting_a_request_back_and_going_on(folders):
     from helpers import assert_close
     assert_close(got[:9], want_a, "float32", "request cut at a page's edge")
     assert_close(got[9:], want_b, "float32", "fork cut inside a shared page")
+
+
+def test_selftest_subcommand_passes():
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "airun"), "selftest", "--verbose"],
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "FAIL" not in r.stdout and "checks passed" in r.stdout
