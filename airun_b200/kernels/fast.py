@@ -108,7 +108,9 @@ def plan_gemm(M: int, N: int, K: int) -> Tuple[bool, int, int]:
     """(swap, bn, ksplit) for a product of M tokens with an [N, K] weight.
 
     Up to 128 tokens the weights are the 128-row operand (swap) and the K range is cut until about
-    TARGET_CTAS CTAs stream them.  Above that, tiles of 128 x 256 on the persistent kernel once
+    TARGET_CTAS CTAs stream them (half as many from 17 tokens on, where the partial tiles that
+    cutting K sends through memory are larger, and then at most 4 slices), a slice keeping at
+    least 10 K-steps.  Above that, tiles of 128 x 256 on the persistent kernel once
     there are 96 of them; fewer tiles leave SMs idle, so the tile narrows to 128 x 128, and only
     if that still fills less than one wave and a slice keeps 32 K-steps is K cut as well (cutting K
     costs a round trip of partial tiles through memory: timed on the Qwen3-1.7B and -8B shapes at 192
@@ -117,7 +119,8 @@ def plan_gemm(M: int, N: int, K: int) -> Tuple[bool, int, int]:
     if M <= 128:
         bn = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128
         tiles = (N + 127) // 128
-        ksplit = max(1, min(TARGET_CTAS // tiles, kb // 4)) if tiles < TARGET_CTAS else 1
+        target = TARGET_CTAS if M <= 16 else TARGET_CTAS // 2
+        ksplit = max(1, min(target // tiles, kb // 10, 64 if M <= 16 else 4)) if tiles < target else 1
         return True, bn, ksplit
     mt = (M + 127) // 128
     if N >= 256 and mt * ((N + 255) // 256) >= 96:
