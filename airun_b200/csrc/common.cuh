@@ -64,6 +64,33 @@ static inline void airun_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block,
     if (e != cudaSuccess && airun_launch_rc == 0) airun_launch_rc = (int)e;
 }
 
+// The same with thread-block clusters of (1, 1, cluster_z) CTAs (grid.z must be a multiple of it).
+template <typename... KArgs, typename... Args>
+static inline void airun_launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                        unsigned cluster_z, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int n = 0;
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = 1;
+    attr[n].val.clusterDim.y = 1;
+    attr[n].val.clusterDim.z = cluster_z;
+    ++n;
+    if (airun_pdl_enabled()) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = n;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+    if (e != cudaSuccess && airun_launch_rc == 0) airun_launch_rc = (int)e;
+}
+
 static inline int airun_launch_status() {
     cudaError_t e = cudaGetLastError();
     int rc = airun_launch_rc;

@@ -82,6 +82,27 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
 }
+// ---- thread-block clusters: the rank of this CTA, a barrier over all threads of all CTAs, and loads
+// from a peer's shared memory
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ float ld_cluster_f32(uint32_t addr) {
+    float v;
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+    return v;
+}
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t cols) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(cols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -148,6 +169,8 @@ struct GemmParams {
     const float* norm_w;          // [weight rows] weight of the norm that follows (EPI_RESID)
     float* ssq_out;               // [parts][ssq_out_ld] (EPI_RESID)
     int ssq_out_ld;
+    int cluster_reduce;           // the ksplit CTAs of a tile are one cluster and add their slices through
+                                  // distributed shared memory instead of the scratch
 };
 
 template <int BN, int STAGES>
@@ -305,7 +328,10 @@ __device__ __forceinline__ void store_resid_swapped(const GemmParams& p, const f
     }
 }
 
-template <int BN, int STAGES, int EPI, bool SWAP>
+// CLUSTER: the build that can add up the slices of a tile through distributed shared memory.  It is a
+// build of its own because the extra code made the plain one slower inside a decode step (by 2 % at
+// batch 8) although nothing of it ran there.
+template <int BN, int STAGES, int EPI, bool SWAP, bool CLUSTER>
 __global__ __launch_bounds__(GEMM_THREADS, 1) void gemm_tcgen05_kernel(
     const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
     using L = SmemLayout<BN, STAGES>;
@@ -357,6 +383,87 @@ __global__ __launch_bounds__(GEMM_THREADS, 1) void gemm_tcgen05_kernel(
     // from here on the results of earlier kernels are read and their buffers written
     pdl_wait();
 
+    // what the epilogue warps (2..5) share between their two phases
+    const int quad = warp & 3;
+    const int a_row = a0 + quad * 32 + lane;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
+    __shared__ float s_scale[SWAP ? BN : 1];
+    float row_scale = 1.0f;
+    bool ok = true;
+    const bool direct = p.ksplit == 1;
+    const bool clustered = CLUSTER && !direct;
+    const int tile = blockIdx.y * gridDim.x + blockIdx.x;
+    // Sums the slices of the tile (or takes the accumulator as it is), applies the epilogue and stores.
+    // rank < 0: all columns, slices from tensor memory (one slice) or from the scratch; rank >= 0: the
+    // chunks of columns that fall to this CTA of the cluster, slices from the peers' shared memory.
+    auto finish_tile = [&](int rank) {
+        float ssq_acc = 0.0f;
+        const float* all = (direct || rank >= 0) ? nullptr : p.scratch + (size_t)tile * p.ksplit * (BN * BM);
+        const uint32_t mine = smem_u32(smem);
+        constexpr int STEP = (EPI == EPI_SWIGLU && !SWAP) ? 32 : 16;
+        for (int c = 0; c < BN; c += STEP) {
+            if (rank >= 0 && (c / STEP) % p.ksplit != rank) continue;
+            float v[16], u[16];
+            if (direct) {
+                if (n_kb > 0) {
+                    tmem_ld16(lane_addr + c, v);
+                    if (STEP == 32) tmem_ld16(lane_addr + c + 16, u);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) { v[i] = 0.0f; u[i] = 0.0f; }
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) { v[i] = 0.0f; u[i] = 0.0f; }
+                // slices are added in order; loads of four slices are in flight at a time
+                for (int s0 = 0; s0 < p.ksplit; s0 += 4) {
+                    float t[4][STEP];
+#pragma unroll
+                    for (int d = 0; d < 4; ++d) {
+                        if (CLUSTER && rank >= 0) {
+                            const uint32_t peer = s0 + d < p.ksplit ? map_to_cta(mine, (uint32_t)(s0 + d)) : 0u;
+#pragma unroll
+                            for (int i = 0; i < STEP; ++i)
+                                t[d][i] = (s0 + d < p.ksplit)
+                                              ? ld_cluster_f32(peer + 4u * (uint32_t)((c + i) * BM + quad * 32 + lane)) : 0.0f;
+                        } else {
+                            const float* ps = all + (size_t)(s0 + d) * (BN * BM) + quad * 32 + lane;
+#pragma unroll
+                            for (int i = 0; i < STEP; ++i)
+                                t[d][i] = (s0 + d < p.ksplit) ? __ldcg(ps + (size_t)(c + i) * BM) : 0.0f;
+                        }
+                    }
+#pragma unroll
+                    for (int d = 0; d < 4; ++d) {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            v[i] += t[d][i];
+                            if (STEP == 32) u[i] += t[d][(STEP == 32 ? 16 : 0) + i];
+                        }
+                    }
+                }
+            }
+            if (p.ssq_in) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float f = SWAP ? s_scale[c + i] : row_scale;
+                    v[i] *= f;
+                    if (STEP == 32) u[i] *= f;
+                }
+            }
+            if (EPI == EPI_SWIGLU) {
+                if (SWAP) store_swiglu_swapped(p, v, a_row, b0, c);
+                else store_swiglu_normal(p, v, u, a_row, b0, c);
+            } else if (EPI == EPI_RESID) {
+                if (SWAP) store_resid_swapped(p, v, a_row, b0, c);
+                else ssq_acc += store_resid_normal(p, v, a_row, b0 + c);
+            } else {
+                store_chunk<EPI, SWAP>(p, v, a_row, b0, c);
+            }
+        }
+        if (EPI == EPI_RESID && !SWAP && a_row < p.a_rows) p.ssq_out[(size_t)blockIdx.y * p.ssq_out_ld + a_row] = ssq_acc;
+    };
+
     if (warp == 0) {
         if (lane == 0) {
             for (int i = 0; i < n_kb; ++i) {
@@ -395,12 +502,7 @@ __global__ __launch_bounds__(GEMM_THREADS, 1) void gemm_tcgen05_kernel(
         }
     } else {
         // epilogue warps 2..5: warp w may touch the 32 TMEM lanes of quadrant w % 4
-        const int quad = warp & 3;
-        const int a_row = a0 + quad * 32 + lane;
-        const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
         // token scales of a normed input, while the MMAs run
-        __shared__ float s_scale[SWAP ? BN : 1];
-        float row_scale = 1.0f;
         if (p.ssq_in) {
             if (SWAP) {
                 for (int j = threadIdx.x - 64; j < BN; j += 128) s_scale[j] = b0 + j < p.b_rows ? token_scale(p, b0 + j) : 0.0f;
@@ -409,16 +511,15 @@ __global__ __launch_bounds__(GEMM_THREADS, 1) void gemm_tcgen05_kernel(
                 row_scale = token_scale(p, a_row);
             }
         }
-        float ssq_acc = 0.0f;
-        bool ok = n_kb == 0 ? true : mbar_wait(accum, 0);
+        ok = n_kb == 0 ? true : mbar_wait(accum, 0);
         if (!ok) { atomicOr(p.err, AIRUN_DEV_TIMEOUT); }
         tc_fence_after();
-        const bool direct = p.ksplit == 1;
         bool last = true;
-        float* part = nullptr;
-        const int tile = blockIdx.y * gridDim.x + blockIdx.x;
         if (!direct) {
-            part = p.scratch + ((size_t)tile * p.ksplit + split) * (BN * BM);
+            // the partial tile goes to this CTA's own shared memory (the stages are free: every MMA is
+            // complete) when the slices of a tile form a cluster, else to the scratch in global memory
+            float* part = clustered ? reinterpret_cast<float*>(smem)
+                                    : p.scratch + ((size_t)tile * p.ksplit + split) * (BN * BM);
             if (ok) {
                 for (int c = 0; c < BN; c += 16) {
                     float v[16];
@@ -431,72 +532,31 @@ __global__ __launch_bounds__(GEMM_THREADS, 1) void gemm_tcgen05_kernel(
                     for (int i = 0; i < 16; ++i) part[(size_t)(c + i) * BM + quad * 32 + lane] = v[i];
                 }
             }
-            __threadfence();
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (threadIdx.x == 64) s_ticket = atomicAdd(p.counters + tile, 1);
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            last = s_ticket == p.ksplit - 1;
-            if (last) {
+            if (clustered) {
+                last = false;                     // the sums are formed after the cluster's barrier, below
+            } else {
                 __threadfence();
-                if (threadIdx.x == 64) p.counters[tile] = 0;       // ready for the next launch
-            }
-        }
-        if (ok && last) {
-            const float* all = direct ? nullptr : p.scratch + (size_t)tile * p.ksplit * (BN * BM);
-            constexpr int STEP = (EPI == EPI_SWIGLU && !SWAP) ? 32 : 16;
-            for (int c = 0; c < BN; c += STEP) {
-                float v[16], u[16];
-                if (direct) {
-                    if (n_kb > 0) {
-                        tmem_ld16(lane_addr + c, v);
-                        if (STEP == 32) tmem_ld16(lane_addr + c + 16, u);
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) { v[i] = 0.0f; u[i] = 0.0f; }
-                    }
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) { v[i] = 0.0f; u[i] = 0.0f; }
-                    // slices are added in order; loads of four slices are in flight at a time
-                    for (int s0 = 0; s0 < p.ksplit; s0 += 4) {
-                        float t[4][STEP];
-#pragma unroll
-                        for (int d = 0; d < 4; ++d) {
-                            const float* ps = all + (size_t)(s0 + d) * (BN * BM) + quad * 32 + lane;
-#pragma unroll
-                            for (int i = 0; i < STEP; ++i)
-                                t[d][i] = (s0 + d < p.ksplit) ? __ldcg(ps + (size_t)(c + i) * BM) : 0.0f;
-                        }
-#pragma unroll
-                        for (int d = 0; d < 4; ++d) {
-#pragma unroll
-                            for (int i = 0; i < 16; ++i) {
-                                v[i] += t[d][i];
-                                if (STEP == 32) u[i] += t[d][(STEP == 32 ? 16 : 0) + i];
-                            }
-                        }
-                    }
-                }
-                if (p.ssq_in) {
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        const float f = SWAP ? s_scale[c + i] : row_scale;
-                        v[i] *= f;
-                        if (STEP == 32) u[i] *= f;
-                    }
-                }
-                if (EPI == EPI_SWIGLU) {
-                    if (SWAP) store_swiglu_swapped(p, v, a_row, b0, c);
-                    else store_swiglu_normal(p, v, u, a_row, b0, c);
-                } else if (EPI == EPI_RESID) {
-                    if (SWAP) store_resid_swapped(p, v, a_row, b0, c);
-                    else ssq_acc += store_resid_normal(p, v, a_row, b0 + c);
-                } else {
-                    store_chunk<EPI, SWAP>(p, v, a_row, b0, c);
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (threadIdx.x == 64) s_ticket = atomicAdd(p.counters + tile, 1);
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                last = s_ticket == p.ksplit - 1;
+                if (last) {
+                    __threadfence();
+                    if (threadIdx.x == 64) p.counters[tile] = 0;       // ready for the next launch
                 }
             }
-            if (EPI == EPI_RESID && !SWAP && a_row < p.a_rows) p.ssq_out[(size_t)blockIdx.y * p.ssq_out_ld + a_row] = ssq_acc;
         }
+        if (ok && last) finish_tile(-1);
+    }
+    if (CLUSTER && clustered) {
+        // Every CTA of the cluster has its partial tile in shared memory.  CTA r takes every ksplit-th
+        // chunk of 16 (or 32) columns, adds the slices in order through distributed shared memory
+        // and stores the result; nobody leaves while a peer may still read its memory.
+        __syncwarp();
+        cluster_sync_all();
+        if (warp >= 2) finish_tile((int)cluster_rank());
+        __syncwarp();
+        cluster_sync_all();
     }
     tc_fence_before();
     __syncthreads();
@@ -684,8 +744,22 @@ int make_map(CUtensorMap* out, const void* ptr, long long rows, long long K, lon
 template <int BN, int STAGES, int EPI, bool SWAP>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, dim3 grid, cudaStream_t stream) {
     using L = SmemLayout<BN, STAGES>;
+    constexpr bool CAN_CLUSTER = !(SWAP && BN < 32);          // see the call site of cluster_reduce
+    if constexpr (CAN_CLUSTER) {
+        if (p.cluster_reduce) {
+            static bool configured_c = false;
+            auto kern = gemm_tcgen05_kernel<BN, STAGES, EPI, SWAP, true>;
+            if (!configured_c) {
+                cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+                if (e != cudaSuccess) return (int)e;
+                configured_c = true;
+            }
+            airun_launch_cluster(kern, dim3(grid), dim3(GEMM_THREADS), L::TOTAL, stream, (unsigned)p.ksplit, ma, mb, p);
+            return airun_launch_status();
+        }
+    }
     static bool configured = false;
-    auto kern = gemm_tcgen05_kernel<BN, STAGES, EPI, SWAP>;
+    auto kern = gemm_tcgen05_kernel<BN, STAGES, EPI, SWAP, false>;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
         if (e != cudaSuccess) return (int)e;
@@ -780,6 +854,14 @@ AIRUN_EXPORT int airun_gemm_tcgen05_ex(const void* x, const void* W, void* out, 
     p.ssq_in = ssq_in; p.ssq_parts = ssq_parts; p.ssq_ld = ssq_ld; p.eps_in = eps_in;
     p.inv_n_in = norm_size > 0 ? 1.0f / (float)norm_size : 0.0f;
     p.resid = resid; p.ld_resid = ld_resid; p.norm_w = norm_w; p.ssq_out = ssq_out; p.ssq_out_ld = ssq_out_ld;
+    // 2 to 8 slices of a tile run as one cluster and add up through distributed shared memory
+    // (AIRUN_GEMM_CLUSTER=0: through the scratch, as more than 8 slices always do).  Not for the
+    // narrowest tiles (up to 16 tokens): their partial tiles are small, and inside a decode step the
+    // clusters, which need all their CTAs placed at once, overlapped less with the kernel before
+    // them than single CTAs do (measured: 2 to 4 % slower steps at batch 1 and 8).
+    static const bool cluster_allowed = !(getenv("AIRUN_GEMM_CLUSTER") && getenv("AIRUN_GEMM_CLUSTER")[0] == '0');
+    p.cluster_reduce = (cluster_allowed && p.ksplit >= 2 && p.ksplit <= 8 && !(swap && bn < 32) &&
+                        !(epi == EPI_RESID && !swap)) ? 1 : 0;
     CUtensorMap ma, mb;
     int r;
     if (swap) {

@@ -16,7 +16,8 @@ from . import ops
 from .ops import _check, _cuda, _fn, _need, _p, _stream
 
 EPI_F32, EPI_BF16, EPI_SWIGLU, EPI_RESID = 0, 1, 2, 3
-TARGET_CTAS = 296                      # two waves of 148 SMs
+STREAM_CTAS = 296                      # two CTAs on each of 148 SMs
+SPLIT_CTAS = 256                       # CTAs a split product may use: its clusters must all be resident together (296 slots)
 
 _SCRATCH: Dict[torch.device, Tuple[torch.Tensor, torch.Tensor]] = {}
 SCRATCH_FLOATS = 16 << 20              # 64 MiB of partial tiles
@@ -107,21 +108,23 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: int, 
 def plan_gemm(M: int, N: int, K: int) -> Tuple[bool, int, int]:
     """(swap, bn, ksplit) for a product of M tokens with an [N, K] weight.
 
-    Up to 128 tokens the weights are the 128-row operand (swap) and the K range is cut until about
-    TARGET_CTAS CTAs stream them (half as many from 17 tokens on, where the partial tiles that
-    cutting K sends through memory are larger, and then at most 4 slices), a slice keeping at
-    least 10 K-steps.  Above that, tiles of 128 x 256 on the persistent kernel once
-    there are 96 of them; fewer tiles leave SMs idle, so the tile narrows to 128 x 128, and only
-    if that still fills less than one wave and a slice keeps 32 K-steps is K cut as well (cutting K
-    costs a round trip of partial tiles through memory: timed on the Qwen3-1.7B and -8B shapes at 192
-    to 2048 tokens, it loses everywhere else)."""
+    Up to 128 tokens the weights are the 128-row operand (swap).  Up to 16 tokens the K range is cut
+    until about STREAM_CTAS CTAs stream the weights (a slice keeping 10 K-steps) and the slices add
+    up through a scratch in memory.  From 17 tokens on, where the partial tiles are larger, it is cut
+    into up to 8 slices that run as one thread-block cluster and add up through distributed shared
+    memory: as many as keep the CTAs within SPLIT_CTAS (all clusters must be resident at once; 288
+    CTAs in clusters of 6 were not and took half as long again) and a slice at 8 K-steps or more.  Above
+    128 tokens, tiles of 128 x 256 on the persistent kernel once there are 96 of them; fewer tiles
+    leave SMs idle, so the tile narrows to 128 x 128, and only if that still fills less than one
+    wave and a slice keeps 32 K-steps is K cut as well.  Both rules come from sweeps over the
+    Qwen3-1.7B and -8B shapes, 1 to 2048 tokens, timed inside CUDA graphs."""
     kb = (K + 63) // 64
     if M <= 128:
         bn = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128
         tiles = (N + 127) // 128
-        target = TARGET_CTAS if M <= 16 else TARGET_CTAS // 2
-        ksplit = max(1, min(target // tiles, kb // 10, 64 if M <= 16 else 4)) if tiles < target else 1
-        return True, bn, ksplit
+        if M <= 16:
+            return True, bn, max(1, min(STREAM_CTAS // tiles, kb // 10))
+        return True, bn, max(1, min(SPLIT_CTAS // tiles, kb // 8, 8))
     mt = (M + 127) // 128
     if N >= 256 and mt * ((N + 255) // 256) >= 96:
         return False, 256, 1
