@@ -27,7 +27,7 @@ DISABLED = set(filter(None, os.environ.get("AIRUN_DISABLE_FAST", "").split(","))
 
 
 def all_libraries():
-    return [("gemm_tcgen05", None), ("attention_plan", None), ("attention_mma", {"HD": 128}), ("attention_mma", {"HD": 64}),
+    return [("gemm_tcgen05", None), ("gemm_tcgen05", {"AIRUN_FOLD_NORM": 1}), ("attention_plan", None), ("attention_mma", {"HD": 128}), ("attention_mma", {"HD": 64}),
             ("attention_tcgen05", {"HD": 128}), ("attention_tcgen05", {"HD": 64})]
 
 
@@ -93,10 +93,12 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: int, 
     if ssq_in is not None:
         _need(ssq_in.dtype == torch.float32 and ssq_in.dim() == 2 and ssq_in.is_contiguous() and ssq_in.shape[1] >= M
               and norm_size > 0, "ssq_in must be float32 [parts, M]")
+    # the build with the folded norm only where it is asked for; the plain one is leaner
+    fold = {"AIRUN_FOLD_NORM": 1} if (ssq_in is not None or epi == EPI_RESID) else None
     f = _fn("gemm_tcgen05", "airun_gemm_tcgen05_ex",
             [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong,
              c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-             c_void_p, c_int, c_int, c_float, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_int])
+             c_void_p, c_int, c_int, c_float, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_int], fold)
     _check(f(_p(x), _p(w), _p(out), M, N, K, x.stride(0) if M > 1 else max(K, x.stride(0)),
              w.stride(0), out.stride(0) if M > 1 else max(out.shape[1], out.stride(0)),
              epi, 1 if swap else 0, bn, ksplit, _p(scratch), _p(counters), _p(err), _stream(),
