@@ -132,6 +132,108 @@ __global__ __launch_bounds__(256) void qkv_post_kernel(
     }
 }
 
+// The same for head_dim 128 with a full-width NeoX rotation (the benchmark's shape): a lane holds four
+// neighbouring values, loads them as one float4 and stores them as one 8- or 16-byte word; the
+// rotation partner of dims 4l .. 4l+3 sits in lane l ^ 16, so it comes by shuffle and not through
+// shared memory.  Same arithmetic, in the same order, as the kernel above.
+template <typename TQ, typename TKV>
+__global__ __launch_bounds__(256) void qkv_post_hd128_kernel(
+    const float* __restrict__ qkv, long long ld_qkv,
+    TQ* __restrict__ q_out,
+    const float* __restrict__ q_norm_w, const float* __restrict__ k_norm_w, float eps,
+    const int32_t* __restrict__ positions, const int32_t* __restrict__ req_of_token,
+    const float* __restrict__ inv_freq,
+    TKV* __restrict__ pool, const int32_t* __restrict__ block_table, int max_blocks,
+    int num_reqs, int num_pages, int page_size, int do_store, int kv_from_qkv,
+    int nh, int nkv, int* __restrict__ err) {
+    pdl_trigger();
+    pdl_wait();
+    constexpr int HD = 128, HALF = 64;
+    __shared__ float cs[2 * HALF];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nwarp = blockDim.x >> 5;
+    const int t = blockIdx.x;
+    const int pos = positions[t];
+    const int req = req_of_token[t];
+    const int total_heads = kv_from_qkv ? nh + 2 * nkv : nh;
+    for (int i = threadIdx.x; i < HALF; i += blockDim.x) {
+        float s, c;
+        sincosf((float)pos * inv_freq[i], &s, &c);
+        cs[i] = c;
+        cs[HALF + i] = s;
+    }
+    __syncthreads();
+    const bool first = lane < 16;
+    const int pair = 4 * (lane & 15);
+    const float4 c4 = *reinterpret_cast<const float4*>(cs + pair);
+    const float4 s4 = *reinterpret_cast<const float4*>(cs + HALF + pair);
+
+    for (int h = blockIdx.y * nwarp + warp; h < total_heads; h += gridDim.y * nwarp) {
+        const bool is_q = h < nh;
+        const bool is_k = !is_q && h < nh + nkv;
+        float4 v = *reinterpret_cast<const float4*>(qkv + (size_t)t * ld_qkv + (size_t)h * HD + 4 * lane);
+        const float* w = is_q ? q_norm_w : (is_k ? k_norm_w : nullptr);
+        if (w) {
+            float ss = fmaf(v.x, v.x, 0.0f);
+            ss = fmaf(v.y, v.y, ss);
+            ss = fmaf(v.z, v.z, ss);
+            ss = fmaf(v.w, v.w, ss);
+            ss = warp_sum(ss);
+            const float inv = rsqrtf(ss / (float)HD + eps);
+            const float4 g = *reinterpret_cast<const float4*>(w + 4 * lane);
+            v.x = v.x * inv * g.x; v.y = v.y * inv * g.y; v.z = v.z * inv * g.z; v.w = v.w * inv * g.w;
+            float4 o;
+            o.x = __shfl_xor_sync(0xffffffffu, v.x, 16);
+            o.y = __shfl_xor_sync(0xffffffffu, v.y, 16);
+            o.z = __shfl_xor_sync(0xffffffffu, v.z, 16);
+            o.w = __shfl_xor_sync(0xffffffffu, v.w, 16);
+            // first half: x_i cos - x_{i+64} sin; second half: x_i sin + x_{i+64} cos (x_i is the partner's)
+            if (first) {
+                v.x = v.x * c4.x - o.x * s4.x; v.y = v.y * c4.y - o.y * s4.y;
+                v.z = v.z * c4.z - o.z * s4.z; v.w = v.w * c4.w - o.w * s4.w;
+            } else {
+                v.x = o.x * s4.x + v.x * c4.x; v.y = o.y * s4.y + v.y * c4.y;
+                v.z = o.z * s4.z + v.z * c4.z; v.w = o.w * s4.w + v.w * c4.w;
+            }
+        }
+        if (is_q) {
+            TQ* dst = q_out + ((size_t)t * nh + h) * HD + 4 * lane;
+            if (sizeof(TQ) == 4) {
+                *reinterpret_cast<float4*>(dst) = v;
+            } else {
+                __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+                uint2 pk;
+                pk.x = *reinterpret_cast<uint32_t*>(&lo);
+                pk.y = *reinterpret_cast<uint32_t*>(&hi);
+                *reinterpret_cast<uint2*>(dst) = pk;
+            }
+        } else if (do_store && req >= 0 && pos >= 0) {
+            if (req >= num_reqs) {
+                if (lane == 0) atomicOr(err, AIRUN_DEV_BAD_REQ);
+                continue;
+            }
+            const int blk = pos / page_size;
+            const int page = blk < max_blocks ? block_table[(size_t)req * max_blocks + blk] : -1;
+            if (page < 0 || page >= num_pages) {
+                if (lane == 0) atomicOr(err, AIRUN_DEV_BAD_PAGE);
+                continue;
+            }
+            const int kvh = is_k ? h - nh : h - nh - nkv;
+            TKV* dst = pool + ((((size_t)page * 2 + (is_k ? 0 : 1)) * nkv + kvh) * page_size
+                               + (pos % page_size)) * HD + 4 * lane;
+            if (sizeof(TKV) == 4) {
+                *reinterpret_cast<float4*>(dst) = v;
+            } else {
+                __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+                uint2 pk;
+                pk.x = *reinterpret_cast<uint32_t*>(&lo);
+                pk.y = *reinterpret_cast<uint32_t*>(&hi);
+                *reinterpret_cast<uint2*>(dst) = pk;
+            }
+        }
+    }
+}
+
 // kv_from_qkv = 0: the row holds q only (the layer reads another layer's cache).
 AIRUN_EXPORT int airun_qkv_post(
     const float* qkv, long long ld_qkv, void* q_out, int q_dtype,
@@ -153,6 +255,21 @@ AIRUN_EXPORT int airun_qkv_post(
     int warps = T <= 64 ? (heads < 2 ? heads : 2) : (heads < 8 ? heads : 8);
     const int blocks_y = T <= 64 ? (heads + warps - 1) / warps : 1;
     const size_t smem = ((size_t)warps * hd + (rope_kind != ROPE_NONE ? rotary_dim : 0)) * sizeof(float);
+    // head_dim 128, both norms, the rotation over the whole head, 16-byte aligned rows: the vector kernel
+    const bool vec128 = hd == 128 && rope_kind == ROPE_NEOX && rotary_dim == 128 && q_norm_w && k_norm_w &&
+                        ld_qkv % 4 == 0 && (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)pool |
+                                             (uintptr_t)q_norm_w | (uintptr_t)k_norm_w) & 15) == 0;
+    if (vec128) {
+#define LAUNCH128(TQ, TKV) \
+    airun_launch(qkv_post_hd128_kernel<TQ, TKV>, dim3(T, blocks_y), dim3(warps * 32), 0, stream, qkv, ld_qkv, (TQ*)q_out, \
+        q_norm_w, k_norm_w, eps, positions, req_of_token, inv_freq, (TKV*)pool, block_table, max_blocks, num_reqs, \
+        num_pages, page_size, do_store, kv_from_qkv, nh, nkv, err)
+        if (q_dtype == AIRUN_DT_F32) LAUNCH128(float, float);
+        else if (q_dtype == AIRUN_DT_BF16) LAUNCH128(__nv_bfloat16, __nv_bfloat16);
+        else return AIRUN_ERR_UNSUPPORTED;
+#undef LAUNCH128
+        return airun_launch_status();
+    }
 #define LAUNCH(TQ, TKV, DPL) \
     airun_launch(qkv_post_kernel<TQ, TKV, DPL>, dim3(T, blocks_y), dim3(warps * 32), smem, stream, qkv, ld_qkv, (TQ*)q_out, q_norm_w, k_norm_w, eps, \
         positions, req_of_token, rope_kind, rotary_dim, inv_freq, (TKV*)pool, block_table, max_blocks, num_reqs, \

@@ -245,7 +245,8 @@ def test_gemm_tcgen05_refuses_what_it_cannot_take():
 
 # ----------------------------------------------------------------------------- q/k norm + rope + cache write
 @pytest.mark.parametrize("nh,nkv,hd,page,dtype", [(4, 2, 16, 4, torch.float32), (6, 3, 48, 16, torch.bfloat16),
-                                                  (8, 1, 128, 8, torch.float32), (3, 3, 80, 32, torch.float32)])
+                                                  (8, 1, 128, 8, torch.float32), (3, 3, 80, 32, torch.float32),
+                                                  (8, 2, 128, 16, torch.bfloat16)])
 def test_qkv_post_against_the_plain_parts(nh, nkv, hd, page, dtype):
     from airun_b200.kernels import ops
     from airun_b200.parts.rope import RotaryNeox
