@@ -798,6 +798,54 @@ int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const GemmPa
     return airun_launch_status();
 }
 
+// How many clusters of `ks` CTAs of this kernel the GPU holds at once (0: unknown or none).  A product
+// whose tiles outnumber them would run its last clusters alone in a second wave.
+template <int BN, int STAGES, int EPI, bool SWAP>
+int cluster_capacity(int ks) {
+    static int cache[9] = {0, 0, 0, 0, 0, 0, 0, 0, 0};
+    if (ks < 2 || ks > 8) return 0;
+    if (cache[ks] == 0) {
+        using L = SmemLayout<BN, STAGES>;
+        auto kern = gemm_tcgen05_kernel<BN, STAGES, EPI, SWAP, true>;
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(1, 1, ks);
+        cfg.blockDim = dim3(GEMM_THREADS);
+        cfg.dynamicSmemBytes = L::TOTAL;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 1;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = ks;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        int n = 0;
+        const cudaError_t e = cudaOccupancyMaxActiveClusters(&n, kern, &cfg);
+        if (e != cudaSuccess) cudaGetLastError();
+        cache[ks] = (e == cudaSuccess && n > 0) ? n : -1;
+    }
+    return cache[ks] > 0 ? cache[ks] : 0;
+}
+
+template <int EPI>
+int cluster_capacity_for(bool swap, int bn, int ks) {
+    if (!swap) return bn == 128 ? cluster_capacity<128, 6, EPI, false>(ks) : bn == 256 ? cluster_capacity<256, 4, EPI, false>(ks) : 0;
+    if (bn == 32) return cluster_capacity<32, 5, EPI, true>(ks);
+    if (bn == 64) return cluster_capacity<64, 4, EPI, true>(ks);
+    if (bn == 128) return cluster_capacity<128, 3, EPI, true>(ks);
+    return 0;
+}
+
+int cluster_capacity_any(int epi, bool swap, int bn, int ks) {
+    if (epi == EPI_F32) return cluster_capacity_for<EPI_F32>(swap, bn, ks);
+    if (epi == EPI_BF16) return cluster_capacity_for<EPI_BF16>(swap, bn, ks);
+    if (epi == EPI_SWIGLU) return cluster_capacity_for<EPI_SWIGLU>(swap, bn, ks);
+#if AIRUN_FOLD_NORM
+    if (epi == EPI_RESID) return cluster_capacity_for<EPI_RESID>(swap, bn, ks);
+#endif
+    return 0;
+}
+
 template <int EPI>
 int dispatch(bool swap, int bn, const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, dim3 grid,
              cudaStream_t stream) {
@@ -848,6 +896,26 @@ AIRUN_EXPORT int airun_gemm_tcgen05_ex(const void* x, const void* W, void* out, 
     if (epi == EPI_RESID && (!resid || !norm_w || !ssq_out || ssq_out_ld < M || ld_resid < N)) return AIRUN_ERR_ARG;
     const int kb_total = (K + BK - 1) / BK;
     if (ksplit > kb_total) ksplit = kb_total;
+    // 2 to 8 slices of a tile run as one cluster and add up through distributed shared memory
+    // (AIRUN_GEMM_CLUSTER=0: through the scratch, as more than 8 slices always do).  Not for the
+    // narrowest tiles (up to 16 tokens): their partial tiles are small, and inside a decode step the
+    // clusters, which need all their CTAs placed at once, overlapped less with the kernel before
+    // them than single CTAs do (measured: 2 to 4 % slower steps at batch 1 and 8).  If the GPU cannot
+    // hold a cluster for every tile at once, fewer slices are cut.
+    static const bool cluster_allowed = !(getenv("AIRUN_GEMM_CLUSTER") && getenv("AIRUN_GEMM_CLUSTER")[0] == '0');
+    bool clustered = cluster_allowed && ksplit >= 2 && ksplit <= 8 && !(swap && bn < 32) && !(epi == EPI_RESID && !swap);
+    if (clustered) {
+        const long long tiles = (long long)(((swap ? N : M) + BM - 1) / BM) * (((swap ? M : N) + bn - 1) / bn);
+        int ks = ksplit;
+        while (ks >= 2) {
+            // the slices may come out fewer than asked for once they are whole K-steps
+            const int per = (kb_total + ks - 1) / ks, real = (kb_total + per - 1) / per;
+            if (real >= 2 && cluster_capacity_any(epi, swap != 0, bn, real) >= tiles) break;
+            --ks;
+        }
+        if (ks >= 2) ksplit = ks;
+        else clustered = false;
+    }
     GemmParams p = {};
     p.a_rows = swap ? N : M;
     p.b_rows = swap ? M : N;
@@ -862,14 +930,7 @@ AIRUN_EXPORT int airun_gemm_tcgen05_ex(const void* x, const void* W, void* out, 
     p.ssq_in = ssq_in; p.ssq_parts = ssq_parts; p.ssq_ld = ssq_ld; p.eps_in = eps_in;
     p.inv_n_in = norm_size > 0 ? 1.0f / (float)norm_size : 0.0f;
     p.resid = resid; p.ld_resid = ld_resid; p.norm_w = norm_w; p.ssq_out = ssq_out; p.ssq_out_ld = ssq_out_ld;
-    // 2 to 8 slices of a tile run as one cluster and add up through distributed shared memory
-    // (AIRUN_GEMM_CLUSTER=0: through the scratch, as more than 8 slices always do).  Not for the
-    // narrowest tiles (up to 16 tokens): their partial tiles are small, and inside a decode step the
-    // clusters, which need all their CTAs placed at once, overlapped less with the kernel before
-    // them than single CTAs do (measured: 2 to 4 % slower steps at batch 1 and 8).
-    static const bool cluster_allowed = !(getenv("AIRUN_GEMM_CLUSTER") && getenv("AIRUN_GEMM_CLUSTER")[0] == '0');
-    p.cluster_reduce = (cluster_allowed && p.ksplit >= 2 && p.ksplit <= 8 && !(swap && bn < 32) &&
-                        !(epi == EPI_RESID && !swap)) ? 1 : 0;
+    p.cluster_reduce = (clustered && p.ksplit >= 2 && p.ksplit <= 8) ? 1 : 0;
     CUtensorMap ma, mb;
     int r;
     if (swap) {
