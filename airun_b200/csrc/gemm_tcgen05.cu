@@ -748,20 +748,31 @@ int make_map(CUtensorMap* out, const void* ptr, long long rows, long long K, lon
     return AIRUN_OK;
 }
 
+// Stages of the clustered build: as many as fit in 200 KB, at most twice the plain build's.
+constexpr int cluster_stages(int bn, int stages) {
+    const int stage_bytes = (BM + bn) * BK * 2;
+    const int fit = (200 * 1024) / stage_bytes;
+    return fit < 2 * stages ? fit : 2 * stages;
+}
+
 template <int BN, int STAGES, int EPI, bool SWAP>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, dim3 grid, cudaStream_t stream) {
     using L = SmemLayout<BN, STAGES>;
     constexpr bool CAN_CLUSTER = !(SWAP && BN < 32);          // see the call site of cluster_reduce
     if constexpr (CAN_CLUSTER) {
         if (p.cluster_reduce) {
+            // clustered CTAs are placed one to an SM at most (ncu: launch__cluster_max_active), so each
+            // may as well use the whole shared memory: twice the stages
+            constexpr int CS = cluster_stages(BN, STAGES);
+            using LC = SmemLayout<BN, CS>;
             static bool configured_c = false;
-            auto kern = gemm_tcgen05_kernel<BN, STAGES, EPI, SWAP, true>;
+            auto kern = gemm_tcgen05_kernel<BN, CS, EPI, SWAP, true>;
             if (!configured_c) {
-                cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+                cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, LC::TOTAL);
                 if (e != cudaSuccess) return (int)e;
                 configured_c = true;
             }
-            airun_launch_cluster(kern, dim3(grid), dim3(GEMM_THREADS), L::TOTAL, stream, (unsigned)p.ksplit, ma, mb, p);
+            airun_launch_cluster(kern, dim3(grid), dim3(GEMM_THREADS), LC::TOTAL, stream, (unsigned)p.ksplit, ma, mb, p);
             return airun_launch_status();
         }
     }
@@ -805,8 +816,8 @@ int cluster_capacity(int ks) {
     static int cache[9] = {0, 0, 0, 0, 0, 0, 0, 0, 0};
     if (ks < 2 || ks > 8) return 0;
     if (cache[ks] == 0) {
-        using L = SmemLayout<BN, STAGES>;
-        auto kern = gemm_tcgen05_kernel<BN, STAGES, EPI, SWAP, true>;
+        using L = SmemLayout<BN, cluster_stages(BN, STAGES)>;
+        auto kern = gemm_tcgen05_kernel<BN, cluster_stages(BN, STAGES), EPI, SWAP, true>;
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(1, 1, ks);
