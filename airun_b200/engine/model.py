@@ -92,6 +92,11 @@ class DecoderModel:
         return all(getattr(l, "device_driven", lambda: False)() for l in self.layers) \
             and getattr(self.final_norm, "device_driven", False)
 
+    def graph_safe(self) -> bool:
+        """False if a part has said that its forward must not be captured into a CUDA graph (it
+        decides on the host what to launch from values it reads back from the device)."""
+        return all(getattr(l, "graph_safe", lambda: True)() for l in self.layers)
+
     # ---- cache needs ----
     def cache_specs(self) -> Tuple[List[object], List[Optional[int]]]:
         return ([self.layers[c.layer].cache_spec() for c in self.order],

@@ -74,7 +74,7 @@ class StepRunner:
         self.ws_pair = (Workspace(self.device), Workspace(self.device))
         self.steps_run = 0
         # CUDA graphs of decode-only steps, one per batch-size bucket
-        self.use_graphs = True
+        self.use_graphs = bool(getattr(model, "graph_safe", lambda: True)())
         self.graph_buckets = [b for b in (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256) if b <= self.R_max]
         if self.graph_buckets and self.graph_buckets[-1] < self.R_max and self.R_max <= 512:
             self.graph_buckets.append(self.R_max)

@@ -30,6 +30,10 @@ FeedForward     forward(ctx, h) -> float32 [T, hidden]
                 device arrays of ctx only (never from ctx.query_lens and the other host lists), and
                 that rows of request -1 are padding it skips.  Steps of a model whose parts all promise
                 this are replayed from CUDA graphs, prompt portions included.
+                ``graph_safe = False`` on a part says the opposite of the least a graph needs: its
+                forward reads values back to the host and launches accordingly (a routed feed-forward
+                that loops over the experts that got tokens, say); a model with such a part runs
+                every step kernel by kernel.
 Block           forward(ctx, x, delta, cache) -> delta of the block's last sub-layer,
                   still to be added to x by whoever norms x next
 """

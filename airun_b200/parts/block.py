@@ -42,6 +42,10 @@ class PreNormBlock(Part):
         """Do all parts of this block read the batch's layout from the device arrays only?"""
         return all(getattr(p, "device_driven", False) for p in self.parts())
 
+    def graph_safe(self) -> bool:
+        """May steps through this block be captured into CUDA graphs at all?"""
+        return all(getattr(p, "graph_safe", True) for p in self.parts())
+
     def accepts_normed(self) -> bool:
         """Can this block start from NormedActivations (its first norm folded into the products)?"""
         return self.dtype == torch.bfloat16 and getattr(self.mixer, "fuses_norms", False) \

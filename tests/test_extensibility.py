@@ -4,6 +4,7 @@ registered from here, built and stepped without a change to the framework's file
 from __future__ import annotations
 
 import json
+import math
 import os
 from dataclasses import dataclass
 from typing import Dict, List
@@ -195,3 +196,177 @@ def test_unknown_parts_and_architectures_are_named():
     assert "rotary_neox" in registered_parts("position")
     with pytest.raises(ConfigError):
         lookup_architecture("NoSuchForCausalLM")
+
+
+# ----------------------------------------------------------------------------- a routed feed-forward, another position encoding
+def define_routed_toy():
+    """A toy feed-forward with routing (every token goes to the one of three small SwiGLU experts
+    its router picks, weighted by the router's probability) and a toy position encoding (rotary
+    over half of each head, positions stretched by a factor), again registered from here."""
+    from airun_b200.config.base import LayerSpec, register_architecture
+    from airun_b200.config.qwen3 import Qwen3Config
+    from airun_b200.engine.model import build_decoder
+    from airun_b200.kernels import ops
+    from airun_b200.parts.base import FeedForward, PositionEncoding, register_part
+    from airun_b200.parts.linear import linear
+    from airun_b200.weights.loader import WeightSpec
+
+    class Top1Experts(FeedForward):
+        graph_safe = False        # which experts run is decided on the host, from values read back
+
+        def __init__(self, prefix, hidden_size, expert_size, num_experts, dtype, device):
+            self.prefix, self.H, self.E, self.n, self.dtype = prefix, hidden_size, expert_size, num_experts, dtype
+
+        def weight_specs(self):
+            specs = [WeightSpec(f"{self.prefix}.router.weight", (self.n, self.H), storage="float32")]
+            for e in range(self.n):
+                specs += [WeightSpec(f"{self.prefix}.experts.{e}.gate_up.weight", (2 * self.E, self.H)),
+                          WeightSpec(f"{self.prefix}.experts.{e}.down.weight", (self.H, self.E))]
+            return specs
+
+        def load_weights(self, tensors):
+            self.router = tensors[f"{self.prefix}.router.weight"]
+            self.gu = [tensors[f"{self.prefix}.experts.{e}.gate_up.weight"] for e in range(self.n)]
+            self.down = [tensors[f"{self.prefix}.experts.{e}.down.weight"] for e in range(self.n)]
+
+        def forward(self, ctx, h):
+            T = h.shape[0]
+            logits = h.float() @ self.router.T                          # router logits in float32
+            prob = torch.softmax(logits, -1)
+            top = prob.argmax(-1)
+            out = ctx.ws.alloc((T, self.H), torch.float32)
+            out.zero_()
+            for e in range(self.n):                                     # the engine's own products, expert by expert
+                rows = (top == e).nonzero().flatten()
+                if rows.numel() == 0:
+                    continue
+                he = h[rows].contiguous()
+                gu = torch.empty(rows.numel(), 2 * self.E, dtype=torch.float32, device=h.device)
+                linear(ctx, he, self.gu[e], gu)
+                g, u = gu[:, :self.E], gu[:, self.E:]
+                act = (g / (1 + torch.exp(-g)) * u).to(self.dtype)
+                y = torch.empty(rows.numel(), self.H, dtype=torch.float32, device=h.device)
+                linear(ctx, act, self.down[e], y)
+                out[rows] = y * prob[rows, e].unsqueeze(1)
+            return out
+
+    class StretchedHalfRotary(PositionEncoding):
+        """NeoX rotation of the first half of every head only, with the position divided by a factor:
+        the fused q/k kernel takes both as parameters (rotary_dim < head_dim, inv_freq as given)."""
+
+        def __init__(self, prefix="", head_dim=0, theta=10000.0, factor=1.0, dtype=None, device=None):
+            self.rotary_dim = head_dim // 2
+            i = torch.arange(0, self.rotary_dim // 2, dtype=torch.float64)
+            self.inv_freq = (torch.pow(torch.tensor(theta, dtype=torch.float64), -2.0 * i / self.rotary_dim)
+                             / factor).to(torch.float32).to(device)
+
+        def fused(self):
+            return ops.ROPE_NEOX, self.rotary_dim, self.inv_freq
+
+    class RoutedConfig(Qwen3Config):
+        def layer_specs(self):
+            specs = Qwen3Config.layer_specs(self)
+            out = []
+            for i, s in enumerate(specs):
+                mixer_args = dict(s.mixer_args, position="toy_stretched_half_rotary",
+                                  position_args=dict(head_dim=self.head_dim, theta=self.rope_theta, factor=4.0))
+                if i % 2 == 1:                                          # every other layer is routed
+                    out.append(LayerSpec(s.mixer, mixer_args, "toy_top1_experts",
+                                         dict(hidden_size=self.hidden_size, expert_size=40, num_experts=3),
+                                         s.norm, s.norm_args))
+                else:
+                    out.append(LayerSpec(s.mixer, mixer_args, s.feed_forward, s.ffn_args, s.norm, s.norm_args))
+            return out
+
+    register_part("feed_forward", "toy_top1_experts", Top1Experts)
+    register_part("position", "toy_stretched_half_rotary", StretchedHalfRotary)
+    register_architecture("ToyRoutedForCausalLM", RoutedConfig, build_decoder)
+    return RoutedConfig
+
+
+def plain_routed_forward(cfg: dict, W: Dict[str, torch.Tensor], tokens: List[int]) -> torch.Tensor:
+    c = P.config_values(cfg)
+    dt = torch.float32
+    T = len(tokens)
+    hd, nh, nkv = c["hd"], c["nh"], c["nkv"]
+    rdim = hd // 2
+    x = P.plain_embedding(W["model.embed_tokens.weight"], tokens, dt)
+    for l in range(c["L"]):
+        p = f"model.layers.{l}"
+        h = P.plain_rmsnorm(x, W[f"{p}.input_layernorm.weight"], c["eps"])
+        q = (h @ W[f"{p}.self_attn.q_proj.weight"].to(dt).T).view(T, nh, hd)
+        k = (h @ W[f"{p}.self_attn.k_proj.weight"].to(dt).T).view(T, nkv, hd)
+        v = (h @ W[f"{p}.self_attn.v_proj.weight"].to(dt).T).view(T, nkv, hd)
+        q = P.plain_rmsnorm(q, W[f"{p}.self_attn.q_norm.weight"], c["eps"])
+        k = P.plain_rmsnorm(k, W[f"{p}.self_attn.k_norm.weight"], c["eps"])
+        half = rdim // 2
+        inv = torch.tensor([c["theta"] ** (-2.0 * i / rdim) for i in range(half)], dtype=torch.float64).float() / 4.0
+        ang = torch.arange(T, dtype=dt).unsqueeze(1) * inv.float().unsqueeze(0)
+        cs, sn = ang.cos().unsqueeze(1), ang.sin().unsqueeze(1)
+
+        def rot(t):
+            a, b, rest = t[..., :half], t[..., half:rdim], t[..., rdim:]
+            return torch.cat([a * cs - b * sn, a * sn + b * cs, rest], -1)
+
+        q, k = rot(q), rot(k)
+        att = torch.zeros(T, nh, hd)
+        for t in range(T):
+            for hh in range(nh):
+                kv = hh // (nh // nkv)
+                s = (k[:t + 1, kv] @ q[t, hh]) / math.sqrt(hd)
+                att[t, hh] = torch.softmax(s, 0) @ v[:t + 1, kv]
+        x = x + att.view(T, nh * hd) @ W[f"{p}.self_attn.o_proj.weight"].to(dt).T
+        h = P.plain_rmsnorm(x, W[f"{p}.post_attention_layernorm.weight"], c["eps"])
+        if l % 2 == 1:
+            prob = torch.softmax(h @ W[f"{p}.mlp.router.weight"].to(dt).T, -1)
+            y = torch.zeros_like(h)
+            for t in range(T):
+                e = int(prob[t].argmax())
+                gu = W[f"{p}.mlp.experts.{e}.gate_up.weight"].to(dt) @ h[t]
+                g, u = gu[:40], gu[40:]
+                y[t] = (W[f"{p}.mlp.experts.{e}.down.weight"].to(dt) @ (g / (1 + torch.exp(-g)) * u)) * prob[t, e]
+            x = x + y
+        else:
+            x = x + P.plain_swiglu_ffn(h, W[f"{p}.mlp.gate_proj.weight"].to(dt), W[f"{p}.mlp.up_proj.weight"].to(dt),
+                                       W[f"{p}.mlp.down_proj.weight"].to(dt))
+    h = P.plain_rmsnorm(x, W["model.norm.weight"], c["eps"])
+    return h @ W["lm_head.weight"].to(dt).T
+
+
+def test_routed_feed_forward_and_another_position_encoding(tmp_path):
+    import math  # noqa: F401  (used by the plain model above through the module's namespace)
+    import airun_b200
+    from airun_b200 import StepEntry
+    from airun_b200.engine.model import DecoderModel
+    from airun_b200.weights import write_model_folder
+    RoutedConfig = define_routed_toy()
+    cfg_obj = RoutedConfig.from_dict(dict(TINY["B"]["cfg"], architectures=["ToyRoutedForCausalLM"]))
+    folder = str(tmp_path / "routed")
+    write_model_folder(folder, cfg_obj, DecoderModel(cfg_obj, torch.float32, "cpu").weight_specs(), seed=9)
+    cfg, W = P.read_model_folder(folder)
+    seqs = [random_tokens(n, cfg["vocab_size"], 400 + i) for i, n in enumerate((29, 18))]
+    want = [plain_routed_forward(cfg, W, s).numpy() for s in seqs]
+    eng = airun_b200.Engine.from_folder(folder, dtype="float32", page_size=8, cache_tokens=256, max_batch_tokens=64,
+                                        max_requests=4)
+    assert not eng.runner.use_graphs            # the toy feed-forward forbids capture: every step runs kernel by kernel
+    for rid in ("a", "b"):
+        eng.manager.add_request(rid)
+    got_a = [eng.runner.step([StepEntry("a", seqs[0][:11], tuple(range(11)))]).cpu().numpy()]
+    rows_b = []
+    pa, pb = 11, 0
+    while pa < len(seqs[0]) or pb < len(seqs[1]):
+        entries = []
+        if pa < len(seqs[0]):
+            entries.append(StepEntry("a", [seqs[0][pa]], (0,)))
+        nb = min(5, len(seqs[1]) - pb)
+        if nb > 0:
+            entries.append(StepEntry("b", seqs[1][pb:pb + nb], tuple(range(nb))))
+        out = eng.runner.step(entries).cpu().numpy()
+        r = 0
+        if pa < len(seqs[0]):
+            got_a.append(out[:1]); r = 1; pa += 1
+        if nb > 0:
+            rows_b.append(out[r:r + nb]); pb += nb
+    eng.runner.raise_on_device_error()
+    assert_close(np.concatenate(got_a), want[0], "float32", "routed toy, portion then single tokens")
+    assert_close(np.concatenate(rows_b), want[1], "float32", "routed toy, portions beside single tokens")
