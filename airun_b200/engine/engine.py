@@ -102,6 +102,7 @@ class Engine:
         self._picked_dev = torch.zeros(R + 1, dtype=torch.int32, device=self.device)
         self._picked_host = torch.zeros(R + 1, dtype=torch.int32, pin_memory=self.device.type == "cuda")
         self.stats = GenerationStats()
+        self._ahead = None        # (requests, prepared step): the next decode step, laid out while this one runs
 
     # ------------------------------------------------------------ construction
     @staticmethod
@@ -180,6 +181,9 @@ class Engine:
     def run_step(self) -> List[Request]:
         """One scheduler step: plan, run, sample.  Returns the requests that finished."""
         t_start = time.perf_counter() if SCHED_TIMING else 0.0
+        ahead, self._ahead = self._ahead, None
+        if ahead is not None and self._ahead_still_holds(ahead[0]):
+            return self._run_prepared(*ahead, t_start)
         plan = self.scheduler.plan()
         finished = list(plan.finished)
         if not plan.entries:
@@ -196,7 +200,7 @@ class Engine:
         logits = self.runner.step(entries, checked=True)
         self.scheduler.advance(plan)
         if wanting:
-            tokens = self._sample(logits, wanting)
+            tokens = self._sample(logits, wanting, look_ahead=len(wanting) == len(plan.entries))
             for req, tok in zip(wanting, tokens):
                 if self.scheduler.accept(req, tok) is not None:
                     finished.append(req)
@@ -209,7 +213,53 @@ class Engine:
                   file=sys.stderr)
         return finished
 
-    def _sample(self, logits: torch.Tensor, reqs: List[Request]) -> List[int]:
+    # While the GPU runs a step of single tokens, the host lays out the next one (pages, positions,
+    # block tables, their copy to the device): all of it but the tokens themselves, which it only
+    # has when it has read this step's result.  If then a request ends, is cancelled, or another
+    # arrives, the lay-out is dropped and the step is planned the ordinary way.
+    def _prepare_ahead(self, reqs: List[Request]) -> None:
+        sch = self.scheduler
+        if sch.waiting or len(sch.running) != len(reqs) or any(a is not b for a, b in zip(sch.running, reqs)):
+            return
+        for r in reqs:
+            # after the token being sampled now: still running, and one token short of its cache
+            if r.cancelled or r.num_computed != r.num_tokens or len(r.output) + 1 >= r.max_new_tokens \
+                    or r.num_tokens + 2 > self.max_context:
+                return
+        try:
+            prep = self.runner.prepare_decode([r.rid for r in reqs])
+        except Exception:                                  # noqa: BLE001 - e.g. out of pages: the ordinary path decides
+            return
+        if prep is not None:
+            self._ahead = (list(reqs), prep)
+
+    def _ahead_still_holds(self, reqs: List[Request]) -> bool:
+        sch = self.scheduler
+        if sch.waiting or len(sch.running) != len(reqs):
+            return False
+        for a, b in zip(sch.running, reqs):
+            if a is not b or a.cancelled or a.finished is not None or a.num_tokens - a.num_computed != 1:
+                return False
+        return True
+
+    def _run_prepared(self, reqs: List[Request], prep: dict, t_start: float) -> List[Request]:
+        logits = self.runner.launch_prepared(prep, [r.output[-1] for r in reqs])
+        for r in reqs:
+            r.num_computed += 1
+        self.scheduler.stats["steps"] += 1
+        finished = []
+        tokens = self._sample(logits, reqs, look_ahead=True)
+        for req, tok in zip(reqs, tokens):
+            if self.scheduler.accept(req, tok) is not None:
+                finished.append(req)
+        self.stats.steps += 1
+        if SCHED_TIMING:
+            import sys
+            print(f"[airun_b200] step {self.stats.steps}: {len(reqs)} requests, {len(reqs)} tokens (laid out ahead), "
+                  f"{(time.perf_counter() - t_start) * 1e3:.3f} ms", file=sys.stderr)
+        return finished
+
+    def _sample(self, logits: torch.Tensor, reqs: List[Request], look_ahead: bool = False) -> List[int]:
         n = len(reqs)
         R = self.runner.R_max
         host = self._small_host.numpy()
@@ -224,6 +274,8 @@ class Engine:
         self._picked_host.copy_(self._picked_dev, non_blocking=True)
         host_rows = [i for i, r in enumerate(reqs) if not r.params.device_ok]
         rows_host = logits[host_rows].cpu().numpy() if host_rows else None
+        if look_ahead and not host_rows:
+            self._prepare_ahead(reqs)                      # the GPU is busy: lay out the next step meanwhile
         torch.cuda.current_stream().synchronize()
         picked = self._picked_host.numpy()
         if picked[R]:

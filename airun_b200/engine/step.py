@@ -193,6 +193,38 @@ class StepRunner:
         self.steps_run += 1
         return logits
 
+    # ---- a decode step in two halves: what does not depend on the tokens, and the rest
+    def prepare_decode(self, rids: Sequence[Hashable]) -> Optional[dict]:
+        """The part of the next step of single tokens (one per request of ``rids``, all logits
+        wanted) that does not need the tokens: pages, the batch's layout, its copy to the device,
+        which queues up behind whatever the stream is running.  ``launch_prepared`` does the rest
+        once the tokens are known.  None when there is no captured graph for this many requests yet
+        (the step then goes the ordinary way); raises OutOfPages like ``step``."""
+        n = len(rids)
+        bucket = next((b for b in self.graph_buckets if b >= n), None)
+        if not self.use_graphs or self.device.type != "cuda" or bucket is None or bucket not in self.graphs:
+            return None
+        self.manager.reserve_many(rids, [1] * n)
+        self.build_context([StepEntry(r, (0,), (0,)) for r in rids], pad_to=bucket)
+        return dict(rids=list(rids), bucket=bucket, slot=self._ring_i)
+
+    def launch_prepared(self, prep: dict, tokens: Sequence[int]) -> torch.Tensor:
+        """Second half of ``prepare_decode``: the tokens go to the device and the graph is replayed.
+        Nothing may have touched the runner or these requests in between."""
+        n = len(prep["rids"])
+        off, _ = self.offsets["token_ids"]
+        host, host_np, event = self._ring[prep["slot"]]
+        host_np[off:off + n] = tokens
+        self.meta_dev[off:off + n].copy_(host[off:off + n], non_blocking=True)
+        if event is not None:
+            event.record()
+        graph, out, kernels = self.graphs[prep["bucket"]]
+        graph.replay()
+        self.graph_launches += kernels
+        self.manager.commit_many(prep["rids"], [1] * n)
+        self.steps_run += 1
+        return out[:n]
+
     def _decode_step_graphed(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """A step of single decoded tokens, all of whose logits are wanted, replayed from a
         CUDA graph of the next larger captured batch size.  The reference captures its decode

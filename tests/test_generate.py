@@ -197,3 +197,38 @@ def test_selftest_subcommand_passes():
                        capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout + r.stderr
     assert "FAIL" not in r.stdout and "checks passed" in r.stdout
+
+
+def test_next_step_laid_out_ahead_is_dropped_when_the_batch_changes(folders):
+    """While a decode step runs, the engine lays out the next one.  A request that ends on an end
+    token, one that is cancelled and one that arrives in between each make that lay-out stale; every
+    request must still get the tokens it gets alone."""
+    import airun_b200
+    name = "A"
+    cfg, W = P.read_model_folder(folders[name])
+    prompts = [random_tokens(n, cfg["vocab_size"], 150 + i) for i, n in enumerate((9, 14, 20, 6))]
+    want = [P.plain_greedy_generate(cfg, W, p, 24) for p in prompts]
+    eog = want[1][7]                                    # request 1 meets its end token at its 8th token
+    cut = want[1].index(eog)
+    eng = airun_b200.Engine.from_folder(folders[name], dtype="float32", page_size=16, cache_tokens=1024,
+                                        max_batch_tokens=32, max_requests=4)
+    greedy = airun_b200.SamplingParams.greedy
+    reqs = [eng.add_request(prompts[0], greedy(), max_new_tokens=24),
+            eng.add_request(prompts[1], greedy(), max_new_tokens=24, eog_tokens=[eog]),
+            eng.add_request(prompts[2], greedy(), max_new_tokens=24)]
+    used_ahead = 0
+    late = None
+    while eng.has_work():
+        if eng._ahead is not None:
+            used_ahead += 1
+        if late is None and len(reqs[0].output) == 12:
+            late = eng.add_request(prompts[3], greedy(), max_new_tokens=24)      # arrives while others decode
+        if len(reqs[2].output) == 15:
+            reqs[2].cancelled = True
+        eng.run_step()
+        eng.manager.check_invariants()
+    assert used_ahead > 5, "the look-ahead path never ran"
+    assert reqs[0].output == want[0] and late.output == want[3]
+    assert reqs[1].output == want[1][:cut] and reqs[1].finished.value == "EndOfGeneration"
+    assert reqs[2].output == want[2][:len(reqs[2].output)] and reqs[2].finished.value == "Cancelled"
+    assert eng.manager.free_pages() == {g.gid: eng.manager.num_pages for g in eng.manager.paged}
