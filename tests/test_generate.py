@@ -232,3 +232,69 @@ def test_next_step_laid_out_ahead_is_dropped_when_the_batch_changes(folders):
     assert reqs[1].output == want[1][:cut] and reqs[1].finished.value == "EndOfGeneration"
     assert reqs[2].output == want[2][:len(reqs[2].output)] and reqs[2].finished.value == "Cancelled"
     assert eng.manager.free_pages() == {g.gid: eng.manager.num_pages for g in eng.manager.paged}
+
+
+@pytest.mark.parametrize("seed", [1, 2])
+def test_random_arrivals_forks_and_cancellations_under_a_small_pool(seed, folders):
+    """Forty requests arrive at random moments into an engine whose pool holds two or three of them:
+    portions, preemption and recomputation, forks that share pages, cancellations, end tokens, the
+    look-ahead path, graph replays.  Every token every request ever gets must be the token the plain
+    implementation gets for the same sequence, and in the end every page is back."""
+    import random
+    import airun_b200
+    name = "B"
+    cfg, W = P.read_model_folder(folders[name])
+    V = cfg["vocab_size"]
+    rng = random.Random(seed)
+    eng = airun_b200.Engine.from_folder(folders[name], dtype="float32", page_size=8, num_pages=22,
+                                        max_batch_tokens=48, max_requests=6, max_context=120)
+    greedy = airun_b200.SamplingParams.greedy
+    plain_cache = {}
+
+    def plain(prompt, n):
+        key = tuple(prompt)
+        if key not in plain_cache or len(plain_cache[key]) < n:
+            plain_cache[key] = P.plain_greedy_generate(cfg, W, list(prompt), n)
+        return plain_cache[key][:n]
+
+    pending = [random_tokens(rng.randint(3, 60), V, 1000 * seed + i) for i in range(40)]
+    live = []                    # (request, prompt it started from, tokens wanted)
+    done = []
+    steps = 0
+    while pending or eng.has_work():
+        if pending and rng.random() < 0.35:
+            p = pending.pop()
+            n = rng.randint(1, 24)
+            eog = ()
+            if rng.random() < 0.3:                          # ends early on one of its own tokens
+                eog = (plain(p, n)[rng.randrange(n)],)
+            live.append((eng.add_request(p, greedy(), max_new_tokens=n, eog_tokens=eog), p, n))
+        running = [t for t in live if t[0] in eng.scheduler.running and t[0].output and t[0].finished is None]
+        if running and rng.random() < 0.08 and eng.manager.has_free_slot():
+            parent, pp, pn = rng.choice(running)
+            if parent.num_computed == parent.num_tokens - 1:
+                try:
+                    child = eng.fork_request(parent, max_new_tokens=rng.randint(1, 10))
+                    live.append((child, list(child.prompt), child.max_new_tokens))
+                except Exception as e:                       # out of pages or slots: the fork is refused whole
+                    assert type(e).__name__ in ("OutOfPages", "CacheError"), e
+        if running and rng.random() < 0.04:
+            rng.choice(running)[0].cancelled = True
+        if eng.has_work():
+            eng.run_step()
+            steps += 1
+            eng.manager.check_invariants()
+        assert steps < 5000, "the engine does not come to an end"
+    assert eng.scheduler.stats["preemptions"] > 0, "the pool was meant to be too small"
+    for req, prompt, n in live:
+        assert req.finished is not None
+        if req.finished.value == "Refused":
+            continue
+        want = plain(prompt, n)
+        got = req.output
+        assert got == want[:len(got)], (req.rid, req.finished, len(prompt))
+        if req.finished.value == "MaxTokens":
+            assert len(got) == n
+        elif req.finished.value == "EndOfGeneration":
+            assert want[len(got)] in req.eog_tokens
+    assert eng.manager.free_pages() == {g.gid: eng.manager.num_pages for g in eng.manager.paged}
