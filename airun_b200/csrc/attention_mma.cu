@@ -327,7 +327,12 @@ __global__ __launch_bounds__(32 * DW) void attn_decode_kernel(const AttnParams p
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    pdl_wait();
+    // Keys and values of earlier positions were written by earlier steps, and the batch's layout was
+    // copied to the device before the step began: with TMA and no row list from a kernel of this step,
+    // the first tiles are requested before waiting for the kernel in front (which writes q and the
+    // newest key), so they stream in under its tail.  The tile that holds the newest key waits.
+    const bool early = TMA && x.n_rows_dev == nullptr;
+    if (!early) pdl_wait();
     __shared__ float s_m[DW][16], s_l[DW][16];
     __shared__ int s_ticket;
 
@@ -356,14 +361,6 @@ __global__ __launch_bounds__(32 * DW) void attn_decode_kernel(const AttnParams p
         ns = max(1, min(ns_stride, (n_tiles_all + 7) / 8));
         if (split >= ns) return;
     }
-
-    // Q rows -> shared memory (rows >= heads are zero)
-    for (int i = threadIdx.x; i < 16 * CHUNKS; i += 32 * DW) {
-        const int r = i / CHUNKS, c = i - r * CHUNKS;
-        const bool valid = r < heads;
-        cp_async16(smem_u32(sQ) + tile_off(r, c), p.q + ((size_t)tok * p.nh + head0 + (valid ? r : 0)) * HD + c * 8, valid);
-    }
-    cp_commit();
 
     // key tiles of this token, this slice, this warp
     const int per_split = (n_tiles_all + ns - 1) / ns;
@@ -423,11 +420,27 @@ __global__ __launch_bounds__(32 * DW) void attn_decode_kernel(const AttnParams p
         }
     };
     if (TMA) {
+        int deferred = -1;
         if (lane == 0)
-            for (int i = 0; i < DSTAGES - 1 && i < my_n; ++i) issue_tile(tb + warp + i * DW, i);
-    } else if (my_n > 0) {
-        load_tile(tb + warp, 0);
+            for (int i = 0; i < DSTAGES - 1 && i < my_n; ++i) {
+                const int tile = tb + warp + i * DW;
+                if (early && tile == pos / DN) deferred = i;           // holds the key the kernel in front writes
+                else issue_tile(tile, i);
+            }
+        if (early) {
+            pdl_wait();
+            if (deferred >= 0) issue_tile(tb + warp + deferred * DW, deferred);
+        }
     }
+    // Q rows -> shared memory (rows >= heads are zero)
+    for (int i = threadIdx.x; i < 16 * CHUNKS; i += 32 * DW) {
+        const int r = i / CHUNKS, c = i - r * CHUNKS;
+        const bool valid = r < heads;
+        cp_async16(smem_u32(sQ) + tile_off(r, c), p.q + ((size_t)tok * p.nh + head0 + (valid ? r : 0)) * HD + c * 8, valid);
+    }
+    cp_commit();
+
+    if (!TMA && my_n > 0) load_tile(tb + warp, 0);
 
     float m0 = NEG_BIG, m1 = NEG_BIG, l0 = 0.0f, l1 = 0.0f;
     float o[HD / 8][4];

@@ -147,12 +147,13 @@ __global__ __launch_bounds__(256) void qkv_post_hd128_kernel(
     int num_reqs, int num_pages, int page_size, int do_store, int kv_from_qkv,
     int nh, int nkv, int* __restrict__ err) {
     pdl_trigger();
-    pdl_wait();
     constexpr int HD = 128, HALF = 64;
     __shared__ float cs[2 * HALF];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nwarp = blockDim.x >> 5;
     const int t = blockIdx.x;
+    // positions and requests of the batch were copied to the device before the step began: the
+    // angles are worked out while the product in front of this kernel is still finishing
     const int pos = positions[t];
     const int req = req_of_token[t];
     const int total_heads = kv_from_qkv ? nh + 2 * nkv : nh;
@@ -163,6 +164,7 @@ __global__ __launch_bounds__(256) void qkv_post_hd128_kernel(
         cs[HALF + i] = s;
     }
     __syncthreads();
+    pdl_wait();
     const bool first = lane < 16;
     const int pair = 4 * (lane & 15);
     const float4 c4 = *reinterpret_cast<const float4*>(cs + pair);
