@@ -364,15 +364,15 @@ class CacheManager:
     # ------------------------------------------------------------ the batch of a step
     def build_batch(self, rids: Sequence[Hashable], qlens: Sequence[int], tokens: np.ndarray,
                     want_counts: Sequence[int], want: Sequence[int], base_ptr: int, offsets: ctypes.Array,
-                    max_reqs: int, bt_cols: int, pad_to: int, pad_want: int) -> Tuple[int, int, int, int, List[int]]:
+                    max_reqs: int, bt_cols: int, pad_to: int, pad_want: int) -> tuple:
         """Lays the batch of a step into the staging buffer at ``base_ptr`` (see csrc/host_core.cpp).
-        Returns (tokens, wanted rows, longest context, longest portion, slots)."""
+        Returns (tokens, wanted rows, longest context, longest portion, slots, shared prefix per group)."""
         slots = [self.requests[r].slot for r in rids]
-        out = (c_longlong * 4)()
+        out = (c_longlong * (4 + max(len(self.paged), 1)))()
         self._check(self._lib.airun_cache_build_batch(
             self._h, len(slots), _ints(slots), _ints(list(qlens)), tokens.ctypes.data, _ints(list(want_counts) or [0]),
             _ints(list(want) or [0]), base_ptr, offsets, max_reqs, bt_cols, pad_to, pad_want, out))
-        return out[0], out[1], out[2], out[3], slots
+        return out[0], out[1], out[2], out[3], slots, [out[4 + g.gid] for g in self.paged]
 
     # ------------------------------------------------------------ views
     def _blocks(self, slot: int, gid: int) -> List[int]:

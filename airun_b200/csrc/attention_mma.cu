@@ -135,28 +135,54 @@ __device__ __forceinline__ const __nv_bfloat16* key_row(const AttnParams& p, con
 
 struct PrefillTile { int req, tok0, n_tok, first_row; };   // tokens [tok0, tok0+n_tok) of the batch, all of request req
 
+// SHARED: the same kernel over a prefix of keys that several decoded tokens have in common (their
+// requests were forked from one: the first pages of their block tables are the same pages).  The
+// tokens of the batch, PM / G to a CTA, are the packed rows; every key below *k_end_dev is visible to
+// all of them; the keys are cut into gridDim.x slices; and instead of an output row the CTA writes
+// each row's (maximum, sum, unnormalised output) into the slice's slot of the decode kernel's
+// scratch, which merges them with the slices of the token's own keys.  The keys and values of the
+// prefix are then read once for all the tokens, not once for each.
+struct SharedArgs {
+    const int32_t* k_end_dev;   // keys [0, *k_end_dev) are shared
+    int n_tok;                  // tokens in the batch (rows 0 .. n_tok-1)
+    float* scratch;             // the decode kernel's partial results
+    int unit_stride, slot0;     // slots per (token, KV head, head group); first slot of this kernel's slices
+};
+
 // n_tiles_dev: null, or the number of tiles another kernel has written (the grid may be larger)
+template <bool SHARED>
 __global__ __launch_bounds__(PTHREADS, 2) void attn_prefill_kernel(const AttnParams p, const int4* __restrict__ tiles,
-                                                                   const int* __restrict__ n_tiles_dev) {
+                                                                   const int* __restrict__ n_tiles_dev, const SharedArgs sh) {
     pdl_trigger();
     pdl_wait();
-    if (n_tiles_dev && (int)blockIdx.x >= *n_tiles_dev) return;
+    if (!SHARED && n_tiles_dev && (int)blockIdx.x >= *n_tiles_dev) return;
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t* sQ = smem;                               // [PM][HD]
     uint8_t* sK = sQ + PM * HD * 2;                   // [2][PN][HD]
     uint8_t* sV = sK + 2 * PN * HD * 2;               // [2][PN][HD]
-    const int4 t4 = tiles[blockIdx.x];
-    const int req = t4.x, tok0 = t4.y, n_tok = t4.z;
-    const int kvh = blockIdx.y;
     const int G = p.G;
+    int req, tok0, n_tok;
+    if (SHARED) {
+        const int per = PM / G;
+        tok0 = blockIdx.z * per;
+        n_tok = min(per, sh.n_tok - tok0);
+        req = p.req_of_token[tok0];
+    } else {
+        const int4 t4 = tiles[blockIdx.x];
+        req = t4.x; tok0 = t4.y; n_tok = t4.z;
+    }
+    const int kvh = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int n_rows = n_tok * G;                     // valid packed rows (<= PM)
-    const int32_t* bt = p.block_table + (size_t)req * p.max_blocks;
+    const bool req_ok = req >= 0 && req < p.num_reqs;  // (a padded batch: rows of no request)
+    const int32_t* bt = p.block_table + (size_t)(req_ok ? req : 0) * p.max_blocks;
     const size_t v_off = (size_t)p.nkv * p.page_size * HD;
 
-    // positions of the first and last token of the tile (tokens of a request are in position order)
-    const int pos_lo = p.positions[tok0], pos_hi = p.positions[tok0 + n_tok - 1];
+    // positions of the first and last token of the tile (tokens of a request are in position order);
+    // SHARED: the last shared key stands for both
+    const int k_end = SHARED ? (req_ok ? *sh.k_end_dev : 0) : 0;
+    const int pos_lo = SHARED ? k_end - 1 : p.positions[tok0], pos_hi = SHARED ? k_end - 1 : p.positions[tok0 + n_tok - 1];
 
     // ---- Q tile -> shared memory
     for (int i = threadIdx.x; i < PM * CHUNKS; i += PTHREADS) {
@@ -167,10 +193,14 @@ __global__ __launch_bounds__(PTHREADS, 2) void attn_prefill_kernel(const AttnPar
     }
     cp_commit();
 
-    const int k_first = p.window > 0 ? max(0, pos_lo - p.window + 1) : 0;
-    const int tile_first = k_first / PN;
-    const int tile_last = pos_hi / PN;
-    const int n_tiles = tile_last - tile_first + 1;
+    const int k_first = (!SHARED && p.window > 0) ? max(0, pos_lo - p.window + 1) : 0;
+    int tile_first = k_first / PN;
+    int n_tiles = pos_hi >= 0 ? pos_hi / PN - tile_first + 1 : 0;
+    if (SHARED) {                                     // this CTA's slice of the shared tiles
+        const int per_slice = (n_tiles + (int)gridDim.x - 1) / (int)gridDim.x;
+        tile_first = min(n_tiles, (int)blockIdx.x * per_slice);
+        n_tiles = min(n_tiles, tile_first + per_slice) - tile_first;
+    }
 
     auto load_kv = [&](int tile, int stage) {
         const int j0 = tile * PN;
@@ -188,12 +218,12 @@ __global__ __launch_bounds__(PTHREADS, 2) void attn_prefill_kernel(const AttnPar
         cp_commit();
     };
 
-    load_kv(tile_first, 0);
+    if (n_tiles > 0) load_kv(tile_first, 0);
 
     // this thread's two rows: warp*16 + g and + 8
     const int r0 = warp * 16 + g, r1 = r0 + 8;
-    const int pos0 = r0 < n_rows ? p.positions[tok0 + r0 / G] : -1;
-    const int pos1 = r1 < n_rows ? p.positions[tok0 + r1 / G] : -1;
+    const int pos0 = r0 < n_rows ? (SHARED ? pos_hi : p.positions[tok0 + r0 / G]) : -1;
+    const int pos1 = r1 < n_rows ? (SHARED ? pos_hi : p.positions[tok0 + r1 / G]) : -1;
 
     float m0 = NEG_BIG, m1 = NEG_BIG, l0 = 0.0f, l1 = 0.0f;
     float o[HD / 8][4];
@@ -230,7 +260,7 @@ __global__ __launch_bounds__(PTHREADS, 2) void attn_prefill_kernel(const AttnPar
             for (int e = 0; e < 4; ++e) {
                 const int j = j0 + n * 8 + 2 * t + (e & 1);
                 const int pos = (e < 2) ? pos0 : pos1;
-                const bool vis = j <= pos && (p.window == 0 || pos - j < p.window);
+                const bool vis = j <= pos && (SHARED || p.window == 0 || pos - j < p.window);
                 const float v = vis ? s[n][e] * p.scale_log2 : NEG_BIG;
                 s[n][e] = v;
                 if (e < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
@@ -278,6 +308,27 @@ __global__ __launch_bounds__(PTHREADS, 2) void attn_prefill_kernel(const AttnPar
     l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    if (SHARED) {
+        if (n_tiles == 0) cp_wait<0>();               // (the Q tile was asked for and never used)
+        // (maximum, sum, unnormalised output) of each row into this slice's slot of the row's unit
+        const int hgroups = (G + 15) / 16;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int r = half ? r1 : r0;
+            if (r >= n_rows) continue;
+            const int tok = tok0 + r / G, hin = r % G;
+            const int unit = tok * (p.nkv * hgroups) + kvh * hgroups + hin / 16;
+            float* dst = sh.scratch + ((size_t)unit * sh.unit_stride + sh.slot0 + blockIdx.x) * (16 * (HD + 2))
+                         + (hin % 16) * (HD + 2);
+            if (t == 0) { dst[0] = half ? m1 : m0; dst[1] = half ? l1 : l0; }
+#pragma unroll
+            for (int n = 0; n < HD / 8; ++n) {
+                dst[2 + n * 8 + 2 * t] = o[n][2 * half];
+                dst[2 + n * 8 + 2 * t + 1] = o[n][2 * half + 1];
+            }
+        }
+        return;
+    }
     const float i0 = l0 > 0.0f ? 1.0f / l0 : 0.0f, i1 = l1 > 0.0f ? 1.0f / l1 : 0.0f;
     if (r0 < n_rows) {
         __nv_bfloat16* dst = p.out + ((size_t)(tok0 + r0 / G) * p.nh + kvh * G + r0 % G) * HD;
@@ -306,11 +357,16 @@ struct DecodeExtra {
     const int32_t* n_rows_dev;  // null, or: the rows in use are read on the device (the grid may be larger) and
     int dyn_slots;              //   every row picks its own number of slices, at most n_splits, so that about
                                 //   dyn_slots CTAs run and a slice has 128 keys or more
+    const int32_t* k_begin_dev; // null, or: keys below *k_begin_dev are not this kernel's (a shared prefix, whose
+    int extra_slices;           //   results another kernel has put into the extra_slices slots after this
+                                //   kernel's n_splits; they are merged with this kernel's own slices)
 };
 
 // TMA = true: K/V tiles arrive by cp.async.bulk.tensor (one lane of each warp issues HD/64 boxes per
 // tile, three stages per warp, an mbarrier per stage); TMA = false: cp.async, two stages, any page size.
-template <bool TMA>
+// WITH_PREFIX: the build that leaves a shared prefix to another kernel and merges its results
+// (k_begin_dev, extra_slices); a build of its own so that the plain one carries none of that code.
+template <bool TMA, bool WITH_PREFIX>
 __global__ __launch_bounds__(32 * DW) void attn_decode_kernel(const AttnParams p, const DecodeExtra x,
                                                               const __grid_constant__ CUtensorMap kv_map) {
     pdl_trigger();
@@ -351,7 +407,8 @@ __global__ __launch_bounds__(32 * DW) void attn_decode_kernel(const AttnParams p
     const bool live = req >= 0 && req < p.num_reqs && pos >= 0;
     const int32_t* bt = p.block_table + (size_t)(live ? req : 0) * p.max_blocks;
     const size_t v_off = (size_t)p.nkv * p.page_size * HD;
-    const int k_first = live ? (p.window > 0 ? max(0, pos - p.window + 1) : 0) : 0;
+    const int k_begin = (WITH_PREFIX && x.k_begin_dev) ? *x.k_begin_dev : 0;
+    const int k_first = live ? max(k_begin, p.window > 0 ? max(0, pos - p.window + 1) : 0) : 0;
     const int tile_first = k_first / DN;
     const int n_tiles_all = live ? pos / DN - tile_first + 1 : 0;
     int ns = x.n_splits, ns_stride = x.n_splits;       // slices of this row; slices the scratch has room for
@@ -546,7 +603,9 @@ __global__ __launch_bounds__(32 * DW) void attn_decode_kernel(const AttnParams p
     __syncthreads();
     // thread i handles element(s) (row, d): row = e / HD
     const int unit = blockIdx.z * gridDim.y + blockIdx.y;
-    float* part = ns > 1 ? x.scratch + ((size_t)unit * ns_stride + split) * (16 * (HD + 2)) : nullptr;
+    const int extra = WITH_PREFIX ? x.extra_slices : 0;
+    const int unit_stride = ns_stride + extra;
+    float* part = ns + extra > 1 ? x.scratch + ((size_t)unit * unit_stride + split) * (16 * (HD + 2)) : nullptr;
     for (int e = threadIdx.x; e < heads * HD; e += 32 * DW) {
         const int r = e / HD, d = e - r * HD;
         float gm = NEG_BIG;
@@ -577,13 +636,15 @@ __global__ __launch_bounds__(32 * DW) void attn_decode_kernel(const AttnParams p
     // The last CTA of this token and head group merges the slices, in slice order.  The loads of
     // several slices and elements are issued together: this part runs alone, so what it costs is
     // the number of dependent round trips to the L2 cache.
-    const float* all = x.scratch + (size_t)unit * ns_stride * (16 * (HD + 2));
+    const float* all = x.scratch + (size_t)unit * unit_stride * (16 * (HD + 2));
+    const int nt = ns + extra;                                 // this kernel's slices, then the other kernel's
+    auto slot = [&](int sp) { return sp < ns ? sp : ns_stride + (sp - ns); };
     __shared__ float s_f[MAX_SPLITS][16];
     __shared__ float s_l2[MAX_SPLITS][16];
     __shared__ float s_inv[16];
-    for (int i = threadIdx.x; i < ns * 16; i += 32 * DW) {
+    for (int i = threadIdx.x; i < nt * 16; i += 32 * DW) {
         const int sp = i >> 4, r = i & 15;
-        const float* ps = all + (size_t)sp * 16 * (HD + 2) + r * (HD + 2);
+        const float* ps = all + (size_t)slot(sp) * 16 * (HD + 2) + r * (HD + 2);
         s_f[sp][r] = r < heads ? __ldcg(ps) : NEG_BIG;          // the slice's maximum
         s_l2[sp][r] = r < heads ? __ldcg(ps + 1) : 0.0f;        // and its sum
     }
@@ -591,9 +652,9 @@ __global__ __launch_bounds__(32 * DW) void attn_decode_kernel(const AttnParams p
     if (threadIdx.x < heads) {
         const int r = threadIdx.x;
         float gm = NEG_BIG;
-        for (int sp = 0; sp < ns; ++sp) gm = fmaxf(gm, s_f[sp][r]);
+        for (int sp = 0; sp < nt; ++sp) gm = fmaxf(gm, s_f[sp][r]);
         float sum = 0.0f;
-        for (int sp = 0; sp < ns; ++sp) {
+        for (int sp = 0; sp < nt; ++sp) {
             const float l = s_l2[sp][r];
             const float f = l > 0.0f ? exp2f(s_f[sp][r] - gm) : 0.0f;
             s_f[sp][r] = f;
@@ -608,7 +669,7 @@ __global__ __launch_bounds__(32 * DW) void attn_decode_kernel(const AttnParams p
         float acc[EG];
 #pragma unroll
         for (int k = 0; k < EG; ++k) acc[k] = 0.0f;
-        for (int s0 = 0; s0 < ns; s0 += SG) {
+        for (int s0 = 0; s0 < nt; s0 += SG) {
             float v[EG][SG];
 #pragma unroll
             for (int k = 0; k < EG; ++k) {
@@ -616,8 +677,8 @@ __global__ __launch_bounds__(32 * DW) void attn_decode_kernel(const AttnParams p
                 const int r = e / HD, d = e - r * HD;
 #pragma unroll
                 for (int j = 0; j < SG; ++j)
-                    v[k][j] = (e < total && s0 + j < ns)
-                                  ? __ldcg(all + (size_t)(s0 + j) * 16 * (HD + 2) + r * (HD + 2) + 2 + d) : 0.0f;
+                    v[k][j] = (e < total && s0 + j < nt)
+                                  ? __ldcg(all + (size_t)slot(s0 + j) * 16 * (HD + 2) + r * (HD + 2) + 2 + d) : 0.0f;
             }
 #pragma unroll
             for (int k = 0; k < EG; ++k) {
@@ -625,7 +686,7 @@ __global__ __launch_bounds__(32 * DW) void attn_decode_kernel(const AttnParams p
                 const int r = e < total ? e / HD : 0;
 #pragma unroll
                 for (int j = 0; j < SG; ++j)
-                    if (s0 + j < ns) acc[k] = fmaf(v[k][j], s_f[s0 + j][r], acc[k]);
+                    if (s0 + j < nt) acc[k] = fmaf(v[k][j], s_f[s0 + j][r], acc[k]);
             }
         }
 #pragma unroll
@@ -711,11 +772,42 @@ AIRUN_EXPORT int airun_attn_prefill(const void* q, void* out, const void* pool, 
     const int smem = (PM + 4 * PN) * HD * 2;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    airun_launch(attn_prefill_kernel, dim3(n_tiles, nkv), dim3(PTHREADS), smem, stream, p, (const int4*)tiles, n_tiles_dev);
+    airun_launch(attn_prefill_kernel<false>, dim3(n_tiles, nkv), dim3(PTHREADS), smem, stream, p, (const int4*)tiles, n_tiles_dev, SharedArgs{});
+    return airun_launch_status();
+}
+
+// The shared prefix of a batch of decoded tokens (rows 0 .. n_tok-1 of the batch, whose block tables
+// begin with the same pages): keys [0, *k_end_dev) in `slices` slices, results into slots
+// n_splits .. n_splits+slices-1 of every (token, KV head, head group) unit of the decode kernel's
+// scratch, which has n_splits + slices slots per unit.  airun_attn_decode with k_begin_dev = k_end_dev
+// and extra_slices = slices, launched after this on the same stream, does the rest.
+AIRUN_EXPORT int airun_attn_shared_prefix(const void* q, const void* pool, const int32_t* block_table, int max_blocks,
+                                          const int32_t* positions, const int32_t* req_of_token, int num_reqs,
+                                          int num_pages, int page_size, int nh, int nkv, float scale, int n_tok,
+                                          const int32_t* k_end_dev, int slices, int n_splits, float* scratch, int* err,
+                                          cudaStream_t stream) {
+    if (n_tok <= 0 || nh <= 0 || nkv <= 0 || nh % nkv != 0 || nh / nkv > PM || page_size <= 0 || !err || !k_end_dev ||
+        !scratch || slices < 1 || n_splits < 1 || slices + n_splits > MAX_SPLITS)
+        return AIRUN_ERR_ARG;
+    const AttnParams p = make_params(q, nullptr, pool, block_table, max_blocks, positions, req_of_token, num_reqs,
+                                     num_pages, page_size, nh, nkv, scale, 0, err);
+    const int per = PM / (nh / nkv);
+    const int groups = (n_tok + per - 1) / per;
+    if (nkv > 65535 || groups > 65535) return AIRUN_ERR_ARG;
+    const int smem = (PM + 4 * PN) * HD * 2;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    SharedArgs sh{k_end_dev, n_tok, scratch, n_splits + slices, n_splits};
+    airun_launch(attn_prefill_kernel<true>, dim3(slices, nkv, groups), dim3(PTHREADS), smem, stream, p,
+                 (const int4*)nullptr, (const int*)nullptr, sh);
     return airun_launch_status();
 }
 
@@ -732,9 +824,11 @@ AIRUN_EXPORT int airun_attn_decode(const void* q, void* out, const void* pool, c
                                    int max_blocks, const int32_t* positions, const int32_t* req_of_token,
                                    int num_reqs, int num_pages, int page_size, int nh, int nkv, float scale,
                                    int window, const int32_t* rows, int n_rows, int n_splits, float* scratch,
-                                   int* counters, const int32_t* n_rows_dev, int dyn_slots, int* err,
-                                   cudaStream_t stream) {
+                                   int* counters, const int32_t* n_rows_dev, int dyn_slots, const int32_t* k_begin_dev,
+                                   int extra_slices, int* err, cudaStream_t stream) {
     if (n_rows_dev && (dyn_slots <= 0 || !rows)) return AIRUN_ERR_ARG;
+    if (extra_slices < 0 || n_splits + extra_slices > MAX_SPLITS || (extra_slices > 0 && (n_rows_dev || !k_begin_dev || !scratch || !counters)))
+        return AIRUN_ERR_ARG;
     if (n_rows < 0 || nh <= 0 || nkv <= 0 || nh % nkv != 0 || page_size <= 0 || n_splits < 1 || n_splits > MAX_SPLITS || !err) return AIRUN_ERR_ARG;
     if (n_splits > 1 && (!scratch || !counters)) return AIRUN_ERR_ARG;
     if (n_rows == 0) return AIRUN_OK;
@@ -742,7 +836,7 @@ AIRUN_EXPORT int airun_attn_decode(const void* q, void* out, const void* pool, c
     if (nkv * hgroups > 65535 || n_rows > 65535) return AIRUN_ERR_ARG;
     const AttnParams p = make_params(q, out, pool, block_table, max_blocks, positions, req_of_token, num_reqs,
                                      num_pages, page_size, nh, nkv, scale, window, err);
-    DecodeExtra x{rows, n_splits, scratch, counters, n_rows_dev, dyn_slots};
+    DecodeExtra x{rows, n_splits, scratch, counters, n_rows_dev, dyn_slots, k_begin_dev, extra_slices};
     // TMA needs whole 16-key tiles inside one page and 128-byte boxes
     static const bool tma_allowed = !(getenv("AIRUN_ATTN_TMA") && getenv("AIRUN_ATTN_TMA")[0] == '0');
     const bool tma = tma_allowed && (HD % 64 == 0) && p.page_shift >= 4 && encode_fn() != nullptr;
@@ -754,14 +848,16 @@ AIRUN_EXPORT int airun_attn_decode(const void* q, void* out, const void* pool, c
     }
     const int stages = tma ? 3 : 2;
     const int smem = DW * stages * 2 * DN * HD * 2 + 16 * HD * 2 + DW * 3 * 8 + 1024;
-    static bool configured[2] = {false, false};
-    if (!configured[tma ? 1 : 0]) {
-        cudaError_t e = tma ? cudaFuncSetAttribute(attn_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)
-                            : cudaFuncSetAttribute(attn_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    static bool configured[4] = {false, false, false, false};
+    const bool prefix = extra_slices > 0 || k_begin_dev != nullptr;
+    const int which = (tma ? 1 : 0) + (prefix ? 2 : 0);
+    auto kern = which == 0 ? attn_decode_kernel<false, false> : which == 1 ? attn_decode_kernel<true, false>
+              : which == 2 ? attn_decode_kernel<false, true> : attn_decode_kernel<true, true>;
+    if (!configured[which]) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return (int)e;
-        configured[tma ? 1 : 0] = true;
+        configured[which] = true;
     }
-    if (tma) airun_launch(attn_decode_kernel<true>, dim3(n_splits, nkv * hgroups, n_rows), dim3(32 * DW), smem, stream, p, x, map);
-    else airun_launch(attn_decode_kernel<false>, dim3(n_splits, nkv * hgroups, n_rows), dim3(32 * DW), smem, stream, p, x, map);
+    airun_launch(kern, dim3(n_splits, nkv * hgroups, n_rows), dim3(32 * DW), smem, stream, p, x, map);
     return airun_launch_status();
 }

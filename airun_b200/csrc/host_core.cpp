@@ -419,7 +419,10 @@ HOST_EXPORT int airun_cache_check(void* h) {
 // want: the wanted places of every entry (relative to its own tokens), want_counts of them each.
 // pad_to > 0: rows up to pad_to belong to request -1 at position -1 and cu_tokens is filled to
 // R_max; pad_want: wanted rows up to pad_want name row 0.  out: {tokens, wanted rows, longest
-// context, longest portion}.
+// context, longest portion, then per group the shared prefix}.  The shared prefix of a group, also
+// written to the word at offs[7 + groups + g], is the number of tokens at the start of every
+// request of the batch that lie in the very same pages (requests forked from one): whole pages only,
+// 0 unless every request brings a single token, there are two or more, and the group has no window.
 HOST_EXPORT int airun_cache_build_batch(void* h, int count, const int* slots, const int* qlens, const int32_t* tokens,
                                         const int* want_counts, const int* want, int32_t* base, const long long* offs,
                                         int R_max, int bt_cols, int pad_to, int pad_want, long long* out) {
@@ -460,6 +463,23 @@ HOST_EXPORT int airun_cache_build_batch(void* h, int count, const int* slots, co
         int32_t* bt = base + offs[7 + g];
         for (int r = 0; r < count; ++r)
             std::memcpy(bt + (size_t)r * bt_cols, c->row((int)g, slots[r]), (size_t)need_blocks * sizeof(int32_t));
+    }
+    for (size_t g = 0; g < c->groups.size(); ++g) {
+        long long shared = 0;
+        if (count >= 2 && max_q == 1 && c->groups[g].window == 0) {
+            long long blocks = c->max_blocks;
+            for (int r = 0; r < count; ++r) blocks = std::min(blocks, c->reqs[slots[r]].num_tokens / c->page_size);
+            const int32_t* first = c->row((int)g, slots[0]);
+            for (int r = 1; r < count && blocks > 0; ++r) {
+                const int32_t* other = c->row((int)g, slots[r]);
+                long long b = 0;
+                while (b < blocks && other[b] == first[b] && first[b] >= 0) ++b;
+                blocks = b;
+            }
+            shared = blocks * c->page_size;
+        }
+        base[offs[7 + c->groups.size() + g]] = (int32_t)shared;
+        out[4 + g] = shared;
     }
     const long long real = t;
     if (pad_to > 0) {

@@ -64,6 +64,8 @@ class CacheView:
     page_size: int = 0
     state: Optional[torch.Tensor] = None        # [max_requests, *shape]
     gid: int = -1
+    shared_prefix: Optional[torch.Tensor] = None   # int32 [1] on the device: tokens at the start of every request of
+                                                   # the batch that lie in the very same pages (0: none, or not known)
 
 
 @dataclass

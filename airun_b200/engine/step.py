@@ -52,6 +52,7 @@ class StepRunner:
                  ("want_rows", self.T_max), ("cu_tokens", self.R_max + 1), ("context_lens", self.R_max),
                  ("state_slots", self.R_max)]
         sizes += [(f"bt{g}", self.R_max * self.max_blocks) for g in range(n_groups)]
+        sizes += [(f"shared{g}", 1) for g in range(n_groups)]      # tokens at the start that all requests share
         self.offsets: Dict[str, tuple] = {}
         off = 0
         for name, n in sizes:
@@ -67,7 +68,7 @@ class StepRunner:
         self._ring_used = [False] * 4
         self.meta_dev = torch.zeros(off, dtype=torch.int32, device=self.device)
         names = ["token_ids", "positions", "req_of_token", "want_rows", "cu_tokens", "context_lens", "state_slots"]
-        names += [f"bt{g}" for g in range(n_groups)]
+        names += [f"bt{g}" for g in range(n_groups)] + [f"shared{g}" for g in range(n_groups)]
         self._offs = (ctypes.c_longlong * len(names))(*[self.offsets[n][0] for n in names])
         self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.ws_main = Workspace(self.device)
@@ -102,7 +103,7 @@ class StepRunner:
             if b.kind == "paged":
                 bt = self._view(f"bt{b.gid}").view(self.R_max, self.max_blocks)
                 views.append(CacheView("paged", b.shared, self.storage.paged[b.gid][b.index], bt,
-                                       self.manager.page_size, gid=b.gid))
+                                       self.manager.page_size, gid=b.gid, shared_prefix=self._view(f"shared{b.gid}")))
             elif b.kind == "state":
                 views.append(CacheView("state", b.shared, state=self.storage.state[b.gid][b.index], gid=b.gid))
             else:
@@ -154,7 +155,7 @@ class StepRunner:
         else:
             toks = np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries])
         want = [w for e in entries for w in e.want]
-        t, n_want, max_ctx, max_q, slots = m.build_batch(
+        t, n_want, max_ctx, max_q, slots, shared = m.build_batch(
             [e.rid for e in entries], qlens, toks, [len(e.want) for e in entries], want,
             self.meta_host.data_ptr(), self._offs, self.R_max, self.max_blocks, pad_to, pad_want)
         clens = self._view("context_lens", dev=False)[:R].tolist()
@@ -172,6 +173,7 @@ class StepRunner:
             query_lens=qlens, context_lens_host=clens, state_slots_host=slots,
             max_query_len=max_q, max_context_len=max_ctx,
             decode_only=max_q == 1)
+        ctx.extras["shared_prefix_host"] = shared
         return ctx, n_want
 
     def step(self, entries: Sequence[StepEntry], checked: bool = False) -> Optional[torch.Tensor]:
@@ -202,11 +204,16 @@ class StepRunner:
         (the step then goes the ordinary way); raises OutOfPages like ``step``."""
         n = len(rids)
         bucket = next((b for b in self.graph_buckets if b >= n), None)
-        if not self.use_graphs or self.device.type != "cuda" or bucket is None or bucket not in self.graphs:
+        if not self.use_graphs or self.device.type != "cuda" or bucket is None:
+            return None
+        if bucket not in self.graphs and ("shared", bucket) not in self.graphs:
             return None
         self.manager.reserve_many(rids, [1] * n)
-        self.build_context([StepEntry(r, (0,), (0,)) for r in rids], pad_to=bucket)
-        return dict(rids=list(rids), bucket=bucket, slot=self._ring_i)
+        ctx, _ = self.build_context([StepEntry(r, (0,), (0,)) for r in rids], pad_to=bucket)
+        key = self._decode_key(ctx, bucket)
+        if key not in self.graphs:
+            return None                 # (the pages are taken and the lay-out is unused: the ordinary path redoes it)
+        return dict(rids=list(rids), key=key, slot=self._ring_i)
 
     def launch_prepared(self, prep: dict, tokens: Sequence[int]) -> torch.Tensor:
         """Second half of ``prepare_decode``: the tokens go to the device and the graph is replayed.
@@ -218,12 +225,25 @@ class StepRunner:
         self.meta_dev[off:off + n].copy_(host[off:off + n], non_blocking=True)
         if event is not None:
             event.record()
-        graph, out, kernels = self.graphs[prep["bucket"]]
+        graph, out, kernels = self.graphs[prep["key"]]
         graph.replay()
         self.graph_launches += kernels
         self.manager.commit_many(prep["rids"], [1] * n)
         self.steps_run += 1
         return out[:n]
+
+    SHARED_PREFIX_MIN = 1024       # tokens all requests of a decode step must share before it pays to read them once
+
+    def _decode_key(self, ctx, bucket: int):
+        """The graph a step of single tokens runs from: the plain one of its batch-size bucket, or,
+        when the requests of the batch begin with the same pages (forks of one request), the one
+        whose attention reads that shared prefix once for all of them."""
+        ctx.extras["planning_context_len"] = self.max_context
+        shared = ctx.extras.get("shared_prefix_host") or [0]
+        if self.mixed_graphs and max(shared) >= self.SHARED_PREFIX_MIN:
+            ctx.extras["use_shared_prefix"] = True
+            return ("shared", bucket)
+        return bucket
 
     def _decode_step_graphed(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """A step of single decoded tokens, all of whose logits are wanted, replayed from a
@@ -238,8 +258,7 @@ class StepRunner:
             ctx, n_want = self.build_context(entries)
             return self.model.forward(ctx, self._view("want_rows"), n_want)
         ctx, n_want = self.build_context(entries, pad_to=bucket)
-        ctx.extras["planning_context_len"] = self.max_context
-        return self._run_graphed(bucket, ctx, self.want_arange, bucket)[:n]
+        return self._run_graphed(self._decode_key(ctx, bucket), ctx, self.want_arange, bucket)[:n]
 
     def _run_graphed(self, key, ctx, want_rows: torch.Tensor, n_want: int) -> Optional[torch.Tensor]:
         """Runs the padded batch of ``ctx``: kernel by kernel the first time a step of this shape comes

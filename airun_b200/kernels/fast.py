@@ -258,11 +258,14 @@ def attn_prefill_tc(ctx, q, out, cache, nh, nkv, hd, scale, window, tiles: torch
 
 
 def attn_decode(ctx, q, out, cache, nh, nkv, hd, scale, window, rows: torch.Tensor, n_rows: int, n_splits: int,
-                n_rows_dev: Optional[torch.Tensor] = None, dyn_slots: int = 0) -> None:
+                n_rows_dev: Optional[torch.Tensor] = None, dyn_slots: int = 0,
+                k_begin_dev: Optional[torch.Tensor] = None, extra_slices: int = 0) -> None:
     """Attention of single decoded tokens (batch rows ``rows``; None: rows 0..n_rows-1), the keys cut
     into ``n_splits`` slices.  With ``n_rows_dev`` (int32 on the device) the launch is made for ``n_rows``
     rows and ``n_splits`` slices, runs the rows counted there, and every row picks its slices itself so
-    that about ``dyn_slots`` CTAs run."""
+    that about ``dyn_slots`` CTAs run.  With ``k_begin_dev`` (int32 on the device) the keys below that
+    position are left out and the ``extra_slices`` results another kernel (``attn_shared_prefix``) has
+    put into the scratch for them are merged in."""
     _cuda(q, out, cache.pool, cache.block_table, rows)
     _need(q.dtype == torch.bfloat16 and cache.pool.dtype == torch.bfloat16 and q.is_contiguous() and out.is_contiguous(),
           "tensor-core attention takes contiguous bfloat16 q, out and pages")
@@ -270,16 +273,41 @@ def attn_decode(ctx, q, out, cache, nh, nkv, hd, scale, window, rows: torch.Tens
         _need(rows.dtype == torch.int32 and rows.is_contiguous() and rows.numel() >= n_rows, "rows must be int32 [n]")
     scratch, counters = scratch_for(q.device)
     hgroups = (nh // nkv + 15) // 16
-    if n_splits > 1:
+    if n_splits + extra_slices > 1:
         # rows picking their own slices use at most max(dyn_slots, rows x head groups) slices together
         units = n_rows * nkv * hgroups
-        need = (units * n_splits if n_rows_dev is None else max(dyn_slots, units)) * 16 * (hd + 2)
+        need = (units * (n_splits + extra_slices) if n_rows_dev is None else max(dyn_slots, units)) * 16 * (hd + 2)
         _need(need <= scratch.numel() and n_rows * nkv * hgroups <= counters.numel(),
               "split-K scratch is too small for this decode launch")
     f = _fn("attention_mma", "airun_attn_decode",
-            _COMMON_SIG + [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p], {"HD": hd})
+            _COMMON_SIG + [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p],
+            {"HD": hd})
     _check(f(*_attn_common_args(q, out, cache, ctx, nh, nkv, scale, window), _p(rows), n_rows, n_splits,
-             _p(scratch), _p(counters), _p(n_rows_dev), int(dyn_slots), _p(ctx.err), _stream()), "attn_decode")
+             _p(scratch), _p(counters), _p(n_rows_dev), int(dyn_slots), _p(k_begin_dev), int(extra_slices),
+             _p(ctx.err), _stream()), "attn_decode")
+
+
+def attn_shared_prefix(ctx, q, cache, nh, nkv, hd, scale, n_rows: int, k_end_dev: torch.Tensor, slices: int,
+                       n_splits: int) -> None:
+    """First half of the attention of decoded tokens whose requests begin with the same pages: the keys
+    [0, k_end) once for all of them (rows 0..n_rows-1 of the batch), in ``slices`` slices whose results go
+    to the decode kernel's scratch; ``attn_decode(..., k_begin_dev=k_end_dev, extra_slices=slices)`` with
+    the same ``n_splits`` must follow on the same stream."""
+    _cuda(q, cache.pool, cache.block_table, k_end_dev)
+    _need(q.dtype == torch.bfloat16 and cache.pool.dtype == torch.bfloat16 and q.is_contiguous(),
+          "tensor-core attention takes contiguous bfloat16 q and pages")
+    _need(k_end_dev.dtype == torch.int32 and k_end_dev.numel() >= 1, "k_end_dev must be int32 [1]")
+    scratch, _ = scratch_for(q.device)
+    hgroups = (nh // nkv + 15) // 16
+    _need(n_rows * nkv * hgroups * (n_splits + slices) * 16 * (hd + 2) <= scratch.numel(),
+          "split-K scratch is too small for this shared-prefix launch")
+    pool, bt = cache.pool, cache.block_table
+    f = _fn("attention_mma", "airun_attn_shared_prefix",
+            [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
+             c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p], {"HD": hd})
+    _check(f(_p(q), _p(pool), _p(bt), bt.stride(0), _p(ctx.positions), _p(ctx.req_of_token), int(ctx.num_reqs),
+             pool.shape[0], pool.shape[3], nh, nkv, float(scale), int(n_rows), _p(k_end_dev), int(slices), int(n_splits),
+             _p(scratch), _p(ctx.err), _stream()), "attn_shared_prefix")
 
 
 def attn_plan(ctx, per_tile: int, tiles: torch.Tensor, rows: torch.Tensor, counts: torch.Tensor) -> None:
@@ -382,7 +410,28 @@ def attention_bf16(ctx, q, out, cache, nh: int, nkv: int, hd: int, scale: float,
             most = max(1, min(64, (context + DECODE_MIN_KEYS_PER_SPLIT - 1) // DECODE_MIN_KEYS_PER_SPLIT, fit))
             attn_decode(ctx, q, out, cache, nh, nkv, hd, scale, window, plan["rows"], plan["n_rows"], most,
                         n_rows_dev, slots)
+        elif (ctx.extras.get("use_shared_prefix") and plan["rows"] is None and window == 0
+              and getattr(cache, "shared_prefix", None) is not None and _shared_prefix_slices(plan["n_rows"], nkv, G, hd) > 0):
+            # the requests of the batch begin with the same pages: those keys once for all tokens (in
+            # slices of their own), each token's later keys as usual, one merge
+            splits = plan_decode_splits(plan["n_rows"], nkv, (G + 15) // 16, min(context, SHARED_SUFFIX_PLAN), hd, slots)
+            slices = _shared_prefix_slices(plan["n_rows"], nkv, G, hd, splits)
+            attn_shared_prefix(ctx, q, cache, nh, nkv, hd, scale, plan["n_rows"], cache.shared_prefix, slices, splits)
+            attn_decode(ctx, q, out, cache, nh, nkv, hd, scale, window, None, plan["n_rows"], splits,
+                        k_begin_dev=cache.shared_prefix, extra_slices=slices)
         else:
             splits = plan_decode_splits(plan["n_rows"], nkv, (G + 15) // 16, context, hd, slots)
             attn_decode(ctx, q, out, cache, nh, nkv, hd, scale, window, plan["rows"], plan["n_rows"], splits)
     return True
+
+
+SHARED_SUFFIX_PLAN = 2048              # keys after the shared prefix the slice count of such a step is chosen for
+
+
+def _shared_prefix_slices(n_rows: int, nkv: int, G: int, hd: int, splits: int = 8) -> int:
+    """Slices of the shared keys: about one CTA per SM slot, as many as the scratch has room for
+    beside the ``splits`` slices of the tokens' own keys, at most 64 of both together."""
+    groups = -(-n_rows * G // PREFILL_ROWS)
+    want = max(1, min(32, 296 // max(1, nkv * groups)))
+    room = SCRATCH_FLOATS // (n_rows * nkv * ((G + 15) // 16) * 16 * (hd + 2)) - splits
+    return max(0, min(want, room, 64 - splits))

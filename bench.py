@@ -268,7 +268,8 @@ def workload_serve(a) -> int:
 def workload_long(a) -> int:
     """Long context: one 32,768-token prompt in portions of 2,048, then 512 tokens decoded alone, then
     15 forks of the request (reading the same prompt pages: 16 private caches would not fit beside
-    the weights) and 512 tokens decoded by all 16 (Qwen3-32B shape)."""
+    the weights; attention reads those pages once per step for all 16) and 512 tokens decoded by all
+    16 (Qwen3-32B shape)."""
     import torch
     from airun_b200 import Engine, EngineOptions, Qwen3Config, SamplingParams
     d = dict(QWEN3_32B)

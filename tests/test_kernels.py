@@ -471,3 +471,59 @@ def test_sample_kernel_distribution():
     counts = np.bincount(out.cpu().numpy(), minlength=4)
     chi2 = float(((counts - n * probs.numpy()) ** 2 / (n * probs.numpy())).sum())
     assert chi2 < 16.3
+
+
+@pytest.mark.parametrize("R,G,S,page", [(16, 8, 1040, 16), (5, 4, 272, 16), (40, 4, 128, 32), (3, 2, 64, 8)])
+def test_shared_prefix_attention(R, G, S, page):
+    """Decoded tokens whose requests begin with the same pages: the shared keys once for all of them
+    (several slices), each token's own later keys by the decode kernel, one merge; against plain
+    attention over each request's whole context."""
+    from airun_b200.kernels import fast
+    torch.manual_seed(11)
+    nkv, hd = 2, 128
+    nh = nkv * G
+    own = [int(x) for x in torch.randint(1, 90, (R,))]
+    shared_k, shared_v = torch.randn(S, nkv, hd), torch.randn(S, nkv, hd)
+    ks = [torch.cat([shared_k, torch.randn(n, nkv, hd)]).to(torch.bfloat16).float() for n in own]
+    vs = [torch.cat([shared_v, torch.randn(n, nkv, hd)]).to(torch.bfloat16).float() for n in own]
+    lens = [S + n for n in own]
+    # pages: the first S / page of every block table are the same pages
+    n_shared = S // page
+    blocks = [(n + page - 1) // page for n in lens]
+    n_pages = n_shared + sum(b - n_shared for b in blocks) + 3
+    perm = np.random.default_rng(3).permutation(n_pages)
+    pool = torch.full((n_pages, 2, nkv, page, hd), 1e4)
+    bt = torch.full((R, max(blocks) + 1), -1, dtype=torch.int32)
+    nxt = n_shared
+    for r in range(R):
+        for b in range(blocks[r]):
+            if b < n_shared:
+                pg = int(perm[b])
+            else:
+                pg = int(perm[nxt]); nxt += 1
+            bt[r, b] = pg
+            n = min(page, lens[r] - b * page)
+            pool[pg, 0, :, :n] = ks[r][b * page:b * page + n].transpose(0, 1)
+            pool[pg, 1, :, :n] = vs[r][b * page:b * page + n].transpose(0, 1)
+    pool, bt = pool.to(torch.bfloat16).to(DEV), bt.to(DEV)
+    pos = [n - 1 for n in lens]
+    ctx = Ctx(pos, list(range(R)), R, [1] * R, lens)
+    q = torch.randn(R, nh, hd).to(torch.bfloat16).float()
+    want = torch.zeros(R, nh, hd, dtype=torch.float64)
+    for r in range(R):                                   # softmax(q K^T / sqrt(d)) V over the request's whole context
+        for h in range(nh):
+            sc = (ks[r][:, h // G].double() @ q[r, h].double()) * hd ** -0.5
+            want[r, h] = torch.softmax(sc, 0) @ vs[r][:, h // G].double()
+    want = want.reshape(R, nh * hd)
+    qd = q.to(torch.bfloat16).to(DEV).view(R, nh * hd)
+    out = torch.zeros_like(qd)
+    cache = Cache(pool, bt, page)
+    k_end = torch.tensor([S], dtype=torch.int32, device=DEV)
+    for splits, slices in ((1, 3), (2, 7)):
+        out.zero_()
+        fast.attn_shared_prefix(ctx, qd, cache, nh, nkv, hd, hd ** -0.5, R, k_end, slices, splits)
+        fast.attn_decode(ctx, qd, out, cache, nh, nkv, hd, hd ** -0.5, 0, None, R, splits,
+                         k_begin_dev=k_end, extra_slices=slices)
+        torch.cuda.synchronize()
+        assert ctx.err.item() == 0
+        assert torch.allclose(out.float().cpu(), want.float(), atol=2e-2, rtol=2e-2), (splits, slices)

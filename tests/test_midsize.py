@@ -206,3 +206,46 @@ def test_layers_of_the_8b_size_bfloat16_agrees_with_float32():
         pick = int(outs["bfloat16"][i].argmax())
         noise = float(np.abs(outs["float32"][i] - outs["bfloat16"][i]).max())
         assert outs["float32"][i].max() - outs["float32"][i][pick] <= 2 * noise, i
+
+
+def test_forked_requests_read_their_shared_prompt_once(engines):
+    """Four requests forked from one 1,300-token prompt decode side by side: the step's attention reads
+    the pages they share once for all of them (a graph of its own).  The logits must be those of the
+    same step with that path switched off, up to the order of sums."""
+    from airun_b200 import StepEntry
+    eng = engines["bfloat16"]
+    g = np.random.default_rng(21)
+    prompt = [int(t) for t in g.integers(0, MID["vocab_size"], size=1300)]
+    tails = [[int(t) for t in g.integers(0, MID["vocab_size"], size=14)] for _ in range(4)]
+    outs = {}
+    for shared_path in (True, False):
+        eng.runner.SHARED_PREFIX_MIN = 1024 if shared_path else 1 << 30
+        m = eng.manager
+        m.add_request("p")
+        eng.runner.step([StepEntry("p", prompt[:700], ())])
+        eng.runner.step([StepEntry("p", prompt[700:], ())])
+        for i in range(1, 4):
+            eng.storage.run_copies(m.fork("p", f"f{i}"))
+        rids = ["p", "f1", "f2", "f3"]
+        rows = []
+        for k in range(14):
+            if k == 9:                                    # one of them leaves: three go on sharing
+                m.free_request("f2")
+                rids.remove("f2")
+            idx = [("p", "f1", "f2", "f3").index(r) for r in rids]
+            out = eng.runner.step([StepEntry(r, [tails[i][k]], (0,)) for r, i in zip(rids, idx)])
+            rows.append(out.float().cpu().numpy())
+        eng.runner.raise_on_device_error()
+        outs[shared_path] = np.concatenate(rows)
+        if shared_path:
+            assert any(isinstance(k, tuple) and k[0] == "shared" for k in eng.runner.graphs), "the shared-prefix path never ran"
+        for r in rids:
+            m.free_request(r)
+        m.check_invariants()
+    eng.runner.SHARED_PREFIX_MIN = 1024
+    a, b = outs[True], outs[False]
+    assert a.shape == b.shape and np.isfinite(a).all()
+    scale = float(np.abs(b).max())
+    assert float(np.abs(a - b).max()) <= 0.02 * scale, float(np.abs(a - b).max()) / scale
+    for i in range(a.shape[0]):
+        assert cosine(a[i], b[i]) > 0.9999, i
