@@ -316,6 +316,7 @@ def workload_long(a) -> int:
     flops = 2.0 * T * L * per_layer + L * cfg.num_attention_heads * 4.0 * cfg.head_dim * T * (T + 1) / 2
     b1_bytes = decode_bytes(cfg, L, 1, T + new // 2, esz)
     bn_bytes = decode_bytes(cfg, L, forks + 1, T + new + new // 2, esz)
+    once_bytes = decode_bytes(cfg, L, 1, T, esz) + (forks + 1) * (new + new // 2) * 2 * cfg.kv_dim * esz * L
     print(json.dumps({
         "workload": "long", "model": "Qwen3-32B shape, random weights", "layers": L, "layers_full": 64,
         "prompt_tokens": T, "portion": 2048, "dtype": a.dtype, "peaks": pk["source"],
@@ -326,7 +327,9 @@ def workload_long(a) -> int:
         f"decode_b{forks + 1}": {"tokens": n_steps * (forks + 1), "tokens_per_s": round(n_steps * (forks + 1) / t_bn, 2),
                                  "ms_per_step": round(t_bn * 1e3 / n_steps, 3), "shared_prompt_pages": True,
                                  "hbm_frac_if_every_request_reads_the_prompt":
-                                     round(bn_bytes / (t_bn / n_steps) / 1e9 / pk["hbm_gbs"], 4)},
+                                     round(bn_bytes / (t_bn / n_steps) / 1e9 / pk["hbm_gbs"], 4),
+                                 "hbm_frac_prompt_read_once":
+                                     round(once_bytes / (t_bn / n_steps) / 1e9 / pk["hbm_gbs"], 4)},
         "clocks": clocks}))
     return 0
 
