@@ -182,10 +182,18 @@ class Engine:
         """One scheduler step: plan, run, sample.  Returns the requests that finished."""
         t_start = time.perf_counter() if SCHED_TIMING else 0.0
         ahead, self._ahead = self._ahead, None
-        if ahead is not None and self._ahead_still_holds(ahead[0]):
-            return self._run_prepared(*ahead, t_start)
-        plan = self.scheduler.plan()
-        finished = list(plan.finished)
+        finished: List[Request] = []
+        plan, prep = None, None
+        if ahead is not None:
+            plan, prep, sampled = ahead
+            finished += plan.finished
+            self.stats.preemptions += len(plan.preempted)
+            if any(r.finished is not None or r.cancelled for r in sampled):
+                plan, prep = None, None      # a request it counted on is gone: plan again (what it admitted stays)
+        if plan is None:
+            plan = self.scheduler.plan()
+            finished += plan.finished
+            self.stats.preemptions += len(plan.preempted)
         if not plan.entries:
             return finished
         entries = []
@@ -197,67 +205,58 @@ class Engine:
                 self.storage.zero_state_slot(self.manager.get(e.request.rid).slot)   # a request starts from zero state
             if e.wants_logits:
                 wanting.append(e.request)
-        logits = self.runner.step(entries, checked=True)
+        if prep is not None:
+            logits = self.runner.launch_prepared(prep, [t for e in entries for t in e.tokens])
+        else:
+            logits = self.runner.step(entries, checked=True)
         self.scheduler.advance(plan)
         if wanting:
-            tokens = self._sample(logits, wanting, look_ahead=len(wanting) == len(plan.entries))
+            tokens = self._sample(logits, wanting, look_ahead=True)
             for req, tok in zip(wanting, tokens):
                 if self.scheduler.accept(req, tok) is not None:
                     finished.append(req)
         self.stats.steps += 1
-        self.stats.preemptions += len(plan.preempted)
         if SCHED_TIMING:
             import sys
             print(f"[airun_b200] step {self.stats.steps}: {len(plan.entries)} requests, "
-                  f"{sum(e.count for e in plan.entries)} tokens, {(time.perf_counter() - t_start) * 1e3:.3f} ms",
-                  file=sys.stderr)
+                  f"{sum(e.count for e in plan.entries)} tokens{' (laid out ahead)' if prep is not None else ''}, "
+                  f"{(time.perf_counter() - t_start) * 1e3:.3f} ms", file=sys.stderr)
         return finished
 
-    # While the GPU runs a step of single tokens, the host lays out the next one (pages, positions,
-    # block tables, their copy to the device): all of it but the tokens themselves, which it only
-    # has when it has read this step's result.  If then a request ends, is cancelled, or another
-    # arrives, the lay-out is dropped and the step is planned the ordinary way.
-    def _prepare_ahead(self, reqs: List[Request]) -> None:
+    # While the GPU runs a step, the host plans and lays out the next one (admission, portions, pages,
+    # positions, block tables, their copy to the device): all of it but the values of the tokens being
+    # sampled right now, which it only has when it has read this step's result.  It does so only when
+    # the requests being sampled are sure to go on (not at their last token) and pages are plentiful, so
+    # that the plan cannot end or preempt anybody; if one of them ends all the same (an end token, a
+    # cancellation), the plan's batch is dropped and the step is planned again.
+    _PLACEHOLDER = 0
+
+    def _prepare_ahead(self, sampled: List[Request]) -> None:
         sch = self.scheduler
-        if sch.waiting or len(sch.running) != len(reqs) or any(a is not b for a, b in zip(sch.running, reqs)):
-            return
-        for r in reqs:
-            # after the token being sampled now: still running, and one token short of its cache
+        for r in sampled:
             if r.cancelled or r.num_computed != r.num_tokens or len(r.output) + 1 >= r.max_new_tokens \
                     or r.num_tokens + 2 > self.max_context:
                 return
-        try:
-            prep = self.runner.prepare_decode([r.rid for r in reqs])
-        except Exception:                                  # noqa: BLE001 - e.g. out of pages: the ordinary path decides
+        ps = self.manager.page_size
+        margin = len(sch.running) + len(sch.waiting) + self.options.max_batch_tokens // ps + 2
+        if any(g.allocator.num_free < margin for g in self.manager.paged):
             return
-        if prep is not None:
-            self._ahead = (list(reqs), prep)
-
-    def _ahead_still_holds(self, reqs: List[Request]) -> bool:
-        sch = self.scheduler
-        if sch.waiting or len(sch.running) != len(reqs):
-            return False
-        for a, b in zip(sch.running, reqs):
-            if a is not b or a.cancelled or a.finished is not None or a.num_tokens - a.num_computed != 1:
-                return False
-        return True
-
-    def _run_prepared(self, reqs: List[Request], prep: dict, t_start: float) -> List[Request]:
-        logits = self.runner.launch_prepared(prep, [r.output[-1] for r in reqs])
-        for r in reqs:
-            r.num_computed += 1
-        self.scheduler.stats["steps"] += 1
-        finished = []
-        tokens = self._sample(logits, reqs, look_ahead=True)
-        for req, tok in zip(reqs, tokens):
-            if self.scheduler.accept(req, tok) is not None:
-                finished.append(req)
-        self.stats.steps += 1
-        if SCHED_TIMING:
-            import sys
-            print(f"[airun_b200] step {self.stats.steps}: {len(reqs)} requests, {len(reqs)} tokens (laid out ahead), "
-                  f"{(time.perf_counter() - t_start) * 1e3:.3f} ms", file=sys.stderr)
-        return finished
+        for r in sampled:
+            r.output.append(self._PLACEHOLDER)             # stands for the token on its way
+        prep = None
+        try:
+            plan = sch.plan()
+            if plan.entries and not plan.preempted:
+                entries = [StepEntry(e.request.rid, e.request.token_slice(e.start, e.count),
+                                     (e.count - 1,) if e.wants_logits else ()) for e in plan.entries]
+                try:
+                    prep = self.runner.prepare_step(entries)
+                except Exception:                          # noqa: BLE001 - e.g. out of pages: the ordinary path decides
+                    prep = None
+        finally:
+            for r in sampled:
+                r.output.pop()
+        self._ahead = (plan, prep, list(sampled))
 
     def _sample(self, logits: torch.Tensor, reqs: List[Request], look_ahead: bool = False) -> List[int]:
         n = len(reqs)
@@ -274,8 +273,8 @@ class Engine:
         self._picked_host.copy_(self._picked_dev, non_blocking=True)
         host_rows = [i for i, r in enumerate(reqs) if not r.params.device_ok]
         rows_host = logits[host_rows].cpu().numpy() if host_rows else None
-        if look_ahead and not host_rows:
-            self._prepare_ahead(reqs)                      # the GPU is busy: lay out the next step meanwhile
+        if look_ahead and not host_rows and self._ahead is None:
+            self._prepare_ahead(reqs)                      # the GPU is busy: plan and lay out the next step meanwhile
         torch.cuda.current_stream().synchronize()
         picked = self._picked_host.numpy()
         if picked[R]:

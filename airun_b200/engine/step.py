@@ -195,30 +195,40 @@ class StepRunner:
         self.steps_run += 1
         return logits
 
-    # ---- a decode step in two halves: what does not depend on the tokens, and the rest
-    def prepare_decode(self, rids: Sequence[Hashable]) -> Optional[dict]:
-        """The part of the next step of single tokens (one per request of ``rids``, all logits
-        wanted) that does not need the tokens: pages, the batch's layout, its copy to the device,
-        which queues up behind whatever the stream is running.  ``launch_prepared`` does the rest
-        once the tokens are known.  None when there is no captured graph for this many requests yet
-        (the step then goes the ordinary way); raises OutOfPages like ``step``."""
-        n = len(rids)
-        bucket = next((b for b in self.graph_buckets if b >= n), None)
-        if not self.use_graphs or self.device.type != "cuda" or bucket is None:
+    # ---- a step in two halves: what does not depend on the newest tokens, and the rest
+    def prepare_step(self, entries: Sequence[StepEntry]) -> Optional[dict]:
+        """The part of a step that does not need the values of its tokens: pages, the batch's layout,
+        its copy to the device, which queues up behind whatever the stream is running.  Tokens not
+        known yet may hold any valid id; ``launch_prepared`` brings the real ones and replays the
+        step's graph.  None when the step's shape has no captured graph yet (it then goes the ordinary
+        way); raises OutOfPages like ``step``."""
+        if not self.use_graphs or self.device.type != "cuda":
             return None
-        if bucket not in self.graphs and ("shared", bucket) not in self.graphs:
-            return None
-        self.manager.reserve_many(rids, [1] * n)
-        ctx, _ = self.build_context([StepEntry(r, (0,), (0,)) for r in rids], pad_to=bucket)
-        key = self._decode_key(ctx, bucket)
+        rids, counts = [e.rid for e in entries], [len(e.tokens) for e in entries]
+        if all(c == 1 and tuple(e.want) == (0,) for c, e in zip(counts, entries)):
+            n = len(entries)
+            bucket = next((b for b in self.graph_buckets if b >= n), None)
+            if bucket is None or (bucket not in self.graphs and ("shared", bucket) not in self.graphs):
+                return None
+            self.manager.reserve_many(rids, counts)
+            ctx, _ = self.build_context(entries, pad_to=bucket)
+            key, n_want = self._decode_key(ctx, bucket), n
+        else:
+            if not self.mixed_graphs:
+                return None
+            key, tb, wb, _, _, n_want = self._mixed_key(entries)
+            if key not in self.graphs:
+                return None
+            self.manager.reserve_many(rids, counts)
+            self.build_context(entries, pad_to=tb, pad_want=wb)
         if key not in self.graphs:
             return None                 # (the pages are taken and the lay-out is unused: the ordinary path redoes it)
-        return dict(rids=list(rids), key=key, slot=self._ring_i)
+        return dict(rids=rids, counts=counts, key=key, slot=self._ring_i, n_want=n_want)
 
-    def launch_prepared(self, prep: dict, tokens: Sequence[int]) -> torch.Tensor:
-        """Second half of ``prepare_decode``: the tokens go to the device and the graph is replayed.
-        Nothing may have touched the runner or these requests in between."""
-        n = len(prep["rids"])
+    def launch_prepared(self, prep: dict, tokens) -> Optional[torch.Tensor]:
+        """Second half of ``prepare_step``: all the step's tokens (one flat sequence) go to the device
+        and the graph is replayed.  Nothing may have touched the runner or these requests in between."""
+        n = len(tokens)
         off, _ = self.offsets["token_ids"]
         host, host_np, event = self._ring[prep["slot"]]
         host_np[off:off + n] = tokens
@@ -228,9 +238,9 @@ class StepRunner:
         graph, out, kernels = self.graphs[prep["key"]]
         graph.replay()
         self.graph_launches += kernels
-        self.manager.commit_many(prep["rids"], [1] * n)
+        self.manager.commit_many(prep["rids"], prep["counts"])
         self.steps_run += 1
-        return out[:n]
+        return out[:prep["n_want"]] if prep["n_want"] else None
 
     SHARED_PREFIX_MIN = 1024       # tokens all requests of a decode step must share before it pays to read them once
 
@@ -282,13 +292,8 @@ class StepRunner:
         self.graph_launches += kernels
         return out
 
-    def _mixed_step_graphed(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
-        """Any other step, replayed from a CUDA graph of the next larger captured shape: tokens,
-        wanted rows, single-token requests and requests with a portion, each rounded up to a bucket.
-        The batch is padded; which rows are portions and which single tokens, how the portions are
-        cut into tiles and how many slices a decoded token's keys get is worked out on the device
-        (kernels/fast.py, ``device_plan``), so one graph serves every batch of its shape.  Shapes
-        beyond the buckets, or more shapes than ``max_mixed_graphs``, run kernel by kernel."""
+    def _mixed_key(self, entries: Sequence[StepEntry]):
+        """(graph key, padded tokens, padded wanted rows, row bucket index, portion bucket, wanted rows)."""
         T = W = singles = portions = 0
         for e in entries:
             n = len(e.tokens)
@@ -302,7 +307,16 @@ class StepRunner:
         wb = next((b for b in self.want_buckets if b >= W), None) if W else 0
         ri = next((i for i, b in enumerate(self.row_buckets) if b >= singles), None) if singles else -1
         pb = next((b for b in self.portion_buckets if b >= portions), None) if portions else 0
-        key = ("mixed", tb, wb, ri, pb)
+        return ("mixed", tb, wb, ri, pb), tb, wb, ri, pb, W
+
+    def _mixed_step_graphed(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Any other step, replayed from a CUDA graph of the next larger captured shape: tokens,
+        wanted rows, single-token requests and requests with a portion, each rounded up to a bucket.
+        The batch is padded; which rows are portions and which single tokens, how the portions are
+        cut into tiles and how many slices a decoded token's keys get is worked out on the device
+        (kernels/fast.py, ``device_plan``), so one graph serves every batch of its shape.  Shapes
+        beyond the buckets, or more shapes than ``max_mixed_graphs``, run kernel by kernel."""
+        key, tb, wb, ri, pb, W = self._mixed_key(entries)
         if None in key or (key not in self.graphs and key not in self._warm_buckets
                            and len(self._warm_buckets) >= self.max_mixed_graphs + len(self.graph_buckets)):
             ctx, n_want = self.build_context(entries)
