@@ -14,6 +14,7 @@ from __future__ import annotations
 import ctypes
 import hashlib
 import os
+import re
 import shutil
 import subprocess
 import sys
@@ -143,10 +144,12 @@ def build(name: str, defines: Optional[Dict[str, object]] = None,
             os.unlink(tmp)
         raise BuildError(f"{os.path.basename(cmd[0])} failed on {source} (exit {proc.returncode}):\n{' '.join(cmd)}\n{out}")
     os.replace(tmp, path)
-    # libraries of older versions of this source (another hash) are of no use any more
-    prefix = os.path.basename(path).rsplit("_", 1)[0] + "_"
+    # libraries of older versions of this source with the same defines (the same name, another
+    # hash) are of no use any more
+    stem = os.path.basename(path).rsplit("_", 1)[0]
+    stale = re.compile(re.escape(stem) + r"_[0-9a-f]{16}\.so$")
     for f in os.listdir(os.path.dirname(path)):
-        if f.startswith(prefix) and f.endswith(".so") and f != os.path.basename(path):
+        if stale.match(f) and f != os.path.basename(path):
             try:
                 os.unlink(os.path.join(os.path.dirname(path), f))
             except OSError:
