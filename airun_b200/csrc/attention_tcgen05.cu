@@ -440,22 +440,28 @@ __global__ __launch_bounds__(TC_THREADS, 1) void attn_prefill_tc_kernel(
             // probabilities -> shared memory (operand layout), row sum.  The P buffer is free once the
             // product of the tile before, which reads it, has landed.
             if (!landed && !mbar_wait(BAR(B_OFULL), (it - 1) & 1)) { ok = false; break; }
-            float rs = 0.0f;
+            // exp2(v * scale - m) for two values at a time (packed float32 multiply-add and add of
+            // sm_100).  A hidden key holds -1e30, which the product sends to exp2(-inf) = 0 without a
+            // test; only a row that has seen no key at all (m = -1e30) must not add its -m.
+            const float2 sc2 = make_float2(sc, sc);
+            const float nm = m > 0.5f * NEG_BIG ? -m : 0.0f;
+            const float2 nm2 = make_float2(nm, nm);
+            float2 rs2 = make_float2(0.0f, 0.0f);
 #pragma unroll
             for (int q8 = 0; q8 < 8; ++q8) {
                 uint32_t w[4];
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    const float a = v[q8 * 8 + 2 * i], b = v[q8 * 8 + 2 * i + 1];
-                    const float p0 = a > 0.5f * NEG_BIG ? ex2(fmaf(a, sc, -m)) : 0.0f;
-                    const float p1 = b > 0.5f * NEG_BIG ? ex2(fmaf(b, sc, -m)) : 0.0f;
-                    rs += p0 + p1;
-                    __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
+                    const float2 e = __ffma2_rn(make_float2(v[q8 * 8 + 2 * i], v[q8 * 8 + 2 * i + 1]), sc2, nm2);
+                    const float2 pp = make_float2(ex2(e.x), ex2(e.y));
+                    rs2 = __fadd2_rn(rs2, pp);
+                    __nv_bfloat162 h2 = __floats2bfloat162_rn(pp.x, pp.y);
                     w[i] = *reinterpret_cast<uint32_t*>(&h2);
                 }
                 *reinterpret_cast<uint4*>(smem + OFF_P + half * ROWBLK + r * 128 + ((q8 ^ (r & 7)) << 4)) =
                     make_uint4(w[0], w[1], w[2], w[3]);
             }
+            const float rs = rs2.x + rs2.y;
             l += rs;
             // P written (and O rescaled if need be): hand over to the MMA thread
             tc_fence_before();
