@@ -212,9 +212,24 @@ constexpr int N_BARS = 16;
 constexpr int SMEM_TOTAL = OFF_BAR + N_BARS * 8 + 64 + 1024;
 enum { B_KFULL = 0, B_KEMPTY = 2, B_VFULL = 4, B_VEMPTY = 6, B_SFULL = 8, B_SFREE = 10, B_PFULL = 12, B_OFULL = 13, B_OFREE = 14, B_XM = 15 };
 
+// SHARED: the same loop over a prefix of keys that the decoded tokens of a batch have in common (their
+// requests begin with the same pages).  The batch's tokens, 128 / G to a CTA (blockIdx.z), are the
+// packed rows; all keys below *k_end_dev are visible to all of them; blockIdx.x picks one of gridDim.x
+// slices of those keys; and instead of an output row each thread writes its row's (maximum, sum,
+// unnormalised output) into the slice's slot of the decode kernel's scratch (attention_mma.cu), which
+// merges them with the slices of each token's own keys.
+struct TcShared {
+    const int32_t* k_end_dev;   // keys [0, *k_end_dev) are shared
+    const int32_t* req_of_token;
+    int n_tok, num_reqs;        // tokens in the batch (rows 0 .. n_tok-1)
+    float* scratch;             // the decode kernel's partial results: [unit][unit_stride][16][HD + 2]
+    int unit_stride, slot0;     // slots per (token, KV head, head group); first slot of this kernel's slices
+};
+
+template <bool SHARED>
 __global__ __launch_bounds__(TC_THREADS, 1) void attn_prefill_tc_kernel(
     const TcParams p, const int4* __restrict__ tiles, const __grid_constant__ CUtensorMap kv_map,
-    const int* __restrict__ n_tiles_dev) {
+    const int* __restrict__ n_tiles_dev, const TcShared sh) {
     pdl_trigger();
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -241,7 +256,7 @@ __global__ __launch_bounds__(TC_THREADS, 1) void attn_prefill_tc_kernel(
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     pdl_wait();
-    if (n_tiles_dev && (int)blockIdx.x >= *n_tiles_dev) {       // a CTA beyond the tiles in use: nothing to do
+    if (!SHARED && n_tiles_dev && (int)blockIdx.x >= *n_tiles_dev) {       // a CTA beyond the tiles in use: nothing to do
         tc_fence_before();
         __syncthreads();
         if (warp == 1) {
@@ -251,16 +266,31 @@ __global__ __launch_bounds__(TC_THREADS, 1) void attn_prefill_tc_kernel(
         return;
     }
 
-    const int4 t4 = tiles[blockIdx.x];
-    const int req = t4.x, tok0 = t4.y, n_tok = t4.z;
-    const int kvh = blockIdx.y;
     const int G = p.G;
+    int req, tok0, n_tok;
+    if (SHARED) {
+        const int per = QM / G;
+        tok0 = blockIdx.z * per;
+        n_tok = min(per, sh.n_tok - tok0);
+        req = sh.req_of_token[tok0];
+    } else {
+        const int4 t4 = tiles[blockIdx.x];
+        req = t4.x; tok0 = t4.y; n_tok = t4.z;
+    }
+    const int kvh = blockIdx.y;
     const int n_rows = n_tok * G;
-    const int32_t* bt = p.block_table + (size_t)req * p.max_blocks;
-    const int pos_lo = p.positions[tok0], pos_hi = p.positions[tok0 + n_tok - 1];
-    const int k_first = p.window > 0 ? max(0, pos_lo - p.window + 1) : 0;
-    const int tile_first = k_first / KN, tile_last = pos_hi / KN;
-    const int n_tiles = tile_last - tile_first + 1;
+    const bool req_ok = !SHARED || (req >= 0 && req < sh.num_reqs);      // (a padded batch: rows of no request)
+    const int32_t* bt = p.block_table + (size_t)(req_ok ? req : 0) * p.max_blocks;
+    const int k_end = SHARED ? (req_ok ? *sh.k_end_dev : 0) : 0;
+    const int pos_lo = SHARED ? k_end - 1 : p.positions[tok0], pos_hi = SHARED ? k_end - 1 : p.positions[tok0 + n_tok - 1];
+    const int k_first = (!SHARED && p.window > 0) ? max(0, pos_lo - p.window + 1) : 0;
+    int tile_first = k_first / KN;
+    int n_tiles = pos_hi >= 0 ? pos_hi / KN - tile_first + 1 : 0;
+    if (SHARED) {                                     // this CTA's slice of the shared tiles
+        const int per_slice = (n_tiles + (int)gridDim.x - 1) / (int)gridDim.x;
+        tile_first = min(n_tiles, (int)blockIdx.x * per_slice);
+        n_tiles = min(n_tiles, tile_first + per_slice) - tile_first;
+    }
 
     if (warp == 0) {
         // ------------------------------------------------ TMA producer
@@ -324,7 +354,7 @@ __global__ __launch_bounds__(TC_THREADS, 1) void attn_prefill_tc_kernel(
                 umma_commit(BAR(B_SFULL + s));
                 return true;
             };
-            if (ok) ok = issue_s(0);
+            if (ok && n_tiles > 0) ok = issue_s(0);          // (a slice of a shared prefix may be empty)
             for (int it = 0; it < n_tiles && ok; ++it) {
                 if (it + 1 < n_tiles) { ok = issue_s(it + 1); if (!ok) break; }
                 const int s = it & 1;
@@ -355,7 +385,7 @@ __global__ __launch_bounds__(TC_THREADS, 1) void attn_prefill_tc_kernel(
         const bool row_ok = r < n_rows;
         const int tok = tok0 + (row_ok ? r / G : 0);
         const int head = kvh * G + (row_ok ? r % G : 0);
-        const int pos = row_ok ? p.positions[tok] : -1;
+        const int pos = row_ok ? (SHARED ? pos_hi : p.positions[tok]) : -1;
         const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
         constexpr int DPT = HD / 2;                               // head dimensions per thread
         float* xm = reinterpret_cast<float*>(smem + OFF_XM);      // [2 tiles][2 halves][128 rows]
@@ -387,7 +417,7 @@ __global__ __launch_bounds__(TC_THREADS, 1) void attn_prefill_tc_kernel(
             if (!mbar_wait(BAR(B_SFULL + s), (it >> 1) & 1)) { ok = false; break; }
             tc_fence_after();
             // every key of the tile is visible to every row: no masks
-            const bool full = p.window == 0 && (tile_first + it) * KN + KN - 1 <= pos_lo;
+            const bool full = (SHARED || p.window == 0) && (tile_first + it) * KN + KN - 1 <= pos_lo;
             float v[64];
             tmem_ld64(lane_addr + s * KN + half * 64, v);
             // the S buffer is in registers: hand it back
@@ -402,7 +432,7 @@ __global__ __launch_bounds__(TC_THREADS, 1) void attn_prefill_tc_kernel(
 #pragma unroll
                 for (int i = 0; i < 64; ++i) {
                     const int j = j0 + i;
-                    const bool vis = j <= pos && (p.window == 0 || pos - j < p.window);
+                    const bool vis = j <= pos && (SHARED || p.window == 0 || pos - j < p.window);
                     v[i] = vis ? v[i] : NEG_BIG;
                     raw = fmaxf(raw, v[i]);
                 }
@@ -490,7 +520,19 @@ __global__ __launch_bounds__(TC_THREADS, 1) void attn_prefill_tc_kernel(
         if (ok && mbar_wait(BAR(B_XM), n_tiles & 1)) l += xl[(half ^ 1) * 128 + r];
         else ok = false;
         if (!ok) atomicOr(p.err, AIRUN_DEV_TIMEOUT);
-        if (row_ok && ok) {
+        if (SHARED) {
+            // (maximum, sum, unnormalised output) of the row into this slice's slot of the row's unit;
+            // each of the row's two threads writes its half of the head dimensions
+            if (row_ok) {
+                const int hgroups = (G + 15) / 16, hin = r % G;
+                const int unit = tok * (p.nkv * hgroups) + kvh * hgroups + hin / 16;
+                float* dst = sh.scratch + ((size_t)unit * sh.unit_stride + sh.slot0 + blockIdx.x) * (16 * (HD + 2))
+                             + (hin % 16) * (HD + 2);
+                if (half == 0) { dst[0] = ok ? m : NEG_BIG; dst[1] = ok ? l : 0.0f; }
+#pragma unroll
+                for (int d = 0; d < DPT; ++d) dst[2 + half * DPT + d] = ok ? o[d] : 0.0f;
+            }
+        } else if (row_ok && ok) {
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
             uint4* dst = reinterpret_cast<uint4*>(p.out + ((size_t)tok * p.nh + head) * HD + half * DPT);
 #pragma unroll
@@ -576,10 +618,45 @@ AIRUN_EXPORT int airun_attn_prefill_tc(const void* q, void* out, const void* poo
     if (r != AIRUN_OK) return r;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    airun_launch(attn_prefill_tc_kernel, dim3(n_tiles, nkv), dim3(TC_THREADS), SMEM_TOTAL, stream, p, (const int4*)tiles, map, n_tiles_dev);
+    airun_launch(attn_prefill_tc_kernel<false>, dim3(n_tiles, nkv), dim3(TC_THREADS), SMEM_TOTAL, stream, p, (const int4*)tiles, map, n_tiles_dev, TcShared{});
+    return airun_launch_status();
+}
+
+// The shared prefix of a batch of decoded tokens on tcgen05: see TcShared.  Same contract as
+// airun_attn_shared_prefix of attention_mma.cu (slots n_splits .. n_splits+slices-1 of every unit of the
+// decode kernel's scratch, n_splits + slices slots per unit).
+AIRUN_EXPORT int airun_attn_shared_prefix_tc(const void* q, const void* pool, const int32_t* block_table, int max_blocks,
+                                             const int32_t* req_of_token, int num_reqs, int num_pages, int page_size,
+                                             int nh, int nkv, float scale, int n_tok, const int32_t* k_end_dev,
+                                             int slices, int n_splits, float* scratch, int* err, cudaStream_t stream) {
+    if (n_tok <= 0 || nh <= 0 || nkv <= 0 || nh % nkv != 0 || nh / nkv > QM || !err || !k_end_dev || !scratch ||
+        !req_of_token || slices < 1 || n_splits < 1)
+        return AIRUN_ERR_ARG;
+    int shift = -1;
+    for (int s = 4; s < 20; ++s) if ((1 << s) == page_size) shift = s;
+    if (shift < 0) return AIRUN_ERR_UNSUPPORTED;
+    TcParams p;
+    p.q = (const __nv_bfloat16*)q; p.out = nullptr; p.block_table = block_table; p.positions = nullptr;
+    p.max_blocks = max_blocks; p.num_pages = num_pages; p.page_size = page_size; p.page_shift = shift;
+    p.nh = nh; p.nkv = nkv; p.G = nh / nkv; p.scale_log2 = scale * LOG2E; p.window = 0; p.err = err;
+    const int per = QM / p.G;
+    const int groups = (n_tok + per - 1) / per;
+    if (nkv > 65535 || groups > 65535) return AIRUN_ERR_ARG;
+    CUtensorMap map;
+    const int r = kv_map_for(&map, pool, (long long)num_pages * 2 * nkv * page_size);
+    if (r != AIRUN_OK) return r;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    TcShared sh{k_end_dev, req_of_token, n_tok, num_reqs, scratch, n_splits + slices, n_splits};
+    airun_launch(attn_prefill_tc_kernel<true>, dim3(slices, nkv, groups), dim3(TC_THREADS), SMEM_TOTAL, stream, p,
+                 (const int4*)nullptr, map, (const int*)nullptr, sh);
     return airun_launch_status();
 }

@@ -302,6 +302,14 @@ def attn_shared_prefix(ctx, q, cache, nh, nkv, hd, scale, n_rows: int, k_end_dev
     _need(n_rows * nkv * hgroups * (n_splits + slices) * 16 * (hd + 2) <= scratch.numel(),
           "split-K scratch is too small for this shared-prefix launch")
     pool, bt = cache.pool, cache.block_table
+    if prefill_tc_supported(hd, cache.page_size):
+        f = _fn("attention_tcgen05", "airun_attn_shared_prefix_tc",
+                [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
+                 c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p], {"HD": hd})
+        _check(f(_p(q), _p(pool), _p(bt), bt.stride(0), _p(ctx.req_of_token), int(ctx.num_reqs), pool.shape[0],
+                 pool.shape[3], nh, nkv, float(scale), int(n_rows), _p(k_end_dev), int(slices), int(n_splits),
+                 _p(scratch), _p(ctx.err), _stream()), "attn_shared_prefix_tc")
+        return
     f = _fn("attention_mma", "airun_attn_shared_prefix",
             [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
              c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p], {"HD": hd})
@@ -415,7 +423,8 @@ def attention_bf16(ctx, q, out, cache, nh: int, nkv: int, hd: int, scale: float,
             # the requests of the batch begin with the same pages: those keys once for all tokens (in
             # slices of their own), each token's later keys as usual, one merge
             splits = plan_decode_splits(plan["n_rows"], nkv, (G + 15) // 16, min(context, SHARED_SUFFIX_PLAN), hd, slots)
-            slices = _shared_prefix_slices(plan["n_rows"], nkv, G, hd, splits)
+            slices = _shared_prefix_slices(plan["n_rows"], nkv, G, hd, splits,
+                                           148 if prefill_tc_supported(hd, cache.page_size) else 296)
             attn_shared_prefix(ctx, q, cache, nh, nkv, hd, scale, plan["n_rows"], cache.shared_prefix, slices, splits)
             attn_decode(ctx, q, out, cache, nh, nkv, hd, scale, window, None, plan["n_rows"], splits,
                         k_begin_dev=cache.shared_prefix, extra_slices=slices)
@@ -428,10 +437,11 @@ def attention_bf16(ctx, q, out, cache, nh: int, nkv: int, hd: int, scale: float,
 SHARED_SUFFIX_PLAN = 2048              # keys after the shared prefix the slice count of such a step is chosen for
 
 
-def _shared_prefix_slices(n_rows: int, nkv: int, G: int, hd: int, splits: int = 8) -> int:
-    """Slices of the shared keys: about one CTA per SM slot, as many as the scratch has room for
-    beside the ``splits`` slices of the tokens' own keys, at most 64 of both together."""
+def _shared_prefix_slices(n_rows: int, nkv: int, G: int, hd: int, splits: int = 8, slots: int = 296) -> int:
+    """Slices of the shared keys: about one CTA per SM slot (``slots``: 148 for the tcgen05 kernel, one
+    CTA to an SM; 296 for the mma.sync one), as many as the scratch has room for beside the ``splits``
+    slices of the tokens' own keys, at most 64 of both together."""
     groups = -(-n_rows * G // PREFILL_ROWS)
-    want = max(1, min(32, 296 // max(1, nkv * groups)))
+    want = max(1, min(37, slots // max(1, nkv * groups)))
     room = SCRATCH_FLOATS // (n_rows * nkv * ((G + 15) // 16) * 16 * (hd + 2)) - splits
     return max(0, min(want, room, 64 - splits))
