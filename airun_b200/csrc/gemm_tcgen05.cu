@@ -606,6 +606,16 @@ __global__ __launch_bounds__(GEMM_THREADS, 1) void gemm_tcgen05_persistent_kerne
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tmem_slot_p;
+    // The weights (the B operand) are written by no kernel: the first stages of this CTA's first tile
+    // ask for their weight blocks before waiting for the kernel in front.
+    const int n_pre = (int)blockIdx.x < total_tiles ? (kb_total < PSTAGES ? kb_total : PSTAGES) : 0;
+    if (warp == 0 && lane == 0) {
+        const int b0 = ((int)blockIdx.x / m_tiles) * PBN;
+        for (int i = 0; i < n_pre; ++i) {
+            mbar_expect_tx(full0 + 8 * i, L::STAGE_BYTES);
+            tma_load_2d(smem_u32(smem + i * L::STAGE_BYTES) + L::A_BYTES, &map_b, full0 + 8 * i, i * BK, b0);
+        }
+    }
     pdl_wait();
 
     if (warp == 0) {
@@ -616,9 +626,13 @@ __global__ __launch_bounds__(GEMM_THREADS, 1) void gemm_tcgen05_persistent_kerne
                 const int a0 = (tile % m_tiles) * BM, b0 = (tile / m_tiles) * PBN;
                 for (int kb = 0; kb < kb_total; ++kb, ++it) {
                     const int s = it % PSTAGES;
+                    const uint32_t sa = smem_u32(smem + s * L::STAGE_BYTES);
+                    if (it < n_pre) {                // the weight half of this stage is already on its way
+                        tma_load_2d(sa, &map_a, full0 + 8 * s, kb * BK, a0);
+                        continue;
+                    }
                     if (!mbar_wait(empty0 + 8 * s, ((it / PSTAGES) & 1) ^ 1)) { atomicOr(p.err, AIRUN_DEV_TIMEOUT); ok = false; break; }
                     mbar_expect_tx(full0 + 8 * s, L::STAGE_BYTES);
-                    const uint32_t sa = smem_u32(smem + s * L::STAGE_BYTES);
                     tma_load_2d(sa, &map_a, full0 + 8 * s, kb * BK, a0);
                     tma_load_2d(sa + L::A_BYTES, &map_b, full0 + 8 * s, kb * BK, b0);
                 }
