@@ -360,6 +360,8 @@ struct DecodeExtra {
     const int32_t* k_begin_dev; // null, or: keys below *k_begin_dev are not this kernel's (a shared prefix, whose
     int extra_slices;           //   results another kernel has put into the extra_slices slots after this
                                 //   kernel's n_splits; they are merged with this kernel's own slices)
+    int early_ok;               // the caller vouches that every key but each token's newest was written before the
+                                //   chain of launches this one belongs to began (a step replayed as one graph)
 };
 
 // TMA = true: K/V tiles arrive by cp.async.bulk.tensor (one lane of each warp issues HD/64 boxes per
@@ -384,10 +386,11 @@ __global__ __launch_bounds__(32 * DW) void attn_decode_kernel(const AttnParams p
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     // Keys and values of earlier positions were written by earlier steps, and the batch's layout was
-    // copied to the device before the step began: with TMA and no row list from a kernel of this step,
-    // the first tiles are requested before waiting for the kernel in front (which writes q and the
-    // newest key), so they stream in under its tail.  The tile that holds the newest key waits.
-    const bool early = TMA && x.n_rows_dev == nullptr;
+    // copied to the device before the step began: with TMA, no row list from a kernel of this step and
+    // the caller's word for it (early_ok), the first tiles are requested before waiting for the kernel
+    // in front (which writes q and the newest key), so they stream in under its tail.  The tile that
+    // holds the newest key waits.
+    const bool early = TMA && x.n_rows_dev == nullptr && x.early_ok != 0;
     if (!early) pdl_wait();
     __shared__ float s_m[DW][16], s_l[DW][16];
     __shared__ int s_ticket;
@@ -825,7 +828,7 @@ AIRUN_EXPORT int airun_attn_decode(const void* q, void* out, const void* pool, c
                                    int num_reqs, int num_pages, int page_size, int nh, int nkv, float scale,
                                    int window, const int32_t* rows, int n_rows, int n_splits, float* scratch,
                                    int* counters, const int32_t* n_rows_dev, int dyn_slots, const int32_t* k_begin_dev,
-                                   int extra_slices, int* err, cudaStream_t stream) {
+                                   int extra_slices, int early_ok, int* err, cudaStream_t stream) {
     if (n_rows_dev && (dyn_slots <= 0 || !rows)) return AIRUN_ERR_ARG;
     if (extra_slices < 0 || n_splits + extra_slices > MAX_SPLITS || (extra_slices > 0 && (n_rows_dev || !k_begin_dev || !scratch || !counters)))
         return AIRUN_ERR_ARG;
@@ -836,7 +839,7 @@ AIRUN_EXPORT int airun_attn_decode(const void* q, void* out, const void* pool, c
     if (nkv * hgroups > 65535 || n_rows > 65535) return AIRUN_ERR_ARG;
     const AttnParams p = make_params(q, out, pool, block_table, max_blocks, positions, req_of_token, num_reqs,
                                      num_pages, page_size, nh, nkv, scale, window, err);
-    DecodeExtra x{rows, n_splits, scratch, counters, n_rows_dev, dyn_slots, k_begin_dev, extra_slices};
+    DecodeExtra x{rows, n_splits, scratch, counters, n_rows_dev, dyn_slots, k_begin_dev, extra_slices, early_ok};
     // TMA needs whole 16-key tiles inside one page and 128-byte boxes
     static const bool tma_allowed = !(getenv("AIRUN_ATTN_TMA") && getenv("AIRUN_ATTN_TMA")[0] == '0');
     const bool tma = tma_allowed && (HD % 64 == 0) && p.page_shift >= 4 && encode_fn() != nullptr;

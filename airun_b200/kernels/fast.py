@@ -259,13 +259,18 @@ def attn_prefill_tc(ctx, q, out, cache, nh, nkv, hd, scale, window, tiles: torch
 
 def attn_decode(ctx, q, out, cache, nh, nkv, hd, scale, window, rows: torch.Tensor, n_rows: int, n_splits: int,
                 n_rows_dev: Optional[torch.Tensor] = None, dyn_slots: int = 0,
-                k_begin_dev: Optional[torch.Tensor] = None, extra_slices: int = 0) -> None:
+                k_begin_dev: Optional[torch.Tensor] = None, extra_slices: int = 0, early: Optional[bool] = None) -> None:
     """Attention of single decoded tokens (batch rows ``rows``; None: rows 0..n_rows-1), the keys cut
     into ``n_splits`` slices.  With ``n_rows_dev`` (int32 on the device) the launch is made for ``n_rows``
     rows and ``n_splits`` slices, runs the rows counted there, and every row picks its slices itself so
     that about ``dyn_slots`` CTAs run.  With ``k_begin_dev`` (int32 on the device) the keys below that
     position are left out and the ``extra_slices`` results another kernel (``attn_shared_prefix``) has
-    put into the scratch for them are merged in."""
+    put into the scratch for them are merged in.  ``early``: the kernel may ask for keys and values
+    before the kernel in front of it has finished, which holds when all but each token's newest key were
+    written before this chain of launches began; by default, when the launch is being captured into a
+    graph (a whole step, bounded by the graph's own launch)."""
+    if early is None:
+        early = torch.cuda.is_current_stream_capturing()
     _cuda(q, out, cache.pool, cache.block_table, rows)
     _need(q.dtype == torch.bfloat16 and cache.pool.dtype == torch.bfloat16 and q.is_contiguous() and out.is_contiguous(),
           "tensor-core attention takes contiguous bfloat16 q, out and pages")
@@ -280,11 +285,11 @@ def attn_decode(ctx, q, out, cache, nh, nkv, hd, scale, window, rows: torch.Tens
         _need(need <= scratch.numel() and n_rows * nkv * hgroups <= counters.numel(),
               "split-K scratch is too small for this decode launch")
     f = _fn("attention_mma", "airun_attn_decode",
-            _COMMON_SIG + [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p],
-            {"HD": hd})
+            _COMMON_SIG + [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p,
+                           c_void_p], {"HD": hd})
     _check(f(*_attn_common_args(q, out, cache, ctx, nh, nkv, scale, window), _p(rows), n_rows, n_splits,
              _p(scratch), _p(counters), _p(n_rows_dev), int(dyn_slots), _p(k_begin_dev), int(extra_slices),
-             _p(ctx.err), _stream()), "attn_decode")
+             1 if early else 0, _p(ctx.err), _stream()), "attn_decode")
 
 
 def attn_shared_prefix(ctx, q, cache, nh, nkv, hd, scale, n_rows: int, k_end_dev: torch.Tensor, slices: int,

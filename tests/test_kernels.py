@@ -383,8 +383,9 @@ def test_decode_attention_slices_agree(splits):
     ctx, cache, q, want, scale = attention_case(nh, nkv, hd, page, window, lens, [1] * len(lens), torch.bfloat16, seed=13)
     out = torch.full_like(q, 9.0)
     rows = torch.arange(len(lens), dtype=torch.int32, device=DEV)
-    for _ in range(2):                                        # counters return to zero
-        fast.attn_decode(ctx, q, out, cache, nh, nkv, hd, scale, window, rows, len(lens), splits)
+    for early in (False, True):                               # twice: the counters return to zero; the second time
+        # the first tiles are requested before the dependency wait, as inside a captured step
+        fast.attn_decode(ctx, q, out, cache, nh, nkv, hd, scale, window, rows, len(lens), splits, early=early)
         torch.cuda.synchronize()
         assert ctx.err.item() == 0
         assert torch.allclose(out.cpu().float(), want, rtol=2e-2, atol=2e-2)
