@@ -96,6 +96,14 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
 }
+// the A operand in tensor memory (rows on the lanes, two 16-bit values per column)
+__device__ __forceinline__ void umma_bf16_ta(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -132,6 +140,18 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* v) {
           "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
           "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
           "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st32u(uint32_t taddr, const uint32_t* v) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr),
+          "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+          "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]),
+          "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]),
+          "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
         : "memory");
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
@@ -555,6 +575,317 @@ __global__ __launch_bounds__(TC_THREADS, 1) void attn_prefill_tc_kernel(
     }
 }
 
+// ---------------------------------------------------------------------------------------------------
+// The wide variant: one CTA = 256 packed query rows, two Q tiles (A: rows 0-127, B: rows 128-255) that
+// share every K and V tile, so a key or value crosses from the L2 cache to the SM once for 256 rows (at
+// 128 rows the load of the tiles, not the tensor cores, bounds a long prompt).  Tensor memory holds
+// S_A, S_B (128 columns each) and O_A, O_B; P overwrites S in place as packed bfloat16 pairs and is the
+// product's A operand from tensor memory, so shared memory holds only Q (two tiles) and two stages each
+// of K and V.
+//   warp 0    : TMA producer, as above;
+//   warp 1    : the products, in the order S_A0 S_B0 | O_A0 S_A1 O_B0 S_B1 | O_A1 S_A2 ...  The tensor
+//               cores run them in this order, so S_X(j+1) may overwrite P_X(j) right behind O_X(j), and
+//               the barrier that reports S_X(j+1) reports O_X(j) too;
+//   warps 2-5 : softmax of Q tile A, one thread per row (all 128 keys of a tile, all head dimensions);
+//   warps 6-9 : the same for Q tile B.  While one warpgroup works on its S tile the tensor cores work
+//               for the other.
+// A tile of at most 128 rows runs with the B half idle.
+constexpr int W_OFF_Q = 0;                              // two Q tiles
+constexpr int W_OFF_K = 2 * Q_BYTES;                    // 2 stages
+constexpr int W_OFF_V = W_OFF_K + 2 * KV_BYTES;         // 2 stages
+constexpr int W_OFF_BAR = W_OFF_V + 2 * KV_BYTES;
+constexpr int W_N_BARS = 13;
+constexpr int W_SMEM_TOTAL = W_OFF_BAR + W_N_BARS * 8 + 64 + 1024;
+enum { W_KFULL = 0, W_KEMPTY = 2, W_VFULL = 4, W_VEMPTY = 6, W_SFULL = 8, W_PFULL = 10, W_FINAL = 12 };
+
+__global__ __launch_bounds__(TC_THREADS, 1) void attn_prefill_wide_kernel(
+    const TcParams p, const int4* __restrict__ tiles, const __grid_constant__ CUtensorMap kv_map,
+    const int* __restrict__ n_tiles_dev) {
+    pdl_trigger();
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = (uint64_t*)(smem + W_OFF_BAR);
+    uint32_t* tmem_slot = (uint32_t*)(bars + W_N_BARS);
+    const uint32_t bar0 = smem_u32(bars);
+    auto BAR = [&](int i) { return bar0 + 8u * (uint32_t)i; };
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < 8; ++i) mbar_init(BAR(i), 1);                 // K/V full and empty
+        mbar_init(BAR(W_SFULL), 1); mbar_init(BAR(W_SFULL + 1), 1);
+        mbar_init(BAR(W_PFULL), 4); mbar_init(BAR(W_PFULL + 1), 4);      // one arrival per warp of the tile's warpgroup
+        mbar_init(BAR(W_FINAL), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(smem_u32(tmem_slot), 512);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    pdl_wait();
+    if (n_tiles_dev && (int)blockIdx.x >= *n_tiles_dev) {       // a CTA beyond the tiles in use: nothing to do
+        tc_fence_before();
+        __syncthreads();
+        if (warp == 1) {
+            tc_fence_after();
+            tmem_dealloc(tmem_base, 512);
+        }
+        return;
+    }
+
+    const int G = p.G;
+    const int4 t4 = tiles[blockIdx.x];
+    const int req = t4.x, tok0 = t4.y, n_tok = t4.z;
+    const int kvh = blockIdx.y;
+    const int n_rows = n_tok * G;
+    const bool two = n_rows > QM;                       // is there a Q tile B?
+    const int32_t* bt = p.block_table + (size_t)req * p.max_blocks;
+    const int pos_lo = p.positions[tok0], pos_hi = p.positions[tok0 + n_tok - 1];
+    const int k_first = p.window > 0 ? max(0, pos_lo - p.window + 1) : 0;
+    const int tile_first = k_first / KN;
+    const int n_tiles = pos_hi >= 0 ? pos_hi / KN - tile_first + 1 : 0;
+
+    if (warp == 0) {
+        // ------------------------------------------------ TMA producer
+        if (lane == 0) {
+            for (int it = 0; it < n_tiles; ++it) {
+                const int s = it & 1;
+                const uint32_t ph = (it >> 1) & 1;
+                const int j0 = (tile_first + it) * KN;
+                if (!mbar_wait(BAR(W_KEMPTY + s), ph ^ 1)) { atomicOr(p.err, AIRUN_DEV_TIMEOUT); break; }
+                mbar_expect_tx(BAR(W_KFULL + s), KV_BYTES);
+                const uint32_t kdst = smem_u32(smem + W_OFF_K + s * KV_BYTES);
+                int rows[KN / 16];
+#pragma unroll
+                for (int gkey = 0; gkey < KN / 16; ++gkey) {
+                    const int j = j0 + gkey * 16;
+                    const int blk = j >> p.page_shift;
+                    int page = (j <= pos_hi && blk < p.max_blocks) ? __ldg(bt + blk) : 0;
+                    if (page < 0 || page >= p.num_pages) {
+                        if (j >= k_first) atomicOr(p.err, AIRUN_DEV_BAD_PAGE);      // a page the window has passed may be gone
+                        page = 0;
+                    }
+                    rows[gkey] = (((page * 2) * p.nkv + kvh) << p.page_shift) + (j & (p.page_size - 1));
+                }
+#pragma unroll
+                for (int gkey = 0; gkey < KN / 16; ++gkey)
+#pragma unroll
+                    for (int h = 0; h < HALVES; ++h)
+                        tma_load_2d(kdst + h * ROWBLK + gkey * 2048, &kv_map, BAR(W_KFULL + s), h * 64, rows[gkey]);
+                if (!mbar_wait(BAR(W_VEMPTY + s), ph ^ 1)) { atomicOr(p.err, AIRUN_DEV_TIMEOUT); break; }
+                mbar_expect_tx(BAR(W_VFULL + s), KV_BYTES);
+                const uint32_t vdst = smem_u32(smem + W_OFF_V + s * KV_BYTES);
+                const int vskip = p.nkv << p.page_shift;
+#pragma unroll
+                for (int gkey = 0; gkey < KN / 16; ++gkey)
+#pragma unroll
+                    for (int h = 0; h < HALVES; ++h)
+                        tma_load_2d(vdst + h * ROWBLK + gkey * 2048, &kv_map, BAR(W_VFULL + s), h * 64, rows[gkey] + vskip);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(KN >> 3) << 17) | ((uint32_t)(QM >> 4) << 24);
+            constexpr uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(QM >> 4) << 24);
+            const uint32_t q_addr = smem_u32(smem + W_OFF_Q);
+            const int last_x = two ? 1 : 0;
+            // first phase of P_full: the Q tiles are in shared memory
+            bool ok = mbar_wait(BAR(W_PFULL), 0) && (!two || mbar_wait(BAR(W_PFULL + 1), 0));
+            auto issue_s = [&](int it, int x) -> bool {          // S of Q tile x and key tile it
+                const int s = it & 1;
+                if (x == 0) {
+                    if (!mbar_wait(BAR(W_KFULL + s), (it >> 1) & 1)) return false;
+                    tc_fence_after();
+                }
+                const uint32_t k_addr = smem_u32(smem + W_OFF_K + s * KV_BYTES);
+#pragma unroll
+                for (int k = 0; k < HD / 16; ++k) {
+                    const uint32_t off = (k >> 2) * ROWBLK + (k & 3) * 32;
+                    umma_bf16(tmem_base + x * KN, desc_kmajor(q_addr + x * Q_BYTES + off), desc_kmajor(k_addr + off), idesc_s,
+                              k > 0 ? 1u : 0u);
+                }
+                if (x == last_x) umma_commit(BAR(W_KEMPTY + s));
+                umma_commit(BAR(W_SFULL + x));
+                return true;
+            };
+            auto issue_o = [&](int it, int x) -> bool {          // O of Q tile x += P V of key tile it
+                const int s = it & 1;
+                if (!mbar_wait(BAR(W_PFULL + x), (it + 1) & 1)) return false;     // P stands where S stood
+                if (x == 0 && !mbar_wait(BAR(W_VFULL + s), (it >> 1) & 1)) return false;
+                tc_fence_after();
+                const uint32_t v_addr = smem_u32(smem + W_OFF_V + s * KV_BYTES);
+#pragma unroll
+                for (int k = 0; k < KN / 16; ++k)                // 16 keys of P = 8 columns of packed pairs
+                    umma_bf16_ta(tmem_base + (2 + x) * KN, tmem_base + x * KN + k * 8, desc_mnmajor(v_addr + k * 2048), idesc_o,
+                                 (it > 0 || k > 0) ? 1u : 0u);
+                if (x == last_x) umma_commit(BAR(W_VEMPTY + s));
+                return true;
+            };
+            if (ok && n_tiles > 0) {
+                ok = issue_s(0, 0);
+                if (ok && two) ok = issue_s(0, 1);
+            }
+            for (int it = 0; it < n_tiles && ok; ++it) {
+                ok = issue_o(it, 0);
+                if (ok && it + 1 < n_tiles) ok = issue_s(it + 1, 0);
+                if (ok && two) {
+                    ok = issue_o(it, 1);
+                    if (ok && it + 1 < n_tiles) ok = issue_s(it + 1, 1);
+                }
+            }
+            if (ok) umma_commit(BAR(W_FINAL));
+            else atomicOr(p.err, AIRUN_DEV_TIMEOUT);
+        }
+    } else if (two || warp < 6) {
+        // ------------------------------------------------ softmax, correction, epilogue
+        const int x = (warp - 2) >> 2;                    // this warpgroup's Q tile
+        const int quad = warp & 3;
+        const int r = quad * 32 + lane;                   // the thread's lane of tensor memory
+        const int row = x * QM + r;
+        const bool row_ok = row < n_rows;
+        const int tok = tok0 + (row_ok ? row / G : 0);
+        const int head = kvh * G + (row_ok ? row % G : 0);
+        const int pos = row_ok ? p.positions[tok] : -1;
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
+        const uint32_t s_addr = lane_addr + x * KN, o_addr = lane_addr + (2 + x) * KN;
+
+        // the Q row -> shared memory in the K-major swizzled layout
+        {
+            const uint4* src = reinterpret_cast<const uint4*>(p.q + ((size_t)tok * p.nh + head) * HD);
+#pragma unroll
+            for (int c = 0; c < HD / 8; ++c) {
+                const uint4 v = row_ok ? src[c] : make_uint4(0, 0, 0, 0);
+                *reinterpret_cast<uint4*>(smem + W_OFF_Q + x * Q_BYTES + (c >> 3) * ROWBLK + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = v;
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(BAR(W_PFULL + x));          // phase 0: Q is ready
+        }
+
+        float m = NEG_BIG, l = 0.0f;
+        bool ok = true;
+        const float sc = p.scale_log2;
+        for (int it = 0; it < n_tiles && ok; ++it) {
+            // S of this key tile has landed, and with it the product of the tile before
+            if (!mbar_wait(BAR(W_SFULL + x), it & 1)) { ok = false; break; }
+            tc_fence_after();
+            const int j0 = (tile_first + it) * KN;
+            const bool full = p.window == 0 && j0 + KN - 1 <= pos_lo;       // every key visible to every row: no masks
+            float v[64];
+            float raw = NEG_BIG;
+            // the row's maximum: keys 64-127, then keys 0-63, which stay in registers
+#pragma unroll
+            for (int c = 1; c >= 0; --c) {
+                tmem_ld64(s_addr + c * 64, v);
+                if (full) {
+#pragma unroll
+                    for (int i = 0; i < 64; ++i) raw = fmaxf(raw, v[i]);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 64; ++i) {
+                        const int j = j0 + c * 64 + i;
+                        const bool vis = j <= pos && (p.window == 0 || pos - j < p.window);
+                        v[i] = vis ? v[i] : NEG_BIG;
+                        raw = fmaxf(raw, v[i]);
+                    }
+                }
+            }
+            const float mx = raw > 0.5f * NEG_BIG ? raw * sc : NEG_BIG;
+            const bool raise = mx > m + 8.0f;
+            if (it == 0) {
+                m = mx;                                              // nothing accumulated yet
+            } else if (__any_sync(0xffffffffu, raise)) {
+                // rescale this warp's rows of O
+                const float f = raise ? ex2(m - mx) : 1.0f;
+#pragma unroll
+                for (int c = 0; c < HD; c += 32) {
+                    float t[32];
+                    tmem_ld32(o_addr + c, t);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) t[i] *= f;
+                    tmem_st32(o_addr + c, t);
+                }
+                l *= f;
+                if (raise) m = mx;
+            }
+            // probabilities as pairs of bfloat16 over the S tile (keys 2c, 2c+1 in column c), row sum.
+            // A hidden key holds -1e30, which the product sends to exp2(-inf) = 0 without a test; only a
+            // row that has seen no key at all (m = -1e30) must not add its -m.
+            const float2 sc2 = make_float2(sc, sc);
+            const float nm = m > 0.5f * NEG_BIG ? -m : 0.0f;
+            const float2 nm2 = make_float2(nm, nm);
+            float2 rs2 = make_float2(0.0f, 0.0f);
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                if (c == 1) {                                        // keys 64-127 again (their columns are untouched)
+                    tmem_ld64(s_addr + 64, v);
+                    if (!full) {
+#pragma unroll
+                        for (int i = 0; i < 64; ++i) {
+                            const int j = j0 + 64 + i;
+                            const bool vis = j <= pos && (p.window == 0 || pos - j < p.window);
+                            v[i] = vis ? v[i] : NEG_BIG;
+                        }
+                    }
+                }
+                uint32_t pw[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const float2 e = __ffma2_rn(make_float2(v[2 * i], v[2 * i + 1]), sc2, nm2);
+                    const float2 pp = make_float2(ex2(e.x), ex2(e.y));
+                    rs2 = __fadd2_rn(rs2, pp);
+                    __nv_bfloat162 h2 = __floats2bfloat162_rn(pp.x, pp.y);
+                    pw[i] = *reinterpret_cast<uint32_t*>(&h2);
+                }
+                tmem_st32u(s_addr + c * 32, pw);
+            }
+            tmem_st_wait();
+            l += rs2.x + rs2.y;
+            // P written (and O rescaled if need be): hand over to the MMA thread
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(BAR(W_PFULL + x));
+        }
+        // the output row
+        if (ok && n_tiles > 0 && !mbar_wait(BAR(W_FINAL), 0)) ok = false;
+        if (!ok) atomicOr(p.err, AIRUN_DEV_TIMEOUT);
+        tc_fence_after();
+        const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+        uint4* dst = reinterpret_cast<uint4*>(p.out + ((size_t)tok * p.nh + head) * HD);
+#pragma unroll
+        for (int c = 0; c < HD; c += 32) {
+            float o[32];
+            if (ok && n_tiles > 0) {
+                tmem_ld32(o_addr + c, o);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) o[i] = 0.0f;
+            }
+            if (row_ok && ok) {
+#pragma unroll
+                for (int q8 = 0; q8 < 4; ++q8) {
+                    uint32_t w[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        __nv_bfloat162 h2 = __floats2bfloat162_rn(o[q8 * 8 + 2 * i] * inv, o[q8 * 8 + 2 * i + 1] * inv);
+                        w[i] = *reinterpret_cast<uint32_t*>(&h2);
+                    }
+                    dst[c / 8 + q8] = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -623,6 +954,34 @@ AIRUN_EXPORT int airun_attn_prefill_tc(const void* q, void* out, const void* poo
         configured = true;
     }
     airun_launch(attn_prefill_tc_kernel<false>, dim3(n_tiles, nkv), dim3(TC_THREADS), SMEM_TOTAL, stream, p, (const int4*)tiles, map, n_tiles_dev, TcShared{});
+    return airun_launch_status();
+}
+
+// The same for tiles of up to 256 / G tokens (attn_prefill_wide_kernel).
+AIRUN_EXPORT int airun_attn_prefill_wide(const void* q, void* out, const void* pool, const int32_t* block_table,
+                                         int max_blocks, const int32_t* positions, int num_pages, int page_size,
+                                         int nh, int nkv, float scale, int window, const void* tiles, int n_tiles,
+                                         const int32_t* n_tiles_dev, int* err, cudaStream_t stream) {
+    if (n_tiles < 0 || nh <= 0 || nkv <= 0 || nh % nkv != 0 || nh / nkv > QM || !err) return AIRUN_ERR_ARG;
+    int shift = -1;
+    for (int s = 4; s < 20; ++s) if ((1 << s) == page_size) shift = s;
+    if (shift < 0) return AIRUN_ERR_UNSUPPORTED;
+    if (n_tiles == 0) return AIRUN_OK;
+    if (nkv > 65535) return AIRUN_ERR_ARG;
+    TcParams p;
+    p.q = (const __nv_bfloat16*)q; p.out = (__nv_bfloat16*)out; p.block_table = block_table; p.positions = positions;
+    p.max_blocks = max_blocks; p.num_pages = num_pages; p.page_size = page_size; p.page_shift = shift;
+    p.nh = nh; p.nkv = nkv; p.G = nh / nkv; p.scale_log2 = scale * LOG2E; p.window = window; p.err = err;
+    CUtensorMap map;
+    const int r = kv_map_for(&map, pool, (long long)num_pages * 2 * nkv * page_size);
+    if (r != AIRUN_OK) return r;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, W_SMEM_TOTAL);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    airun_launch(attn_prefill_wide_kernel, dim3(n_tiles, nkv), dim3(TC_THREADS), W_SMEM_TOTAL, stream, p, (const int4*)tiles, map, n_tiles_dev);
     return airun_launch_status();
 }
 

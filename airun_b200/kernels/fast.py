@@ -197,6 +197,8 @@ DECODE_SLOTS = 444                     # CTAs of the cp.async decode kernel resi
 DECODE_SLOTS_TMA = 296                 # the TMA variant keeps three stages per warp: two CTAs per SM
 DECODE_MIN_KEYS_PER_SPLIT = 128
 PREFILL_ROWS = 128                     # packed rows (tokens x heads of a KV group) of one prefill CTA
+PREFILL_ROWS_WIDE = 256                # of the tcgen05 kernel with two Q tiles
+WIDE_MIN_CTAS = 128                    # fewest CTAs the wide kernel is used for (148 SMs, one CTA each)
 
 
 def _arange(device: torch.device, n: int) -> torch.Tensor:
@@ -241,15 +243,16 @@ def prefill_tc_supported(hd: int, page_size: int) -> bool:
 
 
 def attn_prefill_tc(ctx, q, out, cache, nh, nkv, hd, scale, window, tiles: torch.Tensor, n_tiles: int,
-                    n_tiles_dev: Optional[torch.Tensor] = None) -> None:
-    """Flash attention of prompt portions on tcgen05 (csrc/attention_tcgen05.cu); same tiles as attn_prefill."""
+                    n_tiles_dev: Optional[torch.Tensor] = None, wide: bool = False) -> None:
+    """Flash attention of prompt portions on tcgen05 (csrc/attention_tcgen05.cu); same tiles as attn_prefill.
+    ``wide``: the tiles hold up to PREFILL_ROWS_WIDE // G tokens (the kernel with two Q tiles to a CTA)."""
     _cuda(q, out, cache.pool, cache.block_table, tiles)
     _need(q.dtype == torch.bfloat16 and cache.pool.dtype == torch.bfloat16 and q.is_contiguous() and out.is_contiguous(),
           "tensor-core attention takes contiguous bfloat16 q, out and pages")
     _need(prefill_tc_supported(hd, cache.pool.shape[3]), "head size or page size not taken by the tcgen05 attention")
     _need(tiles.dtype == torch.int32 and tiles.is_contiguous() and tiles.numel() >= 4 * n_tiles, "tiles must be int32 [n, 4]")
     pool, bt = cache.pool, cache.block_table
-    f = _fn("attention_tcgen05", "airun_attn_prefill_tc",
+    f = _fn("attention_tcgen05", "airun_attn_prefill_wide" if wide else "airun_attn_prefill_tc",
             [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int,
              c_void_p, c_int, c_void_p, c_void_p, c_void_p], {"HD": hd})
     _check(f(_p(q), _p(out), _p(pool), _p(bt), bt.stride(0), _p(ctx.positions), pool.shape[0], pool.shape[3],
@@ -354,10 +357,25 @@ def plan_decode_splits(n_rows: int, nkv: int, hgroups: int, context_len: int, hd
     return best
 
 
-def _attention_plan(ctx, G: int):
+def _wide_tiles(ctx, G: int, nkv: int) -> bool:
+    """Whether the step's portions go to tiles of PREFILL_ROWS_WIDE rows: when those tiles still fill
+    the machine (a CTA per tile and KV head).  They read every key once for twice as many rows, which is
+    what bounds a long prompt; a step with few tiles is better spread over more, narrower ones."""
+    shape = ctx.extras.get("device_plan")
+    if shape:
+        # a padded batch: what the shape allows at least
+        if not shape["max_portions"]:
+            return False
+        tiles = (ctx.num_tokens - min(shape["max_rows"], ctx.num_tokens)) * G // PREFILL_ROWS_WIDE
+    else:
+        tiles = sum(-(-n * G // PREFILL_ROWS_WIDE) for n in ctx.query_lens if n > 1)
+    return tiles * nkv >= WIDE_MIN_CTAS
+
+
+def _attention_plan(ctx, G: int, tile_rows: int = PREFILL_ROWS):
     """Which rows are single decoded tokens and how the prompt portions are cut into tiles
-    of PREFILL_ROWS // G tokens; made once per step and group size."""
-    key = ("attn_plan", G)
+    of tile_rows // G tokens; made once per step, group size and tile size."""
+    key = ("attn_plan", G, tile_rows)
     plan = ctx.extras.get(key)
     if plan is not None:
         return plan
@@ -367,7 +385,7 @@ def _attention_plan(ctx, G: int):
         # the batch is padded and its layout is only on the device: lists long enough for any batch
         # of this shape (``shape`` bounds its single tokens and portions), filled by a kernel, the
         # counts read by the attention kernels themselves
-        per = max(1, PREFILL_ROWS // G)
+        per = max(1, tile_rows // G)
         T = ctx.num_tokens
         max_rows, max_portions = min(shape["max_rows"], T), min(shape["max_portions"], T // 2)
         max_tiles = (T // per + max_portions + 1) if max_portions else 0
@@ -380,7 +398,7 @@ def _attention_plan(ctx, G: int):
     elif ctx.decode_only:
         plan = dict(rows=None, n_rows=ctx.num_tokens, tiles=None, n_tiles=0)
     else:
-        per = max(1, PREFILL_ROWS // G)
+        per = max(1, tile_rows // G)
         rows, tiles, t = [], [], 0
         for r, (n, c) in enumerate(zip(ctx.query_lens, ctx.context_lens_host)):
             if n == 1:
@@ -404,11 +422,13 @@ def attention_bf16(ctx, q, out, cache, nh: int, nkv: int, hd: int, scale: float,
     if not attention_supported(hd, nh, nkv) or q.dtype != torch.bfloat16:
         return False
     G = nh // nkv
-    plan = _attention_plan(ctx, G)
+    tc = prefill_tc_supported(hd, cache.page_size)
+    wide = tc and "attention_wide" not in DISABLED and _wide_tiles(ctx, G, nkv)
+    plan = _attention_plan(ctx, G, PREFILL_ROWS_WIDE if wide else PREFILL_ROWS)
     n_tiles_dev, n_rows_dev = plan.get("n_tiles_dev"), plan.get("n_rows_dev")
     if plan["n_tiles"]:
-        if prefill_tc_supported(hd, cache.page_size):
-            attn_prefill_tc(ctx, q, out, cache, nh, nkv, hd, scale, window, plan["tiles"], plan["n_tiles"], n_tiles_dev)
+        if tc:
+            attn_prefill_tc(ctx, q, out, cache, nh, nkv, hd, scale, window, plan["tiles"], plan["n_tiles"], n_tiles_dev, wide)
         else:
             attn_prefill(ctx, q, out, cache, nh, nkv, hd, scale, window, plan["tiles"], plan["n_tiles"], n_tiles_dev)
     if plan["n_rows"]:

@@ -27,6 +27,7 @@ class Ctx:
         self.num_reqs, self.num_tokens = num_reqs, len(positions)
         self.query_lens, self.context_lens_host = query_lens, context_lens
         self.max_context_len = max(context_lens)
+        self.max_query_len = max(query_lens)
         self.decode_only = all(q == 1 for q in query_lens)
         self.err = _err()
         self.extras = {}
@@ -362,9 +363,16 @@ def test_attention_generic(case, dtype):
     assert torch.allclose(out.cpu().float(), want, rtol=tol, atol=tol)
 
 
+@pytest.mark.parametrize("wide", [True, False])
 @pytest.mark.parametrize("case", ATT)
-def test_attention_tensor_core(case):
+def test_attention_tensor_core(case, wide, monkeypatch):
+    """``wide``: prompts with more than 128 packed rows go to the tcgen05 kernel with two Q tiles to a CTA
+    (256 rows), else all go to the one with 128 rows."""
     from airun_b200.kernels import fast
+    if wide:
+        monkeypatch.setattr(fast, "WIDE_MIN_CTAS", 1)
+    else:
+        monkeypatch.setattr(fast, "DISABLED", fast.DISABLED | {"attention_wide"})
     nh, nkv, hd, page, window, lens, qlens = case
     ctx, cache, q, want, scale = attention_case(nh, nkv, hd, page, window, lens, qlens, torch.bfloat16, seed=12)
     out = torch.full_like(q, 9.0)
