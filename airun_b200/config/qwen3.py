@@ -97,9 +97,17 @@ class Qwen3Config(ModelConfig):
         hd_default = H // nh if nh > 0 else 0
         hd = integer("head_dim", hd_default)
         maxpos = integer("max_position_embeddings", 4096)
+        # Newer config.json files carry the rotary constants in a dictionary, ``rope_parameters``
+        # (or ``rope_scaling``): {"rope_type": "default", "rope_theta": ...}.  The plain type is read
+        # like the top-level key; any other type is a scaling rule and is refused below.
+        rope_dicts = [v for v in (d.get("rope_parameters"), d.get("rope_scaling")) if isinstance(v, dict) and v]
+        raw_theta = d.get("rope_theta")
+        for rd in rope_dicts:
+            if raw_theta is None and rd.get("rope_theta") is not None:
+                raw_theta = rd.get("rope_theta")
         try:
             eps = float(d.get("rms_norm_eps") if d.get("rms_norm_eps") is not None else 1e-6)
-            theta = float(d.get("rope_theta") if d.get("rope_theta") is not None else 10000.0)
+            theta = float(raw_theta if raw_theta is not None else 10000.0)
         except (TypeError, ValueError):
             problems.append("rms_norm_eps and rope_theta must be numbers")
             eps, theta = 1e-6, 10000.0
@@ -119,8 +127,15 @@ class Qwen3Config(ModelConfig):
             problems.append(f"rms_norm_eps must be positive, found {eps}")
         if not theta > 0:
             problems.append(f"rope_theta must be positive, found {theta}")
-        if d.get("rope_scaling") not in (None, {}):
-            problems.append("rope_scaling is not supported (only plain rotary positions)")
+        for key in ("rope_scaling", "rope_parameters"):
+            rd = d.get(key)
+            if rd in (None, {}):
+                continue
+            kind = (rd.get("rope_type", rd.get("type", "default")) if isinstance(rd, dict) else rd)
+            extra = sorted(set(rd) - {"rope_type", "type", "rope_theta"}) if isinstance(rd, dict) else []
+            if kind != "default" or extra:
+                problems.append(f"{key} {rd!r} is not supported (only plain rotary positions: "
+                                f"rope_type \"default\" with rope_theta)")
         if d.get("attention_bias"):
             problems.append("attention_bias=true is not supported (the dense Qwen3 decoder has no biases)")
         if d.get("hidden_act", "silu") != "silu":

@@ -50,6 +50,18 @@ def test_every_problem_is_listed():
         assert frag in msg
 
 
+def test_rotary_constants_in_a_dictionary():
+    """Newer config.json files keep rope_theta inside ``rope_parameters``; the plain type is read,
+    a top-level rope_theta wins, and every scaling rule is refused."""
+    base = {k: v for k, v in TINY["A"]["cfg"].items() if k != "rope_theta"}
+    assert Qwen3Config.from_dict(dict(base, rope_parameters={"rope_type": "default", "rope_theta": 5e5})).rope_theta == 5e5
+    assert Qwen3Config.from_dict(dict(base, rope_theta=777.0, rope_parameters={"rope_theta": 5e5})).rope_theta == 777.0
+    assert Qwen3Config.from_dict(dict(base, rope_scaling={"rope_type": "default"})).rope_theta == 10000.0
+    for bad in ({"rope_type": "yarn", "factor": 4.0}, {"type": "linear", "factor": 2.0}, {"rope_type": "default", "factor": 2.0}):
+        with pytest.raises(ConfigError, match="rope_scaling"):
+            Qwen3Config.from_dict(dict(base, rope_scaling=bad))
+
+
 def test_windows_from_layer_types_and_max_window_layers():
     c = Qwen3Config.from_dict(TINY["C"]["cfg"])
     assert c.layer_windows == (0, 24, 0, 24)
