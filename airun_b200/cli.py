@@ -68,7 +68,13 @@ def build_parser() -> argparse.ArgumentParser:
     be.add_argument("model")
     be.add_argument("--prefill", default="128,512", help="prompt lengths to time, comma separated")
     be.add_argument("--decode", type=int, default=128, help="tokens to decode per run")
-    be.add_argument("--decode-at", type=int, default=16, help="context depth at which decoding starts")
+    be.add_argument("--decode-at", default="16", help="context depths at which decoding is timed, comma separated")
+    be.add_argument("-c", "--ctx-size", type=int, default=None, help="longest context of a request (default: what the runs need)")
+    be.add_argument("--random-tokens", action="store_true",
+                    help="prompts of fixed-seed random ids instead of one repeated token")
+    be.add_argument("--forward-only", action="store_true",
+                    help="time exactly N forward steps on fixed tokens, without sampling")
+    be.add_argument("--temp", type=float, default=0.0, help="temperature of the decode runs; 0 is greedy")
     be.add_argument("--parallel", type=int, default=1, help="requests decoding side by side")
     be.add_argument("--runs", type=int, default=3)
     be.add_argument("--warmup", type=int, default=1)
@@ -154,12 +160,25 @@ def cmd_bench(a) -> int:
     from . import Engine, EngineOptions, StepEntry
     from .kernels import ops
     lengths = [int(x) for x in a.prefill.split(",") if x]
-    need = max(lengths + [a.decode_at + a.decode + 1]) + 64
-    eng = Engine.from_folder(a.model, EngineOptions(dtype=a.dtype, cache_tokens=need * max(a.parallel, 1) + 64,
-                                                     max_batch_tokens=max(a.batch_size, 16), max_requests=max(a.parallel, 1),
+    depths = [int(x) for x in str(a.decode_at).split(",") if x] or [16]
+    need = max(lengths + [d + a.decode + 1 for d in depths]) + 64
+    if a.ctx_size is not None:
+        if a.ctx_size < need - 64:
+            raise SystemExit(f"--ctx-size {a.ctx_size} is shorter than the longest run ({need - 64} tokens)")
+        need = max(need, a.ctx_size)
+    n_par = max(a.parallel, 1)
+    eng = Engine.from_folder(a.model, EngineOptions(dtype=a.dtype, cache_tokens=need * n_par + 64,
+                                                     max_batch_tokens=max(a.batch_size, 16), max_requests=n_par,
                                                      max_context=need))
     V = eng.config.vocab_size
-    picked = torch.zeros(max(a.parallel, 1), dtype=torch.int32, device=eng.device)
+    picked = torch.zeros(n_par, dtype=torch.int32, device=eng.device)
+    temps = torch.full((n_par,), float(a.temp), dtype=torch.float32, device=eng.device) if a.temp > 0 else None
+    # Prompts: one repeated token (the reference's default, crates/airun-cli/src/bench.rs:163-169; there
+    # is no tokenizer here, so the filler is id 1) or a fixed-seed random stream (bench.rs:177-187).
+    filler = 1 % V
+
+    def prompt_ids(n, seed=0x9E3779B97F4A7C15):
+        return _random_ids(n, V, seed) if a.random_tokens else [filler] * n
 
     def timed(fn):
         torch.cuda.synchronize()
@@ -179,7 +198,7 @@ def cmd_bench(a) -> int:
 
     report = {"prefill": {}, "decode": {}}
     for n in lengths:
-        toks = _random_ids(n, V)
+        toks = prompt_ids(n)
         ms = []
         for r in range(a.warmup + a.runs):
             t = timed(lambda: prefill("p", toks))
@@ -187,33 +206,45 @@ def cmd_bench(a) -> int:
             if r >= a.warmup:
                 ms.append(t)
         report["prefill"][n] = dict(tokens_per_s=n / (statistics.median(ms) / 1e3), ms=ms)
-    rids = [f"d{i}" for i in range(max(a.parallel, 1))]
-    ms = []
-    for r in range(a.warmup + a.runs):
-        for i, rid in enumerate(rids):
-            prefill(rid, _random_ids(a.decode_at, V, seed=1234 + i))
-        toks = _random_ids(a.decode * len(rids), V, seed=99)
+    rids = [f"d{i}" for i in range(n_par)]
+    report["decode_at"] = {}
+    for depth in depths:
+        ms = []
+        for r in range(a.warmup + a.runs):
+            for i, rid in enumerate(rids):
+                prefill(rid, prompt_ids(depth, seed=1234 + i))
+            fixed = prompt_ids(a.decode * len(rids), seed=99)
+            gen = torch.Generator(device="cpu").manual_seed(7)
 
-        def decode():
-            for s in range(a.decode):
-                logits = eng.runner.step([StepEntry(rid, [toks[s * len(rids) + i]], (0,)) for i, rid in enumerate(rids)])
-                ops.sample(logits, picked)
+            def decode():
+                # --forward-only: fixed tokens, no sampling.  Otherwise every step's tokens are the ones
+                # the step before picked (first maximum, or a draw at --temp), read back like a generation.
+                cur = fixed[:len(rids)]
+                for s in range(a.decode):
+                    if a.forward_only:
+                        cur = fixed[s * len(rids):(s + 1) * len(rids)]
+                    logits = eng.runner.step([StepEntry(rid, [int(cur[i])], (0,)) for i, rid in enumerate(rids)])
+                    if not a.forward_only:
+                        u = torch.rand(len(rids), generator=gen).to(eng.device) if temps is not None else None
+                        ops.sample(logits, picked, temps, u)
+                        cur = picked[:len(rids)].tolist()
 
-        t = timed(decode)
-        for rid in rids:
-            eng.manager.free_request(rid)
-        if r >= a.warmup:
-            ms.append(t)
-    report["decode"] = dict(tokens_per_s=a.decode * len(rids) / (statistics.median(ms) / 1e3), depth=a.decode_at,
-                            parallel=len(rids), ms=ms)
+            t = timed(decode)
+            for rid in rids:
+                eng.manager.free_request(rid)
+            if r >= a.warmup:
+                ms.append(t)
+        report["decode_at"][depth] = dict(tokens_per_s=a.decode * len(rids) / (statistics.median(ms) / 1e3), depth=depth,
+                                          parallel=len(rids), ms=ms)
+    report["decode"] = report["decode_at"][depths[0]]
     eng.runner.raise_on_device_error()
     if a.json:
         print(json.dumps(report))
     else:
         for n, v in report["prefill"].items():
             print(f"prefill {n:6d} tokens: {v['tokens_per_s']:10.1f} tok/s (median of {len(v['ms'])})")
-        d = report["decode"]
-        print(f"decode {a.decode} tokens at depth {d['depth']} x {d['parallel']}: {d['tokens_per_s']:10.1f} tok/s")
+        for d in report["decode_at"].values():
+            print(f"decode {a.decode} tokens at depth {d['depth']} x {d['parallel']}: {d['tokens_per_s']:10.1f} tok/s")
     return 0
 
 

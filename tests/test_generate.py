@@ -123,12 +123,24 @@ def test_perplexity_and_bench_subcommands(folders, tmp_path):
         losses.append(float(re.search(r"loss ([0-9.]+)", out.stdout).group(1)))
     assert abs(losses[0] - want) < 2e-4 and abs(losses[1] - want) < 2e-4
     out = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "airun"), "bench", folders["C"], "--prefill", "33,64",
-                          "--decode", "8", "--decode-at", "20", "--parallel", "2", "--runs", "2", "--json"],
+                          "--decode", "8", "--decode-at", "20", "--parallel", "2", "--runs", "2", "--temp", "0.7", "--json"],
                          capture_output=True, text=True, timeout=300)
     assert out.returncode == 0, out.stderr
     import json
     rep = json.loads(out.stdout.strip().splitlines()[-1])
     assert set(rep["prefill"]) == {"33", "64"} and rep["decode"]["tokens_per_s"] > 0 and rep["decode"]["parallel"] == 2
+    # several depths, random prompts, forwards only (the reference's options of the same names,
+    # crates/airun-cli/src/bench.rs:23-27, 41-43, 73-77), and draws at a temperature
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "airun"), "bench", folders["C"], "--prefill", "16",
+                          "--decode", "4", "--decode-at", "12,30", "--random-tokens", "--forward-only", "--runs", "1",
+                          "--warmup", "0", "--json"], capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr
+    rep = json.loads(out.stdout.strip().splitlines()[-1])
+    assert set(rep["decode_at"]) == {"12", "30"} and all(v["tokens_per_s"] > 0 for v in rep["decode_at"].values())
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "airun"), "bench", folders["C"], "--prefill", "16",
+                          "--decode", "4", "--temp", "0.7", "--runs", "1", "--warmup", "0", "-c", "8"],
+                         capture_output=True, text=True, timeout=300)
+    assert out.returncode != 0 and "--ctx-size" in out.stderr
 
 
 @pytest.mark.parametrize("name", ["A", "B"])
