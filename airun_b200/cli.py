@@ -12,8 +12,8 @@ place of ``--kv-type``: the cache is kept in the compute type.
 
 Subcommands: ``run`` (generate), ``bench`` (prefill and decode rates of a model
 folder, median of runs, in the manner of crates/airun-cli/src/bench.rs:11-92),
-``perplexity`` (loss and top-1 of a token file, token by token or in chunks,
-crates/airun-cli/src/perplexity.rs:97-222), ``init`` (random-weights mode: write
+``perplexity`` (loss and top-1 of a token file; ``--chunk``, ``--batched``,
+``--limit``, ``--worst`` as in crates/airun-cli/src/perplexity.rs:97-222), ``init`` (random-weights mode: write
 a model folder from a config.json and a seed), ``inspect`` (print the
 configuration).
 """
@@ -84,8 +84,16 @@ def build_parser() -> argparse.ArgumentParser:
 
     pp = sub.add_parser("perplexity", help="loss and top-1 accuracy over a file of token ids")
     pp.add_argument("model")
-    pp.add_argument("--tokens-file", required=True)
-    pp.add_argument("--chunk", type=int, default=1, help="tokens per step (1: the decode kernels; more: the prefill kernels)")
+    pp.add_argument("-f", "--file", "--tokens-file", dest="file", help="file of token ids to score")
+    pp.add_argument("-n", "--limit", type=int, default=0, help="stop after this many tokens; 0 scores everything")
+    pp.add_argument("--chunk", type=int, default=0,
+                    help="split the ids into passes of this many tokens, each from an empty context, and count "
+                         "only the predictions of a pass's second half; 0: one pass over everything")
+    pp.add_argument("--batched", action="store_true",
+                    help="with --chunk: feed each pass in one step (the prefill kernels) instead of one token "
+                         "at a time (the decode kernels)")
+    pp.add_argument("--worst", type=int, default=0, help="print this many tokens with the highest loss")
+    pp.add_argument("-c", "--ctx-size", type=int, default=4096, help="context length in tokens")
     pp.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
 
     init = sub.add_parser("init", help="write a model folder with seeded random weights")
@@ -249,28 +257,76 @@ def cmd_bench(a) -> int:
 
 
 def cmd_perplexity(a) -> int:
+    """Scores a file of token ids as the reference's ``airun perplexity`` scores a text
+    (crates/airun-cli/src/perplexity.rs:97-222): one pass over everything, token by token, or with
+    ``--chunk N`` passes of N tokens that each start from an empty context and count only the
+    predictions of their second half; ``--batched`` feeds a pass in one step (the kernels of prompt
+    portions) instead of one token at a time (the decode kernels).  The two agree to rounding."""
     import math
     import torch
     from . import Engine, EngineOptions, StepEntry
-    with open(a.tokens_file) as f:
+    if not a.file:
+        raise SystemExit("perplexity needs --file with the token ids to score (the engine has no tokenizer)")
+    with open(a.file) as f:
         ids = parse_ids(f.read())
     if len(ids) < 2:
-        raise SystemExit("perplexity needs at least two tokens")
-    eng = Engine.from_folder(a.model, EngineOptions(dtype=a.dtype, cache_tokens=len(ids) + 64, max_requests=1,
-                                                     max_batch_tokens=max(a.chunk, 16), max_context=len(ids) + 64))
-    eng.manager.add_request("t")
-    nll, hits, n = 0.0, 0, 0
-    for p0 in range(0, len(ids) - 1, a.chunk):
-        part = ids[p0:min(p0 + a.chunk, len(ids) - 1)]
-        logits = eng.runner.step([StepEntry("t", part, tuple(range(len(part))))]).float()
-        logp = torch.log_softmax(logits, dim=-1).cpu()
-        for i in range(len(part)):
-            target = ids[p0 + i + 1]
-            nll -= float(logp[i, target])
-            hits += int(int(torch.argmax(logp[i])) == target)
-            n += 1
+        raise SystemExit(f"need at least two tokens to score; the file holds {len(ids)}")
+    scored = len(ids) if a.limit <= 0 else min(a.limit, len(ids))
+    if a.batched and a.chunk <= 0:
+        raise SystemExit("--batched needs --chunk")
+    if a.chunk > 0:
+        if a.chunk < 4 or a.chunk > scored:
+            raise SystemExit(f"--chunk {a.chunk} needs at least 4 tokens and at most the file's {scored}")
+        passes = [(c * a.chunk, (c + 1) * a.chunk, a.chunk // 2) for c in range(scored // a.chunk)]
+    else:
+        passes = [(0, scored, 0)]
+    longest = max(e - s0 for s0, e, _ in passes)
+    if longest + 1 >= a.ctx_size:
+        raise SystemExit(f"a pass is {longest} tokens but the context is {a.ctx_size}; raise --ctx-size")
+    eng = Engine.from_folder(a.model, EngineOptions(dtype=a.dtype, cache_tokens=longest + 64, max_requests=1,
+                                                     max_batch_tokens=max(longest if a.batched else 1, 16),
+                                                     max_context=longest + 64))
+    losses = []                                    # (position, token, loss)
+    total, top1 = 0.0, 0
+
+    def score(logits_row, pos):
+        nonlocal total, top1
+        logp = torch.log_softmax(logits_row.double(), dim=-1)
+        nll = -float(logp[ids[pos]])
+        top1 += int(int(torch.argmax(logits_row)) == ids[pos])
+        total += nll
+        losses.append((pos, ids[pos], nll))
+
+    for start, end, first in passes:
+        slot = eng.manager.add_request("t").slot   # an empty context for every pass
+        eng.storage.zero_state_slot(slot)
+        if a.batched:
+            rows = [r for r in range(end - start) if r >= first and r + 1 < end - start]
+            logits = eng.runner.step([StepEntry("t", ids[start:end], tuple(rows))])
+            host = logits.float().cpu() if logits is not None else None
+            for k, r in enumerate(rows):
+                score(host[k], start + r + 1)
+        else:
+            for i in range(start, end - 1):
+                wanted = i - start >= first
+                logits = eng.runner.step([StepEntry("t", [ids[i]], (0,) if wanted else ())])
+                if wanted:
+                    score(logits.float().cpu()[0], i + 1)
+        eng.manager.free_request("t")
+        if len(passes) > 1:
+            print(f"[{len(losses) // max(end - start - 1 - first, 1)}]{math.exp(total / max(len(losses), 1)):.4f},",
+                  end="", file=sys.stderr, flush=True)
+    if len(passes) > 1:
+        print(file=sys.stderr)
     eng.runner.raise_on_device_error()
-    print(f"tokens {n}  loss {nll / n:.4f} nats/token  perplexity {math.exp(nll / n):.3f}  top-1 {100.0 * hits / n:.1f} %")
+    n = len(losses)
+    mean = total / n
+    print(f"\n{n} tokens scored\n  mean loss   {mean:.4f} nats/token\n  perplexity  {math.exp(mean):.2f}\n"
+          f"  top-1       {100.0 * top1 / n:.1f}% ({top1}/{n})")
+    if a.worst > 0:
+        print("\nworst-predicted tokens:")
+        for pos, tok, nll in sorted(losses, key=lambda t: -t[2])[:a.worst]:
+            print(f"  pos {pos:>4}  loss {nll:>8.3f}  token {tok}")
     return 0
 
 

@@ -110,18 +110,21 @@ def test_perplexity_and_bench_subcommands(folders, tmp_path):
     import re
     cfg, W = P.read_model_folder(folders["C"])
     ids = random_tokens(90, cfg["vocab_size"], 21)
-    logp = torch.log_softmax(P.plain_forward(cfg, W, ids, torch.float32), dim=-1)
-    want = -sum(float(logp[i, ids[i + 1]]) for i in range(len(ids) - 1)) / (len(ids) - 1)
+    def plain_loss(seq, first):
+        logp = torch.log_softmax(P.plain_forward(cfg, W, seq, torch.float32).double(), dim=-1)
+        return [-float(logp[r, seq[r + 1]]) for r in range(first, len(seq) - 1)]
+
+    whole = plain_loss(ids, 0)
+    chunks = [x for c in range(90 // 24) for x in plain_loss(ids[c * 24:(c + 1) * 24], 12)]   # second halves, fresh contexts
     f = tmp_path / "ids.txt"
     f.write_text(" ".join(map(str, ids)))
-    losses = []
-    for chunk in ("1", "24"):
+    for flags, want in (([], whole), (["--chunk", "24"], chunks), (["--chunk", "24", "--batched", "--worst", "2"], chunks)):
         out = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "airun"), "perplexity", folders["C"],
-                              "--tokens-file", str(f), "--chunk", chunk, "--dtype", "float32"],
-                             capture_output=True, text=True, timeout=300)
+                              "--file", str(f), "--dtype", "float32"] + flags, capture_output=True, text=True, timeout=300)
         assert out.returncode == 0, out.stderr
-        losses.append(float(re.search(r"loss ([0-9.]+)", out.stdout).group(1)))
-    assert abs(losses[0] - want) < 2e-4 and abs(losses[1] - want) < 2e-4
+        assert int(re.search(r"(\d+) tokens scored", out.stdout).group(1)) == len(want)
+        assert abs(float(re.search(r"mean loss\s+([0-9.]+)", out.stdout).group(1)) - sum(want) / len(want)) < 2e-4
+        assert ("worst-predicted" in out.stdout) == ("--worst" in flags)
     out = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "airun"), "bench", folders["C"], "--prefill", "33,64",
                           "--decode", "8", "--decode-at", "20", "--parallel", "2", "--runs", "2", "--temp", "0.7", "--json"],
                          capture_output=True, text=True, timeout=300)
