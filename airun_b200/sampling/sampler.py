@@ -10,7 +10,11 @@ one candidate.  The draw walks the candidates in descending probability with
 with ``seed | 1``, ``u = (x >> 40) / 2^24`` (sample.rs:778-798); seed 0 means
 "pick one from the clock" (sample.rs:233-242).
 
-Not built: grammar constraints, DRY, XTC, dynamic temperature, mirostat.
+DRY stands behind the penalties, XTC behind top-p, the dynamic temperature takes
+the place of the fixed one in the softmax, and mirostat 1 / 2, when on, replaces
+everything after DRY and top-n-sigma (sample.rs:386-388, :520-596).  Grammar
+constraints and the reasoning budget belong to the reference's server and are not
+built.
 
 A request whose parameters reduce to "argmax of the raw logits" (the
 reference's ``is_pure_greedy``, sample.rs:292-298) or to a plain temperature
@@ -42,6 +46,19 @@ class SamplingParams:
     repeat_last_n: int = 64
     logit_bias: Tuple[Tuple[int, float], ...] = ()
     seed: int = 0
+    # The samplers beyond the classic chain, all off at their usual settings (sample.rs:96-111).
+    dynatemp_range: float = 0.0     # temperature moves within +-range with the candidates' entropy; 0 disables
+    dynatemp_exponent: float = 1.0
+    xtc_probability: float = 0.0    # with this probability drop every candidate >= threshold but the least likely of them
+    xtc_threshold: float = 0.1
+    dry_multiplier: float = 0.0     # 0 disables
+    dry_base: float = 1.75
+    dry_allowed_length: int = 2
+    dry_penalty_last_n: int = 0     # 0: the whole history
+    dry_breakers: Tuple[int, ...] = ()   # token ids that end any repeated sequence
+    mirostat: int = 0               # 1 or 2; 0 disables
+    mirostat_tau: float = 5.0
+    mirostat_eta: float = 0.1
 
     @classmethod
     def greedy(cls) -> "SamplingParams":
@@ -61,11 +78,12 @@ class SamplingParams:
 
     @property
     def changes_logits(self) -> bool:
-        return bool(self.logit_bias) or self.penalizing or self.top_n_sigma > 0.0
+        return bool(self.logit_bias) or self.penalizing or self.top_n_sigma > 0.0 or self.dry_multiplier > 0.0
 
     @property
     def is_pure_greedy(self) -> bool:
-        return self.temperature <= 0.0 and not self.logit_bias and not self.penalizing
+        return (self.temperature <= 0.0 and not self.logit_bias and not self.penalizing
+                and self.dry_multiplier <= 0.0)
 
     @property
     def device_ok(self) -> bool:
@@ -73,7 +91,8 @@ class SamplingParams:
         if self.is_pure_greedy:
             return True
         return (self.temperature > 0.0 and not self.changes_logits and self.top_k == 0
-                and self.top_p >= 1.0 and self.min_p <= 0.0 and self.typical_p >= 1.0)
+                and self.top_p >= 1.0 and self.min_p <= 0.0 and self.typical_p >= 1.0
+                and self.dynatemp_range <= 0.0 and self.xtc_probability <= 0.0 and self.mirostat == 0)
 
 
 class XorShift64:
@@ -123,12 +142,108 @@ def apply_top_n_sigma(logits: np.ndarray, n: float) -> None:
     logits[logits < np.float32(mx - n * np.float32(std))] = -np.inf
 
 
+def apply_dry(logits: np.ndarray, history: Sequence[int], multiplier: float, base: float, allowed_length: int,
+              last_n: int, breakers: Sequence[int] = ()) -> None:
+    """DRY ("don't repeat yourself", sample.rs:598-637).  Wherever an earlier position j holds the
+    newest token, the run of tokens ending at j that equals the run ending at the newest token is a
+    repeat in the making, and the token behind j would make it longer.  Once such a run is
+    ``allowed_length`` long that token loses ``multiplier * base ** (length - allowed_length)``; the
+    longest run counts.  A breaker token ends a run and is itself never punished; only the last
+    ``last_n`` tokens are searched (0: all of them)."""
+    h = list(history)
+    n = len(h)
+    if n < 2:
+        return
+    start = n - (n if last_n <= 0 else min(last_n, n))
+    stop = set(breakers)
+    newest = h[n - 1]
+    if newest in stop:
+        return
+    longest = {}
+    for j in range(start, n - 1):
+        if h[j] != newest:
+            continue
+        length = 0
+        while j - length >= start and h[j - length] == h[n - 1 - length] and h[j - length] not in stop:
+            length += 1
+        follower = h[j + 1]
+        if length >= allowed_length and follower not in stop:
+            longest[follower] = max(longest.get(follower, 0), length)
+    for tok, length in longest.items():
+        if 0 <= tok < logits.shape[0]:
+            logits[tok] -= np.float32(np.float32(multiplier) * np.float32(base) ** np.float32(length - allowed_length))
+
+
+def dynamic_temperature(values: np.ndarray, temperature: float, rng_range: float, exponent: float) -> float:
+    """The temperature between ``temperature - range`` and ``temperature + range`` (not below 0)
+    that the candidates' normalised entropy at temperature 1 calls for (sample.rs:503-518);
+    ``values``: the candidates' logits, the largest first."""
+    if rng_range <= 0.0 or values.shape[0] < 2:
+        return temperature
+    ps = np.exp((values - values[0]).astype(np.float64))
+    ps = ps / ps.sum()
+    pos = ps[ps > 0.0]
+    entropy = -float(np.sum(pos * np.log(pos)))
+    norm = min(max(entropy / math.log(values.shape[0]), 0.0), 1.0)
+    lo, hi = max(temperature - rng_range, 0.0), temperature + rng_range
+    return max(float(np.float32(lo + (hi - lo) * np.float32(norm ** exponent))), 1e-6)
+
+
 class Sampler:
-    """One request's sampler: its parameters and its generator."""
+    """One request's sampler: its parameters, its generator and mirostat's running ``mu``."""
 
     def __init__(self, params: SamplingParams):
         self.params = params
         self.rng = XorShift64(params.seed)
+        self.mu = 2.0 * params.mirostat_tau           # sample.rs:259-262
+
+    def _draw(self, ids: np.ndarray, probs: np.ndarray) -> int:
+        """Index into ``ids`` / ``probs`` (descending) of the inverse-CDF draw (sample.rs:478-485)."""
+        total = float(probs.sum(dtype=np.float32))
+        target = self.rng.next_f32() * total
+        for i, pr in enumerate(probs):
+            target -= float(pr)
+            if target <= 0.0:
+                return i
+        return len(ids) - 1
+
+    def _mirostat(self, logits: np.ndarray) -> int:
+        """Mirostat 1 or 2 over the whole vocabulary at the temperature; ``mu`` follows the surprise
+        of the token picked (sample.rs:520-596)."""
+        p = self.params
+        scaled = np.where(np.isnan(logits), -np.inf, logits).astype(np.float32) * np.float32(1.0 / p.temperature)
+        e = np.exp((scaled - scaled.max()).astype(np.float64)).astype(np.float32)
+        probs = (e.astype(np.float64) / float(e.astype(np.float64).sum())).astype(np.float32)
+        order = np.argsort(-probs, kind="stable")
+        V = probs.shape[0]
+        if p.mirostat == 1:
+            # Zipf exponent from the 100 likeliest tokens, then the k that mu asks for
+            top = probs[order[:101]]
+            m = min(100, top.shape[0] - 1)
+            i = np.arange(m, dtype=np.float64)
+            t = np.log((i + 2.0) / (i + 1.0))
+            tiny = float(np.finfo(np.float32).tiny)
+            b = np.log(top[:m].astype(np.float64) / np.maximum(top[1:m + 1].astype(np.float64), tiny))
+            den = float(np.sum(t * t))
+            s_hat = float(np.sum(t * b)) / den if den > 0.0 else 1.0
+            eps = s_hat - 1.0
+            with np.errstate(all="ignore"):
+                k = np.float64(eps * 2.0 ** self.mu) / (1.0 - np.float64(V) ** (-eps))
+                k = np.power(k, 1.0 / s_hat) if s_hat != 0.0 else np.inf
+            k = int(k) if np.isfinite(k) else V
+            keep = order[:min(max(k, 1), V)]
+        else:
+            floor = np.float32(2.0) ** np.float32(-self.mu)          # surprise at most mu
+            keep = order[probs[order] >= floor]
+            if keep.shape[0] == 0:
+                keep = order[:1]
+        kp = probs[keep]
+        total = float(kp.sum(dtype=np.float32))
+        j = self._draw(keep, kp)
+        tiny32 = float(np.finfo(np.float32).tiny)
+        surprise = -math.log2(max(float(kp[j]) / total, tiny32))
+        self.mu -= p.mirostat_eta * (surprise - p.mirostat_tau)
+        return int(keep[j])
 
     def next_uniform(self) -> float:
         return self.rng.next_f32()
@@ -142,10 +257,15 @@ class Sampler:
         if p.penalizing:
             apply_penalties(logits, history, p.repeat_last_n, p.repeat_penalty,
                             p.presence_penalty, p.frequency_penalty)
+        if p.dry_multiplier > 0.0:
+            apply_dry(logits, history, p.dry_multiplier, p.dry_base, p.dry_allowed_length, p.dry_penalty_last_n,
+                      p.dry_breakers)
         if p.top_n_sigma > 0.0:
             apply_top_n_sigma(logits, p.top_n_sigma)
         if p.temperature <= 0.0:
             return first_argmax(logits)
+        if p.mirostat != 0:
+            return self._mirostat(logits)
         V = logits.shape[0]
         keep = min(max(p.top_k, 1), V) if p.top_k > 0 else V
         clean = np.where(np.isnan(logits), -np.inf, logits)
@@ -156,7 +276,8 @@ class Sampler:
         order = idx[np.argsort(-clean[idx], kind="stable")]
         vals = clean[order].astype(np.float32)
         mx = vals[0]
-        probs = np.exp(((vals - mx) / np.float32(p.temperature)).astype(np.float64)).astype(np.float32)
+        temperature = dynamic_temperature(vals, p.temperature, p.dynatemp_range, p.dynatemp_exponent)
+        probs = np.exp(((vals - mx) / np.float32(temperature)).astype(np.float64)).astype(np.float32)
         s = np.float32(probs.sum(dtype=np.float32))
         probs = probs / s
         ids = order
@@ -170,15 +291,15 @@ class Sampler:
             hit = np.nonzero(cum >= np.float32(p.top_p))[0]
             cut = int(hit[0]) + 1 if hit.size else len(ids)
             ids, probs = ids[:max(cut, 1)], probs[:max(cut, 1)]
-        total = float(probs.sum(dtype=np.float32))
-        if total <= 0.0:
+        if p.xtc_probability > 0.0 and self.rng.next_f32() < p.xtc_probability:
+            # XTC (sample.rs:436-443): of the leading candidates at or above the threshold only the
+            # least likely stays
+            above = int(np.count_nonzero(np.cumprod(probs >= np.float32(p.xtc_threshold))))
+            if above >= 2:
+                ids, probs = ids[above - 1:], probs[above - 1:]
+        if float(probs.sum(dtype=np.float32)) <= 0.0:
             return int(ids[0])
-        target = self.rng.next_f32() * total
-        for i, pr in zip(ids, probs):
-            target -= float(pr)
-            if target <= 0.0:
-                return int(i)
-        return int(ids[-1])
+        return int(ids[self._draw(ids, probs)])
 
 
 def _typical(ids: np.ndarray, probs: np.ndarray, typical_p: float):

@@ -88,3 +88,143 @@ def test_temperature_draw_follows_the_distribution():
     assert chi2 < 16.3                                       # 3 degrees of freedom, p = 0.001
     cold = Sampler(SamplingParams.temperature_only(0.05, seed=77))
     assert all(cold.sample(logits.copy(), []) == 0 for _ in range(50))
+
+
+# ----------------------------------------------------------------------------- the further samplers
+def _plain_dry(history, multiplier, base, allowed, last_n, breakers=()):
+    """Token -> logit it loses, by trying every earlier occurrence of the newest token and
+    comparing backwards one token at a time (crates/airun-core/src/sample.rs:598-637)."""
+    n = len(history)
+    lost = {}
+    if n < 2 or history[-1] in breakers:
+        return lost
+    first = 0 if last_n == 0 else max(0, n - last_n)
+    for j in range(first, n - 1):
+        if history[j] != history[-1]:
+            continue
+        run = 0
+        while j - run >= first and history[j - run] == history[n - 1 - run] and history[j - run] not in breakers:
+            run += 1
+        nxt = history[j + 1]
+        if run >= allowed and nxt not in breakers:
+            lost[nxt] = max(lost.get(nxt, 0.0), multiplier * base ** (run - allowed))
+    return lost
+
+
+def test_dry_punishes_the_token_that_would_extend_a_repeat():
+    from airun_b200.sampling.sampler import apply_dry
+    #          0  1  2  3  4  5  6  7  8
+    history = [5, 6, 7, 8, 1, 5, 6, 7]                       # "5 6 7" again: 8 would repeat a run of three
+    logits = np.zeros(10, dtype=np.float32)
+    apply_dry(logits, history, multiplier=0.8, base=1.75, allowed_length=2, last_n=0)
+    assert logits[8] == pytest.approx(-0.8 * 1.75 ** (3 - 2)) and np.count_nonzero(logits) == 1
+    logits[:] = 0
+    apply_dry(logits, history, 0.8, 1.75, allowed_length=4, last_n=0)      # a run of three is still allowed
+    assert not logits.any()
+    logits[:] = 0
+    apply_dry(logits, history, 0.8, 1.75, 2, last_n=0, breakers=(6,))      # a breaker cuts the run to one token
+    assert not logits.any()
+    logits[:] = 0
+    apply_dry(logits, history, 0.8, 1.75, 2, last_n=4)                     # the first "5 6 7" is outside the window
+    assert not logits.any()
+    rng = np.random.default_rng(3)
+    for _ in range(200):                                      # against the plain restatement, small alphabets repeat a lot
+        h = rng.integers(0, 4, size=int(rng.integers(0, 30))).tolist()
+        allowed, last_n = int(rng.integers(1, 4)), int(rng.choice([0, 5, 12]))
+        breakers = (3,) if rng.random() < 0.3 else ()
+        logits = np.zeros(6, dtype=np.float32)
+        apply_dry(logits, h, 0.7, 1.5, allowed, last_n, breakers)
+        want = _plain_dry(h, 0.7, 1.5, allowed, last_n, breakers)
+        for t in range(6):
+            assert logits[t] == pytest.approx(-want.get(t, 0.0), rel=1e-5)
+    p = SamplingParams.greedy()
+    p.dry_multiplier = 5.0
+    assert not p.is_pure_greedy and not p.device_ok
+    logits = np.zeros(10, dtype=np.float32); logits[8] = 1.0; logits[2] = 0.5
+    assert Sampler(p).sample(logits, history) == 2           # greedy would repeat; DRY moves it
+
+
+def test_xtc_removes_the_top_choices_but_the_last_of_them():
+    probs = np.array([0.4, 0.3, 0.2, 0.1])
+    logits = np.log(probs).astype(np.float32)
+    p = SamplingParams.temperature_only(1.0, seed=11)
+    p.xtc_probability, p.xtc_threshold = 1.0, 0.25            # 0.4 and 0.3 are above: 0.4 goes, 0.3 stays
+    assert not p.device_ok
+    s = Sampler(p)
+    seen = np.bincount([s.sample(logits.copy(), []) for _ in range(600)], minlength=4)
+    assert seen[0] == 0 and all(seen[1:] > 0)
+    p.xtc_threshold = 0.35                                    # one candidate above: nothing is removed
+    s = Sampler(p)
+    assert np.bincount([s.sample(logits.copy(), []) for _ in range(300)], minlength=4)[0] > 0
+    p.xtc_probability, p.xtc_threshold = 0.5, 0.25            # the coin: about half of the draws keep token 0
+    s = Sampler(p)
+    seen = np.bincount([s.sample(logits.copy(), []) for _ in range(2000)], minlength=4)
+    assert 0.12 < seen[0] / 2000 < 0.28                       # 0.5 * 0.4
+
+
+def test_dynamic_temperature_moves_with_the_entropy():
+    from airun_b200.sampling.sampler import dynamic_temperature
+    flat = np.zeros(8, dtype=np.float32)                      # normalised entropy 1: the top of the range
+    peaked = np.array([50.0] + [0.0] * 7, dtype=np.float32)   # entropy ~0: the bottom
+    assert dynamic_temperature(flat, 1.0, 0.5, 1.0) == pytest.approx(1.5)
+    assert dynamic_temperature(peaked, 1.0, 0.5, 1.0) == pytest.approx(0.5, abs=1e-3)
+    assert dynamic_temperature(peaked, 0.3, 0.5, 1.0) == pytest.approx(1e-6, abs=1e-3)      # never below zero
+    assert dynamic_temperature(flat, 0.8, 0.0, 1.0) == 0.8 and dynamic_temperature(flat[:1], 0.8, 0.5, 1.0) == 0.8
+    two = np.log(np.array([0.75, 0.25])).astype(np.float32)
+    h = -(0.75 * np.log(0.75) + 0.25 * np.log(0.25)) / np.log(2)
+    assert dynamic_temperature(two, 1.0, 0.4, 2.0) == pytest.approx(0.6 + 0.8 * h ** 2, rel=1e-5)
+    # in the chain: a peaked distribution is drawn colder than a flat one
+    p = SamplingParams.temperature_only(1.0, seed=5)
+    p.dynatemp_range = 0.9
+    assert not p.device_ok
+    logits = np.array([3.0, 0.0, 0.0, 0.0], dtype=np.float32)
+    hot = Sampler(SamplingParams.temperature_only(1.0, seed=5))
+    a = np.mean([Sampler.sample(hot, logits.copy(), []) == 0 for _ in range(1500)])
+    dyn = Sampler(p)
+    b = np.mean([dyn.sample(logits.copy(), []) == 0 for _ in range(1500)])
+    assert b > a + 0.03
+
+
+@pytest.mark.parametrize("version", [1, 2])
+def test_mirostat_steers_the_surprise_with_tau(version):
+    rng = np.random.default_rng(8)
+    base = (rng.normal(size=2000) * 2.5).astype(np.float32)
+    full = np.exp(base.astype(np.float64) - base.max())
+    full /= full.sum()
+    entropy = -np.sum(full * np.log2(full))                    # the mean surprise of untruncated draws: about 7.3 bits
+    assert entropy > 6.5
+
+    def mean_surprise(tau):
+        p = SamplingParams.temperature_only(1.0, seed=21)
+        p.mirostat, p.mirostat_tau, p.mirostat_eta = version, tau, 0.2
+        assert not p.device_ok
+        s = Sampler(p)
+        assert s.mu == 2.0 * tau                               # starts at twice tau
+        out = []
+        for step in range(400):
+            tok = s.sample(np.roll(base, step).copy(), [])
+            out.append(-np.log2(np.roll(full, step)[tok]))
+        return float(np.mean(out[100:]))
+
+    low, mid, high = mean_surprise(1.0), mean_surprise(3.0), mean_surprise(5.0)
+    assert low < mid - 0.4 and mid < high - 0.4 and high < entropy - 1.0
+    p = SamplingParams.temperature_only(1.0, seed=21)
+    p.mirostat, p.mirostat_tau, p.mirostat_eta = version, 3.0, 0.2
+    # same seed, same tokens; and mirostat replaces top-k / top-p (they have no say)
+    q = SamplingParams(temperature=1.0, seed=21, top_k=1, top_p=0.01, min_p=0.9, repeat_penalty=1.0)
+    q.mirostat, q.mirostat_tau, q.mirostat_eta = version, 3.0, 0.2
+    s1, s2 = Sampler(p), Sampler(q)
+    assert [s1.sample(np.roll(base, i).copy(), []) for i in range(50)] == [s2.sample(np.roll(base, i).copy(), []) for i in range(50)]
+
+
+def test_mirostat_2_keeps_tokens_whose_surprise_is_at_most_mu():
+    probs = np.array([0.5, 0.25, 0.125, 0.0625, 0.0625])
+    logits = np.log(probs).astype(np.float32)
+    p = SamplingParams.temperature_only(1.0, seed=4)
+    p.mirostat, p.mirostat_tau, p.mirostat_eta = 2, 1.0, 0.0   # mu stays 2: tokens with p >= 1/4
+    s = Sampler(p)
+    seen = np.bincount([s.sample(logits.copy(), []) for _ in range(400)], minlength=5)
+    assert seen[0] > 0 and seen[1] > 0 and seen[2:].sum() == 0
+    p.mirostat_tau = 0.1                                       # mu 0.2: nobody passes, the best stays
+    s = Sampler(p)
+    assert all(s.sample(logits.copy(), []) == 0 for _ in range(20))
