@@ -331,6 +331,22 @@ class CacheManager:
             raise CacheError(f"request {rid!r} is freed twice or was never added")
         self._check(self._lib.airun_cache_free(self._h, rc.slot), rid)
 
+    def rename(self, old: Hashable, new: Hashable) -> None:
+        """The live request ``old`` is known as ``new`` from now on (its slot, tokens and pages stay):
+        how a finished request's cache is kept under a name no later request can collide with."""
+        if new in self.requests:
+            raise CacheError(f"request {new!r} is already live")
+        rc = self.get(old)
+        del self.requests[old]
+        rc.rid = new
+        self.requests[new] = rc
+
+    @property
+    def can_rewind(self) -> bool:
+        """Whether ``truncate`` can move any request back: no fixed-size state and no window whose
+        pages are given back behind it."""
+        return not self.state and all(g.window == 0 for g in self.paged)
+
     # ------------------------------------------------------------ sharing and rewinding
     def _plan(self, n: int, state: Optional[Tuple[int, int]] = None) -> CopyPlan:
         c = self._copies

@@ -46,6 +46,7 @@ class EngineOptions:
     max_batch_tokens: int = 2048             # token budget of one step (the reference's -b/--batch-size)
     max_requests: int = 64                   # requests live at a time (the reference's --parallel slots)
     max_context: Optional[int] = None        # longest request (the reference's -c/--ctx-size)
+    prefix_cache: bool = False               # keep finished requests' caches for prompts that begin alike
 
 
 @dataclass
@@ -94,7 +95,8 @@ class Engine:
         self.storage = CacheStorage(self.manager, self.dtype, self.device)
         self.runner = StepRunner(model, self.manager, self.storage, o.max_batch_tokens,
                                  min(o.max_requests, o.max_batch_tokens), self.max_context)
-        self.scheduler = Scheduler(self.manager, o.max_batch_tokens, self.runner.R_max, self.max_context)
+        self.scheduler = Scheduler(self.manager, o.max_batch_tokens, self.runner.R_max, self.max_context,
+                                   prefix_cache=o.prefix_cache, run_copies=self.storage.run_copies)
         self._ids = itertools.count()
         R = self.runner.R_max
         self._small_host = torch.zeros(2 * R, dtype=torch.float32, pin_memory=self.device.type == "cuda")

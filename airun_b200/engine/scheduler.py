@@ -23,17 +23,28 @@ pages:
    slots and pages for at least part of the prompt remain.
 A prompt longer than the whole pool or the context limit is refused at submission.
 
+Prefix reuse (off unless asked for).  The reference keeps every slot's token history and starts a
+new turn from the longest common prefix of that history and the new prompt, at most all but the
+prompt's last token so that one token is always computed for its logits
+(crates/airun-core/src/runtime.rs:3256-3264, :2680-2681), and picks the slot with the longest
+such prefix (crates/airun-cli/src/sched.rs:381-388).  Here a finished request's pages are kept
+under a private name with the tokens they hold; a new request is forked from the kept cache with
+the longest common prefix (a page or more) and cut back to that prefix, so whole pages are shared
+and never written, and only the page the cut falls into is copied.  Kept caches are the first to
+go when pages or request slots run short, the one unused longest first, before anybody is
+preempted.  Models with fixed-size state or windows cannot be cut back and take no part.
+
 The scheduler is host-side only; it decides, the step function runs.
 """
 from __future__ import annotations
 
 import itertools
-from collections import deque
+from collections import OrderedDict, deque
 from dataclasses import dataclass, field
 from enum import Enum
 from typing import Deque, Dict, Hashable, List, Optional, Sequence, Tuple
 
-from ..cache.manager import CacheManager
+from ..cache.manager import CacheError, CacheManager, CopyPlan, OutOfPages
 from ..sampling.sampler import Sampler, SamplingParams
 
 
@@ -102,12 +113,21 @@ class Plan:
 
 
 class Scheduler:
-    def __init__(self, manager: CacheManager, max_batch_tokens: int, max_batch_reqs: int, max_context: int):
+    def __init__(self, manager: CacheManager, max_batch_tokens: int, max_batch_reqs: int, max_context: int,
+                 prefix_cache: bool = False, run_copies=None):
+        """``prefix_cache``: keep the caches of finished requests for later prompts that begin alike.
+        ``run_copies``: called with the CopyPlan of every reuse as soon as it is decided (the engine
+        queues the page copies on its stream, ahead of the step that reads them)."""
         self.manager = manager
         self.max_batch_tokens, self.max_batch_reqs, self.max_context = max_batch_tokens, max_batch_reqs, max_context
         self.waiting: Deque[Request] = deque()
         self.running: List[Request] = []        # in admission order
-        self.stats = dict(steps=0, preemptions=0, admitted=0, refused=0)
+        self.stats = dict(steps=0, preemptions=0, admitted=0, refused=0, prefix_hits=0, prefix_tokens=0,
+                          prefix_evictions=0)
+        self.prefix_cache = bool(prefix_cache) and manager.can_rewind
+        self.run_copies = run_copies
+        self.kept: "OrderedDict[Hashable, List[int]]" = OrderedDict()   # kept cache -> its tokens, least recently used first
+        self._kept_ids = itertools.count()
 
     # ------------------------------------------------------------ submission
     def add(self, req: Request) -> None:
@@ -132,21 +152,93 @@ class Scheduler:
             raise ValueError("only a running request can be forked")
         if child.prompt != parent.tokens:
             raise ValueError("a fork continues the parent's tokens; its prompt must equal them")
-        copies = self.manager.fork(parent.rid, child.rid)
+        while True:
+            try:
+                copies = self.manager.fork(parent.rid, child.rid)
+                break
+            except (OutOfPages, CacheError):
+                if not self._drop_kept():                 # kept caches give way to a fork as well
+                    raise
         child.num_computed = parent.num_computed
         self.running.append(child)
         self.stats["admitted"] += 1
         return copies
 
+    # ------------------------------------------------------------ kept caches of finished requests
+    def _keep(self, req: Request) -> bool:
+        """Keeps the cache of a request that ends instead of freeing it; False if it is not worth it."""
+        if not self.prefix_cache or req.num_computed < self.manager.page_size:
+            return False
+        name = ("kept", next(self._kept_ids))
+        self.manager.rename(req.rid, name)
+        self.manager.truncate(name, req.num_computed)      # pages taken ahead for a token that never came
+        self.kept[name] = req.tokens[:req.num_computed]
+        return True
+
+    def _drop_kept(self, spare: Hashable = None) -> bool:
+        """Frees the kept cache that went unused longest (never ``spare``); False if none is left."""
+        name = next((k for k in self.kept if k != spare), None)
+        if name is None:
+            return False
+        del self.kept[name]
+        self.manager.free_request(name)
+        self.stats["prefix_evictions"] += 1
+        return True
+
+    def _start_from_kept(self, req: Request) -> bool:
+        """Makes ``req`` a live request that starts from the kept cache sharing the longest prefix with
+        its tokens (a page or more, never the last token).  False: nothing to reuse, ``req`` is not live."""
+        toks = req.tokens
+        limit = len(toks) - 1
+        best, best_n = None, 0
+        for name, have in self.kept.items():
+            n, m = 0, min(limit, len(have))
+            if m <= best_n:
+                continue
+            while n < m and have[n] == toks[n]:
+                n += 1
+            if n > best_n:
+                best, best_n = name, n
+        if best is None or best_n < self.manager.page_size:
+            return False
+        while True:
+            # the fork wants a page for a partly filled last page, the cut one for a shared page it
+            # falls into: other kept caches give way to that, the one unused longest first
+            try:
+                forked = self.manager.fork(best, req.rid)
+            except (OutOfPages, CacheError):
+                if self._drop_kept(spare=best):
+                    continue
+                return False
+            try:
+                cut = self.manager.truncate(req.rid, best_n)
+                break
+            except (OutOfPages, CacheError):
+                self.manager.free_request(req.rid)
+                if not self._drop_kept(spare=best):
+                    return False
+        # a copy the fork asked for is moot if the cut gave its page back
+        held = {gid: set(self.manager.block_table(req.rid, gid)) for gid in {g for g, _, _ in forked.pages}}
+        pages = [c for c in forked.pages if c[2] in held[c[0]]] + cut.pages
+        if pages and self.run_copies is not None:
+            self.run_copies(CopyPlan(pages))
+        self.kept.move_to_end(best)
+        req.num_computed = best_n
+        self.stats["prefix_hits"] += 1
+        self.stats["prefix_tokens"] += best_n
+        return True
+
     # ------------------------------------------------------------ planning
     def _need_if_fits(self, req: Request, n: int, planned: Dict[int, int]) -> Optional[Dict[int, int]]:
-        """Pages ``n`` more tokens of ``req`` would take, or None if they are not free."""
+        """Pages ``n`` more tokens of ``req`` would take, or None if they are not free.  Kept caches
+        are given up, the one unused longest first, for as long as that can make them fit."""
         need = self.manager.pages_needed(req.rid, n)
-        free = self.manager.free_pages()
-        for gid, k in need.items():
-            if k + planned.get(gid, 0) > free[gid]:
+        while True:
+            free = self.manager.free_pages()
+            if all(k + planned.get(gid, 0) <= free[gid] for gid, k in need.items()):
+                return need
+            if not self._drop_kept():
                 return None
-        return need
 
     def _pages_fit(self, req: Request, n: int, planned: Dict[int, int]) -> bool:
         return self._need_if_fits(req, n, planned) is not None
@@ -187,7 +279,8 @@ class Scheduler:
         req.finished = reason
         if req in self.running:
             self.running.remove(req)
-            self.manager.free_request(req.rid)
+            if not self._keep(req):
+                self.manager.free_request(req.rid)
 
     def plan(self) -> Plan:
         fast = self._plan_steady_decode()
@@ -218,17 +311,19 @@ class Scheduler:
         for e in entries:
             self._note(e.request, e.count, planned)
         while (self.waiting and budget > 0 and len(entries) < self.max_batch_reqs
-               and self.manager.has_free_slot() and not preempted):
+               and (self.manager.has_free_slot() or self._drop_kept()) and not preempted):
             req = self.waiting[0]
             if req.cancelled:
                 self.waiting.popleft()
                 req.finished = FinishReason.CANCELLED
                 finished.append(req)
                 continue
-            self.manager.add_request(req.rid)
+            if not (self.kept and self._start_from_kept(req)):
+                self.manager.add_request(req.rid)
             want = min(req.num_tokens - req.num_computed, budget)
             if not self._pages_fit(req, want, planned):
                 self.manager.free_request(req.rid)
+                req.num_computed = 0
                 if not self.running:
                     # nothing else holds pages, so this request can never start
                     self.waiting.popleft()
@@ -239,7 +334,7 @@ class Scheduler:
             self.waiting.popleft()
             self.running.append(req)
             self.stats["admitted"] += 1
-            entries.append(PlannedEntry(req, 0, want, want == req.num_tokens))
+            entries.append(PlannedEntry(req, req.num_computed, want, req.num_computed + want == req.num_tokens))
             self._note(req, want, planned)
             budget -= want
         self.stats["steps"] += 1

@@ -313,3 +313,57 @@ def test_random_arrivals_forks_and_cancellations_under_a_small_pool(seed, folder
         elif req.finished.value == "EndOfGeneration":
             assert want[len(got)] in req.eog_tokens
     assert eng.manager.free_pages() == {g.gid: eng.manager.num_pages for g in eng.manager.paged}
+
+
+@pytest.mark.parametrize("name,dtype", [("B", "float32"), ("A", "bfloat16")])
+def test_turns_of_a_conversation_start_from_the_kept_cache(name, dtype, folders):
+    """With ``prefix_cache`` a finished request's pages are kept; a prompt that begins like it (the
+    next turn of a conversation: the first prompt, its answer and more) starts from them.  The tokens
+    are the ones the plain implementation gets for the whole prompt, in a pool so small that kept
+    caches must give way, and beside a request that shares nothing."""
+    import airun_b200
+    cfg, W = P.read_model_folder(folders[name])
+    V, ps = cfg["vocab_size"], TINY[name]["page_size"]
+    eng = airun_b200.Engine.from_folder(folders[name], dtype=dtype, page_size=ps, num_pages={"A": 10, "B": 17}[name],
+                                        max_batch_tokens=32, max_requests=4, max_context=128, prefix_cache=True)
+    greedy = airun_b200.SamplingParams.greedy()
+
+    def agree(prompt, got, what):
+        if dtype == "float32":
+            assert got == P.plain_greedy_generate(cfg, W, prompt, len(got)), what
+        else:
+            # bfloat16: a near-tie may flip with the kernels a token went through (a portion's, a single
+            # token's).  Every token chosen must be, for the plain implementation that rounds where the
+            # engine does, within twice that rounding's own effect on the logits of its best token.
+            seq = list(prompt)
+            for t in got:
+                rounded = P.plain_forward(cfg, W, seq, torch.float32, round_to=torch.bfloat16)[-1]
+                exact = P.plain_forward(cfg, W, seq, torch.float32)[-1]
+                noise = float((rounded - exact).abs().max())
+                assert float(rounded.max() - rounded[t]) <= 2 * noise + 1e-3, what
+                seq.append(t)
+
+    turn1 = random_tokens(3 * ps + 5, V, 300)
+    out1 = eng.generate(turn1, greedy, max_new_tokens=9).token_ids
+    agree(turn1, out1, "first turn")
+    assert len(eng.scheduler.kept) == 1
+    turn2 = turn1 + out1 + random_tokens(11, V, 301)
+    other = random_tokens(2 * ps + 3, V, 302)
+    res = eng.generate([turn2, other], greedy, max_new_tokens=7)
+    agree(turn2, res[0].token_ids, "second turn, from the kept cache")
+    agree(other, res[1].token_ids, "a request that shares nothing")
+    st = eng.scheduler.stats
+    assert st["prefix_hits"] == 1 and st["prefix_tokens"] == len(turn1) + len(out1) - 1
+    # the same prompt again: all but its last token comes from the cache
+    again = eng.generate(turn2, greedy, max_new_tokens=7).token_ids
+    agree(turn2, again, "the same prompt again")
+    assert st["prefix_hits"] == 2 and st["prefix_tokens"] == len(turn1) + len(out1) - 1 + len(turn2) - 1
+    # a prompt that diverges inside a page, while the pool is too small for every kept cache
+    turn3 = turn2[:2 * ps + 3] + random_tokens(40, V, 303)
+    out3 = eng.generate(turn3, greedy, max_new_tokens=6).token_ids
+    agree(turn3, out3, "third prompt, cut inside a shared page")
+    assert st["prefix_hits"] == 3 and st["prefix_evictions"] >= 1
+    eng.manager.check_invariants()
+    while eng.scheduler._drop_kept():
+        pass
+    assert eng.manager.free_pages() == {g.gid: eng.manager.num_pages for g in eng.manager.paged}

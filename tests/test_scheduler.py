@@ -173,3 +173,198 @@ def test_slots_limit_admission():
         seen_running = max(seen_running, len(s.running))
         run(m, s, p)
     assert seen_running == 2 and all(r.finished == FinishReason.MAX_TOKENS for r in rs)
+
+
+# ----------------------------------------------------------------------------- kept caches of finished requests
+class FakePages:
+    """Stands in for the device: what token every (page, place) holds, the page copies the scheduler
+    asks for, and a check that a request's block table names exactly its own tokens."""
+
+    def __init__(self, m):
+        self.m, self.cell, self.copies = m, {}, 0
+
+    def run_copies(self, plan):
+        ps = self.m.page_size
+        for gid, src, dst in plan.pages:
+            self.copies += 1
+            for k in range(ps):
+                self.cell[(dst, k)] = self.cell.get((src, k))
+
+    def step(self, s, plan, token=7):
+        ps = self.m.page_size
+        for e in plan.entries:
+            self.m.reserve(e.request.rid, e.count)
+        for e in plan.entries:                       # the step writes its tokens' keys, then reads all of them
+            bt = self.m.block_table(e.request.rid, 0)
+            toks = e.request.tokens
+            for pos in range(e.start, e.start + e.count):
+                holders = [r for r in self.m.requests if bt[pos // ps] in self.m.block_table(r, 0)]
+                assert holders == [e.request.rid], "a shared page is written"
+                self.cell[(bt[pos // ps], pos % ps)] = toks[pos]
+            for pos in range(e.start + e.count):
+                assert self.cell.get((bt[pos // ps], pos % ps)) == toks[pos], (e.request.rid, pos)
+        for e in plan.entries:
+            self.m.commit(e.request.rid, e.count)
+        s.advance(plan)
+        done = []
+        for e in plan.entries:
+            if e.wants_logits:
+                t = token(e.request) if callable(token) else token
+                if s.accept(e.request, t) is not None:
+                    done.append(e.request)
+        self.m.check_invariants()
+        return done
+
+
+def make_kept(pages=16, page=4, budget=64, reqs=4, ctx=64):
+    m = CacheManager([PagedKVSpec(1, 8, 0)], [None], page, pages, reqs)
+    dev = FakePages(m)
+    return m, Scheduler(m, budget, reqs, ctx, prefix_cache=True, run_copies=dev.run_copies), dev
+
+
+def drain(s, dev, token=7):
+    while s.has_work():
+        dev.step(s, s.plan(), token)
+
+
+def test_a_later_prompt_starts_from_the_kept_cache_of_an_earlier_one():
+    m, s, dev = make_kept()
+    a = Request("a", list(range(100, 114)), SamplingParams.greedy(), 3)          # 14 prompt tokens + 3 generated
+    s.add(a)
+    drain(s, dev)
+    assert a.finished == FinishReason.MAX_TOKENS and len(s.kept) == 1 and len(m.requests) == 1
+    kept_tokens = next(iter(s.kept.values()))
+    assert kept_tokens == a.tokens[:16]                                           # the last token was never fed
+    # same first 10 tokens: two whole pages are shared, the cut falls into the third (copied)
+    b = Request("b", list(range(100, 110)) + [500, 501, 502], SamplingParams.greedy(), 2)
+    s.add(b)
+    p = s.plan()
+    assert [(e.request.rid, e.start, e.count, e.wants_logits) for e in p.entries] == [("b", 10, 3, True)]
+    assert s.stats["prefix_hits"] == 1 and s.stats["prefix_tokens"] == 10 and dev.copies == 1
+    kept_name = next(iter(s.kept))
+    assert m.block_table("b", 0)[:2] == m.block_table(kept_name, 0)[:2] and \
+        m.block_table("b", 0)[2] != m.block_table(kept_name, 0)[2]
+    dev.step(s, p)
+    drain(s, dev)
+    assert b.finished == FinishReason.MAX_TOKENS and len(s.kept) == 2
+    # an identical prompt: everything but its last token is reused, which is computed for the logits
+    c = Request("c", list(range(100, 114)), SamplingParams.greedy(), 1)
+    s.add(c)
+    p = s.plan()
+    assert [(e.start, e.count, e.wants_logits) for e in p.entries] == [(13, 1, True)]
+    dev.step(s, p)
+    # less than a page in common: computed from the start
+    d = Request("d", [100, 101, 9, 9, 9, 9], SamplingParams.greedy(), 1)
+    s.add(d)
+    p = s.plan()
+    assert [(e.start, e.count) for e in p.entries] == [(0, 6)]
+    dev.step(s, p)
+    m.check_invariants()
+
+
+def test_kept_caches_go_before_anybody_is_preempted_oldest_first():
+    m, s, dev = make_kept(pages=8, page=4, reqs=3)
+    for name, first in (("a", 100), ("b", 200)):                # two kept caches of 3 pages each (10 + 2 tokens)
+        s.add(Request(name, list(range(first, first + 10)), SamplingParams.greedy(), 3))
+        drain(s, dev)
+    assert len(s.kept) == 2 and m.free_pages()[0] == 2
+    first_kept, second_kept = list(s.kept)
+    c = Request("c", list(range(300, 318)), SamplingParams.greedy(), 2)      # needs 5 pages: the oldest kept cache goes
+    s.add(c)
+    p = s.plan()
+    assert [(e.start, e.count) for e in p.entries] == [(0, 18)] and not p.preempted
+    assert list(s.kept) == [second_kept] and s.stats["prefix_evictions"] == 1
+    dev.step(s, p)
+    drain(s, dev)                                                 # c decodes past 20 tokens: needs page 6 of 8
+    assert c.finished == FinishReason.MAX_TOKENS and s.stats["preemptions"] == 0
+    # request slots: 3 in all; kept caches hold them until a new request needs one
+    m.check_invariants()
+    for i in range(4):
+        s.add(Request(("e", i), [700 + i, 1, 2, 3, 4], SamplingParams.greedy(), 1))
+    drain(s, dev)
+    assert s.stats["preemptions"] == 0 and len(m.requests) <= 3
+
+
+def test_using_a_kept_cache_makes_it_the_last_to_go_and_forks_evict_too():
+    m, s, dev = make_kept(pages=12, page=4, reqs=4)
+    for name, first in (("a", 100), ("b", 200)):
+        s.add(Request(name, list(range(first, first + 8)), SamplingParams.greedy(), 1))
+        drain(s, dev)
+    ka, kb = list(s.kept)
+    s.add(Request("a2", list(range(100, 108)) + [1], SamplingParams.greedy(), 4))    # uses a's cache
+    p = s.plan()
+    assert p.entries[0].start == 8 and list(s.kept) == [kb, ka]
+    dev.step(s, p)
+    live = s.running[0]
+    child = Request("a3", list(live.tokens), SamplingParams.greedy(), 2)
+    dev.run_copies(s.fork(live, child))
+    drain(s, dev)
+    m.check_invariants()
+
+
+def test_models_that_cannot_be_cut_back_keep_nothing():
+    m = CacheManager([PagedKVSpec(1, 8, 6)], [None], 4, 16, 4)                   # a window of 6 keys
+    s = Scheduler(m, 64, 4, 64, prefix_cache=True)
+    assert not s.prefix_cache
+    s.add(req("a", 9, max_new=2))
+    while s.has_work():
+        run(m, s, s.plan())
+    assert not s.kept and not m.requests
+
+
+def test_random_traffic_with_kept_caches_never_reads_a_wrong_token():
+    import random
+    rnd = random.Random(5)
+    m, s, dev = make_kept(pages=24, page=4, budget=24, reqs=4, ctx=48)
+    stems = [[rnd.randrange(50, 60) for _ in range(20)] for _ in range(3)]
+    done = 0
+    for i in range(60):
+        stem = rnd.choice(stems)
+        prompt = stem[:rnd.randrange(1, 20)] + [rnd.randrange(1000, 1010) for _ in range(rnd.randrange(0, 6))]
+        s.add(Request(("r", i), prompt, SamplingParams.greedy(), rnd.randrange(1, 6)))
+        for _ in range(rnd.randrange(0, 4)):
+            if s.has_work():
+                done += len(dev.step(s, s.plan(), token=lambda r: rnd.randrange(50, 60)))
+    while s.has_work():
+        done += len(dev.step(s, s.plan(), token=lambda r: rnd.randrange(50, 60)))
+    assert done == 60 and s.stats["prefix_hits"] > 5
+    while s._drop_kept():
+        pass
+    assert not m.requests and m.free_pages()[0] == 24
+    m.check_invariants()
+
+
+@pytest.mark.parametrize("ps,pages", [(16, 10), (8, 17)])
+def test_turns_of_a_conversation_in_a_pool_that_is_almost_full(ps, pages):
+    """A first prompt, then the prompt + its answer + more, the same again, and a prompt that leaves the
+    others inside a page, in a pool so small that reuse itself finds no free page until another kept
+    cache has gone."""
+    import random
+    m = CacheManager([PagedKVSpec(1, 8, 0)], [None], ps, pages, 4, max_blocks=(128 + ps - 1) // ps)
+    dev = FakePages(m)
+    s = Scheduler(m, 32, 4, 128, prefix_cache=True, run_copies=dev.run_copies)
+    rnd = random.Random(1)
+
+    def ids(n):
+        return [rnd.randrange(200, 250) for _ in range(n)]
+
+    def generate(prompts, n):
+        rs = [Request(("g", rnd.random()), list(p), SamplingParams.greedy(), n) for p in prompts]
+        for r in rs:
+            s.add(r)
+        drain(s, dev, token=lambda r: sum(r.tokens) % 97 + 3)         # a "model": the next token follows from the sequence
+        return [r.output for r in rs]
+
+    turn1 = ids(3 * ps + 5)
+    out1 = generate([turn1], 9)[0]
+    turn2 = turn1 + out1 + ids(11)
+    res = generate([turn2, ids(2 * ps + 3)], 7)
+    st = s.stats
+    assert st["prefix_hits"] == 1 and st["prefix_tokens"] == len(turn1) + len(out1) - 1
+    assert generate([turn2], 7)[0] == res[0]
+    assert st["prefix_hits"] == 2 and st["prefix_tokens"] == len(turn1) + len(out1) - 1 + len(turn2) - 1
+    generate([turn2[:2 * ps + 3] + ids(40)], 6)
+    assert st["prefix_hits"] == 3 and st["prefix_evictions"] >= 1 and st["preemptions"] == 0
+    while s._drop_kept():
+        pass
+    assert not m.requests and m.free_pages()[0] == pages
