@@ -228,3 +228,31 @@ def test_mirostat_2_keeps_tokens_whose_surprise_is_at_most_mu():
     p.mirostat_tau = 0.1                                       # mu 0.2: nobody passes, the best stays
     s = Sampler(p)
     assert all(s.sample(logits.copy(), []) == 0 for _ in range(20))
+
+
+# ----------------------------------------------------------------------------- the command line's options
+def test_command_line_options_carry_the_reference_names_and_defaults():
+    """``airun run`` (crates/airun-cli/src/run.rs:50-220), ``bench`` (bench.rs:11-92) and ``perplexity``
+    (perplexity.rs:24-66): option names and defaults; parsing needs no GPU."""
+    from airun_b200.cli import build_parser, parse_ids
+    ap = build_parser()
+    a = ap.parse_args(["run", "m", "-p", "1,2 3"])
+    assert (a.predict, a.temp, a.top_k, a.top_p, a.min_p, a.typical_p, a.top_n_sigma) == (256, 0.8, 40, 0.95, 0.05, 1.0, 0.0)
+    assert (a.repeat_penalty, a.presence_penalty, a.frequency_penalty, a.repeat_last_n, a.seed) == (1.1, 0.0, 0.0, 64, 0)
+    assert a.ctx_size is None and a.batch_size == 512 and not a.stats and not a.quiet
+    assert parse_ids(a.prompt) == [1, 2, 3]
+    a = ap.parse_args(["run", "m", "-n", "8", "-c", "100", "-b", "32", "--temp", "0", "--seed", "7", "-q", "--stats"])
+    assert (a.predict, a.ctx_size, a.batch_size, a.temp, a.seed, a.quiet, a.stats) == (8, 100, 32, 0.0, 7, True, True)
+    b = ap.parse_args(["bench", "m"])
+    assert (b.prefill, b.decode, b.decode_at, b.runs, b.warmup, b.temp) == ("128,512", 128, "16", 3, 1, 0.0)
+    assert not b.forward_only and not b.random_tokens and not b.json and b.ctx_size is None
+    b = ap.parse_args(["bench", "m", "--decode-at", "16,4096", "--random-tokens", "--forward-only", "-c", "8192", "--json"])
+    assert b.decode_at == "16,4096" and b.random_tokens and b.forward_only and b.ctx_size == 8192 and b.json
+    p = ap.parse_args(["perplexity", "m", "-f", "ids.txt"])
+    assert (p.file, p.limit, p.chunk, p.batched, p.worst, p.ctx_size) == ("ids.txt", 0, 0, False, 0, 4096)
+    p = ap.parse_args(["perplexity", "m", "--file", "x", "-n", "100", "--chunk", "64", "--batched", "--worst", "5", "-c", "512"])
+    assert (p.limit, p.chunk, p.batched, p.worst, p.ctx_size) == (100, 64, True, 5, 512)
+    s = ap.parse_args(["selftest", "--device", "0", "--verbose"])
+    assert s.device == 0 and s.verbose
+    with pytest.raises(SystemExit):
+        parse_ids("  ")
