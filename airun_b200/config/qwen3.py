@@ -20,7 +20,7 @@ else layers with index >= ``max_window_layers`` do.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field, asdict
+from dataclasses import dataclass
 from typing import Any, Dict, List, Optional, Tuple
 
 from .base import ConfigError, LayerSpec, ModelConfig

@@ -13,8 +13,8 @@ from __future__ import annotations
 
 import itertools
 import time
-from dataclasses import dataclass, field
-from typing import Dict, Hashable, List, Optional, Sequence, Union
+from dataclasses import dataclass
+from typing import Hashable, List, Optional, Sequence, Union
 
 import numpy as np
 import torch
@@ -24,7 +24,7 @@ from ..config.base import ModelConfig, architecture_name, lookup_architecture, r
 from ..kernels import ops
 from ..sampling.sampler import SamplingParams
 from ..weights.loader import open_model_folder
-from .scheduler import FinishReason, Plan, Request, Scheduler
+from .scheduler import FinishReason, Request, Scheduler
 from .step import StepEntry, StepRunner
 
 # AIRUN_SCHED_TIMING=1 prints the host time of every scheduler step (the reference's switch of the

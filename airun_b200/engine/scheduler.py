@@ -42,7 +42,7 @@ import itertools
 from collections import OrderedDict, deque
 from dataclasses import dataclass, field
 from enum import Enum
-from typing import Deque, Dict, Hashable, List, Optional, Sequence, Tuple
+from typing import Deque, Dict, Hashable, List, Optional, Tuple
 
 from ..cache.manager import CacheError, CacheManager, CopyPlan, OutOfPages
 from ..sampling.sampler import Sampler, SamplingParams

@@ -15,7 +15,7 @@ chunk returns nothing and does not synchronise (runtime.rs:2032-2037).
 from __future__ import annotations
 
 import ctypes
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Dict, Hashable, List, Optional, Sequence
 
 import numpy as np

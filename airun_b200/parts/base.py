@@ -40,7 +40,7 @@ Block           forward(ctx, x, delta, cache) -> delta of the block's last sub-l
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Any, Callable, Dict, List, Optional, Tuple
+from typing import Callable, Dict, List, Optional, Tuple
 
 import torch
 

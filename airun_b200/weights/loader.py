@@ -21,7 +21,7 @@ import hashlib
 import json
 import os
 from dataclasses import dataclass
-from typing import Dict, Iterable, List, Optional, Protocol, Sequence, Tuple
+from typing import Dict, Iterable, List, Protocol, Sequence, Tuple
 
 import torch
 

@@ -15,7 +15,7 @@ import json
 import mmap
 import os
 import struct
-from typing import Dict, Iterable, List, Tuple
+from typing import Dict, List, Tuple
 
 import torch
 
