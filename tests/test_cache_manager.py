@@ -302,3 +302,31 @@ def test_random_forks_and_cuts_every_request_reads_its_own_history(seed):
     for rid in list(history):
         m.free_request(rid)
     assert m.free_pages() == {0: 48, 1: 48}
+
+
+def test_rename_keeps_slot_tokens_and_pages_and_refuses_a_live_name():
+    m = manager()
+    a = m.add_request("a")
+    m.reserve("a", 11)
+    m.commit("a", 11)
+    blocks, slot = m.block_table("a", 0), a.slot
+    m.add_request("b")
+    with pytest.raises(CacheError):
+        m.rename("a", "b")                   # "b" is live
+    with pytest.raises(CacheError):
+        m.rename("nobody", "x")
+    m.rename("a", ("kept", 0))
+    assert "a" not in m.requests and m.get(("kept", 0)).slot == slot and m.get(("kept", 0)).rid == ("kept", 0)
+    assert m.get(("kept", 0)).num_tokens == 11 and m.block_table(("kept", 0), 0) == blocks
+    m.add_request("a")                       # the old name is free for a new request
+    m.check_invariants()
+    m.free_request(("kept", 0))
+    m.free_request("a")
+    m.free_request("b")
+    assert m.free_pages() == {0: 12}
+
+
+def test_can_rewind_only_without_windows_and_state():
+    assert manager([FULL, FULL]).can_rewind
+    assert not manager([FULL, WIN]).can_rewind
+    assert not manager([FULL, StateSpec((3,))]).can_rewind
