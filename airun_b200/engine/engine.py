@@ -22,7 +22,7 @@ import torch
 from ..cache.manager import CacheManager, CacheStorage
 from ..config.base import ModelConfig, architecture_name, lookup_architecture, read_config_json
 from ..kernels import ops
-from ..sampling.sampler import SamplingParams
+from ..sampling.sampler import SamplingParams, sample_rows
 from ..weights.loader import open_model_folder
 from .scheduler import FinishReason, Request, Scheduler
 from .step import StepEntry, StepRunner
@@ -283,8 +283,10 @@ class Engine:
             self.runner.err.zero_()
             raise RuntimeError("a kernel reported: " + ops.describe_device_error(int(picked[R])))
         out = [int(picked[i]) for i in range(n)]
-        for j, i in enumerate(host_rows):
-            out[i] = reqs[i].sampler.sample(rows_host[j], reqs[i].tokens)
+        if host_rows:
+            picked_host = sample_rows([reqs[i].sampler for i in host_rows], rows_host, [reqs[i].tokens for i in host_rows])
+            for i, tok in zip(host_rows, picked_host):
+                out[i] = tok
         return out
 
     # ------------------------------------------------------------ generation

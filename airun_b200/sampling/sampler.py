@@ -27,7 +27,7 @@ from __future__ import annotations
 import math
 import time
 from dataclasses import dataclass
-from typing import Sequence, Tuple
+from typing import List, Optional, Sequence, Tuple
 
 import numpy as np
 
@@ -249,7 +249,13 @@ class Sampler:
         return self.rng.next_f32()
 
     def sample(self, logits: np.ndarray, history: Sequence[int]) -> int:
-        """The full chain on the host; ``logits`` (float32 [V]) is modified in place."""
+        """The full chain on the host for one row; ``logits`` (float32 [V]) is modified in place."""
+        return sample_rows([self], logits.reshape(1, -1), [history])[0]
+
+    # The chain in three stages, so that several rows share one call of the native top-k.
+    def _before_candidates(self, logits: np.ndarray, history: Sequence[int]) -> Optional[int]:
+        """Everything that works on the whole row.  Returns the token when the chain ends here (greedy,
+        mirostat), else None: the row then goes on with its ``candidate_count`` largest logits."""
         p = self.params
         for tok, bias in p.logit_bias:
             if 0 <= tok < logits.shape[0]:
@@ -266,21 +272,22 @@ class Sampler:
             return first_argmax(logits)
         if p.mirostat != 0:
             return self._mirostat(logits)
-        V = logits.shape[0]
-        keep = min(max(p.top_k, 1), V) if p.top_k > 0 else V
-        clean = np.where(np.isnan(logits), -np.inf, logits)
-        if keep < V:
-            idx = np.argpartition(-clean, keep - 1)[:keep]
-        else:
-            idx = np.arange(V)
-        order = idx[np.argsort(-clean[idx], kind="stable")]
-        vals = clean[order].astype(np.float32)
+        return None
+
+    def candidate_count(self, vocab: int) -> int:
+        """top-k first: it is the cheapest cut, and everything behind it sorts (sample.rs:390-403)."""
+        k = self.params.top_k
+        return min(max(k, 1), vocab) if k > 0 else vocab
+
+    def _from_candidates(self, ids: np.ndarray, vals: np.ndarray) -> int:
+        """Softmax over the candidates (``vals`` float32, the largest first), the filters on
+        probabilities, the draw."""
+        p = self.params
         mx = vals[0]
         temperature = dynamic_temperature(vals, p.temperature, p.dynatemp_range, p.dynatemp_exponent)
         probs = np.exp(((vals - mx) / np.float32(temperature)).astype(np.float64)).astype(np.float32)
         s = np.float32(probs.sum(dtype=np.float32))
         probs = probs / s
-        ids = order
         if p.typical_p < 1.0:
             ids, probs = _typical(ids, probs, p.typical_p)
         if p.min_p > 0.0:
@@ -300,6 +307,77 @@ class Sampler:
         if float(probs.sum(dtype=np.float32)) <= 0.0:
             return int(ids[0])
         return int(ids[self._draw(ids, probs)])
+
+
+def largest_logits(row: np.ndarray, k: int) -> Tuple[np.ndarray, np.ndarray]:
+    """(ids, values) of the ``k`` largest entries of a float32 row, the largest first, with numpy: the
+    plain twin of the native top-k, and what serves when every logit is a candidate (top-k off).
+    NaN counts as -inf; which of several equal values at the cut stays is numpy's choice."""
+    clean = np.where(np.isnan(row), -np.inf, row).astype(np.float32, copy=False)
+    n = clean.shape[0]
+    idx = np.argpartition(-clean, k - 1)[:k] if k < n else np.arange(n)
+    order = idx[np.argsort(-clean[idx], kind="stable")]
+    return order, clean[order]
+
+
+NATIVE_TOPK_MAX = 4096        # candidates up to which the one-pass heap of csrc/sampler_core.cpp is used
+_TOPK_THREADS = 8
+
+
+def _native_topk():
+    """``airun_topk_rows`` of csrc/sampler_core.cpp, compiled with the C++ compiler at first use."""
+    global _TOPK_FN
+    if _TOPK_FN is None:
+        import ctypes
+        from ..csrc import build
+        f = build.load("sampler_core").airun_topk_rows
+        f.restype = ctypes.c_int
+        f.argtypes = [ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int, ctypes.c_longlong, ctypes.c_void_p,
+                      ctypes.c_void_p, ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int]
+        _TOPK_FN = f
+    return _TOPK_FN
+
+
+_TOPK_FN = None
+
+
+def largest_logits_rows(rows: np.ndarray, ks: Sequence[int]) -> List[Tuple[np.ndarray, np.ndarray]]:
+    """The ``ks[r]`` largest logits of every row of ``rows`` (float32 [R, V], rows contiguous), the rows
+    side by side on threads of the native core.  Equal values come by ascending id."""
+    R, V = rows.shape
+    if rows.dtype != np.float32 or rows.strides[1] != 4 or rows.strides[0] % 4 != 0 or rows.strides[0] < 4 * V:
+        raise ValueError("largest_logits_rows wants float32 rows that are contiguous")
+    kmax = max(ks)
+    ks_arr = np.asarray(ks, dtype=np.int32)
+    idx = np.empty((R, kmax), dtype=np.int32)
+    val = np.empty((R, kmax), dtype=np.float32)
+    status = _native_topk()(rows.ctypes.data, rows.strides[0] // 4, R, V, ks_arr.ctypes.data, idx.ctypes.data,
+                            val.ctypes.data, kmax, _TOPK_THREADS)
+    if status != 0:
+        raise ValueError("the native top-k refused its arguments")
+    return [(idx[r, :ks[r]], val[r, :ks[r]]) for r in range(R)]
+
+
+def sample_rows(samplers: Sequence["Sampler"], rows: np.ndarray, histories: Sequence[Sequence[int]]) -> List[int]:
+    """One token for every row: ``rows[r]`` (float32 [V], modified in place) goes through the chain of
+    ``samplers[r]`` with the tokens of its request so far, ``histories[r]``.  The rows whose chain
+    reaches the candidates share one native top-k call."""
+    out: List[Optional[int]] = []
+    for s, row, h in zip(samplers, rows, histories):
+        out.append(s._before_candidates(row, h))
+    V = rows.shape[1]
+    pending = [r for r, t in enumerate(out) if t is None]
+    native = [r for r in pending if samplers[r].candidate_count(V) < V and samplers[r].candidate_count(V) <= NATIVE_TOPK_MAX]
+    if native:
+        sub = rows if len(native) == len(rows) else rows[native]
+        found = largest_logits_rows(np.ascontiguousarray(sub), [samplers[r].candidate_count(V) for r in native])
+        for r, (ids, vals) in zip(native, found):
+            out[r] = samplers[r]._from_candidates(ids, vals)
+    for r in pending:
+        if out[r] is None:
+            ids, vals = largest_logits(rows[r], samplers[r].candidate_count(V))
+            out[r] = samplers[r]._from_candidates(ids, vals)
+    return [int(t) for t in out]
 
 
 def _typical(ids: np.ndarray, probs: np.ndarray, typical_p: float):

@@ -256,3 +256,66 @@ def test_command_line_options_carry_the_reference_names_and_defaults():
     assert s.device == 0 and s.verbose
     with pytest.raises(SystemExit):
         parse_ids("  ")
+
+
+# ----------------------------------------------------------------------------- the native top-k
+def test_native_largest_logits_against_numpy():
+    from airun_b200.sampling.sampler import largest_logits, largest_logits_rows
+    rng = np.random.default_rng(12)
+    for V, ks in ((1000, [1, 40, 999, 7]), (151936, [40, 1, 256]), (33, [33, 5])):
+        rows = (rng.normal(size=(len(ks), V)) * 4).astype(np.float32)
+        rows[0, rng.integers(0, V, size=5)] = np.nan              # NaN never wins
+        if V > 100:
+            rows[1, :50] = -np.inf
+        got = largest_logits_rows(rows, ks)
+        for r, k in enumerate(ks):
+            ids, vals = got[r]
+            want_ids, want_vals = largest_logits(rows[r], k)
+            assert ids.shape == (k,) and np.array_equal(vals, want_vals)
+            finite = np.isfinite(vals)                                        # random floats: no ties but among -inf
+            assert np.array_equal(ids[finite], want_ids[finite])
+            clean = np.where(np.isnan(rows[r]), -np.inf, rows[r])
+            assert np.array_equal(clean[ids], vals) and np.all(vals[:-1] >= vals[1:]) and len(set(ids.tolist())) == k
+            assert np.all(np.diff(ids[~finite]) > 0)                          # equal values by ascending id
+    # a view with a row stride beyond its length, as a slice of a wider array is
+    wide = (rng.normal(size=(3, 700))).astype(np.float32)
+    view = wide[:, :500]
+    for (ids, vals), row in zip(largest_logits_rows(view, [9, 9, 9]), view):
+        assert np.array_equal(ids, largest_logits(row, 9)[0])
+    with pytest.raises(ValueError):
+        largest_logits_rows(wide[:, ::2], [3, 3, 3])
+    with pytest.raises(ValueError):
+        largest_logits_rows(view, [3, 3, 501])
+
+
+def test_native_largest_logits_orders_equal_values_by_id():
+    from airun_b200.sampling.sampler import largest_logits_rows
+    row = np.array([[1.0, 5.0, 5.0, 0.0, 5.0, 1.0, 1.0, np.nan, 7.0]], dtype=np.float32)
+    ids, vals = largest_logits_rows(row, [3])[0]
+    assert ids.tolist() == [8, 1, 2] and vals.tolist() == [7.0, 5.0, 5.0]     # of three 5s the first two stay
+    ids, _ = largest_logits_rows(row, [6])[0]
+    assert ids.tolist() == [8, 1, 2, 4, 0, 5]
+    flat = np.full((1, 50), -np.inf, dtype=np.float32)
+    assert largest_logits_rows(flat, [4])[0][0].tolist() == [0, 1, 2, 3]
+
+
+def test_rows_sampled_together_get_what_they_get_alone():
+    from airun_b200.sampling.sampler import sample_rows
+    rng = np.random.default_rng(13)
+    V = 5000
+    base = (rng.normal(size=(6, V)) * 3).astype(np.float32)
+    hist = [rng.integers(0, V, size=30).tolist() for _ in range(6)]
+
+    def make():
+        ps = [SamplingParams(seed=3), SamplingParams.greedy(), SamplingParams(seed=4, top_k=0, min_p=0.02),
+              SamplingParams(seed=5, top_k=5, dry_multiplier=0.8), SamplingParams(seed=6, mirostat=2),
+              SamplingParams(seed=7, top_k=V + 10, xtc_probability=0.5)]
+        return [Sampler(p) for p in ps]
+
+    together, alone = make(), make()
+    for step in range(12):
+        rows = np.roll(base, step, axis=1).copy()
+        got = sample_rows(together, rows, hist)
+        want = [s.sample(np.roll(base[r], step).copy(), hist[r]) for r, s in enumerate(alone)]
+        assert got == want
+        assert got[1] == int(np.argmax(np.roll(base[1], step)))
