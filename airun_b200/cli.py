@@ -14,8 +14,10 @@ Subcommands: ``run`` (generate), ``bench`` (prefill and decode rates of a model
 folder, median of runs, in the manner of crates/airun-cli/src/bench.rs:11-92),
 ``perplexity`` (loss and top-1 of a token file; ``--chunk``, ``--batched``,
 ``--limit``, ``--worst`` as in crates/airun-cli/src/perplexity.rs:97-222), ``init`` (random-weights mode: write
-a model folder from a config.json and a seed), ``inspect`` (print the
-configuration).
+a model folder from a config.json and a seed), ``inspect`` (describe a model
+folder: configuration, tensors, whether it can be loaded; ``--tensors``,
+``--json``, ``--values TENSOR --count N`` as crates/airun-cli/src/inspect.rs:10-36),
+``selftest``.
 """
 from __future__ import annotations
 
@@ -101,8 +103,12 @@ def build_parser() -> argparse.ArgumentParser:
     init.add_argument("out", help="folder to write")
     init.add_argument("--seed", type=int, default=1)
 
-    ins = sub.add_parser("inspect", help="print the configuration of a model folder")
+    ins = sub.add_parser("inspect", help="describe a model folder: configuration, tensors, whether it can be loaded")
     ins.add_argument("model")
+    ins.add_argument("--tensors", action="store_true", help="list every tensor with its shape, type and size")
+    ins.add_argument("--json", action="store_true", help="machine-readable JSON instead of a report")
+    ins.add_argument("--values", metavar="TENSOR", help="print a tensor's first values and summary statistics")
+    ins.add_argument("--count", type=int, default=16, help="how many values --values prints")
 
     st = sub.add_parser("selftest", help="every kernel against a plain reference of the same operation")
     st.add_argument("--device", type=int, default=0)
@@ -344,10 +350,80 @@ def cmd_init(a) -> int:
     return 0
 
 
+def _human_bytes(n: int) -> str:
+    for unit in ("B", "KiB", "MiB", "GiB"):
+        if n < 1024 or unit == "GiB":
+            return f"{n} B" if unit == "B" else f"{n:.2f} {unit}"
+        n /= 1024.0
+    return f"{n:.2f} GiB"
+
+
 def cmd_inspect(a) -> int:
-    from .config import load_config
-    print(load_config(a.model).summary())
-    return 0
+    """Describes a model folder in the manner of the reference's ``airun inspect``
+    (crates/airun-cli/src/inspect.rs:10-36: ``--tensors``, ``--json``, ``--values TENSOR --count N``):
+    the configuration, the tensors of its safetensors files, and whether they are what the
+    architecture wants (the error a load would raise, without loading anything).  Needs no GPU."""
+    import torch
+    from .config import architecture_name, load_config, lookup_architecture, read_config_json
+    from .weights import WeightError, check_source, open_model_folder
+    config = load_config(a.model)
+    src = open_model_folder(a.model)
+    try:
+        if a.values:
+            if a.values not in src.names():
+                raise SystemExit(f"no tensor named {a.values!r} in {a.model} (see --tensors)")
+            t = src.read(a.values)
+            flat = t.reshape(-1)
+            head = flat[:max(a.count, 0)].tolist()
+            print(f"{a.values}  {str(t.dtype).replace('torch.', '')}  {list(t.shape)}")
+            print("first values: " + " ".join(f"{v:.6g}" for v in head))
+            if flat.numel() and t.dtype.is_floating_point:
+                d = flat.double()
+                print(f"min {float(d.min()):.6g}  max {float(d.max()):.6g}  mean {float(d.mean()):.6g}  "
+                      f"std {float(d.std(unbiased=False)):.6g}  non-finite {int((~torch.isfinite(d)).sum())}")
+            return 0
+        tensors = []
+        for name in sorted(src.names()):
+            dt, shape = src.info(name)
+            n = 1
+            for k in shape:
+                n *= int(k)
+            tensors.append(dict(name=name, dtype=str(dt).replace("torch.", ""), shape=list(shape),
+                                bytes=n * torch.empty(0, dtype=dt).element_size()))
+        _, builder = lookup_architecture(architecture_name(read_config_json(a.model)))
+        model = builder(config, torch.float32, "meta")
+        problem = None
+        try:
+            check_source(model.weight_specs(), src, model.ignorable_tensors())
+        except WeightError as e:
+            problem = str(e)
+    finally:
+        src.close()
+    total = sum(t["bytes"] for t in tensors)
+    by_type = {}
+    for t in tensors:
+        by_type[t["dtype"]] = by_type.get(t["dtype"], 0) + t["bytes"]
+    if a.json:
+        out = dict(folder=a.model, architecture=config.architecture, config=config.to_dict(), summary=config.summary(),
+                   tensor_count=len(tensors), tensor_bytes=total, bytes_by_dtype=by_type, loadable=problem is None,
+                   problem=problem)
+        if a.tensors:
+            out["tensors"] = tensors
+        print(json.dumps(out))
+        return 0 if problem is None else 1
+    print(f"folder    {a.model}")
+    print(f"model     {config.summary()}")
+    print(f"tensors   {len(tensors)}, {_human_bytes(total)} (" +
+          ", ".join(f"{k} {_human_bytes(v)}" for k, v in sorted(by_type.items())) + ")")
+    print("weights   " + ("every tensor the architecture wants is there, with the right shape" if problem is None
+                          else "NOT loadable:"))
+    if problem is not None:
+        print(problem)
+    if a.tensors:
+        width = max((len(t["name"]) for t in tensors), default=4)
+        for t in tensors:
+            print(f"  {t['name']:<{width}}  {t['dtype']:<9} {str(t['shape']):<20} {_human_bytes(t['bytes'])}")
+    return 0 if problem is None else 1
 
 
 def cmd_selftest(a) -> int:

@@ -240,3 +240,41 @@ def test_sharded_folder(tmp_path):
     assert sorted(f.names()) == ["a", "b"]
     assert torch.equal(f.read("b"), torch.arange(3, dtype=torch.int64))
     f.close()
+
+
+def test_inspect_subcommand_describes_a_folder_and_says_whether_it_loads(tmp_path, capsys):
+    """``airun inspect`` (options of crates/airun-cli/src/inspect.rs:10-36) needs no GPU."""
+    from airun_b200.cli import main
+    cfg, m = _model("B")
+    good = str(tmp_path / "good")
+    write_model_folder(good, cfg, m.weight_specs(), seed=4)
+    assert main(["inspect", good]) == 0
+    out = capsys.readouterr().out
+    assert "Qwen3ForCausalLM" in out and "every tensor the architecture wants is there" in out
+    assert main(["inspect", good, "--tensors", "--json"]) == 0
+    rep = json.loads(capsys.readouterr().out)
+    want = random_tensors(m.weight_specs(), 4)
+    assert rep["loadable"] and rep["tensor_count"] == len(want) and rep["config"]["hidden_size"] == cfg.hidden_size
+    assert {t["name"]: tuple(t["shape"]) for t in rep["tensors"]} == {n: tuple(t.shape) for n, t in want.items()}
+    assert rep["tensor_bytes"] == sum(t.numel() * t.element_size() for t in want.values())
+    assert main(["inspect", good, "--values", "model.norm.weight", "--count", "3"]) == 0
+    out = capsys.readouterr().out
+    first = [float(x) for x in out.splitlines()[1].split(":")[1].split()]
+    assert first == pytest.approx(want["model.norm.weight"][:3].tolist(), rel=1e-5) and "std" in out
+    with pytest.raises(SystemExit):
+        main(["inspect", good, "--values", "nobody"])
+    # a folder that cannot be loaded: one tensor gone, one too many, one of the wrong shape
+    bad = str(tmp_path / "bad")
+    os.makedirs(bad)
+    with open(os.path.join(bad, "config.json"), "w") as f:
+        json.dump(cfg.to_dict(), f)
+    t = dict(want)
+    del t["model.layers.1.mlp.up_proj.weight"]
+    t["model.layers.0.extra.weight"] = torch.zeros(3)
+    t["model.norm.weight"] = torch.ones(5)
+    write_safetensors(os.path.join(bad, "model.safetensors"), t)
+    assert main(["inspect", bad]) == 1
+    out = capsys.readouterr().out
+    assert "NOT loadable" in out
+    for frag in ("model.layers.1.mlp.up_proj.weight", "model.layers.0.extra.weight", "model.norm.weight"):
+        assert frag in out
