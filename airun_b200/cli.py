@@ -110,6 +110,9 @@ def build_parser() -> argparse.ArgumentParser:
     ins.add_argument("--values", metavar="TENSOR", help="print a tensor's first values and summary statistics")
     ins.add_argument("--count", type=int, default=16, help="how many values --values prints")
 
+    gp = sub.add_parser("gpu", help="the CUDA devices the engine can see and whether it can run on them")
+    gp.add_argument("--json", action="store_true", help="machine-readable JSON instead of a report")
+
     st = sub.add_parser("selftest", help="every kernel against a plain reference of the same operation")
     st.add_argument("--device", type=int, default=0)
     st.add_argument("--verbose", action="store_true")
@@ -426,6 +429,42 @@ def cmd_inspect(a) -> int:
     return 0 if problem is None else 1
 
 
+def cmd_gpu(a) -> int:
+    """The reference's ``airun gpu`` (crates/airun-cli/src/gpu.rs:8-95): the CUDA devices in CUDA's own
+    order, their architecture, memory and size, and whether this engine runs on them (its kernels
+    are built for sm_100a only).  It reads; it changes no setting of any device."""
+    import torch
+    devices = []
+    n = torch.cuda.device_count() if torch.cuda.is_available() else 0
+    for i in range(n):
+        pr = torch.cuda.get_device_properties(i)
+        try:
+            free, total = torch.cuda.mem_get_info(i)
+        except RuntimeError:
+            free, total = 0, int(pr.total_memory)
+        devices.append(dict(ordinal=i, name=pr.name, compute_capability=f"{pr.major}.{pr.minor}",
+                            supported=(pr.major, pr.minor) == (10, 0), free_bytes=int(free), total_bytes=int(total),
+                            sm_count=int(pr.multi_processor_count),
+                            threads_per_sm=int(getattr(pr, "max_threads_per_multi_processor", 0)),
+                            l2_bytes=int(getattr(pr, "L2_cache_size", 0))))
+    if a.json:
+        print(json.dumps(dict(cuda_runtime=torch.version.cuda, devices=devices)))
+        return 0
+    print(f"CUDA runtime {torch.version.cuda} (the one PyTorch was built with)")
+    if not devices:
+        print("\nNo CUDA device found.")
+        print("  - Check that an NVIDIA GPU is present and `nvidia-smi` works.")
+        print("  - airun_b200 has no CPU path: it needs a B200 (sm_100a).")
+        return 0
+    print(f"\n{len(devices)} CUDA device(s). Ordinals below are CUDA's, which need not match nvidia-smi's order.\n")
+    for d in devices:
+        print(f"GPU {d['ordinal']} - {d['name']}" + ("" if d["supported"] else "  [UNSUPPORTED: the kernels are built for sm_100a]"))
+        print(f"  arch          compute {d['compute_capability']}")
+        print(f"  memory        {_human_bytes(d['free_bytes'])} free of {_human_bytes(d['total_bytes'])}")
+        print(f"  compute       {d['sm_count']} SMs, {d['threads_per_sm']} threads/SM, {_human_bytes(d['l2_bytes'])} L2")
+    return 0
+
+
 def cmd_selftest(a) -> int:
     """The reference's ``airun selftest --device N --verbose`` (crates/airun-cli/src/selftest.rs:13-22)."""
     from . import selftest
@@ -435,7 +474,7 @@ def cmd_selftest(a) -> int:
 def main(argv: Optional[List[str]] = None) -> int:
     a = build_parser().parse_args(argv)
     return {"run": cmd_run, "bench": cmd_bench, "perplexity": cmd_perplexity, "init": cmd_init,
-            "inspect": cmd_inspect, "selftest": cmd_selftest}[a.cmd](a)
+            "inspect": cmd_inspect, "gpu": cmd_gpu, "selftest": cmd_selftest}[a.cmd](a)
 
 
 if __name__ == "__main__":

@@ -278,3 +278,24 @@ def test_inspect_subcommand_describes_a_folder_and_says_whether_it_loads(tmp_pat
     assert "NOT loadable" in out
     for frag in ("model.layers.1.mlp.up_proj.weight", "model.layers.0.extra.weight", "model.norm.weight"):
         assert frag in out
+
+
+def test_gpu_subcommand_with_and_without_devices(monkeypatch, capsys):
+    """``airun gpu`` (crates/airun-cli/src/gpu.rs:8-95) against a stand-in for the CUDA runtime."""
+    from types import SimpleNamespace
+    from airun_b200.cli import main
+    monkeypatch.setattr(torch.cuda, "is_available", lambda: False)
+    assert main(["gpu"]) == 0 and "No CUDA device found" in capsys.readouterr().out
+    props = [SimpleNamespace(name="NVIDIA B200", major=10, minor=0, total_memory=192 << 30, multi_processor_count=148,
+                             max_threads_per_multi_processor=2048, L2_cache_size=126 << 20),
+             SimpleNamespace(name="Something older", major=9, minor=0, total_memory=80 << 30, multi_processor_count=132)]
+    monkeypatch.setattr(torch.cuda, "is_available", lambda: True)
+    monkeypatch.setattr(torch.cuda, "device_count", lambda: 2)
+    monkeypatch.setattr(torch.cuda, "get_device_properties", lambda i: props[i])
+    monkeypatch.setattr(torch.cuda, "mem_get_info", lambda i: (100 << 30, props[i].total_memory))
+    assert main(["gpu"]) == 0
+    out = capsys.readouterr().out
+    assert "GPU 0 - NVIDIA B200\n" in out and "148 SMs" in out and "UNSUPPORTED" in out.split("GPU 1")[1]
+    assert main(["gpu", "--json"]) == 0
+    rep = json.loads(capsys.readouterr().out)
+    assert [d["supported"] for d in rep["devices"]] == [True, False] and rep["devices"][0]["l2_bytes"] == 126 << 20
