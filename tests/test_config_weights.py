@@ -32,6 +32,18 @@ def test_8b_shape_cache_bytes():
     assert c.attn_scale == 128 ** -0.5
 
 
+def test_1_7b_shape_matches_the_reference_config_tests():
+    """crates/airun-core/src/config.rs:977-991: q_dim 2048, kv_dim 1024, two query heads per KV head,
+    16 MiB of 16-bit keys and values per layer at 4,096 tokens, 28 layers."""
+    c = Qwen3Config.from_dict(dict(architectures=["Qwen3ForCausalLM"], vocab_size=151936, hidden_size=2048,
+                                   num_hidden_layers=28, num_attention_heads=16, num_key_value_heads=8,
+                                   head_dim=128, intermediate_size=6144, tie_word_embeddings=True))
+    assert (c.q_dim, c.kv_dim, c.gqa_ratio) == (2048, 1024, 2)
+    assert c.kv_bytes_per_token(2) * 4096 == 28 * 16 * 1024 * 1024
+    with pytest.raises(ConfigError):                                     # config.rs:994-1006: 5 KV heads do not divide 16
+        Qwen3Config.from_dict(dict(c.to_dict(), num_key_value_heads=5))
+
+
 def test_missing_keys_are_all_named():
     with pytest.raises(ConfigError) as e:
         Qwen3Config.from_dict(dict(architectures=["Qwen3ForCausalLM"], hidden_size=64))
