@@ -72,6 +72,7 @@ class GenerationResult:
     token_ids: List[int]
     finish_reason: str
     prompt_tokens: int
+    logprobs: Optional[list] = None          # TokenProbs per sampled token when SamplingParams.logprobs is set
 
 
 class Engine:
@@ -326,6 +327,7 @@ class Engine:
         self.stats.prefill_ms = (t_first - t0) * 1e3
         self.stats.decode_ms = (t1 - t_first) * 1e3
         self.stats.generated_tokens = sum(len(r.output) for r in reqs)
-        res = [GenerationResult(list(r.output), (r.finished or FinishReason.CANCELLED).value, len(r.prompt))
+        res = [GenerationResult(list(r.output), (r.finished or FinishReason.CANCELLED).value, len(r.prompt),
+                                list(r.sampler.probs) if r.params.logprobs is not None else None)
                for r in reqs]
         return res[0] if single else res

@@ -59,6 +59,9 @@ class SamplingParams:
     mirostat: int = 0               # 1 or 2; 0 disables
     mirostat_tau: float = 5.0
     mirostat_eta: float = 0.1
+    # None: off.  n >= 0: record every sampled token's log-probability under the raw logits and the n
+    # likeliest alternatives (the reference's with_probs, sample.rs:128-140, :280-284).
+    logprobs: Optional[int] = None
 
     @classmethod
     def greedy(cls) -> "SamplingParams":
@@ -83,7 +86,7 @@ class SamplingParams:
     @property
     def is_pure_greedy(self) -> bool:
         return (self.temperature <= 0.0 and not self.logit_bias and not self.penalizing
-                and self.dry_multiplier <= 0.0)
+                and self.dry_multiplier <= 0.0 and self.logprobs is None)
 
     @property
     def device_ok(self) -> bool:
@@ -92,7 +95,30 @@ class SamplingParams:
             return True
         return (self.temperature > 0.0 and not self.changes_logits and self.top_k == 0
                 and self.top_p >= 1.0 and self.min_p <= 0.0 and self.typical_p >= 1.0
-                and self.dynatemp_range <= 0.0 and self.xtc_probability <= 0.0 and self.mirostat == 0)
+                and self.dynatemp_range <= 0.0 and self.xtc_probability <= 0.0 and self.mirostat == 0
+                and self.logprobs is None)
+
+
+@dataclass
+class TokenProbs:
+    """One sampled token's log-probability under softmax(raw logits), before any sampler touched
+    them, and the likeliest alternatives, the best first (sample.rs:128-137, :489-503)."""
+    token: int
+    logprob: float
+    top: List[Tuple[int, float]]
+
+
+def token_probs(logits: np.ndarray, token: int, n: int) -> TokenProbs:
+    clean = np.where(np.isnan(logits), -np.inf, logits).astype(np.float32, copy=False)
+    mx = np.float32(clean.max())
+    lse = np.float32(mx + np.float32(math.log(float(np.exp((clean - mx).astype(np.float64)).sum()))))
+    n = min(max(int(n), 0), clean.shape[0])
+    top: List[Tuple[int, float]] = []
+    if n > 0:
+        ids, vals = largest_logits(clean, n)
+        top = [(int(i), float(np.float32(v - lse))) for i, v in zip(ids, vals)]
+    logprob = float(np.float32(clean[token] - lse)) if 0 <= token < clean.shape[0] else float("-inf")
+    return TokenProbs(int(token), logprob, top)
 
 
 class XorShift64:
@@ -196,6 +222,7 @@ class Sampler:
         self.params = params
         self.rng = XorShift64(params.seed)
         self.mu = 2.0 * params.mirostat_tau           # sample.rs:259-262
+        self.probs: List[TokenProbs] = []             # one per sampled token when params.logprobs is set
 
     def _draw(self, ids: np.ndarray, probs: np.ndarray) -> int:
         """Index into ``ids`` / ``probs`` (descending) of the inverse-CDF draw (sample.rs:478-485)."""
@@ -363,6 +390,7 @@ def sample_rows(samplers: Sequence["Sampler"], rows: np.ndarray, histories: Sequ
     ``samplers[r]`` with the tokens of its request so far, ``histories[r]``.  The rows whose chain
     reaches the candidates share one native top-k call."""
     out: List[Optional[int]] = []
+    raw = {r: rows[r].copy() for r, s in enumerate(samplers) if s.params.logprobs is not None}
     for s, row, h in zip(samplers, rows, histories):
         out.append(s._before_candidates(row, h))
     V = rows.shape[1]
@@ -377,6 +405,8 @@ def sample_rows(samplers: Sequence["Sampler"], rows: np.ndarray, histories: Sequ
         if out[r] is None:
             ids, vals = largest_logits(rows[r], samplers[r].candidate_count(V))
             out[r] = samplers[r]._from_candidates(ids, vals)
+    for r, before in raw.items():
+        samplers[r].probs.append(token_probs(before, int(out[r]), samplers[r].params.logprobs))
     return [int(t) for t in out]
 
 

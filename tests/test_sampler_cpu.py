@@ -319,3 +319,35 @@ def test_rows_sampled_together_get_what_they_get_alone():
         want = [s.sample(np.roll(base[r], step).copy(), hist[r]) for r, s in enumerate(alone)]
         assert got == want
         assert got[1] == int(np.argmax(np.roll(base[1], step)))
+
+
+def test_token_log_probabilities_come_from_the_raw_logits():
+    """The reference's with_probs (crates/airun-core/src/sample.rs:128-140, :489-503): the sampled token's
+    log-probability under softmax of the logits before bias, penalties or filters, and the n best."""
+    from airun_b200.sampling.sampler import sample_rows, token_probs
+    rng = np.random.default_rng(3)
+    logits = (rng.normal(size=300) * 4).astype(np.float32)
+    logits[5] = np.nan
+    want = np.where(np.isnan(logits), -np.inf, logits).astype(np.float64)
+    want = want - (want.max() + np.log(np.exp(want - want.max()).sum()))
+    tp = token_probs(logits, 17, 4)
+    assert tp.token == 17 and tp.logprob == pytest.approx(want[17], abs=1e-5)
+    order = np.argsort(-want)[:4]
+    assert [i for i, _ in tp.top] == order.tolist() and [l for _, l in tp.top] == pytest.approx(want[order].tolist(), abs=1e-5)
+    assert token_probs(logits, 17, 0).top == [] and token_probs(logits, 5, 1).logprob == float("-inf")
+    # in the chain: recorded per sampled token, from the logits as they came, not as the penalties left them
+    p = SamplingParams(seed=2, repeat_penalty=5.0, logprobs=2)
+    q = SamplingParams.greedy()
+    q.logprobs = 0
+    assert not p.device_ok and not q.device_ok and not q.is_pure_greedy and SamplingParams.greedy().device_ok
+    sp, sq, plain = Sampler(p), Sampler(q), Sampler(SamplingParams(seed=2, repeat_penalty=5.0))
+    hist = [int(np.argmax(want))] * 3
+    for step in range(5):
+        rows = np.stack([np.roll(logits, step), np.roll(logits, step)])
+        toks = sample_rows([sp, sq], rows, [hist, hist])
+        assert toks[0] == plain.sample(np.roll(logits, step).copy(), hist)       # recording changes no draw
+        w = np.roll(want, step)
+        assert sp.probs[step].token == toks[0] and sp.probs[step].logprob == pytest.approx(w[toks[0]], abs=1e-5)
+        assert len(sp.probs[step].top) == 2 and sp.probs[step].top[0][0] == int(np.argmax(w))
+        assert sq.probs[step].token == toks[1] == int(np.argmax(w)) and sq.probs[step].top == []
+    assert len(sp.probs) == len(sq.probs) == 5 and plain.probs == []
