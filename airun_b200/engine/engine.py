@@ -178,6 +178,19 @@ class Engine:
         self.storage.run_copies(self.scheduler.fork(parent, child))
         return child
 
+    def cancel(self, req: Request) -> None:
+        """Ends ``req`` with ``Cancelled`` at the next step's planning (its pages are given back then);
+        a request that is still waiting never starts."""
+        req.cancelled = True
+
+    def clear_prefix_cache(self) -> int:
+        """Gives back the pages of every kept cache (``EngineOptions.prefix_cache``); returns how many
+        caches were dropped."""
+        n = 0
+        while self.scheduler._drop_kept():
+            n += 1
+        return n
+
     def has_work(self) -> bool:
         return self.scheduler.has_work()
 
