@@ -368,3 +368,30 @@ def test_turns_of_a_conversation_in_a_pool_that_is_almost_full(ps, pages):
     while s._drop_kept():
         pass
     assert not m.requests and m.free_pages()[0] == pages
+
+
+# ----------------------------------------------------------------------------- the product's tile plan (host arithmetic)
+def test_product_plan_takes_every_shape_and_stays_within_the_kernel_limits():
+    """``plan_gemm`` decides (swapped, tile width, K slices) on the host; whatever the sizes, its answer
+    must be one the kernel's entry point accepts: a tile width it is built for, at least one slice and
+    no more than there are 64-wide K blocks, and for split products few enough CTAs to be resident at once."""
+    import random
+    from airun_b200.kernels.fast import SPLIT_CTAS, STREAM_CTAS, plan_gemm
+    rnd = random.Random(0)
+    shapes = [(1, 4096, 4096), (8, 6144, 4096), (8, 24576, 4096), (8, 4096, 12288), (64, 4096, 12288), (17, 4096, 4096),
+              (2048, 6144, 4096), (2048, 24576, 4096), (129, 256, 64), (300, 100, 8), (1, 151936, 4096), (128, 151936, 4096)]
+    shapes += [(rnd.randrange(1, 3000), rnd.randrange(1, 40000), 8 * rnd.randrange(1, 2000)) for _ in range(2000)]
+    for M, N, K in shapes:
+        swap, bn, ks = plan_gemm(M, N, K)
+        kb = (K + 63) // 64
+        assert ks >= 1 and ks <= max(kb, 1), (M, N, K, ks)
+        if swap:
+            assert M <= 128 and bn in (16, 32, 64, 128) and bn >= min(M, 128)
+            tiles = (N + 127) // 128
+            if ks > 1:
+                assert tiles * ks <= (STREAM_CTAS if M <= 16 else SPLIT_CTAS) and (M <= 16 or ks <= 8)
+        else:
+            assert M > 128 and bn in (128, 256)
+            if ks > 1:
+                assert ((M + 127) // 128) * ((N + bn - 1) // bn) * ks <= 148
+    assert plan_gemm(8, 24576, 4096) == (True, 16, 1) and plan_gemm(2048, 24576, 4096) == (False, 256, 1)
