@@ -330,3 +330,100 @@ def test_can_rewind_only_without_windows_and_state():
     assert manager([FULL, FULL]).can_rewind
     assert not manager([FULL, WIN]).can_rewind
     assert not manager([FULL, StateSpec((3,))]).can_rewind
+
+
+@pytest.mark.parametrize("seed", [0, 1, 2, 3])
+def test_batch_layout_of_random_steps(seed):
+    """The native core lays a step's batch into the staging buffer (tokens, positions, owner of every
+    row, wanted rows, row offsets, context lengths, slots, one block table per group, the shared
+    prefix); every word is checked against the plain meaning of the batch, with and without padding."""
+    import ctypes
+    import numpy as np
+    rnd = random.Random(seed)
+    page, R_max, T_max, pages = 4, 6, 64, 60
+    m = CacheManager([FULL, WIN, FULL], [None, None, None], page, pages, R_max, max_blocks=24)
+    n_groups = len(m.paged)
+    sizes = [T_max, T_max, T_max, T_max, R_max + 1, R_max, R_max] + [R_max * m.max_blocks] * n_groups + [1] * n_groups
+    offs, total = [], 0
+    for n in sizes:
+        offs.append(total)
+        total += (n + 63) // 64 * 64
+    buf = np.full(total, -777, dtype=np.int32)
+    c_offs = (ctypes.c_longlong * len(offs))(*offs)
+    held = {}                                               # rid -> tokens so far
+    for step in range(60):
+        # a few requests come, go, or are forked; then a batch of some of the live ones
+        if len(held) < R_max and (not held or rnd.random() < 0.4):
+            rid = ("r", step)
+            m.add_request(rid)
+            held[rid] = 0
+        if held and rnd.random() < 0.15:
+            rid = rnd.choice(list(held))
+            m.free_request(rid)
+            del held[rid]
+            continue
+        forked = None
+        if held and len(held) < R_max and rnd.random() < 0.3:
+            par = rnd.choice(list(held))
+            try:
+                m.fork(par, ("f", step))
+                held[("f", step)] = held[par]
+                forked = [par, ("f", step)]
+            except OutOfPages:
+                pass
+        rids = forked if forked and rnd.random() < 0.7 else rnd.sample(list(held), rnd.randrange(1, len(held) + 1))
+        decode = rnd.random() < 0.5 or rids is forked
+        qlens = [1 if decode else rnd.randrange(1, 9) for _ in rids]
+        qlens = [min(q, 90 - held[r]) for q, r in zip(qlens, rids)]
+        rids, qlens = [r for r, q in zip(rids, qlens) if q > 0], [q for q in qlens if q > 0]
+        if not rids or sum(qlens) > T_max:
+            continue
+        try:
+            m.reserve_many(rids, qlens)
+        except OutOfPages:
+            continue
+        toks = np.array([rnd.randrange(1000) for _ in range(sum(qlens))], dtype=np.int32)
+        wants = [sorted(rnd.sample(range(q), rnd.randrange(0, q + 1))) for q in qlens]
+        pad_to = rnd.choice([0, 0, T_max]) if sum(qlens) <= T_max else 0
+        n_want = sum(len(w) for w in wants)
+        pad_want = n_want + rnd.randrange(0, 3) if pad_to else 0
+        buf[:] = -777
+        t, nw, max_ctx, max_q, slots, shared = m.build_batch(
+            rids, qlens, toks, [len(w) for w in wants], [x for w in wants for x in w], buf.ctypes.data, c_offs,
+            R_max, m.max_blocks, pad_to, pad_want)
+        T = sum(qlens)
+        assert (t, nw, max_q) == (T, n_want, max(qlens)) and max_ctx == max(held[r] + q for r, q in zip(rids, qlens))
+        assert slots == [m.get(r).slot for r in rids]
+        tok, pos, owner, wr, cu, cl, sl = (buf[o:o + n] for o, n in zip(offs[:7], sizes[:7]))
+        assert tok[:T].tolist() == toks.tolist()
+        row = 0
+        for i, (r, q) in enumerate(zip(rids, qlens)):
+            assert cu[i] == row and cl[i] == held[r] + q and sl[i] == slots[i]
+            assert pos[row:row + q].tolist() == list(range(held[r], held[r] + q)) and set(owner[row:row + q]) == {i}
+            row += q
+        assert cu[len(rids)] == T
+        assert wr[:n_want].tolist() == [c + x for c, w in zip(np.cumsum([0] + qlens[:-1]).tolist(), wants) for x in w]
+        if pad_to:
+            assert set(pos[T:pad_to].tolist()) <= {-1} and set(owner[T:pad_to].tolist()) <= {-1}
+            assert set(cu[len(rids):R_max + 1].tolist()) == {T} and set(wr[n_want:pad_want].tolist()) <= {0}
+        for g in m.paged:
+            bt = buf[offs[7 + g.gid]:offs[7 + g.gid] + R_max * m.max_blocks].reshape(R_max, m.max_blocks)
+            for i, (r, q) in enumerate(zip(rids, qlens)):
+                blocks = m.block_table(r, g.gid)
+                need = -(-(held[r] + q) // page)
+                assert bt[i, :need].tolist() == blocks[:need]
+                first_key = max(0, held[r] + q - 1 - (g.window - 1)) if g.window else 0     # oldest key the newest token sees
+                assert all(b >= 0 for b in blocks[first_key // page:need])
+            # the shared prefix: whole pages at the start that every request of a decode batch holds alike
+            want_shared = 0
+            if len(rids) >= 2 and max(qlens) == 1 and g.window == 0:
+                tables = [m.block_table(r, g.gid) for r in rids]
+                limit = min(held[r] // page for r in rids)
+                while want_shared < limit and len({tb[want_shared] for tb in tables}) == 1:
+                    want_shared += 1
+                want_shared *= page
+            assert shared[g.gid] == want_shared == buf[offs[7 + n_groups + g.gid]]
+        m.commit_many(rids, qlens)
+        for r, q in zip(rids, qlens):
+            held[r] += q
+        m.check_invariants()
