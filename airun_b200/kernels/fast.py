@@ -3,6 +3,12 @@
 Each ``*_bf16`` function returns True when a fast kernel took the call and False
 when the sizes are outside what the fast kernels accept, in which case the
 caller runs the plain kernel.  ``gemm_tcgen05`` is the raw entry.
+
+The reference chooses between its kernels the same way, by operand type and row
+count, in one place (``matvec``, crates/airun-core/src/runtime.rs:5531-5625: the
+half-precision matvec for a few rows, the wmma product for many; its attention
+runs the flash kernel from 16 tokens on and the plain or split kernels below,
+crates/airun-cuda/kernels/ops.cu:2130-2142, crates/airun-cuda/src/ops.rs:1207-1318).
 """
 from __future__ import annotations
 

@@ -4,6 +4,10 @@ Each function checks shapes, types and contiguity, refuses what its kernel does
 not take with a clear error, and launches on torch's current CUDA stream through
 the library's C entry point.  Nothing here computes on the CPU and nothing falls
 back to a library routine: a missing or failing extension raises.
+
+The reference has the same layer: safe wrappers that check sizes before they hand
+raw pointers to ``extern "C"`` launchers (crates/airun-cuda/src/ops.rs:1-6, :290-330;
+the launchers at crates/airun-cuda/kernels/ops.cu:2222-2578).
 """
 from __future__ import annotations
 

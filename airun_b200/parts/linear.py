@@ -3,7 +3,9 @@
 ``linear`` picks the kernel by operand type and shape: float32 operands always
 run on the CUDA cores with float32 accumulation (the true 32-bit path);
 bfloat16 operands use the tensor-core kernels where one takes the sizes, and the
-plain CUDA-core kernel otherwise.  Both accumulate in float32.
+plain CUDA-core kernel otherwise.  Both accumulate in float32.  Every projection is
+y = W x over row-major rows of length K, without a bias, as in the reference
+(crates/airun-cuda/src/ops.rs:290-293; crates/airun-core/src/model.rs:906-912).
 """
 from __future__ import annotations
 
