@@ -148,16 +148,20 @@ def first_argmax(logits: np.ndarray) -> int:
 
 def apply_penalties(logits: np.ndarray, history: Sequence[int], last_n: int, repeat: float,
                     presence: float, frequency: float) -> None:
-    window = list(history)[max(0, len(history) - last_n):]
-    counts = {}
-    for t in window:
-        if 0 <= t < logits.shape[0]:
-            counts[t] = counts.get(t, 0) + 1
-    for t, c in counts.items():
-        l = float(logits[t])
-        if repeat != 1.0:
-            l = l / repeat if l > 0.0 else l * repeat
-        logits[t] = np.float32(l - (c * frequency + presence))
+    """Repetition, presence and frequency penalties over the last ``last_n`` tokens, once per distinct
+    token however often it occurs (sample.rs:651-705): a positive logit is divided by ``repeat``, a
+    negative one multiplied; then ``count * frequency + presence`` is taken off."""
+    n = len(history)
+    window = np.asarray(history[max(0, n - last_n):] if last_n > 0 else [], dtype=np.int64)
+    if window.size == 0:
+        return
+    ids, counts = np.unique(window, return_counts=True)
+    inside = (ids >= 0) & (ids < logits.shape[0])
+    ids, counts = ids[inside], counts[inside]
+    l = logits[ids].astype(np.float64)
+    if repeat != 1.0:
+        l = np.where(l > 0.0, l / repeat, l * repeat)
+    logits[ids] = (l - (counts * frequency + presence)).astype(np.float32)
 
 
 def apply_top_n_sigma(logits: np.ndarray, n: float) -> None:
