@@ -46,7 +46,7 @@ def find_nvcc() -> str:
                      "(set CUDA_HOME or AIRUN_NVCC)")
 
 
-HOST_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden", "-Wall", "-pthread"]
+HOST_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden", "-Wall", "-pthread", "-ffp-contract=off"]
 
 
 def find_cxx() -> str:

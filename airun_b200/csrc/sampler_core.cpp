@@ -84,3 +84,125 @@ HOST_EXPORT int airun_topk_rows(const float* x, long long ld, int n_rows, long l
     for (std::thread& t : pool) t.join();
     return 0;
 }
+
+// ---------------------------------------------------------------------------------------------------
+// The usual chain in one call: bias -> penalties -> top-k -> softmax at a fixed temperature -> min-p ->
+// top-p -> draw, for the rows whose parameters ask for nothing else (sampling/sampler.py decides; DRY,
+// top-n-sigma, typical, XTC, dynamic temperature, mirostat and log-probabilities stay with the Python
+// chain, which is also this one's plain twin in the tests).  Every step keeps the arithmetic of that
+// twin: float32 where it is float32, double where it is double, sums one after the other, so the two
+// pick the same token from the same logits and generator state.  Order and formulas as the reference's
+// sampler (crates/airun-core/src/sample.rs:348-486, penalties :651-705, generator :778-798).
+struct ChainParams {
+    double temperature, top_p, min_p, repeat, presence, frequency;
+    int top_k, penalize;                 // penalize: the three penalties are on
+    int n_bias;
+    const int* bias_ids;
+    const float* bias_vals;
+};
+
+struct ChainRow {
+    float* logits;                       // [vocab], modified in place
+    const long long* window;             // the last repeat_last_n tokens of the request
+    long long n_window;
+    const ChainParams* params;
+    unsigned long long* rng_state;       // xorshift64 state, advanced by the draw
+    int out;                             // the token picked
+};
+
+namespace {
+
+inline double next_uniform(unsigned long long* state) {       // (x >> 40) / 2^24
+    unsigned long long x = *state;
+    x ^= x << 13;
+    x ^= x >> 7;
+    x ^= x << 17;
+    *state = x;
+    return (double)(x >> 40) / 16777216.0;
+}
+
+void chain_row(ChainRow& row, long long vocab) {
+    const ChainParams& p = *row.params;
+    float* logits = row.logits;
+    for (int b = 0; b < p.n_bias; ++b)
+        if (p.bias_ids[b] >= 0 && p.bias_ids[b] < vocab) logits[p.bias_ids[b]] += p.bias_vals[b];
+    if (p.penalize && row.n_window > 0) {
+        // once per distinct token: sorted copy of the window, runs of equal ids give the counts
+        std::vector<long long> w(row.window, row.window + row.n_window);
+        std::sort(w.begin(), w.end());
+        for (size_t i = 0; i < w.size();) {
+            size_t j = i;
+            while (j < w.size() && w[j] == w[i]) ++j;
+            const long long t = w[i];
+            if (t >= 0 && t < vocab) {
+                double l = (double)logits[t];
+                if (p.repeat != 1.0) l = l > 0.0 ? l / p.repeat : l * p.repeat;
+                logits[t] = (float)(l - ((double)(j - i) * p.frequency + p.presence));
+            }
+            i = j;
+        }
+    }
+    long long keep = p.top_k > 0 ? std::min<long long>(std::max(p.top_k, 1), vocab) : vocab;
+    std::vector<int> ids((size_t)keep);
+    std::vector<float> probs((size_t)keep);
+    topk_row(logits, vocab, (int)keep, ids.data(), probs.data());          // probs holds the logits for now
+    const float mx = probs[0];
+    const float temperature = (float)p.temperature;
+    size_t n = (size_t)keep;
+    float sum = 0.0f;
+    for (size_t i = 0; i < n; ++i) {
+        const float scaled = (probs[i] - mx) / temperature;
+        probs[i] = (float)std::exp((double)scaled);
+        sum += probs[i];
+    }
+    for (size_t i = 0; i < n; ++i) probs[i] = probs[i] / sum;
+    if (p.min_p > 0.0) {
+        const float threshold = (float)p.min_p * probs[0];
+        size_t k = 0;
+        for (size_t i = 0; i < n; ++i) k += probs[i] >= threshold;
+        n = std::max<size_t>(k, 1);
+    }
+    if (p.top_p < 1.0) {
+        const float top_p = (float)p.top_p;
+        float cumulative = 0.0f;
+        size_t cut = n;
+        for (size_t i = 0; i < n; ++i) {
+            cumulative += probs[i];
+            if (cumulative >= top_p) { cut = i + 1; break; }                 // the token that crossed the threshold stays
+        }
+        n = std::max<size_t>(cut, 1);
+    }
+    float total = 0.0f;
+    for (size_t i = 0; i < n; ++i) total += probs[i];
+    if (!((double)total > 0.0)) {
+        if (total == total) { row.out = ids[0]; return; }                   // every survivor rounded to zero
+    }
+    double target = next_uniform(row.rng_state) * (double)total;
+    row.out = ids[n - 1];
+    for (size_t i = 0; i < n; ++i) {
+        target -= (double)probs[i];
+        if (target <= 0.0) { row.out = ids[i]; break; }
+    }
+}
+
+}  // namespace
+
+// One token for every row.  Returns 0, or 1 for arguments it cannot take.
+HOST_EXPORT int airun_sample_chain_rows(ChainRow* rows, int n_rows, long long vocab, int max_threads) {
+    if (!rows || n_rows < 0 || vocab <= 0 || vocab > 2147483647LL) return 1;
+    for (int r = 0; r < n_rows; ++r)
+        if (!rows[r].logits || !rows[r].params || !rows[r].rng_state || rows[r].n_window < 0 || !(rows[r].params->temperature > 0.0)) return 1;
+    const int workers = std::max(1, std::min(max_threads, n_rows));
+    if (workers == 1) {
+        for (int r = 0; r < n_rows; ++r) chain_row(rows[r], vocab);
+        return 0;
+    }
+    std::vector<std::thread> pool;
+    pool.reserve((size_t)workers);
+    for (int w = 0; w < workers; ++w)
+        pool.emplace_back([&, w] {
+            for (int r = w; r < n_rows; r += workers) chain_row(rows[r], vocab);
+        });
+    for (std::thread& t : pool) t.join();
+    return 0;
+}

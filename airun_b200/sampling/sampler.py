@@ -24,6 +24,7 @@ this chain.
 """
 from __future__ import annotations
 
+import ctypes
 import math
 import time
 from dataclasses import dataclass
@@ -230,7 +231,7 @@ class Sampler:
 
     def _draw(self, ids: np.ndarray, probs: np.ndarray) -> int:
         """Index into ``ids`` / ``probs`` (descending) of the inverse-CDF draw (sample.rs:478-485)."""
-        total = float(probs.sum(dtype=np.float32))
+        total = float(np.cumsum(probs, dtype=np.float32)[-1])
         target = self.rng.next_f32() * total
         for i, pr in enumerate(probs):
             target -= float(pr)
@@ -269,7 +270,7 @@ class Sampler:
             if keep.shape[0] == 0:
                 keep = order[:1]
         kp = probs[keep]
-        total = float(kp.sum(dtype=np.float32))
+        total = float(np.cumsum(kp, dtype=np.float32)[-1])
         j = self._draw(keep, kp)
         tiny32 = float(np.finfo(np.float32).tiny)
         surprise = -math.log2(max(float(kp[j]) / total, tiny32))
@@ -316,8 +317,9 @@ class Sampler:
         p = self.params
         mx = vals[0]
         temperature = dynamic_temperature(vals, p.temperature, p.dynatemp_range, p.dynatemp_exponent)
-        probs = np.exp(((vals - mx) / np.float32(temperature)).astype(np.float64)).astype(np.float32)
-        s = np.float32(probs.sum(dtype=np.float32))
+        with np.errstate(invalid="ignore"):               # a row of nothing but -inf gives NaN, as in the reference
+            probs = np.exp(((vals - mx) / np.float32(temperature)).astype(np.float64)).astype(np.float32)
+        s = np.cumsum(probs, dtype=np.float32)[-1]        # float32, one after the other (sample.rs:409-418)
         probs = probs / s
         if p.typical_p < 1.0:
             ids, probs = _typical(ids, probs, p.typical_p)
@@ -335,7 +337,7 @@ class Sampler:
             above = int(np.count_nonzero(np.cumprod(probs >= np.float32(p.xtc_threshold))))
             if above >= 2:
                 ids, probs = ids[above - 1:], probs[above - 1:]
-        if float(probs.sum(dtype=np.float32)) <= 0.0:
+        if float(np.cumsum(probs, dtype=np.float32)[-1]) <= 0.0:
             return int(ids[0])
         return int(ids[self._draw(ids, probs)])
 
@@ -389,10 +391,92 @@ def largest_logits_rows(rows: np.ndarray, ks: Sequence[int]) -> List[Tuple[np.nd
     return [(idx[r, :ks[r]], val[r, :ks[r]]) for r in range(R)]
 
 
-def sample_rows(samplers: Sequence["Sampler"], rows: np.ndarray, histories: Sequence[Sequence[int]]) -> List[int]:
+class _ChainParams(ctypes.Structure):           # ChainParams of csrc/sampler_core.cpp
+    _fields_ = [("temperature", ctypes.c_double), ("top_p", ctypes.c_double), ("min_p", ctypes.c_double),
+                ("repeat", ctypes.c_double), ("presence", ctypes.c_double), ("frequency", ctypes.c_double),
+                ("top_k", ctypes.c_int), ("penalize", ctypes.c_int), ("n_bias", ctypes.c_int),
+                ("bias_ids", ctypes.c_void_p), ("bias_vals", ctypes.c_void_p)]
+
+
+class _ChainRow(ctypes.Structure):              # ChainRow of csrc/sampler_core.cpp
+    _fields_ = [("logits", ctypes.c_void_p), ("window", ctypes.c_void_p), ("n_window", ctypes.c_longlong),
+                ("params", ctypes.c_void_p), ("rng_state", ctypes.c_void_p), ("out", ctypes.c_int)]
+
+
+_CHAIN_FN = None
+
+
+def _native_chain():
+    """``airun_sample_chain_rows`` of csrc/sampler_core.cpp."""
+    global _CHAIN_FN
+    if _CHAIN_FN is None:
+        from ..csrc import build
+        f = build.load("sampler_core").airun_sample_chain_rows
+        f.restype = ctypes.c_int
+        f.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_int]
+        _CHAIN_FN = f
+    return _CHAIN_FN
+
+
+def usual_chain(p: SamplingParams, vocab: int) -> bool:
+    """Whether the native chain takes these parameters: bias, penalties, top-k (on, and small enough for
+    the one-pass heap), a fixed temperature, min-p, top-p, and nothing else."""
+    return (p.temperature > 0.0 and 0 < p.top_k < vocab and p.top_k <= NATIVE_TOPK_MAX and p.typical_p >= 1.0
+            and p.top_n_sigma <= 0.0 and p.dry_multiplier <= 0.0 and p.dynatemp_range <= 0.0
+            and p.xtc_probability <= 0.0 and p.mirostat == 0 and p.logprobs is None)
+
+
+def _sample_rows_native(samplers: Sequence["Sampler"], rows: np.ndarray, histories: Sequence[Sequence[int]],
+                        which: Sequence[int]) -> List[int]:
+    """The rows ``which`` through the native chain, side by side on threads; the samplers' generators
+    move on as if the Python chain had drawn."""
+    n, V = len(which), rows.shape[1]
+    c_rows = (_ChainRow * n)()
+    c_params = (_ChainParams * n)()
+    states = np.empty(n, dtype=np.uint64)
+    keep = []                                                     # arrays the structures point into
+    for j, r in enumerate(which):
+        p = samplers[r].params
+        last_n = p.repeat_last_n if p.penalizing else 0
+        h = histories[r]
+        window = np.asarray(h[max(0, len(h) - last_n):] if last_n > 0 else [], dtype=np.int64)
+        bias_ids = np.asarray([t for t, _ in p.logit_bias], dtype=np.int32)
+        bias_vals = np.asarray([b for _, b in p.logit_bias], dtype=np.float32)
+        keep += [window, bias_ids, bias_vals]
+        c_params[j] = _ChainParams(p.temperature, p.top_p, p.min_p, p.repeat_penalty, p.presence_penalty,
+                                   p.frequency_penalty, p.top_k, 1 if p.penalizing else 0, len(p.logit_bias),
+                                   bias_ids.ctypes.data, bias_vals.ctypes.data)
+        states[j] = samplers[r].rng.state
+        c_rows[j] = _ChainRow(rows[r].ctypes.data, window.ctypes.data, window.shape[0],
+                              ctypes.addressof(c_params) + j * ctypes.sizeof(_ChainParams),
+                              states.ctypes.data + 8 * j, -1)
+    if _native_chain()(ctypes.addressof(c_rows), n, V, _TOPK_THREADS) != 0:
+        raise ValueError("the native sampling chain refused its arguments")
+    for j, r in enumerate(which):
+        samplers[r].rng.state = int(states[j])
+    return [int(c_rows[j].out) for j in range(n)]
+
+
+def sample_rows(samplers: Sequence["Sampler"], rows: np.ndarray, histories: Sequence[Sequence[int]],
+                native: bool = True) -> List[int]:
     """One token for every row: ``rows[r]`` (float32 [V], modified in place) goes through the chain of
-    ``samplers[r]`` with the tokens of its request so far, ``histories[r]``.  The rows whose chain
-    reaches the candidates share one native top-k call."""
+    ``samplers[r]`` with the tokens of its request so far, ``histories[r]``.  Rows with the usual
+    parameters (``usual_chain``) run in the native core, all in one call; the others run the chain
+    below, sharing one native top-k call.  ``native=False``: everything in Python (the plain twin)."""
+    V = rows.shape[1]
+    fast = [r for r, s in enumerate(samplers) if usual_chain(s.params, V)] if native else []
+    if fast and rows.dtype == np.float32 and rows.strides[1] == 4:
+        picked = _sample_rows_native(samplers, rows, histories, fast)
+        if len(fast) == len(samplers):
+            return picked
+        rest = [r for r in range(len(samplers)) if r not in set(fast)]
+        others = sample_rows([samplers[r] for r in rest], rows[rest], [histories[r] for r in rest], native=False)
+        out_all: List[int] = [0] * len(samplers)
+        for r, t in zip(fast, picked):
+            out_all[r] = t
+        for r, t in zip(rest, others):
+            out_all[r] = t
+        return out_all
     out: List[Optional[int]] = []
     raw = {r: rows[r].copy() for r, s in enumerate(samplers) if s.params.logprobs is not None}
     for s, row, h in zip(samplers, rows, histories):

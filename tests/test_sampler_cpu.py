@@ -351,3 +351,60 @@ def test_token_log_probabilities_come_from_the_raw_logits():
         assert len(sp.probs[step].top) == 2 and sp.probs[step].top[0][0] == int(np.argmax(w))
         assert sq.probs[step].token == toks[1] == int(np.argmax(w)) and sq.probs[step].top == []
     assert len(sp.probs) == len(sq.probs) == 5 and plain.probs == []
+
+
+# ----------------------------------------------------------------------------- the native usual-case chain
+def _random_params(rng, V):
+    p = SamplingParams(
+        temperature=float(rng.choice([0.05, 0.5, 0.8, 1.0, 2.5])), top_k=int(rng.integers(1, min(V - 1, 60) + 1)),
+        top_p=float(rng.choice([1.0, 0.95, 0.9, 0.5, 0.01])), min_p=float(rng.choice([0.0, 0.05, 0.3, 1.0])),
+        repeat_penalty=float(rng.choice([1.0, 1.1, 1.5])), presence_penalty=float(rng.choice([0.0, 0.4])),
+        frequency_penalty=float(rng.choice([0.0, 0.25])), repeat_last_n=int(rng.choice([0, 5, 64])),
+        seed=int(rng.integers(1, 1 << 40)))
+    if rng.random() < 0.3:
+        p.logit_bias = ((int(rng.integers(0, V)), float(rng.normal() * 3)), (V + 5, 1.0), (int(rng.integers(0, V)), float("-inf")))
+    return p
+
+
+def test_native_chain_picks_what_the_python_chain_picks():
+    """Rows with the usual parameters run in csrc/sampler_core.cpp; the Python chain is its plain twin:
+    same token, same generator state afterwards, same logits left behind, over random parameters,
+    histories (with ids outside the vocabulary), NaN and -inf logits, and equal logits at the cut."""
+    from airun_b200.sampling.sampler import sample_rows, usual_chain
+    rng = np.random.default_rng(21)
+    checked = 0
+    for trial in range(300):
+        V = int(rng.choice([41, 64, 300, 5000]))
+        R = int(rng.integers(1, 7))
+        params = [_random_params(rng, V) for _ in range(R)]
+        assert all(usual_chain(p, V) for p in params)
+        a = [Sampler(p) for p in params]
+        b = [Sampler(SamplingParams(**p.__dict__)) for p in params]
+        hist = [rng.integers(-2, V + 3, size=int(rng.integers(0, 90))).tolist() for _ in range(R)]
+        for step in range(4):
+            rows = (rng.normal(size=(R, V)) * float(rng.choice([0.5, 3.0, 12.0]))).astype(np.float32)
+            if rng.random() < 0.3:
+                rows[0, rng.integers(0, V, size=3)] = np.nan
+            if rng.random() < 0.2:
+                rows[-1, :] = -np.inf
+            if rng.random() < 0.3:
+                rows[0, : V // 2] = np.float32(1.25)                 # many equal logits: ties at the cut
+            ra, rb = rows.copy(), rows.copy()
+            ta = sample_rows(a, ra, hist)
+            tb = sample_rows(b, rb, hist, native=False)
+            assert ta == tb, (trial, step, [p for p in params])
+            assert [s.rng.state for s in a] == [s.rng.state for s in b]
+            assert np.array_equal(ra, rb, equal_nan=True)
+            for r in range(R):
+                hist[r].append(ta[r])
+            checked += R
+    assert checked > 3000
+
+
+def test_native_chain_is_left_to_python_for_everything_else():
+    from airun_b200.sampling.sampler import usual_chain
+    V = 1000
+    assert usual_chain(SamplingParams(), V)
+    for kw in (dict(temperature=0.0), dict(top_k=0), dict(top_k=V), dict(top_k=5000), dict(typical_p=0.9), dict(top_n_sigma=1.0),
+               dict(dry_multiplier=0.5), dict(dynatemp_range=0.2), dict(xtc_probability=0.1), dict(mirostat=2), dict(logprobs=0)):
+        assert not usual_chain(SamplingParams(**kw), V), kw
