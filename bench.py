@@ -13,8 +13,20 @@ host tokens in and out), ``prefill`` a 2,048-token prompt in one step,
 decode rate at batch 1 and 64.  ``--workload serve`` and ``--workload long`` run
 two further workloads end to end (continuous batching of 128 requests on the
 Qwen3-1.7B shape; a 32,768-token prompt on the Qwen3-32B shape) and print a line
-of their own.  ``--impl reference`` reports that the reference
-cannot be installed here.
+of their own.
+
+Every decode point is the median of several repeats of ``--steps`` steps (at least 192 timed steps
+together); between repeats the requests are cut back to where they began, so the contexts stay
+just below ``--context``.  The bytes of the roofline are counted at the contexts that ran.  After
+the timing, one step is run both from its CUDA graph and kernel by kernel and the two sets of
+logits are compared, so the number belongs to a step that computes the right thing.
+
+``--impl reference``: the reference is a Rust workspace and cannot be installed here (no cargo),
+but its CUDA kernels compile unmodified for sm_100.  When ``baseline/_ref`` holds that library
+(``python baseline/reference_kernels.py --build <reference checkout>``) the arm runs the same
+decode step and prefill on the reference's own kernels through their C entry points, in the
+order its runtime calls them, and says so in ``reference_class``; otherwise it prints why it is
+unavailable.
 """
 from __future__ import annotations
 
@@ -60,13 +72,26 @@ class ClockSampler:
     Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self):
-        self.lines, self.proc = [], None
+    def __init__(self, period_ms: int = 50):
+        self.lines, self.proc, self.period_ms = [], None, period_ms
+        self.marks = []                         # (name, first sample index, last sample index)
+
+    def region(self, name):
+        """with sampler.region("b8"): ... remembers which samples fell into the block."""
+        sampler = self
+
+        class _R:
+            def __enter__(self):
+                self.i0 = len(sampler.lines)
+
+            def __exit__(self, *exc):
+                sampler.marks.append((name, self.i0, len(sampler.lines)))
+        return _R()
 
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.Q}",
-                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                          "--format=csv,noheader,nounits", "-lms", str(self.period_ms)],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
@@ -83,21 +108,27 @@ class ClockSampler:
                 self.proc.wait(timeout=5)
             except subprocess.TimeoutExpired:
                 self.proc.kill()
-        sm, mx, reasons = [], 0, set()
-        for l in self.lines:
+        sm, mx, reasons, at = [], 0, set(), {}
+        for i, l in enumerate(self.lines):
             parts = [x.strip() for x in l.split(",")]
             if len(parts) < 6:
                 continue
             try:
                 sm.append(int(parts[0]))
+                at[i] = int(parts[0])
                 mx = max(mx, int(parts[1]))
             except ValueError:
                 continue
             for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[2:6]):
                 if v.lower().startswith("active"):
                     reasons.add(name)
-        return dict(sm_mhz=int(statistics.median(sm)) if sm else None, sm_max_mhz=mx or None,
-                    reasons=sorted(reasons), samples=len(sm))
+        out = dict(sm_mhz=int(statistics.median(sm)) if sm else None, sm_max_mhz=mx or None,
+                   reasons=sorted(reasons), samples=len(sm), period_ms=self.period_ms)
+        for name, i0, i1 in self.marks:
+            got = [at[i] for i in range(i0, i1) if i in at]
+            out[f"sm_mhz_{name}"] = int(statistics.median(got)) if got else None
+            out[f"samples_{name}"] = len(got)
+        return out
 
 
 def decode_bytes(cfg, n_layers, batch, context, esz=2):
@@ -135,70 +166,124 @@ def fill_contexts(eng, rids, context, seed=0):
                               .mul_(0.5).to(pool.dtype))
 
 
-def time_decode(eng, batch, context, steps, warmup, tag):
-    """Device time of ``steps`` decode steps of ``batch`` requests standing at ``context``."""
+def repeats_for(steps: int) -> int:
+    """Repeats of ``steps`` timed steps: three at least, and 192 timed steps together."""
+    return max(3, -(-192 // max(steps, 1)))
+
+
+def time_decode(eng, batch, context, steps, warmup, tag, check=False):
+    """Device time of ``steps`` decode steps of ``batch`` requests whose contexts end just below
+    ``context``: the median of ``repeats_for(steps)`` repeats, each bracketed by CUDA events; the
+    requests are cut back to their first length between repeats.  Returns (ms per step, kernel
+    launches of one repeat, mean context of the timed steps, ms of every repeat)."""
     import torch
     from airun_b200 import StepEntry
     from airun_b200.kernels import ops
     rids = [f"{tag}{i}" for i in range(batch)]
-    fill_contexts(eng, rids, context - steps - warmup - 1)
+    start = context - steps - 1
+    fill_contexts(eng, rids, start)
     V = eng.config.vocab_size
-    toks = torch.randint(0, V, (steps + warmup + 1, batch), generator=torch.Generator().manual_seed(1)).tolist()
+    toks = torch.randint(0, V, (steps + 1, batch), generator=torch.Generator().manual_seed(1)).tolist()
     picked = torch.zeros(batch, dtype=torch.int32, device=eng.device)
 
     def one(i):
         logits = eng.runner.step([StepEntry(r, [toks[i][j]], (0,)) for j, r in enumerate(rids)])
         ops.sample(logits, picked)
+        return logits
+
+    def rewind():
+        for r in rids:
+            eng.manager.truncate(r, start)
 
     for i in range(warmup):
-        one(i)
-    torch.cuda.synchronize()
-    l0 = ops.LAUNCHES[0] + getattr(eng.runner, "graph_launches", 0)
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    ev0.record()
-    for i in range(warmup, warmup + steps):
-        one(i)
-    ev1.record()
-    torch.cuda.synchronize()
-    launches = ops.LAUNCHES[0] + getattr(eng.runner, "graph_launches", 0) - l0
-    ms = ev0.elapsed_time(ev1) / steps
+        if i and i % steps == 0:
+            rewind()
+        one(i % steps)
+    rewind()
+    times, launches = [], 0
+    for _ in range(repeats_for(steps)):
+        torch.cuda.synchronize()
+        l0 = ops.LAUNCHES[0] + getattr(eng.runner, "graph_launches", 0)
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        for i in range(steps):
+            one(i)
+        ev1.record()
+        torch.cuda.synchronize()
+        launches = ops.LAUNCHES[0] + getattr(eng.runner, "graph_launches", 0) - l0
+        times.append(ev0.elapsed_time(ev1) / steps)
+        rewind()
     eng.runner.raise_on_device_error()
+    if check:
+        check_step(eng, rids, toks[0], start)
     for r in rids:
         eng.manager.free_request(r)
-    return ms, launches
+    # contexts of the timed steps: start + 1 .. start + steps keys
+    return statistics.median(times), launches, start + (steps + 1) / 2.0, times
+
+
+def check_step(eng, rids, tokens, start):
+    """The step that was timed, once from its CUDA graph and once kernel by kernel: finite logits,
+    the same picks, the same values up to the rounding of another split of the keys."""
+    import torch
+    from airun_b200 import StepEntry
+    entries = [StepEntry(r, [tokens[j]], (0,)) for j, r in enumerate(rids)]
+    a = eng.runner.step(entries).clone()
+    for r in rids:
+        eng.manager.truncate(r, start)
+    graphs = eng.runner.use_graphs
+    eng.runner.use_graphs = False
+    try:
+        b = eng.runner.step(entries).clone()
+    finally:
+        eng.runner.use_graphs = graphs
+    for r in rids:
+        eng.manager.truncate(r, start)
+    torch.cuda.synchronize()
+    if not (torch.isfinite(a).all() and torch.isfinite(b).all()):
+        raise RuntimeError("the timed decode step gave non-finite logits")
+    scale = float(b.abs().max())
+    err = float((a - b).abs().max())
+    if err > 0.02 * scale:
+        raise RuntimeError(f"the timed decode step differs from its kernel-by-kernel run: {err:.4g} of {scale:.4g}")
+    return err / max(scale, 1e-30)
 
 
 def time_e2e(eng, batch, context, steps, warmup):
     """The same decode through the Python entry point: requests live in the scheduler, every step
-    copies the step's inputs from pinned host memory and reads the sampled tokens back."""
+    copies the step's inputs from pinned host memory and reads the sampled tokens back.  Median of
+    three repeats of ``steps`` steps by the host clock."""
     import torch
     from airun_b200 import SamplingParams
     from airun_b200.engine.scheduler import Request
     rids = [f"e{i}" for i in range(batch)]
-    start = context - steps - warmup - 1
+    reps = 3
+    start = context - reps * steps - warmup - 1
     fill_contexts(eng, rids, start - 1)
     g = torch.Generator().manual_seed(2)
     reqs = []
     for rid in rids:
         prompt = torch.randint(0, eng.config.vocab_size, (start,), generator=g).tolist()
-        r = Request(rid, prompt, SamplingParams.greedy(), steps + warmup + 8)
+        r = Request(rid, prompt, SamplingParams.greedy(), reps * steps + warmup + 8)
         r.num_computed = start - 1                # its cache stands one token short of the prompt
         eng.scheduler.running.append(r)
         reqs.append(r)
     for _ in range(warmup):
         eng.run_step()
-    torch.cuda.synchronize()
-    t0 = time.perf_counter()
-    for _ in range(steps):
-        eng.run_step()
-    torch.cuda.synchronize()
-    ms = (time.perf_counter() - t0) * 1e3 / steps
-    assert all(len(r.output) == steps + warmup for r in reqs), "the entry point did not decode every step"
+    times = []
+    for _ in range(reps):
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            eng.run_step()
+        torch.cuda.synchronize()
+        times.append((time.perf_counter() - t0) * 1e3 / steps)
+    assert all(len(r.output) == reps * steps + warmup for r in reqs), "the entry point did not decode every step"
     for r in reqs:
         eng.scheduler._finish(r, "bench")
     h2d = eng.runner.meta_host.numel() * 4 + eng._small_host.numel() * 4
     d2h = eng._picked_host.numel() * 4
-    return ms, h2d, d2h
+    return statistics.median(times), h2d, d2h
 
 
 def time_prefill(eng, T, runs=3):
@@ -334,6 +419,175 @@ def workload_long(a) -> int:
     return 0
 
 
+REFERENCE_CLASS = "reference kernels through their C ABI; host loop restated, Rust runtime not buildable"
+
+
+def reference_arm(a) -> int:
+    """The same metric on the reference's own CUDA kernels (compiled unmodified for sm_100), called
+    through their C entry points in the order the reference's runtime calls them
+    (baseline/reference_kernels.py).  The decode step is captured into a CUDA graph as the reference
+    captures its own; no scheduler, sampler or host transfer of the reference runs, so there is no
+    end-to-end figure."""
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    try:
+        import reference_kernels as rk
+        if not rk.available():
+            raise FileNotFoundError("baseline/_ref/libairun_ref_kernels.so has not been built")
+        rk.load()
+    except (OSError, ImportError) as e:
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference is a Rust workspace (pip: 'not installable', no cargo or rustc in this image) "
+                          f"and its CUDA kernels are not built here: {e}"}))
+        return 0
+    if a.gpus != 1:
+        print(json.dumps({"impl": "reference", "unavailable": "the reference arm here drives one GPU"}))
+        return 0
+    import torch
+    if not torch.cuda.is_available():
+        print(json.dumps({"impl": "reference", "unavailable": "no GPU is visible to this process"}))
+        return 0
+    a.warmup = max(a.warmup, 3)
+    cfg = dict(QWEN3_8B)
+    if a.layers:
+        cfg["num_hidden_layers"] = a.layers
+    L, H, V = cfg["num_hidden_layers"], cfg["hidden_size"], cfg["vocab_size"]
+    nh, nkv, hd, I = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"], cfg["intermediate_size"]
+    dev = torch.device("cuda:0")
+    g = torch.Generator(device=dev).manual_seed(0)
+
+    def mat(r, c):
+        return (0.02 * torch.randn(r, c, generator=g, device=dev, dtype=torch.float32)).to(torch.bfloat16)
+
+    def vec(n):
+        return 1.0 + 0.1 * torch.randn(n, generator=g, device=dev, dtype=torch.float32)
+
+    W = {"model.embed_tokens.weight": mat(V, H), "model.norm.weight": vec(H), "lm_head.weight": mat(V, H)}
+    for l in range(L):
+        p = f"model.layers.{l}"
+        W.update({f"{p}.input_layernorm.weight": vec(H), f"{p}.post_attention_layernorm.weight": vec(H),
+                  f"{p}.self_attn.q_proj.weight": mat(nh * hd, H), f"{p}.self_attn.k_proj.weight": mat(nkv * hd, H),
+                  f"{p}.self_attn.v_proj.weight": mat(nkv * hd, H), f"{p}.self_attn.o_proj.weight": mat(H, nh * hd),
+                  f"{p}.self_attn.q_norm.weight": vec(hd), f"{p}.self_attn.k_norm.weight": vec(hd),
+                  f"{p}.mlp.gate_proj.weight": mat(I, H), f"{p}.mlp.up_proj.weight": mat(I, H),
+                  f"{p}.mlp.down_proj.weight": mat(H, I)})
+    slots = max(64, a.batch) if not a.skip_points else a.batch
+    dec = rk.ReferenceDecoder(cfg, W, ctx=a.context, slots=slots, max_batch=512, logit_rows=max(64, a.batch))
+    for s_ in range(slots):                          # random keys and values, as in the other arm
+        dec.kc[s_].normal_(0.0, 0.5, generator=g)
+        dec.vc[s_].normal_(0.0, 0.5, generator=g)
+    pk = peaks()
+    sampler = ClockSampler()
+    sampler.start()
+
+    def time_rows(batch, steps):
+        start = a.context - steps - 1
+        rows = list(range(batch))
+        dec.prepare_rows(rows)
+        toks = torch.randint(0, V, (steps + 1, batch), generator=torch.Generator().manual_seed(1)).to(dev, torch.int32)
+        pos = torch.zeros(batch, dtype=torch.int32, device=dev)
+        graph = None
+
+        def one(i):
+            dec.tokens[:batch].copy_(toks[i])
+            dec.positions[:batch].copy_(pos)
+            pos.add_(1)
+            if graph is None:
+                dec.launch_rows()
+            else:
+                graph.replay()
+
+        pos.fill_(start)
+        one(0)                                          # loads and configures every kernel
+        torch.cuda.synchronize()
+        try:
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr):
+                dec.launch_rows()
+            graph = gr
+        except Exception as e:                          # the reference falls back the same way (runtime.rs:3096-3103)
+            print(f"note: the reference arm's decode runs without a CUDA graph: {e}", file=sys.stderr)
+            torch.cuda.synchronize()
+        for i in range(a.warmup):
+            pos.fill_(start + (i % steps))
+            one(i % steps)
+        times = []
+        for _ in range(repeats_for(steps)):
+            pos.fill_(start)
+            torch.cuda.synchronize()
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ev0.record()
+            for i in range(steps):
+                one(i)
+            ev1.record()
+            torch.cuda.synchronize()
+            times.append(ev0.elapsed_time(ev1) / steps)
+        if not torch.isfinite(dec.logits[:batch]).all():
+            raise RuntimeError("the reference arm's decode step gave non-finite logits")
+        return statistics.median(times), start + (steps + 1) / 2.0, graph is not None
+
+    esz = 2
+    cfgo = QwenShape(cfg)
+    with sampler.region("b%d" % a.batch):
+        ms, mean_ctx, graphed = time_rows(a.batch, a.steps)
+    value = a.batch / (ms / 1e3)
+    gbs = decode_bytes(cfgo, L, a.batch, mean_ctx, esz) / (ms / 1e3) / 1e9
+    points, detail = {}, {}
+    if not a.skip_points:
+        for b in (1, 64):
+            with sampler.region(f"b{b}"):
+                pms, pctx, _ = time_rows(b, max(4, a.steps // 2))
+            points[f"decode_b{b}"] = round(b / (pms / 1e3), 2)
+            detail[f"decode_b{b}"] = {"tok_s": round(b / (pms / 1e3), 2), "ms_per_step": round(pms, 4), "hbm_frac": round(
+                decode_bytes(cfgo, L, b, pctx, esz) / (pms / 1e3) / 1e9 / pk["hbm_gbs"], 4)}
+    T = 2048
+    ptoks = torch.randint(0, V, (T,), generator=torch.Generator().manual_seed(3)).tolist()
+    ptimes = []
+    with sampler.region("prefill"):
+        for i in range(3):
+            dec.n_past[0] = 0
+            torch.cuda.synchronize()
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ev0.record()
+            dec.forward(0, ptoks)                         # portions of 512 tokens, the reference's default batch
+            ev1.record()
+            torch.cuda.synchronize()
+            ptimes.append(ev0.elapsed_time(ev1))
+    pre_ms = statistics.median(ptimes[1:])
+    clocks = sampler.stop()
+    flops = prefill_flops(cfgo, L, T)
+    out = {
+        "metric": "Qwen3-8B decode tok/s @ batch 1/8/64; prefill tok/s @ 2048 tok; % roofline",
+        "value": round(value, 2), "unit": "tokens/s", "value_of": f"decode tok/s at batch {a.batch}, context {a.context}",
+        "n_gpus": 1, "steps": a.steps, "warmup": a.warmup, "ms_per_step": round(ms, 4), "repeats": repeats_for(a.steps),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "impl": "reference", "reference_class": REFERENCE_CLASS,
+        "config": {"model": "Qwen3-8B shape, random weights", "layers": L, "layers_full": QWEN3_8B["num_hidden_layers"],
+                   "hidden": H, "heads": nh, "kv_heads": nkv, "head_dim": hd, "intermediate": I, "vocab": V,
+                   "global_batch": a.batch, "seq_len": a.context, "kv_cache": "float16, contiguous per slot",
+                   "activations": "float32", "decode_graph": graphed, "prefill_portion": 512,
+                   "parallelism": "single GPU", "l2": "inputs larger than L2 (weights and cache are read once per step)",
+                   "peaks": pk["source"]},
+        "e2e": None, "gpu_launches": 0,
+        "prefill": {"value": round(T / (pre_ms / 1e3), 1), "tokens": T, "ms": round(pre_ms, 3),
+                    "frac": round(flops / (pre_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(gbs / pk["hbm_gbs"], 4), "mean_context": round(mean_ctx, 1)},
+        "points": points, "points_detail": detail, "clocks": clocks,
+    }
+    print(json.dumps(out))
+    return 0
+
+
+class QwenShape:
+    """The sizes ``decode_bytes`` and ``prefill_flops`` read, from a config dictionary."""
+
+    def __init__(self, d):
+        self.hidden_size, self.intermediate_size, self.vocab_size = d["hidden_size"], d["intermediate_size"], d["vocab_size"]
+        self.num_attention_heads, self.head_dim = d["num_attention_heads"], d["head_dim"]
+        self.q_dim = d["num_attention_heads"] * d["head_dim"]
+        self.kv_dim = d["num_key_value_heads"] * d["head_dim"]
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -356,10 +610,7 @@ def main() -> int:
     ap.add_argument("--forks", type=int, default=15, help="long: forks of the request for the batched decode")
     a = ap.parse_args()
     if a.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "the reference is a Rust workspace (no setup.py or pyproject.toml: pip reports "
-                          "'not installable') and neither cargo nor rustc is in this image"}))
-        return 0
+        return reference_arm(a)
     if a.gpus != 1:
         print(f"bench.py measures one GPU; --gpus {a.gpus} is not supported (the engine is single-GPU)")
         return 2
@@ -389,30 +640,40 @@ def main() -> int:
 
     sampler = ClockSampler()
     sampler.start()
-    ms, launches = time_decode(eng, a.batch, a.context, a.steps, a.warmup, "d")
-    clocks = sampler.stop()
+    with sampler.region(f"b{a.batch}"):
+        ms, launches, mean_ctx, reps = time_decode(eng, a.batch, a.context, a.steps, a.warmup, "d", check=True)
     value = a.batch / (ms / 1e3)
 
     if a.decode_only:
+        sampler.stop()
         print(json.dumps({"decode_only": True, "ms_per_step": round(ms, 4), "value": round(value, 2),
                           "layers": L, "batch": a.batch, "context": a.context}))
         return 0
-    e2e_ms, h2d, d2h = time_e2e(eng, a.batch, a.context, a.steps, a.warmup)
-    points = {}
+    with sampler.region("e2e"):
+        e2e_ms, h2d, d2h = time_e2e(eng, a.batch, a.context, a.steps, a.warmup)
+    points, detail = {}, {}
     if not a.skip_points:
         for b in (1, 64):
-            pms, _ = time_decode(eng, b, a.context, max(4, a.steps // 2), a.warmup, f"b{b}_")
+            with sampler.region(f"b{b}"):
+                pms, _, pctx, _ = time_decode(eng, b, a.context, a.steps, a.warmup, f"b{b}_", check=True)
             points[f"decode_b{b}"] = round(b / (pms / 1e3), 2)
+            detail[f"decode_b{b}"] = {"tok_s": round(b / (pms / 1e3), 2), "ms_per_step": round(pms, 4), "hbm_frac": round(
+                decode_bytes(cfg, L, b, pctx, esz) / (pms / 1e3) / 1e9 / pk["hbm_gbs"], 4)}
     T = 2048
-    pre_ms = time_prefill(eng, T)
-    peak_flops = pk["bf16_tflops"] * 1e12 if a.dtype == "bfloat16" else None
-    pre = {"value": round(T / (pre_ms / 1e3), 1), "tokens": T, "ms": round(pre_ms, 3),
-           "frac": round(prefill_flops(cfg, L, T) / (pre_ms / 1e3) / peak_flops, 4) if peak_flops else None}
-    gbs = decode_bytes(cfg, L, a.batch, a.context, esz) / (ms / 1e3) / 1e9
+    with sampler.region("prefill"):
+        pre_ms = time_prefill(eng, T)
+    clocks = sampler.stop()
+    flops = prefill_flops(cfg, L, T)
+    pre = {"value": round(T / (pre_ms / 1e3), 1), "tokens": T, "ms": round(pre_ms, 3), "frac": None}
+    if a.dtype == "bfloat16":
+        pre["frac"] = pre["frac_burst"] = round(flops / (pre_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)
+        pre["frac_sustained"] = round(flops / (pre_ms / 1e3) / (pk["bf16_tflops_sustained"] * 1e12), 4)
+    gbs = decode_bytes(cfg, L, a.batch, mean_ctx, esz) / (ms / 1e3) / 1e9
     out = {
         "metric": "Qwen3-8B decode tok/s @ batch 1/8/64; prefill tok/s @ 2048 tok; % roofline",
         "value": round(value, 2), "unit": "tokens/s", "value_of": f"decode tok/s at batch {a.batch}, context {a.context}",
         "n_gpus": 1, "steps": a.steps, "warmup": a.warmup, "ms_per_step": round(ms, 4),
+        "repeats": len(reps), "ms_per_step_repeats": [round(t, 4) for t in reps],
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16" if a.dtype == "bfloat16" else "fp32", "data": "synthetic", "impl": "ours",
         "config": {"model": "Qwen3-8B shape, random weights", "layers": L, "layers_full": full_layers,
@@ -427,8 +688,9 @@ def main() -> int:
         "gpu_launches": launches,
         "prefill": pre,
         "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
-                     "frac": round(gbs / pk["hbm_gbs"], 4)},
-        "points": points,
+                     "frac": round(gbs / pk["hbm_gbs"], 4), "mean_context": round(mean_ctx, 1)},
+        "points": points, "points_detail": detail,
+        "checked": "each timed decode step: finite logits, graph replay against a kernel-by-kernel run",
         "clocks": clocks,
     }
     print(json.dumps(out))
