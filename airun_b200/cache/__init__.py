@@ -1,3 +1,3 @@
 """Paged key/value cache and per-request state slots."""
-from .manager import (CacheBinding, CacheError, CacheManager, CacheStorage, OutOfPages, PageAllocator,
+from .manager import (CacheBinding, CacheError, CacheManager, CacheStorage, OutOfPages, OutOfSlots, PageAllocator,
                       PagedGroup, RequestCache, StateGroup)

@@ -57,6 +57,10 @@ class CacheError(RuntimeError):
     """Misuse of the manager (unknown request, double free, ...)."""
 
 
+class OutOfSlots(CacheError):
+    """Every request slot is in use; nothing was taken.  A shortage like OutOfPages, not a misuse."""
+
+
 _LIB = None
 
 
@@ -283,7 +287,7 @@ class CacheManager:
             raise CacheError(f"request {rid!r} is already live")
         slot = self._lib.airun_cache_add(self._h)
         if slot < 0:
-            raise CacheError(f"all {self.max_requests} request slots are in use")
+            raise OutOfSlots(f"all {self.max_requests} request slots are in use")
         rc = RequestCache(rid, slot, self)
         self.requests[rid] = rc
         return rc
@@ -361,6 +365,8 @@ class CacheManager:
         prc = self.get(parent)
         if child in self.requests:
             raise CacheError(f"request {child!r} is already live")
+        if not self.has_free_slot():
+            raise OutOfSlots(f"all {self.max_requests} request slots are in use")
         slot, n = c_int(-1), c_int(0)
         self._check(self._lib.airun_cache_fork(self._h, prc.slot, ctypes.byref(slot), self._copies, ctypes.byref(n)),
                     parent)

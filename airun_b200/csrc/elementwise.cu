@@ -8,6 +8,7 @@
 //   add+norm   x += delta, then the norm of the sum    (ops.cu:47-78);
 //   SwiGLU     out = g / (1 + exp(-g)) * u             (ops.cu:191-200).
 #include "common.cuh"
+#include <type_traits>
 
 template <typename TTab>
 __global__ void embed_kernel(const TTab* __restrict__ table, const int32_t* __restrict__ ids,
@@ -272,5 +273,63 @@ AIRUN_EXPORT int airun_gather_rows(const void* in, void* out, const int32_t* row
     if (n_rows < 0 || row_bytes <= 0 || row_bytes % 4 != 0) return AIRUN_ERR_ARG;
     if (n_rows == 0) return AIRUN_OK;
     airun_launch(gather_rows_kernel, dim3(n_rows), dim3(256), 0, stream, (const uint32_t*)in, (uint32_t*)out, rows, row_bytes / 4);
+    return airun_launch_status();
+}
+
+// Random weights from a counter: element i of a tensor with key k is a function of (k, i) alone, so
+// the host and the device fill the same tensor bit for bit and no generator state is carried.
+//   h(c)  = mix(k + c * 0x9E3779B97F4A7C15), mix = the finaliser of splitmix64;
+//   z     = (sum of the twelve 16-bit fields of h(3i), h(3i+1), h(3i+2) - 393210) / 65536:
+//           integers up to there, so exact; mean 0, variance 1 - 2^-32, |z| <= 6;
+//   kind 0: w = z * scale            (one float32 product)
+//   kind 1: w = 1 + z * scale        (product, then sum: two roundings, never fused)
+//   kind 2: w = h(3i) & 0x7fff       (int32)
+// The reference has no random-weights mode; its benchmark makes token ids from a seeded xorshift the
+// same stateless way (crates/airun-cli/src/bench.rs:177-187).
+__device__ __forceinline__ unsigned long long fill_mix(unsigned long long z) {
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+
+template <typename TOut>
+__global__ void fill_random_kernel(TOut* __restrict__ out, long long n, unsigned long long key, int kind, float scale) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const unsigned long long c = 3ull * (unsigned long long)i;
+    const unsigned long long h0 = fill_mix(key + c * 0x9E3779B97F4A7C15ull);
+    if constexpr (std::is_same<TOut, int32_t>::value) {
+        out[i] = (int32_t)(h0 & 0x7fffull);
+    } else {
+        const unsigned long long h1 = fill_mix(key + (c + 1) * 0x9E3779B97F4A7C15ull);
+        const unsigned long long h2 = fill_mix(key + (c + 2) * 0x9E3779B97F4A7C15ull);
+        int s = 0;
+#pragma unroll
+        for (int f = 0; f < 4; ++f)
+            s += (int)((h0 >> (16 * f)) & 0xffff) + (int)((h1 >> (16 * f)) & 0xffff) + (int)((h2 >> (16 * f)) & 0xffff);
+        const float z = (float)(s - 393210) * (1.0f / 65536.0f);
+        float w = __fmul_rn(z, scale);
+        if (kind == 1) w = __fadd_rn(1.0f, w);
+        out[i] = from_f32<TOut>(w);
+    }
+}
+
+AIRUN_EXPORT int airun_fill_random(void* out, int out_dtype, long long n, unsigned long long key, int kind, float scale,
+                                   cudaStream_t stream) {
+    if (n < 0 || kind < 0 || kind > 2) return AIRUN_ERR_ARG;
+    if (n == 0) return AIRUN_OK;
+    const int threads = 256;
+    const long long blocks = (n + threads - 1) / threads;
+    if (blocks > 0x7fffffffll) return AIRUN_ERR_ARG;
+    if (kind == 2) {
+        if (out_dtype != 2) return AIRUN_ERR_UNSUPPORTED;
+        fill_random_kernel<int32_t><<<(unsigned)blocks, threads, 0, stream>>>((int32_t*)out, n, key, kind, scale);
+    } else if (out_dtype == AIRUN_DT_F32) {
+        fill_random_kernel<float><<<(unsigned)blocks, threads, 0, stream>>>((float*)out, n, key, kind, scale);
+    } else if (out_dtype == AIRUN_DT_BF16) {
+        fill_random_kernel<__nv_bfloat16><<<(unsigned)blocks, threads, 0, stream>>>((__nv_bfloat16*)out, n, key, kind, scale);
+    } else {
+        return AIRUN_ERR_UNSUPPORTED;
+    }
     return airun_launch_status();
 }

@@ -21,7 +21,8 @@
 //
 // Every wait on an mbarrier is bounded: when it runs out the kernel sets an
 // error bit, skips the rest of its work, frees its tensor memory and returns.
-// No cluster launch and no multicast are used.
+// From 17 tokens on the K slices of a tile run as one thread-block cluster and add up through distributed
+// shared memory (see cluster_reduce); no TMA load uses multicast.
 //
 // The reference's counterparts are its wmma prefill GEMM and its half-precision
 // matvec kernels (crates/airun-cuda/kernels/matmul.cu:518-636, :1498-1563); its
@@ -769,6 +770,16 @@ constexpr int cluster_stages(int bn, int stages) {
     return fit < 2 * stages ? fit : 2 * stages;
 }
 
+// True the first time it is asked on the current device (``mask``: one bit per device, of one kernel).
+// cudaFuncSetAttribute holds for one device only, so each kernel is configured once on each.
+static inline bool first_on_device(unsigned long long& mask) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return true;
+    if ((mask >> dev) & 1ull) return false;
+    mask |= 1ull << dev;
+    return true;
+}
+
 template <int BN, int STAGES, int EPI, bool SWAP>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, dim3 grid, cudaStream_t stream) {
     using L = SmemLayout<BN, STAGES>;
@@ -779,23 +790,21 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, di
             // may as well use the whole shared memory: twice the stages
             constexpr int CS = cluster_stages(BN, STAGES);
             using LC = SmemLayout<BN, CS>;
-            static bool configured_c = false;
+            static unsigned long long configured_c = 0;       // one bit per device: the attribute is the device's
             auto kern = gemm_tcgen05_kernel<BN, CS, EPI, SWAP, true>;
-            if (!configured_c) {
+            if (first_on_device(configured_c)) {
                 cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, LC::TOTAL);
                 if (e != cudaSuccess) return (int)e;
-                configured_c = true;
             }
             airun_launch_cluster(kern, dim3(grid), dim3(GEMM_THREADS), LC::TOTAL, stream, (unsigned)p.ksplit, ma, mb, p);
             return airun_launch_status();
         }
     }
-    static bool configured = false;
+    static unsigned long long configured = 0;
     auto kern = gemm_tcgen05_kernel<BN, STAGES, EPI, SWAP, false>;
-    if (!configured) {
+    if (first_on_device(configured)) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
         if (e != cudaSuccess) return (int)e;
-        configured = true;
     }
     airun_launch(kern, dim3(grid), dim3(GEMM_THREADS), L::TOTAL, stream, ma, mb, p);
     return airun_launch_status();
@@ -805,17 +814,18 @@ template <int EPI>
 int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, cudaStream_t stream) {
     using L = SmemLayout<PBN, PSTAGES>;
     constexpr int SMEM = L::TOTAL + 64;
-    static bool configured = false;
-    static int n_sm = 0;
+    static unsigned long long configured = 0;
+    static int sms_of[64];
     auto kern = gemm_tcgen05_persistent_kernel<EPI>;
-    if (!configured) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) return AIRUN_ERR_ARG;
+    if (first_on_device(configured)) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
         if (e != cudaSuccess) return (int)e;
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
-        configured = true;
+        cudaDeviceGetAttribute(&sms_of[dev], cudaDevAttrMultiProcessorCount, dev);
     }
+    const int n_sm = sms_of[dev];
     const int m_tiles = (p.a_rows + BM - 1) / BM, n_tiles = (p.b_rows + PBN - 1) / PBN;
     const int total = m_tiles * n_tiles;
     const int grid = total < n_sm ? total : n_sm;
@@ -827,8 +837,10 @@ int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const GemmPa
 // whose tiles outnumber them would run its last clusters alone in a second wave.
 template <int BN, int STAGES, int EPI, bool SWAP>
 int cluster_capacity(int ks) {
-    static int cache[9] = {0, 0, 0, 0, 0, 0, 0, 0, 0};
-    if (ks < 2 || ks > 8) return 0;
+    static int per_device[64][9];                             // zero: not asked yet on that device
+    int dev = 0;
+    if (ks < 2 || ks > 8 || cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+    int* cache = per_device[dev];
     if (cache[ks] == 0) {
         using L = SmemLayout<BN, cluster_stages(BN, STAGES)>;
         auto kern = gemm_tcgen05_kernel<BN, cluster_stages(BN, STAGES), EPI, SWAP, true>;
@@ -986,7 +998,10 @@ AIRUN_EXPORT int airun_gemm_tcgen05(const void* x, const void* W, void* out, int
 
 // ------------------------------------------------------------------ no-allocation variant
 // See gemm_tcgen05_static.h: the same kernel, with its split-K scratch in arrays that belong
-// to this library instead of buffers the caller allocates.
+// to this library instead of buffers the caller allocates.  Only the plain build of this file
+// carries the arrays and the entry point: the build with the folded norm (AIRUN_FOLD_NORM=1) is a
+// second library of the same process and would hold a second copy of them on every GPU.
+#if !AIRUN_FOLD_NORM
 #include "gemm_tcgen05_static.h"
 
 static __device__ __align__(256) float g_static_scratch[AIRUN_STATIC_SCRATCH_FLOATS];
@@ -1079,3 +1094,4 @@ AIRUN_EXPORT int airun_gemm_tcgen05_static(const void* x, const void* W, void* o
     if (epi == EPI_SWIGLU) return dispatch<EPI_SWIGLU>(swap != 0, bn, ma, mb, p, grid, stream);
     return AIRUN_ERR_UNSUPPORTED;
 }
+#endif  // !AIRUN_FOLD_NORM

@@ -15,7 +15,9 @@
 //
 // Limits.  The arrays hold AIRUN_STATIC_SCRATCH_FLOATS floats (16 MiB) and
 // AIRUN_STATIC_COUNTERS counters; every GPU on which the library is loaded keeps that much
-// memory until the process ends.  A call that would need more (tiles * ksplit * bn * 128
+// memory until the process ends.  Of the two builds of gemm_tcgen05.cu only the plain one (without
+// AIRUN_FOLD_NORM) carries the arrays and exports this symbol, so a process that loads both
+// libraries still holds them once.  A call that would need more (tiles * ksplit * bn * 128
 // floats, or more tiles than counters) is refused with AIRUN_ERR_STATIC_TOO_LARGE before
 // anything is launched; use fewer slices or the regular entry point.
 //

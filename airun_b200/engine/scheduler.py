@@ -44,7 +44,7 @@ from dataclasses import dataclass, field
 from enum import Enum
 from typing import Deque, Dict, Hashable, List, Optional, Tuple
 
-from ..cache.manager import CacheError, CacheManager, CopyPlan, OutOfPages
+from ..cache.manager import CacheError, CacheManager, CopyPlan, OutOfPages, OutOfSlots
 from ..sampling.sampler import Sampler, SamplingParams
 
 
@@ -134,6 +134,10 @@ class Scheduler:
         capacity = self.manager.max_tokens_possible()
         if len(req.prompt) == 0:
             req.finished = FinishReason.REFUSED
+        elif (req.rid in self.manager.requests or any(r.rid == req.rid for r in self.waiting)
+              or any(r.rid == req.rid for r in self.running)):
+            # a second request under a live id would wedge the queue at admission
+            req.finished = FinishReason.REFUSED
         elif len(req.prompt) + 1 > min(capacity, self.max_context):
             req.finished = FinishReason.REFUSED
         if req.finished is not None:
@@ -152,12 +156,14 @@ class Scheduler:
             raise ValueError("only a running request can be forked")
         if child.prompt != parent.tokens:
             raise ValueError("a fork continues the parent's tokens; its prompt must equal them")
+        if child.rid in self.manager.requests or any(r.rid == child.rid for r in self.waiting):
+            raise ValueError(f"request id {child.rid!r} is in use")
         while True:
             try:
                 copies = self.manager.fork(parent.rid, child.rid)
                 break
-            except (OutOfPages, CacheError):
-                if not self._drop_kept():                 # kept caches give way to a fork as well
+            except (OutOfPages, OutOfSlots):              # a shortage: kept caches give way to a fork as well
+                if not self._drop_kept():
                     raise
         child.num_computed = parent.num_computed
         self.running.append(child)
@@ -206,14 +212,14 @@ class Scheduler:
             # falls into: other kept caches give way to that, the one unused longest first
             try:
                 forked = self.manager.fork(best, req.rid)
-            except (OutOfPages, CacheError):
+            except (OutOfPages, OutOfSlots):
                 if self._drop_kept(spare=best):
                     continue
                 return False
             try:
                 cut = self.manager.truncate(req.rid, best_n)
                 break
-            except (OutOfPages, CacheError):
+            except OutOfPages:
                 self.manager.free_request(req.rid)
                 if not self._drop_kept(spare=best):
                     return False
@@ -313,6 +319,9 @@ class Scheduler:
         while (self.waiting and budget > 0 and len(entries) < self.max_batch_reqs
                and (self.manager.has_free_slot() or self._drop_kept()) and not preempted):
             req = self.waiting[0]
+            if req.finished is not None:                  # ended while it waited (after a preemption)
+                self.waiting.popleft()
+                continue
             if req.cancelled:
                 self.waiting.popleft()
                 req.finished = FinishReason.CANCELLED

@@ -22,8 +22,41 @@ from . import ops
 from .ops import _check, _cuda, _fn, _need, _p, _stream
 
 EPI_F32, EPI_BF16, EPI_SWIGLU, EPI_RESID = 0, 1, 2, 3
-STREAM_CTAS = 296                      # two CTAs on each of 148 SMs
-SPLIT_CTAS = 256                       # CTAs a split product may use: its clusters must all be resident together (296 slots)
+B200_SMS = 148                         # the SM count the plans are sized for when no GPU can be asked
+
+
+class Machine:
+    """How many CTAs of each kernel the GPU holds at once: the SM count read from the device, times the
+    CTAs of that kernel one SM holds (fixed by the kernels' shared memory and registers)."""
+
+    def __init__(self, sms: int):
+        self.sms = int(sms)
+        self.stream_ctas = 2 * self.sms                   # streaming product: two CTAs per SM
+        # CTAs a split product may use: its clusters (of up to 8) must all be resident together, so a
+        # margin is left below the 2-per-SM slots: the multiples of 32 that fit in nine tenths of them
+        self.split_ctas = max(32, (2 * self.sms * 9 // 10) // 32 * 32)
+        self.decode_slots = 3 * self.sms                  # cp.async decode attention: three CTAs per SM
+        self.decode_slots_tma = 2 * self.sms              # its TMA variant keeps three stages per warp: two per SM
+        self.wide_min_ctas = self.sms * 128 // B200_SMS   # fewest CTAs the two-tile prefill attention is used for
+
+
+_MACHINES: Dict[object, Machine] = {}
+
+
+def machine(device=None) -> Machine:
+    """The Machine of ``device`` (default: the current CUDA device; without a GPU, a B200's numbers)."""
+    if not torch.cuda.is_available():
+        return _MACHINES.setdefault(None, Machine(B200_SMS))
+    idx = torch.device(device).index if device is not None and torch.device(device).index is not None \
+        else torch.cuda.current_device()
+    m = _MACHINES.get(idx)
+    if m is None:
+        m = _MACHINES[idx] = Machine(torch.cuda.get_device_properties(idx).multi_processor_count)
+    return m
+
+
+STREAM_CTAS = Machine(B200_SMS).stream_ctas    # the B200's figures, for callers that plan without a device
+SPLIT_CTAS = Machine(B200_SMS).split_ctas
 
 _SCRATCH: Dict[torch.device, Tuple[torch.Tensor, torch.Tensor]] = {}
 SCRATCH_FLOATS = 16 << 20              # 64 MiB of partial tiles
@@ -113,7 +146,7 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: int, 
              _p(norm_w), _p(ssq_out), ssq_out.shape[1] if ssq_out is not None else 0), "gemm_tcgen05")
 
 
-def plan_gemm(M: int, N: int, K: int) -> Tuple[bool, int, int]:
+def plan_gemm(M: int, N: int, K: int, mach: Optional[Machine] = None) -> Tuple[bool, int, int]:
     """(swap, bn, ksplit) for a product of M tokens with an [N, K] weight.
 
     Up to 128 tokens the weights are the 128-row operand (swap).  Up to 16 tokens the K range is cut
@@ -126,18 +159,19 @@ def plan_gemm(M: int, N: int, K: int) -> Tuple[bool, int, int]:
     leave SMs idle, so the tile narrows to 128 x 128, and only if that still fills less than one
     wave and a slice keeps 32 K-steps is K cut as well.  Both rules come from sweeps over the
     Qwen3-1.7B and -8B shapes, 1 to 2048 tokens, timed inside CUDA graphs."""
+    mach = mach or machine()
     kb = (K + 63) // 64
     if M <= 128:
         bn = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128
         tiles = (N + 127) // 128
         if M <= 16:
-            return True, bn, max(1, min(STREAM_CTAS // tiles, kb // 10))
-        return True, bn, max(1, min(SPLIT_CTAS // tiles, kb // 8, 8))
+            return True, bn, max(1, min(mach.stream_ctas // tiles, kb // 10))
+        return True, bn, max(1, min(mach.split_ctas // tiles, kb // 8, 8))
     mt = (M + 127) // 128
-    if N >= 256 and mt * ((N + 255) // 256) >= 96:
+    if N >= 256 and mt * ((N + 255) // 256) >= mach.sms * 96 // B200_SMS:
         return False, 256, 1
     tiles = mt * ((N + 127) // 128)
-    return False, 128, max(1, min(148 // tiles, kb // 32))
+    return False, 128, max(1, min(mach.sms // tiles, kb // 32))
 
 
 def _usable(x: torch.Tensor, w: torch.Tensor) -> bool:
@@ -199,12 +233,10 @@ def max_resid_parts(N: int) -> int:
 
 # ---------------------------------------------------------------- attention
 _ARANGE: Dict[torch.device, torch.Tensor] = {}
-DECODE_SLOTS = 444                     # CTAs of the cp.async decode kernel resident at once: three on each of 148 SMs
-DECODE_SLOTS_TMA = 296                 # the TMA variant keeps three stages per warp: two CTAs per SM
 DECODE_MIN_KEYS_PER_SPLIT = 128
 PREFILL_ROWS = 128                     # packed rows (tokens x heads of a KV group) of one prefill CTA
 PREFILL_ROWS_WIDE = 256                # of the tcgen05 kernel with two Q tiles
-WIDE_MIN_CTAS = 128                    # fewest CTAs the wide kernel is used for (148 SMs, one CTA each)
+WIDE_MIN_CTAS = None                   # fewest CTAs the wide kernel is used for; None: the machine's (one CTA per SM)
 
 
 def _arange(device: torch.device, n: int) -> torch.Tensor:
@@ -346,10 +378,11 @@ def attn_plan(ctx, per_tile: int, tiles: torch.Tensor, rows: torch.Tensor, count
              _p(rows), rows.numel(), _p(counts), _p(ctx.err), _stream()), "attn_plan")
 
 
-def plan_decode_splits(n_rows: int, nkv: int, hgroups: int, context_len: int, hd: int, slots: int = DECODE_SLOTS) -> int:
+def plan_decode_splits(n_rows: int, nkv: int, hgroups: int, context_len: int, hd: int, slots: Optional[int] = None) -> int:
     """Slices of the keys per (token, KV head).  A CTA costs a fixed part (set-up, merge of its warps,
     its share of the merge of the slices) plus a part per key; CTAs run in waves of ``slots``.  The
     constants come from timing the kernel at batch 1, 8 and 64 with 4096 keys."""
+    slots = slots or machine().decode_slots
     units = max(1, n_rows * nkv * hgroups)
     most = max(1, min(64, (context_len + DECODE_MIN_KEYS_PER_SPLIT - 1) // DECODE_MIN_KEYS_PER_SPLIT))
     best, best_cost = 1, None
@@ -375,7 +408,7 @@ def _wide_tiles(ctx, G: int, nkv: int) -> bool:
         tiles = (ctx.num_tokens - min(shape["max_rows"], ctx.num_tokens)) * G // PREFILL_ROWS_WIDE
     else:
         tiles = sum(-(-n * G // PREFILL_ROWS_WIDE) for n in ctx.query_lens if n > 1)
-    return tiles * nkv >= WIDE_MIN_CTAS
+    return tiles * nkv >= (WIDE_MIN_CTAS if WIDE_MIN_CTAS is not None else machine().wide_min_ctas)
 
 
 def _attention_plan(ctx, G: int, tile_rows: int = PREFILL_ROWS):
@@ -442,7 +475,8 @@ def attention_bf16(ctx, q, out, cache, nh: int, nkv: int, hd: int, scale: float,
         if window > 0:
             context = min(context, window)
         tma = hd % 64 == 0 and cache.page_size % 16 == 0 and (cache.page_size & (cache.page_size - 1)) == 0
-        slots = DECODE_SLOTS_TMA if tma else DECODE_SLOTS
+        mach = machine(q.device)
+        slots = mach.decode_slots_tma if tma else mach.decode_slots
         if n_rows_dev is not None:
             # no row takes more slices than fit when the fewest rows of this shape are there
             fit = max(1, slots // (plan["min_rows"] * nkv * ((G + 15) // 16)))
@@ -455,7 +489,7 @@ def attention_bf16(ctx, q, out, cache, nh: int, nkv: int, hd: int, scale: float,
             # slices of their own), each token's later keys as usual, one merge
             splits = plan_decode_splits(plan["n_rows"], nkv, (G + 15) // 16, min(context, SHARED_SUFFIX_PLAN), hd, slots)
             slices = _shared_prefix_slices(plan["n_rows"], nkv, G, hd, splits,
-                                           148 if prefill_tc_supported(hd, cache.page_size) else 296)
+                                           mach.sms if prefill_tc_supported(hd, cache.page_size) else 2 * mach.sms)
             attn_shared_prefix(ctx, q, cache, nh, nkv, hd, scale, plan["n_rows"], cache.shared_prefix, slices, splits)
             attn_decode(ctx, q, out, cache, nh, nkv, hd, scale, window, None, plan["n_rows"], splits,
                         k_begin_dev=cache.shared_prefix, extra_slices=slices)
@@ -468,10 +502,11 @@ def attention_bf16(ctx, q, out, cache, nh: int, nkv: int, hd: int, scale: float,
 SHARED_SUFFIX_PLAN = 2048              # keys after the shared prefix the slice count of such a step is chosen for
 
 
-def _shared_prefix_slices(n_rows: int, nkv: int, G: int, hd: int, splits: int = 8, slots: int = 296) -> int:
-    """Slices of the shared keys: about one CTA per SM slot (``slots``: 148 for the tcgen05 kernel, one
-    CTA to an SM; 296 for the mma.sync one), as many as the scratch has room for beside the ``splits``
-    slices of the tokens' own keys, at most 64 of both together."""
+def _shared_prefix_slices(n_rows: int, nkv: int, G: int, hd: int, splits: int = 8, slots: Optional[int] = None) -> int:
+    """Slices of the shared keys: about one CTA per SM slot (``slots``: the SM count for the tcgen05 kernel,
+    one CTA to an SM; twice that for the mma.sync one), as many as the scratch has room for beside the
+    ``splits`` slices of the tokens' own keys, at most 64 of both together."""
+    slots = slots or 2 * machine().sms
     groups = -(-n_rows * G // PREFILL_ROWS)
     want = max(1, min(37, slots // max(1, nkv * groups)))
     room = SCRATCH_FLOATS // (n_rows * nkv * ((G + 15) // 16) * 16 * (hd + 2)) - splits

@@ -17,12 +17,12 @@ Storage rules:
 """
 from __future__ import annotations
 
-import hashlib
 import json
 import os
 from dataclasses import dataclass
 from typing import Dict, Iterable, List, Protocol, Sequence, Tuple
 
+import numpy as np
 import torch
 
 from .safetensors_io import SafetensorsFolder, write_safetensors
@@ -138,33 +138,103 @@ def load_tensors(specs: Sequence[WeightSpec], source: TensorSource,
     return out
 
 
-def _seed_for(seed: int, name: str) -> int:
-    h = hashlib.sha256(f"{seed}:{name}".encode("utf-8")).digest()
-    return int.from_bytes(h[:8], "little") & 0x7FFFFFFFFFFFFFFF
+_M64 = (1 << 64) - 1
+_GOLDEN = 0x9E3779B97F4A7C15
+
+
+def _mix64(z: int) -> int:
+    z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & _M64
+    z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & _M64
+    return z ^ (z >> 31)
+
+
+def tensor_key(seed: int, name: str) -> int:
+    """The 64-bit key of a tensor: the seed mixed with the FNV-1a hash of its name."""
+    h = 0xCBF29CE484222325
+    for byte in name.encode("utf-8"):
+        h = ((h ^ byte) * 0x100000001B3) & _M64
+    return _mix64((h ^ ((int(seed) * _GOLDEN) & _M64)) & _M64)
+
+
+def _np_mix(z: np.ndarray) -> np.ndarray:
+    z = (z ^ (z >> np.uint64(30))) * np.uint64(0xBF58476D1CE4E5B9)
+    z = (z ^ (z >> np.uint64(27))) * np.uint64(0x94D049BB133111EB)
+    return z ^ (z >> np.uint64(31))
+
+
+def fill_random_host(n: int, key: int, kind: str, scale: float) -> np.ndarray:
+    """Element i of the tensor with ``key`` as a function of (key, i) alone: the arithmetic of
+    ``fill_random_kernel`` (csrc/elementwise.cu), integer up to one float32 product (and one sum
+    for ``kind == "norm"``), so the device fills the same tensor bit for bit.  Returns float32
+    (``normal``: z * scale, ``norm``: 1 + z * scale) or int32 (``int``)."""
+    out = np.empty(n, dtype=np.int32 if kind == "int" else np.float32)
+    step = 1 << 22
+    gold, k = np.uint64(_GOLDEN), np.uint64(key)
+    with np.errstate(over="ignore"):
+        for s in range(0, n, step):
+            e = min(n, s + step)
+            c = np.arange(s, e, dtype=np.uint64) * np.uint64(3)
+            h0 = _np_mix(k + c * gold)
+            if kind == "int":
+                out[s:e] = (h0 & np.uint64(0x7FFF)).astype(np.int32)
+                continue
+            h1 = _np_mix(k + (c + np.uint64(1)) * gold)
+            h2 = _np_mix(k + (c + np.uint64(2)) * gold)
+            total = np.zeros(e - s, dtype=np.int64)
+            for h in (h0, h1, h2):
+                for f in range(4):
+                    total += ((h >> np.uint64(16 * f)) & np.uint64(0xFFFF)).astype(np.int64)
+            z = (total - 393210).astype(np.float32) * np.float32(1.0 / 65536.0)
+            w = z * np.float32(scale)
+            if kind == "norm":
+                w = np.float32(1.0) + w
+            out[s:e] = w
+    return out
+
+
+def _fill_random_device(t: torch.Tensor, key: int, kind: str, scale: float) -> None:
+    import ctypes
+    from ..csrc import build
+    lib = build.load("elementwise")
+    f = lib.airun_fill_random
+    f.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_ulonglong, ctypes.c_int, ctypes.c_float,
+                  ctypes.c_void_p]
+    f.restype = ctypes.c_int
+    dt = {torch.float32: 0, torch.bfloat16: 1, torch.int32: 2}[t.dtype]
+    with torch.cuda.device(t.device):
+        rc = f(t.data_ptr(), dt, t.numel(), key, {"normal": 0, "norm": 1, "int": 2}[kind], float(scale),
+               torch.cuda.current_stream().cuda_stream)
+    if rc != 0:
+        raise RuntimeError(f"fill_random: status {rc}")
 
 
 def random_tensors(specs: Sequence[WeightSpec], seed: int,
                    device: torch.device | str = "cpu",
                    matrix_dtype: torch.dtype = torch.bfloat16,
                    std: float = 0.02, norm_std: float = 0.1) -> Dict[str, torch.Tensor]:
-    """Seeded random weights, one generator per tensor name so the order of the
-    specs does not matter: matrices N(0, std) stored in ``matrix_dtype``, norm
-    weights 1 + N(0, norm_std) in float32."""
+    """Seeded random weights: matrices N(0, std) stored in ``matrix_dtype``, norm weights
+    1 + N(0, norm_std) in float32.  Element i of tensor ``name`` depends on (seed, name, i) only (a
+    counter-based generator, ``fill_random_host``), so the order of the specs does not matter and a
+    tensor filled on the GPU by ``fill_random_kernel`` equals the one made here on the CPU bit for
+    bit: a plain implementation can make the weights of a model again without a file."""
     out: Dict[str, torch.Tensor] = {}
     dev = torch.device(device)
     for s in specs:
-        g = torch.Generator(device=dev)
-        g.manual_seed(_seed_for(seed, s.name))
-        if s.init == "norm":
-            t = 1.0 + norm_std * torch.randn(s.shape, generator=g, device=dev, dtype=torch.float32)
-        elif s.init == "zeros":
-            t = torch.zeros(s.shape, device=dev, dtype=torch.float32)
-        elif s.init == "int":
-            t = torch.randint(0, 2 ** 15, s.shape, generator=g, device=dev, dtype=torch.int32)
+        n = 1
+        for d in s.shape:
+            n *= int(d)
+        kind = {"norm": "norm", "int": "int", "zeros": "zeros"}.get(s.init, "normal")
+        dtype = torch.int32 if kind == "int" else (matrix_dtype if s.storage == "compute" else torch.float32)
+        if kind == "zeros":
+            out[s.name] = torch.zeros(s.shape, device=dev, dtype=dtype)
+            continue
+        key = tensor_key(seed, s.name)
+        scale = norm_std if kind == "norm" else std
+        if dev.type == "cuda":
+            t = torch.empty(s.shape, device=dev, dtype=dtype)
+            _fill_random_device(t, key, kind, scale)
         else:
-            t = std * torch.randn(s.shape, generator=g, device=dev, dtype=torch.float32)
-        if s.storage == "compute":
-            t = t.to(matrix_dtype)
+            t = torch.from_numpy(fill_random_host(n, key, kind, scale)).view(s.shape).to(dtype)
         out[s.name] = t
     return out
 

@@ -3,6 +3,7 @@ import json
 import os
 import struct
 
+import numpy as np
 import pytest
 import torch
 
@@ -311,3 +312,24 @@ def test_gpu_subcommand_with_and_without_devices(monkeypatch, capsys):
     assert main(["gpu", "--json"]) == 0
     rep = json.loads(capsys.readouterr().out)
     assert [d["supported"] for d in rep["devices"]] == [True, False] and rep["devices"][0]["l2_bytes"] == 126 << 20
+
+
+def test_random_weights_are_a_function_of_seed_name_and_index():
+    """Counter-based: the host fill has the moments of a normal variate, equals the tests' own statement
+    of the generator, and a tensor does not depend on which other tensors are made."""
+    from airun_b200.weights.loader import fill_random_host, tensor_key
+    from helpers import plain_random_tensor, plain_random_weights
+    z = fill_random_host(400_000, tensor_key(1, "t"), "normal", 1.0)
+    assert abs(float(z.mean())) < 0.01 and abs(float(z.std()) - 1.0) < 0.01 and float(np.abs(z).max()) <= 6.0
+    assert 2.8 < float(((z - z.mean()) ** 4).mean() / z.var() ** 2) < 3.1
+    assert not np.array_equal(z[:1000], fill_random_host(1000, tensor_key(2, "t"), "normal", 1.0))
+    assert not np.array_equal(z[:1000], fill_random_host(1000, tensor_key(1, "u"), "normal", 1.0))
+    cfg = Qwen3Config.from_dict(TINY["B"]["cfg"])
+    m = DecoderModel(cfg, torch.float32, "cpu")
+    ours = random_tensors(m.weight_specs(), 77)
+    mine = plain_random_weights(TINY["B"]["cfg"], 77)
+    assert set(ours) == set(mine)
+    for n in ours:
+        assert ours[n].dtype == mine[n].dtype and torch.equal(ours[n], mine[n]), n
+    i = fill_random_host(1000, tensor_key(1, "t"), "int", 0.0)
+    assert i.dtype == np.int32 and i.min() >= 0 and i.max() < 2 ** 15

@@ -249,19 +249,23 @@ def test_next_step_laid_out_ahead_is_dropped_when_the_batch_changes(folders):
     assert eng.manager.free_pages() == {g.gid: eng.manager.num_pages for g in eng.manager.paged}
 
 
-@pytest.mark.parametrize("seed", [1, 2])
-def test_random_arrivals_forks_and_cancellations_under_a_small_pool(seed, folders):
+@pytest.mark.parametrize("seed,name,dtype", [(1, "B", "float32"), (2, "B", "float32"), (3, "B", "bfloat16"),
+                                             (4, "D", "bfloat16")])
+def test_random_arrivals_forks_and_cancellations_under_a_small_pool(seed, name, dtype, folders):
     """Forty requests arrive at random moments into an engine whose pool holds two or three of them:
     portions, preemption and recomputation, forks that share pages, cancellations, end tokens, the
-    look-ahead path, graph replays.  Every token every request ever gets must be the token the plain
-    implementation gets for the same sequence, and in the end every page is back."""
+    look-ahead path, graph replays.  In float32 every token every request ever gets must be the token the
+    plain implementation gets for the same sequence; in bfloat16 (B: the mma.sync attention at head size
+    32; D: the tcgen05 and TMA attention at head size 128) every token must be, for the plain implementation
+    that rounds where the engine does, within twice that rounding's own effect of its best token.  In the
+    end every page is back."""
     import random
     import airun_b200
-    name = "B"
     cfg, W = P.read_model_folder(folders[name])
     V = cfg["vocab_size"]
     rng = random.Random(seed)
-    eng = airun_b200.Engine.from_folder(folders[name], dtype="float32", page_size=8, num_pages=22,
+    ps = TINY[name]["page_size"]
+    eng = airun_b200.Engine.from_folder(folders[name], dtype=dtype, page_size=ps, num_pages=22 * 8 // ps,
                                         max_batch_tokens=48, max_requests=6, max_context=120)
     greedy = airun_b200.SamplingParams.greedy
     plain_cache = {}
@@ -305,14 +309,78 @@ def test_random_arrivals_forks_and_cancellations_under_a_small_pool(seed, folder
         assert req.finished is not None
         if req.finished.value == "Refused":
             continue
-        want = plain(prompt, n)
         got = req.output
-        assert got == want[:len(got)], (req.rid, req.finished, len(prompt))
         if req.finished.value == "MaxTokens":
             assert len(got) == n
-        elif req.finished.value == "EndOfGeneration":
-            assert want[len(got)] in req.eog_tokens
+        if dtype == "float32":
+            want = plain(prompt, n)
+            assert got == want[:len(got)], (req.rid, req.finished, len(prompt))
+            if req.finished.value == "EndOfGeneration":
+                assert want[len(got)] in req.eog_tokens
+            continue
+        # one pass over prompt + output scores every choice (position len(prompt) - 1 + t chose token t)
+        seq = list(prompt) + list(got)
+        rounded = P.plain_forward(cfg, W, seq, torch.float32, round_to=torch.bfloat16)
+        exact = P.plain_forward(cfg, W, seq, torch.float32)
+        noise = (rounded - exact).abs().max(dim=-1).values
+        first = len(prompt) - 1
+        for t, tok in enumerate(got):
+            row = rounded[first + t]
+            assert float(row.max() - row[tok]) <= 2 * float(noise[first + t]) + 1e-3, (req.rid, t, req.finished)
+        if req.finished.value == "EndOfGeneration":
+            row = rounded[first + len(got)]
+            assert min(float(row.max() - row[e]) for e in req.eog_tokens) <= 2 * float(noise[first + len(got)]) + 1e-3
     assert eng.manager.free_pages() == {g.gid: eng.manager.num_pages for g in eng.manager.paged}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_steps_of_more_than_a_hundred_requests(dtype, folders):
+    """One step of 128 single tokens, then one of 100 single tokens beside a prompt portion, through the
+    step function (batch sizes above every other test's, the largest graph bucket), each row against the
+    plain implementation on its own sequence."""
+    import airun_b200
+    from airun_b200 import StepEntry
+    from helpers import assert_close, bf16_noise
+    name = "B"
+    cfg, W = P.read_model_folder(folders[name])
+    V = cfg["vocab_size"]
+    eng = airun_b200.Engine.from_folder(folders[name], dtype=dtype, page_size=8, cache_tokens=128 * 40 + 256,
+                                        max_batch_tokens=256, max_requests=130, max_context=64)
+    assert eng.runner.graph_buckets[-1] >= 128
+    seqs = [random_tokens(3 + (7 * i) % 28, V, 5000 + i) for i in range(128)]
+    long_one = random_tokens(61, V, 6000)
+    for i in range(128):
+        eng.manager.add_request(i)
+    eng.manager.add_request("p")
+    # prompts, all but the last two tokens of each, in steps of up to 256 tokens
+    batch, count = [], 0
+    for i, s in enumerate(seqs):
+        if count + len(s) - 2 > 256 or len(batch) == 130:
+            eng.runner.step(batch)
+            batch, count = [], 0
+        batch.append(StepEntry(i, s[:-2], ()))
+        count += len(s) - 2
+    eng.runner.step(batch)
+    got = {}
+    for rep in range(2):                                   # twice: the first step of a size runs kernel by kernel, the second is captured
+        a = eng.runner.step([StepEntry(i, [seqs[i][-2]], (0,)) for i in range(128)]).float().cpu().numpy()
+        for i in range(128):
+            eng.manager.truncate(i, len(seqs[i]) - 2)
+        got["a"] = a
+    a = eng.runner.step([StepEntry(i, [seqs[i][-2]], (0,)) for i in range(128)]).float().cpu().numpy()
+    b = eng.runner.step([StepEntry(i, [seqs[i][-1]], (0,)) for i in range(100)]
+                        + [StepEntry("p", long_one, (0, 60))]).float().cpu().numpy()
+    eng.runner.raise_on_device_error()
+    for i in list(range(0, 128, 9)) + [127]:
+        exact = P.plain_forward(cfg, W, seqs[i], torch.float32).numpy()
+        want = exact if dtype == "float32" else P.plain_forward(cfg, W, seqs[i], torch.float32, round_to=torch.bfloat16).numpy()
+        noise = bf16_noise(want, exact)
+        assert_close(a[i:i + 1], want[-2:-1], dtype, f"128 rows, request {i}", noise[-2:-1])
+        if i < 100:
+            assert_close(b[i:i + 1], want[-1:], dtype, f"100 rows + a portion, request {i}", noise[-1:])
+    exact = P.plain_forward(cfg, W, long_one, torch.float32).numpy()
+    want = exact if dtype == "float32" else P.plain_forward(cfg, W, long_one, torch.float32, round_to=torch.bfloat16).numpy()
+    assert_close(b[100:], want[[0, 60]], dtype, "the portion beside 100 single tokens", bf16_noise(want, exact)[[0, 60]])
 
 
 @pytest.mark.parametrize("name,dtype", [("B", "float32"), ("A", "bfloat16")])

@@ -346,6 +346,8 @@ ATT = [  # nh, nkv, hd, page, window, context lengths, query lengths
     (8, 2, 128, 32, 200, [900, 260], [400, 260]),         # window across tiles, pages of 32
     (12, 4, 64, 16, 0, [513, 64], [513, 2]),              # head size 64, three heads in a group
     (5, 1, 128, 64, 0, [260], [260]),                     # a group of 5: 25 tokens per tile, rows left over
+    (8, 2, 64, 24, 0, [100, 49, 75], [1, 49, 3]),         # pages of 24 tokens: no power of two, no divisor of 64
+    (4, 2, 128, 24, 30, [200, 48], [1, 48]),              # the same with a window and head size 128
 ]
 
 
@@ -398,6 +400,57 @@ def test_decode_attention_slices_agree(splits):
         assert ctx.err.item() == 0
         assert torch.allclose(out.cpu().float(), want, rtol=2e-2, atol=2e-2)
         out.fill_(9.0)
+
+
+def test_decode_attention_over_32768_keys():
+    """One decoded token of each of five requests at positions 0, 15, 16, 4095 and 32767, one KV head, the far
+    key of every head made to dominate (the first key for even heads, a middle one for odd heads): against a
+    float64 softmax over all keys.  The reference checks its split attention the same way at 6,000 and 212,992
+    keys (crates/airun-cli/src/selftest.rs:2748-2861)."""
+    from airun_b200.kernels import fast, ops
+    torch.manual_seed(31)
+    nh, nkv, hd, page = 4, 1, 128, 16
+    lens = [1, 16, 17, 4096, 32768]
+    ks = [torch.randn(n, nkv, hd) for n in lens]
+    vs = [torch.randn(n, nkv, hd) for n in lens]
+    q = torch.randn(len(lens), nh, hd) * 0.3
+    for r, n in enumerate(lens):
+        for h in range(nh):
+            far = 0 if h % 2 == 0 else (n - 1) // 2
+            q[r, h] += ks[r][far, 0] * (16.0 / math.sqrt(hd))
+    for dtype in (torch.bfloat16, torch.float32):
+        kd = [k.to(dtype).float() for k in ks]
+        vd = [v.to(dtype).float() for v in vs]
+        qd = q.to(dtype).float()
+        want = torch.zeros(len(lens), nh, hd, dtype=torch.float64)
+        for r in range(len(lens)):
+            for h in range(nh):
+                sc = (kd[r][:, 0].double() @ qd[r, h].double()) * hd ** -0.5
+                want[r, h] = torch.softmax(sc, 0) @ vd[r][:, 0].double()
+        want = want.reshape(len(lens), nh * hd).float()
+        assert float(want[-1].abs().max()) > 1.0                  # the far keys do dominate, among 32768 too
+        pool, bt = paged_from_dense(kd, vd, page, dtype, seed=31)
+        ctx = Ctx([n - 1 for n in lens], list(range(len(lens))), len(lens), [1] * len(lens), lens)
+        cache = Cache(pool, bt, page)
+        qdev = qd.reshape(len(lens), nh * hd).to(dtype).to(DEV)
+        out = torch.full_like(qdev, 9.0)
+        if dtype == torch.float32:
+            ops.attention_generic(qdev, out, pool, bt, ctx.positions, ctx.req_of_token, ctx.num_reqs, nh, nkv, hd,
+                                  hd ** -0.5, 0, ctx.err)
+            torch.cuda.synchronize()
+            assert ctx.err.item() == 0
+            assert torch.allclose(out.cpu(), want, rtol=1e-3, atol=1e-3)
+            continue
+        assert fast.attention_bf16(ctx, qdev, out, cache, nh, nkv, hd, hd ** -0.5, 0)     # the slices its cost model picks
+        torch.cuda.synchronize()
+        assert ctx.err.item() == 0
+        assert torch.allclose(out.float().cpu(), want, rtol=2e-2, atol=2e-2)
+        for splits in (1, 37, 64):
+            out.fill_(9.0)
+            fast.attn_decode(ctx, qdev, out, cache, nh, nkv, hd, hd ** -0.5, 0, None, len(lens), splits)
+            torch.cuda.synchronize()
+            assert ctx.err.item() == 0
+            assert torch.allclose(out.float().cpu(), want, rtol=2e-2, atol=2e-2), splits
 
 
 def test_window_of_one_returns_the_value_at_its_own_place():
@@ -482,7 +535,8 @@ def test_sample_kernel_distribution():
     assert chi2 < 16.3
 
 
-@pytest.mark.parametrize("R,G,S,page", [(16, 8, 1040, 16), (5, 4, 272, 16), (40, 4, 128, 32), (3, 2, 64, 8)])
+@pytest.mark.parametrize("R,G,S,page", [(16, 8, 1040, 16), (5, 4, 272, 16), (40, 4, 128, 32), (3, 2, 64, 8),
+                                        (3, 4, 32768, 16)])
 def test_shared_prefix_attention(R, G, S, page):
     """Decoded tokens whose requests begin with the same pages: the shared keys once for all of them
     (several slices), each token's own later keys by the decode kernel, one merge; against plain
@@ -517,13 +571,19 @@ def test_shared_prefix_attention(R, G, S, page):
     pool, bt = pool.to(torch.bfloat16).to(DEV), bt.to(DEV)
     pos = [n - 1 for n in lens]
     ctx = Ctx(pos, list(range(R)), R, [1] * R, lens)
-    q = torch.randn(R, nh, hd).to(torch.bfloat16).float()
+    q = torch.randn(R, nh, hd) * 0.3
+    for r in range(R):                                   # one key dominates: a shared one (even heads), an own one (odd)
+        for h in range(nh):
+            far = (S // 3 + 7 * r) % S if h % 2 == 0 else S + (own[r] - 1) // 2
+            q[r, h] += ks[r][far, h // G] * (16.0 / math.sqrt(hd))
+    q = q.to(torch.bfloat16).float()
     want = torch.zeros(R, nh, hd, dtype=torch.float64)
     for r in range(R):                                   # softmax(q K^T / sqrt(d)) V over the request's whole context
         for h in range(nh):
             sc = (ks[r][:, h // G].double() @ q[r, h].double()) * hd ** -0.5
             want[r, h] = torch.softmax(sc, 0) @ vs[r][:, h // G].double()
     want = want.reshape(R, nh * hd)
+    assert float(want.abs().max()) > 1.0
     qd = q.to(torch.bfloat16).to(DEV).view(R, nh * hd)
     out = torch.zeros_like(qd)
     cache = Cache(pool, bt, page)
@@ -536,3 +596,30 @@ def test_shared_prefix_attention(R, G, S, page):
         torch.cuda.synchronize()
         assert ctx.err.item() == 0
         assert torch.allclose(out.float().cpu(), want.float(), atol=2e-2, rtol=2e-2), (splits, slices)
+
+
+@pytest.mark.parametrize("kind,dtype", [("normal", torch.bfloat16), ("normal", torch.float32), ("norm", torch.float32),
+                                        ("int", torch.int32)])
+def test_random_fill_is_the_same_on_the_device_and_on_the_host(kind, dtype):
+    """A tensor filled by the kernel equals the host's fill of the same (seed, name) bit for bit, and
+    both equal the tests' own statement of the generator."""
+    from airun_b200.weights.loader import WeightSpec, random_tensors
+    from helpers import plain_random_tensor
+    specs = [WeightSpec("model.layers.7.mlp.up_proj.weight", (37, 1001), "compute" if dtype == torch.bfloat16 else "as_stored",
+                        kind if kind != "normal" else "normal"),
+             WeightSpec("x", (5,), "compute" if dtype == torch.bfloat16 else "as_stored", kind)]
+    host = random_tensors(specs, 1234, "cpu", torch.bfloat16)
+    dev = random_tensors(specs, 1234, "cuda:0", torch.bfloat16)
+    torch.cuda.synchronize()
+    for s in specs:
+        h, d = host[s.name], dev[s.name].cpu()
+        assert h.dtype == d.dtype == dtype and h.shape == d.shape
+        assert torch.equal(h.view(torch.int16 if dtype == torch.bfloat16 else torch.int32),
+                           d.view(torch.int16 if dtype == torch.bfloat16 else torch.int32)), s.name
+        if kind != "int":
+            mine = plain_random_tensor(1234, s.name, s.shape, kind == "norm")
+            if dtype == torch.float32 and kind == "normal":
+                mine = plain_random_tensor(1234, s.name, s.shape, False).float()   # bfloat16 of the same value
+                assert torch.equal(h.to(torch.bfloat16).float(), mine)
+            else:
+                assert torch.equal(h, mine), s.name

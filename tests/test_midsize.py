@@ -4,9 +4,16 @@ products, split-K decode products): its bfloat16 path against its own float32 pa
 execution modes against one another."""
 from __future__ import annotations
 
+import os
+import sys
+
 import numpy as np
 import pytest
 import torch
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+import plain_qwen3 as P                                   # noqa: E402
+from helpers import assert_close, bf16_noise, plain_random_weights   # noqa: E402
 
 pytestmark = pytest.mark.gpu
 
@@ -49,6 +56,70 @@ def engines():
         out[dt] = airun_b200.Engine.from_config(cfg, seed=3, dtype=dt, page_size=16, cache_tokens=4096,
                                                 max_batch_tokens=1024, max_requests=8, max_context=2048)
     return out
+
+
+@pytest.fixture(scope="module")
+def plain_mid():
+    """The plain implementation on the weights ``Engine.from_config(MID, seed=3)`` fills the device with
+    (made again on the CPU from the seed), for two sequences: without rounding and with the bfloat16
+    path's rounding places."""
+    W = plain_random_weights(MID, 3)
+    g = np.random.default_rng(5)
+    seqs = {"a": [int(t) for t in g.integers(0, MID["vocab_size"], size=700)],
+            "b": [int(t) for t in g.integers(0, MID["vocab_size"], size=333)]}
+    exact = {r: P.plain_forward(MID, W, s, torch.float32).numpy() for r, s in seqs.items()}
+    rounded = {r: P.plain_forward(MID, W, s, torch.float32, round_to=torch.bfloat16).numpy() for r, s in seqs.items()}
+    return seqs, exact, rounded
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_whole_and_cut_against_the_plain_implementation(engines, plain_mid, dtype):
+    """Head size 128 on the tcgen05 attention and the TMA decode attention, persistent many-tile
+    products and split-K decode products, inside the engine, against the plain implementation: each
+    request whole, then cut into portions beside the other request and single tokens from graphs."""
+    seqs, exact, rounded = plain_mid
+    a, b = seqs["a"], seqs["b"]
+    want = exact if dtype == "float32" else rounded
+    whole = logits_of(engines[dtype], [[("a", a)], [("b", b)]])
+    cut = [[("a", a[:300])], [("a", a[300:302]), ("b", b[:129])], [("a", a[302:650]), ("b", b[129:300])]]
+    cut += [[("a", [a[650 + i]]), ("b", [b[300 + i]])] for i in range(33)]
+    cut += [[("a", a[683:])]]
+    mixed = logits_of(engines[dtype], cut)
+    for rid in ("a", "b"):
+        noise = bf16_noise(rounded[rid], exact[rid])
+        assert_close(whole[rid], want[rid], dtype, f"mid {dtype} whole {rid}", noise)
+        assert_close(mixed[rid], want[rid], dtype, f"mid {dtype} cut {rid}", noise)
+
+
+def test_forks_against_the_plain_implementation(engines):
+    """Four requests forked from one 1,300-token prompt and decoded side by side (the shared pages are
+    read once per step for all of them), each against the plain implementation on prompt + its tail."""
+    from airun_b200 import StepEntry
+    W = plain_random_weights(MID, 3)
+    g = np.random.default_rng(21)
+    n_prompt = 1100
+    prompt = [int(t) for t in g.integers(0, MID["vocab_size"], size=n_prompt)]
+    tails = [[int(t) for t in g.integers(0, MID["vocab_size"], size=6)] for _ in range(4)]
+    eng = engines["bfloat16"]
+    m = eng.manager
+    m.add_request("p")
+    eng.runner.step([StepEntry("p", prompt[:700], ())])
+    eng.runner.step([StepEntry("p", prompt[700:], ())])
+    rids = ["p", "f1", "f2", "f3"]
+    for r in rids[1:]:
+        eng.storage.run_copies(m.fork("p", r))
+    rows = [eng.runner.step([StepEntry(r, [tails[i][k]], (0,)) for i, r in enumerate(rids)]).float().cpu().numpy()
+            for k in range(6)]
+    eng.runner.raise_on_device_error()
+    assert any(isinstance(k, tuple) and k[0] == "shared" for k in eng.runner.graphs), "the shared-prefix path never ran"
+    for r in rids:
+        m.free_request(r)
+    got = np.stack(rows)                                          # [step, request, V]
+    for i in (3,):
+        seq = prompt + tails[i]
+        exact = P.plain_forward(MID, W, seq, torch.float32).numpy()[n_prompt:]
+        rounded = P.plain_forward(MID, W, seq, torch.float32, round_to=torch.bfloat16).numpy()[n_prompt:]
+        assert_close(got[:, i], rounded, "bfloat16", f"fork {i}", bf16_noise(rounded, exact))
 
 
 def test_bfloat16_path_agrees_with_the_float32_path_and_with_itself(engines):

@@ -395,3 +395,69 @@ def test_product_plan_takes_every_shape_and_stays_within_the_kernel_limits():
             if ks > 1:
                 assert ((M + 127) // 128) * ((N + bn - 1) // bn) * ks <= 148
     assert plan_gemm(8, 24576, 4096) == (True, 16, 1) and plan_gemm(2048, 24576, 4096) == (False, 256, 1)
+    # a GPU with another SM count gets plans sized for it, not for 148 SMs
+    from airun_b200.kernels.fast import Machine
+    small = Machine(66)
+    assert small.stream_ctas == 132 and small.split_ctas <= 2 * 66 and small.decode_slots == 198
+    for M, N, K in shapes[:200]:
+        swap, bn, ks = plan_gemm(M, N, K, small)
+        if swap and ks > 1:
+            assert ((N + 127) // 128) * ks <= (small.stream_ctas if M <= 16 else small.split_ctas)
+        if not swap and ks > 1:
+            assert ((M + 127) // 128) * ((N + bn - 1) // bn) * ks <= 66
+
+
+def test_a_second_request_under_a_live_id_is_refused_and_the_queue_moves_on():
+    m, s = make(pages=16, page=4, budget=16)
+    a = req("a", 5)
+    s.add(a)
+    again = req("a", 3)
+    s.add(again)                                 # while the first one waits
+    assert again.finished == FinishReason.REFUSED
+    run(m, s, s.plan())
+    running_again = req("a", 3)
+    s.add(running_again)                         # while the first one runs
+    assert running_again.finished == FinishReason.REFUSED
+    b = req("b", 4)
+    s.add(b)
+    while s.has_work():
+        run(m, s, s.plan())
+    assert a.finished == FinishReason.MAX_TOKENS and b.finished == FinishReason.MAX_TOKENS
+    later = req("a", 3)                          # the id is free again once its request has ended
+    s.add(later)
+    assert later.finished is None
+    while s.has_work():
+        run(m, s, s.plan())
+    assert later.finished == FinishReason.MAX_TOKENS and m.free_pages() == {0: 16}
+
+
+def test_a_request_that_ended_while_it_waited_is_not_run_again():
+    m, s = make(pages=6, page=4, budget=32)
+    a, b = req("a", 10, max_new=20), req("b", 9, max_new=20)
+    s.add(a)
+    s.add(b)
+    for _ in range(3):
+        run(m, s, s.plan())
+    p = s.plan()
+    assert p.preempted == [b] and s.waiting[0] is b
+    b.finished = FinishReason.MAX_TOKENS         # as a token accepted for the step planned ahead would end it
+    run(m, s, p)
+    while s.has_work():
+        p = s.plan()
+        assert all(e.request is not b for e in p.entries)
+        run(m, s, p)
+    assert b not in s.running and "b" not in m.requests and m.free_pages() == {0: 6}
+
+
+def test_a_misuse_of_fork_does_not_cost_the_kept_caches():
+    m, s, dev = make_kept(pages=12, page=4, reqs=4)
+    s.add(Request("a", list(range(100, 108)), SamplingParams.greedy(), 1))
+    drain(s, dev)
+    assert len(s.kept) == 1
+    s.add(Request("live", list(range(300, 305)), SamplingParams.greedy(), 6))
+    dev.step(s, s.plan())
+    live = s.running[0]
+    with pytest.raises(ValueError):
+        s.fork(live, Request("live", list(live.tokens), SamplingParams.greedy(), 2))   # the child's id is in use
+    assert len(s.kept) == 1 and s.stats["prefix_evictions"] == 0
+    drain(s, dev)
