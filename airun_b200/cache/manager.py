@@ -439,9 +439,27 @@ class CacheStorage:
             t[:, slot].zero_()
 
     def run_copies(self, plan: CopyPlan) -> None:
-        """Runs the copies of a fork or cut-back on the current stream."""
+        """Runs the copies of a fork or cut-back on the current stream, in the order of the plan: the
+        pages of a cache group go in one kernel launch (all owner layers at once) as long as no copy
+        reads or overwrites a page an earlier copy of the same launch writes (a copy of a copy: the
+        partly filled page a fork copied, cut back again); such a copy starts the next launch."""
+        batches: List[Tuple[int, List[Tuple[int, int]]]] = []
         for gid, src, dst in plan.pages:
-            self.paged[gid][:, dst].copy_(self.paged[gid][:, src])
+            if batches and batches[-1][0] == gid:
+                written = {d for _, d in batches[-1][1]}
+                read = {s_ for s_, _ in batches[-1][1]}
+                if src not in written and dst not in written and dst not in read:
+                    batches[-1][1].append((src, dst))
+                    continue
+            batches.append((gid, [(src, dst)]))
+        for gid, pairs in batches:
+            pool = self.paged[gid]
+            if pool.is_cuda:
+                from ..kernels import ops
+                ops.copy_pages(pool, torch.tensor(pairs, dtype=torch.int32).to(pool.device, non_blocking=True))
+            else:
+                for src, dst in pairs:
+                    pool[:, dst].copy_(pool[:, src])
         if plan.state is not None:
             for t in self.state:
                 t[:, plan.state[1]].copy_(t[:, plan.state[0]])

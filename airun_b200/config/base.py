@@ -67,6 +67,14 @@ class ModelConfig:
     def execution_order(self) -> List[LayerCall]:
         return [LayerCall(i) for i in range(len(self.layer_specs()))]
 
+    def embedding(self) -> Tuple[str, dict]:
+        """(registered name, constructor arguments) of the embedding part, e.g. ("token_embedding", {"scale": 8.0})."""
+        return "token_embedding", {}
+
+    def head(self) -> Tuple[str, dict]:
+        """(registered name, constructor arguments) of the output head, e.g. ("lm_head", {"soft_cap": 30.0})."""
+        return "lm_head", {}
+
 
 _REGISTRY: Dict[str, Tuple[type, Callable]] = {}
 

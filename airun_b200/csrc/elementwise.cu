@@ -12,7 +12,7 @@
 
 template <typename TTab>
 __global__ void embed_kernel(const TTab* __restrict__ table, const int32_t* __restrict__ ids,
-                             float* __restrict__ out, int H, int V, int* __restrict__ err) {
+                             float* __restrict__ out, int H, int V, float scale, int* __restrict__ err) {
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x;
@@ -23,18 +23,19 @@ __global__ void embed_kernel(const TTab* __restrict__ table, const int32_t* __re
     }
     const TTab* src = table + (size_t)id * H;
     float* dst = out + (size_t)t * H;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = to_f32<TTab>(src[i]);
+    // scale 1 (no scaling, as the reference) leaves the value as it is: x * 1.0f is exact
+    for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = to_f32<TTab>(src[i]) * scale;
 }
 
 AIRUN_EXPORT int airun_embed(const void* table, int table_dtype, const int32_t* ids, float* out,
-                             int T, int H, int V, int* err, cudaStream_t stream) {
+                             int T, int H, int V, float scale, int* err, cudaStream_t stream) {
     if (T < 0 || H <= 0 || V <= 0) return AIRUN_ERR_ARG;
     if (T == 0) return AIRUN_OK;
     const int threads = H >= 1024 ? 256 : 128;
     if (table_dtype == AIRUN_DT_F32)
-        airun_launch(embed_kernel<float>, dim3(T), dim3(threads), 0, stream, (const float*)table, ids, out, H, V, err);
+        airun_launch(embed_kernel<float>, dim3(T), dim3(threads), 0, stream, (const float*)table, ids, out, H, V, scale, err);
     else if (table_dtype == AIRUN_DT_BF16)
-        airun_launch(embed_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, (const __nv_bfloat16*)table, ids, out, H, V, err);
+        airun_launch(embed_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, (const __nv_bfloat16*)table, ids, out, H, V, scale, err);
     else
         return AIRUN_ERR_UNSUPPORTED;
     return airun_launch_status();
@@ -48,8 +49,14 @@ AIRUN_EXPORT int airun_embed(const void* table, int table_dtype, const int32_t* 
 template <typename TOut, int VEC>
 __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta,
                                const float* __restrict__ w, TOut* __restrict__ out,
-                               const int32_t* __restrict__ rows, int n, float eps, int write_back) {
+                               const int32_t* __restrict__ rows, int n, float eps, int write_back,
+                               const void* __restrict__ pf_ptr, long long pf_bytes) {
     pdl_trigger();
+    // a few rows keep few SMs busy for a few microseconds: meanwhile the weights of the product that follows
+    // are asked into L2 (they depend on no kernel, so this runs before the wait for the kernel in front)
+    if ((threadIdx.x & 31) == 0)
+        l2_prefetch_slice(pf_ptr, pf_bytes, (int)(blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)),
+                          (int)(gridDim.x * (blockDim.x >> 5)));
     pdl_wait();
     __shared__ float red[33];
     const int r = blockIdx.x;
@@ -191,8 +198,10 @@ __global__ __launch_bounds__(256) void rmsnorm_rows_kernel(float* __restrict__ x
 
 AIRUN_EXPORT int airun_rmsnorm(float* x, const float* delta, const float* w, void* out, int out_dtype,
                                const int32_t* rows, int n_rows, int n, float eps, int write_back,
-                               cudaStream_t stream) {
+                               const void* pf_ptr, long long pf_bytes, cudaStream_t stream) {
     if (n_rows < 0 || n <= 0) return AIRUN_ERR_ARG;
+    if (pf_ptr && (((uintptr_t)pf_ptr & 15) || pf_bytes < 0 || pf_bytes % 16 != 0)) return AIRUN_ERR_ARG;
+    if (!pf_ptr) pf_bytes = 0;
     if (rows && write_back) return AIRUN_ERR_ARG;
     if (n_rows == 0) return AIRUN_OK;
     const bool vec = n % 4 == 0 && (((uintptr_t)x | (uintptr_t)delta) & 15) == 0;
@@ -214,7 +223,7 @@ AIRUN_EXPORT int airun_rmsnorm(float* x, const float* delta, const float* w, voi
     if (threads < 32) threads = 32;
     if (n_rows <= 64 && threads > 256 && vec) threads = 256;      // few rows: more loads in flight per thread
 #define LAUNCH(TOut, VEC) \
-    airun_launch(rmsnorm_kernel<TOut, VEC>, dim3(n_rows), dim3(threads), 0, stream, x, delta, w, (TOut*)out, rows, n, eps, write_back)
+    airun_launch(rmsnorm_kernel<TOut, VEC>, dim3(n_rows), dim3(threads), 0, stream, x, delta, w, (TOut*)out, rows, n, eps, write_back, pf_ptr, pf_bytes)
     if (out_dtype == AIRUN_DT_F32) { if (vec) LAUNCH(float, 4); else LAUNCH(float, 1); }
     else if (out_dtype == AIRUN_DT_BF16) { if (vec) LAUNCH(__nv_bfloat16, 4); else LAUNCH(__nv_bfloat16, 1); }
     else return AIRUN_ERR_UNSUPPORTED;
@@ -331,5 +340,50 @@ AIRUN_EXPORT int airun_fill_random(void* out, int out_dtype, long long n, unsign
     } else {
         return AIRUN_ERR_UNSUPPORTED;
     }
+    return airun_launch_status();
+}
+
+
+// x = cap * tanh(x / cap), in place: a soft limit on logits.  The dense Qwen3 head has none (the
+// reference applies no cap, crates/airun-core/src/runtime.rs:2632-2651); a head part may ask for one.
+__global__ void soft_cap_kernel(float* __restrict__ x, long long n, float cap) {
+    pdl_trigger();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) x[i] = cap * tanhf(x[i] / cap);
+}
+
+AIRUN_EXPORT int airun_soft_cap(float* x, long long n, float cap, cudaStream_t stream) {
+    if (n < 0 || !(cap > 0.0f)) return AIRUN_ERR_ARG;
+    if (n == 0) return AIRUN_OK;
+    const long long blocks = (n + 255) / 256;
+    if (blocks > 0x7fffffffll) return AIRUN_ERR_ARG;
+    airun_launch(soft_cap_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, x, n, cap);
+    return airun_launch_status();
+}
+
+// Copies whole cache pages inside the pools of one cache group: for every pair (src, dst) and every
+// owner layer, page dst = page src.  pool: [owners][pages][page_words] 16-byte words.  Pairs whose
+// ids are outside the pool set the bad-page bit and are skipped.
+__global__ void copy_pages_kernel(uint4* __restrict__ pool, long long owner_words, long long page_words,
+                                  const int32_t* __restrict__ pairs, int num_pages, int* __restrict__ err) {
+    const int src = pairs[2 * blockIdx.x], dst = pairs[2 * blockIdx.x + 1];
+    if (src < 0 || src >= num_pages || dst < 0 || dst >= num_pages) {
+        if (threadIdx.x == 0 && err) atomicOr(err, AIRUN_DEV_BAD_PAGE);
+        return;
+    }
+    const uint4* s = pool + (long long)blockIdx.y * owner_words + (long long)src * page_words;
+    uint4* d = pool + (long long)blockIdx.y * owner_words + (long long)dst * page_words;
+    for (long long i = threadIdx.x; i < page_words; i += blockDim.x) d[i] = s[i];
+}
+
+AIRUN_EXPORT int airun_copy_pages(void* pool, int owners, int num_pages, long long page_bytes, const int32_t* pairs,
+                                  int n_pairs, int* err, cudaStream_t stream) {
+    if (owners <= 0 || num_pages <= 0 || page_bytes <= 0 || page_bytes % 16 != 0 || n_pairs < 0 || ((uintptr_t)pool & 15))
+        return AIRUN_ERR_ARG;
+    if (n_pairs == 0) return AIRUN_OK;
+    if (owners > 65535) return AIRUN_ERR_ARG;
+    copy_pages_kernel<<<dim3(n_pairs, owners), 256, 0, stream>>>((uint4*)pool, (long long)num_pages * (page_bytes / 16),
+                                                                 page_bytes / 16, pairs, num_pages, err);
     return airun_launch_status();
 }

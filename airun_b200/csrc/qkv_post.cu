@@ -7,10 +7,12 @@
 //   per head row h of head_dim values: h = h * rsqrt(sum(h^2)/head_dim + eps) * w
 //   (one weight vector shared by all heads, same eps as the layer norms, before
 //   the rotation; v is not normed);
-//   rotation (NeoX pairing): pair i couples dims i and i + r/2,
-//   theta = pos * inv_freq[i],  x'_i = x_i cos - x_{i+r/2} sin,
-//   x'_{i+r/2} = x_i sin + x_{i+r/2} cos; dims >= r are left alone; the accurate
-//   sincosf is used on purpose (angles reach thousands of radians).
+//   rotation: pair i couples dims lo and hi, theta = rpos * inv_freq[i],
+//   x'_lo = x_lo cos - x_hi sin,  x'_hi = x_lo sin + x_hi cos; dims >= r are left alone; the accurate
+//   sincosf is used on purpose (angles reach thousands of radians).  NeoX pairing: lo = i, hi = i + r/2;
+//   interleaved (GPT-J) pairing: lo = 2i, hi = 2i + 1 (ops.cu:154-157, :176-179 keeps both as a kernel
+//   parameter).  rpos is the token's cache position unless the caller gives rotation positions of
+//   their own (the reference's shift / mpos indirection, airun.cuh:121-143).
 // inv_freq[i] = theta_base^(-2i/r) is computed on the host in double precision
 // and rounded once to float32, so the device and a plain implementation multiply
 // the position by the very same constant.
@@ -23,6 +25,7 @@
 
 #define ROPE_NONE 0
 #define ROPE_NEOX 1
+#define ROPE_INTERLEAVED 2
 #define MAX_PER_LANE 8   // head_dim <= 256
 
 // DPL: values of a head per lane, ceil(head_dim / 32) rounded up to 1, 2, 4 or 8.
@@ -32,11 +35,14 @@ __global__ __launch_bounds__(256) void qkv_post_kernel(
     TQ* __restrict__ q_out,
     const float* __restrict__ q_norm_w, const float* __restrict__ k_norm_w, float eps,
     const int32_t* __restrict__ positions, const int32_t* __restrict__ req_of_token,
-    int rope_kind, int rotary_dim, const float* __restrict__ inv_freq,
+    int rope_kind, int rotary_dim, const float* __restrict__ inv_freq, const int32_t* __restrict__ rope_positions,
     TKV* __restrict__ pool, const int32_t* __restrict__ block_table, int max_blocks,
     int num_reqs, int num_pages, int page_size, int do_store, int kv_from_qkv,
-    int nh, int nkv, int hd, int* __restrict__ err) {
+    int nh, int nkv, int hd, int* __restrict__ err, const void* __restrict__ pf_ptr, long long pf_bytes) {
     pdl_trigger();
+    if ((threadIdx.x & 31) == 0)           // weights of a later product into L2 while this small kernel runs
+        l2_prefetch_slice(pf_ptr, pf_bytes, (int)((blockIdx.x * gridDim.y + blockIdx.y) * (blockDim.x >> 5) + (threadIdx.x >> 5)),
+                          (int)(gridDim.x * gridDim.y * (blockDim.x >> 5)));
     pdl_wait();
     extern __shared__ float smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -48,10 +54,11 @@ __global__ __launch_bounds__(256) void qkv_post_kernel(
     const int req = req_of_token[t];
     const int total_heads = kv_from_qkv ? nh + 2 * nkv : nh;
     const int half = rotary_dim / 2;
-    if (rope_kind == ROPE_NEOX) {
+    if (rope_kind != ROPE_NONE) {
+        const int rpos = rope_positions ? rope_positions[t] : pos;
         for (int i = threadIdx.x; i < half; i += blockDim.x) {
             float s, c;
-            sincosf((float)pos * inv_freq[i], &s, &c);
+            sincosf((float)rpos * inv_freq[i], &s, &c);
             cs[i] = c;
             cs[half + i] = s;
         }
@@ -80,7 +87,7 @@ __global__ __launch_bounds__(256) void qkv_post_kernel(
                 if (d < hd) x[i] = x[i] * inv * w[d];
             }
         }
-        if (rope_kind == ROPE_NEOX && (is_q || is_k)) {
+        if (rope_kind != ROPE_NONE && (is_q || is_k)) {
             __syncwarp();
 #pragma unroll
             for (int i = 0; i < DPL; ++i) {
@@ -92,9 +99,10 @@ __global__ __launch_bounds__(256) void qkv_post_kernel(
             for (int i = 0; i < DPL; ++i) {
                 const int d = lane + i * 32;
                 if (d < rotary_dim && d < hd) {
-                    const bool first = d < half;
-                    const int pair = first ? d : d - half;
-                    const int other = first ? d + half : d - half;
+                    const bool neox = rope_kind == ROPE_NEOX;
+                    const bool first = neox ? d < half : (d & 1) == 0;
+                    const int pair = neox ? (first ? d : d - half) : d >> 1;
+                    const int other = neox ? (first ? d + half : d - half) : d ^ 1;
                     const float c = cs[pair], s = cs[half + pair];
                     const float x0 = first ? row[d] : row[other];
                     const float x1 = first ? row[other] : row[d];
@@ -145,8 +153,11 @@ __global__ __launch_bounds__(256) void qkv_post_hd128_kernel(
     const float* __restrict__ inv_freq,
     TKV* __restrict__ pool, const int32_t* __restrict__ block_table, int max_blocks,
     int num_reqs, int num_pages, int page_size, int do_store, int kv_from_qkv,
-    int nh, int nkv, int* __restrict__ err) {
+    int nh, int nkv, int* __restrict__ err, const void* __restrict__ pf_ptr, long long pf_bytes) {
     pdl_trigger();
+    if ((threadIdx.x & 31) == 0)           // weights of a later product into L2 while this small kernel runs
+        l2_prefetch_slice(pf_ptr, pf_bytes, (int)((blockIdx.x * gridDim.y + blockIdx.y) * (blockDim.x >> 5) + (threadIdx.x >> 5)),
+                          (int)(gridDim.x * gridDim.y * (blockDim.x >> 5)));
     constexpr int HD = 128, HALF = 64;
     __shared__ float cs[2 * HALF];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -241,11 +252,14 @@ AIRUN_EXPORT int airun_qkv_post(
     const float* qkv, long long ld_qkv, void* q_out, int q_dtype,
     const float* q_norm_w, const float* k_norm_w, float eps,
     const int32_t* positions, const int32_t* req_of_token, int T,
-    int rope_kind, int rotary_dim, const float* inv_freq,
+    int rope_kind, int rotary_dim, const float* inv_freq, const int32_t* rope_positions,
     void* pool, int kv_dtype, const int32_t* block_table, int max_blocks, int num_reqs,
     int num_pages, int page_size, int do_store, int kv_from_qkv,
-    int nh, int nkv, int hd, int* err, cudaStream_t stream) {
+    int nh, int nkv, int hd, int* err, const void* pf_ptr, long long pf_bytes, cudaStream_t stream) {
     if (T < 0 || nh <= 0 || nkv <= 0 || hd <= 0 || hd > 32 * MAX_PER_LANE) return AIRUN_ERR_ARG;
+    if (pf_ptr && (((uintptr_t)pf_ptr & 15) || pf_bytes < 0 || pf_bytes % 16 != 0)) return AIRUN_ERR_ARG;
+    if (!pf_ptr) pf_bytes = 0;
+    if (rope_kind != ROPE_NONE && rope_kind != ROPE_NEOX && rope_kind != ROPE_INTERLEAVED) return AIRUN_ERR_UNSUPPORTED;
     if (rope_kind != ROPE_NONE && (rotary_dim <= 0 || rotary_dim > hd || rotary_dim % 2 != 0 || !inv_freq))
         return AIRUN_ERR_ARG;
     if (do_store && (page_size <= 0 || num_pages <= 0 || !pool || !block_table || !err)) return AIRUN_ERR_ARG;
@@ -258,14 +272,14 @@ AIRUN_EXPORT int airun_qkv_post(
     const int blocks_y = T <= 64 ? (heads + warps - 1) / warps : 1;
     const size_t smem = ((size_t)warps * hd + (rope_kind != ROPE_NONE ? rotary_dim : 0)) * sizeof(float);
     // head_dim 128, both norms, the rotation over the whole head, 16-byte aligned rows: the vector kernel
-    const bool vec128 = hd == 128 && rope_kind == ROPE_NEOX && rotary_dim == 128 && q_norm_w && k_norm_w &&
+    const bool vec128 = hd == 128 && rope_kind == ROPE_NEOX && rotary_dim == 128 && !rope_positions && q_norm_w && k_norm_w &&
                         ld_qkv % 4 == 0 && (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)pool |
                                              (uintptr_t)q_norm_w | (uintptr_t)k_norm_w) & 15) == 0;
     if (vec128) {
 #define LAUNCH128(TQ, TKV) \
     airun_launch(qkv_post_hd128_kernel<TQ, TKV>, dim3(T, blocks_y), dim3(warps * 32), 0, stream, qkv, ld_qkv, (TQ*)q_out, \
         q_norm_w, k_norm_w, eps, positions, req_of_token, inv_freq, (TKV*)pool, block_table, max_blocks, num_reqs, \
-        num_pages, page_size, do_store, kv_from_qkv, nh, nkv, err)
+        num_pages, page_size, do_store, kv_from_qkv, nh, nkv, err, pf_ptr, pf_bytes)
         if (q_dtype == AIRUN_DT_F32) LAUNCH128(float, float);
         else if (q_dtype == AIRUN_DT_BF16) LAUNCH128(__nv_bfloat16, __nv_bfloat16);
         else return AIRUN_ERR_UNSUPPORTED;
@@ -274,8 +288,8 @@ AIRUN_EXPORT int airun_qkv_post(
     }
 #define LAUNCH(TQ, TKV, DPL) \
     airun_launch(qkv_post_kernel<TQ, TKV, DPL>, dim3(T, blocks_y), dim3(warps * 32), smem, stream, qkv, ld_qkv, (TQ*)q_out, q_norm_w, k_norm_w, eps, \
-        positions, req_of_token, rope_kind, rotary_dim, inv_freq, (TKV*)pool, block_table, max_blocks, num_reqs, \
-        num_pages, page_size, do_store, kv_from_qkv, nh, nkv, hd, err)
+        positions, req_of_token, rope_kind, rotary_dim, inv_freq, rope_positions, (TKV*)pool, block_table, max_blocks, num_reqs, \
+        num_pages, page_size, do_store, kv_from_qkv, nh, nkv, hd, err, pf_ptr, pf_bytes)
 #define LAUNCH_DPL(TQ, TKV) \
     do { if (hd <= 32) LAUNCH(TQ, TKV, 1); else if (hd <= 64) LAUNCH(TQ, TKV, 2); \
          else if (hd <= 128) LAUNCH(TQ, TKV, 4); else LAUNCH(TQ, TKV, 8); } while (0)

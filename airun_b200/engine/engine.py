@@ -106,19 +106,29 @@ class Engine:
         self._picked_host = torch.zeros(R + 1, dtype=torch.int32, pin_memory=self.device.type == "cuda")
         self.stats = GenerationStats()
         self._ahead = None        # (requests, prepared step): the next decode step, laid out while this one runs
+        self._host_rows = None    # buffers for the logits rows the host samples
 
     # ------------------------------------------------------------ construction
     @staticmethod
     def _tokens_that_fit(specs, cache_from, o: EngineOptions) -> int:
-        from ..parts.base import PagedKVSpec
+        """Tokens of cache the free memory holds: ``memory_fraction`` of it, less the fixed-size state of
+        ``max_requests`` requests, over the bytes a token takes in all paged layers."""
+        from ..parts.base import PagedKVSpec, StateSpec
         dt = _DTYPES[o.dtype]
         esz = 2 if dt == torch.bfloat16 else 4
         per_token = sum(2 * s.num_kv_heads * s.head_dim * esz
                         for s, src in zip(specs, cache_from) if isinstance(s, PagedKVSpec) and src is None)
         if per_token == 0:
             return o.page_size
+        state = 0
+        for s, src in zip(specs, cache_from):
+            if isinstance(s, StateSpec) and src is None:
+                n = torch.empty((), dtype=s.dtype).element_size()
+                for d in s.shape:
+                    n *= int(d)
+                state += n * o.max_requests
         free, _ = torch.cuda.mem_get_info(torch.device(o.device))
-        return max(o.page_size, int(free * o.memory_fraction) // per_token)
+        return max(o.page_size, (int(free * o.memory_fraction) - state) // per_token)
 
     @classmethod
     def from_folder(cls, model_dir: str, options: Optional[EngineOptions] = None, **kw) -> "Engine":
@@ -217,8 +227,6 @@ class Engine:
         for e in plan.entries:
             toks = e.request.token_slice(e.start, e.count)
             entries.append(StepEntry(e.request.rid, toks, (e.count - 1,) if e.wants_logits else ()))
-            if e.start == 0 and self.storage.state:
-                self.storage.zero_state_slot(self.manager.get(e.request.rid).slot)   # a request starts from zero state
             if e.wants_logits:
                 wanting.append(e.request)
         if prep is not None:
@@ -288,7 +296,7 @@ class Engine:
         self._picked_dev[R:R + 1].copy_(self.runner.err)
         self._picked_host.copy_(self._picked_dev, non_blocking=True)
         host_rows = [i for i, r in enumerate(reqs) if not r.params.device_ok]
-        rows_host = logits[host_rows].cpu().numpy() if host_rows else None
+        rows_host = self._rows_to_host(logits, host_rows) if host_rows else None
         if look_ahead and not host_rows and self._ahead is None:
             self._prepare_ahead(reqs)                      # the GPU is busy: plan and lay out the next step meanwhile
         torch.cuda.current_stream().synchronize()
@@ -302,6 +310,23 @@ class Engine:
             for i, tok in zip(host_rows, picked_host):
                 out[i] = tok
         return out
+
+    def _rows_to_host(self, logits: torch.Tensor, rows: List[int]) -> np.ndarray:
+        """The logits of the rows the host samples: gathered by the engine's own kernel into one buffer
+        and copied to pinned memory in one transfer (queued; the caller synchronises the stream)."""
+        n, V = len(rows), logits.shape[1]
+        if self._host_rows is None or self._host_rows[0].shape[0] < n:
+            cap = max(n, min(self.runner.R_max, 8))
+            self._host_rows = (torch.empty((cap, V), dtype=torch.float32, device=self.device),
+                               torch.empty((cap, V), dtype=torch.float32, pin_memory=True),
+                               torch.empty(cap, dtype=torch.int32, pin_memory=True),
+                               torch.empty(cap, dtype=torch.int32, device=self.device))
+        dev, host, idx_host, idx_dev = self._host_rows
+        idx_host[:n] = torch.as_tensor(rows, dtype=torch.int32)
+        idx_dev[:n].copy_(idx_host[:n], non_blocking=True)
+        ops.gather_rows(logits, idx_dev[:n], dev)
+        host[:n].copy_(dev[:n], non_blocking=True)
+        return host[:n].numpy()
 
     # ------------------------------------------------------------ generation
     def generate(self, prompts: Union[Sequence[int], Sequence[Sequence[int]]],

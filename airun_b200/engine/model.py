@@ -18,8 +18,9 @@ from typing import Dict, List, Optional, Tuple
 import torch
 
 from ..config.base import LayerCall, ModelConfig
+from .batch import WeightStream
 from ..parts.base import make_part
-from ..parts.embedding import LMHead, TokenEmbedding
+from ..parts import embedding as _embedding_parts      # noqa: F401  (registers the embedding and head parts)
 from ..weights.loader import (DictSource, TensorSource, WeightSpec, load_tensors, random_tensors)
 
 # AIRUN_TRACE_LAYERS=1 prints the residual stream's rms and mean after every block (the reference's
@@ -41,7 +42,9 @@ class DecoderModel:
         self.names = names
         V, H = config.vocab_size, config.hidden_size
         self.V, self.H = V, H
-        self.embedding = TokenEmbedding(names["embed"], V, H)
+        emb_name, emb_args = config.embedding() if hasattr(config, "embedding") else ("token_embedding", {})
+        self.embedding = make_part("embedding", emb_name, prefix=names["embed"], vocab_size=V, hidden_size=H,
+                                   dtype=dtype, device=self.device, **emb_args)
         self.layers = []
         for i, spec in enumerate(config.layer_specs()):
             p = names["layer"].format(i=i)
@@ -61,7 +64,9 @@ class DecoderModel:
         self.final_norm = make_part("norm", fn_name, prefix=names["final_norm"], dtype=dtype,
                                     device=self.device, **fn_args)
         tied = bool(getattr(config, "tie_word_embeddings", False))
-        self.head = LMHead(names["head"], V, H, self.embedding if tied else None)
+        head_name, head_args = config.head() if hasattr(config, "head") else ("lm_head", {})
+        self.head = make_part("head", head_name, prefix=names["head"], vocab_size=V, hidden_size=H,
+                              tied_to=self.embedding if tied else None, dtype=dtype, device=self.device, **head_args)
         self.tied = tied
 
     # ---- weights ----
@@ -79,6 +84,15 @@ class DecoderModel:
         tensors = load_tensors(self.weight_specs(), source, self.dtype, self.device, self.ignorable_tensors())
         for p in self.parts():
             p.load_weights(tensors)
+        self.weight_stream = None
+        if self.dtype == torch.bfloat16 and self.device.type == "cuda":
+            from ..kernels import fast
+            if fast.PREFETCH_ON:
+                # the matrices of one pass in the order it reads them: every entry of the execution order, then the head
+                ws = [w for c in self.order for w in getattr(self.layers[c.layer], "stream_weights", lambda: [])()]
+                ws += getattr(self.head, "stream_weights", lambda: [])()
+                if ws:
+                    self.weight_stream = WeightStream([w for w in ws if w is not None])
 
     def load_random(self, seed: int) -> None:
         """Seeded random weights made on the model's device, through the same loading path."""
@@ -106,6 +120,12 @@ class DecoderModel:
     def forward(self, ctx, want_rows: Optional[torch.Tensor], n_want: int) -> Optional[torch.Tensor]:
         T = ctx.num_tokens
         ctx.ws_main.reset()
+        ctx.weights = None
+        if getattr(self, "weight_stream", None) is not None:
+            from ..kernels import fast
+            if T <= fast.PREFETCH_MAX_TOKENS:
+                self.weight_stream.reset()
+                ctx.weights = self.weight_stream
         x = ctx.ws_main.alloc((T, self.H), torch.float32)
         self.embedding.forward(ctx, ctx.token_ids[:T], x)
         delta = None

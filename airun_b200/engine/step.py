@@ -136,6 +136,18 @@ class StepRunner:
     def reserve(self, entries: Sequence[StepEntry]) -> None:
         """Takes the pages of all entries, or of none."""
         self.manager.reserve_many([e.rid for e in entries], [len(e.tokens) for e in entries])
+        self._start_requests(entries)
+
+    def _start_requests(self, entries: Sequence[StepEntry]) -> None:
+        """A request whose first tokens arrive starts from zero state: its slot of every fixed-size state
+        tensor is cleared before the step runs (the slot may have served another request before).  The
+        step function owns this rule, so no caller has to know it; a forked request arrives with tokens
+        and keeps the copy of its parent's state."""
+        if self.storage.state:
+            for e in entries:
+                rc = self.manager.get(e.rid)
+                if rc.num_tokens == 0:
+                    self.storage.zero_state_slot(rc.slot)
 
     def build_context(self, entries: Sequence[StepEntry], pad_to: int = 0, pad_want: int = 0) -> tuple:
         """Fills the staging buffer and returns (StepContext, n_want).  With ``pad_to`` the
@@ -211,6 +223,7 @@ class StepRunner:
             if bucket is None or (bucket not in self.graphs and ("shared", bucket) not in self.graphs):
                 return None
             self.manager.reserve_many(rids, counts)
+            self._start_requests(entries)
             ctx, _ = self.build_context(entries, pad_to=bucket)
             key, n_want = self._decode_key(ctx, bucket), n
         else:
@@ -220,6 +233,7 @@ class StepRunner:
             if key not in self.graphs:
                 return None
             self.manager.reserve_many(rids, counts)
+            self._start_requests(entries)
             self.build_context(entries, pad_to=tb, pad_want=wb)
         if key not in self.graphs:
             return None                 # (the pages are taken and the lay-out is unused: the ordinary path redoes it)

@@ -20,7 +20,7 @@ import torch
 from ..csrc import build
 
 DT_F32, DT_BF16 = 0, 1
-ROPE_NONE, ROPE_NEOX = 0, 1
+ROPE_NONE, ROPE_NEOX, ROPE_INTERLEAVED = 0, 1, 2
 _DT = {torch.float32: DT_F32, torch.bfloat16: DT_BF16}
 
 DEV_ERR_BITS = {1: "a block-table entry outside the page pool", 2: "a token naming a request outside the batch",
@@ -93,8 +93,9 @@ def required_libraries(dtype: torch.dtype, head_dim: int):
 
 
 # ---------------------------------------------------------------- elementwise
-def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, err: Optional[torch.Tensor] = None) -> None:
-    """out[t] = table[ids[t]] widened to float32."""
+def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, err: Optional[torch.Tensor] = None,
+          scale: float = 1.0) -> None:
+    """out[t] = table[ids[t]] widened to float32 (times ``scale``; 1 leaves the values as they are)."""
     _cuda(table, ids, out, err)
     _need(table.dim() == 2 and table.is_contiguous(), "embedding table must be a contiguous [V, H] tensor")
     _need(ids.dtype == torch.int32 and ids.dim() == 1 and ids.is_contiguous(), "ids must be int32 [T]")
@@ -102,17 +103,41 @@ def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, err: Option
     _need(out.dtype == torch.float32 and tuple(out.shape) == (T, H) and out.is_contiguous(),
           "embedding output must be float32 [T, H]")
     f = _fn("elementwise", "airun_embed",
-            [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p])
-    _check(f(_p(table), _dt(table), _p(ids), _p(out), T, H, V, _p(err), _stream()), "embed")
+            [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_void_p])
+    _check(f(_p(table), _dt(table), _p(ids), _p(out), T, H, V, float(scale), _p(err), _stream()), "embed")
+
+
+def soft_cap(x: torch.Tensor, cap: float) -> None:
+    """x = cap * tanh(x / cap), in place."""
+    _cuda(x)
+    _need(x.dtype == torch.float32 and x.is_contiguous(), "soft_cap takes a contiguous float32 tensor")
+    _need(cap > 0.0, "the cap must be positive")
+    f = _fn("elementwise", "airun_soft_cap", [c_void_p, c_longlong, c_float, c_void_p])
+    _check(f(_p(x), x.numel(), float(cap), _stream()), "soft_cap")
+
+
+def copy_pages(pool: torch.Tensor, pairs: torch.Tensor, err: Optional[torch.Tensor] = None) -> None:
+    """pool: [owners, pages, ...] cache pages of one group; pairs: int32 [n, 2] (source page, destination page) on
+    the device.  Every owner layer's page ``dst`` becomes a copy of its page ``src``."""
+    _cuda(pool, pairs, err)
+    _need(pool.dim() >= 3 and pool.is_contiguous(), "pool must be contiguous [owners, pages, ...]")
+    _need(pairs.dtype == torch.int32 and pairs.dim() == 2 and pairs.shape[1] == 2 and pairs.is_contiguous(),
+          "pairs must be int32 [n, 2]")
+    page_bytes = pool[0, 0].numel() * pool.element_size()
+    _need(page_bytes % 16 == 0, "a page must be a multiple of 16 bytes")
+    f = _fn("elementwise", "airun_copy_pages", [c_void_p, c_int, c_int, c_longlong, c_void_p, c_int, c_void_p, c_void_p])
+    _check(f(_p(pool), pool.shape[0], pool.shape[1], page_bytes, _p(pairs), pairs.shape[0], _p(err), _stream()), "copy_pages")
 
 
 def rmsnorm(x: torch.Tensor, weight: Optional[torch.Tensor], eps: float, out: torch.Tensor,
-            delta: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None) -> None:
+            delta: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None,
+            prefetch=(0, 0)) -> None:
     """out = rmsnorm(x [+ delta]) * weight.
 
     With ``delta`` and no ``rows`` the sum is written back into ``x`` (the
     residual stream).  With ``rows`` only those rows are normed, into
-    out[0..len(rows)), and ``x`` is left as it is.
+    out[0..len(rows)), and ``x`` is left as it is.  ``prefetch``: (address, bytes) of weights a later
+    product reads, asked into L2 meanwhile (StepContext.prefetch; used when few rows are normed).
     """
     _cuda(x, weight, out, delta, rows)
     _need(x.dtype == torch.float32 and x.dim() == 2 and x.is_contiguous(), "x must be float32 [T, n]")
@@ -130,10 +155,11 @@ def rmsnorm(x: torch.Tensor, weight: Optional[torch.Tensor], eps: float, out: to
     _need(out.dim() == 2 and out.shape[0] >= n_rows and out.shape[1] == n and out.is_contiguous(),
           "norm output must be [rows, n]")
     f = _fn("elementwise", "airun_rmsnorm",
-            [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_int, c_void_p])
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_int, c_void_p,
+             c_longlong, c_void_p])
     write_back = 1 if (delta is not None and rows is None) else 0
     _check(f(_p(x), _p(delta), _p(weight), _p(out), _dt(out), _p(rows), n_rows, n, float(eps), write_back,
-             _stream()), "rmsnorm")
+             c_void_p(prefetch[0] or None), int(prefetch[1]), _stream()), "rmsnorm")
 
 
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor, group: int) -> None:
@@ -183,11 +209,17 @@ def qkv_post(qkv: torch.Tensor, q_out: torch.Tensor, q_norm_w: Optional[torch.Te
              req_of_token: torch.Tensor, rope_kind: int, rotary_dim: int, inv_freq: Optional[torch.Tensor],
              pool: Optional[torch.Tensor], block_table: Optional[torch.Tensor], num_reqs: int,
              page_size: int, nh: int, nkv: int, hd: int, err: torch.Tensor,
-             store: bool = True, kv_in_row: bool = True) -> None:
+             store: bool = True, kv_in_row: bool = True, rope_positions: Optional[torch.Tensor] = None,
+             prefetch=(0, 0)) -> None:
     """Per-head norm, rotary encoding, q out, k/v into their pages (see csrc/qkv_post.cu).
 
-    ``pool`` is one layer's pages [num_pages, 2, nkv, page_size, hd]."""
-    _cuda(qkv, q_out, q_norm_w, k_norm_w, positions, req_of_token, inv_freq, pool, block_table, err)
+    ``pool`` is one layer's pages [num_pages, 2, nkv, page_size, hd].  ``rope_kind``: ROPE_NONE, ROPE_NEOX
+    (pair i couples dims i and i + r/2) or ROPE_INTERLEAVED (dims 2i and 2i + 1).  ``rope_positions``
+    (int32 [T]): the position each row is rotated by, when that is not its place in the cache."""
+    _cuda(qkv, q_out, q_norm_w, k_norm_w, positions, req_of_token, inv_freq, pool, block_table, err, rope_positions)
+    if rope_positions is not None:
+        _need(rope_positions.dtype == torch.int32 and rope_positions.is_contiguous() and rope_positions.shape[0] >= qkv.shape[0],
+              "rope_positions must be int32 [T]")
     T = qkv.shape[0]
     width = (nh + 2 * nkv) * hd if kv_in_row else nh * hd
     _need(qkv.dtype == torch.float32 and qkv.dim() == 2 and qkv.shape[1] == width and qkv.stride(1) == 1,
@@ -213,12 +245,13 @@ def qkv_post(qkv: torch.Tensor, q_out: torch.Tensor, q_norm_w: Optional[torch.Te
         num_pages, max_blocks = pool.shape[0], block_table.stride(0)
     f = _fn("qkv_post", "airun_qkv_post",
             [c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int,
-             c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-             c_int, c_int, c_int, c_void_p, c_void_p])
+             c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+             c_int, c_int, c_int, c_void_p, c_void_p, c_longlong, c_void_p])
     _check(f(_p(qkv), qkv.stride(0), _p(q_out), _dt(q_out), _p(q_norm_w), _p(k_norm_w), float(eps),
-             _p(positions), _p(req_of_token), T, int(rope_kind), int(rotary_dim), _p(inv_freq),
+             _p(positions), _p(req_of_token), T, int(rope_kind), int(rotary_dim), _p(inv_freq), _p(rope_positions),
              _p(pool), _dt(q_out), _p(block_table), max_blocks, int(num_reqs), num_pages, int(page_size),
-             1 if do_store else 0, 1 if kv_in_row else 0, nh, nkv, hd, _p(err), _stream()), "qkv_post")
+             1 if do_store else 0, 1 if kv_in_row else 0, nh, nkv, hd, _p(err), c_void_p(prefetch[0] or None),
+             int(prefetch[1]), _stream()), "qkv_post")
 
 
 def attention_generic(q: torch.Tensor, out: torch.Tensor, pool: torch.Tensor, block_table: torch.Tensor,

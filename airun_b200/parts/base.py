@@ -16,7 +16,10 @@ Part            weight_specs() -> [WeightSpec];  load_weights(tensors: dict) -> 
 Norm            forward(ctx, x, out, delta=None, rows=None)
                   out = norm(x [+ delta]); with delta and no rows, x += delta in place
 PositionEncoding fused() -> (kind, rotary_dim, inv_freq) the attention prologue
-                  kernel understands
+                  kernel understands (none, NeoX pairing, interleaved pairing);
+                rotation_positions(ctx) -> int32 [T] or None (None: the cache positions)
+Embedding       forward(ctx, token_ids, out float32 [T, hidden]); .table for a tied head
+Head            forward(ctx, h [rows, hidden], out float32 [rows, vocab])
 Mixer           cache_spec() -> PagedKVSpec | StateSpec | None
                 forward(ctx, h, cache) -> float32 [T, hidden] (the residual delta)
 FeedForward     forward(ctx, h) -> float32 [T, hidden]
@@ -103,7 +106,32 @@ class Norm(Part):
 
 class PositionEncoding(Part):
     def fused(self) -> Optional[Tuple[int, int, Optional[torch.Tensor]]]:
+        """(kind, rotary_dim, inv_freq) for the q/k prologue kernel: kind is ops.ROPE_NONE, ops.ROPE_NEOX
+        (pair i couples dims i and i + r/2) or ops.ROPE_INTERLEAVED (dims 2i and 2i + 1)."""
         return None
+
+    def rotation_positions(self, ctx) -> Optional[torch.Tensor]:
+        """int32 [T] on the device: the position every row of the step is rotated by, when that is not
+        its place in the cache (positions that restart after an inserted block, say); None: the cache
+        positions ``ctx.positions``.  To stay replayable from a CUDA graph the tensor must be made from
+        device arrays of ``ctx`` by kernels, at the same address for every step of a shape."""
+        return None
+
+
+class Embedding(Part):
+    """forward(ctx, token_ids int32 [T], out float32 [T, hidden]); ``table`` is the [vocab, hidden]
+    matrix a tied head may use."""
+    table: Optional[torch.Tensor] = None
+
+    def forward(self, ctx, token_ids: torch.Tensor, out: torch.Tensor) -> None:
+        raise NotImplementedError
+
+
+class Head(Part):
+    """forward(ctx, h [rows, hidden] in the compute type, out float32 [rows, vocab])."""
+
+    def forward(self, ctx, h: torch.Tensor, out: torch.Tensor) -> None:
+        raise NotImplementedError
 
 
 class Mixer(Part):
@@ -120,7 +148,7 @@ class FeedForward(Part):
 
 
 _REGISTRIES: Dict[str, Dict[str, Callable]] = {
-    "mixer": {}, "feed_forward": {}, "norm": {}, "position": {}, "arrangement": {}}
+    "mixer": {}, "feed_forward": {}, "norm": {}, "position": {}, "arrangement": {}, "embedding": {}, "head": {}}
 
 
 def register_part(kind: str, name: str, factory: Callable) -> None:

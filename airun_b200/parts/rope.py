@@ -18,6 +18,8 @@ from .base import PositionEncoding, register_part
 
 
 class RotaryNeox(PositionEncoding):
+    kind = ops.ROPE_NEOX
+
     def __init__(self, prefix: str = "", rotary_dim: int = 0, theta: float = 10000.0,
                  dtype=None, device=None):
         if rotary_dim <= 0 or rotary_dim % 2:
@@ -28,7 +30,14 @@ class RotaryNeox(PositionEncoding):
         self.inv_freq = inv.to(torch.float32).to(device)
 
     def fused(self) -> Optional[Tuple[int, int, Optional[torch.Tensor]]]:
-        return ops.ROPE_NEOX, self.rotary_dim, self.inv_freq
+        return self.kind, self.rotary_dim, self.inv_freq
+
+
+class RotaryInterleaved(RotaryNeox):
+    """The same angles with the older pairing of neighbouring dimensions (2i, 2i + 1), which the reference
+    keeps as a kernel parameter beside the NeoX pairing (crates/airun-cuda/kernels/ops.cu:154-157, :176-179).
+    The dense Qwen3 decoder does not use it."""
+    kind = ops.ROPE_INTERLEAVED
 
 
 class NoPosition(PositionEncoding):
@@ -40,4 +49,5 @@ class NoPosition(PositionEncoding):
 
 
 register_part("position", "rotary_neox", RotaryNeox)
+register_part("position", "rotary_interleaved", RotaryInterleaved)
 register_part("position", "none", NoPosition)

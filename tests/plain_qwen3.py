@@ -96,6 +96,24 @@ def plain_rope_neox(x: torch.Tensor, positions: Sequence[int], theta: float, rot
     return out
 
 
+def plain_rope_interleaved(x: torch.Tensor, positions: Sequence[int], theta: float, rotary_dim: int) -> torch.Tensor:
+    """The same angles with the older pairing: pair i couples dims 2i and 2i + 1
+    (crates/airun-cuda/kernels/ops.cu:154-157, :176-183).  Not used by the dense Qwen3 decoder; here for
+    parts that ask the fused prologue for it."""
+    T, heads, hd = x.shape
+    out = x.clone()
+    fdt = torch.float32 if x.dtype == torch.float32 else torch.float64
+    pos = torch.tensor([float(p) for p in positions], dtype=fdt)
+    for i in range(rotary_dim // 2):
+        inv_freq = torch.tensor(float(theta) ** (-2.0 * i / rotary_dim), dtype=torch.float64).to(fdt)
+        ang = pos * inv_freq
+        c, s = torch.cos(ang).to(x.dtype)[:, None], torch.sin(ang).to(x.dtype)[:, None]
+        x0, x1 = x[:, :, 2 * i], x[:, :, 2 * i + 1]
+        out[:, :, 2 * i] = x0 * c - x1 * s
+        out[:, :, 2 * i + 1] = x0 * s + x1 * c
+    return out
+
+
 def plain_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, positions: Sequence[int],
                     scale: float, window: int) -> torch.Tensor:
     """q: [T, nh, hd]; k, v: [T, nkv, hd] of one whole sequence.  Head h reads KV head

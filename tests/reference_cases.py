@@ -98,9 +98,11 @@ def _norm_case(n: int, rows: int, eps: float, seed: int) -> Case:
 
 
 # ----------------------------------------------------------------------------- q/k norm + rotation + cache write
-def _prologue_case(nh: int, nkv: int, hd: int, positions: List[int], theta: float, eps: float, seed: int) -> Case:
+def _prologue_case(nh: int, nkv: int, hd: int, positions: List[int], theta: float, eps: float, seed: int,
+                   interleaved: bool = False) -> Case:
     max_seq = 64
     T = len(positions)
+    rope = P.plain_rope_interleaved if interleaved else P.plain_rope_neox
 
     def make():
         g = np.random.default_rng(seed)
@@ -110,8 +112,8 @@ def _prologue_case(nh: int, nkv: int, hd: int, positions: List[int], theta: floa
 
     def plain(d):
         q, k, v, qn, kn = (torch.from_numpy(d[n]) for n in ("q", "k", "v", "qn", "kn"))
-        qo = P.plain_rope_neox(P.plain_rmsnorm(q, qn, eps), positions, theta, hd)
-        ko = P.plain_rope_neox(P.plain_rmsnorm(k, kn, eps), positions, theta, hd)
+        qo = rope(P.plain_rmsnorm(q, qn, eps), positions, theta, hd)
+        ko = rope(P.plain_rmsnorm(k, kn, eps), positions, theta, hd)
         return dict(q=qo.numpy(), k_rows=_f16(ko.numpy()), v_rows=_f16(v.numpy()))
 
     def reference(d):
@@ -120,7 +122,8 @@ def _prologue_case(nh: int, nkv: int, hd: int, positions: List[int], theta: floa
         kc = torch.zeros(nkv, max_seq, hd, dtype=torch.float16, device="cuda:0")
         vc = torch.zeros_like(kc)
         pos = _dev(np.asarray(positions, dtype=np.int32))
-        rk.qk_norm_rope_store(q, k, v, qn, kn, kc, vc, pos, T, nh, nkv, hd, max_seq, eps, hd, theta)
+        rk.qk_norm_rope_store(q, k, v, qn, kn, kc, vc, pos, T, nh, nkv, hd, max_seq, eps, hd, theta,
+                              interleaved=interleaved)
         torch.cuda.synchronize()
         rows = torch.tensor(positions, device="cuda:0")
         untouched = torch.ones(max_seq, dtype=torch.bool, device="cuda:0")
@@ -131,7 +134,8 @@ def _prologue_case(nh: int, nkv: int, hd: int, positions: List[int], theta: floa
                     v_rows=vc[:, rows].permute(1, 0, 2).float().cpu().numpy())
 
     # float16 storage of values up to ~2: half an ulp is 5e-4; the rotation's sincosf and powf are accurate
-    return Case(f"qk_norm_rope_store_{nh}_{nkv}_{hd}", make, plain, reference, atol=1.2e-3, rtol=0.0)
+    return Case(f"qk_norm_rope_store_{nh}_{nkv}_{hd}" + ("_interleaved" if interleaved else ""), make, plain, reference,
+                atol=1.2e-3, rtol=0.0)
 
 
 def _rope_case(hd: int, rotary: int, theta: float, seed: int) -> Case:
@@ -419,6 +423,7 @@ def all_cases() -> List[Case]:
         _prologue_case(8, 2, 128, [3, 17, 40, 41, 63], 1e6, 1e-6, 4),
         _prologue_case(8, 1, 32, [0, 1, 2, 31, 62], 1e6, 1e-5, 5),
         _prologue_case(4, 2, 64, [5, 6, 7, 8, 9, 10], 1e4, 1e-6, 6),
+        _prologue_case(4, 2, 64, [0, 9, 33, 63], 1e4, 1e-6, 9, interleaved=True),
         _rope_case(128, 128, 1e6, 7), _rope_case(64, 32, 1e4, 8),
         _attention_case(8, 2, 64, few, 0, 10, "8_2_64_few"),
         _attention_case(16, 2, 128, few, 0, 11, "16_2_128_few"),

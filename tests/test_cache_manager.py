@@ -427,3 +427,19 @@ def test_batch_layout_of_random_steps(seed):
         for r, q in zip(rids, qlens):
             held[r] += q
         m.check_invariants()
+
+
+def test_fixed_size_state_is_taken_off_the_memory_the_pages_get(monkeypatch):
+    """The cache size worked out from free memory leaves room for the state slots of every request."""
+    import torch
+    from airun_b200.engine.engine import Engine, EngineOptions
+    from airun_b200.parts.base import PagedKVSpec, StateSpec
+    monkeypatch.setattr(torch.cuda, "mem_get_info", lambda dev=None: (1 << 30, 1 << 31))
+    o = EngineOptions(dtype="bfloat16", memory_fraction=0.5, max_requests=16, page_size=16)
+    kv = PagedKVSpec(2, 64, 0)
+    per_token = 2 * 2 * 64 * 2
+    plain = Engine._tokens_that_fit([kv], [None], o)
+    assert plain == (1 << 29) // per_token
+    state = StateSpec((1024, 256), torch.float32)                      # 1 MiB per request and owner layer
+    with_state = Engine._tokens_that_fit([kv, state, state], [None, None, 1], o)     # the second reads the first's
+    assert with_state == ((1 << 29) - 16 * (1 << 20)) // per_token

@@ -370,3 +370,110 @@ def test_routed_feed_forward_and_another_position_encoding(tmp_path):
     eng.runner.raise_on_device_error()
     assert_close(np.concatenate(got_a), want[0], "float32", "routed toy, portion then single tokens")
     assert_close(np.concatenate(rows_b), want[1], "float32", "routed toy, portions beside single tokens")
+
+
+# ----------------------------------------------------------------------------- parts only the registries reach
+def define_scaled_toy():
+    """A toy architecture whose embedding is scaled, whose logits are soft-capped, and whose rotary
+    encoding pairs neighbouring dimensions and turns by positions that are not the cache positions."""
+    from airun_b200.config.base import LayerSpec, register_architecture
+    from airun_b200.config.qwen3 import Qwen3Config
+    from airun_b200.engine.model import build_decoder
+    from airun_b200.kernels import ops
+    from airun_b200.parts.base import PositionEncoding, register_part
+
+    class ShiftedInterleavedRotary(PositionEncoding):
+        """Pairs (2i, 2i + 1); a row at cache position p is rotated by p // 2 + 3."""
+
+        def __init__(self, prefix="", head_dim=0, theta=10000.0, dtype=None, device=None):
+            self.rotary_dim = head_dim
+            i = torch.arange(0, head_dim // 2, dtype=torch.float64)
+            self.inv_freq = torch.pow(torch.tensor(theta, dtype=torch.float64), -2.0 * i / head_dim).float().to(device)
+
+        def fused(self):
+            return ops.ROPE_INTERLEAVED, self.rotary_dim, self.inv_freq
+
+        def rotation_positions(self, ctx):
+            pos = ctx.positions[:ctx.num_tokens]
+            return (torch.div(pos.clamp(min=0), 2, rounding_mode="floor") + 3).to(torch.int32).contiguous()
+
+    class ScaledConfig(Qwen3Config):
+        def embedding(self):
+            return "token_embedding", dict(scale=math.sqrt(self.hidden_size))
+
+        def head(self):
+            return "lm_head", dict(soft_cap=0.5)
+
+        def layer_specs(self):
+            out = []
+            for s in Qwen3Config.layer_specs(self):
+                mixer_args = dict(s.mixer_args, position="toy_shifted_interleaved_rotary",
+                                  position_args=dict(head_dim=self.head_dim, theta=self.rope_theta))
+                out.append(LayerSpec(s.mixer, mixer_args, s.feed_forward, s.ffn_args, s.norm, s.norm_args))
+            return out
+
+    register_part("position", "toy_shifted_interleaved_rotary", ShiftedInterleavedRotary)
+    register_architecture("ToyScaledForCausalLM", ScaledConfig, build_decoder)
+    return ScaledConfig
+
+
+def plain_scaled_forward(cfg: dict, W: Dict[str, torch.Tensor], tokens: List[int], round_to=None) -> torch.Tensor:
+    c = P.config_values(cfg)
+    dt = torch.float32
+    T = len(tokens)
+    hd, nh, nkv = c["hd"], c["nh"], c["nkv"]
+    r = (lambda t: t) if round_to is None else (lambda t: t.to(round_to).to(dt))
+    x = P.plain_embedding(W["model.embed_tokens.weight"], tokens, dt) * torch.tensor(math.sqrt(c["H"]), dtype=dt)
+    rpos = [p // 2 + 3 for p in range(T)]
+    for l in range(c["L"]):
+        p = f"model.layers.{l}"
+        h = r(P.plain_rmsnorm(x, W[f"{p}.input_layernorm.weight"], c["eps"]))
+        q = (h @ W[f"{p}.self_attn.q_proj.weight"].to(dt).T).view(T, nh, hd)
+        k = (h @ W[f"{p}.self_attn.k_proj.weight"].to(dt).T).view(T, nkv, hd)
+        v = r((h @ W[f"{p}.self_attn.v_proj.weight"].to(dt).T).view(T, nkv, hd))
+        q = r(P.plain_rope_interleaved(P.plain_rmsnorm(q, W[f"{p}.self_attn.q_norm.weight"], c["eps"]), rpos, c["theta"], hd))
+        k = r(P.plain_rope_interleaved(P.plain_rmsnorm(k, W[f"{p}.self_attn.k_norm.weight"], c["eps"]), rpos, c["theta"], hd))
+        att = r(P.plain_attention(q, k, v, list(range(T)), hd ** -0.5, 0)).reshape(T, nh * hd)
+        x = x + att @ W[f"{p}.self_attn.o_proj.weight"].to(dt).T
+        h = r(P.plain_rmsnorm(x, W[f"{p}.post_attention_layernorm.weight"], c["eps"]))
+        x = x + P.plain_swiglu_ffn(h, W[f"{p}.mlp.gate_proj.weight"].to(dt), W[f"{p}.mlp.up_proj.weight"].to(dt),
+                                   W[f"{p}.mlp.down_proj.weight"].to(dt), round_to)
+    h = r(P.plain_rmsnorm(x, W["model.norm.weight"], c["eps"]))
+    logits = h @ W["lm_head.weight"].to(dt).T
+    return 0.5 * torch.tanh(logits / 0.5)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_scaled_embedding_capped_head_and_rotation_positions_of_their_own(dtype, tmp_path):
+    """The embedding and the head come from the part registries with their constants as parameters; the
+    position encoding asks the fused prologue for the interleaved pairing and gives it rotation positions
+    that are not the cache positions.  Whole, in portions and token by token (graph replay), against a
+    plain implementation of the toy."""
+    import airun_b200
+    from airun_b200 import StepEntry
+    from airun_b200.engine.model import DecoderModel
+    from airun_b200.weights import write_model_folder
+    from helpers import bf16_noise
+    ScaledConfig = define_scaled_toy()
+    cfg_obj = ScaledConfig.from_dict(dict(TINY["B"]["cfg"], architectures=["ToyScaledForCausalLM"]))
+    folder = str(tmp_path / "scaled")
+    write_model_folder(folder, cfg_obj, DecoderModel(cfg_obj, torch.float32, "cpu").weight_specs(), seed=10)
+    cfg, W = P.read_model_folder(folder)
+    seq = random_tokens(41, cfg["vocab_size"], 500)
+    exact = plain_scaled_forward(cfg, W, seq).numpy()
+    want = exact if dtype == "float32" else plain_scaled_forward(cfg, W, seq, torch.bfloat16).numpy()
+    noise = bf16_noise(want, exact)
+    assert 0.3 < float(np.abs(exact).max()) < 0.5                # the cap does bend these logits
+    eng = airun_b200.Engine.from_folder(folder, dtype=dtype, page_size=8, cache_tokens=256, max_batch_tokens=64,
+                                        max_requests=4)
+    assert eng.model.embedding.scale == math.sqrt(cfg["hidden_size"]) and eng.model.head.soft_cap == 0.5
+    eng.manager.add_request("w")
+    whole = eng.runner.step([StepEntry("w", seq, tuple(range(len(seq))))]).cpu().numpy()
+    eng.manager.add_request("c")
+    rows = [eng.runner.step([StepEntry("c", seq[:13], tuple(range(13)))]).cpu().numpy(),
+            eng.runner.step([StepEntry("c", seq[13:15], (0, 1))]).cpu().numpy()]
+    for t in seq[15:]:
+        rows.append(eng.runner.step([StepEntry("c", [t], (0,))]).cpu().numpy())
+    eng.runner.raise_on_device_error()
+    assert_close(whole, want, dtype, "scaled toy, whole", noise)
+    assert_close(np.concatenate(rows), want, dtype, "scaled toy, portions then single tokens", noise)

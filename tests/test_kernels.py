@@ -295,6 +295,65 @@ def test_qkv_post_against_the_plain_parts(nh, nkv, hd, page, dtype):
     assert err.item() == 1
 
 
+@pytest.mark.parametrize("hd,rdim", [(128, 128), (48, 32), (16, 16)])
+def test_qkv_post_interleaved_pairing_and_rotation_positions(hd, rdim):
+    """The other pairing (dims 2i, 2i + 1), a partial rotation, and rows rotated by positions that are not
+    their places in the cache: keys still land at the cache positions."""
+    from airun_b200.kernels import ops
+    from airun_b200.parts.rope import RotaryInterleaved
+    torch.manual_seed(8)
+    nh, nkv, page = 4, 2, 8
+    positions, rpos = [5, 6, 7, 30], [100, 3, 0, 4095]
+    T = len(positions)
+    qkv = torch.randn(T, (nh + 2 * nkv) * hd)
+    qw, kw = 1 + 0.5 * torch.rand(hd), 1 + 0.5 * torch.rand(hd)
+    eps, theta = 1e-6, 1e4
+    kind, r, inv = RotaryInterleaved(rotary_dim=rdim, theta=theta, device=DEV).fused()
+    assert kind == ops.ROPE_INTERLEAVED
+    pool = torch.zeros(6, 2, nkv, page, hd, device=DEV)
+    bt = torch.tensor([[4, 2, 0, 5, 1]], dtype=torch.int32, device=DEV)
+    q_out = torch.empty(T, nh * hd, device=DEV)
+    err = _err()
+    ops.qkv_post(qkv.to(DEV), q_out, qw.to(DEV), kw.to(DEV), eps, torch.tensor(positions, dtype=torch.int32, device=DEV),
+                 torch.zeros(T, dtype=torch.int32, device=DEV), kind, r, inv, pool, bt, 1, page, nh, nkv, hd, err,
+                 rope_positions=torch.tensor(rpos, dtype=torch.int32, device=DEV))
+    assert err.item() == 0
+    q = qkv[:, :nh * hd].view(T, nh, hd)
+    k = qkv[:, nh * hd:(nh + nkv) * hd].view(T, nkv, hd)
+    want_q = P.plain_rope_interleaved(P.plain_rmsnorm(q, qw, eps), rpos, theta, rdim)
+    want_k = P.plain_rope_interleaved(P.plain_rmsnorm(k, kw, eps), rpos, theta, rdim)
+    assert torch.allclose(q_out.cpu().view(T, nh, hd), want_q, rtol=2e-5, atol=2e-5)
+    for t in range(T):
+        pg, row = int(bt[0, positions[t] // page]), positions[t] % page
+        assert torch.allclose(pool[pg, 0, :, row].cpu(), want_k[t], rtol=2e-5, atol=2e-5)
+
+
+def test_copy_pages_and_soft_cap():
+    from airun_b200.kernels import ops
+    torch.manual_seed(9)
+    pool = torch.randn(3, 10, 2, 2, 8, 16, device=DEV).to(torch.bfloat16)      # owners, pages, K/V, heads, page, head size
+    before = pool.clone()
+    err = _err()
+    ops.copy_pages(pool, torch.tensor([[1, 7], [4, 0], [1, 9]], dtype=torch.int32, device=DEV), err)
+    torch.cuda.synchronize()
+    want = before.clone()
+    for s_, d_ in ((1, 7), (4, 0), (1, 9)):
+        want[:, d_] = before[:, s_]
+    assert torch.equal(pool, want) and err.item() == 0
+    ops.copy_pages(pool, torch.tensor([[1, 10]], dtype=torch.int32, device=DEV), err)       # outside the pool: flagged, skipped
+    torch.cuda.synchronize()
+    assert torch.equal(pool, want) and err.item() == 1
+    x = torch.randn(7, 333, device=DEV) * 20
+    y = x.clone()
+    ops.soft_cap(y, 30.0)
+    assert torch.allclose(y.cpu(), 30.0 * torch.tanh(x.cpu().double() / 30.0).float(), rtol=1e-5, atol=1e-5)
+    table = torch.randn(11, 64).to(torch.bfloat16).to(DEV)
+    ids = torch.tensor([3, 10, 0], dtype=torch.int32, device=DEV)
+    out = torch.empty(3, 64, device=DEV)
+    ops.embed(table, ids, out, err, scale=8.0)
+    assert torch.equal(out.cpu(), table.float().cpu()[[3, 10, 0]] * 8.0)
+
+
 # ----------------------------------------------------------------------------- attention
 def attention_case(nh, nkv, hd, page, window, lens, qlens, dtype, seed, peaked=True):
     """Requests with contexts ``lens``; the last ``qlens[i]`` tokens of each are this step's queries.
