@@ -155,7 +155,11 @@ __global__ __launch_bounds__(PTHREADS, 2) void attn_prefill_kernel(const AttnPar
                                                                    const int* __restrict__ n_tiles_dev, const SharedArgs sh) {
     pdl_trigger();
     pdl_wait();
-    if (!SHARED && n_tiles_dev && (int)blockIdx.x >= *n_tiles_dev) return;
+    // the KV heads of a tile before the next tile (blocks start in the order of their linear index): the
+    // tiles with the most keys, of all heads, start first
+    const int lin = (int)(blockIdx.y * gridDim.x + blockIdx.x);
+    const int tile_idx = SHARED ? (int)blockIdx.x : lin / (int)gridDim.y;
+    if (!SHARED && n_tiles_dev && tile_idx >= *n_tiles_dev) return;
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t* sQ = smem;                               // [PM][HD]
     uint8_t* sK = sQ + PM * HD * 2;                   // [2][PN][HD]
@@ -168,10 +172,10 @@ __global__ __launch_bounds__(PTHREADS, 2) void attn_prefill_kernel(const AttnPar
         n_tok = min(per, sh.n_tok - tok0);
         req = p.req_of_token[tok0];
     } else {
-        const int4 t4 = tiles[blockIdx.x];
+        const int4 t4 = tiles[tile_idx];
         req = t4.x; tok0 = t4.y; n_tok = t4.z;
     }
-    const int kvh = blockIdx.y;
+    const int kvh = SHARED ? (int)blockIdx.y : lin % (int)gridDim.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int n_rows = n_tok * G;                     // valid packed rows (<= PM)
@@ -362,8 +366,6 @@ struct DecodeExtra {
                                 //   kernel's n_splits; they are merged with this kernel's own slices)
     int early_ok;               // the caller vouches that every key but each token's newest was written before the
                                 //   chain of launches this one belongs to began (a step replayed as one graph)
-    const void* pf_ptr;         // weights of a later product to ask into L2 when a warp has issued its last tile
-    long long pf_bytes;         //   (l2_prefetch_slice); null: none
 };
 
 // TMA = true: K/V tiles arrive by cp.async.bulk.tensor (one lane of each warp issues HD/64 boxes per
@@ -517,14 +519,8 @@ __global__ __launch_bounds__(32 * DW) void attn_decode_kernel(const AttnParams p
         ldsm4(qf[k], smem_u32(sQ) + tile_off((lane & 7) + ((lane >> 3) & 1) * 8, 2 * k + (lane >> 4)));
 
     bool timed_out = false;
-    // once this warp has no tile left to ask for, it asks for its share of the next product's weights
-    const int pf_at = my_n > DSTAGES - 1 ? my_n - (DSTAGES - 1) : 0;
-    const int pf_unit = (int)(blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z)) * DW + warp;
-    const int pf_units = (int)(gridDim.x * gridDim.y * gridDim.z) * DW;
-    if (my_n == 0 && lane == 0) l2_prefetch_slice(x.pf_ptr, x.pf_bytes, pf_unit, pf_units);
     for (int it = 0; it < my_n; ++it) {
         const int stage = TMA ? it % DSTAGES : (it & 1);
-        if (lane == 0 && it == pf_at) l2_prefetch_slice(x.pf_ptr, x.pf_bytes, pf_unit, pf_units);
         if (TMA) {
             if (lane == 0 && it + DSTAGES - 1 < my_n) {
                 // the stage being refilled was read (by ldmatrix) in the iteration before this one
@@ -836,10 +832,8 @@ AIRUN_EXPORT int airun_attn_decode(const void* q, void* out, const void* pool, c
                                    int num_reqs, int num_pages, int page_size, int nh, int nkv, float scale,
                                    int window, const int32_t* rows, int n_rows, int n_splits, float* scratch,
                                    int* counters, const int32_t* n_rows_dev, int dyn_slots, const int32_t* k_begin_dev,
-                                   int extra_slices, int early_ok, const void* pf_ptr, long long pf_bytes, int* err,
-                                   cudaStream_t stream) {
+                                   int extra_slices, int early_ok, int* err, cudaStream_t stream) {
     if (n_rows_dev && (dyn_slots <= 0 || !rows)) return AIRUN_ERR_ARG;
-    if (pf_ptr && (((uintptr_t)pf_ptr & 15) || pf_bytes < 0 || pf_bytes % 16 != 0)) return AIRUN_ERR_ARG;
     if (extra_slices < 0 || n_splits + extra_slices > MAX_SPLITS || (extra_slices > 0 && (n_rows_dev || !k_begin_dev || !scratch || !counters)))
         return AIRUN_ERR_ARG;
     if (n_rows < 0 || nh <= 0 || nkv <= 0 || nh % nkv != 0 || page_size <= 0 || n_splits < 1 || n_splits > MAX_SPLITS || !err) return AIRUN_ERR_ARG;
@@ -849,8 +843,7 @@ AIRUN_EXPORT int airun_attn_decode(const void* q, void* out, const void* pool, c
     if (nkv * hgroups > 65535 || n_rows > 65535) return AIRUN_ERR_ARG;
     const AttnParams p = make_params(q, out, pool, block_table, max_blocks, positions, req_of_token, num_reqs,
                                      num_pages, page_size, nh, nkv, scale, window, err);
-    DecodeExtra x{rows, n_splits, scratch, counters, n_rows_dev, dyn_slots, k_begin_dev, extra_slices, early_ok,
-                  pf_ptr, pf_ptr ? pf_bytes : 0};
+    DecodeExtra x{rows, n_splits, scratch, counters, n_rows_dev, dyn_slots, k_begin_dev, extra_slices, early_ok};
     // TMA needs whole 16-key tiles inside one page and 128-byte boxes
     static const bool tma_allowed = !(getenv("AIRUN_ATTN_TMA") && getenv("AIRUN_ATTN_TMA")[0] == '0');
     const bool tma = tma_allowed && (HD % 64 == 0) && p.page_shift >= 4 && encode_fn() != nullptr;

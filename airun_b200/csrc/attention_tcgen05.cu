@@ -276,7 +276,13 @@ __global__ __launch_bounds__(TC_THREADS, 1) void attn_prefill_tc_kernel(
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     pdl_wait();
-    if (!SHARED && n_tiles_dev && (int)blockIdx.x >= *n_tiles_dev) {       // a CTA beyond the tiles in use: nothing to do
+    // Blocks are handed out in the order of their linear index, and the work list has the tiles with the most
+    // keys first: so the linear index counts the KV heads of a tile before it moves on to the next tile, and
+    // the long tiles of ALL heads start first (with the head as the slow index the long tiles of the last
+    // heads started last, on top of a machine already half done).
+    const int lin = (int)(blockIdx.y * gridDim.x + blockIdx.x);
+    const int tile_idx = SHARED ? (int)blockIdx.x : lin / (int)gridDim.y;
+    if (!SHARED && n_tiles_dev && tile_idx >= *n_tiles_dev) {       // a CTA beyond the tiles in use: nothing to do
         tc_fence_before();
         __syncthreads();
         if (warp == 1) {
@@ -294,10 +300,10 @@ __global__ __launch_bounds__(TC_THREADS, 1) void attn_prefill_tc_kernel(
         n_tok = min(per, sh.n_tok - tok0);
         req = sh.req_of_token[tok0];
     } else {
-        const int4 t4 = tiles[blockIdx.x];
+        const int4 t4 = tiles[tile_idx];
         req = t4.x; tok0 = t4.y; n_tok = t4.z;
     }
-    const int kvh = blockIdx.y;
+    const int kvh = SHARED ? (int)blockIdx.y : lin % (int)gridDim.y;
     const int n_rows = n_tok * G;
     const bool req_ok = !SHARED || (req >= 0 && req < sh.num_reqs);      // (a padded batch: rows of no request)
     const int32_t* bt = p.block_table + (size_t)(req_ok ? req : 0) * p.max_blocks;
@@ -624,7 +630,10 @@ __global__ __launch_bounds__(TC_THREADS, 1) void attn_prefill_wide_kernel(
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     pdl_wait();
-    if (n_tiles_dev && (int)blockIdx.x >= *n_tiles_dev) {       // a CTA beyond the tiles in use: nothing to do
+    // the KV heads of a tile before the next tile: the tiles with the most keys, of all heads, start first
+    const int lin = (int)(blockIdx.y * gridDim.x + blockIdx.x);
+    const int tile_idx = lin / (int)gridDim.y;
+    if (n_tiles_dev && tile_idx >= *n_tiles_dev) {       // a CTA beyond the tiles in use: nothing to do
         tc_fence_before();
         __syncthreads();
         if (warp == 1) {
@@ -635,9 +644,9 @@ __global__ __launch_bounds__(TC_THREADS, 1) void attn_prefill_wide_kernel(
     }
 
     const int G = p.G;
-    const int4 t4 = tiles[blockIdx.x];
+    const int4 t4 = tiles[tile_idx];
     const int req = t4.x, tok0 = t4.y, n_tok = t4.z;
-    const int kvh = blockIdx.y;
+    const int kvh = lin % (int)gridDim.y;
     const int n_rows = n_tok * G;
     const bool two = n_rows > QM;                       // is there a Q tile B?
     const int32_t* bt = p.block_table + (size_t)req * p.max_blocks;

@@ -34,27 +34,6 @@
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
-// Weights that a LATER kernel of the step will read, asked into the L2 cache by this one: when a kernel has
-// issued its last loads (or is one of the small kernels that move little), the memory system would idle
-// until the next kernel's first loads arrive; a prefetch of the next weights' first megabytes keeps it busy
-// across the boundary, and the next kernel starts on L2 hits.  `base` .. `base + bytes` (16-byte aligned, a
-// multiple of 16) is cut into `n_units` slices; unit `unit` asks for its slice in pieces of 16 KB.  Nothing
-// waits for a prefetch and nothing depends on it.
-__device__ __forceinline__ void l2_prefetch_slice(const void* base, long long bytes, int unit, int n_units) {
-    if (base == nullptr || bytes <= 0 || n_units <= 0) return;
-    long long per = (bytes + n_units - 1) / n_units;
-    per = (per + 15) & ~15ll;
-    const long long off = per * unit;
-    if (off >= bytes) return;
-    long long n = bytes - off < per ? bytes - off : per;
-    n &= ~15ll;
-    const char* ptr = reinterpret_cast<const char*>(base) + off;
-    for (long long o = 0; o < n; o += 16384) {
-        const uint32_t c = (uint32_t)(n - o < 16384 ? n - o : 16384);
-        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(ptr + o), "r"(c) : "memory");
-    }
-}
-
 static thread_local int airun_launch_rc = 0;
 
 static inline bool airun_pdl_enabled() {

@@ -49,14 +49,8 @@ AIRUN_EXPORT int airun_embed(const void* table, int table_dtype, const int32_t* 
 template <typename TOut, int VEC>
 __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta,
                                const float* __restrict__ w, TOut* __restrict__ out,
-                               const int32_t* __restrict__ rows, int n, float eps, int write_back,
-                               const void* __restrict__ pf_ptr, long long pf_bytes) {
+                               const int32_t* __restrict__ rows, int n, float eps, int write_back) {
     pdl_trigger();
-    // a few rows keep few SMs busy for a few microseconds: meanwhile the weights of the product that follows
-    // are asked into L2 (they depend on no kernel, so this runs before the wait for the kernel in front)
-    if ((threadIdx.x & 31) == 0)
-        l2_prefetch_slice(pf_ptr, pf_bytes, (int)(blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)),
-                          (int)(gridDim.x * (blockDim.x >> 5)));
     pdl_wait();
     __shared__ float red[33];
     const int r = blockIdx.x;
@@ -198,10 +192,8 @@ __global__ __launch_bounds__(256) void rmsnorm_rows_kernel(float* __restrict__ x
 
 AIRUN_EXPORT int airun_rmsnorm(float* x, const float* delta, const float* w, void* out, int out_dtype,
                                const int32_t* rows, int n_rows, int n, float eps, int write_back,
-                               const void* pf_ptr, long long pf_bytes, cudaStream_t stream) {
+                               cudaStream_t stream) {
     if (n_rows < 0 || n <= 0) return AIRUN_ERR_ARG;
-    if (pf_ptr && (((uintptr_t)pf_ptr & 15) || pf_bytes < 0 || pf_bytes % 16 != 0)) return AIRUN_ERR_ARG;
-    if (!pf_ptr) pf_bytes = 0;
     if (rows && write_back) return AIRUN_ERR_ARG;
     if (n_rows == 0) return AIRUN_OK;
     const bool vec = n % 4 == 0 && (((uintptr_t)x | (uintptr_t)delta) & 15) == 0;
@@ -223,7 +215,7 @@ AIRUN_EXPORT int airun_rmsnorm(float* x, const float* delta, const float* w, voi
     if (threads < 32) threads = 32;
     if (n_rows <= 64 && threads > 256 && vec) threads = 256;      // few rows: more loads in flight per thread
 #define LAUNCH(TOut, VEC) \
-    airun_launch(rmsnorm_kernel<TOut, VEC>, dim3(n_rows), dim3(threads), 0, stream, x, delta, w, (TOut*)out, rows, n, eps, write_back, pf_ptr, pf_bytes)
+    airun_launch(rmsnorm_kernel<TOut, VEC>, dim3(n_rows), dim3(threads), 0, stream, x, delta, w, (TOut*)out, rows, n, eps, write_back)
     if (out_dtype == AIRUN_DT_F32) { if (vec) LAUNCH(float, 4); else LAUNCH(float, 1); }
     else if (out_dtype == AIRUN_DT_BF16) { if (vec) LAUNCH(__nv_bfloat16, 4); else LAUNCH(__nv_bfloat16, 1); }
     else return AIRUN_ERR_UNSUPPORTED;

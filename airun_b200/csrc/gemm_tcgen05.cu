@@ -179,8 +179,6 @@ struct GemmParams {
     int ssq_out_ld;
     int cluster_reduce;           // the ksplit CTAs of a tile are one cluster and add their slices through
                                   // distributed shared memory instead of the scratch
-    const void* pf_ptr;           // weights of a later product to ask into L2 once this CTA has issued its last
-    long long pf_bytes;           //   loads (l2_prefetch_slice); null: none
 };
 
 template <int BN, int STAGES>
@@ -491,9 +489,6 @@ __global__ __launch_bounds__(GEMM_THREADS, 1) void gemm_tcgen05_kernel(
                 tma_load_2d(sa, &map_a, full0 + 8 * s, k, a0);
                 tma_load_2d(sa + L::A_BYTES, &map_b, full0 + 8 * s, k, b0);
             }
-            // this CTA's stream is issued: from here to the next kernel's first loads the memory would idle
-            l2_prefetch_slice(p.pf_ptr, p.pf_bytes, (int)(blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z)),
-                              (int)(gridDim.x * gridDim.y * gridDim.z));
         }
     } else if (warp == 1) {
         if (lane == 0) {
@@ -928,9 +923,8 @@ AIRUN_EXPORT int airun_gemm_tcgen05_ex(const void* x, const void* W, void* out, 
                                        int ksplit, float* scratch, int* counters, int* err, cudaStream_t stream,
                                        const float* ssq_in, int ssq_parts, int ssq_ld, float eps_in, int norm_size,
                                        float* resid, long long ld_resid, const float* norm_w, float* ssq_out,
-                                       int ssq_out_ld, const void* pf_ptr, long long pf_bytes) {
+                                       int ssq_out_ld) {
     if (M <= 0 || N <= 0 || K <= 0 || !err) return M == 0 ? AIRUN_OK : AIRUN_ERR_ARG;
-    if (pf_ptr && (((uintptr_t)pf_ptr & 15) || pf_bytes < 0 || pf_bytes % 16 != 0)) return AIRUN_ERR_ARG;
     if (K % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0 || ((uintptr_t)x & 15) || ((uintptr_t)W & 15)) return AIRUN_ERR_ARG;
     if (epi == EPI_SWIGLU && (N % 32 != 0)) return AIRUN_ERR_ARG;
     if (ksplit < 1 || (ksplit > 1 && (!scratch || !counters))) return AIRUN_ERR_ARG;
@@ -974,7 +968,6 @@ AIRUN_EXPORT int airun_gemm_tcgen05_ex(const void* x, const void* W, void* out, 
     p.inv_n_in = norm_size > 0 ? 1.0f / (float)norm_size : 0.0f;
     p.resid = resid; p.ld_resid = ld_resid; p.norm_w = norm_w; p.ssq_out = ssq_out; p.ssq_out_ld = ssq_out_ld;
     p.cluster_reduce = (clustered && p.ksplit >= 2 && p.ksplit <= 8) ? 1 : 0;
-    p.pf_ptr = pf_ptr; p.pf_bytes = pf_ptr ? pf_bytes : 0;
     CUtensorMap ma, mb;
     int r;
     if (swap) {
@@ -1000,7 +993,7 @@ AIRUN_EXPORT int airun_gemm_tcgen05(const void* x, const void* W, void* out, int
                                     int ksplit, float* scratch, int* counters, int* err, cudaStream_t stream) {
     if (epi == EPI_RESID) return AIRUN_ERR_ARG;
     return airun_gemm_tcgen05_ex(x, W, out, M, N, K, ldx, ldw, ldc, epi, swap, bn, ksplit, scratch, counters, err, stream,
-                                 nullptr, 0, 0, 0.0f, 0, nullptr, 0, nullptr, nullptr, 0, nullptr, 0);
+                                 nullptr, 0, 0, 0.0f, 0, nullptr, 0, nullptr, nullptr, 0);
 }
 
 // ------------------------------------------------------------------ no-allocation variant

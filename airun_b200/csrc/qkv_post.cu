@@ -38,11 +38,8 @@ __global__ __launch_bounds__(256) void qkv_post_kernel(
     int rope_kind, int rotary_dim, const float* __restrict__ inv_freq, const int32_t* __restrict__ rope_positions,
     TKV* __restrict__ pool, const int32_t* __restrict__ block_table, int max_blocks,
     int num_reqs, int num_pages, int page_size, int do_store, int kv_from_qkv,
-    int nh, int nkv, int hd, int* __restrict__ err, const void* __restrict__ pf_ptr, long long pf_bytes) {
+    int nh, int nkv, int hd, int* __restrict__ err) {
     pdl_trigger();
-    if ((threadIdx.x & 31) == 0)           // weights of a later product into L2 while this small kernel runs
-        l2_prefetch_slice(pf_ptr, pf_bytes, (int)((blockIdx.x * gridDim.y + blockIdx.y) * (blockDim.x >> 5) + (threadIdx.x >> 5)),
-                          (int)(gridDim.x * gridDim.y * (blockDim.x >> 5)));
     pdl_wait();
     extern __shared__ float smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -153,11 +150,8 @@ __global__ __launch_bounds__(256) void qkv_post_hd128_kernel(
     const float* __restrict__ inv_freq,
     TKV* __restrict__ pool, const int32_t* __restrict__ block_table, int max_blocks,
     int num_reqs, int num_pages, int page_size, int do_store, int kv_from_qkv,
-    int nh, int nkv, int* __restrict__ err, const void* __restrict__ pf_ptr, long long pf_bytes) {
+    int nh, int nkv, int* __restrict__ err) {
     pdl_trigger();
-    if ((threadIdx.x & 31) == 0)           // weights of a later product into L2 while this small kernel runs
-        l2_prefetch_slice(pf_ptr, pf_bytes, (int)((blockIdx.x * gridDim.y + blockIdx.y) * (blockDim.x >> 5) + (threadIdx.x >> 5)),
-                          (int)(gridDim.x * gridDim.y * (blockDim.x >> 5)));
     constexpr int HD = 128, HALF = 64;
     __shared__ float cs[2 * HALF];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -255,10 +249,8 @@ AIRUN_EXPORT int airun_qkv_post(
     int rope_kind, int rotary_dim, const float* inv_freq, const int32_t* rope_positions,
     void* pool, int kv_dtype, const int32_t* block_table, int max_blocks, int num_reqs,
     int num_pages, int page_size, int do_store, int kv_from_qkv,
-    int nh, int nkv, int hd, int* err, const void* pf_ptr, long long pf_bytes, cudaStream_t stream) {
+    int nh, int nkv, int hd, int* err, cudaStream_t stream) {
     if (T < 0 || nh <= 0 || nkv <= 0 || hd <= 0 || hd > 32 * MAX_PER_LANE) return AIRUN_ERR_ARG;
-    if (pf_ptr && (((uintptr_t)pf_ptr & 15) || pf_bytes < 0 || pf_bytes % 16 != 0)) return AIRUN_ERR_ARG;
-    if (!pf_ptr) pf_bytes = 0;
     if (rope_kind != ROPE_NONE && rope_kind != ROPE_NEOX && rope_kind != ROPE_INTERLEAVED) return AIRUN_ERR_UNSUPPORTED;
     if (rope_kind != ROPE_NONE && (rotary_dim <= 0 || rotary_dim > hd || rotary_dim % 2 != 0 || !inv_freq))
         return AIRUN_ERR_ARG;
@@ -279,7 +271,7 @@ AIRUN_EXPORT int airun_qkv_post(
 #define LAUNCH128(TQ, TKV) \
     airun_launch(qkv_post_hd128_kernel<TQ, TKV>, dim3(T, blocks_y), dim3(warps * 32), 0, stream, qkv, ld_qkv, (TQ*)q_out, \
         q_norm_w, k_norm_w, eps, positions, req_of_token, inv_freq, (TKV*)pool, block_table, max_blocks, num_reqs, \
-        num_pages, page_size, do_store, kv_from_qkv, nh, nkv, err, pf_ptr, pf_bytes)
+        num_pages, page_size, do_store, kv_from_qkv, nh, nkv, err)
         if (q_dtype == AIRUN_DT_F32) LAUNCH128(float, float);
         else if (q_dtype == AIRUN_DT_BF16) LAUNCH128(__nv_bfloat16, __nv_bfloat16);
         else return AIRUN_ERR_UNSUPPORTED;
@@ -289,7 +281,7 @@ AIRUN_EXPORT int airun_qkv_post(
 #define LAUNCH(TQ, TKV, DPL) \
     airun_launch(qkv_post_kernel<TQ, TKV, DPL>, dim3(T, blocks_y), dim3(warps * 32), smem, stream, qkv, ld_qkv, (TQ*)q_out, q_norm_w, k_norm_w, eps, \
         positions, req_of_token, rope_kind, rotary_dim, inv_freq, rope_positions, (TKV*)pool, block_table, max_blocks, num_reqs, \
-        num_pages, page_size, do_store, kv_from_qkv, nh, nkv, hd, err, pf_ptr, pf_bytes)
+        num_pages, page_size, do_store, kv_from_qkv, nh, nkv, hd, err)
 #define LAUNCH_DPL(TQ, TKV) \
     do { if (hd <= 32) LAUNCH(TQ, TKV, 1); else if (hd <= 64) LAUNCH(TQ, TKV, 2); \
          else if (hd <= 128) LAUNCH(TQ, TKV, 4); else LAUNCH(TQ, TKV, 8); } while (0)

@@ -10,7 +10,6 @@ same thing.
 """
 from __future__ import annotations
 
-import bisect
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional
 
@@ -55,75 +54,6 @@ class Workspace:
         return sum(c.numel() for c in self.chunks)
 
 
-class WeightStream:
-    """The weight matrices of one pass over the model, in the order the pass reads them, and how far ahead
-    of the product now running the L2 cache has been asked for them.
-
-    A decode step is bound by streaming the weights from memory, and at every boundary between two kernels
-    the stream would pause: the kernel in front has issued its last loads, the next one has not started.
-    Kernels therefore ask the L2 cache for the first megabytes of the weights that come NEXT (a kernel
-    parameter: pointer and bytes; csrc/common.cuh ``l2_prefetch_slice``).  This class hands those ranges
-    out on the host while the step's kernels are launched (or captured into a graph: the ranges are the same
-    for every replay): ``consume(w)`` when a product over ``w`` is launched, ``claim(n)`` for the next ``n``
-    bytes nobody has asked for yet, never more than ``max_ahead`` bytes beyond the product now running (what
-    the cache can hold beside the step's other traffic).  After the last matrix the first one follows: the
-    next step's.  The reference keeps its weights streaming the same way across kernels of a decode step by
-    launching the next kernel early (its graphs; crates/airun-core/src/runtime.rs:2285-2311); it has no L2
-    prefetch."""
-
-    def __init__(self, tensors: List[torch.Tensor], max_ahead: int = 48 << 20):
-        self.ptrs = [t.data_ptr() for t in tensors]
-        self.sizes = [t.numel() * t.element_size() for t in tensors]
-        self.starts = [0]
-        for n in self.sizes:
-            self.starts.append(self.starts[-1] + n)
-        self.total = self.starts[-1]
-        self.where: Dict[int, List[int]] = {}
-        for i, ptr in enumerate(self.ptrs):
-            self.where.setdefault(ptr, []).append(i)
-        self.max_ahead = int(max_ahead)
-        # positions in the endless stream matrix 0, 1, ..., last, 0, 1, ...: bytes from the start of this pass
-        self.front = 0                    # first byte nobody has asked for
-        self.reset()
-
-    def reset(self) -> None:
-        """A new pass begins.  What the pass before asked for beyond its own end are this pass's first bytes."""
-        self.front = self.front - self.total if self.front > self.total > 0 else 0
-        self.cur_start = -1               # where the matrix of the product now running starts
-        self.cur_end = 0                  # and ends
-
-    def consume(self, w: torch.Tensor) -> None:
-        """A product over ``w`` is being launched (matrices unknown to the stream are ignored)."""
-        places = self.where.get(w.data_ptr())
-        if not places:
-            return
-        starts = [self.starts[i] for i in places] + [self.total + self.starts[places[0]]]
-        start = next(s for s in starts if s > self.cur_start)
-        i = places[starts.index(start) % len(places)]
-        self.cur_start, self.cur_end = start, start + self.sizes[i]
-        self.front = max(self.front, self.cur_end)
-
-    def claim(self, nbytes: int):
-        """(address, bytes) of the next range to ask for, or (0, 0): at most ``nbytes``, inside one matrix,
-        a multiple of 256 bytes, and within ``max_ahead`` of the end of the matrix now being read."""
-        if self.total <= 0:
-            return 0, 0
-        for _ in range(2):
-            room = self.max_ahead - (self.front - self.cur_end)
-            rem = self.front % self.total
-            i = bisect.bisect_right(self.starts, rem) - 1
-            off = rem - self.starts[i]
-            left = self.sizes[i] - off
-            take = min(int(nbytes), left, room) // 256 * 256
-            if take > 0:
-                self.front += take
-                return self.ptrs[i] + off, take
-            if left >= 256 or room < 256:
-                return 0, 0
-            self.front += left            # a ragged end of less than 256 bytes: on to the next matrix
-        return 0, 0
-
-
 @dataclass
 class CacheView:
     """The cache of one entry of the execution order, as its mixer sees it."""
@@ -161,8 +91,3 @@ class StepContext:
     max_context_len: int = 0
     decode_only: bool = False
     extras: Dict[str, object] = field(default_factory=dict)
-    weights: Optional[WeightStream] = None     # set by the model for steps of few tokens (see WeightStream)
-
-    def prefetch(self, nbytes: int):
-        """(address, bytes) of weights a kernel launched now should ask into L2, or (0, 0)."""
-        return self.weights.claim(nbytes) if self.weights is not None else (0, 0)

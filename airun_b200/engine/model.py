@@ -18,7 +18,6 @@ from typing import Dict, List, Optional, Tuple
 import torch
 
 from ..config.base import LayerCall, ModelConfig
-from .batch import WeightStream
 from ..parts.base import make_part
 from ..parts import embedding as _embedding_parts      # noqa: F401  (registers the embedding and head parts)
 from ..weights.loader import (DictSource, TensorSource, WeightSpec, load_tensors, random_tensors)
@@ -84,15 +83,6 @@ class DecoderModel:
         tensors = load_tensors(self.weight_specs(), source, self.dtype, self.device, self.ignorable_tensors())
         for p in self.parts():
             p.load_weights(tensors)
-        self.weight_stream = None
-        if self.dtype == torch.bfloat16 and self.device.type == "cuda":
-            from ..kernels import fast
-            if fast.PREFETCH_ON:
-                # the matrices of one pass in the order it reads them: every entry of the execution order, then the head
-                ws = [w for c in self.order for w in getattr(self.layers[c.layer], "stream_weights", lambda: [])()]
-                ws += getattr(self.head, "stream_weights", lambda: [])()
-                if ws:
-                    self.weight_stream = WeightStream([w for w in ws if w is not None])
 
     def load_random(self, seed: int) -> None:
         """Seeded random weights made on the model's device, through the same loading path."""
@@ -120,12 +110,6 @@ class DecoderModel:
     def forward(self, ctx, want_rows: Optional[torch.Tensor], n_want: int) -> Optional[torch.Tensor]:
         T = ctx.num_tokens
         ctx.ws_main.reset()
-        ctx.weights = None
-        if getattr(self, "weight_stream", None) is not None:
-            from ..kernels import fast
-            if T <= fast.PREFETCH_MAX_TOKENS:
-                self.weight_stream.reset()
-                ctx.weights = self.weight_stream
         x = ctx.ws_main.alloc((T, self.H), torch.float32)
         self.embedding.forward(ctx, ctx.token_ids[:T], x)
         delta = None

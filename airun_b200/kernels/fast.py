@@ -64,24 +64,6 @@ SCRATCH_COUNTERS = 1 << 16
 
 DISABLED = set(filter(None, os.environ.get("AIRUN_DISABLE_FAST", "").split(",")))
 
-# Bytes of the weights that come next which a kernel of a decode step asks into L2 (engine/batch.py
-# WeightStream): a product once its own stream is issued, decode attention likewise, the small kernels (norm,
-# q/k prologue) while they run.  About what memory delivers during the pause between two kernels.
-# AIRUN_PREFETCH=0 turns it off; AIRUN_PREFETCH_MB="product,attention,small" sets the three sizes.
-_pf = [float(v) for v in os.environ.get("AIRUN_PREFETCH_MB", "16,16,12").split(",")]
-PREFETCH_ON = os.environ.get("AIRUN_PREFETCH", "1") not in ("0", "")
-PF_PRODUCT, PF_ATTENTION, PF_SMALL = (int(v * (1 << 20)) for v in _pf)
-PREFETCH_MAX_TOKENS = 128              # steps of more tokens are not bound by streaming weights
-
-
-def claim(ctx, nbytes: int):
-    return ctx.prefetch(nbytes) if getattr(ctx, "weights", None) is not None else (0, 0)
-
-
-def consume(ctx, w: torch.Tensor) -> None:
-    if getattr(ctx, "weights", None) is not None:
-        ctx.weights.consume(w)
-
 
 def all_libraries():
     return [("gemm_tcgen05", None), ("gemm_tcgen05", {"AIRUN_FOLD_NORM": 1}), ("attention_plan", None), ("attention_mma", {"HD": 128}), ("attention_mma", {"HD": 64}),
@@ -108,10 +90,8 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: int, 
                  ksplit: int, err: torch.Tensor, scratch: Optional[torch.Tensor] = None,
                  counters: Optional[torch.Tensor] = None, ssq_in: Optional[torch.Tensor] = None,
                  eps_in: float = 0.0, norm_size: int = 0, resid: Optional[torch.Tensor] = None,
-                 norm_w: Optional[torch.Tensor] = None, ssq_out: Optional[torch.Tensor] = None,
-                 prefetch=(0, 0)) -> None:
-    """out = x @ w^T on tcgen05 (see csrc/gemm_tcgen05.cu for the modes).  ``prefetch``: (address, bytes) of
-    weights a later product reads, asked into L2 once this one's loads are issued.
+                 norm_w: Optional[torch.Tensor] = None, ssq_out: Optional[torch.Tensor] = None) -> None:
+    """out = x @ w^T on tcgen05 (see csrc/gemm_tcgen05.cu for the modes).
 
     ``ssq_in`` [parts, M] float32: x is bfloat16(residual * norm weight) and each token's results are
     scaled by rsqrt(sum of its parts / norm_size + eps_in).  ``epi == EPI_RESID``: ``resid`` [M, N]
@@ -157,15 +137,13 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: int, 
     f = _fn("gemm_tcgen05", "airun_gemm_tcgen05_ex",
             [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong,
              c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-             c_void_p, c_int, c_int, c_float, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_int,
-             c_void_p, c_longlong], fold)
+             c_void_p, c_int, c_int, c_float, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_int], fold)
     _check(f(_p(x), _p(w), _p(out), M, N, K, x.stride(0) if M > 1 else max(K, x.stride(0)),
              w.stride(0), out.stride(0) if M > 1 else max(out.shape[1], out.stride(0)),
              epi, 1 if swap else 0, bn, ksplit, _p(scratch), _p(counters), _p(err), _stream(),
              _p(ssq_in), ssq_in.shape[0] if ssq_in is not None else 0, ssq_in.shape[1] if ssq_in is not None else 0,
              float(eps_in), int(norm_size), _p(resid), resid.stride(0) if resid is not None and M > 1 else N,
-             _p(norm_w), _p(ssq_out), ssq_out.shape[1] if ssq_out is not None else 0,
-             c_void_p(prefetch[0] or None), int(prefetch[1])), "gemm_tcgen05")
+             _p(norm_w), _p(ssq_out), ssq_out.shape[1] if ssq_out is not None else 0), "gemm_tcgen05")
 
 
 def plan_gemm(M: int, N: int, K: int, mach: Optional[Machine] = None) -> Tuple[bool, int, int]:
@@ -213,9 +191,8 @@ def linear_bf16(ctx, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, normed
     if not _usable(x, w) or out.dtype not in (torch.float32, torch.bfloat16):
         return False
     swap, bn, ksplit = plan_gemm(x.shape[0], w.shape[0], x.shape[1])
-    consume(ctx, w)
     gemm_tcgen05(x, w, out, EPI_F32 if out.dtype == torch.float32 else EPI_BF16, swap, bn, ksplit, ctx.err,
-                 prefetch=claim(ctx, PF_PRODUCT), **_normed_args(normed))
+                 **_normed_args(normed))
     return True
 
 
@@ -223,9 +200,7 @@ def linear_swiglu_bf16(ctx, x: torch.Tensor, w_gu: torch.Tensor, out: torch.Tens
     if group != 16 or not _usable(x, w_gu) or w_gu.shape[0] % 32 != 0:
         return False
     swap, bn, ksplit = plan_gemm(x.shape[0], w_gu.shape[0], x.shape[1])
-    consume(ctx, w_gu)
-    gemm_tcgen05(x, w_gu, out, EPI_SWIGLU, swap, bn, ksplit, ctx.err, prefetch=claim(ctx, PF_PRODUCT),
-                 **_normed_args(normed))
+    gemm_tcgen05(x, w_gu, out, EPI_SWIGLU, swap, bn, ksplit, ctx.err, **_normed_args(normed))
     return True
 
 
@@ -248,9 +223,7 @@ def linear_resid_norm_bf16(ctx, x: torch.Tensor, w: torch.Tensor, resid: torch.T
     M, K = x.shape
     N = w.shape[0]
     swap, bn, ksplit = plan_gemm(M, N, K)
-    consume(ctx, w)
-    gemm_tcgen05(x, w, h_out, EPI_RESID, swap, bn, ksplit, ctx.err, resid=resid, norm_w=norm_w, ssq_out=ssq_out,
-                 prefetch=claim(ctx, PF_PRODUCT))
+    gemm_tcgen05(x, w, h_out, EPI_RESID, swap, bn, ksplit, ctx.err, resid=resid, norm_w=norm_w, ssq_out=ssq_out)
     return resid_parts(N, swap, bn)
 
 
@@ -327,8 +300,7 @@ def attn_prefill_tc(ctx, q, out, cache, nh, nkv, hd, scale, window, tiles: torch
 
 def attn_decode(ctx, q, out, cache, nh, nkv, hd, scale, window, rows: torch.Tensor, n_rows: int, n_splits: int,
                 n_rows_dev: Optional[torch.Tensor] = None, dyn_slots: int = 0,
-                k_begin_dev: Optional[torch.Tensor] = None, extra_slices: int = 0, early: Optional[bool] = None,
-                prefetch=(0, 0)) -> None:
+                k_begin_dev: Optional[torch.Tensor] = None, extra_slices: int = 0, early: Optional[bool] = None) -> None:
     """Attention of single decoded tokens (batch rows ``rows``; None: rows 0..n_rows-1), the keys cut
     into ``n_splits`` slices.  With ``n_rows_dev`` (int32 on the device) the launch is made for ``n_rows``
     rows and ``n_splits`` slices, runs the rows counted there, and every row picks its slices itself so
@@ -355,10 +327,10 @@ def attn_decode(ctx, q, out, cache, nh, nkv, hd, scale, window, rows: torch.Tens
               "split-K scratch is too small for this decode launch")
     f = _fn("attention_mma", "airun_attn_decode",
             _COMMON_SIG + [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p,
-                           c_longlong, c_void_p, c_void_p], {"HD": hd})
+                           c_void_p], {"HD": hd})
     _check(f(*_attn_common_args(q, out, cache, ctx, nh, nkv, scale, window), _p(rows), n_rows, n_splits,
              _p(scratch), _p(counters), _p(n_rows_dev), int(dyn_slots), _p(k_begin_dev), int(extra_slices),
-             1 if early else 0, c_void_p(prefetch[0] or None), int(prefetch[1]), _p(ctx.err), _stream()), "attn_decode")
+             1 if early else 0, _p(ctx.err), _stream()), "attn_decode")
 
 
 def attn_shared_prefix(ctx, q, cache, nh, nkv, hd, scale, n_rows: int, k_end_dev: torch.Tensor, slices: int,
@@ -510,7 +482,7 @@ def attention_bf16(ctx, q, out, cache, nh: int, nkv: int, hd: int, scale: float,
             fit = max(1, slots // (plan["min_rows"] * nkv * ((G + 15) // 16)))
             most = max(1, min(64, (context + DECODE_MIN_KEYS_PER_SPLIT - 1) // DECODE_MIN_KEYS_PER_SPLIT, fit))
             attn_decode(ctx, q, out, cache, nh, nkv, hd, scale, window, plan["rows"], plan["n_rows"], most,
-                        n_rows_dev, slots, prefetch=claim(ctx, PF_ATTENTION))
+                        n_rows_dev, slots)
         elif (ctx.extras.get("use_shared_prefix") and plan["rows"] is None and window == 0
               and getattr(cache, "shared_prefix", None) is not None and _shared_prefix_slices(plan["n_rows"], nkv, G, hd) > 0):
             # the requests of the batch begin with the same pages: those keys once for all tokens (in
@@ -520,11 +492,10 @@ def attention_bf16(ctx, q, out, cache, nh: int, nkv: int, hd: int, scale: float,
                                            mach.sms if prefill_tc_supported(hd, cache.page_size) else 2 * mach.sms)
             attn_shared_prefix(ctx, q, cache, nh, nkv, hd, scale, plan["n_rows"], cache.shared_prefix, slices, splits)
             attn_decode(ctx, q, out, cache, nh, nkv, hd, scale, window, None, plan["n_rows"], splits,
-                        k_begin_dev=cache.shared_prefix, extra_slices=slices, prefetch=claim(ctx, PF_ATTENTION))
+                        k_begin_dev=cache.shared_prefix, extra_slices=slices)
         else:
             splits = plan_decode_splits(plan["n_rows"], nkv, (G + 15) // 16, context, hd, slots)
-            attn_decode(ctx, q, out, cache, nh, nkv, hd, scale, window, plan["rows"], plan["n_rows"], splits,
-                        prefetch=claim(ctx, PF_ATTENTION))
+            attn_decode(ctx, q, out, cache, nh, nkv, hd, scale, window, plan["rows"], plan["n_rows"], splits)
     return True
 
 

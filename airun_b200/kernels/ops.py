@@ -130,14 +130,12 @@ def copy_pages(pool: torch.Tensor, pairs: torch.Tensor, err: Optional[torch.Tens
 
 
 def rmsnorm(x: torch.Tensor, weight: Optional[torch.Tensor], eps: float, out: torch.Tensor,
-            delta: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None,
-            prefetch=(0, 0)) -> None:
+            delta: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None) -> None:
     """out = rmsnorm(x [+ delta]) * weight.
 
     With ``delta`` and no ``rows`` the sum is written back into ``x`` (the
     residual stream).  With ``rows`` only those rows are normed, into
-    out[0..len(rows)), and ``x`` is left as it is.  ``prefetch``: (address, bytes) of weights a later
-    product reads, asked into L2 meanwhile (StepContext.prefetch; used when few rows are normed).
+    out[0..len(rows)), and ``x`` is left as it is.
     """
     _cuda(x, weight, out, delta, rows)
     _need(x.dtype == torch.float32 and x.dim() == 2 and x.is_contiguous(), "x must be float32 [T, n]")
@@ -155,11 +153,10 @@ def rmsnorm(x: torch.Tensor, weight: Optional[torch.Tensor], eps: float, out: to
     _need(out.dim() == 2 and out.shape[0] >= n_rows and out.shape[1] == n and out.is_contiguous(),
           "norm output must be [rows, n]")
     f = _fn("elementwise", "airun_rmsnorm",
-            [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_int, c_void_p,
-             c_longlong, c_void_p])
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_int, c_void_p])
     write_back = 1 if (delta is not None and rows is None) else 0
     _check(f(_p(x), _p(delta), _p(weight), _p(out), _dt(out), _p(rows), n_rows, n, float(eps), write_back,
-             c_void_p(prefetch[0] or None), int(prefetch[1]), _stream()), "rmsnorm")
+             _stream()), "rmsnorm")
 
 
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor, group: int) -> None:
@@ -209,8 +206,7 @@ def qkv_post(qkv: torch.Tensor, q_out: torch.Tensor, q_norm_w: Optional[torch.Te
              req_of_token: torch.Tensor, rope_kind: int, rotary_dim: int, inv_freq: Optional[torch.Tensor],
              pool: Optional[torch.Tensor], block_table: Optional[torch.Tensor], num_reqs: int,
              page_size: int, nh: int, nkv: int, hd: int, err: torch.Tensor,
-             store: bool = True, kv_in_row: bool = True, rope_positions: Optional[torch.Tensor] = None,
-             prefetch=(0, 0)) -> None:
+             store: bool = True, kv_in_row: bool = True, rope_positions: Optional[torch.Tensor] = None) -> None:
     """Per-head norm, rotary encoding, q out, k/v into their pages (see csrc/qkv_post.cu).
 
     ``pool`` is one layer's pages [num_pages, 2, nkv, page_size, hd].  ``rope_kind``: ROPE_NONE, ROPE_NEOX
@@ -246,12 +242,11 @@ def qkv_post(qkv: torch.Tensor, q_out: torch.Tensor, q_norm_w: Optional[torch.Te
     f = _fn("qkv_post", "airun_qkv_post",
             [c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int,
              c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-             c_int, c_int, c_int, c_void_p, c_void_p, c_longlong, c_void_p])
+             c_int, c_int, c_int, c_void_p, c_void_p])
     _check(f(_p(qkv), qkv.stride(0), _p(q_out), _dt(q_out), _p(q_norm_w), _p(k_norm_w), float(eps),
              _p(positions), _p(req_of_token), T, int(rope_kind), int(rotary_dim), _p(inv_freq), _p(rope_positions),
              _p(pool), _dt(q_out), _p(block_table), max_blocks, int(num_reqs), num_pages, int(page_size),
-             1 if do_store else 0, 1 if kv_in_row else 0, nh, nkv, hd, _p(err), c_void_p(prefetch[0] or None),
-             int(prefetch[1]), _stream()), "qkv_post")
+             1 if do_store else 0, 1 if kv_in_row else 0, nh, nkv, hd, _p(err), _stream()), "qkv_post")
 
 
 def attention_generic(q: torch.Tensor, out: torch.Tensor, pool: torch.Tensor, block_table: torch.Tensor,

@@ -70,10 +70,6 @@ class GQAAttention(Mixer):
             self.q_norm_w, self.k_norm_w = tensors[nm["q_norm"]], tensors[nm["k_norm"]]
         self.pos.load_weights(tensors)
 
-    def stream_weights(self) -> List[torch.Tensor]:
-        """The matrices a pass reads, in order (engine/batch.py WeightStream)."""
-        return [self.w_qkv, self.w_o]
-
     # ---- cache ----
     def cache_spec(self):
         return PagedKVSpec(self.nkv, self.hd, self.window)
@@ -88,14 +84,10 @@ class GQAAttention(Mixer):
         linear(ctx, h, self.w_qkv if owns else self.w_q, qkv)
         q = ws.alloc((T, self.nh * self.hd), self.dtype)
         kind, rdim, inv_freq = self.pos.fused()
-        prefetch = (0, 0)
-        if getattr(ctx, "weights", None) is not None:
-            from ..kernels import fast
-            prefetch = ctx.prefetch(fast.PF_SMALL)
         ops.qkv_post(qkv, q, self.q_norm_w, self.k_norm_w, self.qk_norm_eps, ctx.positions, ctx.req_of_token,
                      kind, rdim, inv_freq, cache.pool, cache.block_table, ctx.num_reqs, cache.page_size,
                      self.nh, self.nkv, self.hd, ctx.err, store=owns, kv_in_row=owns,
-                     rope_positions=self.pos.rotation_positions(ctx), prefetch=prefetch)
+                     rope_positions=self.pos.rotation_positions(ctx))
         attn = ws.alloc((T, self.nh * self.hd), self.dtype)
         self.attend(ctx, q, attn, cache)
         fused = linear_into_residual(ctx, attn, self.w_o, sink)

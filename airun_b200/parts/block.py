@@ -38,10 +38,6 @@ class PreNormBlock(Part):
     def cache_spec(self):
         return self.mixer.cache_spec()
 
-    def stream_weights(self) -> List[torch.Tensor]:
-        """The matrices a pass through this block reads, in order (parts without the method have none to tell)."""
-        return [w for p in (self.mixer, self.ffn) for w in getattr(p, "stream_weights", lambda: [])()]
-
     def device_driven(self) -> bool:
         """Do all parts of this block read the batch's layout from the device arrays only?"""
         return all(getattr(p, "device_driven", False) for p in self.parts())

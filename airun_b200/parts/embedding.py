@@ -56,9 +56,6 @@ class LMHead(Head):
     def load_weights(self, tensors: Dict[str, torch.Tensor]) -> None:
         self.weight = self.tied_to.table if self.tied_to is not None else tensors[self.name]
 
-    def stream_weights(self) -> List[torch.Tensor]:
-        return [self.weight]
-
     def forward(self, ctx, h: torch.Tensor, out: torch.Tensor) -> None:
         linear(ctx, h, self.weight, out)
         if self.soft_cap is not None:

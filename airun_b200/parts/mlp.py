@@ -48,10 +48,6 @@ class SwiGLU(FeedForward):
             .reshape(2 * self.I, self.H).contiguous()
         self.w_down = tensors.pop(nm["down"])
 
-    def stream_weights(self) -> List[torch.Tensor]:
-        """The matrices a pass reads, in order (engine/batch.py WeightStream)."""
-        return [self.w_gu, self.w_down]
-
     def forward(self, ctx, h, sink=None):
         normed = h if isinstance(h, NormedActivations) else None
         hx = normed.h if normed is not None else h

@@ -32,12 +32,7 @@ class RMSNorm(Norm):
         self.weight = tensors[self.name]
 
     def forward(self, ctx, x, out, delta=None, rows=None) -> None:
-        n_rows = rows.shape[0] if rows is not None else x.shape[0]
-        prefetch = (0, 0)
-        if n_rows < 256 and getattr(ctx, "weights", None) is not None:
-            from ..kernels import fast
-            prefetch = ctx.prefetch(fast.PF_SMALL)       # few rows: the weights that come next into L2 meanwhile
-        ops.rmsnorm(x, self.weight, self.eps, out, delta=delta, rows=rows, prefetch=prefetch)
+        ops.rmsnorm(x, self.weight, self.eps, out, delta=delta, rows=rows)
 
     def fusable(self):
         """(weight, eps) for products that fold this norm in (out = x * rsqrt(mean x^2 + eps) * weight)."""
