@@ -314,25 +314,33 @@ __device__ __forceinline__ float store_resid_normal(const GemmParams& p, const f
 }
 
 // EPI_RESID, swapped mode: this lane's weight row a_row, 16 tokens from b0 + c0.  The sums of squares
-// over the warp's 32 weight rows go to part (a_row / 32) of each token.
-__device__ __forceinline__ void store_resid_swapped(const GemmParams& p, const float* v, int a_row, int b0, int c0) {
+// over the warp's 32 weight rows go to ssq_warp[c0 + token] in shared memory; the caller adds the four
+// warps of the tile and stores one part per tile and token.
+__device__ __forceinline__ void store_resid_swapped(const GemmParams& p, const float* v, int a_row, int b0, int c0,
+                                                    float* ssq_warp) {
     const int lane = threadIdx.x & 31;
     const bool row_ok = a_row < p.a_rows;
     const float g = row_ok ? p.norm_w[a_row] : 0.0f;
+    // the residual's values of all 16 tokens first: sixteen loads in flight, not sixteen round trips in turn
+    float xv[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const int tok = b0 + c0 + i;
+        xv[i] = (row_ok && tok < p.b_rows) ? __ldcg(p.resid + (size_t)tok * p.ld_resid + a_row) : 0.0f;
+    }
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
         const int tok = b0 + c0 + i;
         float sq = 0.0f;
         if (row_ok && tok < p.b_rows) {
-            float* xr = p.resid + (size_t)tok * p.ld_resid + a_row;
-            const float xn = *xr + v[i];
-            *xr = xn;
+            const float xn = xv[i] + v[i];
+            p.resid[(size_t)tok * p.ld_resid + a_row] = xn;
             sq = xn * xn;
             ((__nv_bfloat16*)p.out)[(size_t)tok * p.ldc + a_row] = __float2bfloat16_rn(xn * g);
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
-        if (lane == 0 && tok < p.b_rows) p.ssq_out[(size_t)(a_row >> 5) * p.ssq_out_ld + tok] = sq;
+        if (lane == 0) ssq_warp[c0 + i] = sq;
     }
 }
 
@@ -396,6 +404,7 @@ __global__ __launch_bounds__(GEMM_THREADS, 1) void gemm_tcgen05_kernel(
     const int a_row = a0 + quad * 32 + lane;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
     __shared__ float s_scale[SWAP ? BN : 1];
+    __shared__ float s_ssq[4][(SWAP && AIRUN_FOLD_NORM) ? BN : 1];       // per epilogue warp: sums of squares per token
     float row_scale = 1.0f;
     bool ok = true;
     const bool direct = p.ksplit == 1;
@@ -463,13 +472,22 @@ __global__ __launch_bounds__(GEMM_THREADS, 1) void gemm_tcgen05_kernel(
                 if (SWAP) store_swiglu_swapped(p, v, a_row, b0, c);
                 else store_swiglu_normal(p, v, u, a_row, b0, c);
             } else if (EPI == EPI_RESID) {
-                if (SWAP) store_resid_swapped(p, v, a_row, b0, c);
+                if (SWAP) store_resid_swapped(p, v, a_row, b0, c, s_ssq[quad]);
                 else ssq_acc += store_resid_normal(p, v, a_row, b0 + c);
             } else {
                 store_chunk<EPI, SWAP>(p, v, a_row, b0, c);
             }
         }
         if (EPI == EPI_RESID && !SWAP && a_row < p.a_rows) p.ssq_out[(size_t)blockIdx.y * p.ssq_out_ld + a_row] = ssq_acc;
+        if (AIRUN_FOLD_NORM && EPI == EPI_RESID && SWAP) {
+            // one part per tile of 128 weight rows: the four warps' sums, for the tokens this block has stored
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            for (int j = threadIdx.x - 64; j < BN; j += 128) {
+                const bool mine = rank < 0 || (j / STEP) % p.ksplit == rank;
+                if (mine && b0 + j < p.b_rows)
+                    p.ssq_out[(size_t)blockIdx.x * p.ssq_out_ld + b0 + j] = s_ssq[0][j] + s_ssq[1][j] + s_ssq[2][j] + s_ssq[3][j];
+            }
+        }
     };
 
     if (warp == 0) {
@@ -513,7 +531,30 @@ __global__ __launch_bounds__(GEMM_THREADS, 1) void gemm_tcgen05_kernel(
         // token scales of a normed input, while the MMAs run
         if (AIRUN_FOLD_NORM && p.ssq_in) {
             if (SWAP) {
-                for (int j = threadIdx.x - 64; j < BN; j += 128) s_scale[j] = b0 + j < p.b_rows ? token_scale(p, b0 + j) : 0.0f;
+                // the parts of 16 tokens at a time: every thread takes every 128th part, the warps add theirs up
+                // and the four warp sums meet in shared memory (one round trip to L2 for all parts)
+                const int t = threadIdx.x - 64;
+                for (int j0 = 0; j0 < BN; j0 += 16) {
+                    float acc[16];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) acc[i] = 0.0f;
+                    for (int part = t; part < p.ssq_parts; part += 128) {
+                        const float* src = p.ssq_in + (size_t)part * p.ssq_ld + b0 + j0;
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) acc[i] += (b0 + j0 + i < p.b_rows) ? __ldcg(src + i) : 0.0f;
+                    }
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        float a = acc[i];
+#pragma unroll
+                        for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+                        if (lane == 0) s_ssq[quad][j0 + i] = a;
+                    }
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                for (int j = t; j < BN; j += 128)
+                    s_scale[j] = b0 + j < p.b_rows
+                        ? rsqrtf((s_ssq[0][j] + s_ssq[1][j] + s_ssq[2][j] + s_ssq[3][j]) * p.inv_n_in + p.eps_in) : 0.0f;
                 asm volatile("bar.sync 1, 128;" ::: "memory");
             } else if (a_row < p.a_rows) {
                 row_scale = token_scale(p, a_row);
@@ -913,7 +954,7 @@ AIRUN_EXPORT long long airun_gemm_tcgen05_scratch_floats(int M, int N, int swap,
 // out[M][N] = x[M][K] * W[N][K]^T.  x, W bfloat16 row-major (K % 8 == 0, 16-byte aligned rows).
 // epi: 0 float32 out [M][N]; 1 bfloat16 out [M][N]; 2 SwiGLU, bfloat16 out [M][N/2];
 //      3 residual + norm: resid[M][N] += result, out[M][N] = bfloat16(resid * norm_w), ssq_out[parts][ssq_out_ld]
-//        = sums of resid^2 per token; parts = 4 * ceil(N / 128) when swapped, ceil(N / bn) otherwise.
+//        = sums of resid^2 per token; parts = ceil(N / 128) when swapped, ceil(N / bn) otherwise.
 // swap: weights as the 128-row operand (bn >= M, one B tile per 'bn' tokens).
 // counters: one int per tile, zero on entry when ksplit > 1 (the kernel leaves them zero).
 // ssq_in: when not null, x is an un-normalised bfloat16(resid * norm_w) and every token's results are

@@ -83,7 +83,7 @@ def scratch_for(device: torch.device) -> Tuple[torch.Tensor, torch.Tensor]:
 
 def resid_parts(N: int, swap: bool, bn: int) -> int:
     """Parts the residual + norm epilogue writes the sums of squares in."""
-    return 4 * ((N + 127) // 128) if swap else (N + bn - 1) // bn
+    return (N + 127) // 128 if swap else (N + bn - 1) // bn
 
 
 def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: int, swap: bool, bn: int,
@@ -228,7 +228,7 @@ def linear_resid_norm_bf16(ctx, x: torch.Tensor, w: torch.Tensor, resid: torch.T
 
 
 def max_resid_parts(N: int) -> int:
-    return 4 * ((N + 127) // 128)
+    return (N + 127) // 128
 
 
 # ---------------------------------------------------------------- attention

@@ -184,7 +184,7 @@ def test_gemm_tcgen05_against_the_plain_kernel(M, N, K, epi, swap, bn, ksplit):
 @pytest.mark.parametrize("M,N,K,swap,bn,ksplit", [(8, 256, 512, True, 16, 1), (5, 328, 1024, True, 16, 4),
                                                    (40, 1024, 2048, True, 64, 3), (100, 264, 512, True, 128, 2),
                                                    (300, 520, 256, False, 256, 1), (1000, 2304, 320, False, 256, 1),
-                                                   (200, 392, 512, False, 128, 2)])
+                                                   (200, 392, 512, False, 128, 2), (8, 16640, 256, True, 16, 1)])
 def test_gemm_tcgen05_folded_norm(M, N, K, swap, bn, ksplit):
     """The product that ends a sub-layer adds into the residual and prepares the next norm; the
     product that starts the next sub-layer applies the token scales: together they equal
