@@ -10,13 +10,16 @@
 // in float32; probabilities are rounded to bfloat16 for the P.V product.  Key j is
 // visible to a query at position p iff j <= p and (window == 0 or p - j < window).
 //
-//  attn_prefill: one CTA = 64 packed rows (64/G tokens x G heads) of one request and
-//    KV head; 4 warps x 16 rows; K/V tiles of 64 keys gathered page by page with
+//  attn_prefill: one CTA = 128 packed rows (128/G tokens x G heads) of one request and
+//    KV head; 8 warps x 16 rows; K/V tiles of 64 keys gathered page by page with
 //    cp.async into double-buffered, swizzled shared memory; tiles wholly hidden by
-//    the causal rule or the window are skipped.
+//    the causal rule or the window are skipped.  The blocks of the tiles with the most
+//    keys, of all KV heads, start first.
 //  attn_decode: one CTA = one token, one KV head (16 heads of its group at most),
-//    one slice of the keys; its 4 warps take 16-key tiles in turn with private
-//    cp.async stages and merge in shared memory.  With more than one slice each CTA
+//    one slice of the keys; its 4 warps take 16-key tiles in turn with private stages
+//    (three, filled by cp.async.bulk.tensor, when pages are powers of two >= 16 and the
+//    head size a multiple of 64; else two, filled by cp.async) and merge in shared
+//    memory.  With more than one slice each CTA
 //    writes (max, sum, acc) to scratch and the last CTA of the token and head (a
 //    counter, no spinning) merges the slices in order.
 #include "common.cuh"

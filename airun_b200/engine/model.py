@@ -83,6 +83,77 @@ class DecoderModel:
         tensors = load_tensors(self.weight_specs(), source, self.dtype, self.device, self.ignorable_tensors())
         for p in self.parts():
             p.load_weights(tensors)
+        del tensors
+        if self.device.type == "cuda":
+            self.pack_weights()
+
+    ARENA_ALIGN = 256
+
+    def pack_weights(self) -> None:
+        """Moves every tensor the parts hold (weights as the parts keep them: stacked, interleaved, tables)
+        into ONE allocation, each at a 256-byte boundary, and gives the memory they came from back.  The
+        reference keeps a layer's weights in one arena with 256-byte aligned sub-allocations for the same
+        reasons: one allocation instead of hundreds, none of the allocator's rounding per tensor, and
+        addresses that suit vector and bulk loads (crates/airun-core/src/model.rs:1332-1393).  Tensors that
+        share memory (a tied head and the table; the q rows of the stacked q/k/v matrix) still do afterwards.
+        Parts are found by walking the attributes of the model's parts, so a part needs nothing for it."""
+        slots = []                                           # (holder, key, tensor): holder[key] or holder.key
+        seen = set()
+
+        def walk(obj):
+            if id(obj) in seen:
+                return
+            seen.add(id(obj))
+            items = vars(obj).items() if hasattr(obj, "__dict__") else ()
+            for key, val in list(items):
+                if isinstance(val, torch.Tensor):
+                    if val.device == self.device:
+                        slots.append((obj, key, val))
+                elif isinstance(val, (list, tuple)):
+                    if isinstance(val, list):
+                        for i, v in enumerate(val):
+                            if isinstance(v, torch.Tensor) and v.device == self.device:
+                                slots.append((val, i, v))
+                            elif hasattr(v, "weight_specs"):
+                                walk(v)
+                    else:
+                        for v in val:
+                            if hasattr(v, "weight_specs"):
+                                walk(v)
+                elif hasattr(val, "weight_specs"):
+                    walk(val)
+
+        for p in self.parts():
+            walk(p)
+        if not slots:
+            return
+        storages = {}                                        # storage address -> (bytes, offset in the arena)
+        total = 0
+        for _, _, t in slots:
+            st = t.untyped_storage()
+            if st.data_ptr() not in storages:
+                storages[st.data_ptr()] = (st, total)
+                total += (st.nbytes() + self.ARENA_ALIGN - 1) // self.ARENA_ALIGN * self.ARENA_ALIGN
+        arena = torch.empty(total + self.ARENA_ALIGN, dtype=torch.uint8, device=self.device)
+        base = (-arena.data_ptr()) % self.ARENA_ALIGN        # torch aligns to 512 bytes already; be sure of it
+        moved = {}
+        for ptr, (st, off) in storages.items():
+            n = st.nbytes()
+            dst = arena[base + off: base + off + n]
+            dst.copy_(torch.empty(0, dtype=torch.uint8, device=self.device).set_(st, 0, (n,), (1,)))
+            moved[ptr] = dst
+        for holder, key, t in slots:
+            dst = moved[t.untyped_storage().data_ptr()]
+            esz = t.element_size()
+            view = dst.view(t.dtype) if dst.numel() % esz == 0 else dst[: dst.numel() // esz * esz].view(t.dtype)
+            new = torch.as_strided(view, t.shape, t.stride(), view.storage_offset() + t.storage_offset())
+            if isinstance(holder, list):
+                holder[key] = new
+            else:
+                setattr(holder, key, new)
+        self.weight_arena = arena
+        del storages, moved, slots
+        torch.cuda.empty_cache()
 
     def load_random(self, seed: int) -> None:
         """Seeded random weights made on the model's device, through the same loading path."""

@@ -332,11 +332,17 @@ def workload_serve(a) -> int:
         torch.cuda.synchronize()
         t0 = time.perf_counter()
         steps = 0
+        events = []
         while eng.has_work():
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ev0.record()
             eng.run_step()
+            ev1.record()
+            events.append((ev0, ev1))
             steps += 1
         torch.cuda.synchronize()
         sec = time.perf_counter() - t0
+        gpu_sec = sum(a.elapsed_time(b) for a, b in events) / 1e3     # device time inside the steps; the rest is the host's
         clocks = sampler.stop()
         gen = sum(len(r.output) for r in reqs)
         assert gen == n_req * new, "a request ended early"
@@ -345,6 +351,7 @@ def workload_serve(a) -> int:
                "step_budget": a.budget, "seconds": round(sec, 3), "steps": steps,
                "ms_per_step": round(sec * 1e3 / steps, 3),
                "total_tokens_per_s": round((sum(lens) + gen) / sec, 1), "decode_tokens_per_s": round(gen / sec, 1),
+               "device_seconds_in_steps": round(gpu_sec, 3), "host_share": round(max(0.0, 1.0 - gpu_sec / sec), 4),
                "preemptions": eng.scheduler.stats["preemptions"], "dtype": a.dtype, "clocks": clocks}
     print(json.dumps(res))
     return 0

@@ -333,3 +333,25 @@ def test_random_weights_are_a_function_of_seed_name_and_index():
         assert ours[n].dtype == mine[n].dtype and torch.equal(ours[n], mine[n]), n
     i = fill_random_host(1000, tensor_key(1, "t"), "int", 0.0)
     assert i.dtype == np.int32 and i.min() >= 0 and i.max() < 2 ** 15
+
+
+def test_weights_are_packed_into_one_allocation():
+    """Every tensor the parts hold moves into one arena, 256-byte aligned, unchanged, and tensors that shared
+    memory (a tied head and the table, the q rows of the stacked q/k/v matrix) still share it."""
+    cfg = Qwen3Config.from_dict(TINY["A"]["cfg"])                      # tied head
+    m = DecoderModel(cfg, torch.float32, "cpu")
+    m.load(DictSource(random_tensors(m.weight_specs(), 1)))
+    mx, ffn = m.layers[0].mixer, m.layers[1].ffn
+    before = [t.clone() for t in (mx.w_qkv, mx.w_q, mx.w_o, ffn.w_gu, ffn.w_down, m.final_norm.weight, mx.pos.inv_freq,
+                                  m.embedding.table)]
+    import unittest.mock
+    with unittest.mock.patch.object(torch.cuda, "empty_cache", lambda: None):
+        m.pack_weights()
+    after = (mx.w_qkv, mx.w_q, mx.w_o, ffn.w_gu, ffn.w_down, m.final_norm.weight, mx.pos.inv_freq, m.embedding.table)
+    lo, hi = m.weight_arena.data_ptr(), m.weight_arena.data_ptr() + m.weight_arena.numel()
+    for b, a in zip(before, after):
+        assert torch.equal(a, b) and a.dtype == b.dtype
+        assert lo <= a.data_ptr() and a.data_ptr() + a.numel() * a.element_size() <= hi
+    for t in (mx.w_qkv, mx.w_o, ffn.w_gu, ffn.w_down, m.final_norm.weight, m.embedding.table):
+        assert t.data_ptr() % 256 == 0
+    assert mx.w_q.data_ptr() == mx.w_qkv.data_ptr() and m.head.weight.data_ptr() == m.embedding.table.data_ptr()
