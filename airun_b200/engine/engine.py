@@ -57,6 +57,8 @@ class GenerationStats:
     decode_ms: float = 0.0
     steps: int = 0
     preemptions: int = 0
+    host_gap_ms: float = 0.0       # time from reading a step's result to having launched the next step: the GPU
+                                   # may idle for as long (an upper bound on what the host costs)
 
     @property
     def prefill_tps(self) -> float:
@@ -107,6 +109,7 @@ class Engine:
         self.stats = GenerationStats()
         self._ahead = None        # (requests, prepared step): the next decode step, laid out while this one runs
         self._host_rows = None    # buffers for the logits rows the host samples
+        self._result_read_at = None
 
     # ------------------------------------------------------------ construction
     @staticmethod
@@ -233,6 +236,9 @@ class Engine:
             logits = self.runner.launch_prepared(prep, [t for e in entries for t in e.tokens])
         else:
             logits = self.runner.step(entries, checked=True)
+        if self._result_read_at is not None:
+            self.stats.host_gap_ms += (time.perf_counter() - self._result_read_at) * 1e3
+            self._result_read_at = None
         self.scheduler.advance(plan)
         if wanting:
             tokens = self._sample(logits, wanting, look_ahead=True)
@@ -300,6 +306,7 @@ class Engine:
         if look_ahead and not host_rows and self._ahead is None:
             self._prepare_ahead(reqs)                      # the GPU is busy: plan and lay out the next step meanwhile
         torch.cuda.current_stream().synchronize()
+        self._result_read_at = time.perf_counter()
         picked = self._picked_host.numpy()
         if picked[R]:
             self.runner.err.zero_()
