@@ -104,6 +104,28 @@ __device__ __forceinline__ void umma_bf16_ta(uint32_t tmem_d, uint32_t tmem_a, u
         "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
         ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
 }
+// The same with each descriptor as (low word, high word).  The low word holds the start address in units of 16
+// bytes (shared memory ends below 2^18, so adding an offset never carries out of the field): a step along K is
+// one 32-bit add on a value computed once, which keeps the issuing thread, that shares its scheduler with two
+// softmax warps, ahead of the tensor cores.
+__device__ __forceinline__ void umma_bf16_lh(uint32_t tmem_d, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
+                                             uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "mov.b64 da, {%1, %2};\n\t"
+        "mov.b64 db, {%3, %4};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}"
+        ::"r"(tmem_d), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_bf16_ta_lh(uint32_t tmem_d, uint32_t tmem_a, uint32_t b_lo, uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -591,7 +613,8 @@ __global__ __launch_bounds__(TC_THREADS, 1) void attn_prefill_tc_kernel(
 //   warp 0    : TMA producer, as above;
 //   warp 1    : the products, in the order S_A0 S_B0 | O_A0 S_A1 O_B0 S_B1 | O_A1 S_A2 ...  The tensor
 //               cores run them in this order, so S_X(j+1) may overwrite P_X(j) right behind O_X(j), and
-//               the barrier that reports S_X(j+1) reports O_X(j) too;
+//               the barrier that reports S_X(j+1) reports O_X(j) too.  O_X(j) starts on keys 0-63 as soon
+//               as their P stands (a barrier of its own), while the softmax still works on keys 64-127;
 //   warps 2-5 : softmax of Q tile A, one thread per row (all 128 keys of a tile, all head dimensions);
 //   warps 6-9 : the same for Q tile B.  While one warpgroup works on its S tile the tensor cores work
 //               for the other.
@@ -600,9 +623,9 @@ constexpr int W_OFF_Q = 0;                              // two Q tiles
 constexpr int W_OFF_K = 2 * Q_BYTES;                    // 2 stages
 constexpr int W_OFF_V = W_OFF_K + 2 * KV_BYTES;         // 2 stages
 constexpr int W_OFF_BAR = W_OFF_V + 2 * KV_BYTES;
-constexpr int W_N_BARS = 13;
+constexpr int W_N_BARS = 15;
 constexpr int W_SMEM_TOTAL = W_OFF_BAR + W_N_BARS * 8 + 64 + 1024;
-enum { W_KFULL = 0, W_KEMPTY = 2, W_VFULL = 4, W_VEMPTY = 6, W_SFULL = 8, W_PFULL = 10, W_FINAL = 12 };
+enum { W_KFULL = 0, W_KEMPTY = 2, W_VFULL = 4, W_VEMPTY = 6, W_SFULL = 8, W_PFULL = 10, W_FINAL = 12, W_PHALF = 13 };
 
 __global__ __launch_bounds__(TC_THREADS, 1) void attn_prefill_wide_kernel(
     const TcParams p, const int4* __restrict__ tiles, const __grid_constant__ CUtensorMap kv_map,
@@ -621,6 +644,7 @@ __global__ __launch_bounds__(TC_THREADS, 1) void attn_prefill_wide_kernel(
         mbar_init(BAR(W_SFULL), 1); mbar_init(BAR(W_SFULL + 1), 1);
         mbar_init(BAR(W_PFULL), 4); mbar_init(BAR(W_PFULL + 1), 4);      // one arrival per warp of the tile's warpgroup
         mbar_init(BAR(W_FINAL), 1);
+        mbar_init(BAR(W_PHALF), 4); mbar_init(BAR(W_PHALF + 1), 4);      // P of keys 0-63 of a tile
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -698,8 +722,12 @@ __global__ __launch_bounds__(TC_THREADS, 1) void attn_prefill_wide_kernel(
         if (lane == 0) {
             constexpr uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(KN >> 3) << 17) | ((uint32_t)(QM >> 4) << 24);
             constexpr uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(QM >> 4) << 24);
-            const uint32_t q_addr = smem_u32(smem + W_OFF_Q);
             const int last_x = two ? 1 : 0;
+            // descriptors of the first Q, K and V tiles; the others and the steps along K are offsets of the low word
+            const uint64_t qd = desc_kmajor(smem_u32(smem + W_OFF_Q)), kd = desc_kmajor(smem_u32(smem + W_OFF_K)),
+                           vd = desc_mnmajor(smem_u32(smem + W_OFF_V));
+            const uint32_t q_lo = (uint32_t)qd, q_hi = (uint32_t)(qd >> 32), k_lo = (uint32_t)kd, k_hi = (uint32_t)(kd >> 32),
+                           v_lo = (uint32_t)vd, v_hi = (uint32_t)(vd >> 32);
             // first phase of P_full: the Q tiles are in shared memory
             bool ok = mbar_wait(BAR(W_PFULL), 0) && (!two || mbar_wait(BAR(W_PFULL + 1), 0));
             auto issue_s = [&](int it, int x) -> bool {          // S of Q tile x and key tile it
@@ -708,12 +736,11 @@ __global__ __launch_bounds__(TC_THREADS, 1) void attn_prefill_wide_kernel(
                     if (!mbar_wait(BAR(W_KFULL + s), (it >> 1) & 1)) return false;
                     tc_fence_after();
                 }
-                const uint32_t k_addr = smem_u32(smem + W_OFF_K + s * KV_BYTES);
+                const uint32_t qx = q_lo + x * (Q_BYTES >> 4), ks = k_lo + s * (KV_BYTES >> 4), d = tmem_base + x * KN;
 #pragma unroll
                 for (int k = 0; k < HD / 16; ++k) {
-                    const uint32_t off = (k >> 2) * ROWBLK + (k & 3) * 32;
-                    umma_bf16(tmem_base + x * KN, desc_kmajor(q_addr + x * Q_BYTES + off), desc_kmajor(k_addr + off), idesc_s,
-                              k > 0 ? 1u : 0u);
+                    const uint32_t off = ((k >> 2) * ROWBLK + (k & 3) * 32) >> 4;
+                    umma_bf16_lh(d, qx + off, q_hi, ks + off, k_hi, idesc_s, k > 0 ? 1u : 0u);
                 }
                 if (x == last_x) umma_commit(BAR(W_KEMPTY + s));
                 umma_commit(BAR(W_SFULL + x));
@@ -721,14 +748,19 @@ __global__ __launch_bounds__(TC_THREADS, 1) void attn_prefill_wide_kernel(
             };
             auto issue_o = [&](int it, int x) -> bool {          // O of Q tile x += P V of key tile it
                 const int s = it & 1;
-                if (!mbar_wait(BAR(W_PFULL + x), (it + 1) & 1)) return false;     // P stands where S stood
+                if (!mbar_wait(BAR(W_PHALF + x), it & 1)) return false;           // P of keys 0-63 stands where S stood
                 if (x == 0 && !mbar_wait(BAR(W_VFULL + s), (it >> 1) & 1)) return false;
                 tc_fence_after();
-                const uint32_t v_addr = smem_u32(smem + W_OFF_V + s * KV_BYTES);
+                const uint32_t vs = v_lo + s * (KV_BYTES >> 4), d = tmem_base + (2 + x) * KN, pa = tmem_base + x * KN;
+                const uint32_t acc0 = it > 0 ? 1u : 0u;
 #pragma unroll
-                for (int k = 0; k < KN / 16; ++k)                // 16 keys of P = 8 columns of packed pairs
-                    umma_bf16_ta(tmem_base + (2 + x) * KN, tmem_base + x * KN + k * 8, desc_mnmajor(v_addr + k * 2048), idesc_o,
-                                 (it > 0 || k > 0) ? 1u : 0u);
+                for (int k = 0; k < KN / 32; ++k)                // 16 keys of P = 8 columns of packed pairs
+                    umma_bf16_ta_lh(d, pa + k * 8, vs + k * (2048 >> 4), v_hi, idesc_o, k > 0 ? 1u : acc0);
+                if (!mbar_wait(BAR(W_PFULL + x), (it + 1) & 1)) return false;     // and of keys 64-127
+                tc_fence_after();
+#pragma unroll
+                for (int k = KN / 32; k < KN / 16; ++k)
+                    umma_bf16_ta_lh(d, pa + k * 8, vs + k * (2048 >> 4), v_hi, idesc_o, 1u);
                 if (x == last_x) umma_commit(BAR(W_VEMPTY + s));
                 return true;
             };
@@ -783,24 +815,26 @@ __global__ __launch_bounds__(TC_THREADS, 1) void attn_prefill_wide_kernel(
             const int j0 = (tile_first + it) * KN;
             const bool full = p.window == 0 && j0 + KN - 1 <= pos_lo;       // every key visible to every row: no masks
             float v[64];
-            float raw = NEG_BIG;
-            // the row's maximum: keys 64-127, then keys 0-63, which stay in registers
+            // the row's maximum, as four chains that the scheduler can interleave: keys 64-127, then keys 0-63,
+            // which stay in registers
+            float r0 = NEG_BIG, r1 = NEG_BIG, r2 = NEG_BIG, r3 = NEG_BIG;
 #pragma unroll
             for (int c = 1; c >= 0; --c) {
                 tmem_ld64(s_addr + c * 64, v);
-                if (full) {
-#pragma unroll
-                    for (int i = 0; i < 64; ++i) raw = fmaxf(raw, v[i]);
-                } else {
+                if (!full) {
 #pragma unroll
                     for (int i = 0; i < 64; ++i) {
                         const int j = j0 + c * 64 + i;
                         const bool vis = j <= pos && (p.window == 0 || pos - j < p.window);
                         v[i] = vis ? v[i] : NEG_BIG;
-                        raw = fmaxf(raw, v[i]);
                     }
                 }
+#pragma unroll
+                for (int i = 0; i < 64; i += 4) {
+                    r0 = fmaxf(r0, v[i]); r1 = fmaxf(r1, v[i + 1]); r2 = fmaxf(r2, v[i + 2]); r3 = fmaxf(r3, v[i + 3]);
+                }
             }
+            const float raw = fmaxf(fmaxf(r0, r1), fmaxf(r2, r3));
             const float mx = raw > 0.5f * NEG_BIG ? raw * sc : NEG_BIG;
             const bool raise = mx > m + 8.0f;
             if (it == 0) {
@@ -849,6 +883,12 @@ __global__ __launch_bounds__(TC_THREADS, 1) void attn_prefill_wide_kernel(
                     pw[i] = *reinterpret_cast<uint32_t*>(&h2);
                 }
                 tmem_st32u(s_addr + c * 32, pw);
+                if (c == 0) {                                        // the product may start on keys 0-63
+                    tmem_st_wait();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(BAR(W_PHALF + x));
+                }
             }
             tmem_st_wait();
             l += rs2.x + rs2.y;
