@@ -428,6 +428,76 @@ def workload_long(a) -> int:
 REFERENCE_CLASS = "reference kernels through their C ABI; host loop restated, Rust runtime not buildable"
 
 
+def workload_ablate(a) -> int:
+    """What each kind of kernel adds to the decode step: the step is captured and timed again with one kind left out.
+
+    The logits of such a step are wrong on purpose; only its time is read.  The difference to the whole step is the
+    kind's marginal cost on the step's critical path, which is what a faster kernel could win back: it is smaller than
+    the kernel's own duration where the next kernel's prologue overlaps it (programmatic dependent launch).
+    ``rmsnorm_as_empty_kernel`` puts a kernel that does next to nothing in the norm's place: what one more
+    launch boundary costs.  One JSON line per kind.
+    """
+    import torch
+    from airun_b200 import Engine, EngineOptions, Qwen3Config
+    from airun_b200.kernels import fast, ops
+    d = dict(QWEN3_8B)
+    if a.layers:
+        d["num_hidden_layers"] = a.layers
+    cfg = Qwen3Config.from_dict(d)
+    L = cfg.num_hidden_layers
+    eng = Engine.from_config(cfg, seed=0, options=EngineOptions(
+        dtype="bfloat16", page_size=16, cache_tokens=64 * a.context + 4096, max_batch_tokens=2048, max_requests=64,
+        max_context=a.context))
+    qkv_rows = (cfg.num_attention_heads + 2 * cfg.num_key_value_heads) * cfg.head_dim
+    kinds = {(qkv_rows, cfg.hidden_size): "product_qkv",
+             (2 * cfg.intermediate_size, cfg.hidden_size): "product_gate_up",
+             (cfg.hidden_size, cfg.intermediate_size): "product_down",
+             (cfg.vocab_size, cfg.hidden_size): "product_head"}
+    kinds.setdefault((cfg.hidden_size, cfg.num_attention_heads * cfg.head_dim), "product_o")
+    skip: set = set()
+    gemm, rms, post, att = fast.gemm_tcgen05, ops.rmsnorm, ops.qkv_post, fast.attn_decode
+    src, rows, dst = (torch.zeros(8, 64, device="cuda"), torch.zeros(1, dtype=torch.int32, device="cuda"),
+                      torch.zeros(8, 64, device="cuda"))
+
+    def gemm_or_not(x, w, *args, **kw):
+        return None if kinds.get(tuple(w.shape)) in skip else gemm(x, w, *args, **kw)
+
+    def rms_or_not(*args, **kw):
+        if "rmsnorm" in skip:
+            return None
+        if "rmsnorm_as_empty_kernel" in skip:
+            return ops.gather_rows(src, rows, dst)
+        return rms(*args, **kw)
+
+    fast.gemm_tcgen05 = gemm_or_not
+    ops.rmsnorm = rms_or_not
+    ops.qkv_post = lambda *args, **kw: None if "qkv_post" in skip else post(*args, **kw)
+    fast.attn_decode = lambda *args, **kw: None if "attention" in skip else att(*args, **kw)
+    base = {}
+    try:
+        for kind in [None, "rmsnorm", "rmsnorm_as_empty_kernel", "qkv_post", "attention", *sorted(set(kinds.values()))]:
+            skip.clear()
+            if kind:
+                skip.add(kind)
+            eng.runner.graphs.clear()
+            eng.runner._warm_buckets.clear()
+            res = {}
+            for b in (8, 1, 64):
+                ms, _, _, _ = time_decode(eng, b, a.context, a.steps, a.warmup, f"ab{b}_")
+                res[f"b{b}"] = round(ms, 4)
+                if kind is None:
+                    base[b] = ms
+            line = {"workload": "ablate", "left_out": kind, "layers": L, "context": a.context, "ms_per_step": res}
+            if kind:
+                per = 1 if kind == "product_head" else L
+                line["marginal_us_each" if kind == "product_head" else "marginal_us_per_layer"] = {
+                    f"b{b}": round((base[b] - res[f"b{b}"]) * 1e3 / per, 2) for b in (8, 1, 64)}
+            print(json.dumps(line), flush=True)
+    finally:
+        fast.gemm_tcgen05, ops.rmsnorm, ops.qkv_post, fast.attn_decode = gemm, rms, post, att
+    return 0
+
+
 def reference_arm(a) -> int:
     """The same metric on the reference's own CUDA kernels (compiled unmodified for sm_100), called
     through their C entry points in the order the reference's runtime calls them
@@ -606,9 +676,10 @@ def main() -> int:
     ap.add_argument("--dtype", default="bfloat16")
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--decode-only", action="store_true", help="time the decode step only (for profiling runs)")
-    ap.add_argument("--workload", default="decode", choices=("decode", "serve", "long"),
+    ap.add_argument("--workload", default="decode", choices=("decode", "serve", "long", "ablate"),
                     help="decode: the headline line; serve: 128 requests continuously batched (Qwen3-1.7B shape); "
-                         "long: a 32,768-token prompt, then decoding alone and as 16 forks (Qwen3-32B shape)")
+                         "long: a 32,768-token prompt, then decoding alone and as 16 forks (Qwen3-32B shape); "
+                         "ablate: the decode step timed with one kind of kernel left out at a time")
     ap.add_argument("--requests", type=int, default=128, help="serve: requests")
     ap.add_argument("--new-tokens", type=int, default=None, help="serve / long: tokens decoded per request")
     ap.add_argument("--budget", type=int, default=512, help="serve: tokens per step")
@@ -627,6 +698,8 @@ def main() -> int:
     if a.workload == "long":
         a.new_tokens = a.new_tokens or 512
         return workload_long(a)
+    if a.workload == "ablate":
+        return workload_ablate(a)
 
     import torch
     from airun_b200 import Engine, EngineOptions, Qwen3Config
