@@ -246,6 +246,8 @@ class Engine:
                 if self.scheduler.accept(req, tok) is not None:
                     finished.append(req)
         self.stats.steps += 1
+        if not self.scheduler.has_work():
+            self._result_read_at = None                    # idle from here on: what follows is not a gap between steps
         if SCHED_TIMING:
             import sys
             print(f"[airun_b200] step {self.stats.steps}: {len(plan.entries)} requests, "
@@ -255,24 +257,31 @@ class Engine:
 
     # While the GPU runs a step, the host plans and lays out the next one (admission, portions, pages,
     # positions, block tables, their copy to the device): all of it but the values of the tokens being
-    # sampled right now, which it only has when it has read this step's result.  It does so only when
-    # the requests being sampled are sure to go on (not at their last token) and pages are plentiful, so
-    # that the plan cannot end or preempt anybody; if one of them ends all the same (an end token, a
-    # cancellation), the plan's batch is dropped and the step is planned again.
+    # sampled right now, which it only has when it has read this step's result.  A request whose token on
+    # its way is certainly its last (its length or the context ends there) is left out of that plan; it
+    # keeps its pages and slot until the token has been read.  The others are taken to go on; it is only
+    # done when pages are plentiful, so that the plan cannot end or preempt anybody, and if one of them
+    # ends all the same (an end token, a cancellation), the plan's batch is dropped and the step is
+    # planned again.
     _PLACEHOLDER = 0
 
     def _prepare_ahead(self, sampled: List[Request]) -> None:
         sch = self.scheduler
+        going: List[Request] = []
+        ending: List[Request] = []
         for r in sampled:
-            if r.cancelled or r.num_computed != r.num_tokens or len(r.output) + 1 >= r.max_new_tokens \
-                    or r.num_tokens + 2 > self.max_context:
+            if r.cancelled or r.num_computed != r.num_tokens:
                 return
+            last = len(r.output) + 1 >= r.max_new_tokens or r.num_tokens + 2 > self.max_context
+            (ending if last else going).append(r)
         ps = self.manager.page_size
         margin = len(sch.running) + len(sch.waiting) + self.options.max_batch_tokens // ps + 2
         if any(g.allocator.num_free < margin for g in self.manager.paged):
             return
-        for r in sampled:
+        for r in going:
             r.output.append(self._PLACEHOLDER)             # stands for the token on its way
+        for r in ending:
+            r.ending = True
         prep = None
         try:
             plan = sch.plan()
@@ -284,9 +293,11 @@ class Engine:
                 except Exception:                          # noqa: BLE001 - e.g. out of pages: the ordinary path decides
                     prep = None
         finally:
-            for r in sampled:
+            for r in going:
                 r.output.pop()
-        self._ahead = (plan, prep, list(sampled))
+            for r in ending:
+                r.ending = False
+        self._ahead = (plan, prep, list(going))
 
     def _sample(self, logits: torch.Tensor, reqs: List[Request], look_ahead: bool = False) -> List[int]:
         n = len(reqs)

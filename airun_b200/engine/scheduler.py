@@ -69,6 +69,7 @@ class Request:
     cancelled: bool = False
     preemptions: int = 0
     sampler: Optional[Sampler] = None
+    ending: bool = False             # the token being sampled right now is its last: a plan made meanwhile leaves it out
 
     def __post_init__(self):
         if self.sampler is None:
@@ -362,6 +363,8 @@ class Scheduler:
                 return None
         entries = []
         for req in running:
+            if req.ending:
+                continue
             if req.cancelled or req.num_computed < len(req.prompt) or req.num_tokens - req.num_computed != 1:
                 return None
             entries.append(PlannedEntry(req, req.num_computed, 1, True))
@@ -379,6 +382,8 @@ class Scheduler:
         for req in self.running:
             if budget <= 0 or len(entries) >= self.max_batch_reqs:
                 break
+            if req.ending:
+                continue
             want = min(req.num_tokens - req.num_computed, budget)
             n, need = self._largest_portion(req, want, planned)
             if n == 0:

@@ -461,3 +461,23 @@ def test_a_misuse_of_fork_does_not_cost_the_kept_caches():
         s.fork(live, Request("live", list(live.tokens), SamplingParams.greedy(), 2))   # the child's id is in use
     assert len(s.kept) == 1 and s.stats["prefix_evictions"] == 0
     drain(s, dev)
+
+
+def test_a_plan_made_while_a_request_samples_its_last_token_leaves_it_out():
+    """The entry point plans the next step while the GPU still runs the current one; a request whose
+    token on its way is certainly its last is marked ``ending`` meanwhile: it gets no entry, keeps its
+    pages and slot, and nothing else about the plan changes (steady decoding and the general planner)."""
+    m, s = make(pages=32, budget=16)
+    a, b, c = req("a", 3, max_new=2), req("b", 4, max_new=8), req("c", 20, max_new=8)
+    s.add(a)
+    s.add(b)
+    run(m, s, s.plan())                                  # both prompts whole, one token each
+    a.ending = True                                      # a's second token is its last
+    p = s.plan()                                         # nobody waits: the steady-decode plan
+    assert [(e.request.rid, e.count) for e in p.entries] == [("b", 1)]
+    assert a in s.running and "a" in m.requests          # a keeps what it holds until its token is read
+    s.add(c)
+    p = s.plan()                                         # somebody waits: the general planner
+    assert [(e.request.rid, e.start, e.count) for e in p.entries] == [("b", 4, 1), ("c", 0, 15)]
+    a.ending = False
+    m.check_invariants()
