@@ -678,6 +678,7 @@ def main() -> int:
     ap.add_argument("--dtype", default="bfloat16")
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--decode-only", action="store_true", help="time the decode step only (for profiling runs)")
+    ap.add_argument("--prefill-only", action="store_true", help="time the 2,048-token prompt only (for profiling runs)")
     ap.add_argument("--workload", default="decode", choices=("decode", "serve", "long", "ablate"),
                     help="decode: the headline line; serve: 128 requests continuously batched (Qwen3-1.7B shape); "
                          "long: a 32,768-token prompt, then decoding alone and as 16 forks (Qwen3-32B shape); "
@@ -719,6 +720,11 @@ def main() -> int:
         max_requests=max_batch, max_context=a.context))
     esz = 2 if a.dtype == "bfloat16" else 4
 
+    if a.prefill_only:
+        pre_ms = time_prefill(eng, 2048)
+        print(json.dumps({"prefill_only": True, "tokens": 2048, "ms": round(pre_ms, 3),
+                          "value": round(2048 / (pre_ms / 1e3), 1), "layers": L}))
+        return 0
     sampler = ClockSampler()
     sampler.start()
     with sampler.region(f"b{a.batch}"):
