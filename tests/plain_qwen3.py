@@ -8,8 +8,16 @@ paths within the reference project).
 
 The reference's model code is Rust calling CUDA kernels and has no CPU forward
 pass; neither cargo nor rustc is installed here, so it can be neither imported
-nor compiled on the CPU.  This file therefore rests on the formulas; there are
-no golden outputs of the reference's own code.
+nor compiled on the CPU.  Its CUDA kernels, however, compile unmodified for a
+B200 behind their C entry points, and this file is pinned on them: the outputs
+of the reference's own kernels for 28 cases (every part, and two whole tiny
+models run in the order its runtime calls the kernels) are stored in
+``tests/golden/reference_kernel_outputs.npz`` by
+``tests/golden/make_reference_kernel_outputs.py`` (run once on a B200), and
+``tests/test_reference_golden.py`` compares the functions below with them on
+any machine; ``tests/test_reference_kernels.py`` runs both sides on a GPU.
+Head sizes below 32 (not accepted by the reference's kernels) rest on the
+formulas alone.
 
 ``round_to`` emulates where the engine's bfloat16 path rounds activations
 (normed hidden states, q, cached k and v, the attention output, the SwiGLU
