@@ -43,6 +43,14 @@ TINY = {
                        rope_theta=1000000.0, tie_word_embeddings=False),
               page_size=16, seed=44),
 }
+# Sizes the tensor-core kernels refuse, so that the plain kernels run inside the bfloat16 engine: a width of 100
+# (not a multiple of 8: no TMA rows), an intermediate size of 180 (no fused SwiGLU tile), one layer, as many KV
+# heads as heads (groups of 1), head size 80, a prime vocabulary, tied head, page 32
+TINY["E"] = dict(cfg=dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=257, hidden_size=100,
+                          num_hidden_layers=1, num_attention_heads=3, num_key_value_heads=3, head_dim=80,
+                          intermediate_size=180, max_position_embeddings=256, rms_norm_eps=2e-5,
+                          rope_theta=20000.0, tie_word_embeddings=True),
+                 page_size=32, seed=55)
 # A again with pages of 24 tokens: a page size that is no power of two and does not divide 64
 TINY["A24"] = dict(TINY["A"], page_size=24)
 

@@ -15,7 +15,7 @@ from helpers import TINY, Replay, assert_close, bf16_noise, make_model_folder, r
 pytestmark = pytest.mark.gpu
 
 LENGTHS = {"A": [5, 17, 33, 100], "B": [70, 40, 9, 121], "C": [90, 50, 130, 37], "D": [150, 16, 129, 45],
-           "A24": [5, 17, 33, 100]}
+           "A24": [5, 17, 33, 100], "E": [41, 100, 12, 66]}
 CHUNKS = [7, 2, 13, 3, 2, 24, 5, 2, 31, 4]
 
 
