@@ -149,7 +149,7 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: int, 
 def plan_gemm(M: int, N: int, K: int, mach: Optional[Machine] = None) -> Tuple[bool, int, int]:
     """(swap, bn, ksplit) for a product of M tokens with an [N, K] weight.
 
-    Up to 128 tokens the weights are the 128-row operand (swap).  Up to 16 tokens the K range is cut
+    Up to 128 tokens the weights are the 128-row operand (swap), except for the widest products from 65 tokens on.  Up to 16 tokens the K range is cut
     until about STREAM_CTAS CTAs stream the weights (a slice keeping 10 K-steps) and the slices add
     up through a scratch in memory.  From 17 tokens on, where the partial tiles are larger, it is cut
     into up to 8 slices that run as one thread-block cluster and add up through distributed shared
@@ -161,6 +161,12 @@ def plan_gemm(M: int, N: int, K: int, mach: Optional[Machine] = None) -> Tuple[b
     Qwen3-1.7B and -8B shapes, 1 to 2048 tokens, timed inside CUDA graphs."""
     mach = mach or machine()
     kb = (K + 63) // 64
+    if 64 < M <= 128 and N >= 256 and (N + 255) // 256 >= mach.sms * 96 // B200_SMS:
+        # Above 64 tokens a swapped CTA reads as many activation bytes from the L2 cache as weight bytes, and the
+        # two together, not the weights alone, meet the limit of what the SMs take in (about 7 TB/s here): tiles
+        # of 128 tokens x 256 weight rows read half the activations per weight byte (gate/up at 128 tokens: 46
+        # against 55 us; at 64 tokens the two orientations take the same time)
+        return False, 256, 1
     if M <= 128:
         bn = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128
         tiles = (N + 127) // 128

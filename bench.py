@@ -713,8 +713,13 @@ def main() -> int:
     cfg = Qwen3Config.from_dict(d)
     L = cfg.num_hidden_layers
     pk = peaks()
-    max_batch = max(64, a.batch)
+    max_batch = a.batch if (a.decode_only or a.skip_points or a.prefill_only) else max(64, a.batch)
     cache_tokens = max_batch * a.context + 4096
+    cache_gb = cache_tokens * full_layers * 2 * cfg.num_key_value_heads * cfg.head_dim * (2 if a.dtype == "bfloat16" else 4) / 1e9
+    if cache_gb > 140.0:
+        print(f"bench.py: a cache of {cache_tokens} tokens ({cache_gb:.0f} GB) does not fit beside the weights; "
+              f"lower --batch or --context" + ("" if max_batch == a.batch else " or pass --skip-points"))
+        return 2
     eng = Engine.from_config(cfg, seed=0, options=EngineOptions(
         dtype=a.dtype, page_size=16, cache_tokens=cache_tokens, max_batch_tokens=2048,
         max_requests=max_batch, max_context=a.context))
@@ -734,7 +739,8 @@ def main() -> int:
     if a.decode_only:
         sampler.stop()
         print(json.dumps({"decode_only": True, "ms_per_step": round(ms, 4), "value": round(value, 2),
-                          "layers": L, "batch": a.batch, "context": a.context}))
+                          "layers": L, "batch": a.batch, "context": a.context, "mean_context": round(mean_ctx, 1),
+                          "hbm_frac": round(decode_bytes(cfg, L, a.batch, mean_ctx, esz) / (ms / 1e3) / 1e9 / pk["hbm_gbs"], 4)}))
         return 0
     with sampler.region("e2e"):
         e2e_ms, h2d, d2h = time_e2e(eng, a.batch, a.context, a.steps, a.warmup)

@@ -391,10 +391,13 @@ def test_product_plan_takes_every_shape_and_stays_within_the_kernel_limits():
             if ks > 1:
                 assert tiles * ks <= (STREAM_CTAS if M <= 16 else SPLIT_CTAS) and (M <= 16 or ks <= 8)
         else:
-            assert M > 128 and bn in (128, 256)
+            assert (M > 128 and bn in (128, 256)) or (64 < M <= 128 and bn == 256 and ks == 1 and (N + 255) // 256 >= 96)
             if ks > 1:
                 assert ((M + 127) // 128) * ((N + bn - 1) // bn) * ks <= 148
     assert plan_gemm(8, 24576, 4096) == (True, 16, 1) and plan_gemm(2048, 24576, 4096) == (False, 256, 1)
+    # the widest products read fewer activation bytes per weight byte as 128 x 256 tiles from 65 tokens on
+    assert plan_gemm(64, 24576, 4096) == (True, 64, 1) and plan_gemm(65, 24576, 4096) == (False, 256, 1)
+    assert plan_gemm(128, 151936, 4096) == (False, 256, 1) and plan_gemm(128, 4096, 12288)[0] is True
     # a GPU with another SM count gets plans sized for it, not for 148 SMs
     from airun_b200.kernels.fast import Machine
     small = Machine(66)
