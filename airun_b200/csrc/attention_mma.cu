@@ -780,11 +780,10 @@ AIRUN_EXPORT int airun_attn_prefill(const void* q, void* out, const void* pool, 
     const AttnParams p = make_params(q, out, pool, block_table, max_blocks, positions, req_of_token, num_reqs,
                                      num_pages, page_size, nh, nkv, scale, window, err);
     const int smem = (PM + 4 * PN) * HD * 2;
-    static bool configured = false;
-    if (!configured) {
+    static unsigned long long configured = 0;            // one bit per device
+    if (first_on_device(configured)) {
         cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return (int)e;
-        configured = true;
     }
     airun_launch(attn_prefill_kernel<false>, dim3(n_tiles, nkv), dim3(PTHREADS), smem, stream, p, (const int4*)tiles, n_tiles_dev, SharedArgs{});
     return airun_launch_status();
@@ -809,11 +808,10 @@ AIRUN_EXPORT int airun_attn_shared_prefix(const void* q, const void* pool, const
     const int groups = (n_tok + per - 1) / per;
     if (nkv > 65535 || groups > 65535) return AIRUN_ERR_ARG;
     const int smem = (PM + 4 * PN) * HD * 2;
-    static bool configured = false;
-    if (!configured) {
+    static unsigned long long configured = 0;            // one bit per device
+    if (first_on_device(configured)) {
         cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return (int)e;
-        configured = true;
     }
     SharedArgs sh{k_end_dev, n_tok, scratch, n_splits + slices, n_splits};
     airun_launch(attn_prefill_kernel<true>, dim3(slices, nkv, groups), dim3(PTHREADS), smem, stream, p,
@@ -858,15 +856,14 @@ AIRUN_EXPORT int airun_attn_decode(const void* q, void* out, const void* pool, c
     }
     const int stages = tma ? 3 : 2;
     const int smem = DW * stages * 2 * DN * HD * 2 + 16 * HD * 2 + DW * 3 * 8 + 1024;
-    static bool configured[4] = {false, false, false, false};
+    static unsigned long long configured[4] = {0, 0, 0, 0};          // one bit per device each
     const bool prefix = extra_slices > 0 || k_begin_dev != nullptr;
     const int which = (tma ? 1 : 0) + (prefix ? 2 : 0);
     auto kern = which == 0 ? attn_decode_kernel<false, false> : which == 1 ? attn_decode_kernel<true, false>
               : which == 2 ? attn_decode_kernel<false, true> : attn_decode_kernel<true, true>;
-    if (!configured[which]) {
+    if (first_on_device(configured[which])) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return (int)e;
-        configured[which] = true;
     }
     airun_launch(kern, dim3(n_splits, nkv * hgroups, n_rows), dim3(32 * DW), smem, stream, p, x, map);
     return airun_launch_status();

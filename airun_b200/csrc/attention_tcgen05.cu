@@ -996,11 +996,10 @@ AIRUN_EXPORT int airun_attn_prefill_tc(const void* q, void* out, const void* poo
     CUtensorMap map;
     const int r = kv_map_for(&map, pool, (long long)num_pages * 2 * nkv * page_size);
     if (r != AIRUN_OK) return r;
-    static bool configured = false;
-    if (!configured) {
+    static unsigned long long configured = 0;            // one bit per device
+    if (first_on_device(configured)) {
         cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
         if (e != cudaSuccess) return (int)e;
-        configured = true;
     }
     airun_launch(attn_prefill_tc_kernel<false>, dim3(n_tiles, nkv), dim3(TC_THREADS), SMEM_TOTAL, stream, p, (const int4*)tiles, map, n_tiles_dev, TcShared{});
     return airun_launch_status();
@@ -1024,11 +1023,10 @@ AIRUN_EXPORT int airun_attn_prefill_wide(const void* q, void* out, const void* p
     CUtensorMap map;
     const int r = kv_map_for(&map, pool, (long long)num_pages * 2 * nkv * page_size);
     if (r != AIRUN_OK) return r;
-    static bool configured = false;
-    if (!configured) {
+    static unsigned long long configured = 0;            // one bit per device
+    if (first_on_device(configured)) {
         cudaError_t e = cudaFuncSetAttribute(attn_prefill_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, W_SMEM_TOTAL);
         if (e != cudaSuccess) return (int)e;
-        configured = true;
     }
     airun_launch(attn_prefill_wide_kernel, dim3(n_tiles, nkv), dim3(TC_THREADS), W_SMEM_TOTAL, stream, p, (const int4*)tiles, map, n_tiles_dev);
     return airun_launch_status();
@@ -1057,11 +1055,10 @@ AIRUN_EXPORT int airun_attn_shared_prefix_tc(const void* q, const void* pool, co
     CUtensorMap map;
     const int r = kv_map_for(&map, pool, (long long)num_pages * 2 * nkv * page_size);
     if (r != AIRUN_OK) return r;
-    static bool configured = false;
-    if (!configured) {
+    static unsigned long long configured = 0;            // one bit per device
+    if (first_on_device(configured)) {
         cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
         if (e != cudaSuccess) return (int)e;
-        configured = true;
     }
     TcShared sh{k_end_dev, req_of_token, n_tok, num_reqs, scratch, n_splits + slices, n_splits};
     airun_launch(attn_prefill_tc_kernel<true>, dim3(slices, nkv, groups), dim3(TC_THREADS), SMEM_TOTAL, stream, p,

@@ -136,3 +136,13 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 }
 
 static inline int ceil_div_i(long long a, long long b) { return (int)((a + b - 1) / b); }
+
+// True the first time it is asked on the current device (``mask``: one bit per device, of one kernel).
+// cudaFuncSetAttribute holds for one device only, so each kernel is configured once on each.
+static inline bool first_on_device(unsigned long long& mask) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return true;
+    if ((mask >> dev) & 1ull) return false;
+    mask |= 1ull << dev;
+    return true;
+}

@@ -811,16 +811,6 @@ constexpr int cluster_stages(int bn, int stages) {
     return fit < 2 * stages ? fit : 2 * stages;
 }
 
-// True the first time it is asked on the current device (``mask``: one bit per device, of one kernel).
-// cudaFuncSetAttribute holds for one device only, so each kernel is configured once on each.
-static inline bool first_on_device(unsigned long long& mask) {
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return true;
-    if ((mask >> dev) & 1ull) return false;
-    mask |= 1ull << dev;
-    return true;
-}
-
 template <int BN, int STAGES, int EPI, bool SWAP>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, dim3 grid, cudaStream_t stream) {
     using L = SmemLayout<BN, STAGES>;
