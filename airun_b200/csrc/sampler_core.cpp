@@ -14,6 +14,7 @@
 #include <cstdint>
 #include <limits>
 #include <thread>
+#include <utility>
 #include <vector>
 
 #define HOST_EXPORT extern "C" __attribute__((visibility("default")))
@@ -206,3 +207,54 @@ HOST_EXPORT int airun_sample_chain_rows(ChainRow* rows, int n_rows, long long vo
     for (std::thread& t : pool) t.join();
     return 0;
 }
+
+// The same chain on each row's largest raw logits instead of the whole row (found on the device with their ids: see
+// largest_logits_kernel in sampling.cu; enough of them that the chain's cut to top_k cannot reach beyond them).  The
+// candidates, in ascending order of their ids, stand as a short row of their own, the window's tokens become
+// positions in it (a token that is no candidate cannot be picked and is left out), and chain_row runs unchanged, so
+// equal values fall as in the whole row.  ids: [n][n_cand], < 0 is padding; window: the rows' windows one after the
+// other, win_off[r] .. win_off[r + 1]; params: [n] with n_bias 0; states: [n]; out: [n] token ids.
+HOST_EXPORT int airun_sample_candidates(int n_rows, int n_cand, const int* ids, const float* vals, const long long* window,
+                                        const long long* win_off, const ChainParams* params, unsigned long long* states,
+                                        int* out, int max_threads) {
+    if (n_rows < 0 || n_cand <= 0 || !ids || !vals || !win_off || !params || !states || !out) return 1;
+    for (int r = 0; r < n_rows; ++r)
+        if (!(params[r].temperature > 0.0) || params[r].n_bias != 0 || win_off[r + 1] < win_off[r]) return 1;
+    auto one = [&](int r) {
+        std::vector<std::pair<int, float>> cand;
+        cand.reserve((size_t)n_cand);
+        for (int i = 0; i < n_cand; ++i)
+            if (ids[(size_t)r * n_cand + i] >= 0) cand.emplace_back(ids[(size_t)r * n_cand + i], vals[(size_t)r * n_cand + i]);
+        if (cand.empty()) { out[r] = 0; return; }
+        std::sort(cand.begin(), cand.end(), [](const std::pair<int, float>& a, const std::pair<int, float>& b) { return a.first < b.first; });
+        std::vector<float> logits(cand.size());
+        for (size_t i = 0; i < cand.size(); ++i) logits[i] = cand[i].second;
+        std::vector<long long> positions;
+        for (long long i = win_off[r]; i < win_off[r + 1]; ++i) {
+            const long long t = window[i];
+            size_t lo = 0, hi = cand.size();
+            while (lo < hi) {
+                const size_t mid = (lo + hi) / 2;
+                if ((long long)cand[mid].first < t) lo = mid + 1; else hi = mid;
+            }
+            if (lo < cand.size() && (long long)cand[lo].first == t) positions.push_back((long long)lo);
+        }
+        ChainRow row{logits.data(), positions.data(), (long long)positions.size(), &params[r], &states[r], -1};
+        chain_row(row, (long long)logits.size());
+        out[r] = row.out >= 0 && (size_t)row.out < cand.size() ? cand[(size_t)row.out].first : 0;
+    };
+    const int workers = std::max(1, std::min(max_threads, n_rows));
+    if (workers == 1) {
+        for (int r = 0; r < n_rows; ++r) one(r);
+        return 0;
+    }
+    std::vector<std::thread> pool;
+    pool.reserve((size_t)workers);
+    for (int w = 0; w < workers; ++w)
+        pool.emplace_back([&, w] {
+            for (int r = w; r < n_rows; r += workers) one(r);
+        });
+    for (std::thread& t : pool) t.join();
+    return 0;
+}
+

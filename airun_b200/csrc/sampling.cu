@@ -154,3 +154,95 @@ AIRUN_EXPORT int airun_sample(const float* logits, long long ld, int rows, int V
     airun_launch(sample_kernel, dim3(rows), dim3(SAMPLE_THREADS), 0, stream, logits, ld, V, temperature, uniform, out, partial);
     return airun_launch_status();
 }
+
+// ------------------------------------------------------------------ the largest logits of a row
+// For requests whose sampling chain cuts to the k largest logits anyway (top-k, the reference's default), only those
+// candidates have to travel to the host: the chain's earlier stages can only LOWER logits (repetition, presence and
+// frequency penalties over the last n tokens), so the k largest after them are among the k + n largest before.
+// Row rows[r] of logits -> its n_cand largest values with their ids, the largest first, equal values by ascending
+// id (the order the host's top-k uses, so that a tie at the cut falls the same way).  NaN never wins.
+// One block per row: every thread keeps the CAND_PER_THREAD largest of its strided share in registers as 64-bit keys
+// (orderable value bits, then the inverted id), the 4,096 keys are sorted in shared memory (bitonic), the first
+// n_cand leave.  If a thread's share held more than CAND_PER_THREAD of the row's n_cand largest, one of them may be
+// missing: the row's flag says so and the host takes the whole row instead (with ids strided over 1,024 threads the
+// chance is about one in ten thousand for 105 of 151,936).
+#define CAND_THREADS 1024
+#define CAND_PER_THREAD 4
+#define CAND_MAX 512
+
+__device__ __forceinline__ unsigned long long cand_key(float v, int id) {
+    if (v != v) return 0ull;                                     // NaN: no candidate at all
+    unsigned u = __float_as_uint(v);
+    u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);              // ascending order of the floats
+    return ((unsigned long long)u << 32) | (unsigned long long)(0xFFFFFFFFu - (unsigned)id);
+}
+
+__global__ __launch_bounds__(CAND_THREADS) void largest_logits_kernel(
+    const float* __restrict__ logits, long long ld, int V, const int32_t* __restrict__ rows, int n_cand,
+    int32_t* __restrict__ out_ids, float* __restrict__ out_vals, int32_t* __restrict__ out_flags) {
+    pdl_trigger();
+    extern __shared__ unsigned long long s_keys[];               // CAND_THREADS * CAND_PER_THREAD
+    __shared__ int s_flag;
+    pdl_wait();
+    const int r = blockIdx.x;
+    const float* row = logits + (size_t)rows[r] * ld;
+    unsigned long long best[CAND_PER_THREAD];                     // descending
+#pragma unroll
+    for (int i = 0; i < CAND_PER_THREAD; ++i) best[i] = 0ull;
+    int seen = 0;
+    for (int j = threadIdx.x; j < V; j += CAND_THREADS, ++seen) {
+        unsigned long long k = cand_key(row[j], j);
+        if (k > best[CAND_PER_THREAD - 1]) {
+#pragma unroll
+            for (int i = 0; i < CAND_PER_THREAD; ++i) {          // insertion into the sorted few
+                if (k > best[i]) { const unsigned long long t = best[i]; best[i] = k; k = t; }
+            }
+        }
+    }
+    if (threadIdx.x == 0) s_flag = 0;
+#pragma unroll
+    for (int i = 0; i < CAND_PER_THREAD; ++i) s_keys[threadIdx.x * CAND_PER_THREAD + i] = best[i];
+    __syncthreads();
+    constexpr int N = CAND_THREADS * CAND_PER_THREAD;
+    for (int k = 2; k <= N; k <<= 1) {
+        for (int j = k >> 1; j > 0; j >>= 1) {
+            for (int i = threadIdx.x; i < N; i += CAND_THREADS) {
+                const int ixj = i ^ j;
+                if (ixj > i) {
+                    const unsigned long long a = s_keys[i], b = s_keys[ixj];
+                    const bool descending = (i & k) == 0;
+                    if (descending ? a < b : a > b) { s_keys[i] = b; s_keys[ixj] = a; }
+                }
+            }
+            __syncthreads();
+        }
+    }
+    // a thread that kept as many as it can and whose last is among the row's n_cand largest may have dropped one that is too
+    const unsigned long long cut = s_keys[n_cand - 1];
+    if (seen > CAND_PER_THREAD && best[CAND_PER_THREAD - 1] >= cut && cut != 0ull) s_flag = 1;
+    __syncthreads();
+    for (int i = threadIdx.x; i < n_cand; i += CAND_THREADS) {
+        const unsigned long long k = s_keys[i];
+        const int id = (int)(0xFFFFFFFFu - (unsigned)(k & 0xFFFFFFFFull));
+        const bool real = k != 0ull && id >= 0 && id < V;
+        out_ids[(size_t)r * n_cand + i] = real ? id : -1;
+        out_vals[(size_t)r * n_cand + i] = real ? row[id] : -INFINITY;
+    }
+    if (threadIdx.x == 0) out_flags[r] = s_flag;
+}
+
+// rows: [n] int32 row indices into logits (on the device); out_ids / out_vals: [n][n_cand]; out_flags: [n].
+AIRUN_EXPORT int airun_largest_logits(const float* logits, long long ld, int V, const int32_t* rows, int n, int n_cand,
+                                      int32_t* out_ids, float* out_vals, int32_t* out_flags, cudaStream_t stream) {
+    if (n < 0 || V <= 0 || ld < V || n_cand < 1 || n_cand > CAND_MAX || !rows || !out_ids || !out_vals || !out_flags) return AIRUN_ERR_ARG;
+    if (n == 0) return AIRUN_OK;
+    if (n > 65535) return AIRUN_ERR_ARG;
+    constexpr int SMEM = CAND_THREADS * CAND_PER_THREAD * 8;
+    static unsigned long long configured = 0;                    // one bit per device
+    if (first_on_device(configured)) {
+        cudaError_t e = cudaFuncSetAttribute(largest_logits_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        if (e != cudaSuccess) return (int)e;
+    }
+    airun_launch(largest_logits_kernel, dim3(n), dim3(CAND_THREADS), SMEM, stream, logits, ld, V, rows, n_cand, out_ids, out_vals, out_flags);
+    return airun_launch_status();
+}

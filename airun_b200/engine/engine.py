@@ -12,6 +12,7 @@ milliseconds, stop reason) are ``GenerationStats`` (runtime.rs:5130-5165).
 from __future__ import annotations
 
 import itertools
+import os
 import time
 from dataclasses import dataclass
 from typing import Hashable, List, Optional, Sequence, Union
@@ -22,7 +23,7 @@ import torch
 from ..cache.manager import CacheManager, CacheStorage
 from ..config.base import ModelConfig, architecture_name, lookup_architecture, read_config_json
 from ..kernels import ops
-from ..sampling.sampler import SamplingParams, sample_rows
+from ..sampling.sampler import SamplingParams, sample_candidates, sample_rows
 from ..weights.loader import open_model_folder
 from .scheduler import FinishReason, Request, Scheduler
 from .step import StepEntry, StepRunner
@@ -109,6 +110,9 @@ class Engine:
         self.stats = GenerationStats()
         self._ahead = None        # (requests, prepared step): the next decode step, laid out while this one runs
         self._host_rows = None    # buffers for the logits rows the host samples
+        self._cand_bufs = None    # buffers for the largest logits of the rows whose chain cuts to them anyway
+        # AIRUN_NARROW_ROWS=0: every row the host samples travels whole (the plain way; tests compare the two)
+        self._narrow_rows = os.environ.get("AIRUN_NARROW_ROWS", "1") != "0"
         self._result_read_at = None
 
     # ------------------------------------------------------------ construction
@@ -312,7 +316,12 @@ class Engine:
         ops.sample(logits, self._picked_dev, self._small_dev[:R], self._small_dev[R:])
         self._picked_dev[R:R + 1].copy_(self.runner.err)
         self._picked_host.copy_(self._picked_dev, non_blocking=True)
-        host_rows = [i for i, r in enumerate(reqs) if not r.params.device_ok]
+        # Rows the device kernel cannot pick alone: those whose chain cuts to its k largest logits anyway send only
+        # their largest logits to the host (found on the device), the others their whole row.
+        need = [0 if r.params.device_ok else r.params.candidates_needed(ops.LARGEST_LOGITS_MAX) for r in reqs]
+        cand_rows = [i for i, r in enumerate(reqs) if not r.params.device_ok and need[i] > 0 and self._narrow_rows]
+        host_rows = [i for i, r in enumerate(reqs) if not r.params.device_ok and i not in set(cand_rows)]
+        cands = self._candidates_to_host(logits, cand_rows, max(need[i] for i in cand_rows)) if cand_rows else None
         rows_host = self._rows_to_host(logits, host_rows) if host_rows else None
         if look_ahead and not host_rows and self._ahead is None:
             self._prepare_ahead(reqs)                      # the GPU is busy: plan and lay out the next step meanwhile
@@ -323,11 +332,50 @@ class Engine:
             self.runner.err.zero_()
             raise RuntimeError("a kernel reported: " + ops.describe_device_error(int(picked[R])))
         out = [int(picked[i]) for i in range(n)]
+        if cand_rows:
+            ids, vals, flags = cands
+            unsure = [i for j, i in enumerate(cand_rows) if flags[j]]
+            if unsure:                                      # the kernel could not vouch for these lists: whole rows
+                more = self._rows_to_host(logits, unsure)
+                torch.cuda.current_stream().synchronize()
+                for i, tok in zip(unsure, sample_rows([reqs[i].sampler for i in unsure], more, [reqs[i].tokens for i in unsure])):
+                    out[i] = tok
+            sure = [j for j, i in enumerate(cand_rows) if not flags[j]]
+            if sure:
+                rq = [reqs[cand_rows[j]] for j in sure]
+                windows = [r.token_slice(max(0, r.num_tokens - r.params.repeat_last_n), min(r.num_tokens, r.params.repeat_last_n))
+                           if r.params.penalizing else [] for r in rq]
+                for j, tok in zip(sure, sample_candidates([r.sampler for r in rq], ids[sure], vals[sure], windows)):
+                    out[cand_rows[j]] = tok
         if host_rows:
             picked_host = sample_rows([reqs[i].sampler for i in host_rows], rows_host, [reqs[i].tokens for i in host_rows])
             for i, tok in zip(host_rows, picked_host):
                 out[i] = tok
         return out
+
+    def _candidates_to_host(self, logits: torch.Tensor, rows: List[int], n_cand: int):
+        """The ``n_cand`` largest logits of each of ``rows`` with their ids, found by the engine's own kernel and
+        copied to pinned memory (queued; the caller synchronises the stream): ids, values, flags as numpy views."""
+        n, cap = len(rows), self.runner.R_max
+        if self._cand_bufs is None:
+            C = ops.LARGEST_LOGITS_MAX
+            self._cand_bufs = (torch.empty(cap, dtype=torch.int32, pin_memory=True),
+                               torch.empty(cap, dtype=torch.int32, device=self.device),
+                               torch.empty(cap * C, dtype=torch.int32, device=self.device),
+                               torch.empty(cap * C, dtype=torch.float32, device=self.device),
+                               torch.empty(cap, dtype=torch.int32, device=self.device),
+                               torch.empty(cap * C, dtype=torch.int32, pin_memory=True),
+                               torch.empty(cap * C, dtype=torch.float32, pin_memory=True),
+                               torch.empty(cap, dtype=torch.int32, pin_memory=True))
+        idx_host, idx_dev, ids_dev, vals_dev, flags_dev, ids_host, vals_host, flags_host = self._cand_bufs
+        idx_host[:n] = torch.as_tensor(rows, dtype=torch.int32)
+        idx_dev[:n].copy_(idx_host[:n], non_blocking=True)
+        ops.largest_logits(logits, idx_dev, n, n_cand, ids_dev, vals_dev, flags_dev)
+        ids_host[:n * n_cand].copy_(ids_dev[:n * n_cand], non_blocking=True)
+        vals_host[:n * n_cand].copy_(vals_dev[:n * n_cand], non_blocking=True)
+        flags_host[:n].copy_(flags_dev[:n], non_blocking=True)
+        return (ids_host[:n * n_cand].numpy().reshape(n, n_cand), vals_host[:n * n_cand].numpy().reshape(n, n_cand),
+                flags_host[:n].numpy())
 
     def _rows_to_host(self, logits: torch.Tensor, rows: List[int]) -> np.ndarray:
         """The logits of the rows the host samples: gathered by the engine's own kernel into one buffer

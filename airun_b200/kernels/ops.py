@@ -296,6 +296,27 @@ def sample(logits: torch.Tensor, out: torch.Tensor, temperature: Optional[torch.
 
 _SAMPLE_SCRATCH = {}
 
+LARGEST_LOGITS_MAX = 512
+
+
+def largest_logits(logits: torch.Tensor, rows: torch.Tensor, n: int, n_cand: int, out_ids: torch.Tensor,
+                   out_vals: torch.Tensor, out_flags: torch.Tensor) -> None:
+    """For the ``n`` rows ``rows[i]`` of ``logits``: out_ids[i], out_vals[i] = the ``n_cand`` largest logits with
+    their ids, the largest first, equal values by ascending id (-1 / -inf beyond the row's size); out_flags[i] != 0
+    when the kernel cannot vouch for the list (the caller then takes the whole row)."""
+    _cuda(logits, rows, out_ids, out_vals, out_flags)
+    _need(logits.dtype == torch.float32 and logits.dim() == 2 and logits.stride(1) == 1, "logits must be float32 [R, V]")
+    _need(1 <= n_cand <= LARGEST_LOGITS_MAX, f"1 to {LARGEST_LOGITS_MAX} candidates a row")
+    _need(rows.dtype == torch.int32 and rows.numel() >= n and rows.is_contiguous(), "rows must be int32 [n]")
+    _need(out_ids.dtype == torch.int32 and out_ids.is_contiguous() and out_ids.numel() >= n * n_cand
+          and out_vals.dtype == torch.float32 and out_vals.is_contiguous() and out_vals.numel() >= n * n_cand
+          and out_flags.dtype == torch.int32 and out_flags.numel() >= n, "candidate outputs are [n, n_cand] and [n]")
+    R, V = logits.shape
+    f = _fn("sampling", "airun_largest_logits",
+            [c_void_p, c_longlong, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
+    _check(f(_p(logits), logits.stride(0) if R > 1 else max(V, logits.stride(0)), V, _p(rows), int(n), int(n_cand),
+             _p(out_ids), _p(out_vals), _p(out_flags), _stream()), "largest_logits")
+
 
 def describe_device_error(bits: int) -> str:
     return "; ".join(msg for b, msg in DEV_ERR_BITS.items() if bits & b) or f"unknown error bits {bits}"

@@ -89,6 +89,21 @@ class SamplingParams:
         return (self.temperature <= 0.0 and not self.logit_bias and not self.penalizing
                 and self.dry_multiplier <= 0.0 and self.logprobs is None)
 
+    def candidates_needed(self, limit: int) -> int:
+        """How many of a row's largest RAW logits (with their ids) are enough to run this request's chain exactly, or 0
+        when the chain needs the whole row.  The chain cuts to the ``top_k`` largest after stages that can only lower
+        logits, of at most ``repeat_last_n`` distinct tokens (the penalties): the k largest afterwards are among the
+        k + n largest before.  A bias may raise any token, top-n-sigma and mirostat read the whole row's statistics,
+        log-probabilities its normaliser, and DRY's reach is the whole history: those take the whole row."""
+        if self.logit_bias or self.top_n_sigma > 0.0 or self.dry_multiplier > 0.0 or self.mirostat != 0 \
+                or self.logprobs is not None:
+            return 0
+        k = 1 if self.temperature <= 0.0 else self.top_k
+        if k <= 0:
+            return 0
+        n = k + (self.repeat_last_n if self.penalizing else 0) + 1
+        return n if n <= limit else 0
+
     @property
     def device_ok(self) -> bool:
         """True when the device kernel alone gives this request's draw."""
@@ -228,6 +243,7 @@ class Sampler:
         self.rng = XorShift64(params.seed)
         self.mu = 2.0 * params.mirostat_tau           # sample.rs:259-262
         self.probs: List[TokenProbs] = []             # one per sampled token when params.logprobs is set
+        self._packed = None                           # the parameters as a record of the native core (packed_params)
 
     def _draw(self, ids: np.ndarray, probs: np.ndarray) -> int:
         """Index into ``ids`` / ``probs`` (descending) of the inverse-CDF draw (sample.rs:478-485)."""
@@ -279,6 +295,14 @@ class Sampler:
 
     def next_uniform(self) -> float:
         return self.rng.next_f32()
+
+    def packed_params(self) -> np.ndarray:
+        """This request's parameters as one ChainParams record of the native core (made once)."""
+        if self._packed is None:
+            p = self.params
+            self._packed = np.array([(p.temperature, p.top_p, p.min_p, p.repeat_penalty, p.presence_penalty, p.frequency_penalty,
+                                      p.top_k, 1 if p.penalizing else 0, 0, 0, 0)], dtype=_CAND_PARAMS)[0]
+        return self._packed
 
     def sample(self, logits: np.ndarray, history: Sequence[int]) -> int:
         """The full chain on the host for one row; ``logits`` (float32 [V]) is modified in place."""
@@ -496,6 +520,77 @@ def sample_rows(samplers: Sequence["Sampler"], rows: np.ndarray, histories: Sequ
     for r, before in raw.items():
         samplers[r].probs.append(token_probs(before, int(out[r]), samplers[r].params.logprobs))
     return [int(t) for t in out]
+
+
+_CAND_PARAMS = np.dtype([("temperature", "f8"), ("top_p", "f8"), ("min_p", "f8"), ("repeat", "f8"), ("presence", "f8"),
+                         ("frequency", "f8"), ("top_k", "i4"), ("penalize", "i4"), ("n_bias", "i4"), ("bias_ids", "u8"),
+                         ("bias_vals", "u8")], align=True)            # ChainParams of csrc/sampler_core.cpp
+_CAND_FN = None
+
+
+def _sample_candidates_native(samplers: Sequence["Sampler"], cand_ids: np.ndarray, cand_vals: np.ndarray,
+                              windows: Sequence[Sequence[int]]) -> List[int]:
+    """``sample_candidates`` for rows with the usual parameters, whole in the native core
+    (``airun_sample_candidates`` of csrc/sampler_core.cpp), rows side by side on threads."""
+    global _CAND_FN
+    if _CAND_FN is None:
+        from ..csrc import build
+        assert _CAND_PARAMS.itemsize == ctypes.sizeof(_ChainParams)
+        f = build.load("sampler_core").airun_sample_candidates
+        f.restype = ctypes.c_int
+        f.argtypes = [ctypes.c_int, ctypes.c_int] + [ctypes.c_void_p] * 7 + [ctypes.c_int]
+        _CAND_FN = f
+    n, C = cand_ids.shape
+    ids = np.ascontiguousarray(cand_ids, dtype=np.int32)
+    vals = np.ascontiguousarray(cand_vals, dtype=np.float32)
+    params = np.empty(n, dtype=_CAND_PARAMS)
+    states = np.empty(n, dtype=np.uint64)
+    win_off = np.zeros(n + 1, dtype=np.int64)
+    for r, s in enumerate(samplers):
+        params[r] = s.packed_params()
+        states[r] = s.rng.state
+        win_off[r + 1] = win_off[r] + len(windows[r])
+    window = np.fromiter((t for w in windows for t in w), dtype=np.int64, count=int(win_off[n]))
+    out = np.empty(n, dtype=np.int32)
+    if _CAND_FN(n, C, ids.ctypes.data, vals.ctypes.data, window.ctypes.data, win_off.ctypes.data, params.ctypes.data,
+                states.ctypes.data, out.ctypes.data, _TOPK_THREADS) != 0:
+        raise ValueError("the native candidate chain refused its arguments")
+    for r, s in enumerate(samplers):
+        s.rng.state = int(states[r])
+    return [int(t) for t in out]
+
+
+def sample_candidates(samplers: Sequence["Sampler"], cand_ids: np.ndarray, cand_vals: np.ndarray,
+                      windows: Sequence[Sequence[int]]) -> List[int]:
+    """One token for every row from its largest raw logits instead of the whole row: ``cand_ids[r]`` / ``cand_vals[r]``
+    are at least ``samplers[r].params.candidates_needed`` of them (any order; ids < 0 are padding), ``windows[r]`` the
+    request's last ``repeat_last_n`` tokens.  The candidates, in ascending order of their ids, stand as a short row of
+    their own, the window's tokens become positions in it (a token that is no candidate cannot be picked and is left
+    out), and the row goes through ``sample_rows`` unchanged: same stages, same arithmetic, same use of the
+    generator; equal values fall as in the whole row because positions keep the order of the ids."""
+    n, C = cand_ids.shape
+    if n and all(usual_chain(s.params, C) and not s.params.logit_bias for s in samplers):
+        return _sample_candidates_native(samplers, cand_ids, cand_vals, windows)
+    rows = np.full((n, C), -np.inf, dtype=np.float32)
+    maps = []
+    hist = []
+    for r in range(n):
+        ids = cand_ids[r]
+        keep = np.nonzero(ids >= 0)[0]
+        order = keep[np.argsort(ids[keep], kind="stable")]
+        idmap = ids[order].astype(np.int64)
+        rows[r, :len(order)] = cand_vals[r][order]
+        maps.append(idmap)
+        w = np.asarray(windows[r], dtype=np.int64)
+        if w.size and idmap.size:
+            pos = np.searchsorted(idmap, w)
+            pos_ok = (pos < idmap.size)
+            pos_ok[pos_ok] &= idmap[pos[pos_ok]] == w[pos_ok]
+            hist.append(pos[pos_ok].tolist())
+        else:
+            hist.append([])
+    picked = sample_rows(samplers, rows, hist)
+    return [int(maps[r][t]) if 0 <= t < len(maps[r]) else 0 for r, t in enumerate(picked)]
 
 
 def _typical(ids: np.ndarray, probs: np.ndarray, typical_p: float):

@@ -282,6 +282,27 @@ def check_sampling(dev) -> Tuple[float, float]:
     return bad, 0.5
 
 
+def check_largest_logits(dev) -> Tuple[float, float]:
+    """A row's largest logits with their ids, the largest first, equal values by ascending id."""
+    from .kernels import ops
+    V, n_cand = 151936, 105
+    g = torch.Generator().manual_seed(7)
+    logits = torch.round(torch.randn(2, V, generator=g) * 3.0)                   # few distinct values: ties at the cut
+    ids = torch.zeros(2 * n_cand, dtype=torch.int32, device=dev)
+    vals = torch.zeros(2 * n_cand, dtype=torch.float32, device=dev)
+    flags = torch.zeros(2, dtype=torch.int32, device=dev)
+    ops.largest_logits(logits.to(dev), torch.tensor([1, 0], dtype=torch.int32, device=dev), 2, n_cand, ids, vals, flags)
+    bad = 0.0
+    for j, r in enumerate((1, 0)):
+        if int(flags[j].item()):
+            continue                                                         # the caller would take the whole row
+        row = logits[r].double()
+        order = torch.argsort(-row, stable=True)[:n_cand]                   # value down; a stable sort keeps ids ascending
+        if ids[j * n_cand:(j + 1) * n_cand].cpu().tolist() != order.tolist():
+            bad = 1.0
+    return bad, 0.5
+
+
 CHECKS: List[Tuple[str, Callable]] = [
     ("embedding gather", check_embedding),
     ("rmsnorm + residual add", check_rmsnorm),
@@ -295,6 +316,7 @@ CHECKS: List[Tuple[str, Callable]] = [
     ("attention, tcgen05 prefill + split-K decode", check_attention_tensor_core),
     ("attention, mma.sync prefill + decode", check_attention_mma),
     ("sampling", check_sampling),
+    ("largest logits of a row", check_largest_logits),
 ]
 
 

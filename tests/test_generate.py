@@ -72,6 +72,28 @@ def test_temperature_sampling_is_seeded_and_independent_of_the_batch(folders):
     assert c.token_ids == d.token_ids and len(c.token_ids) == 8
 
 
+def test_rows_sent_to_the_host_as_their_largest_logits_give_the_tokens_of_whole_rows(folders, monkeypatch):
+    """A request whose chain cuts to its k largest logits travels to the host as k + n + 1 candidates found on the
+    device; ``AIRUN_NARROW_ROWS=0`` sends whole rows instead.  Both must generate the same tokens: default parameters
+    (top-k 40 with the repetition penalty over 64 tokens), greedy with penalties, a row beside device-sampled rows."""
+    import airun_b200
+    name = "B"
+    cfg, _ = P.read_model_folder(folders[name])
+    prompts = [random_tokens(n, cfg["vocab_size"], 190 + i) for i, n in enumerate((40, 12, 9, 30))]
+    params = [airun_b200.SamplingParams(seed=7), airun_b200.SamplingParams(temperature=0.0, top_k=0, repeat_penalty=1.3, seed=1),
+              airun_b200.SamplingParams.greedy(), airun_b200.SamplingParams(seed=9, top_k=5, min_p=0.0, top_p=0.8, xtc_probability=0.3)]
+    out = {}
+    for narrow in ("1", "0"):
+        monkeypatch.setenv("AIRUN_NARROW_ROWS", narrow)
+        eng = airun_b200.Engine.from_folder(folders[name], dtype="float32", page_size=8, cache_tokens=2048,
+                                            max_batch_tokens=64, max_requests=4)
+        assert eng._narrow_rows == (narrow == "1")
+        res = eng.generate(prompts, [airun_b200.SamplingParams(**{**p.__dict__}) for p in params], max_new_tokens=24)
+        out[narrow] = [r.token_ids for r in res]
+        assert (eng._cand_bufs is not None) == (narrow == "1")
+    assert out["1"] == out["0"] and all(len(t) == 24 for t in out["1"])
+
+
 def test_end_token_stops_and_is_not_emitted(folders):
     import airun_b200
     cfg, W = P.read_model_folder(folders["B"])

@@ -579,6 +579,46 @@ def test_sample_kernel_first_maximum_and_temperature():
         assert lo - 1e-4 <= float(u[r]) <= float(cdf[i]) + 1e-4
 
 
+@pytest.mark.parametrize("V,n_cand", [(151936, 105), (300, 41), (20000, 512), (5000, 8), (37, 64)])
+def test_largest_logits_kernel_against_a_sort(V, n_cand):
+    """The rows' n largest logits with their ids, the largest first and equal values by ascending id, as
+    ``np.lexsort`` gives them: random rows, a row of few distinct values (ties everywhere, also at the cut), a row
+    with NaN and infinities, a row whose largest values all fall to one thread's share (the kernel must either list
+    them or raise the row's flag), and rows picked out of order."""
+    from airun_b200.kernels import ops
+    rng = np.random.default_rng(V + n_cand)
+    R = 6
+    rows = (rng.standard_normal((R, V)) * 4).astype(np.float32)
+    rows[1] = np.round(rows[1])
+    rows[2, rng.integers(0, V, max(1, V // 50))] = np.nan
+    rows[2, rng.integers(0, V, 3)] = np.inf
+    rows[2, rng.integers(0, V, 3)] = -np.inf
+    rows[3, ::1024] += 100.0                                   # one thread's share holds all the largest values
+    pick = np.array([4, 1, 2, 3, 0, 1], dtype=np.int32)
+    logits = torch.from_numpy(rows).to(DEV)
+    ids = torch.full((len(pick) * n_cand,), -7, dtype=torch.int32, device=DEV)
+    vals = torch.zeros(len(pick) * n_cand, dtype=torch.float32, device=DEV)
+    flags = torch.full((len(pick),), -1, dtype=torch.int32, device=DEV)
+    ops.largest_logits(logits, torch.from_numpy(pick).to(DEV), len(pick), n_cand, ids, vals, flags)
+    ids, vals, flags = ids.cpu().numpy().reshape(len(pick), n_cand), vals.cpu().numpy().reshape(len(pick), n_cand), flags.cpu().numpy()
+    flagged = 0
+    for j, r in enumerate(pick):
+        real = np.nonzero(~np.isnan(rows[r]))[0]                # NaN never wins: it is not listed at all
+        order = real[np.lexsort((real, -rows[r][real]))]
+        want = order[:n_cand]
+        if flags[j]:                                            # the kernel cannot vouch for this list: the caller takes the row
+            flagged += 1
+            assert V > 4 * 1024 and n_cand > 4                  # never where a thread's share is at most what it keeps
+            assert r == 3 or n_cand > 256                       # at the engine's sizes only the planted row
+            continue
+        got = ids[j][:len(want)]
+        assert np.array_equal(got, want), (V, n_cand, r)
+        assert np.array_equal(vals[j][:len(want)], rows[r][want])
+        assert (ids[j][len(real):] == -1).all() and np.isneginf(vals[j][len(real):]).all()      # beyond the row's values
+    if V > 4 * 1024 and n_cand > 4:
+        assert flagged >= 1                                     # 149 values of one thread's share cannot all be listed
+
+
 def test_sample_kernel_distribution():
     from airun_b200.kernels import ops
     probs = torch.tensor([0.4, 0.3, 0.2, 0.1])

@@ -408,3 +408,39 @@ def test_native_chain_is_left_to_python_for_everything_else():
     for kw in (dict(temperature=0.0), dict(top_k=0), dict(top_k=V), dict(top_k=5000), dict(typical_p=0.9), dict(top_n_sigma=1.0),
                dict(dry_multiplier=0.5), dict(dynatemp_range=0.2), dict(xtc_probability=0.1), dict(mirostat=2), dict(logprobs=0)):
         assert not usual_chain(SamplingParams(**kw), V), kw
+
+
+def test_the_chain_on_a_rows_largest_logits_picks_what_the_whole_row_picks():
+    """Requests whose chain cuts to the k largest logits send only their k + n + 1 largest raw logits to the host (n:
+    the tokens the penalties may lower).  ``sample_candidates`` must pick the token the whole row gives and leave the
+    generator where the whole row leaves it: rows with many equal values, histories that hit the largest logits,
+    every stage behind the cut (typical, min-p, top-p, XTC, dynamic temperature), greedy with penalties."""
+    from airun_b200.sampling.sampler import Sampler, SamplingParams, sample_candidates, sample_rows
+    rng = np.random.default_rng(0)
+    V = 5000
+    for trial in range(1, 240):
+        p = SamplingParams(temperature=float(rng.choice([0.0, 0.7, 1.3])), top_k=int(rng.choice([1, 5, 40, 100])),
+                           top_p=float(rng.choice([1.0, 0.9, 0.5])), min_p=float(rng.choice([0.0, 0.05, 0.3])),
+                           repeat_penalty=float(rng.choice([1.0, 1.1, 1.5])), presence_penalty=float(rng.choice([0, 0.5])),
+                           frequency_penalty=float(rng.choice([0, 0.2])), repeat_last_n=int(rng.choice([0, 16, 64])),
+                           seed=trial, typical_p=float(rng.choice([1.0, 0.8])), xtc_probability=float(rng.choice([0.0, 0.5])),
+                           dynatemp_range=float(rng.choice([0.0, 0.3])))
+        need = p.candidates_needed(512)
+        assert need == (1 if p.temperature <= 0 else p.top_k) + (p.repeat_last_n if p.penalizing else 0) + 1
+        row = (rng.standard_normal(V) * 3).astype(np.float32)
+        if trial % 3 == 0:
+            row = np.round(row)                                   # many equal values, also at the cut
+        hist = rng.integers(0, V, 200).tolist()
+        hist[-30:] = rng.choice(np.argsort(-row, kind="stable")[:60], 30).tolist()     # the penalties hit the top
+        a, b = Sampler(p), Sampler(p)
+        want = sample_rows([a], row.copy().reshape(1, -1), [hist])[0]
+        order = np.lexsort((np.arange(V), -row))[:need]           # what the device kernel sends: value down, id up
+        order = order[rng.permutation(need)]                      # in any order
+        window = hist[-p.repeat_last_n:] if p.penalizing else []
+        got = sample_candidates([b], order.astype(np.int32).reshape(1, -1), row[order].reshape(1, -1), [window])[0]
+        assert got == want and a.rng.state == b.rng.state, (trial, p)
+    # what needs the whole row says so
+    assert SamplingParams(logit_bias=((3, 1.0),)).candidates_needed(512) == 0
+    assert SamplingParams(top_k=0).candidates_needed(512) == 0 and SamplingParams(mirostat=2).candidates_needed(512) == 0
+    assert SamplingParams(logprobs=0).candidates_needed(512) == 0 and SamplingParams(top_k=500).candidates_needed(512) == 0
+    assert SamplingParams().candidates_needed(512) == 40 + 64 + 1
