@@ -243,7 +243,8 @@ HOST_EXPORT int airun_sample_candidates(int n_rows, int n_cand, const int* ids, 
         chain_row(row, (long long)logits.size());
         out[r] = row.out >= 0 && (size_t)row.out < cand.size() ? cand[(size_t)row.out].first : 0;
     };
-    const int workers = std::max(1, std::min(max_threads, n_rows));
+    // a row takes a few microseconds, starting a thread tens: threads only from 16 rows each on
+    const int workers = std::max(1, std::min(max_threads, n_rows / 16));
     if (workers == 1) {
         for (int r = 0; r < n_rows; ++r) one(r);
         return 0;

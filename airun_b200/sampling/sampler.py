@@ -25,6 +25,7 @@ this chain.
 from __future__ import annotations
 
 import ctypes
+import itertools
 import math
 import time
 from dataclasses import dataclass
@@ -550,7 +551,7 @@ def _sample_candidates_native(samplers: Sequence["Sampler"], cand_ids: np.ndarra
         params[r] = s.packed_params()
         states[r] = s.rng.state
         win_off[r + 1] = win_off[r] + len(windows[r])
-    window = np.fromiter((t for w in windows for t in w), dtype=np.int64, count=int(win_off[n]))
+    window = np.fromiter(itertools.chain.from_iterable(windows), dtype=np.int64, count=int(win_off[n]))
     out = np.empty(n, dtype=np.int32)
     if _CAND_FN(n, C, ids.ctypes.data, vals.ctypes.data, window.ctypes.data, win_off.ctypes.data, params.ctypes.data,
                 states.ctypes.data, out.ctypes.data, _TOPK_THREADS) != 0:

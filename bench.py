@@ -249,14 +249,16 @@ def check_step(eng, rids, tokens, start):
     return err / max(scale, 1e-30)
 
 
-def time_e2e(eng, batch, context, steps, warmup):
+def time_e2e(eng, batch, context, steps, warmup, sampled=False):
     """The same decode through the Python entry point: requests live in the scheduler, every step
     copies the step's inputs from pinned host memory and reads the sampled tokens back.  Median of
-    three repeats of ``steps`` steps by the host clock."""
+    three repeats of ``steps`` steps by the host clock.  ``sampled``: the requests sample with the
+    reference's default parameters (temperature 0.8, top-k 40, top-p 0.95, min-p 0.05, repetition penalty 1.1
+    over 64 tokens) instead of greedily, which brings the host's sampling chain into every step."""
     import torch
     from airun_b200 import SamplingParams
     from airun_b200.engine.scheduler import Request
-    rids = [f"e{i}" for i in range(batch)]
+    rids = [f"{'s' if sampled else 'e'}{i}" for i in range(batch)]
     reps = 3
     start = context - reps * steps - warmup - 1
     fill_contexts(eng, rids, start - 1)
@@ -264,7 +266,7 @@ def time_e2e(eng, batch, context, steps, warmup):
     reqs = []
     for rid in rids:
         prompt = torch.randint(0, eng.config.vocab_size, (start,), generator=g).tolist()
-        r = Request(rid, prompt, SamplingParams.greedy(), reps * steps + warmup + 8)
+        r = Request(rid, prompt, SamplingParams(seed=len(reqs) + 1) if sampled else SamplingParams.greedy(), reps * steps + warmup + 8)
         r.num_computed = start - 1                # its cache stands one token short of the prompt
         eng.scheduler.running.append(r)
         reqs.append(r)
@@ -744,6 +746,8 @@ def main() -> int:
         return 0
     with sampler.region("e2e"):
         e2e_ms, h2d, d2h = time_e2e(eng, a.batch, a.context, a.steps, a.warmup)
+        e2e_gap = getattr(time_e2e, "host_gap_ms", 0.0)
+        e2e_sampled_ms, _, _ = time_e2e(eng, a.batch, a.context, a.steps, a.warmup, sampled=True)
     points, detail = {}, {}
     if not a.skip_points:
         for b in (1, 64):
@@ -778,7 +782,9 @@ def main() -> int:
                    "peaks": pk["source"]},
         "e2e": {"value": round(a.batch / (e2e_ms / 1e3), 2), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "host_gap_ms_per_step": round(getattr(time_e2e, "host_gap_ms", 0.0), 4)},
+                "host_gap_ms_per_step": round(e2e_gap, 4),
+                "sampled_with_reference_defaults": {"value": round(a.batch / (e2e_sampled_ms / 1e3), 2),
+                                                    "ms_per_step": round(e2e_sampled_ms, 4)}},
         "gpu_launches": launches,
         "prefill": pre,
         "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
