@@ -8,7 +8,8 @@ A step is one decode step of a batch of requests whose contexts stand at
 random keys and values (synthetic data) so that no time goes to prefilling them.
 Prints ONE JSON line: ``value`` is the device-timed decode rate of the step
 function, ``e2e`` the rate through the Python entry point (scheduler, sampling,
-host tokens in and out), ``prefill`` a 2,048-token prompt in one step,
+host tokens in and out; ``sampled_with_reference_defaults`` inside it: the same with the reference's default
+sampling parameters instead of greedy picks), ``prefill`` a 2,048-token prompt in one step,
 ``roofline`` the bytes a decode step must read over its time, ``points`` the
 decode rate at batch 1 and 64.  ``--workload serve`` and ``--workload long`` run
 two further workloads end to end (continuous batching of 128 requests on the
