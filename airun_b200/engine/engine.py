@@ -309,7 +309,7 @@ class Engine:
         host = self._small_host.numpy()
         for i, r in enumerate(reqs):
             p = r.params
-            dev = p.device_ok
+            dev = r.sampler.device_ok
             host[i] = p.temperature if (dev and p.temperature > 0.0) else 0.0
             host[R + i] = r.sampler.next_uniform() if (dev and p.temperature > 0.0) else 0.0
         self._small_dev.copy_(self._small_host, non_blocking=True)
@@ -318,10 +318,17 @@ class Engine:
         self._picked_host.copy_(self._picked_dev, non_blocking=True)
         # Rows the device kernel cannot pick alone: those whose chain cuts to its k largest logits anyway send only
         # their largest logits to the host (found on the device), the others their whole row.
-        need = [0 if r.params.device_ok else r.params.candidates_needed(ops.LARGEST_LOGITS_MAX) for r in reqs]
-        cand_rows = [i for i, r in enumerate(reqs) if not r.params.device_ok and need[i] > 0 and self._narrow_rows]
-        host_rows = [i for i, r in enumerate(reqs) if not r.params.device_ok and i not in set(cand_rows)]
-        cands = self._candidates_to_host(logits, cand_rows, max(need[i] for i in cand_rows)) if cand_rows else None
+        cand_rows, host_rows, n_cand = [], [], 0
+        for i, r in enumerate(reqs):
+            if r.sampler.device_ok:
+                continue
+            need = r.sampler.candidates_needed if self._narrow_rows else 0
+            if need > 0:
+                cand_rows.append(i)
+                n_cand = max(n_cand, need)
+            else:
+                host_rows.append(i)
+        cands = self._candidates_to_host(logits, cand_rows, n_cand) if cand_rows else None
         rows_host = self._rows_to_host(logits, host_rows) if host_rows else None
         if look_ahead and not host_rows and self._ahead is None:
             self._prepare_ahead(reqs)                      # the GPU is busy: plan and lay out the next step meanwhile

@@ -245,6 +245,9 @@ class Sampler:
         self.mu = 2.0 * params.mirostat_tau           # sample.rs:259-262
         self.probs: List[TokenProbs] = []             # one per sampled token when params.logprobs is set
         self._packed = None                           # the parameters as a record of the native core (packed_params)
+        # what the engine asks every step, worked out once (the parameters of a live request do not change)
+        self.device_ok = params.device_ok
+        self.candidates_needed = params.candidates_needed(512)
 
     def _draw(self, ids: np.ndarray, probs: np.ndarray) -> int:
         """Index into ``ids`` / ``probs`` (descending) of the inverse-CDF draw (sample.rs:478-485)."""
