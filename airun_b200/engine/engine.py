@@ -113,6 +113,7 @@ class Engine:
         self._cand_bufs = None    # buffers for the largest logits of the rows whose chain cuts to them anyway
         # AIRUN_NARROW_ROWS=0: every row the host samples travels whole (the plain way; tests compare the two)
         self._narrow_rows = os.environ.get("AIRUN_NARROW_ROWS", "1") != "0"
+        self._distrust_candidates = False   # tests: treat every list of largest logits as one the kernel could not vouch for
         self._result_read_at = None
 
     # ------------------------------------------------------------ construction
@@ -341,13 +342,13 @@ class Engine:
         out = [int(picked[i]) for i in range(n)]
         if cand_rows:
             ids, vals, flags = cands
-            unsure = [i for j, i in enumerate(cand_rows) if flags[j]]
+            unsure = [i for j, i in enumerate(cand_rows) if flags[j] or self._distrust_candidates]
             if unsure:                                      # the kernel could not vouch for these lists: whole rows
                 more = self._rows_to_host(logits, unsure)
                 torch.cuda.current_stream().synchronize()
                 for i, tok in zip(unsure, sample_rows([reqs[i].sampler for i in unsure], more, [reqs[i].tokens for i in unsure])):
                     out[i] = tok
-            sure = [j for j, i in enumerate(cand_rows) if not flags[j]]
+            sure = [j for j, i in enumerate(cand_rows) if not (flags[j] or self._distrust_candidates)]
             if sure:
                 rq = [reqs[cand_rows[j]] for j in sure]
                 windows = [r.token_slice(max(0, r.num_tokens - r.params.repeat_last_n), min(r.num_tokens, r.params.repeat_last_n))

@@ -92,6 +92,13 @@ def test_rows_sent_to_the_host_as_their_largest_logits_give_the_tokens_of_whole_
         out[narrow] = [r.token_ids for r in res]
         assert (eng._cand_bufs is not None) == (narrow == "1")
     assert out["1"] == out["0"] and all(len(t) == 24 for t in out["1"])
+    # the way out when the kernel cannot vouch for a list (a second copy, of the whole row) gives the same tokens too
+    monkeypatch.setenv("AIRUN_NARROW_ROWS", "1")
+    eng = airun_b200.Engine.from_folder(folders[name], dtype="float32", page_size=8, cache_tokens=2048,
+                                        max_batch_tokens=64, max_requests=4)
+    eng._distrust_candidates = True
+    res = eng.generate(prompts, [airun_b200.SamplingParams(**{**p.__dict__}) for p in params], max_new_tokens=24)
+    assert [r.token_ids for r in res] == out["0"]
 
 
 def test_end_token_stops_and_is_not_emitted(folders):
